@@ -1,0 +1,146 @@
+/* C ABI of libsana_b200: the B200 (sm_100a) kernels behind the Sana Linear-DiT block.
+ *
+ * Upstream (NVlabs/Sana) has no C/FFI plugin interface for this path; its seams are the
+ * Python modules LiteLA / GLUMBConv / SanaMSBlock.  Each entry point below names the
+ * upstream Python statement(s) it replaces.  The torch-side glue (sana_b200/ops.py) is the
+ * only caller: it passes raw device pointers, sizes in elements, and the current CUDA
+ * stream.
+ *
+ * Conventions
+ *  - every pointer is a device pointer unless stated otherwise; the caller owns all memory
+ *    (inputs, outputs, workspaces); unless an entry point says otherwise the library
+ *    allocates nothing on the device and keeps no device state;
+ *  - all tensors are token-major ("channels last"): a [T, C] activation is T rows of C
+ *    contiguous elements with a row stride given in ELEMENTS (ld*);
+ *  - `stream` is a cudaStream_t passed as void*; every call is asynchronous on it;
+ *  - return value: 0 = ok; <0 = invalid argument detected on the host before any launch;
+ *    >0 = a CUDA runtime error code.  sana_last_error() returns a message for the last
+ *    non-zero status on the calling thread.  Nothing throws or exits across this boundary.
+ */
+#ifndef SANA_B200_H_
+#define SANA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SANA_OK 0
+#define SANA_ERR_INVALID (-1)
+#define SANA_ERR_UNSUPPORTED (-2)
+#define SANA_ERR_DRIVER (-3)
+
+/* element types of activations / weights */
+#define SANA_F32 0
+#define SANA_BF16 1
+
+/* library ABI version (bumped when a signature changes) */
+int sana_abi_version(void);
+/* message for the last failing call on this thread ("" if none) */
+const char* sana_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * adaLN-single LayerNorm + modulate:  z = LN(x) * (1 + scale_b) + shift_b
+ *   scale_b[c] = table[scale_row, c] + t[b, scale_row*C + c]   (same for shift_row)
+ * Replaces `t2i_modulate(self.norm1(x), shift_msa, scale_msa)` and the norm2 twin,
+ * diffusion/model/nets/sana_multi_scale.py:148-155 with sana_blocks.py:44-45; LayerNorm is
+ * affine-free with biased variance and eps (1e-6 in the block).
+ *   x, z  [B*N, C] (row stride C);  table [6, C];  t [B, 6*C];  all of `dtype`.
+ * Statistics and the modulation are computed in fp32, one rounding on store.
+ * C must be a multiple of 8 and one row at most 16 KiB (8192 bf16 / 4096 fp32 channels).
+ */
+int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
+                     int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * ReLU linear attention, state reduction:
+ *   state[b, h, i, j] = sum_n v1[b, n, h, i] * relu(k[b, n, h, j]),  v1 = [v ; 1]
+ * i in [0, 33), j in [0, 32): 32 value rows plus the "ones" row that upstream creates with
+ * F.pad(v, (0,0,0,1), value=1).  Replaces `vk = torch.matmul(v_pad, relu(k))` (and the
+ * .float() casts before it), LiteLA.attn_matmul, diffusion/model/nets/sana_blocks.py:246-256.
+ *   k, v   [B*N, *] rows of H*32 contiguous channels (head-major), row stride ld elements
+ *   state  [B, H, 33, 32] fp32
+ *   workspace: sana_la_state_workspace_bytes(B, N, H) bytes, 256-byte aligned; holds
+ *   per-chunk partial states that a second launch adds in a fixed order (bit-reproducible).
+ * Head dimension is fixed at 32 (upstream linear_head_dim).  Accumulation is fp32.
+ */
+int64_t sana_la_state_workspace_bytes(int64_t B, int64_t N, int64_t H);
+int sana_la_state(const void* k, const void* v, int64_t ld, float* state, void* workspace,
+                  int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * ReLU linear attention, apply + normalise:
+ *   o[b, n, h, i] = (sum_j state[b,h,i,j] relu(q[b,n,h,j])) / (sum_j state[b,h,32,j] relu(q[b,n,h,j]) + eps)
+ * Replaces `out = torch.matmul(vk, relu(q)); out[:, :, :-1] / (out[:, :, -1:] + eps)` and the
+ * cast back to the model dtype, sana_blocks.py:257-263,286, written token-major so that no
+ * transpose precedes the output projection (sana_blocks.py:288-289).
+ *   q [B*N, *] (row stride ldq), out [B*N, *] (row stride ldo), both of `dtype`.
+ */
+int sana_la_apply(const void* q, int64_t ldq, const float* state, void* out, int64_t ldo, int64_t B,
+                  int64_t N, int64_t H, float eps, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * 3x3 depthwise conv + bias + SiLU-GLU on channels-last rows:
+ *   w[y, x, c]  = b[c] + sum_{dy,dx} K[c, dy, dx] * u[y+dy-1, x+dx-1, c]   (zero outside a frame)
+ *   out[y, x, c] = w[y, x, c] * silu(w[y, x, hid + c]),  c in [0, hid)
+ * Replaces `depth_conv` -> `chunk(2, dim=1)` -> `glu_act` -> `a * g`,
+ * GLUMBConv._apply_spatial, diffusion/model/nets/basic_modules.py:164-167 (per image, or
+ * per frame when HW has three entries, :187-195).
+ *   u        [rows, W, 2*hid]  local image rows; global row index = row0 + local row; a frame
+ *            is H consecutive global rows (rows of different frames never mix)
+ *   halo_top [W, 2*hid] = global row row0-1, halo_bot = global row row0+rows; either may be
+ *            NULL when that row lies in another frame (or for a single-GPU call with
+ *            row0 % H == 0 and (row0+rows) % H == 0)
+ *   weight   [2*hid, 3, 3] (upstream's [2*hid, 1, 3, 3]), bias [2*hid] or NULL
+ *   out      [rows, W, hid]
+ * hid must be a multiple of 8.  fp32 accumulation, one rounding on store.
+ */
+int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
+                    const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
+                    int64_t hid, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Dense projection with fused epilogue:  out = epilogue(A @ Wt^T)
+ *   A   [M, K] row stride lda;  Wt [N, K] row stride ldw (torch Linear / 1x1 Conv2d weight
+ *   layout);  out [M, N] row stride ldo.
+ * Epilogue, in this order, all in fp32 with one rounding on store:
+ *   v = acc;  v += bias[n];  act;  v *= gate_b[n];  v += residual[m, n]
+ *   act: 0 none, 1 SiLU, 2 ReLU on columns n < relu_cols
+ *   gate_b[n] = gate_table[gate_row, n] + gate_t[m / rows_per_batch, gate_row*N + n]
+ * Replaces self.qkv / self.proj (sana_blocks.py:268,289), q_linear / kv_linear / proj of the
+ * cross-attention (sana_blocks.py:74-75,95), inverted_conv (+ in-place SiLU) and point_conv
+ * (basic_modules.py:163,167), and the gate-multiply + residual adds of
+ * SanaMSBlock.forward (sana_multi_scale.py:151-155).
+ * bf16: TMA-fed tcgen05 kernel, fp32 accumulation in tensor memory; requires 16-byte aligned
+ * base pointers and lda, ldw, ldo, ldr multiples of 8.  f32: SIMT kernel (parity path).
+ */
+typedef struct sana_gemm_epilogue {
+  const void* bias;       /* [N] or NULL */
+  int32_t act;            /* 0 none, 1 SiLU, 2 ReLU on columns < relu_cols */
+  int32_t gate_row;       /* row of the [6, N] table (2 = gate_msa, 5 = gate_mlp) */
+  int64_t relu_cols;
+  const void* gate_table; /* [6, N] or NULL */
+  const void* gate_t;     /* [B, 6*N]; required when gate_table != NULL */
+  int64_t rows_per_batch; /* tokens per batch element (row m belongs to b = m / rows_per_batch) */
+  const void* residual;   /* [M, N] row stride ldr, or NULL */
+  int64_t ldr;
+} sana_gemm_epilogue;
+
+int sana_gemm(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
+              int64_t N, int64_t K, const sana_gemm_epilogue* ep, int dtype, void* stream);
+
+/* Same contract as sana_gemm but always the SIMT kernel (any dtype).  Not used by the
+ * modules for bf16; it exists so tests can cross-check the tensor-core kernel on the device. */
+int sana_gemm_simt(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
+                   int64_t N, int64_t K, const sana_gemm_epilogue* ep, int dtype, void* stream);
+
+/* Soft-error word of the tensor-core GEMM: its bounded waits record a code here instead of
+ * spinning forever.  Returns 0 when no wait ever timed out on the current device since the
+ * last call (host-synchronising: use in tests / after a failure, not per step). */
+int sana_gemm_take_device_status(int* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SANA_B200_H_ */

@@ -1,0 +1,311 @@
+"""CPU restatement of the Sana Linear-DiT block arithmetic.  TEST INFRASTRUCTURE ONLY.
+
+This file is the checker the CUDA path is compared with.  Only the test-suite, the
+smoke entry and the CPU-baseline / reference legs of the benchmark may import it; the
+product package never does, and fails loudly when its CUDA library is missing.
+
+Every function follows one upstream function (path inside NVlabs/Sana given in its
+docstring) op by op and dtype by dtype, so that running it in bf16 rounds at exactly the
+places upstream rounds and running it in fp32/fp64 gives the "golden" result.  Parity of
+this restatement is PINNED: ``tests/golden/make_golden.py`` runs the unmodified upstream
+modules (imported on CPU) on seeded inputs and commits inputs/outputs as fixtures;
+``tests/test_oracle_golden.py`` requires this file to reproduce those outputs bit for bit
+(fp32 and bf16) on the same CPU kernels.
+
+Parameters are passed as plain ``dict[str, Tensor]`` using upstream's state-dict keys:
+
+    scale_shift_table                      [6, C]
+    attn.qkv.weight                        [3C, C]      (rows q | k | v, head-major, 32/head)
+    attn.proj.weight / attn.proj.bias      [C, C] / [C]
+    cross_attn.q_linear.weight / .bias     [C, C] / [C]
+    cross_attn.kv_linear.weight / .bias    [2C, C] / [2C]   (rows k | v)
+    cross_attn.proj.weight / .bias         [C, C] / [C]
+    mlp.inverted_conv.conv.weight / .bias  [2*hid, C, 1, 1] / [2*hid]
+    mlp.depth_conv.conv.weight / .bias     [2*hid, 1, 3, 3] / [2*hid]
+    mlp.point_conv.conv.weight             [C, hid, 1, 1]
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+Params = Dict[str, torch.Tensor]
+
+LN_EPS = 1e-6  # nn.LayerNorm(hidden, elementwise_affine=False, eps=1e-6), sana_multi_scale.py:76,111
+BLOCK_LA_EPS = 1e-8  # LiteLA(..., eps=1e-8) as built by the block, sana_multi_scale.py:90
+PAD_VAL = 1  # LiteLA.PAD_VAL, sana_blocks.py:214
+
+
+def sub(params: Params, prefix: str) -> Params:
+    """Sub-dictionary of ``params`` under ``prefix.`` with the prefix removed."""
+    p = prefix + "."
+    return {k[len(p):]: v for k, v in params.items() if k.startswith(p)}
+
+
+def t2i_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """diffusion/model/nets/sana_blocks.py:44-45"""
+    return x * (1 + scale) + shift
+
+
+def layer_norm(x: torch.Tensor) -> torch.Tensor:
+    """norm1 / norm2 of the block: affine-free LayerNorm over C, eps 1e-6
+    (diffusion/model/nets/sana_multi_scale.py:76,111)."""
+    return F.layer_norm(x, (x.shape[-1],), None, None, LN_EPS)
+
+
+def lite_la_attn_matmul(q, k, v, eps: float, fp32_attention: bool = True) -> torch.Tensor:
+    """LiteLA.attn_matmul, diffusion/model/nets/sana_blocks.py:245-263.
+
+    q, v: [B, h, d, N]; k: [B, h, N, d].  Returns fp32 (or input dtype for fp32/fp64 inputs)
+    [B, h, d, N]."""
+    q = F.relu(q)
+    k = F.relu(k)
+    if fp32_attention:
+        q, k, v = q.float(), k.float(), v.float()
+    v = F.pad(v, (0, 0, 0, 1), mode="constant", value=PAD_VAL)
+    vk = torch.matmul(v, k)
+    out = torch.matmul(vk, q)
+    if out.dtype in (torch.float16, torch.bfloat16):
+        out = out.float()
+    return out[:, :, :-1] / (out[:, :, -1:] + eps)
+
+
+def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, eps: float = 1e-15,
+                    fp32_attention: bool = True, keep_dtype: bool = False) -> torch.Tensor:
+    """LiteLA.forward, diffusion/model/nets/sana_blocks.py:265-291 (qk_norm off, no rotary).
+
+    ``p`` holds ``qkv.weight`` (+ optional ``qkv.bias``), ``proj.weight``, ``proj.bias``.
+    ``keep_dtype`` runs the fp32_attention region in the input dtype instead of fp32 - used
+    only to produce fp64 golden values (upstream's ``.float()`` would truncate them)."""
+    B, N, C = x.shape
+    heads = heads or C // dim
+    hd = C // heads
+    qkv = F.linear(x, p["qkv.weight"], p.get("qkv.bias")).reshape(B, N, 3, C)
+    q, k, v = qkv.unbind(2)
+    dtype = q.dtype
+    q = q.transpose(-1, -2).reshape(B, C // hd, hd, N)
+    k = k.transpose(-1, -2).reshape(B, C // hd, hd, N)
+    v = v.transpose(-1, -2).reshape(B, C // hd, hd, N)
+    out = lite_la_attn_matmul(q, k.transpose(-1, -2), v, eps, fp32_attention and not keep_dtype).to(dtype)
+    out = out.view(B, C, N).permute(0, 2, 1)
+    return F.linear(out, p["proj.weight"], p["proj.bias"])
+
+
+def lite_la_state(k_relu: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Token-major restatement of the first product of attn_matmul (sana_blocks.py:255-256):
+    k_relu, v: [B, N, h, d] -> state [B, h, d+1, d] with state[b,h,i,j] = sum_n v1[n,i] k[n,j],
+    v1 = [v ; 1].  Used to check the sharded (sequence-parallel) sum: a state over a token
+    range is a plain sum, so shards add."""
+    ones = torch.ones_like(v[..., :1])
+    v1 = torch.cat([v, ones], dim=-1)
+    return torch.einsum("bnhi,bnhj->bhij", v1, k_relu)
+
+
+def lite_la_apply(q_relu: torch.Tensor, state: torch.Tensor, eps: float) -> torch.Tensor:
+    """Second product + normalisation (sana_blocks.py:257-261), token-major:
+    q_relu [B, N, h, d], state [B, h, d+1, d] -> [B, N, h, d]."""
+    out = torch.einsum("bhij,bnhj->bnhi", state, q_relu)
+    return out[..., :-1] / (out[..., -1:] + eps)
+
+
+def glumbconv_forward(x, p: Params, HW: Sequence[int]) -> torch.Tensor:
+    """GLUMBConv.forward / _apply_spatial, diffusion/model/nets/basic_modules.py:161-199.
+
+    ``HW`` = (H, W) or (T, H, W); with three entries the depthwise conv runs per frame.
+    In-place SiLU after the 1x1 expand (act.py:31), separate SiLU for the gate."""
+    B, N, C = x.shape
+    if len(HW) == 2:
+        H, W = HW
+        BT = B
+    elif len(HW) == 3:
+        T, H, W = HW
+        BT = B * T
+    else:
+        raise ValueError("HW must have 2 or 3 entries")
+    x = x.reshape(BT, H, W, C).permute(0, 3, 1, 2)
+    x = F.conv2d(x, p["inverted_conv.conv.weight"], p.get("inverted_conv.conv.bias"))
+    x = F.silu(x)
+    wd = p["depth_conv.conv.weight"]
+    x = F.conv2d(x, wd, p.get("depth_conv.conv.bias"), padding=wd.shape[-1] // 2, groups=wd.shape[0])
+    a, g = torch.chunk(x, 2, dim=1)
+    g = F.silu(g)
+    x = F.conv2d(a * g, p["point_conv.conv.weight"], p.get("point_conv.conv.bias"))
+    Cout = x.shape[1]
+    if len(HW) == 3:
+        return x.reshape(BT, Cout, H * W).permute(0, 2, 1).reshape(B, N, Cout)
+    return x.reshape(B, Cout, N).permute(0, 2, 1)
+
+
+def cross_attention_forward(x, cond, p: Params, num_heads: int, mask=None) -> torch.Tensor:
+    """MultiHeadCrossAttention.forward, SDPA branch (no xformers),
+    diffusion/model/nets/sana_blocks.py:69-98.  ``mask``: None or [B, L] of 0/1."""
+    B, N, C = x.shape
+    hd = C // num_heads
+    q = F.linear(x, p["q_linear.weight"], p["q_linear.bias"])
+    kv = F.linear(cond, p["kv_linear.weight"], p["kv_linear.bias"]).view(B, -1, 2, C)
+    k, v = kv.unbind(2)
+    q = q.view(B, -1, num_heads, hd).transpose(1, 2)
+    k = k.view(B, -1, num_heads, hd).transpose(1, 2)
+    v = v.view(B, -1, num_heads, hd).transpose(1, 2)
+    if mask is not None and mask.ndim == 2:
+        mask = (1 - mask.to(q.dtype)) * -10000.0
+        mask = mask[:, None, None].repeat(1, num_heads, 1, 1)
+    o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=0.0, is_causal=False)
+    o = o.transpose(1, 2).reshape(B, -1, C)
+    return F.linear(o, p["proj.weight"], p["proj.bias"])
+
+
+def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int], mask=None,
+                          linear_head_dim: int = 32, fp32_attention: bool = True,
+                          keep_dtype: bool = False, return_branches: bool = False):
+    """SanaMSBlock.forward with attn_type="linear", ffn_type="glumbconv", drop_path 0,
+    diffusion/model/nets/sana_multi_scale.py:145-157.
+
+    x [B, N, C], y [B, L, C], t [B, 6C].  With ``return_branches`` also returns the outputs
+    of LiteLA.forward and GLUMBConv.forward (before gate and residual), the two places where
+    parity is asserted besides the block output."""
+    B, N, C = x.shape
+    mod = (p["scale_shift_table"][None] + t.reshape(B, 6, -1)).chunk(6, dim=1)
+    shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
+    a = lite_la_forward(t2i_modulate(layer_norm(x), shift_msa, scale_msa), sub(p, "attn"),
+                        heads=C // linear_head_dim, eps=BLOCK_LA_EPS,
+                        fp32_attention=fp32_attention, keep_dtype=keep_dtype)
+    x = x + gate_msa * a
+    x = x + cross_attention_forward(x, y, sub(p, "cross_attn"), num_heads, mask)
+    f = glumbconv_forward(t2i_modulate(layer_norm(x), shift_mlp, scale_mlp), sub(p, "mlp"), HW)
+    x = x + gate_mlp * f
+    if return_branches:
+        return x, a, f
+    return x
+
+
+def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: int = 10000) -> torch.Tensor:
+    """TimestepEmbedder.timestep_embedding, diffusion/model/nets/sana_blocks.py:980-999."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(0, half, dtype=torch.float32) / half)
+    args = t[:, None].float() * freqs[None]
+    emb = torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+    if dim % 2:
+        emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
+    return emb
+
+
+def adaln_single(t_scalar: torch.Tensor, p: Params, dtype=torch.float32) -> torch.Tensor:
+    """t -> [B, 6C]: TimestepEmbedder.forward (sana_blocks.py:1001-1004) followed by
+    t_block = SiLU -> Linear(C, 6C) (sana_multi_scale.py:240).  Keys: ``mlp.0.*``,
+    ``mlp.2.*`` (embedder) and ``t_block.1.*``."""
+    e = timestep_embedding(t_scalar, p["mlp.0.weight"].shape[1]).to(dtype)
+    e = F.linear(e, p["mlp.0.weight"], p["mlp.0.bias"])
+    e = F.linear(F.silu(e), p["mlp.2.weight"], p["mlp.2.bias"])
+    return F.linear(F.silu(e), p["t_block.1.weight"], p["t_block.1.bias"])
+
+
+# ----------------------------------------------------------------------------------------
+# Sequence-parallel restatement (no upstream counterpart for LiteLA: the state is a plain
+# sum over tokens, so shards add; the depthwise conv needs one row of halo inside a frame).
+# The partition rule mirrors the contiguous-rank layout of upstream's context-parallel
+# groups (diffusion/distributed/context_parallel/config.py:155-178) but splits image rows,
+# not frames.
+# ----------------------------------------------------------------------------------------
+def row_partition(total_rows: int, world: int) -> Sequence[Tuple[int, int]]:
+    """Contiguous, balanced [start, end) row ranges; the first ``total_rows % world`` ranks
+    get one extra row."""
+    base, extra = divmod(total_rows, world)
+    out, s = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((s, s + n))
+        s += n
+    return out
+
+
+def depthwise_glu_rows(u_rows, halo_top, halo_bot, wd, bd, row0: int, H: int) -> torch.Tensor:
+    """3x3 depthwise conv + bias + SiLU-GLU on a contiguous range of image rows.
+
+    u_rows [R, W, 2*hid] are global rows ``row0 .. row0+R`` of a stack of frames that are
+    ``H`` rows tall; halo_top / halo_bot [W, 2*hid] are global rows ``row0-1`` / ``row0+R``
+    (ignored when that row lies in another frame, where upstream zero-pads).  Same math as
+    basic_modules.py:164-167 applied per frame."""
+    R, W, C2 = u_rows.shape
+    out = torch.empty(R, W, C2 // 2, dtype=u_rows.dtype)
+    zero = torch.zeros(W, C2, dtype=u_rows.dtype)
+    for r in range(R):
+        g = row0 + r
+        fr = g % H
+        up = zero if fr == 0 else (u_rows[r - 1] if r > 0 else halo_top)
+        dn = zero if fr == H - 1 else (u_rows[r + 1] if r < R - 1 else halo_bot)
+        tile = torch.stack([up, u_rows[r], dn], 0).permute(2, 0, 1)[None]  # [1, C2, 3, W]
+        w = F.conv2d(F.pad(tile, (1, 1, 0, 0)), wd, bd, groups=C2)  # [1, C2, 1, W]
+        a, gt = torch.chunk(w[0, :, 0], 2, dim=0)
+        out[r] = (a * F.silu(gt)).permute(1, 0)
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# NVFP4 fake quantisation (E2M1 values, one E4M3 scale per 16 contiguous elements of the
+# contraction dimension, one fp32 scale per tensor).  Upstream holds no FP4 arithmetic of
+# its own (it calls Transformer Engine, which is not vendored), so nothing upstream pins
+# these numbers: parity of this section is UNPINNED; the block-level check is "upstream
+# block run on the dequantised tensors".
+# ----------------------------------------------------------------------------------------
+E2M1_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+E2M1_MAX = 6.0
+E4M3_MAX = 448.0
+
+
+def _round_to_e2m1(x: torch.Tensor) -> torch.Tensor:
+    """Round-to-nearest-even onto the E2M1 grid {0,.5,1,1.5,2,3,4,6} with sign, saturating."""
+    s = torch.sign(x)
+    a = x.abs().clamp(max=E2M1_MAX)
+    # midpoints: ties go to the value with even mantissa (0, 1, 2, 4 | .5->0? see below)
+    # grid index by thresholds; ties resolved to even code (codes 0..7; even codes 0,2,4,6)
+    grid = E2M1_VALUES.to(x.dtype)
+    mids = (grid[:-1] + grid[1:]) / 2  # .25 .75 1.25 1.75 2.5 3.5 5
+    idx = torch.zeros_like(a, dtype=torch.long)
+    for i in range(7):
+        lower_code_even = (i % 2 == 0)
+        if lower_code_even:
+            idx = idx + (a > mids[i]).long()  # tie stays at the lower (even) code
+        else:
+            idx = idx + (a >= mids[i]).long()  # tie goes up to the even code
+    return s * grid[idx]
+
+
+def _round_to_e4m3(x: torch.Tensor) -> torch.Tensor:
+    """Positive values -> nearest E4M3 (fn variant, max 448) via torch's float8_e4m3fn."""
+    return x.clamp(max=E4M3_MAX).to(torch.float8_e4m3fn).to(torch.float32)
+
+
+def nvfp4_quantize(x: torch.Tensor):
+    """Quantise along the last dimension (length a multiple of 16).
+
+    Returns (codes_value fp32 on the E2M1 grid, block_scale fp32 holding E4M3 values
+    [..., K/16], tensor_scale python float) with
+    ``dequant = codes_value * block_scale[..., None] * tensor_scale``.
+
+    tensor_scale = amax / (6 * 448); block scale = E4M3(block_amax / (6 * tensor_scale))."""
+    xf = x.float()
+    K = xf.shape[-1]
+    assert K % 16 == 0
+    amax = xf.abs().max().clamp(min=1e-30)
+    ts = (amax / (E2M1_MAX * E4M3_MAX)).item()
+    blocks = xf.reshape(*xf.shape[:-1], K // 16, 16)
+    bamax = blocks.abs().amax(dim=-1)
+    bs = _round_to_e4m3(bamax / (E2M1_MAX * ts))
+    denom = (bs * ts)[..., None]
+    scaled = torch.where(denom > 0, blocks / denom, torch.zeros_like(blocks))
+    vals = _round_to_e2m1(scaled)
+    return vals.reshape(xf.shape), bs, ts
+
+
+def nvfp4_dequantize(vals: torch.Tensor, bs: torch.Tensor, ts: float) -> torch.Tensor:
+    K = vals.shape[-1]
+    return (vals.reshape(*vals.shape[:-1], K // 16, 16) * (bs * ts)[..., None]).reshape(vals.shape)
+
+
+def nvfp4_fake_quant(x: torch.Tensor) -> torch.Tensor:
+    """dequant(quant(x)) along the last dimension, returned in x's dtype."""
+    return nvfp4_dequantize(*nvfp4_quantize(x)).to(x.dtype)

@@ -1,0 +1,12 @@
+"""sana_b200: the Sana Linear-DiT block (LiteLA + GLUMBConv inside SanaMSBlock) on B200.
+
+CUDA kernels for sm_100a behind a C ABI (include/sana_b200.h, built into
+sana_b200/lib/libsana_b200.so by ``python -m sana_b200.build``) and drop-in PyTorch modules
+that keep upstream's signatures.  There is no CPU path.
+"""
+from . import ops, sharding, synthetic  # noqa: F401
+from ._lib import SanaLibraryError, load as load_library  # noqa: F401
+from .modules import ConvLayer, GLUMBConv, LiteLA, MultiHeadCrossAttention, SanaMSBlock  # noqa: F401
+
+__all__ = ["LiteLA", "GLUMBConv", "ConvLayer", "MultiHeadCrossAttention", "SanaMSBlock", "ops", "sharding",
+           "synthetic", "load_library", "SanaLibraryError"]

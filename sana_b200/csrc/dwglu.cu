@@ -1,0 +1,294 @@
+// 3x3 depthwise conv + bias + SiLU-GLU over channels-last image rows (the Mix-FFN middle).
+//
+// bf16 kernel: a CTA owns a tile of 16 columns x 64 value channels (+ their 64 gate
+// channels) and marches down a segment of rows.  Each input row tile (with a one-column
+// halo, zero-filled at image edges) is staged once in shared memory by 16-byte cp.async
+// through an 8-deep ring; a lane owns 8 contiguous channels of one role (value or gate),
+// reads the three horizontal neighbours with 128-bit shared loads and feeds three rolling
+// fp32 accumulators (output rows y-1, y, y+1) with packed f32x2 FMAs, so every input
+// element is read from global memory once per CTA and from shared memory three times.
+// Value and gate lanes swap half of their channels by warp shuffle for the GLU.
+#include "common.cuh"
+
+namespace sana {
+
+constexpr int DW_TW = 16;      // output columns per CTA
+constexpr int DW_CV = 8;       // 8-channel vectors per role per CTA
+constexpr int DW_STAGES = 8;   // ring depth (input rows in flight)
+constexpr int DW_THREADS = 256;
+constexpr int DW_ROW_CHUNKS = (DW_TW + 2) * 2 * DW_CV;  // 16-byte chunks per staged row = 288
+constexpr int DW_STAGE_BYTES = DW_ROW_CHUNKS * 16;
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
+  const int sz = valid ? 16 : 0;  // src-size 0 => 16 bytes of zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+struct DwArgs {
+  const __nv_bfloat16* u;
+  const __nv_bfloat16* halo_top;
+  const __nv_bfloat16* halo_bot;
+  const __nv_bfloat16* weight;  // [2*hid, 9]
+  const __nv_bfloat16* bias;    // [2*hid] or null
+  __nv_bfloat16* out;
+  int rows, W, H, hid, seg_rows;
+  int64_t row0;
+};
+
+__global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const DwArgs p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int role = lane >> 4, xs = (lane >> 3) & 1, cv = lane & 7;
+  const int nvec = p.hid >> 3;
+  const int cvec = blockIdx.x * DW_CV + cv;  // 8-channel vector index inside a role
+  const int x0 = blockIdx.y * DW_TW;
+  const int lx = 2 * warp + xs;  // column inside the tile
+  const int x = x0 + lx;
+  const int ys = blockIdx.z * p.seg_rows;
+  const int ye = min(p.rows, ys + p.seg_rows);
+  const int C2 = 2 * p.hid;
+  const bool lane_ok = (cvec < nvec) && (x < p.W);
+  const int ch = role * p.hid + (min(cvec, nvec - 1) << 3);  // first of this lane's 8 channels
+
+  // per-lane taps: w2[tap][pair] as float2, tap = 3*dy + dx
+  float2 w2[9][4];
+  float bv[8];
+  {
+    const __nv_bfloat16* wp = p.weight + (int64_t)ch * 9;
+#pragma unroll
+    for (int tap = 0; tap < 9; ++tap)
+#pragma unroll
+      for (int c2 = 0; c2 < 4; ++c2)
+        w2[tap][c2] = make_float2(__bfloat162float(wp[(2 * c2) * 9 + tap]), __bfloat162float(wp[(2 * c2 + 1) * 9 + tap]));
+#pragma unroll
+    for (int c = 0; c < 8; ++c) bv[c] = p.bias ? __bfloat162float(p.bias[ch + c]) : 0.f;
+  }
+
+  // which input rows exist for this segment: local rows ys-1 .. ye
+  const int fr_first = (int)((p.row0 + ys) % p.H);
+  const int fr_last = (int)((p.row0 + ye - 1) % p.H);
+  const bool need_top = fr_first != 0;
+  const bool need_bot = fr_last != p.H - 1;
+  const int nin = ye - ys + 2;  // input-row slots k = 0 .. nin-1  <->  local row ys-1+k
+
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+
+  auto row_ptr = [&](int k) -> const __nv_bfloat16* {
+    const int r = ys - 1 + k;
+    if (k == 0 && !need_top) return nullptr;
+    if (k == nin - 1 && !need_bot) return nullptr;
+    if (r < 0) return p.halo_top;
+    if (r >= p.rows) return p.halo_bot;
+    return p.u + (int64_t)r * p.W * C2;
+  };
+
+  auto issue_row = [&](int k) {
+    if (k < nin) {
+      const __nv_bfloat16* rp = row_ptr(k);
+      if (rp != nullptr) {
+        const uint32_t sbase = smem_base + (k % DW_STAGES) * DW_STAGE_BYTES;
+        for (int q = tid; q < DW_ROW_CHUNKS; q += DW_THREADS) {
+          const int px = q >> 4, rem = q & 15, rl = rem >> 3, c = rem & 7;
+          const int gx = x0 - 1 + px;
+          const int gv = blockIdx.x * DW_CV + c;
+          const bool ok = (gx >= 0) && (gx < p.W) && (gv < nvec);
+          const __nv_bfloat16* src = ok ? rp + (int64_t)gx * C2 + rl * p.hid + (gv << 3) : rp;
+          cp_async_16(sbase + q * 16, src, ok);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  float2 acc[3][4];
+#pragma unroll
+  for (int s = 0; s < 3; ++s)
+#pragma unroll
+    for (int c2 = 0; c2 < 4; ++c2) acc[s][c2] = make_float2(0.f, 0.f);
+
+#pragma unroll 1
+  for (int k = 0; k < DW_STAGES - 1; ++k) issue_row(k);
+
+  // One step: consume input slot k.  PREV/CUR/NEXT are the accumulator slots of output rows
+  // (r-1, r, r+1) for input row r; they rotate with k so no register moves are needed.
+  auto step = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
+    constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
+    cp_async_wait<DW_STAGES - 2>();
+    __syncthreads();
+    issue_row(k + DW_STAGES - 1);
+    const int r = ys - 1 + k;  // local input row
+    const bool have = row_ptr(k) != nullptr;
+    const int fr = (int)((p.row0 + r + p.H) % p.H);  // frame row of the input row (r may be -1)
+    if (have) {
+      const unsigned char* sp = smem + (k % DW_STAGES) * DW_STAGE_BYTES + ((lx * 16 + role * 8 + cv) << 4);
+      const uint4 vm = *reinterpret_cast<const uint4*>(sp);
+      const uint4 vc = *reinterpret_cast<const uint4*>(sp + 256);
+      const uint4 vp = *reinterpret_cast<const uint4*>(sp + 512);
+      float2 xm[4], xc[4], xp[4];
+      xm[0] = make_float2(bf16_lo(vm.x), bf16_hi(vm.x)), xm[1] = make_float2(bf16_lo(vm.y), bf16_hi(vm.y));
+      xm[2] = make_float2(bf16_lo(vm.z), bf16_hi(vm.z)), xm[3] = make_float2(bf16_lo(vm.w), bf16_hi(vm.w));
+      xc[0] = make_float2(bf16_lo(vc.x), bf16_hi(vc.x)), xc[1] = make_float2(bf16_lo(vc.y), bf16_hi(vc.y));
+      xc[2] = make_float2(bf16_lo(vc.z), bf16_hi(vc.z)), xc[3] = make_float2(bf16_lo(vc.w), bf16_hi(vc.w));
+      xp[0] = make_float2(bf16_lo(vp.x), bf16_hi(vp.x)), xp[1] = make_float2(bf16_lo(vp.y), bf16_hi(vp.y));
+      xp[2] = make_float2(bf16_lo(vp.z), bf16_hi(vp.z)), xp[3] = make_float2(bf16_lo(vp.w), bf16_hi(vp.w));
+      // input row r is the row BELOW output r-1 (taps 6..8), the centre of output r (taps 3..5)
+      // and the row ABOVE output r+1 (taps 0..2); vertical neighbours must share the frame.
+      if (r - 1 >= ys && r - 1 < ye && fr != 0) {
+#pragma unroll
+        for (int c2 = 0; c2 < 4; ++c2) {
+          acc[PREV][c2] = ffma2(w2[6][c2], xm[c2], acc[PREV][c2]);
+          acc[PREV][c2] = ffma2(w2[7][c2], xc[c2], acc[PREV][c2]);
+          acc[PREV][c2] = ffma2(w2[8][c2], xp[c2], acc[PREV][c2]);
+        }
+      }
+      if (r >= ys && r < ye) {
+#pragma unroll
+        for (int c2 = 0; c2 < 4; ++c2) {
+          acc[CUR][c2] = ffma2(w2[3][c2], xm[c2], acc[CUR][c2]);
+          acc[CUR][c2] = ffma2(w2[4][c2], xc[c2], acc[CUR][c2]);
+          acc[CUR][c2] = ffma2(w2[5][c2], xp[c2], acc[CUR][c2]);
+        }
+      }
+      if (r + 1 >= ys && r + 1 < ye && fr != p.H - 1) {
+#pragma unroll
+        for (int c2 = 0; c2 < 4; ++c2) {
+          acc[NEXT][c2] = ffma2(w2[0][c2], xm[c2], acc[NEXT][c2]);
+          acc[NEXT][c2] = ffma2(w2[1][c2], xc[c2], acc[NEXT][c2]);
+          acc[NEXT][c2] = ffma2(w2[2][c2], xp[c2], acc[NEXT][c2]);
+        }
+      }
+    }
+    // output row r-1 is complete
+    const int ro = r - 1;
+    if (ro >= ys && ro < ye) {
+      float v[8];
+#pragma unroll
+      for (int c2 = 0; c2 < 4; ++c2) {
+        v[2 * c2] = acc[PREV][c2].x + bv[2 * c2];
+        v[2 * c2 + 1] = acc[PREV][c2].y + bv[2 * c2 + 1];
+      }
+      // value lane keeps channels 0..3 and receives gate 0..3; gate lane keeps 4..7 and receives value 4..7
+      float other[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float send = role == 0 ? v[4 + i] : v[i];
+        other[i] = __shfl_xor_sync(0xffffffffu, send, 16);
+      }
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = role == 0 ? v[i] * silu(other[i]) : other[i] * silu(v[4 + i]);
+      if (lane_ok) {
+        uint2 pk = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+        __nv_bfloat16* op = p.out + ((int64_t)ro * p.W + x) * p.hid + (cvec << 3) + role * 4;
+        *reinterpret_cast<uint2*>(op) = pk;
+      }
+    }
+#pragma unroll
+    for (int c2 = 0; c2 < 4; ++c2) acc[PREV][c2] = make_float2(0.f, 0.f);  // becomes NEXT of the next step
+  };
+
+  using I0 = std::integral_constant<int, 0>;
+  using I1 = std::integral_constant<int, 1>;
+  using I2 = std::integral_constant<int, 2>;
+#pragma unroll 1
+  for (int k = 0; k < nin; k += 3) {
+    step(k, I0{}, I1{}, I2{});
+    if (k + 1 < nin) step(k + 1, I1{}, I2{}, I0{});
+    if (k + 2 < nin) step(k + 2, I2{}, I0{}, I1{});
+  }
+  // the last input slot (k = nin-1, local row ye) completes output row ye-1 inside its own step.
+  cp_async_wait<0>();
+}
+
+// Plain fp32 version (parity path): one thread per (row, x, channel pair value/gate).
+__global__ void dwconv_glu_f32_kernel(const float* __restrict__ u, const float* __restrict__ halo_top,
+                                      const float* __restrict__ halo_bot, const float* __restrict__ weight,
+                                      const float* __restrict__ bias, float* __restrict__ out, int rows, int W, int H,
+                                      int hid, int64_t row0) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)rows * W * hid;
+  if (idx >= total) return;
+  const int c = (int)(idx % hid);
+  const int x = (int)((idx / hid) % W);
+  const int r = (int)(idx / ((int64_t)hid * W));
+  const int C2 = 2 * hid;
+  const int fr = (int)((row0 + r) % H);
+  float acc[2];
+#pragma unroll
+  for (int role = 0; role < 2; ++role) {
+    const int chn = role * hid + c;
+    float s = bias ? bias[chn] : 0.f;
+    for (int dy = -1; dy <= 1; ++dy) {
+      if ((dy < 0 && fr == 0) || (dy > 0 && fr == H - 1)) continue;
+      const int rr = r + dy;
+      const float* rp = rr < 0 ? halo_top : (rr >= rows ? halo_bot : u + (int64_t)rr * W * C2);
+      for (int dx = -1; dx <= 1; ++dx) {
+        const int xx = x + dx;
+        if (xx < 0 || xx >= W) continue;
+        s = fmaf(weight[chn * 9 + (dy + 1) * 3 + (dx + 1)], rp[(int64_t)xx * C2 + chn], s);
+      }
+    }
+    acc[role] = s;
+  }
+  out[idx] = acc[0] * (acc[1] / (1.0f + expf(-acc[1])));
+}
+
+}  // namespace sana
+
+using namespace sana;
+
+extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
+                               const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
+                               int64_t hid, int dtype, void* stream) {
+  SANA_REQUIRE(u && weight && out, "sana_dwconv_glu: null pointer");
+  SANA_REQUIRE(rows > 0 && W > 0 && H > 0 && hid > 0 && row0 >= 0, "sana_dwconv_glu: sizes must be positive");
+  SANA_REQUIRE(hid % 8 == 0, "sana_dwconv_glu: hid must be a multiple of 8");
+  SANA_REQUIRE(rows < (1 << 24) && W < (1 << 20) && hid < (1 << 20), "sana_dwconv_glu: size out of range");
+  SANA_REQUIRE((row0 % H == 0) || halo_top, "sana_dwconv_glu: halo_top required (first row is inside a frame)");
+  SANA_REQUIRE(((row0 + rows) % H == 0) || halo_bot, "sana_dwconv_glu: halo_bot required (last row is inside a frame)");
+  SANA_REQUIRE(aligned16(u) && aligned16(out) && (!halo_top || aligned16(halo_top)) &&
+                   (!halo_bot || aligned16(halo_bot)),
+               "sana_dwconv_glu: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == SANA_BF16) {
+    DwArgs a;
+    a.u = static_cast<const __nv_bfloat16*>(u);
+    a.halo_top = static_cast<const __nv_bfloat16*>(halo_top);
+    a.halo_bot = static_cast<const __nv_bfloat16*>(halo_bot);
+    a.weight = static_cast<const __nv_bfloat16*>(weight);
+    a.bias = static_cast<const __nv_bfloat16*>(bias);
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.rows = (int)rows, a.W = (int)W, a.H = (int)H, a.hid = (int)hid, a.row0 = row0;
+    const int64_t gx = ceil_div(hid / 8, DW_CV), gy = ceil_div(W, DW_TW);
+    // rows per CTA: long segments amortise the two halo rows; shorten them until the grid
+    // covers the device a few times over.
+    int seg = 32;
+    while (seg > 4 && gx * gy * ceil_div(rows, seg) < 4 * (int64_t)sm_count()) seg >>= 1;
+    a.seg_rows = seg;
+    const int64_t gz = ceil_div(rows, seg);
+    SANA_REQUIRE(gy < 65536 && gz < 65536, "sana_dwconv_glu: grid too large");
+    static bool attr_set = false;
+    const int smem_bytes = DW_STAGES * DW_STAGE_BYTES;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(dwconv_glu_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+      if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dwconv_glu)");
+      attr_set = true;
+    }
+    dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, smem_bytes, st>>>(a);
+  } else if (dtype == SANA_F32) {
+    const int64_t total = rows * W * hid;
+    dwconv_glu_f32_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
+        static_cast<const float*>(u), static_cast<const float*>(halo_top), static_cast<const float*>(halo_bot),
+        static_cast<const float*>(weight), static_cast<const float*>(bias), static_cast<float*>(out), (int)rows, (int)W,
+        (int)H, (int)hid, row0);
+  } else {
+    return fail(SANA_ERR_UNSUPPORTED, "sana_dwconv_glu: unsupported dtype %d", dtype);
+  }
+  SANA_LAUNCH_CHECK("dwconv_glu kernel");
+  return SANA_OK;
+}

@@ -1,0 +1,406 @@
+// bf16 projection on the 5th-generation tensor cores: out = epilogue(A[M,K] @ Wt[N,K]^T).
+//
+// Persistent, warp-specialised kernel, one CTA per SM, 128 x BN output tiles:
+//   warp 0 (one lane)  TMA producer: 128x64 A tile + BNx64 W tile per K block into a ring of
+//                      128-byte-swizzled shared-memory stages (no multicast; out-of-range
+//                      rows / K tail are zero-filled by the TMA unit)
+//   warp 1 (one lane)  issues tcgen05.mma (M=128, N=BN, K=16 per instruction), accumulating
+//                      in tensor memory; two accumulator buffers so the epilogue of tile i
+//                      overlaps the MMAs of tile i+1
+//   warps 2..5         epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step), fused
+//                      bias / activation / adaLN gate / residual in fp32, 16-byte stores
+// Every wait is bounded: after ~2 s a role records a code in g_gemm_status, raises the
+// CTA-wide abort flag and all roles fall through to the common teardown (TMEM is freed).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "epilogue.cuh"
+
+namespace sana {
+
+__device__ int g_gemm_status = 0;
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;                       // 64 bf16 = one 128-byte swizzle row
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
+constexpr int TC_THREADS = 192;
+constexpr int TC_SMEM_LIMIT = 232448;           // 227 KiB opt-in maximum per CTA
+constexpr int TC_CTRL_BYTES = 1024;             // barriers + tmem pointer + abort flag
+
+template <int BN>
+struct TcCfg {
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (TC_SMEM_LIMIT - TC_CTRL_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TC_CTRL_BYTES + 1024;  // +1024 alignment slack
+  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  // instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7, 10), both K-major, N>>3 at 17, M>>4 at 24
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                    ((uint32_t)(TC_BM >> 4) << 24);
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(STAGES >= 3, "not enough shared memory for the ring");
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+// Bounded wait.  Returns false (and raises the abort flag) on time-out or when another role
+// already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) {
+        *abort_flag = code;
+        atomicExch(&g_gemm_status, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the mbarrier once all previously issued MMAs of this thread have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// bits 0-13 address>>4, 16-29 leading offset (1, unused for swizzled K-major), 32-45 stride
+// offset (1024>>4), 46-47 descriptor version 1, 61-63 layout 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+struct TcArgs {
+  __nv_bfloat16* out;
+  int64_t ldo;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  EpiParams ep;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
+  using Cfg = TcCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;           // swizzled tiles need 1024-byte alignment
+  unsigned char* gen_base = smem_raw + (tiles_base - raw);
+  const uint32_t ctrl = tiles_base + STAGES * Cfg::STAGE_BYTES;  // control block after the ring
+  unsigned char* ctrl_gen = gen_base + STAGES * Cfg::STAGE_BYTES;
+  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort
+  const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
+  const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int kblocks = (args.K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / args.tiles_n) * TC_BM, n0 = (tile % args.tiles_n) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1)) { ok = false; break; }
+          const uint32_t sa = tiles_base + stage * Cfg::STAGE_BYTES;
+          mbar_expect_tx(bar_full + 8 * stage, Cfg::STAGE_BYTES);
+          tma_load_2d(sa, &tmA, bar_full + 8 * stage, kb * TC_BK, m0);
+          tma_load_2d(sa + TC_A_BYTES, &tmB, bar_full + 8 * stage, kb * TC_BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA tears down
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc_phase = 0u;  // bit a = phase of accumulator buffer a
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int a = it & 1;
+        if (!mbar_wait(bar_tempty + 8 * a, ((acc_phase >> a) & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+        acc_phase ^= 1u << a;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + TC_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            // +32 bytes per K=16 step inside the 128-byte swizzle row (address field is >>4)
+            umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), Cfg::IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * a);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps -----------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t full_phase = 0u;  // bit a = phase of accumulator buffer a
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int a = it & 1;
+      const int m0 = (tile / args.tiles_n) * TC_BM, n0 = (tile % args.tiles_n) * BN;
+      if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4)) { ok = false; break; }
+      full_phase ^= 1u << a;
+      tcgen05_fence_after();
+      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const bool row_ok = m < args.M;
+      const int64_t batch = row_ok ? m / args.ep.rows_per_batch : 0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
+      __nv_bfloat16* orow = args.out + m * args.ldo;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= args.N) break;  // uniform: whole chunk outside the matrix
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            const int64_t n = (int64_t)n0 + c0 + 8 * v8;
+            if (n < args.N) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * v8 + e]);
+              const uint4 o = epi_vec8_bf16(v, m, n, args.N, batch, args.ep);
+              *reinterpret_cast<uint4*>(orow + n) = o;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
+    }
+  }
+
+  // ------------------------------- teardown ---------------------------------------------
+  __syncwarp();  // single-lane roles rejoin their warp before the CTA-wide barrier
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows, cols] bf16 matrix, row stride ld elements; box = box_rows x 64 columns, 128-byte swizzle.
+static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SANA_OK;
+}
+
+template <int BN>
+static int launch_bn(const CUtensorMap& tmA, const void* Wt, int64_t ldw, int64_t N, int64_t K, TcArgs& args,
+                     cudaStream_t st) {
+  using Cfg = TcCfg<BN>;
+  CUtensorMap tmB;
+  int rc = make_tmap(&tmB, Wt, N, K, ldw, BN);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_bf16_tc)");
+    attr_done = true;
+  }
+  args.tiles_n = (int)ceil_div(N, BN);
+  const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  gemm_bf16_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, args);
+  SANA_LAUNCH_CHECK("gemm_bf16_tc kernel");
+  return SANA_OK;
+}
+
+// Tile width: minimise (waves over the SMs) x BN, i.e. padded work including the last partial wave.
+static int pick_bn(int64_t M, int64_t N) {
+  const int cands[4] = {256, 224, 192, 128};
+  const int64_t sms = sm_count();
+  const int64_t tm = ceil_div(M, TC_BM);
+  int best = 128;
+  int64_t best_cost = -1;
+  for (int bn : cands) {
+    const int64_t tiles = tm * ceil_div(N, bn);
+    const int64_t cost = ceil_div(tiles, sms) * bn;
+    if (best_cost < 0 || cost < best_cost) best_cost = cost, best = bn;
+  }
+  return best;
+}
+
+int gemm_tc_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
+                   int64_t N, int64_t K, const EpiParams& ep, cudaStream_t st) {
+  SANA_REQUIRE(aligned16(A) && aligned16(Wt) && aligned16(out), "sana_gemm: pointers must be 16-byte aligned");
+  SANA_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ldo % 8 == 0, "sana_gemm: row strides must be multiples of 8 (bf16)");
+  SANA_REQUIRE(N % 8 == 0, "sana_gemm: N must be a multiple of 8 (bf16)");
+  SANA_REQUIRE(!ep.residual || (aligned16(ep.residual) && ep.ldr % 8 == 0), "sana_gemm: residual alignment");
+  SANA_REQUIRE(!ep.bias || aligned16(ep.bias), "sana_gemm: bias alignment");
+  SANA_REQUIRE(!ep.gate_table || (aligned16(ep.gate_table) && aligned16(ep.gate_t)), "sana_gemm: gate alignment");
+  CUtensorMap tmA;
+  int rc = make_tmap(&tmA, A, M, K, lda, TC_BM);
+  if (rc) return rc;
+  TcArgs args;
+  args.out = static_cast<__nv_bfloat16*>(out);
+  args.ldo = ldo;
+  args.M = (int)M, args.N = (int)N, args.K = (int)K;
+  args.tiles_m = (int)ceil_div(M, TC_BM);
+  args.tiles_n = 0;
+  args.ep = ep;
+  switch (pick_bn(M, N)) {
+    case 256: return launch_bn<256>(tmA, Wt, ldw, N, K, args, st);
+    case 224: return launch_bn<224>(tmA, Wt, ldw, N, K, args, st);
+    case 192: return launch_bn<192>(tmA, Wt, ldw, N, K, args, st);
+    default: return launch_bn<128>(tmA, Wt, ldw, N, K, args, st);
+  }
+}
+
+}  // namespace sana
+
+extern "C" int sana_gemm_take_device_status(int* status_out) {
+  if (!status_out) return sana::fail(SANA_ERR_INVALID, "sana_gemm_take_device_status: null pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, sana::g_gemm_status, sizeof(int));
+  if (e != cudaSuccess) return sana::cuda_status(e, "cudaMemcpyFromSymbol(g_gemm_status)");
+  if (v != 0) {
+    int zero = 0;
+    e = cudaMemcpyToSymbol(sana::g_gemm_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return sana::cuda_status(e, "cudaMemcpyToSymbol(g_gemm_status)");
+  }
+  *status_out = v;
+  return SANA_OK;
+}

@@ -1,0 +1,414 @@
+// ReLU linear attention core: per-head 33x32 state reduction and apply+normalise.
+//
+// bf16 kernels keep one head per warp and feed warp-level bf16 tensor-core products
+// (exact bf16 x bf16 products, fp32 accumulation) straight from global loads: the token /
+// channel indices of the MMA fragments are permuted so that each lane's fragment registers
+// are contiguous channels of a token row, so no shared-memory transpose is needed and the
+// kernels are plain streaming reads at HBM speed.  fp32 kernels are FFMA (parity path).
+#include "common.cuh"
+
+namespace sana {
+
+constexpr int HD = 32;           // head dimension (upstream linear_head_dim)
+constexpr int SROWS = HD + 1;    // 32 value rows + ones row
+constexpr int SSIZE = SROWS * HD;  // 1056 floats per head
+
+constexpr int LA_WARPS = 8;  // heads per CTA
+
+// ------------------------------------------------------------------------------------------
+// state, bf16.  grid (chunks, ceil(H/8), B); warp w -> head hg*8+w, tokens [c*Lc, min(N,(c+1)*Lc)).
+// Lane (g = lane>>2, t = lane&3) loads 8 bytes = channels 4g..4g+3 of tokens n+2t, n+2t+1,
+// n+2t+8, n+2t+9 for both k and v.  MMA roles: A = v^T (rows = value channel), B = relu(k).
+//   A rows of M-tile mt: logical row r (<8) -> channel 4r+2mt, row r+8 -> channel 4r+2mt+1
+//   B cols of N-tile nt: logical col c -> channel 4c+nt
+// The ones row is a third M-tile whose A fragment is the constant "row 0 = 1".
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(LA_WARPS * 32)
+la_state_bf16_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int64_t ld,
+                     float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int h = blockIdx.y * LA_WARPS + warp;
+  if (h >= H) return;
+  const int b = blockIdx.z, chunk = blockIdx.x;
+  const int n_begin = chunk * Lc;
+  const int n_end = min(N, n_begin + Lc);
+
+  float acc[3][4][4];
+#pragma unroll
+  for (int m = 0; m < 3; ++m)
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.f;
+
+  const uint32_t ones = (g == 0) ? 0x3F803F80u : 0u;  // bf16 (1, 1) in logical row 0
+  const int64_t col = (int64_t)h * HD + 4 * g;
+  const __nv_bfloat16* kbase = kp + (int64_t)b * N * ld + col;
+  const __nv_bfloat16* vbase = vp + (int64_t)b * N * ld + col;
+
+  constexpr int U = 2;  // 16-token steps in flight per iteration
+  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
+    uint2 kr[U][4], vr[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int tok = n0 + 16 * u + 2 * t + (i & 1) + 8 * (i >> 1);
+        if (tok < n_end) {
+          kr[u][i] = ldg_nc_u2(kbase + (int64_t)tok * ld);
+          vr[u][i] = ldg_nc_u2(vbase + (int64_t)tok * ld);
+        } else {
+          kr[u][i] = make_uint2(0u, 0u);
+          vr[u][i] = make_uint2(0u, 0u);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint32_t bfr[4][2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kr[u][i].x = relu_bf16x2(kr[u][i].x);
+        kr[u][i].y = relu_bf16x2(kr[u][i].y);
+      }
+      // b0 pairs tokens (2t, 2t+1), b1 pairs tokens (2t+8, 2t+9)
+      bfr[0][0] = __byte_perm(kr[u][0].x, kr[u][1].x, 0x5410);
+      bfr[1][0] = __byte_perm(kr[u][0].x, kr[u][1].x, 0x7632);
+      bfr[2][0] = __byte_perm(kr[u][0].y, kr[u][1].y, 0x5410);
+      bfr[3][0] = __byte_perm(kr[u][0].y, kr[u][1].y, 0x7632);
+      bfr[0][1] = __byte_perm(kr[u][2].x, kr[u][3].x, 0x5410);
+      bfr[1][1] = __byte_perm(kr[u][2].x, kr[u][3].x, 0x7632);
+      bfr[2][1] = __byte_perm(kr[u][2].y, kr[u][3].y, 0x5410);
+      bfr[3][1] = __byte_perm(kr[u][2].y, kr[u][3].y, 0x7632);
+      uint32_t afr[2][4];
+      afr[0][0] = __byte_perm(vr[u][0].x, vr[u][1].x, 0x5410);
+      afr[0][1] = __byte_perm(vr[u][0].x, vr[u][1].x, 0x7632);
+      afr[0][2] = __byte_perm(vr[u][2].x, vr[u][3].x, 0x5410);
+      afr[0][3] = __byte_perm(vr[u][2].x, vr[u][3].x, 0x7632);
+      afr[1][0] = __byte_perm(vr[u][0].y, vr[u][1].y, 0x5410);
+      afr[1][1] = __byte_perm(vr[u][0].y, vr[u][1].y, 0x7632);
+      afr[1][2] = __byte_perm(vr[u][2].y, vr[u][3].y, 0x5410);
+      afr[1][3] = __byte_perm(vr[u][2].y, vr[u][3].y, 0x7632);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        mma_bf16_16816(acc[0][nt], afr[0][0], afr[0][1], afr[0][2], afr[0][3], bfr[nt][0], bfr[nt][1]);
+        mma_bf16_16816(acc[1][nt], afr[1][0], afr[1][1], afr[1][2], afr[1][3], bfr[nt][0], bfr[nt][1]);
+        mma_bf16_16816(acc[2][nt], ones, 0u, ones, 0u, bfr[nt][0], bfr[nt][1]);
+      }
+    }
+  }
+
+  float* out = partial + (((int64_t)b * nchunks + chunk) * H + h) * SSIZE;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int i0 = 4 * g + 2 * mt;
+      const int j0 = 8 * t + nt, j1 = 8 * t + 4 + nt;
+      out[i0 * HD + j0] = acc[mt][nt][0];
+      out[i0 * HD + j1] = acc[mt][nt][1];
+      out[(i0 + 1) * HD + j0] = acc[mt][nt][2];
+      out[(i0 + 1) * HD + j1] = acc[mt][nt][3];
+    }
+  if (g == 0) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      out[HD * HD + 8 * t + nt] = acc[2][nt][0];
+      out[HD * HD + 8 * t + 4 + nt] = acc[2][nt][1];
+    }
+  }
+}
+
+// state, fp32 (FFMA).  grid (chunks, H, B), 256 threads: thread (ib = tid>>5, j = tid&31)
+// owns state rows ib, ib+8, ib+16, ib+24 (and warp 0 the ones row) of column j.
+__global__ void __launch_bounds__(256)
+la_state_f32_kernel(const float* __restrict__ kp, const float* __restrict__ vp, int64_t ld,
+                    float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
+  constexpr int TN = 64;
+  __shared__ float ks[TN][HD];
+  __shared__ float vs[TN][HD + 1];
+  const int tid = threadIdx.x, j = tid & 31, ib = tid >> 5;
+  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
+  const float* kbase = kp + (int64_t)b * N * ld + (int64_t)h * HD;
+  const float* vbase = vp + (int64_t)b * N * ld + (int64_t)h * HD;
+  float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int n0 = n_begin; n0 < n_end; n0 += TN) {
+    __syncthreads();
+    for (int e = tid; e < TN * HD; e += 256) {
+      const int r = e >> 5, c = e & 31, tok = n0 + r;
+      float kv = 0.f, vv = 0.f;
+      if (tok < n_end) {
+        kv = fmaxf(kbase[(int64_t)tok * ld + c], 0.f);
+        vv = vbase[(int64_t)tok * ld + c];
+      }
+      ks[r][c] = kv;
+      vs[r][c] = vv;
+    }
+    __syncthreads();
+    const int lim = min(TN, n_end - n0);
+    for (int r = 0; r < lim; ++r) {
+      const float kv = ks[r][j];
+      acc[0] = fmaf(vs[r][ib], kv, acc[0]);
+      acc[1] = fmaf(vs[r][ib + 8], kv, acc[1]);
+      acc[2] = fmaf(vs[r][ib + 16], kv, acc[2]);
+      acc[3] = fmaf(vs[r][ib + 24], kv, acc[3]);
+      acc[4] += kv;
+    }
+  }
+  float* out = partial + (((int64_t)b * nchunks + chunk) * H + h) * SSIZE;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) out[(ib + 8 * r) * HD + j] = acc[r];
+  if (ib == 0) out[HD * HD + j] = acc[4];
+}
+
+// Adds the per-chunk partial states in chunk order (fixed order => bit-reproducible).
+__global__ void la_state_reduce_kernel(const float* __restrict__ partial, float* __restrict__ state, int nchunks,
+                                       int64_t per_batch /* H*SSIZE */, int64_t total /* B*H*SSIZE */) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t b = idx / per_batch, r = idx - b * per_batch;
+  const float* p = partial + b * nchunks * per_batch + r;
+  float s = 0.f;
+  for (int c = 0; c < nchunks; ++c) s += p[(int64_t)c * per_batch];
+  state[idx] = s;
+}
+
+// ------------------------------------------------------------------------------------------
+// apply, bf16.  grid (chunks, ceil(H/8), B); warp -> one head, 16 tokens per step.
+// A = relu(q) rows (tokens), B = state^T split into bf16 hi + lo parts (two MMAs, ~2^-17
+// relative error), denominator in plain fp32.  Lane (g, t) loads the 16 contiguous bytes
+// q[token g (and g+8)][8t .. 8t+7]; logical K index kk of K-step s maps to channel
+// 8*((kk&7)>>1) + 4s + 2*(kk>>3) + (kk&1); logical output column c of N-tile nt maps to
+// value channel 8*(c>>1) + 2nt + (c&1), so each lane ends with 8 contiguous outputs of a
+// row (one 16-byte store).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(LA_WARPS * 32)
+la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ state,
+                     __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int h = blockIdx.y * LA_WARPS + warp;
+  if (h >= H) return;
+  const int b = blockIdx.z;
+  const int n_begin = blockIdx.x * Lc, n_end = min(N, n_begin + Lc);
+  const float* S = state + ((int64_t)b * H + h) * SSIZE;
+
+  uint32_t bhi[4][2][2], blo[4][2][2];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int i = 8 * (g >> 1) + 2 * nt + (g & 1);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const float4 sv = *reinterpret_cast<const float4*>(S + i * HD + 8 * t + 4 * s);
+      const uint32_t h0 = pack_bf16(sv.x, sv.y), h1 = pack_bf16(sv.z, sv.w);
+      bhi[nt][s][0] = h0;
+      bhi[nt][s][1] = h1;
+      blo[nt][s][0] = pack_bf16(sv.x - bf16_lo(h0), sv.y - bf16_hi(h0));
+      blo[nt][s][1] = pack_bf16(sv.z - bf16_lo(h1), sv.w - bf16_hi(h1));
+    }
+  }
+  float sd[8];
+  {
+    const float4 d0 = *reinterpret_cast<const float4*>(S + HD * HD + 8 * t);
+    const float4 d1 = *reinterpret_cast<const float4*>(S + HD * HD + 8 * t + 4);
+    sd[0] = d0.x, sd[1] = d0.y, sd[2] = d0.z, sd[3] = d0.w;
+    sd[4] = d1.x, sd[5] = d1.y, sd[6] = d1.z, sd[7] = d1.w;
+  }
+
+  const int64_t col = (int64_t)h * HD + 8 * t;
+  const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
+  __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
+
+  constexpr int U = 2;
+  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
+    uint4 qr[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int tok = n0 + 16 * u + g + 8 * r;
+        qr[u][r] = (tok < n_end) ? ldg_nc_u4(qbase + (int64_t)tok * ldq) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint32_t a[2][4];  // [row half][word]
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        a[r][0] = relu_bf16x2(qr[u][r].x);
+        a[r][1] = relu_bf16x2(qr[u][r].y);
+        a[r][2] = relu_bf16x2(qr[u][r].z);
+        a[r][3] = relu_bf16x2(qr[u][r].w);
+      }
+      float den[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float d = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          d = fmaf(bf16_lo(a[r][w]), sd[2 * w], d);
+          d = fmaf(bf16_hi(a[r][w]), sd[2 * w + 1], d);
+        }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        den[r] = d;
+      }
+      float c[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          // K-step s: a0 = row g word 2s, a1 = row g+8 word 2s, a2 = row g word 2s+1, a3 = row g+8 word 2s+1
+          mma_bf16_16816(c[nt], a[0][2 * s], a[1][2 * s], a[0][2 * s + 1], a[1][2 * s + 1], blo[nt][s][0],
+                         blo[nt][s][1]);
+          mma_bf16_16816(c[nt], a[0][2 * s], a[1][2 * s], a[0][2 * s + 1], a[1][2 * s + 1], bhi[nt][s][0],
+                         bhi[nt][s][1]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int tok = n0 + 16 * u + g + 8 * r;
+        if (tok < n_end) {
+          const float inv = 1.0f / (den[r] + eps);
+          uint4 o;
+          o.x = pack_bf16(c[0][2 * r] * inv, c[0][2 * r + 1] * inv);
+          o.y = pack_bf16(c[1][2 * r] * inv, c[1][2 * r + 1] * inv);
+          o.z = pack_bf16(c[2][2 * r] * inv, c[2][2 * r + 1] * inv);
+          o.w = pack_bf16(c[3][2 * r] * inv, c[3][2 * r + 1] * inv);
+          *reinterpret_cast<uint4*>(obase + (int64_t)tok * ldo) = o;
+        }
+      }
+    }
+  }
+}
+
+// apply, fp32.  grid (chunks, H, B), 128 threads; one token per thread per step.
+__global__ void __launch_bounds__(128)
+la_apply_f32_kernel(const float* __restrict__ qp, int64_t ldq, const float* __restrict__ state,
+                    float* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+  __shared__ __align__(16) float S[SSIZE];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const float* Sg = state + ((int64_t)b * H + h) * SSIZE;
+  for (int e = threadIdx.x; e < SSIZE; e += 128) S[e] = Sg[e];
+  __syncthreads();
+  const int n_begin = blockIdx.x * Lc, n_end = min(N, n_begin + Lc);
+  for (int tok = n_begin + threadIdx.x; tok < n_end; tok += 128) {
+    const float* qrow = qp + ((int64_t)b * N + tok) * ldq + (int64_t)h * HD;
+    float* orow = op + ((int64_t)b * N + tok) * ldo + (int64_t)h * HD;
+    float q[HD];
+#pragma unroll
+    for (int v4 = 0; v4 < HD / 4; ++v4) {
+      const float4 x = *reinterpret_cast<const float4*>(qrow + 4 * v4);
+      q[4 * v4] = fmaxf(x.x, 0.f), q[4 * v4 + 1] = fmaxf(x.y, 0.f);
+      q[4 * v4 + 2] = fmaxf(x.z, 0.f), q[4 * v4 + 3] = fmaxf(x.w, 0.f);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < HD; ++jj) den = fmaf(S[HD * HD + jj], q[jj], den);
+    den += eps;
+#pragma unroll 1
+    for (int i4 = 0; i4 < HD / 4; ++i4) {
+      float r[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float s = 0.f;
+        const float* Si = S + (4 * i4 + e) * HD;
+#pragma unroll
+        for (int jj = 0; jj < HD; ++jj) s = fmaf(Si[jj], q[jj], s);
+        r[e] = s / den;
+      }
+      *reinterpret_cast<float4*>(orow + 4 * i4) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+  }
+}
+
+// Host-side split of the token axis: enough CTAs to fill the device, chunks a multiple of 64.
+static void la_chunking(int64_t B, int64_t N, int64_t head_groups, int target_ctas_per_sm, int* Lc, int* nchunks) {
+  const int64_t target = (int64_t)sm_count() * target_ctas_per_sm;
+  int64_t want = ceil_div(target, B * head_groups);
+  if (want < 1) want = 1;
+  int64_t lc = ceil_div(ceil_div(N, want), 64) * 64;
+  if (lc < 64) lc = 64;
+  *Lc = (int)lc;
+  *nchunks = (int)ceil_div(N, lc);
+}
+
+static void la_state_plan(int64_t B, int64_t N, int64_t H, int dtype, int* Lc, int* nchunks) {
+  // The plan must not depend on dtype-specific grids so that the workspace query needs no dtype:
+  // use the bf16 head grouping (the fp32 kernel simply launches more, smaller CTAs).
+  (void)dtype;
+  la_chunking(B, N, ceil_div(H, LA_WARPS), 2, Lc, nchunks);
+}
+
+}  // namespace sana
+
+using namespace sana;
+
+extern "C" int64_t sana_la_state_workspace_bytes(int64_t B, int64_t N, int64_t H) {
+  if (B <= 0 || N <= 0 || H <= 0) return 0;
+  int Lc, nchunks;
+  la_state_plan(B, N, H, SANA_BF16, &Lc, &nchunks);
+  return B * (int64_t)nchunks * H * SSIZE * (int64_t)sizeof(float);
+}
+
+extern "C" int sana_la_state(const void* k, const void* v, int64_t ld, float* state, void* workspace,
+                             int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype, void* stream) {
+  SANA_REQUIRE(k && v && state && workspace, "sana_la_state: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_state: B, N, H must be positive");
+  SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_state: size out of range");
+  SANA_REQUIRE(ld >= H * HD && ld % 8 == 0, "sana_la_state: ld must be >= H*32 and a multiple of 8");
+  SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(state) && aligned16(workspace),
+               "sana_la_state: pointers must be 16-byte aligned");
+  SANA_REQUIRE(workspace_bytes >= sana_la_state_workspace_bytes(B, N, H), "sana_la_state: workspace too small");
+  int Lc, nchunks;
+  la_state_plan(B, N, H, dtype, &Lc, &nchunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  if (dtype == SANA_BF16) {
+    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
+                                                        static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
+                                                        (int)H, Lc, nchunks);
+  } else if (dtype == SANA_F32) {
+    dim3 grid(nchunks, (unsigned)H, (unsigned)B);
+    la_state_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(v), ld,
+                                              partial, (int)N, (int)H, Lc, nchunks);
+  } else {
+    return fail(SANA_ERR_UNSUPPORTED, "sana_la_state: unsupported dtype %d", dtype);
+  }
+  SANA_LAUNCH_CHECK("la_state kernel");
+  const int64_t total = B * H * SSIZE;
+  la_state_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(partial, state, nchunks, H * SSIZE, total);
+  SANA_LAUNCH_CHECK("la_state_reduce kernel");
+  return SANA_OK;
+}
+
+extern "C" int sana_la_apply(const void* q, int64_t ldq, const float* state, void* out, int64_t ldo, int64_t B,
+                             int64_t N, int64_t H, float eps, int dtype, void* stream) {
+  SANA_REQUIRE(q && state && out, "sana_la_apply: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_apply: B, N, H must be positive");
+  SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_apply: size out of range");
+  SANA_REQUIRE(ldq >= H * HD && ldq % 8 == 0 && ldo >= H * HD && ldo % 8 == 0,
+               "sana_la_apply: row strides must be >= H*32 and multiples of 8");
+  SANA_REQUIRE(aligned16(q) && aligned16(state) && aligned16(out), "sana_la_apply: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int Lc, nchunks;
+  if (dtype == SANA_BF16) {
+    la_chunking(B, N, ceil_div(H, LA_WARPS), 4, &Lc, &nchunks);
+    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    la_apply_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(q), ldq, state,
+                                                        static_cast<__nv_bfloat16*>(out), ldo, (int)N, (int)H, Lc,
+                                                        eps);
+  } else if (dtype == SANA_F32) {
+    la_chunking(B, N, H, 4, &Lc, &nchunks);
+    dim3 grid(nchunks, (unsigned)H, (unsigned)B);
+    la_apply_f32_kernel<<<grid, 128, 0, st>>>(static_cast<const float*>(q), ldq, state, static_cast<float*>(out),
+                                              ldo, (int)N, (int)H, Lc, eps);
+  } else {
+    return fail(SANA_ERR_UNSUPPORTED, "sana_la_apply: unsupported dtype %d", dtype);
+  }
+  SANA_LAUNCH_CHECK("la_apply kernel");
+  return SANA_OK;
+}

@@ -1,0 +1,142 @@
+// adaLN-single LayerNorm + modulate: one warp per token row, the row held in registers
+// (packed, as loaded) so global memory is read once and written once.
+#include "common.cuh"
+
+namespace sana {
+
+template <typename T>
+struct Vec16;  // 16-byte vector of T
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void unpack(const uint4& v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x), f[1] = bf16_hi(v.x), f[2] = bf16_lo(v.y), f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z), f[5] = bf16_hi(v.z), f[6] = bf16_lo(v.w), f[7] = bf16_hi(v.w);
+  }
+  __device__ static uint4 pack(const float (&f)[8]) {
+    return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+  }
+};
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void unpack(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x), f[1] = __uint_as_float(v.y), f[2] = __uint_as_float(v.z), f[3] = __uint_as_float(v.w);
+  }
+  __device__ static uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256)
+ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T* __restrict__ t, T* __restrict__ z,
+                   int64_t rows, int N, int C, int shift_row, int scale_row, float eps) {
+  constexpr int VN = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = C / VN;
+  const int b = (int)(row / N);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+  uint4 raw[MAXV];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      raw[i] = ldg_nc_u4(xr + v);
+      float f[VN];
+      Vec16<T>::unpack(raw[i], f);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) sum += f[e];
+    }
+  }
+  const float mean = warp_sum(sum) / (float)C;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float f[VN];
+      Vec16<T>::unpack(raw[i], f);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        const float d = f[e] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / (float)C + eps);
+  const uint4* tsh = reinterpret_cast<const uint4*>(t + ((int64_t)b * 6 + shift_row) * C);
+  const uint4* tsc = reinterpret_cast<const uint4*>(t + ((int64_t)b * 6 + scale_row) * C);
+  const uint4* bsh = reinterpret_cast<const uint4*>(table + (int64_t)shift_row * C);
+  const uint4* bsc = reinterpret_cast<const uint4*>(table + (int64_t)scale_row * C);
+  uint4* zr = reinterpret_cast<uint4*>(z + row * C);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float f[VN], s1[VN], s2[VN], h1[VN], h2[VN];
+      Vec16<T>::unpack(raw[i], f);
+      Vec16<T>::unpack(__ldg(tsc + v), s1);
+      Vec16<T>::unpack(__ldg(bsc + v), s2);
+      Vec16<T>::unpack(__ldg(tsh + v), h1);
+      Vec16<T>::unpack(__ldg(bsh + v), h2);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) f[e] = fmaf((f[e] - mean) * rstd, 1.0f + (s1[e] + s2[e]), h1[e] + h2[e]);
+      zr[v] = Vec16<T>::pack(f);
+    }
+  }
+}
+
+template <typename T>
+static int launch_ln(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N, int64_t C,
+                     int shift_row, int scale_row, float eps, cudaStream_t st) {
+  const int64_t rows = B * N;
+  const int nvec = (int)(C / Vec16<T>::N);
+  const int per_lane = (nvec + 31) / 32;
+  const unsigned grid = (unsigned)ceil_div(rows, 8);
+  const T* xp = static_cast<const T*>(x);
+  const T* tb = static_cast<const T*>(table);
+  const T* tp = static_cast<const T*>(t);
+  T* zp = static_cast<T*>(z);
+#define SANA_LN_CASE(MV)                                                                                   \
+  if (per_lane <= MV) {                                                                                    \
+    ln_modulate_kernel<T, MV><<<grid, 256, 0, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, shift_row, scale_row, eps); \
+    SANA_LAUNCH_CHECK("ln_modulate kernel");                                                               \
+    return SANA_OK;                                                                                        \
+  }
+  SANA_LN_CASE(5)
+  SANA_LN_CASE(9)
+  SANA_LN_CASE(16)
+  SANA_LN_CASE(32)
+#undef SANA_LN_CASE
+  return fail(SANA_ERR_UNSUPPORTED, "sana_ln_modulate: C=%lld too large", (long long)C);
+}
+
+}  // namespace sana
+
+using namespace sana;
+
+extern "C" int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
+                                int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream) {
+  SANA_REQUIRE(x && table && t && z, "sana_ln_modulate: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && C > 0, "sana_ln_modulate: sizes must be positive");
+  SANA_REQUIRE(C % 8 == 0 && C * (dtype == SANA_F32 ? 4 : 2) <= 16384,
+               "sana_ln_modulate: C must be a multiple of 8 and a row at most 16 KiB");
+  SANA_REQUIRE(shift_row >= 0 && shift_row < 6 && scale_row >= 0 && scale_row < 6, "sana_ln_modulate: bad table row");
+  SANA_REQUIRE(aligned16(x) && aligned16(table) && aligned16(t) && aligned16(z),
+               "sana_ln_modulate: pointers must be 16-byte aligned");
+  SANA_REQUIRE(B * N < ((int64_t)1 << 31) * 8, "sana_ln_modulate: too many rows");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == SANA_BF16) return launch_ln<__nv_bfloat16>(x, table, t, z, B, N, C, shift_row, scale_row, eps, st);
+  if (dtype == SANA_F32) return launch_ln<float>(x, table, t, z, B, N, C, shift_row, scale_row, eps, st);
+  return fail(SANA_ERR_UNSUPPORTED, "sana_ln_modulate: unsupported dtype %d", dtype);
+}

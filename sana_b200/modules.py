@@ -1,0 +1,284 @@
+"""Drop-in PyTorch modules with upstream's constructor arguments, attribute names, state-dict
+keys and forward signatures, computing through libsana_b200's CUDA kernels.
+
+  LiteLA                   diffusion/model/nets/sana_blocks.py:211-301
+  GLUMBConv (+ ConvLayer)  diffusion/model/nets/basic_modules.py:32-199
+  MultiHeadCrossAttention  diffusion/model/nets/sana_blocks.py:48-98
+  SanaMSBlock              diffusion/model/nets/sana_multi_scale.py:54-157
+
+Inference only (no autograd through the kernels).  Feature combinations the kernels do not
+cover raise; nothing falls back to eager PyTorch arithmetic, except the small softmax core
+of the cross-attention which still calls torch's scaled_dot_product_attention.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .sharding import SequenceShard
+
+LN_EPS = 1e-6
+
+
+def val2tuple(x, min_len: int = 1):
+    """diffusion/model/utils.py val2tuple: scalar -> tuple repeated to ``min_len``."""
+    x = tuple(x) if isinstance(x, (list, tuple)) else (x,)
+    return x + (x[-1],) * max(0, min_len - len(x))
+
+
+def _as2d(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1])
+
+
+class LiteLA(nn.Module):
+    """ReLU linear attention.  Same arguments and attributes as upstream's LiteLA (which
+    derives from timm's Attention: ``qkv``, ``proj``, ``num_heads``, ``scale``,
+    ``attn_drop``, ``proj_drop``)."""
+
+    PAD_VAL = 1
+
+    def __init__(self, in_dim: int, out_dim: int, heads: Optional[int] = None, heads_ratio: float = 1.0, dim=32,
+                 eps=1e-15, use_bias=False, qk_norm=False, norm_eps=1e-5):
+        super().__init__()
+        heads = heads or int(out_dim // dim * heads_ratio)
+        if qk_norm:
+            raise NotImplementedError("LiteLA(qk_norm=True) is not covered by the CUDA kernels yet")
+        if in_dim != out_dim or out_dim // heads != ops.HEAD_DIM or out_dim % heads != 0:
+            raise NotImplementedError("the linear-attention kernels need in_dim == out_dim and head dimension 32")
+        self.num_heads = heads
+        self.scale = (in_dim // heads) ** -0.5
+        self.qkv = nn.Linear(in_dim, in_dim * 3, bias=use_bias)
+        self.attn_drop = nn.Dropout(0.0)
+        self.proj = nn.Linear(in_dim, in_dim)
+        self.proj_drop = nn.Dropout(0.0)
+        self.in_dim = in_dim
+        self.out_dim = out_dim
+        self.heads = heads
+        self.dim = out_dim // heads
+        self.eps = eps
+        self.kernel_func = nn.ReLU(inplace=False)
+        self.q_norm = nn.Identity()
+        self.k_norm = nn.Identity()
+        self.seq_shard: Optional[SequenceShard] = None
+
+    # -- pieces shared with the fused block path --------------------------------------------
+    def _core(self, qkv: torch.Tensor, B: int, N: int) -> torch.Tensor:
+        """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``)."""
+        C = self.out_dim
+        state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, self.heads)
+        if self.seq_shard is not None:
+            self.seq_shard.allreduce_state(state)
+        return ops.la_apply(qkv[:, :C], state, B, N, self.heads, float(self.eps))
+
+    def attn_matmul(self, q, k, v: torch.Tensor) -> torch.Tensor:
+        """Upstream layout (sana_blocks.py:245-263): q, v [B, h, d, N], k [B, h, N, d]; returns
+        fp32 [B, h, d, N].  Kept for the guidance processors that call it directly."""
+        B, h, d, N = q.shape
+        dt = q.dtype
+        qt = q.permute(0, 3, 1, 2).reshape(B * N, h * d).contiguous()
+        kt = k.permute(0, 2, 1, 3).reshape(B * N, h * d).contiguous()
+        vt = v.permute(0, 3, 1, 2).reshape(B * N, h * d).contiguous()
+        state = ops.la_state(kt, vt, B, N, h)
+        o = ops.la_apply(qt, state, B, N, h, float(self.eps))
+        return o.to(dt).float().reshape(B, N, h, d).permute(0, 2, 3, 1)
+
+    def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_id=None, block_mask=None):
+        if rotary_emb is not None:
+            raise NotImplementedError("LiteLA with rotary embeddings is not covered by the CUDA kernels yet")
+        B, N, C = x.shape
+        qkv = ops.gemm(_as2d(x), self.qkv.weight, bias=self.qkv.bias)
+        o = self._core(qkv, B, N)
+        return ops.gemm(o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
+
+    @property
+    def module_str(self) -> str:
+        return f"{type(self).__name__}(i={self.in_dim},o={self.out_dim},h={self.heads},d={self.dim},eps={self.eps:.1E}"
+
+    def __repr__(self):
+        return f"EPS{self.eps}-" + super().__repr__()
+
+
+class ConvLayer(nn.Module):
+    """Parameter holder with upstream's ``conv`` / ``norm`` / ``act`` attributes
+    (basic_modules.py:32-99) so checkpoints load unchanged; GLUMBConv reads the weights and
+    runs the fused kernels instead of calling this layer."""
+
+    def __init__(self, in_dim: int, out_dim: int, kernel_size=3, stride=1, dilation=1, groups=1, padding=None,
+                 use_bias=False, dropout=0.0, conv_type="2d", norm=None, act=None):
+        super().__init__()
+        if stride != 1 or dilation != 1 or dropout > 0 or conv_type != "2d" or norm is not None:
+            raise NotImplementedError("ConvLayer: only stride 1, dilation 1, no dropout, no norm, 2-D is covered")
+        if padding is None:
+            padding = kernel_size // 2
+        self.in_dim, self.out_dim, self.kernel_size = in_dim, out_dim, kernel_size
+        self.stride, self.dilation, self.groups, self.padding, self.use_bias = stride, dilation, groups, padding, use_bias
+        self.dropout = None
+        self.conv = nn.Conv2d(in_dim, out_dim, kernel_size=(kernel_size, kernel_size), stride=(stride, stride),
+                              padding=padding, dilation=(dilation, dilation), groups=groups, bias=use_bias)
+        self.norm = None
+        self.act_name = act
+        self.act = nn.SiLU(inplace=True) if act == "silu" else None
+        if act not in (None, "silu"):
+            raise NotImplementedError(f"ConvLayer: activation {act!r} is not covered")
+
+    def forward(self, x):
+        raise NotImplementedError("ConvLayer is a parameter holder here; call GLUMBConv.forward")
+
+
+class GLUMBConv(nn.Module):
+    """Mix-FFN: 1x1 expand + SiLU, 3x3 depthwise, SiLU-GLU, 1x1 project."""
+
+    def __init__(self, in_features: int, hidden_features: int, out_feature=None, kernel_size=3, stride=1,
+                 padding=None, use_bias=False, norm=(None, None, None), act=("silu", "silu", None), dilation=1):
+        super().__init__()
+        out_feature = out_feature or in_features
+        use_bias = val2tuple(use_bias, 3)
+        norm = val2tuple(norm, 3)
+        act = val2tuple(act, 3)
+        if kernel_size != 3 or stride != 1 or dilation != 1 or any(n is not None for n in norm):
+            raise NotImplementedError("GLUMBConv: only kernel 3, stride 1, dilation 1, no norms is covered")
+        if tuple(act) != ("silu", "silu", None):
+            raise NotImplementedError("GLUMBConv: only act=('silu','silu',None) is covered")
+        if hidden_features % 8 != 0 or in_features % 8 != 0 or out_feature % 8 != 0:
+            raise NotImplementedError("GLUMBConv: feature sizes must be multiples of 8")
+        self.glu_act = nn.SiLU(inplace=False)
+        self.inverted_conv = ConvLayer(in_features, hidden_features * 2, 1, use_bias=use_bias[0], act=act[0])
+        self.depth_conv = ConvLayer(hidden_features * 2, hidden_features * 2, kernel_size, groups=hidden_features * 2,
+                                    padding=padding, use_bias=use_bias[1], act=None)
+        self.point_conv = ConvLayer(hidden_features, out_feature, 1, use_bias=use_bias[2], act=act[2])
+        self.in_features, self.hidden_features, self.out_feature = in_features, hidden_features, out_feature
+        self.seq_shard: Optional[SequenceShard] = None
+
+    def _expand(self, z2d: torch.Tensor) -> torch.Tensor:
+        c = self.inverted_conv.conv
+        return ops.gemm(z2d, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias, act=ops.ACT_SILU)
+
+    def _depthwise_glu(self, u: torch.Tensor, B: int, N: int, HW: Sequence[int]) -> torch.Tensor:
+        if HW is None or len(HW) not in (2, 3):
+            raise ValueError("GLUMBConv.forward needs HW=(H, W) or (T, H, W)")
+        H, W = HW[-2], HW[-1]
+        c = self.depth_conv.conv
+        sh = self.seq_shard
+        if sh is not None:
+            if B != 1 or N != sh.tokens or (H, W) != (sh.H, sh.W):
+                raise ValueError("sequence-parallel GLUMBConv: batch must be 1 and x the local token shard")
+            top, bot = sh.exchange_halo(u)
+            return ops.dwconv_glu(u, c.weight, c.bias, W, H, row0=sh.row0, halo_top=top, halo_bot=bot)
+        frames = HW[0] if len(HW) == 3 else 1
+        if N != frames * H * W:
+            raise ValueError(f"GLUMBConv: N={N} does not match HW={tuple(HW)}")
+        return ops.dwconv_glu(u, c.weight, c.bias, W, H)
+
+    def forward(self, x: torch.Tensor, HW=None) -> torch.Tensor:
+        B, N, C = x.shape
+        u = self._expand(_as2d(x))
+        g = self._depthwise_glu(u, B, N, HW)
+        c = self.point_conv.conv
+        out = ops.gemm(g, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias)
+        return out.reshape(B, N, -1)
+
+
+class MultiHeadCrossAttention(nn.Module):
+    """Softmax attention of image tokens over the text tokens (SDPA branch upstream)."""
+
+    def __init__(self, d_model, num_heads, attn_drop=0.0, proj_drop=0.0, qk_norm=False, **block_kwargs):
+        super().__init__()
+        assert d_model % num_heads == 0, "d_model must be divisible by num_heads"
+        if qk_norm:
+            raise NotImplementedError("MultiHeadCrossAttention(qk_norm=True) is not covered yet")
+        self.d_model, self.num_heads, self.head_dim = d_model, num_heads, d_model // num_heads
+        self.q_linear = nn.Linear(d_model, d_model)
+        self.kv_linear = nn.Linear(d_model, d_model * 2)
+        self.attn_drop = nn.Dropout(attn_drop)
+        self.proj = nn.Linear(d_model, d_model)
+        self.proj_drop = nn.Dropout(proj_drop)
+        self.q_norm = nn.Identity()
+        self.k_norm = nn.Identity()
+
+    def _attend(self, x2d: torch.Tensor, cond: torch.Tensor, mask, B: int) -> torch.Tensor:
+        """Returns the attention output [B*N, C] before ``proj``."""
+        C, h, hd = self.d_model, self.num_heads, self.head_dim
+        q = ops.gemm(x2d, self.q_linear.weight, bias=self.q_linear.bias)
+        kv = ops.gemm(_as2d(cond), self.kv_linear.weight, bias=self.kv_linear.bias).view(B, -1, 2, C)
+        k, v = kv.unbind(2)
+        q = q.view(B, -1, h, hd).transpose(1, 2)
+        k = k.reshape(B, -1, h, hd).transpose(1, 2)
+        v = v.reshape(B, -1, h, hd).transpose(1, 2)
+        if mask is not None:
+            if not torch.is_tensor(mask) or mask.ndim != 2:
+                raise NotImplementedError("cross-attention mask must be None or a [B, L] 0/1 tensor")
+            mask = ((1 - mask.to(q.dtype)) * -10000.0)[:, None, None].expand(B, h, 1, -1)
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=0.0, is_causal=False)
+        return o.transpose(1, 2).reshape(-1, C)
+
+    def forward(self, x, cond, mask=None):
+        B, N, C = x.shape
+        o = self._attend(_as2d(x), cond, mask, B)
+        return ops.gemm(o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
+
+
+class SanaMSBlock(nn.Module):
+    """adaLN-single Linear-DiT block: modulate -> LiteLA -> gate+residual -> cross-attention
+    + residual -> modulate -> GLUMBConv -> gate+residual.  Eight GEMM launches with fused
+    bias / SiLU / gate / residual epilogues, plus LN-modulate, linear-attention state/apply and
+    depthwise-GLU kernels."""
+
+    def __init__(self, hidden_size, num_heads, mlp_ratio=4.0, drop_path=0.0, qk_norm=False, attn_type="flash",
+                 ffn_type="mlp", mlp_acts=("silu", "silu", None), linear_head_dim=32, cross_norm=False,
+                 cross_attn_type="flash", **block_kwargs):
+        super().__init__()
+        if attn_type != "linear" or ffn_type != "glumbconv":
+            raise NotImplementedError("SanaMSBlock here covers attn_type='linear' with ffn_type='glumbconv' only")
+        if drop_path != 0.0:
+            raise NotImplementedError("drop_path > 0 (training) is not covered")
+        if cross_attn_type not in ("flash", "linear"):
+            raise ValueError(f"{cross_attn_type} type is not defined.")
+        self.hidden_size = hidden_size
+        self.norm1 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
+        self.attn = LiteLA(hidden_size, hidden_size, heads=hidden_size // linear_head_dim, eps=1e-8, qk_norm=qk_norm)
+        self.cross_attn = MultiHeadCrossAttention(hidden_size, num_heads, qk_norm=cross_norm, **block_kwargs)
+        self.norm2 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
+        self.mlp = GLUMBConv(in_features=hidden_size, hidden_features=int(hidden_size * mlp_ratio),
+                             use_bias=(True, True, False), norm=(None, None, None), act=mlp_acts)
+        self.drop_path = nn.Identity()
+        self.scale_shift_table = nn.Parameter(torch.randn(6, hidden_size) / hidden_size ** 0.5)
+
+    def set_sequence_shard(self, shard: Optional[SequenceShard]) -> None:
+        """Run this block on one rank's slice of the token grid (see sharding.SequenceShard)."""
+        self.attn.seq_shard = shard
+        self.mlp.seq_shard = shard
+
+    @torch.no_grad()
+    def forward(self, x, y, t, mask=None, HW=None, image_rotary_emb=None, **kwargs):
+        if image_rotary_emb is not None:
+            raise NotImplementedError("rotary embeddings are not covered by the CUDA kernels yet")
+        B, N, C = x.shape
+        x2 = _as2d(x.contiguous())
+        table = self.scale_shift_table
+        t = t.reshape(B, 6 * C)
+        attn, mlp, ca = self.attn, self.mlp, self.cross_attn
+        if "forward" in attn.__dict__:
+            # an attention processor was installed on this instance (guidance code does that):
+            # keep its semantics, at the cost of the fused epilogues
+            z = ops.ln_modulate(x, table, t, 0, 1, LN_EPS)
+            a = attn.forward(z, HW=HW, rotary_emb=image_rotary_emb)
+            gate = (table[2][None] + t.reshape(B, 6, C)[:, 2])[:, None]
+            x2 = _as2d((x + gate * a).contiguous())
+        else:
+            z = ops.ln_modulate(x, table, t, 0, 1, LN_EPS)
+            qkv = ops.gemm(_as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
+            o = attn._core(qkv, B, N)
+            x2 = ops.gemm(o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
+        o = ca._attend(x2, y, mask, B)
+        x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
+        z = ops.ln_modulate(x2.view(B, N, C), table, t, 3, 4, LN_EPS)
+        u = mlp._expand(_as2d(z))
+        g = mlp._depthwise_glu(u, B, N, HW)
+        pc = mlp.point_conv.conv
+        x2 = ops.gemm(g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias, gate=(table, t, 5, N),
+                      residual=x2)
+        return x2.view(B, N, C)

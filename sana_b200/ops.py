@@ -1,0 +1,193 @@
+"""Tensor-level wrappers of the C ABI: validate torch tensors, allocate outputs with torch,
+pass raw device pointers and the current CUDA stream to libsana_b200.so.
+
+PyTorch is used here only for device memory and streams; all arithmetic happens in the
+library's CUDA kernels.  Nothing here falls back to torch math.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import SANA_BF16, SANA_F32, GemmEpilogue, SanaLibraryError
+
+HEAD_DIM = 32
+STATE_ROWS = HEAD_DIM + 1
+
+ACT_NONE, ACT_SILU, ACT_RELU_COLS = 0, 1, 2
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return SANA_BF16
+    if dt == torch.float32:
+        return SANA_F32
+    raise SanaLibraryError(f"unsupported dtype {dt}: the kernels exist for bfloat16 and float32 only")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise SanaLibraryError("sana_b200 operators run on CUDA tensors only (no CPU path)")
+
+
+def _rows2d(t: torch.Tensor, what: str) -> Tuple[int, int, int]:
+    """(rows, cols, row stride) of a 2-D tensor whose last dimension is contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise SanaLibraryError(f"{what}: expected a 2-D tensor with contiguous rows, got shape {tuple(t.shape)} "
+                               f"strides {t.stride()}")
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+def ln_modulate(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row: int, scale_row: int,
+                eps: float = 1e-6) -> torch.Tensor:
+    """z = LayerNorm(x) * (1 + scale) + shift with scale/shift = table[row] + t[b, row].
+
+    x [B, N, C]; table [6, C]; t [B, 6*C]."""
+    _need_cuda(x, table, t)
+    B, N, Cc = x.shape
+    x = x.contiguous()
+    table = table.contiguous()
+    t = t.reshape(B, 6 * Cc).contiguous()
+    if table.shape != (6, Cc) or table.dtype != x.dtype or t.dtype != x.dtype:
+        raise SanaLibraryError("ln_modulate: table must be [6, C] and t [B, 6C] in x's dtype")
+    z = torch.empty_like(x)
+    lib = _lib.load()
+    _lib.check(lib.sana_ln_modulate(x.data_ptr(), table.data_ptr(), t.data_ptr(), z.data_ptr(), B, N, Cc,
+                                    shift_row, scale_row, eps, _dtype_code(x.dtype), _stream()), "sana_ln_modulate")
+    return z
+
+
+def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.Tensor:
+    """state[b,h,i,j] = sum_n [v;1][b,n,h,i] * relu(k[b,n,h,j]); k, v are [B*N, H*32] views
+    (e.g. column slices of the qkv projection).  Returns fp32 [B, H, 33, 32]."""
+    _need_cuda(k, v)
+    rk, ck, ldk = _rows2d(k, "la_state k")
+    rv, cv, ldv = _rows2d(v, "la_state v")
+    if rk != B * N or rv != B * N or ck != H * HEAD_DIM or cv != H * HEAD_DIM or ldk != ldv or k.dtype != v.dtype:
+        raise SanaLibraryError("la_state: k and v must be [B*N, H*32] with the same row stride and dtype")
+    lib = _lib.load()
+    ws_bytes = lib.sana_la_state_workspace_bytes(B, N, H)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=k.device)
+    state = torch.empty(B, H, STATE_ROWS, HEAD_DIM, dtype=torch.float32, device=k.device)
+    _lib.check(lib.sana_la_state(k.data_ptr(), v.data_ptr(), ldk, state.data_ptr(), ws.data_ptr(), ws.numel(), B, N, H,
+                                 _dtype_code(k.dtype), _stream()), "sana_la_state")
+    return state
+
+
+def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o[b,n,h,:] = state[b,h,:32] relu(q) / (state[b,h,32] . relu(q) + eps); q [B*N, H*32] view."""
+    _need_cuda(q, state)
+    rq, cq, ldq = _rows2d(q, "la_apply q")
+    if rq != B * N or cq != H * HEAD_DIM:
+        raise SanaLibraryError("la_apply: q must be [B*N, H*32]")
+    if state.shape != (B, H, STATE_ROWS, HEAD_DIM) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise SanaLibraryError("la_apply: state must be contiguous fp32 [B, H, 33, 32]")
+    if out is None:
+        out = torch.empty(B * N, H * HEAD_DIM, dtype=q.dtype, device=q.device)
+    ro, co, ldo = _rows2d(out, "la_apply out")
+    if ro != B * N or co != H * HEAD_DIM or out.dtype != q.dtype:
+        raise SanaLibraryError("la_apply: bad output tensor")
+    lib = _lib.load()
+    _lib.check(lib.sana_la_apply(q.data_ptr(), ldq, state.data_ptr(), out.data_ptr(), ldo, B, N, H, eps,
+                                 _dtype_code(q.dtype), _stream()), "sana_la_apply")
+    return out
+
+
+def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], W: int, H: int, row0: int = 0,
+               halo_top: Optional[torch.Tensor] = None, halo_bot: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """3x3 depthwise conv + bias + SiLU-GLU.  u [rows*W, 2*hid] (channels last, image rows
+    stacked; frames are H rows tall, global row = row0 + local row); weight [2*hid, 1, 3, 3]
+    or [2*hid, 3, 3]; halos [W, 2*hid].  Returns [rows*W, hid]."""
+    _need_cuda(u, weight, bias, halo_top, halo_bot)
+    if u.dim() != 2 or not u.is_contiguous():
+        raise SanaLibraryError("dwconv_glu: u must be a contiguous [rows*W, 2*hid] tensor")
+    T, C2 = u.shape
+    if T % W != 0 or C2 % 2 != 0:
+        raise SanaLibraryError("dwconv_glu: u rows must be a multiple of W and channels even")
+    rows, hid = T // W, C2 // 2
+    weight = weight.reshape(C2, 9).contiguous()
+    if weight.dtype != u.dtype or (bias is not None and (bias.dtype != u.dtype or bias.numel() != C2)):
+        raise SanaLibraryError("dwconv_glu: weight/bias dtype or size mismatch")
+    for hname, h in (("halo_top", halo_top), ("halo_bot", halo_bot)):
+        if h is not None and (h.shape != (W, C2) or h.dtype != u.dtype or not h.is_contiguous()):
+            raise SanaLibraryError(f"dwconv_glu: {hname} must be contiguous [W, 2*hid] in u's dtype")
+    out = torch.empty(T, hid, dtype=u.dtype, device=u.device)
+    lib = _lib.load()
+    _lib.check(lib.sana_dwconv_glu(u.data_ptr(), halo_top.data_ptr() if halo_top is not None else None,
+                                   halo_bot.data_ptr() if halo_bot is not None else None, weight.data_ptr(),
+                                   bias.contiguous().data_ptr() if bias is not None else None, out.data_ptr(), rows, W, H,
+                                   row0, hid, _dtype_code(u.dtype), _stream()), "sana_dwconv_glu")
+    return out
+
+
+def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, gate, residual, out):
+    _need_cuda(a, w, bias, residual, out)
+    M, K, lda = _rows2d(a, "gemm A")
+    Nn, Kw, ldw = _rows2d(w, "gemm W")
+    if Kw != K or w.dtype != a.dtype:
+        raise SanaLibraryError(f"gemm: A is [{M},{K}] but W is [{Nn},{Kw}] ({a.dtype} vs {w.dtype})")
+    if out is None:
+        out = torch.empty(M, Nn, dtype=a.dtype, device=a.device)
+    Mo, No, ldo = _rows2d(out, "gemm out")
+    if Mo != M or No != Nn or out.dtype != a.dtype:
+        raise SanaLibraryError("gemm: bad output tensor")
+    ep = GemmEpilogue()
+    keep = []
+    if bias is not None:
+        if bias.numel() != Nn or bias.dtype != a.dtype:
+            raise SanaLibraryError("gemm: bias must be [N] in A's dtype")
+        bias = bias.contiguous()
+        keep.append(bias)
+        ep.bias = bias.data_ptr()
+    ep.act = act
+    ep.relu_cols = relu_cols
+    ep.rows_per_batch = 1
+    if gate is not None:
+        table, t, row, rows_per_batch = gate
+        if table.shape != (6, Nn) or t.numel() % (6 * Nn) != 0 or table.dtype != a.dtype or t.dtype != a.dtype:
+            raise SanaLibraryError("gemm: gate table must be [6, N] and t [B, 6N] in A's dtype")
+        if (M + rows_per_batch - 1) // rows_per_batch > t.numel() // (6 * Nn):
+            raise SanaLibraryError("gemm: gate t has fewer batch rows than M / rows_per_batch")
+        table, t = table.contiguous(), t.contiguous()
+        keep += [table, t]
+        ep.gate_table, ep.gate_t, ep.gate_row, ep.rows_per_batch = table.data_ptr(), t.data_ptr(), row, rows_per_batch
+    if residual is not None:
+        Mr, Nr, ldr = _rows2d(residual, "gemm residual")
+        if Mr != M or Nr != Nn or residual.dtype != a.dtype:
+            raise SanaLibraryError("gemm: residual must be [M, N] in A's dtype")
+        ep.residual, ep.ldr = residual.data_ptr(), ldr
+    lib = _lib.load()
+    _lib.check(getattr(lib, fn_name)(a.data_ptr(), lda, w.data_ptr(), ldw, out.data_ptr(), ldo, M, Nn, K, C.byref(ep),
+                                     _dtype_code(a.dtype), _stream()), fn_name)
+    return out
+
+
+def gemm(a, w, bias=None, act: int = ACT_NONE, relu_cols: int = 0, gate=None, residual=None, out=None) -> torch.Tensor:
+    """out = epilogue(a @ w.T); a [M, K], w [N, K] (nn.Linear layout).
+
+    epilogue: +bias, activation (ACT_SILU, or ACT_RELU_COLS on the first ``relu_cols``
+    columns), * gate, + residual.  ``gate`` = (scale_shift_table [6, N], t [B, 6N], row,
+    rows_per_batch).  bf16 runs the tcgen05 tensor-core kernel, fp32 the SIMT kernel."""
+    return _gemm("sana_gemm", a, w, bias, act, relu_cols, gate, residual, out)
+
+
+def gemm_simt(a, w, bias=None, act: int = ACT_NONE, relu_cols: int = 0, gate=None, residual=None, out=None):
+    """Same contract as :func:`gemm`, always the SIMT kernel (device-side cross-check)."""
+    return _gemm("sana_gemm_simt", a, w, bias, act, relu_cols, gate, residual, out)
+
+
+def take_gemm_device_status() -> int:
+    """Code recorded by a timed-out wait inside the tensor-core GEMM (0 = none).  Synchronises."""
+    v = C.c_int(0)
+    lib = _lib.load()
+    _lib.check(lib.sana_gemm_take_device_status(C.byref(v)), "sana_gemm_take_device_status")
+    return v.value

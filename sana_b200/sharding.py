@@ -1,0 +1,113 @@
+"""Partitioning of the Linear-DiT block over the GPUs of one node.
+
+Two ways to split, both one process per GPU:
+
+* by batch (independent images): no communication in the forward;
+* by sequence (long token grids): tokens are row-major ``(frame, row, col)``; the
+  ``frames * H`` image rows are cut into contiguous, balanced ranges.  Per block this needs
+  one fp32 all-reduce of the linear-attention state ``[B, h, 33, 32]`` (the state is a plain
+  sum over tokens) and, for the 3x3 depthwise conv, one image row of halo from each
+  neighbour whose boundary row lies inside the same frame.
+
+Upstream has context parallelism only for its video/GDN nets
+(diffusion/distributed/context_parallel/: contiguous rank groups config.py:155-178, halo
+exchange halo_exchange.py:44-127); plain LiteLA has no sequence-parallel path upstream.  The
+halo exchange here follows the same contract (neighbour p2p, zero padding at the ends) at
+row instead of frame granularity.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def row_partition(total_rows: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous balanced [start, end) ranges; the first ``total_rows % world`` ranks get one
+    extra row."""
+    if world <= 0 or total_rows < world:
+        raise ValueError(f"cannot split {total_rows} rows over {world} ranks")
+    base, extra = divmod(total_rows, world)
+    out, s = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((s, s + n))
+        s += n
+    return out
+
+
+def batch_partition(batch: int, world: int) -> List[Tuple[int, int]]:
+    if batch % world != 0:
+        raise ValueError(f"batch {batch} is not divisible by {world} ranks")
+    per = batch // world
+    return [(r * per, (r + 1) * per) for r in range(world)]
+
+
+@dataclass
+class SequenceShard:
+    """This rank's slice of a ``(frames, H, W)`` token grid (``frames`` = 1 for an image)."""
+
+    frames: int
+    H: int
+    W: int
+    rank: int
+    world: int
+    group: Optional[dist.ProcessGroup] = None
+
+    def __post_init__(self):
+        self.ranges = row_partition(self.frames * self.H, self.world)
+        self.row0, self.row1 = self.ranges[self.rank]
+
+    @property
+    def rows(self) -> int:
+        return self.row1 - self.row0
+
+    @property
+    def tokens(self) -> int:
+        return self.rows * self.W
+
+    @property
+    def token_range(self) -> Tuple[int, int]:
+        return self.row0 * self.W, self.row1 * self.W
+
+    def needs_top(self) -> bool:
+        """True when the row above this shard's first row belongs to the same frame."""
+        return self.row0 % self.H != 0
+
+    def needs_bot(self) -> bool:
+        return self.row1 % self.H != 0
+
+    # ---- collectives -------------------------------------------------------------------
+    def allreduce_state(self, state: torch.Tensor) -> torch.Tensor:
+        """Sums the per-rank partial linear-attention states in place (fp32)."""
+        if self.world > 1:
+            dist.all_reduce(state, op=dist.ReduceOp.SUM, group=self.group)
+        return state
+
+    def exchange_halo(self, u: torch.Tensor) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """u [rows*W, C2] local rows.  Returns (halo_top, halo_bot) = the neighbour's last /
+        first row ([W, C2]) where that row is in the same frame, else None."""
+        W = self.W
+        top = torch.empty(W, u.shape[1], dtype=u.dtype, device=u.device) if self.needs_top() else None
+        bot = torch.empty(W, u.shape[1], dtype=u.dtype, device=u.device) if self.needs_bot() else None
+        if self.world == 1:
+            return top, bot
+        ops = []
+        peer = lambda r: r if self.group is None else dist.get_global_rank(self.group, r)
+        if self.needs_top():  # my first row is the neighbour's halo_bot and vice versa
+            ops.append(dist.P2POp(dist.isend, u[:W].contiguous(), peer(self.rank - 1), self.group))
+            ops.append(dist.P2POp(dist.irecv, top, peer(self.rank - 1), self.group))
+        if self.needs_bot():
+            ops.append(dist.P2POp(dist.isend, u[-W:].contiguous(), peer(self.rank + 1), self.group))
+            ops.append(dist.P2POp(dist.irecv, bot, peer(self.rank + 1), self.group))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        return top, bot
+
+    def scatter_tokens(self, x_full: torch.Tensor) -> torch.Tensor:
+        """[B, N, C] full sequence -> this rank's [B, tokens, C] slice (a copy)."""
+        a, b = self.token_range
+        return x_full[:, a:b].contiguous()

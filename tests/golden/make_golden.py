@@ -1,0 +1,133 @@
+"""Generates tests/golden/*.pt by running the UNMODIFIED upstream modules on CPU.
+
+Run on a machine with a checkout of NVlabs/Sana:
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+Each fixture stores the seeded inputs, the parameters (upstream state-dict keys) and the
+outputs of upstream's LiteLA / GLUMBConv / SanaMSBlock forward, in fp32 and (for the block)
+bf16, at shapes small enough to commit (a few hundred KB in total).  Full-size
+configurations are pinned through sub-sampled outputs: the inputs are regenerated from the
+seed by sana_b200.synthetic, only every `stride`-th token row of the output is stored.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from ref_loader import load_reference, set_fp32_attention  # noqa: E402
+
+from sana_b200 import synthetic  # noqa: E402
+
+
+def _block(R, C, heads, params, dtype):
+    blk = R.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(params, strict=True)
+    set_fp32_attention(blk)
+    return blk.to(dtype)
+
+
+def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False):
+    hid = int(C * 2.5)
+    shape = synthetic.BlockShape(name, C, heads, B, tuple(HW), text_len=L)
+    params = synthetic.make_block_params(C, hid, seed, std=0.05)
+    x, y, t = synthetic.make_block_inputs(shape, seed=seed, std=0.05, text_dim=96)
+    mask = None
+    if with_mask:
+        mask = torch.ones(B, L)
+        for b in range(B):
+            mask[b, L - 1 - b:] = 0
+    out = {"C": C, "heads": heads, "B": B, "HW": tuple(HW), "L": L, "params": params, "x": x, "y": y, "t": t,
+           "mask": mask}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            blk = _block(R, C, heads, params, dt)
+            xx, yy, tt = x.to(dt), y.to(dt), t.to(dt)
+            # branch outputs: what LiteLA.forward / GLUMBConv.forward return inside the block
+            mod = (blk.scale_shift_table[None] + tt.reshape(B, 6, -1)).chunk(6, dim=1)
+            z1 = R.t2i_modulate(blk.norm1(xx), mod[0], mod[1])
+            out[f"attn_in_{tag}"] = z1
+            out[f"attn_out_{tag}"] = blk.attn(z1, HW=tuple(HW))
+            out[f"mlp_out_{tag}"] = blk.mlp(z1, HW=tuple(HW))  # GLUMBConv on the same modulated input
+            out[f"cross_out_{tag}"] = blk.cross_attn(xx, yy, mask)
+            out[f"block_out_{tag}"] = blk(xx, yy, tt, mask, tuple(HW))
+    return out
+
+
+def litela_cfg1_case(R, stride=64):
+    x, p = synthetic.make_litela_cfg1(seed=0)
+    C = x.shape[-1]
+    m = R.LiteLA(C, C, heads=C // 32, eps=1e-8).eval()
+    m.load_state_dict(p, strict=True)
+    set_fp32_attention(m)
+    with torch.no_grad():
+        o32 = m(x, HW=(32, 32))
+        m64 = m.double()
+        # fp64 golden: upstream's .float() inside attn_matmul is bypassed by clearing the flag
+        for mod in m64.modules():
+            mod.fp32_attention = False
+        o64 = m64(x.double(), HW=(32, 32))
+    return {"stride": stride, "out_f32_rows": o32[:, ::stride].clone(), "out_f64_rows": o64[:, ::stride].clone(),
+            "out_f32_absmax": o32.abs().max().item(), "out_f32_sum": o32.double().sum().item()}
+
+
+def block_cfg2_case(R, stride=256):
+    shp = synthetic.CFG2
+    C, hid = shp.hidden, shp.ffn_hidden
+    params = synthetic.make_block_params(C, hid, seed=0)
+    x, y, t = synthetic.make_block_inputs(shp, seed=0)
+    out = {"stride": stride}
+    with torch.no_grad():
+        # golden: fp32 math on the bf16-rounded tensors; native: upstream run in bf16
+        pb = {k: v.bfloat16() for k, v in params.items()}
+        xb, yb, tb = x.bfloat16(), y.bfloat16(), t.bfloat16()
+        blk = _block(R, C, shp.cross_heads, {k: v.float() for k, v in pb.items()}, torch.float32)
+        xx, yy, tt = xb.float(), yb.float(), tb.float()
+        mod = (blk.scale_shift_table[None] + tt.reshape(shp.batch, 6, -1)).chunk(6, dim=1)
+        z1 = R.t2i_modulate(blk.norm1(xx), mod[0], mod[1]).bfloat16().float()
+        out["attn_in_rows"] = z1[:, ::stride].clone()
+        out["attn_out_golden_rows"] = blk.attn(z1, HW=shp.grid)[:, ::stride].clone()
+        out["mlp_out_golden_rows"] = blk.mlp(z1, HW=shp.grid)[:, ::stride].clone()
+        full = blk(xx, yy, tt, None, shp.grid)
+        out["block_out_golden_rows"] = full[:, ::stride].clone()
+        out["block_out_golden_absmax"] = full.abs().max().item()
+        blk16 = _block(R, C, shp.cross_heads, pb, torch.bfloat16)
+        full16 = blk16(xb, yb, tb, None, shp.grid)
+        out["block_out_bf16_rows"] = full16[:, ::stride].clone()
+    return out
+
+
+def video_case(R, seed=3):
+    """3-tuple HW (per-frame depthwise conv), small."""
+    return small_block_case(R, "video", 64, 4, 1, (3, 5, 8), 7, seed)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    R = load_reference(a.ref)
+    cases = {
+        "small_block_a": small_block_case(R, "a", 64, 4, 2, (6, 5), 9, seed=1),
+        "small_block_masked": small_block_case(R, "m", 64, 2, 2, (4, 7), 11, seed=2, with_mask=True),
+        "small_block_video": video_case(R),
+        "litela_cfg1": litela_cfg1_case(R),
+        "block_cfg2": block_cfg2_case(R),
+    }
+    for name, c in cases.items():
+        path = os.path.join(HERE, name + ".pt")
+        torch.save(c, path)
+        print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()
