@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the Linear-DiT block hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload stack|seqpar]
+
+Default workload ("stack"): the Sana-1.6B transformer stack - 20 SanaMSBlocks, hidden 2240,
+70 linear-attention heads x 32, FFN hidden 5600, bf16, 128x128 latent grid = 16 384 tokens,
+300 text tokens - at global batch 8, batch-data-parallel over N GPUs (8/N images per GPU, no
+collective in the forward; "strong" scaling).  One step = one forward of the stack over this
+rank's images.  value = block-tokens/s of the whole job = 8 * 16384 * 20 / step time.
+
+"seqpar": one block on a 21x45x80 = 75 600-token grid, rows sharded over the N GPUs
+(linear-attention state all-reduce + one-row conv halos); value = tokens/s of the block.
+
+Timing: W >= 3 warm-up steps, then K steps between barrier + synchronize, CUDA events on the
+compute stream, max over ranks.  Every step reads > 3 GB of weights and activations (inputs
+larger than the 126 MB L2), so no explicit L2 flush is needed.
+
+--impl reference times the CPU restatement of upstream's block (oracle/) on the host cores
+(upstream is pure PyTorch; its own modules cannot travel to a box without a checkout, the
+restatement is pinned bit-for-bit to them by the golden fixtures).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "Linear-DiT block tokens/s, Sana-1.6B width, 16K tokens"
+UNIT = "block-tokens/s"
+C, HEADS, HID, DEPTH, GRID, TEXT = 2240, 20, 5600, 20, (128, 128), 300
+GLOBAL_BATCH = 8
+SEQPAR_GRID = (21, 45, 80)
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists for that shape).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def block_roofline_seconds(T: int, B: int, peaks: dict) -> float:
+    """Serial sum of per-kernel bounds for one block: tensor time of the GEMM FLOPs plus HBM
+    time of the bandwidth-bound kernels (linear-attention core 4*T*C*e + depthwise-GLU 3*T*hid*e)."""
+    f_gemm = 27.0 * T * C * C + 4.0 * B * TEXT * C * C + 4.0 * T * TEXT * C
+    bytes_bw = 11.5 * T * C * 2
+    return f_gemm / (peaks["tflops"] * 1e12) + bytes_bw / (peaks["hbm_gbs"] * 1e9)
+
+
+def load_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"tflops": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "tflops_burst": float(d["bf16_tflops"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake": 0x80, "sync_boost": 0x10}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                r = get(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_block_tokens_per_s(tokens_grid=(32, 32), budget_s: float = 12.0, max_runs: int = 20):
+    """Times the oracle's SanaMSBlock forward (fp32, all host threads) on a bounded sample."""
+    from oracle import sana_oracle as O
+    from sana_b200 import synthetic
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    shp = synthetic.BlockShape("cpu", C, HEADS, 1, tuple(tokens_grid))
+    params = synthetic.make_block_params(C, HID, seed=0)
+    x, y, t = synthetic.make_block_inputs(shp, seed=0)
+    with torch.no_grad():
+        O.sana_ms_block_forward(x, y, t, params, HEADS, shp.grid)  # warm-up
+        times = []
+        t_begin = time.perf_counter()
+        while len(times) < max_runs and (time.perf_counter() - t_begin < budget_s or len(times) < 2):
+            t0 = time.perf_counter()
+            O.sana_ms_block_forward(x, y, t, params, HEADS, shp.grid)
+            times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return shp.tokens / med, threads, f"1 block, fp32, {shp.tokens} tokens ({tokens_grid[0]}x{tokens_grid[1]} grid) at 1.6B width, median of {len(times)} runs"
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import sana_oracle as O
+    from sana_b200 import synthetic
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    grid = (64, 64)  # 4096 tokens per step: a bounded sample of the 16 384-token workload
+    shp = synthetic.BlockShape("cpu", C, HEADS, 1, grid)
+    params = synthetic.make_block_params(C, HID, seed=0)
+    x, y, t = synthetic.make_block_inputs(shp, seed=0)
+    with torch.no_grad():
+        for _ in range(max(1, min(args.warmup, 2))):
+            O.sana_ms_block_forward(x, y, t, params, HEADS, grid)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            O.sana_ms_block_forward(x, y, t, params, HEADS, grid)
+        dt = time.perf_counter() - t0
+    val = shp.tokens * args.steps / dt
+    sample = f"1 block x {shp.tokens} tokens (64x64 grid) per step, fp32, CPU restatement of upstream's block"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg3: Sana-1.6B stack (20 blocks, hidden 2240, 16384 tokens, batch 8)", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
+    ap.add_argument("--depth", type=int, default=DEPTH)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+
+    import sana_b200
+    from sana_b200 import ops, sharding, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    dt = torch.bfloat16
+    peaks = load_peaks()
+
+    if args.workload == "stack":
+        depth = args.depth
+        b0, b1 = sharding.batch_partition(args.batch, world)[rank]
+        Bl = b1 - b0
+        grid, tokens = GRID, GRID[0] * GRID[1]
+        shard = None
+        total_units = args.batch * tokens * depth
+        workload = (f"cfg3: Sana-1.6B stack, {depth} SanaMSBlocks, hidden {C}, {C // 32} LA heads x 32, FFN {HID}, "
+                    f"{GRID[0]}x{GRID[1]} grid = {tokens} tokens, global batch {args.batch}")
+        parallelism = f"dp{world}"
+        scaling = "strong"
+    else:
+        depth = 1
+        Bl = 1
+        shard = sharding.SequenceShard(*SEQPAR_GRID, rank, world)
+        grid, tokens = SEQPAR_GRID, shard.tokens
+        total_units = SEQPAR_GRID[0] * SEQPAR_GRID[1] * SEQPAR_GRID[2]
+        workload = (f"cfg4: one SanaMSBlock, hidden {C}, 21x45x80 = 75600 tokens, rows sharded over {world} GPUs "
+                    f"(state all-reduce + one-row conv halo)")
+        parallelism = f"sp{world}"
+        scaling = "strong"
+
+    stack = sana_b200.BlockStack(C, HEADS, depth).eval()
+    stack = stack.to(device=dev, dtype=dt)
+    for i, blk in enumerate(stack.blocks):
+        blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, i, 0.02, dt, dev), strict=True)
+    stack.set_sequence_shard(shard)
+
+    # host-resident inputs (pinned) for the end-to-end leg; device copies for the kernel leg
+    g = torch.Generator().manual_seed(1234 + rank)
+    x_h = torch.randn(Bl, tokens, C, generator=g).to(dt).pin_memory()
+    y_h = torch.randn(Bl, TEXT, C, generator=g).to(dt).pin_memory()
+    t_h = (torch.randn(Bl, 6 * C, generator=g) * 0.1).to(dt).pin_memory()
+    out_h = torch.empty(Bl, tokens, C, dtype=dt).pin_memory()
+    x_d, y_d, t_d = x_h.to(dev), y_h.to(dev), t_h.to(dev)
+
+    def step():
+        return stack(x_d, y_d, t_d, None, grid)
+
+    def step_e2e():
+        xd = x_h.to(dev, non_blocking=True)
+        yd = y_h.to(dev, non_blocking=True)
+        td = t_h.to(dev, non_blocking=True)
+        out_h.copy_(stack(xd, yd, td, None, grid), non_blocking=True)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        sync_all()
+        return ms.item()
+
+    for _ in range(args.warmup):
+        step()
+    ops.counters.reset()
+    ops.counters.gemm_timing = True
+    with ClockSampler(local) as clk:
+        total_ms = timed(step, args.steps)
+    ops.counters.gemm_timing = False
+    launches = ops.counters.launches
+    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in ops.counters.gemm_events)
+    gemm_flops = sum(f for _, _, f in ops.counters.gemm_events)
+    n_gemm = len(ops.counters.gemm_events)
+    status = ops.take_gemm_device_status()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        value = total_units / (ms_per_step * 1e-3)
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        T_local = Bl * tokens
+        roof_s = block_roofline_seconds(T_local, Bl, peaks) * depth
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload, "parallelism": parallelism, "per_gpu_batch": Bl,
+                       "l2": "inputs larger than L2 (>3 GB of weights and activations per step)",
+                       "cross_attention_core": "torch SDPA (projections on the tcgen05 GEMM)"},
+            "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel (tcgen05, all 8 projections of a block)",
+                         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"], "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
+                         "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
+                         "share_of_step": gemm_ms / total_ms, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+            "block_roofline": {"t_roof_ms_per_step": roof_s * 1e3, "frac": roof_s * 1e3 / ms_per_step,
+                               "formula": "F_gemm/P_tensor + 11.5*T*C*e/BW_hbm, per block"},
+            "e2e": {"value": total_units / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": x_h.nbytes + y_h.nbytes + t_h.nbytes, "d2h_bytes_per_step": out_h.nbytes,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "gemm_device_status": status, "clocks": clk.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, sample = cpu_block_tokens_per_s()
+            out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

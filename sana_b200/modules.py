@@ -282,3 +282,24 @@ class SanaMSBlock(nn.Module):
         x2 = ops.gemm(g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias, gate=(table, t, 5, N),
                       residual=x2)
         return x2.view(B, N, C)
+
+
+class BlockStack(nn.Module):
+    """``depth`` SanaMSBlocks applied in sequence with a shared (y, t, mask, HW): the block loop
+    of upstream's SanaMS.forward (diffusion/model/nets/sana_multi_scale.py:368-383)."""
+
+    def __init__(self, hidden_size, num_heads, depth, mlp_ratio=2.5, **block_kwargs):
+        super().__init__()
+        self.blocks = nn.ModuleList([
+            SanaMSBlock(hidden_size, num_heads, mlp_ratio=mlp_ratio, attn_type="linear", ffn_type="glumbconv",
+                        **block_kwargs) for _ in range(depth)])
+
+    def set_sequence_shard(self, shard: Optional[SequenceShard]) -> None:
+        for b in self.blocks:
+            b.set_sequence_shard(shard)
+
+    @torch.no_grad()
+    def forward(self, x, y, t, mask=None, HW=None, **kwargs):
+        for block in self.blocks:
+            x = block(x, y, t, mask, HW, **kwargs)
+        return x

@@ -20,6 +20,23 @@ STATE_ROWS = HEAD_DIM + 1
 ACT_NONE, ACT_SILU, ACT_RELU_COLS = 0, 1, 2
 
 
+class _Counters:
+    """Kernel launches issued through this module (the benchmark reports them) and, when
+    ``gemm_timing`` is on, CUDA-event pairs around every tensor-core GEMM launch."""
+
+    def __init__(self):
+        self.launches = 0
+        self.gemm_timing = False
+        self.gemm_events = []  # (start, end, flops)
+
+    def reset(self):
+        self.launches = 0
+        self.gemm_events = []
+
+
+counters = _Counters()
+
+
 def _dtype_code(dt: torch.dtype) -> int:
     if dt == torch.bfloat16:
         return SANA_BF16
@@ -62,6 +79,7 @@ def ln_modulate(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row
     lib = _lib.load()
     _lib.check(lib.sana_ln_modulate(x.data_ptr(), table.data_ptr(), t.data_ptr(), z.data_ptr(), B, N, Cc,
                                     shift_row, scale_row, eps, _dtype_code(x.dtype), _stream()), "sana_ln_modulate")
+    counters.launches += 1
     return z
 
 
@@ -79,6 +97,7 @@ def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.
     state = torch.empty(B, H, STATE_ROWS, HEAD_DIM, dtype=torch.float32, device=k.device)
     _lib.check(lib.sana_la_state(k.data_ptr(), v.data_ptr(), ldk, state.data_ptr(), ws.data_ptr(), ws.numel(), B, N, H,
                                  _dtype_code(k.dtype), _stream()), "sana_la_state")
+    counters.launches += 2  # partial states + fixed-order reduction
     return state
 
 
@@ -99,6 +118,7 @@ def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: 
     lib = _lib.load()
     _lib.check(lib.sana_la_apply(q.data_ptr(), ldq, state.data_ptr(), out.data_ptr(), ldo, B, N, H, eps,
                                  _dtype_code(q.dtype), _stream()), "sana_la_apply")
+    counters.launches += 1
     return out
 
 
@@ -126,6 +146,7 @@ def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
                                    halo_bot.data_ptr() if halo_bot is not None else None, weight.data_ptr(),
                                    bias.contiguous().data_ptr() if bias is not None else None, out.data_ptr(), rows, W, H,
                                    row0, hid, _dtype_code(u.dtype), _stream()), "sana_dwconv_glu")
+    counters.launches += 1
     return out
 
 
@@ -166,8 +187,16 @@ def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, 
             raise SanaLibraryError("gemm: residual must be [M, N] in A's dtype")
         ep.residual, ep.ldr = residual.data_ptr(), ldr
     lib = _lib.load()
+    timed = counters.gemm_timing and fn_name == "sana_gemm" and a.dtype == torch.bfloat16
+    if timed:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     _lib.check(getattr(lib, fn_name)(a.data_ptr(), lda, w.data_ptr(), ldw, out.data_ptr(), ldo, M, Nn, K, C.byref(ep),
                                      _dtype_code(a.dtype), _stream()), fn_name)
+    if timed:
+        e1.record()
+        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K))
+    counters.launches += 1
     return out
 
 

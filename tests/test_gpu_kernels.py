@@ -1,0 +1,213 @@
+"""Kernel-level parity on a B200: every C-ABI entry point against the CPU oracle on the same
+seeded inputs.  Tolerances (normalised max error, max|a-ref|/max|ref|): fp32 <= 1e-5; bf16
+kernels are compared with the oracle evaluated in fp64 on the bf16-rounded inputs, where
+the only differences are the fp32 accumulation order and one bf16 rounding of the output
+(<= 2^-8 relative = 3.9e-3; the block-level budget is 2e-2)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import sana_oracle as O
+from sana_b200 import ops
+
+from conftest import nmax_err
+
+pytestmark = pytest.mark.gpu
+
+BF16_OUT = 5e-3  # one bf16 rounding of the output plus accumulation-order noise
+DEV = "cuda"
+
+
+def _r(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+# ------------------------------------------------------------------ LN + modulate
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
+@pytest.mark.parametrize("B,N,C", [(2, 37, 64), (1, 130, 1152), (3, 9, 2240), (1, 5, 4096)])
+def test_ln_modulate(dt, tol, B, N, C):
+    x, table, t = _r(B, N, C, seed=1, scale=2.0) + 0.3, _r(6, C, seed=2, scale=0.1), _r(B, 6 * C, seed=3, scale=0.5)
+    xd, td, tt = x.to(dt), table.to(dt), t.to(dt)
+    for (sh, sc) in ((0, 1), (3, 4)):
+        z = ops.ln_modulate(xd.to(DEV), td.to(DEV), tt.to(DEV), sh, sc)
+        m = (td.double()[None] + tt.double().reshape(B, 6, C))
+        ref = O.t2i_modulate(O.layer_norm(xd.double()), m[:, sh:sh + 1], m[:, sc:sc + 1])
+        assert z.dtype == dt and nmax_err(z, ref) < tol
+
+
+# ------------------------------------------------------------------ linear attention core
+def _la_ref(q, k, v, eps):
+    """fp64 oracle on token-major [B, N, h, 32] tensors."""
+    st = O.lite_la_state(torch.relu(k.double()), v.double())
+    return st, O.lite_la_apply(torch.relu(q.double()), st, eps)
+
+
+@pytest.mark.parametrize("dt,tol_state,tol_out", [(torch.float32, 1e-5, 1e-5), (torch.bfloat16, 1e-5, BF16_OUT)])
+@pytest.mark.parametrize("B,N,H", [(1, 16, 1), (2, 100, 3), (1, 1024, 36), (1, 33, 9), (2, 777, 10), (1, 4096, 70)])
+def test_la_state_apply(dt, tol_state, tol_out, B, N, H):
+    C = H * 32
+    qkv = _r(B * N, 3 * C, seed=N + H).to(dt)
+    q, k, v = (qkv[:, i * C:(i + 1) * C].reshape(B, N, H, 32) for i in range(3))
+    st_ref, o_ref = _la_ref(q, k, v, 1e-8)
+    d = qkv.to(DEV)
+    state = ops.la_state(d[:, C:2 * C], d[:, 2 * C:], B, N, H)
+    assert state.shape == (B, H, 33, 32) and state.dtype == torch.float32
+    assert nmax_err(state, st_ref) < tol_state
+    out = ops.la_apply(d[:, :C], state, B, N, H, 1e-8)
+    assert out.dtype == dt and nmax_err(out.reshape(B, N, H, 32), o_ref) < tol_out
+    # bit-reproducible (fixed reduction order)
+    state2 = ops.la_state(d[:, C:2 * C], d[:, 2 * C:], B, N, H)
+    assert torch.equal(state, state2)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_la_all_negative_query_gives_zero(dt):
+    B, N, H = 1, 48, 2
+    qkv = _r(B * N, 3 * 64, seed=5).to(dt)
+    qkv[7, :64] = -qkv[7, :64].abs() - 0.1
+    d = qkv.to(DEV)
+    state = ops.la_state(d[:, 64:128], d[:, 128:], B, N, H)
+    out = ops.la_apply(d[:, :64], state, B, N, H, 1e-8)
+    assert torch.all(out[7] == 0) and torch.isfinite(out).all()
+
+
+def test_la_state_is_additive_over_token_shards():
+    """The sequence-parallel identity: states of disjoint token ranges add up."""
+    B, N, H = 1, 1000, 4
+    qkv = _r(N, 3 * 128, seed=9).bfloat16().to(DEV)
+    full = ops.la_state(qkv[:, 128:256], qkv[:, 256:], B, N, H)
+    parts = sum(ops.la_state(qkv[a:b, 128:256], qkv[a:b, 256:], B, b - a, H) for a, b in ((0, 336), (336, 672), (672, 1000)))
+    assert nmax_err(parts, full) < 1e-6
+
+
+# ------------------------------------------------------------------ depthwise conv + GLU
+def _dw_ref(u, w, b, frames, H, W):
+    """fp64 oracle: per-frame conv2d + chunk + SiLU-GLU, channels-last in/out."""
+    C2 = u.shape[-1]
+    x = u.double().reshape(frames, H, W, C2).permute(0, 3, 1, 2)
+    y = F.conv2d(x, w.double().reshape(C2, 1, 3, 3), None if b is None else b.double(), padding=1, groups=C2)
+    a, g = torch.chunk(y, 2, dim=1)
+    return (a * F.silu(g)).permute(0, 2, 3, 1).reshape(frames * H * W, C2 // 2)
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
+@pytest.mark.parametrize("frames,H,W,hid,bias", [(1, 6, 5, 8, True), (2, 4, 7, 160, True), (3, 5, 8, 72, False),
+                                                  (1, 32, 32, 2880, True), (4, 9, 33, 200, True), (1, 70, 17, 64, True)])
+def test_dwconv_glu(dt, tol, frames, H, W, hid, bias):
+    C2 = 2 * hid
+    u = _r(frames * H * W, C2, seed=hid + W).to(dt)
+    w = _r(C2, 1, 3, 3, seed=1, scale=0.3).to(dt)
+    b = _r(C2, seed=2, scale=0.2).to(dt) if bias else None
+    ref = _dw_ref(u, w, b, frames, H, W)
+    out = ops.dwconv_glu(u.to(DEV), w.to(DEV), b.to(DEV) if bias else None, W, H)
+    assert out.dtype == dt and out.shape == (frames * H * W, hid)
+    assert nmax_err(out, ref) < tol
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
+def test_dwconv_glu_row_shards_with_halo(dt, tol):
+    """Row-range calls with neighbour halos reproduce the full-grid result (frames 3 x 5 rows;
+    the cuts at rows 4, 5 (a frame boundary), 9 and 13 cover every halo combination)."""
+    frames, H, W, hid = 3, 5, 8, 40
+    C2 = 2 * hid
+    u = _r(frames * H * W, C2, seed=4).to(dt)
+    w = _r(C2, 1, 3, 3, seed=5, scale=0.3).to(dt)
+    b = _r(C2, seed=6, scale=0.2).to(dt)
+    ref = _dw_ref(u, w, b, frames, H, W)
+    ud, wd, bd = u.to(DEV), w.to(DEV), b.to(DEV)
+    rows = ud.reshape(frames * H, W, C2)
+    cuts = [0, 4, 5, 9, 13, 15]
+    outs = []
+    for r0, r1 in zip(cuts, cuts[1:]):
+        top = rows[r0 - 1].contiguous() if r0 % H != 0 else None
+        bot = rows[r1].contiguous() if r1 % H != 0 else None
+        outs.append(ops.dwconv_glu(rows[r0:r1].reshape(-1, C2).contiguous(), wd, bd, W, H, row0=r0, halo_top=top,
+                                   halo_bot=bot))
+    assert nmax_err(torch.cat(outs), ref) < tol
+    # CPU oracle of the same sharded computation agrees with the full-grid oracle
+    o = O.depthwise_glu_rows(u.double().reshape(frames * H, W, C2)[4:9], u.double().reshape(frames * H, W, C2)[3],
+                             u.double().reshape(frames * H, W, C2)[9], w.double(), b.double(), 4, H)
+    assert nmax_err(o.reshape(-1, hid), ref[4 * W:9 * W]) < 1e-12
+
+
+# ------------------------------------------------------------------ projections
+def _gemm_ref(a, w, bias, act, relu_cols, gate, residual):
+    v = a.double() @ w.double().t()
+    if bias is not None:
+        v = v + bias.double()
+    if act == ops.ACT_SILU:
+        v = F.silu(v)
+    elif act == ops.ACT_RELU_COLS:
+        v[:, :relu_cols] = torch.relu(v[:, :relu_cols])
+    if gate is not None:
+        table, t, row, rpb = gate
+        N = w.shape[0]
+        g = table.double()[row][None] + t.double().reshape(-1, 6, N)[:, row]  # [B, N]
+        v = v * g.repeat_interleave(rpb, dim=0)[: v.shape[0]]
+    if residual is not None:
+        v = v + residual.double()
+    return v
+
+
+GEMM_SHAPES = [(128, 128, 64), (200, 136, 72), (1, 8, 8), (300, 448, 2240), (1024, 1152, 1152), (77, 3456, 1152),
+               (4096, 2240, 5600), (513, 520, 200)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_bf16_tensor_core_plain(M, N, K):
+    a, w = _r(M, K, seed=M).bfloat16(), _r(N, K, seed=N + 1, scale=0.05).bfloat16()
+    ref = _gemm_ref(a, w, None, 0, 0, None, None)
+    out = ops.gemm(a.to(DEV), w.to(DEV))
+    torch.cuda.synchronize()
+    assert ops.take_gemm_device_status() == 0
+    assert nmax_err(out, ref) < BF16_OUT
+    simt = ops.gemm_simt(a.to(DEV), w.to(DEV))
+    assert nmax_err(simt, ref) < BF16_OUT
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
+@pytest.mark.parametrize("variant", ["bias", "bias_silu", "relu_cols", "gate_res", "bias_gate_res", "res"])
+def test_gemm_epilogues(dt, tol, variant):
+    B, rpb, N, K = 3, 50, 192, 136
+    M = B * rpb - 7  # last batch element is ragged
+    a, w = _r(M, K, seed=1).to(dt), _r(N, K, seed=2, scale=0.1).to(dt)
+    bias = _r(N, seed=3).to(dt) if "bias" in variant else None
+    act = ops.ACT_SILU if "silu" in variant else (ops.ACT_RELU_COLS if variant == "relu_cols" else 0)
+    relu_cols = 128 if variant == "relu_cols" else 0
+    gate = (_r(6, N, seed=4).to(dt), _r(B, 6 * N, seed=5).to(dt), 2, rpb) if "gate" in variant else None
+    res = _r(M, N, seed=6).to(dt) if "res" in variant else None
+    ref = _gemm_ref(a, w, bias, act, relu_cols, gate, res)
+    dgate = (gate[0].to(DEV), gate[1].to(DEV), gate[2], gate[3]) if gate else None
+    out = ops.gemm(a.to(DEV), w.to(DEV), bias=bias.to(DEV) if bias is not None else None, act=act, relu_cols=relu_cols,
+                   gate=dgate, residual=res.to(DEV) if res is not None else None)
+    assert out.dtype == dt and nmax_err(out, ref) < tol
+    if dt == torch.bfloat16:
+        assert ops.take_gemm_device_status() == 0
+
+
+def test_gemm_strided_operands():
+    """A and the output may be column slices of wider tensors (qkv slices, residual views)."""
+    M, N, K = 160, 64, 96
+    big = _r(M, 3 * K, seed=1).bfloat16().to(DEV)
+    w = _r(N, K, seed=2, scale=0.1).bfloat16().to(DEV)
+    a = big[:, K:2 * K]
+    outbuf = torch.zeros(M, 2 * N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(a, w, out=outbuf[:, N:])
+    ref = _gemm_ref(a.cpu(), w.cpu(), None, 0, 0, None, None)
+    assert nmax_err(outbuf[:, N:], ref) < BF16_OUT and torch.all(outbuf[:, :N] == 0)
+
+
+def test_gemm_full_size_sampled_rows():
+    """The 1.6B-width QKV projection at 16 384 tokens, checked on rows sampled from every
+    128-row tile position against the CPU oracle."""
+    M, N, K = 16384, 6720, 2240
+    g = torch.Generator(device=DEV).manual_seed(0)
+    a = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    w = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    out = ops.gemm(a, w)
+    torch.cuda.synchronize()
+    assert ops.take_gemm_device_status() == 0
+    rows = torch.arange(0, M, 129)[:100]
+    ref = a[rows].cpu().double() @ w.cpu().double().t()
+    assert nmax_err(out[rows], ref) < BF16_OUT
