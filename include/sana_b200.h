@@ -70,6 +70,29 @@ int sana_la_state(const void* k, const void* v, int64_t ld, float* state, void* 
                   int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * sana_la_state for hosts that cannot allocate device memory.  No counterpart upstream: it
+ * exists for callers that may not call cudaMalloc where they run the block - a serving
+ * process whose device memory is a fixed arena owned by another runtime, a plugin sandbox
+ * without allocation calls, a loop that cannot afford the implicit device synchronisation
+ * of cudaMalloc/cudaFree.  Same inputs, output and arithmetic as sana_la_state, but the
+ * per-chunk partial states go to a scratch array built into the library image
+ * (SANA_LA_STATE_NOALLOC_MAX_BYTES of device memory on every GPU that loads the library,
+ * held until the process exits) instead of a caller workspace.  The call itself allocates
+ * and frees nothing.
+ *  - Limit: sana_la_state_workspace_bytes(B, N, H) must not exceed
+ *    SANA_LA_STATE_NOALLOC_MAX_BYTES, otherwise SANA_ERR_INVALID (use sana_la_state).
+ *  - The first call on each device looks up the array's device address (one host-side query,
+ *    no allocation); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call
+ *    left; nothing in it needs clearing because each call overwrites every element it later
+ *    reads.  Two calls that overlap on the GPU (different streams, or different host threads
+ *    on different streams) race on it: serialise them.
+ */
+#define SANA_LA_STATE_NOALLOC_MAX_BYTES (16 * 1024 * 1024)
+int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, float* state, int64_t B, int64_t N,
+                          int64_t H, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * ReLU linear attention, apply + normalise:
  *   o[b, n, h, i] = (sum_j state[b,h,i,j] relu(q[b,n,h,j])) / (sum_j state[b,h,32,j] relu(q[b,n,h,j]) + eps)
  * Replaces `out = torch.matmul(vk, relu(q)); out[:, :, :-1] / (out[:, :, -1:] + eps)` and the

@@ -5,11 +5,13 @@
 // channel indices of the MMA fragments are permuted so that each lane's fragment registers
 // are contiguous channels of a token row, so no shared-memory transpose is needed and the
 // kernels are plain streaming reads at HBM speed.  fp32 kernels are FFMA (parity path).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sana {
 
-constexpr int HD = 32;           // head dimension (upstream linear_head_dim)
+constexpr int HD = 32;          // head dimension (upstream linear_head_dim)
 constexpr int SROWS = HD + 1;    // 32 value rows + ones row
 constexpr int SSIZE = SROWS * HD;  // 1056 floats per head
 
@@ -410,5 +412,84 @@ extern "C" int sana_la_apply(const void* q, int64_t ldq, const float* state, voi
     return fail(SANA_ERR_UNSUPPORTED, "sana_la_apply: unsupported dtype %d", dtype);
   }
   SANA_LAUNCH_CHECK("la_apply kernel");
+  return SANA_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// State reduction for hosts that cannot allocate device memory.
+//
+// sana_la_state needs a scratch buffer for its per-chunk partial states, and somebody has to
+// allocate it.  Some hosts cannot: a serving process whose device memory was carved up front
+// into a fixed arena owned by another runtime, a plugin sandbox that forbids allocation
+// calls, or a loop that must not hit the implicit device synchronisation of
+// cudaMalloc/cudaFree while other streams are busy.  For them the scratch lives in the
+// library image itself: a fixed 16 MiB array in device global memory.  Every GPU that loads
+// the library carries these 16 MiB from load until the process exits, used or not.
+//
+// In host code the array's name is only a host-side handle, not a device address, so the
+// address is fetched once per device with cudaGetSymbolAddress (that device current) and that
+// pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_la_static_scratch[SANA_LA_STATE_NOALLOC_MAX_BYTES / sizeof(float)];
+
+namespace sana {
+static std::mutex g_scratch_mutex;
+static float* g_scratch_ptr[64] = {nullptr};
+
+// First use on a device: resolve the device address of the static scratch array.
+static int static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(SANA_ERR_UNSUPPORTED, "sana_la_state_noalloc: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_la_static_scratch);
+    if (e != cudaSuccess) return cuda_status(e, "cudaGetSymbolAddress(static scratch)");
+    if (p == nullptr) return fail(SANA_ERR_DRIVER, "sana_la_state_noalloc: static scratch has no device address");
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return SANA_OK;
+}
+}  // namespace sana
+
+extern "C" int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, float* state, int64_t B, int64_t N,
+                                     int64_t H, int dtype, void* stream) {
+  SANA_REQUIRE(k && v && state, "sana_la_state_noalloc: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_state_noalloc: B, N, H must be positive");
+  SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_state_noalloc: size out of range");
+  SANA_REQUIRE(ld >= H * HD && ld % 8 == 0, "sana_la_state_noalloc: ld must be >= H*32 and a multiple of 8");
+  SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(state), "sana_la_state_noalloc: pointers must be 16-byte aligned");
+  SANA_REQUIRE(dtype == SANA_BF16 || dtype == SANA_F32, "sana_la_state_noalloc: unsupported dtype %d", dtype);
+  const int64_t need = sana_la_state_workspace_bytes(B, N, H);
+  if (need > (int64_t)SANA_LA_STATE_NOALLOC_MAX_BYTES)
+    return fail(SANA_ERR_INVALID,
+                "sana_la_state_noalloc: this problem needs %lld bytes of scratch but the built-in scratch holds %lld; "
+                "use sana_la_state with a caller-provided workspace",
+                (long long)need, (long long)SANA_LA_STATE_NOALLOC_MAX_BYTES);
+  float* partial = nullptr;
+  int rc = static_scratch(&partial);
+  if (rc) return rc;
+  int Lc, nchunks;
+  la_state_plan(B, N, H, dtype, &Lc, &nchunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Nothing in the scratch has to start at zero: the first launch overwrites every partial
+  // state (all 1056 floats of every (batch, chunk, head)) that the second launch reads.
+  if (dtype == SANA_BF16) {
+    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
+                                                        static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
+                                                        (int)H, Lc, nchunks);
+  } else {
+    dim3 grid(nchunks, (unsigned)H, (unsigned)B);
+    la_state_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(v), ld,
+                                              partial, (int)N, (int)H, Lc, nchunks);
+  }
+  SANA_LAUNCH_CHECK("la_state kernel (static scratch)");
+  const int64_t total = B * H * SSIZE;
+  la_state_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(partial, state, nchunks, H * SSIZE, total);
+  SANA_LAUNCH_CHECK("la_state_reduce kernel (static scratch)");
   return SANA_OK;
 }
