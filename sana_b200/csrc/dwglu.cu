@@ -29,6 +29,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ float fast_silu(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
+}
+
 struct DwArgs {
   const __nv_bfloat16* u;
   const __nv_bfloat16* halo_top;
@@ -40,7 +47,7 @@ struct DwArgs {
   int64_t row0;
 };
 
-__global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const DwArgs p) {
+__global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const DwArgs p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int role = lane >> 4, xs = (lane >> 3) & 1, cv = lane & 7;
@@ -55,9 +62,9 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
   const bool lane_ok = (cvec < nvec) && (x < p.W);
   const int ch = role * p.hid + (min(cvec, nvec - 1) << 3);  // first of this lane's 8 channels
 
-  // per-lane taps: w2[tap][pair] as float2, tap = 3*dy + dx
+  // per-lane taps: w2[tap][pair] as float2, tap = 3*dy + dx; the bias seeds the accumulators
   float2 w2[9][4];
-  float bv[8];
+  float2 bv[4];
   {
     const __nv_bfloat16* wp = p.weight + (int64_t)ch * 9;
 #pragma unroll
@@ -66,40 +73,46 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
       for (int c2 = 0; c2 < 4; ++c2)
         w2[tap][c2] = make_float2(__bfloat162float(wp[(2 * c2) * 9 + tap]), __bfloat162float(wp[(2 * c2 + 1) * 9 + tap]));
 #pragma unroll
-    for (int c = 0; c < 8; ++c) bv[c] = p.bias ? __bfloat162float(p.bias[ch + c]) : 0.f;
+    for (int c2 = 0; c2 < 4; ++c2)
+      bv[c2] = p.bias ? make_float2(__bfloat162float(p.bias[ch + 2 * c2]), __bfloat162float(p.bias[ch + 2 * c2 + 1]))
+                      : make_float2(0.f, 0.f);
   }
 
-  // which input rows exist for this segment: local rows ys-1 .. ye
-  const int fr_first = (int)((p.row0 + ys) % p.H);
-  const int fr_last = (int)((p.row0 + ye - 1) % p.H);
-  const bool need_top = fr_first != 0;
-  const bool need_bot = fr_last != p.H - 1;
-  const int nin = ye - ys + 2;  // input-row slots k = 0 .. nin-1  <->  local row ys-1+k
+  // input-row slots k = 0 .. nin-1  <->  local rows ys-1 .. ye; the first and last slot exist
+  // only when that row lies in the same frame as its neighbour inside the segment
+  const int nin = ye - ys + 2;
+  const int fr_top = (int)((p.row0 + ys + p.H - 1) % p.H);   // frame row of local row ys-1
+  const bool need_top = fr_top != p.H - 1;
+  const bool need_bot = (int)((p.row0 + ye) % p.H) != 0;
+  const int64_t row_elems = (int64_t)p.W * C2;
+  const __nv_bfloat16* top_ptr = !need_top ? nullptr : (ys > 0 ? p.u + (int64_t)(ys - 1) * row_elems : p.halo_top);
+  const __nv_bfloat16* bot_ptr = !need_bot ? nullptr : (ye < p.rows ? p.u + (int64_t)ye * row_elems : p.halo_bot);
+  const __nv_bfloat16* mid_ptr = p.u + (int64_t)ys * row_elems;  // slot 1
 
+  // this thread's (at most two) 16-byte chunks of a staged row: fixed offsets, computed once
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-
-  auto row_ptr = [&](int k) -> const __nv_bfloat16* {
-    const int r = ys - 1 + k;
-    if (k == 0 && !need_top) return nullptr;
-    if (k == nin - 1 && !need_bot) return nullptr;
-    if (r < 0) return p.halo_top;
-    if (r >= p.rows) return p.halo_bot;
-    return p.u + (int64_t)r * p.W * C2;
-  };
+  int64_t src_off[2];
+  uint32_t dst_off[2];
+  bool src_ok[2], has[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int q = tid + i * DW_THREADS;
+    has[i] = q < DW_ROW_CHUNKS;
+    const int px = q >> 4, rem = q & 15, rl = rem >> 3, c = rem & 7;
+    const int gx = x0 - 1 + px;
+    const int gv = blockIdx.x * DW_CV + c;
+    src_ok[i] = has[i] && (gx >= 0) && (gx < p.W) && (gv < nvec);
+    src_off[i] = src_ok[i] ? (int64_t)gx * C2 + rl * p.hid + (gv << 3) : 0;
+    dst_off[i] = q * 16;
+  }
 
   auto issue_row = [&](int k) {
     if (k < nin) {
-      const __nv_bfloat16* rp = row_ptr(k);
+      const __nv_bfloat16* rp = (k == 0) ? top_ptr : ((k == nin - 1) ? bot_ptr : mid_ptr + (int64_t)(k - 1) * row_elems);
       if (rp != nullptr) {
         const uint32_t sbase = smem_base + (k % DW_STAGES) * DW_STAGE_BYTES;
-        for (int q = tid; q < DW_ROW_CHUNKS; q += DW_THREADS) {
-          const int px = q >> 4, rem = q & 15, rl = rem >> 3, c = rem & 7;
-          const int gx = x0 - 1 + px;
-          const int gv = blockIdx.x * DW_CV + c;
-          const bool ok = (gx >= 0) && (gx < p.W) && (gv < nvec);
-          const __nv_bfloat16* src = ok ? rp + (int64_t)gx * C2 + rl * p.hid + (gv << 3) : rp;
-          cp_async_16(sbase + q * 16, src, ok);
-        }
+        cp_async_16(sbase + dst_off[0], rp + src_off[0], src_ok[0]);
+        if (has[1]) cp_async_16(sbase + dst_off[1], rp + src_off[1], src_ok[1]);
       }
     }
     cp_async_commit();
@@ -109,21 +122,23 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
 #pragma unroll
   for (int s = 0; s < 3; ++s)
 #pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2) acc[s][c2] = make_float2(0.f, 0.f);
+    for (int c2 = 0; c2 < 4; ++c2) acc[s][c2] = bv[c2];
 
 #pragma unroll 1
   for (int k = 0; k < DW_STAGES - 1; ++k) issue_row(k);
 
-  // One step: consume input slot k.  PREV/CUR/NEXT are the accumulator slots of output rows
-  // (r-1, r, r+1) for input row r; they rotate with k so no register moves are needed.
+  int fr = fr_top;  // frame row of the input row of the current slot
+  __nv_bfloat16* out_ptr = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + (cvec << 3) + role * 4;  // row of slot k-1's output
+
+  // One step: consume input slot k (local row r = ys-1+k).  PREV/CUR/NEXT are the accumulator
+  // slots of output rows (r-1, r, r+1); they rotate with k so no register moves are needed.
   auto step = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
     cp_async_wait<DW_STAGES - 2>();
     __syncthreads();
     issue_row(k + DW_STAGES - 1);
-    const int r = ys - 1 + k;  // local input row
-    const bool have = row_ptr(k) != nullptr;
-    const int fr = (int)((p.row0 + r + p.H) % p.H);  // frame row of the input row (r may be -1)
+    const bool first = (k == 0), last = (k == nin - 1);
+    const bool have = first ? need_top : (last ? need_bot : true);
     if (have) {
       const unsigned char* sp = smem + (k % DW_STAGES) * DW_STAGE_BYTES + ((lx * 16 + role * 8 + cv) << 4);
       const uint4 vm = *reinterpret_cast<const uint4*>(sp);
@@ -138,7 +153,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
       xp[2] = make_float2(bf16_lo(vp.z), bf16_hi(vp.z)), xp[3] = make_float2(bf16_lo(vp.w), bf16_hi(vp.w));
       // input row r is the row BELOW output r-1 (taps 6..8), the centre of output r (taps 3..5)
       // and the row ABOVE output r+1 (taps 0..2); vertical neighbours must share the frame.
-      if (r - 1 >= ys && r - 1 < ye && fr != 0) {
+      if (k >= 2 && fr != 0) {  // output r-1 is inside the segment
 #pragma unroll
         for (int c2 = 0; c2 < 4; ++c2) {
           acc[PREV][c2] = ffma2(w2[6][c2], xm[c2], acc[PREV][c2]);
@@ -146,7 +161,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
           acc[PREV][c2] = ffma2(w2[8][c2], xp[c2], acc[PREV][c2]);
         }
       }
-      if (r >= ys && r < ye) {
+      if (!first && !last) {
 #pragma unroll
         for (int c2 = 0; c2 < 4; ++c2) {
           acc[CUR][c2] = ffma2(w2[3][c2], xm[c2], acc[CUR][c2]);
@@ -154,7 +169,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
           acc[CUR][c2] = ffma2(w2[5][c2], xp[c2], acc[CUR][c2]);
         }
       }
-      if (r + 1 >= ys && r + 1 < ye && fr != p.H - 1) {
+      if (k + 2 < nin && fr != p.H - 1) {  // output r+1 is inside the segment
 #pragma unroll
         for (int c2 = 0; c2 < 4; ++c2) {
           acc[NEXT][c2] = ffma2(w2[0][c2], xm[c2], acc[NEXT][c2]);
@@ -163,33 +178,30 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
         }
       }
     }
-    // output row r-1 is complete
-    const int ro = r - 1;
-    if (ro >= ys && ro < ye) {
-      float v[8];
-#pragma unroll
-      for (int c2 = 0; c2 < 4; ++c2) {
-        v[2 * c2] = acc[PREV][c2].x + bv[2 * c2];
-        v[2 * c2 + 1] = acc[PREV][c2].y + bv[2 * c2 + 1];
-      }
+    if (k >= 2) {  // output row r-1 = ys + k - 2 is complete
       // value lane keeps channels 0..3 and receives gate 0..3; gate lane keeps 4..7 and receives value 4..7
-      float other[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float send = role == 0 ? v[4 + i] : v[i];
-        other[i] = __shfl_xor_sync(0xffffffffu, send, 16);
-      }
-      float o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[i] = role == 0 ? v[i] * silu(other[i]) : other[i] * silu(v[4 + i]);
+      const float2 keep0 = role == 0 ? acc[PREV][0] : acc[PREV][2];
+      const float2 keep1 = role == 0 ? acc[PREV][1] : acc[PREV][3];
+      const float2 send0 = role == 0 ? acc[PREV][2] : acc[PREV][0];
+      const float2 send1 = role == 0 ? acc[PREV][3] : acc[PREV][1];
+      float2 got0, got1;
+      got0.x = __shfl_xor_sync(0xffffffffu, send0.x, 16);
+      got0.y = __shfl_xor_sync(0xffffffffu, send0.y, 16);
+      got1.x = __shfl_xor_sync(0xffffffffu, send1.x, 16);
+      got1.y = __shfl_xor_sync(0xffffffffu, send1.y, 16);
+      // value lane: keep = a, got = gate;  gate lane: keep = gate, got = a
+      const float2 a0 = role == 0 ? keep0 : got0, a1 = role == 0 ? keep1 : got1;
+      const float2 g0 = role == 0 ? got0 : keep0, g1 = role == 0 ? got1 : keep1;
       if (lane_ok) {
-        uint2 pk = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
-        __nv_bfloat16* op = p.out + ((int64_t)ro * p.W + x) * p.hid + (cvec << 3) + role * 4;
-        *reinterpret_cast<uint2*>(op) = pk;
+        const uint2 pk = make_uint2(pack_bf16(a0.x * fast_silu(g0.x), a0.y * fast_silu(g0.y)),
+                                    pack_bf16(a1.x * fast_silu(g1.x), a1.y * fast_silu(g1.y)));
+        *reinterpret_cast<uint2*>(out_ptr) = pk;
       }
     }
 #pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2) acc[PREV][c2] = make_float2(0.f, 0.f);  // becomes NEXT of the next step
+    for (int c2 = 0; c2 < 4; ++c2) acc[PREV][c2] = bv[c2];  // becomes NEXT of the next step
+    out_ptr += (int64_t)p.W * p.hid;
+    fr = (fr + 1 == p.H) ? 0 : fr + 1;
   };
 
   using I0 = std::integral_constant<int, 0>;
@@ -201,7 +213,6 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dwconv_glu_bf16_kernel(const Dw
     if (k + 1 < nin) step(k + 1, I1{}, I2{}, I0{});
     if (k + 2 < nin) step(k + 2, I2{}, I0{}, I1{});
   }
-  // the last input slot (k = nin-1, local row ye) completes output row ye-1 inside its own step.
   cp_async_wait<0>();
 }
 

@@ -7,7 +7,9 @@
 //   warp 1 (one lane)  issues tcgen05.mma (M=128, N=BN, K=16 per instruction), accumulating
 //                      in tensor memory; two accumulator buffers so the epilogue of tile i
 //                      overlaps the MMAs of tile i+1
-//   warps 2..5         epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step), fused
+//   warps 2..9         epilogue: two warps per TMEM lane quadrant (left / right half of the
+//                      tile), tcgen05.ld of 16 columns per step with the next step's
+//                      accumulator, bias, gate and residual operands already in flight;
 //                      bias / activation / adaLN gate / residual in fp32, 16-byte stores
 // Every wait is bounded: after ~2 s a role records a code in g_gemm_status, raises the
 // CTA-wide abort flag and all roles fall through to the common teardown (TMEM is freed).
@@ -24,21 +26,24 @@ __device__ int g_gemm_status = 0;
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;                       // 64 bf16 = one 128-byte swizzle row
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
-constexpr int TC_THREADS = 192;
+constexpr int TC_EPI_WARPS = 8;                 // two warps per TMEM lane quadrant (left / right half of the tile)
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr int TC_SMEM_LIMIT = 232448;           // 227 KiB opt-in maximum per CTA
-constexpr int TC_CTRL_BYTES = 1024;             // barriers + tmem pointer + abort flag
+constexpr int TC_CTRL_BYTES = 256;              // barriers + tmem pointer + abort flag
 
 template <int BN>
 struct TcCfg {
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (TC_SMEM_LIMIT - TC_CTRL_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int MAX_STAGES = (TC_SMEM_LIMIT - TC_CTRL_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TC_CTRL_BYTES + 1024;  // +1024 alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TC_CTRL_BYTES;
   static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
   // instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7, 10), both K-major, N>>3 at 17, M>>4 at 24
   static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TC_BM >> 4) << 24);
+  static constexpr int HALF = BN / 2;        // columns per epilogue warp
+  static constexpr int NCHUNK = HALF / 16;   // 16-column steps per epilogue warp
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
   static_assert(STAGES >= 3, "not enough shared memory for the ring");
 };
@@ -134,6 +139,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return ((uint64_t)hi << 32) | lo;
 }
 
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_silu(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
+}
+
 struct TcArgs {
   __nv_bfloat16* out;
   int64_t ldo;
@@ -142,22 +164,31 @@ struct TcArgs {
   EpiParams ep;
 };
 
+// Operands of one 16-column epilogue step of one row, fetched one step ahead of their use.
+struct EpiStep {
+  uint32_t acc[16];
+  uint4 bias[2], gtab[2], gt[2], res[2];
+};
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t tiles_base = (raw + 1023u) & ~1023u;           // swizzled tiles need 1024-byte alignment
-  unsigned char* gen_base = smem_raw + (tiles_base - raw);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t tiles_base = smem_u32(smem_raw);                // swizzled tiles need 1024-byte alignment
   const uint32_t ctrl = tiles_base + STAGES * Cfg::STAGE_BYTES;  // control block after the ring
-  unsigned char* ctrl_gen = gen_base + STAGES * Cfg::STAGE_BYTES;
+  unsigned char* ctrl_gen = smem_raw + STAGES * Cfg::STAGE_BYTES;
   // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
+
+  if ((tiles_base & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0) atomicExch(&g_gemm_status, 9);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = args.tiles_m * args.tiles_n;
@@ -170,7 +201,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 4);
+      mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -241,37 +272,98 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------- epilogue warps -----------------------------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // warp w reads TMEM lanes 32*(w%4)..+31 (hardware rule) and the left or right half of the
+    // tile's columns; 16 columns per step, operands of step c+1 in flight while step c is
+    // computed and stored.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const EpiParams& ep = args.ep;
+    const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(ep.bias);
+    const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
+    const __nv_bfloat16* gt = static_cast<const __nv_bfloat16*>(ep.gate_t);
+    const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(ep.residual);
+    const int64_t N = args.N;
     uint32_t full_phase = 0u;  // bit a = phase of accumulator buffer a
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       const int a = it & 1;
-      const int m0 = (tile / args.tiles_n) * TC_BM, n0 = (tile % args.tiles_n) * BN;
+      const int m0 = (tile / args.tiles_n) * TC_BM;
+      const int64_t nbase = (int64_t)(tile % args.tiles_n) * BN + half * Cfg::HALF;
+      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const bool row_ok = m < args.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
+      __nv_bfloat16* orow = args.out + m * args.ldo;
+      const __nv_bfloat16* gtrow = nullptr;
+      if (gtab) gtrow = gt + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N;
+      const __nv_bfloat16* grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
+      const __nv_bfloat16* rrow = res ? res + m * ep.ldr : nullptr;
+
+      // operands that do not depend on the accumulator (step 0) are requested before the wait
+      EpiStep st[2];
+      auto fetch_side = [&](EpiStep& s, int c) {
+        const int64_t n = nbase + 16 * c;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int64_t nj = n + 8 * j;
+          const bool in = nj < N;
+          s.bias[j] = (bias && in) ? __ldg(reinterpret_cast<const uint4*>(bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          if (gtab) {
+            s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+            s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          s.res[j] = (res && in && row_ok) ? ldg_nc_u4(rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      fetch_side(st[0], 0);
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      const int64_t m = (int64_t)m0 + quad * 32 + lane;
-      const bool row_ok = m < args.M;
-      const int64_t batch = row_ok ? m / args.ep.rows_per_batch : 0;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-      __nv_bfloat16* orow = args.out + m * args.ldo;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= args.N) break;  // uniform: whole chunk outside the matrix
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+      if (nbase < N) tmem_ld_32x16(taddr, st[0].acc);
+#pragma unroll
+      for (int c = 0; c < Cfg::NCHUNK; ++c) {
+        const int64_t n = nbase + 16 * c;
+        if (n >= N) break;  // uniform: the rest of this half lies outside the matrix
+        EpiStep& cur = st[c & 1];
         tmem_ld_wait();
+        if (c + 1 < Cfg::NCHUNK && n + 16 < N) {
+          tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
+          fetch_side(st[(c + 1) & 1], c + 1);
+        }
         if (row_ok) {
 #pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
-            const int64_t n = (int64_t)n0 + c0 + 8 * v8;
-            if (n < args.N) {
-              float v[8];
+          for (int j = 0; j < 2; ++j) {
+            if (n + 8 * j < N) {
+              float v[8], f[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * v8 + e]);
-              const uint4 o = epi_vec8_bf16(v, m, n, args.N, batch, args.ep);
-              *reinterpret_cast<uint4*>(orow + n) = o;
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]);
+              if (bias) {
+                unpack8(cur.bias[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              if (ep.act == 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+              } else if (ep.act == 2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+              }
+              if (gtab) {
+                float g[8];
+                unpack8(cur.gtab[j], g);
+                unpack8(cur.gt[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+              }
+              if (res) {
+                unpack8(cur.res[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              *reinterpret_cast<uint4*>(orow + n + 8 * j) =
+                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             }
           }
         }
