@@ -3,18 +3,18 @@
 // bf16 kernel: a CTA owns a tile of 16 columns x 64 value channels (+ their 64 gate
 // channels) and marches down a segment of rows.  Each input row tile (with a one-column
 // halo, zero-filled at image edges) is staged once in shared memory by 16-byte cp.async
-// through an 8-deep ring; a lane owns 8 contiguous channels of one role (value or gate),
-// reads the three horizontal neighbours with 128-bit shared loads and feeds three rolling
-// fp32 accumulators (output rows y-1, y, y+1) with packed f32x2 FMAs, so every input
-// element is read from global memory once per CTA and from shared memory three times.
-// Value and gate lanes swap half of their channels by warp shuffle for the GLU.
+// through a 10-deep ring (one CTA barrier per two rows); a lane owns one pair of value
+// channels and the gate pair of the same index at two neighbouring columns, reads the four
+// input columns their windows share from shared memory and feeds three rolling fp32
+// accumulators per output (rows y-1, y, y+1) with packed f32x2 FMAs; every input element is
+// read from global memory once per CTA, and the GLU needs no exchange between lanes.
 #include "common.cuh"
 
 namespace sana {
 
 constexpr int DW_TW = 16;      // output columns per CTA
 constexpr int DW_CV = 8;       // 8-channel vectors per role per CTA
-constexpr int DW_STAGES = 8;   // ring depth (input rows in flight)
+constexpr int DW_STAGES = 10;  // ring depth (input rows in flight)
 constexpr int DW_THREADS = 256;
 constexpr int DW_ROW_CHUNKS = (DW_TW + 2) * 2 * DW_CV;  // 16-byte chunks per staged row = 288
 constexpr int DW_STAGE_BYTES = DW_ROW_CHUNKS * 16;
@@ -47,41 +47,71 @@ struct DwArgs {
   int64_t row0;
 };
 
+// packed fp32x2 helpers on 64-bit registers (one instruction per two lanes of math)
+typedef unsigned long long u64;
+__device__ __forceinline__ u64 f2_pack(float lo, float hi) {
+  u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(u64 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 f2_fma(u64 a, u64 b, u64 c) {
+  u64 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ u64 f2_add(u64 a, u64 b) {
+  u64 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// two bf16 in one 32-bit word -> packed (fp32, fp32)
+__device__ __forceinline__ u64 bf2_to_f2(uint32_t v) {
+  u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(v << 16), "r"(v & 0xffff0000u));
+  return r;
+}
+
 __global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const DwArgs p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int role = lane >> 4, xs = (lane >> 3) & 1, cv = lane & 7;
-  const int nvec = p.hid >> 3;
-  const int cvec = blockIdx.x * DW_CV + cv;  // 8-channel vector index inside a role
+  // a lane owns one pair of value channels and the gate pair of the same index, at two
+  // neighbouring columns (x, x+1): the 3x3 window of both outputs shares 4 input columns
   const int x0 = blockIdx.y * DW_TW;
-  const int lx = 2 * warp + xs;  // column inside the tile
-  const int x = x0 + lx;
+  const int x = x0 + 2 * warp;
   const int ys = blockIdx.z * p.seg_rows;
   const int ye = min(p.rows, ys + p.seg_rows);
   const int C2 = 2 * p.hid;
-  const bool lane_ok = (cvec < nvec) && (x < p.W);
-  const int ch = role * p.hid + (min(cvec, nvec - 1) << 3);  // first of this lane's 8 channels
+  const int c0 = blockIdx.x * (DW_CV * 8) + lane * 2;  // first of this lane's 2 value channels
+  const bool ch_ok = c0 < p.hid;
+  const bool ok0 = ch_ok && (x < p.W), ok1 = ch_ok && (x + 1 < p.W);
+  const int cw = min(c0, p.hid - 2);
 
-  // per-lane taps: w2[tap][pair] as float2, tap = 3*dy + dx; the bias seeds the accumulators
-  float2 w2[9][4];
-  float2 bv[4];
+  // taps as packed pairs: w2[tap][0] = value channels (c, c+1), w2[tap][1] = gate channels
+  u64 w2[9][2];
+  u64 bv[2];
   {
-    const __nv_bfloat16* wp = p.weight + (int64_t)ch * 9;
+    const __nv_bfloat16* wv = p.weight + (int64_t)cw * 9;
+    const __nv_bfloat16* wg = p.weight + (int64_t)(p.hid + cw) * 9;
 #pragma unroll
-    for (int tap = 0; tap < 9; ++tap)
-#pragma unroll
-      for (int c2 = 0; c2 < 4; ++c2)
-        w2[tap][c2] = make_float2(__bfloat162float(wp[(2 * c2) * 9 + tap]), __bfloat162float(wp[(2 * c2 + 1) * 9 + tap]));
-#pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2)
-      bv[c2] = p.bias ? make_float2(__bfloat162float(p.bias[ch + 2 * c2]), __bfloat162float(p.bias[ch + 2 * c2 + 1]))
-                      : make_float2(0.f, 0.f);
+    for (int tap = 0; tap < 9; ++tap) {
+      w2[tap][0] = f2_pack(__bfloat162float(wv[tap]), __bfloat162float(wv[9 + tap]));
+      w2[tap][1] = f2_pack(__bfloat162float(wg[tap]), __bfloat162float(wg[9 + tap]));
+    }
+    if (p.bias) {
+      bv[0] = f2_pack(__bfloat162float(p.bias[cw]), __bfloat162float(p.bias[cw + 1]));
+      bv[1] = f2_pack(__bfloat162float(p.bias[p.hid + cw]), __bfloat162float(p.bias[p.hid + cw + 1]));
+    } else {
+      bv[0] = bv[1] = 0ull;
+    }
   }
 
   // input-row slots k = 0 .. nin-1  <->  local rows ys-1 .. ye; the first and last slot exist
   // only when that row lies in the same frame as its neighbour inside the segment
   const int nin = ye - ys + 2;
-  const int fr_top = (int)((p.row0 + ys + p.H - 1) % p.H);   // frame row of local row ys-1
+  const int fr_top = (int)((p.row0 + ys + p.H - 1) % p.H);  // frame row of local row ys-1
   const bool need_top = fr_top != p.H - 1;
   const bool need_bot = (int)((p.row0 + ye) % p.H) != 0;
   const int64_t row_elems = (int64_t)p.W * C2;
@@ -91,6 +121,7 @@ __global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const Dw
 
   // this thread's (at most two) 16-byte chunks of a staged row: fixed offsets, computed once
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+  const int nvec = p.hid >> 3;
   int64_t src_off[2];
   uint32_t dst_off[2];
   bool src_ok[2], has[2];
@@ -118,88 +149,80 @@ __global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const Dw
     cp_async_commit();
   };
 
-  float2 acc[3][4];
+  u64 acc[3][2][2];  // [output-row slot][column x / x+1][value / gate]
 #pragma unroll
   for (int s = 0; s < 3; ++s)
 #pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2) acc[s][c2] = bv[c2];
+    for (int xo = 0; xo < 2; ++xo) acc[s][xo][0] = acc[s][xo][1] = 0ull;
 
 #pragma unroll 1
-  for (int k = 0; k < DW_STAGES - 1; ++k) issue_row(k);
+  for (int k = 0; k < DW_STAGES - 2; ++k) issue_row(k);
 
   int fr = fr_top;  // frame row of the input row of the current slot
-  __nv_bfloat16* out_ptr = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + (cvec << 3) + role * 4;  // row of slot k-1's output
+  __nv_bfloat16* out_ptr = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + c0;  // output row of slot k is ys-2+k
+  // byte offset of this lane's value word of staged pixel 2*warp (= column x-1), role 0
+  const uint32_t rd_off = (uint32_t)(2 * warp * 256 + lane * 4);
 
   // One step: consume input slot k (local row r = ys-1+k).  PREV/CUR/NEXT are the accumulator
   // slots of output rows (r-1, r, r+1); they rotate with k so no register moves are needed.
+  // The CTA synchronises once per two rows (on even k).
   auto step = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
-    cp_async_wait<DW_STAGES - 2>();
-    __syncthreads();
-    issue_row(k + DW_STAGES - 1);
+    if ((k & 1) == 0) {
+      cp_async_wait<DW_STAGES - 4>();  // rows k and k+1 have landed (for this thread's copies)
+      __syncthreads();                 // ... for everybody's; and rows k-2, k-1 are no longer read
+      issue_row(k + DW_STAGES - 2);
+      issue_row(k + DW_STAGES - 1);
+    }
     const bool first = (k == 0), last = (k == nin - 1);
     const bool have = first ? need_top : (last ? need_bot : true);
     if (have) {
-      const unsigned char* sp = smem + (k % DW_STAGES) * DW_STAGE_BYTES + ((lx * 16 + role * 8 + cv) << 4);
-      const uint4 vm = *reinterpret_cast<const uint4*>(sp);
-      const uint4 vc = *reinterpret_cast<const uint4*>(sp + 256);
-      const uint4 vp = *reinterpret_cast<const uint4*>(sp + 512);
-      float2 xm[4], xc[4], xp[4];
-      xm[0] = make_float2(bf16_lo(vm.x), bf16_hi(vm.x)), xm[1] = make_float2(bf16_lo(vm.y), bf16_hi(vm.y));
-      xm[2] = make_float2(bf16_lo(vm.z), bf16_hi(vm.z)), xm[3] = make_float2(bf16_lo(vm.w), bf16_hi(vm.w));
-      xc[0] = make_float2(bf16_lo(vc.x), bf16_hi(vc.x)), xc[1] = make_float2(bf16_lo(vc.y), bf16_hi(vc.y));
-      xc[2] = make_float2(bf16_lo(vc.z), bf16_hi(vc.z)), xc[3] = make_float2(bf16_lo(vc.w), bf16_hi(vc.w));
-      xp[0] = make_float2(bf16_lo(vp.x), bf16_hi(vp.x)), xp[1] = make_float2(bf16_lo(vp.y), bf16_hi(vp.y));
-      xp[2] = make_float2(bf16_lo(vp.z), bf16_hi(vp.z)), xp[3] = make_float2(bf16_lo(vp.w), bf16_hi(vp.w));
+      const unsigned char* sp = smem + (k % DW_STAGES) * DW_STAGE_BYTES + rd_off;
+      u64 col[4][2];  // input columns x-1 .. x+2, [value / gate]
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        col[c][0] = bf2_to_f2(*reinterpret_cast<const uint32_t*>(sp + c * 256));
+        col[c][1] = bf2_to_f2(*reinterpret_cast<const uint32_t*>(sp + c * 256 + 128));
+      }
       // input row r is the row BELOW output r-1 (taps 6..8), the centre of output r (taps 3..5)
       // and the row ABOVE output r+1 (taps 0..2); vertical neighbours must share the frame.
       if (k >= 2 && fr != 0) {  // output r-1 is inside the segment
 #pragma unroll
-        for (int c2 = 0; c2 < 4; ++c2) {
-          acc[PREV][c2] = ffma2(w2[6][c2], xm[c2], acc[PREV][c2]);
-          acc[PREV][c2] = ffma2(w2[7][c2], xc[c2], acc[PREV][c2]);
-          acc[PREV][c2] = ffma2(w2[8][c2], xp[c2], acc[PREV][c2]);
-        }
+        for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+          for (int dx = 0; dx < 3; ++dx)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) acc[PREV][xo][h] = f2_fma(w2[6 + dx][h], col[xo + dx][h], acc[PREV][xo][h]);
       }
       if (!first && !last) {
 #pragma unroll
-        for (int c2 = 0; c2 < 4; ++c2) {
-          acc[CUR][c2] = ffma2(w2[3][c2], xm[c2], acc[CUR][c2]);
-          acc[CUR][c2] = ffma2(w2[4][c2], xc[c2], acc[CUR][c2]);
-          acc[CUR][c2] = ffma2(w2[5][c2], xp[c2], acc[CUR][c2]);
-        }
+        for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+          for (int dx = 0; dx < 3; ++dx)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) acc[CUR][xo][h] = f2_fma(w2[3 + dx][h], col[xo + dx][h], acc[CUR][xo][h]);
       }
       if (k + 2 < nin && fr != p.H - 1) {  // output r+1 is inside the segment
 #pragma unroll
-        for (int c2 = 0; c2 < 4; ++c2) {
-          acc[NEXT][c2] = ffma2(w2[0][c2], xm[c2], acc[NEXT][c2]);
-          acc[NEXT][c2] = ffma2(w2[1][c2], xc[c2], acc[NEXT][c2]);
-          acc[NEXT][c2] = ffma2(w2[2][c2], xp[c2], acc[NEXT][c2]);
-        }
+        for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+          for (int dx = 0; dx < 3; ++dx)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) acc[NEXT][xo][h] = f2_fma(w2[dx][h], col[xo + dx][h], acc[NEXT][xo][h]);
       }
     }
     if (k >= 2) {  // output row r-1 = ys + k - 2 is complete
-      // value lane keeps channels 0..3 and receives gate 0..3; gate lane keeps 4..7 and receives value 4..7
-      const float2 keep0 = role == 0 ? acc[PREV][0] : acc[PREV][2];
-      const float2 keep1 = role == 0 ? acc[PREV][1] : acc[PREV][3];
-      const float2 send0 = role == 0 ? acc[PREV][2] : acc[PREV][0];
-      const float2 send1 = role == 0 ? acc[PREV][3] : acc[PREV][1];
-      float2 got0, got1;
-      got0.x = __shfl_xor_sync(0xffffffffu, send0.x, 16);
-      got0.y = __shfl_xor_sync(0xffffffffu, send0.y, 16);
-      got1.x = __shfl_xor_sync(0xffffffffu, send1.x, 16);
-      got1.y = __shfl_xor_sync(0xffffffffu, send1.y, 16);
-      // value lane: keep = a, got = gate;  gate lane: keep = gate, got = a
-      const float2 a0 = role == 0 ? keep0 : got0, a1 = role == 0 ? keep1 : got1;
-      const float2 g0 = role == 0 ? got0 : keep0, g1 = role == 0 ? got1 : keep1;
-      if (lane_ok) {
-        const uint2 pk = make_uint2(pack_bf16(a0.x * fast_silu(g0.x), a0.y * fast_silu(g0.y)),
-                                    pack_bf16(a1.x * fast_silu(g1.x), a1.y * fast_silu(g1.y)));
-        *reinterpret_cast<uint2*>(out_ptr) = pk;
+#pragma unroll
+      for (int xo = 0; xo < 2; ++xo) {
+        float a0, a1, g0, g1;
+        f2_unpack(f2_add(acc[PREV][xo][0], bv[0]), a0, a1);
+        f2_unpack(f2_add(acc[PREV][xo][1], bv[1]), g0, g1);
+        if (xo == 0 ? ok0 : ok1)
+          *reinterpret_cast<uint32_t*>(out_ptr + xo * p.hid) = pack_bf16(a0 * fast_silu(g0), a1 * fast_silu(g1));
       }
     }
 #pragma unroll
-    for (int c2 = 0; c2 < 4; ++c2) acc[PREV][c2] = bv[c2];  // becomes NEXT of the next step
+    for (int xo = 0; xo < 2; ++xo) acc[PREV][xo][0] = acc[PREV][xo][1] = 0ull;  // becomes NEXT of the next step
     out_ptr += (int64_t)p.W * p.hid;
     fr = (fr + 1 == p.H) ? 0 : fr + 1;
   };
@@ -207,11 +230,16 @@ __global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const Dw
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
+  // six slots per trip so that both the accumulator rotation (period 3) and the barrier
+  // cadence (period 2) are compile-time
 #pragma unroll 1
-  for (int k = 0; k < nin; k += 3) {
+  for (int k = 0; k < nin; k += 6) {
     step(k, I0{}, I1{}, I2{});
     if (k + 1 < nin) step(k + 1, I1{}, I2{}, I0{});
     if (k + 2 < nin) step(k + 2, I2{}, I0{}, I1{});
+    if (k + 3 < nin) step(k + 3, I0{}, I1{}, I2{});
+    if (k + 4 < nin) step(k + 4, I1{}, I2{}, I0{});
+    if (k + 5 < nin) step(k + 5, I2{}, I0{}, I1{});
   }
   cp_async_wait<0>();
 }
