@@ -45,6 +45,42 @@ def batch_partition(batch: int, world: int) -> List[Tuple[int, int]]:
     return [(r * per, (r + 1) * per) for r in range(world)]
 
 
+class PeerLostError(RuntimeError):
+    """A peer rank did not report the expected step in time."""
+
+
+class PeerHealth:
+    """Host-side failure detector for a group of ranks that step in lock-step.
+
+    After finishing step ``s`` (all of its kernels and collectives complete) a rank calls
+    ``report(s)``; before launching step ``s+1`` it calls ``require(s)``, which raises
+    ``PeerLostError`` if some peer has not reported step ``s`` within ``timeout_s``.  A rank
+    that died between steps is therefore noticed on the host before the next collective is
+    launched, instead of inside a kernel or an NCCL call.  Works with any
+    ``torch.distributed`` store (TCPStore / FileStore / the default process-group store)."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "sana_health"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+
+    def _key(self, rank: int, step: int) -> str:
+        return f"{self.prefix}/{rank}/{step}"
+
+    def report(self, step: int) -> None:
+        self.store.set(self._key(self.rank, step), b"1")
+
+    def require(self, step: int) -> None:
+        import datetime
+
+        keys = [self._key(r, step) for r in range(self.world) if r != self.rank]
+        if not keys:
+            return
+        try:
+            self.store.wait(keys, datetime.timedelta(seconds=self.timeout_s))
+        except Exception as e:  # noqa: BLE001 - the store raises backend-specific errors on time-out
+            raise PeerLostError(f"rank {self.rank}: a peer did not finish step {step} within {self.timeout_s}s "
+                                f"({type(e).__name__})") from e
+
+
 @dataclass
 class SequenceShard:
     """This rank's slice of a ``(frames, H, W)`` token grid (``frames`` = 1 for an image)."""

@@ -114,6 +114,30 @@ def _dies_before_collective(rank, world):
     return "unexpected success"
 
 
+def _peer_health(rank, world):
+    from sana_b200 import sharding
+
+    store = dist.distributed_c10d._get_default_store()
+    h = sharding.PeerHealth(store, rank, world, timeout_s=2.0)
+    h.report(0)
+    h.require(0)  # everybody reported step 0
+    if rank == world - 1:
+        return "left"  # leaves between steps
+    h.report(1)
+    try:
+        h.require(1)
+    except sharding.PeerLostError as e:
+        return f"detected: {e}"
+    return "not detected"
+
+
+def test_peer_health_detects_a_rank_that_left_between_steps():
+    res = _run(3, _peer_health, timeout_s=20, join_s=60)
+    assert res[2] == ("ok", "left"), res
+    for r in (0, 1):
+        assert res[r][0] == "ok" and res[r][1].startswith("detected"), res
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_sequence_parallel_block_matches_single_process(world):
     res = _run(world, _seqpar_block)
