@@ -158,6 +158,34 @@ int sana_gemm(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out
 int sana_gemm_simt(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
                    int64_t N, int64_t K, const sana_gemm_epilogue* ep, int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * NVFP4 (block-scaled 4-bit) projections.  Upstream has no FP4 arithmetic of its own (it
+ * wraps nn.Linear in Transformer Engine's te.Linear under an NVFP4 recipe,
+ * inference_video_scripts/wm/inference_sana_wm.py:388-406); these entry points replace the
+ * same nn.Linear / 1x1 Conv2d calls as sana_gemm with both operands quantised.
+ *
+ * Format: E2M1 values {0, .5, 1, 1.5, 2, 3, 4, 6} with sign, two per byte (even K index in
+ * the low nibble), one E4M3 scale per 16 consecutive K elements, one fp32 scale per tensor:
+ *   x ~ code * block_scale * tensor_scale,  tensor_scale = amax / (6 * 448),
+ *   block_scale = E4M3(block_amax / (6 * tensor_scale)),  code = E2M1(x / (block_scale * tensor_scale))
+ * (round to nearest even, saturating).  Block scales are stored in 512-byte tiles of
+ * 128 rows x 4 blocks, byte (r % 32) * 16 + (r / 32) * 4 + b, tiles K-fastest with the K-tile
+ * count padded to a multiple of 4 (sana_nvfp4_sf_bytes gives the buffer size).
+ *
+ * sana_nvfp4_quantize: x [rows, K] bf16 (row stride ld) -> q [rows, K/2] bytes, sf (scale
+ *   tiles), scales[2] = {amax, tensor_scale} (device floats).  K % 32 == 0.  Three launches:
+ *   absolute maximum, then quantise; nothing is read back to the host.
+ * sana_gemm_nvfp4: out[M, N] bf16 = epilogue(a_scales[1] * w_scales[1] * Aq @ Wq^T) with the
+ *   sana_gemm epilogue.  tcgen05.mma kind::mxf4nvf4 (block 16) with scales in tensor memory.
+ */
+int64_t sana_nvfp4_sf_bytes(int64_t rows, int64_t K);
+int sana_nvfp4_quantize(const void* x, int64_t ld, void* q, void* sf, float* scales, int64_t rows, int64_t K,
+                        void* stream);
+int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_scales, const void* Wq, const void* sfw,
+                    const float* w_scales, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                    const sana_gemm_epilogue* ep, void* stream);
+int sana_gemm_nvfp4_take_device_status(int* status_out);
+
 /* Soft-error word of the tensor-core GEMM: its bounded waits record a code here instead of
  * spinning forever.  Returns 0 when no wait ever timed out on the current device since the
  * last call (host-synchronising: use in tests / after a failure, not per step). */

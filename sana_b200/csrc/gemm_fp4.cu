@@ -1,0 +1,473 @@
+// NVFP4 projection: out = epilogue(a_scale * w_scale * (Aq . SFa) @ (Wq . SFw)^T).
+//
+// Operands are E2M1 values packed two per byte (K-major), with one E4M3 scale per 16
+// consecutive K elements and one fp32 scale per tensor.  The block scales live in global
+// memory in the 512-byte tiles the tensor core consumes: tile (row block of 128, K block of
+// 64) holds byte [(r % 32) * 16 + (r / 32) * 4 + kb] for row r and 16-element block kb; tiles
+// are ordered K-fastest and the K-tile count is padded to a multiple of 4, so one pipeline
+// stage (K = 256) needs 2 KiB contiguous scale bytes per operand.
+//
+// Same persistent, warp-specialised structure as the bf16 kernel (128 x 128 tiles, K = 256
+// per stage): the producer adds two bulk copies for the scale tiles, the MMA lane copies
+// them from shared to tensor memory (tcgen05.cp 32x128b.warpx4 replicates each 512-byte tile
+// over the four lane quadrants) and issues tcgen05.mma kind::mxf4nvf4 with block-16 scales,
+// K = 64 per instruction.  TMEM: two 128-column accumulators + 32 scale columns per stage.
+#include <cuda_fp8.h>
+
+#include "tc_common.cuh"
+
+namespace sana {
+
+__device__ int g_fp4_status = 0;
+
+constexpr int F4_BM = 128, F4_BN = 128;
+constexpr int F4_BK = 256;                          // elements per stage = 128 bytes per row
+constexpr int F4_A_BYTES = F4_BM * 128;             // 16 KiB
+constexpr int F4_B_BYTES = F4_BN * 128;             // 16 KiB
+constexpr int F4_SF_BYTES = 4 * 512;                // four 512-byte scale tiles per operand and stage
+constexpr int F4_STAGE_BYTES = F4_A_BYTES + F4_B_BYTES + 2 * F4_SF_BYTES;  // 36 KiB
+constexpr int F4_STAGES = 6;
+constexpr int F4_CTRL_BYTES = 256;
+constexpr int F4_SMEM_BYTES = F4_STAGES * F4_STAGE_BYTES + F4_CTRL_BYTES;
+constexpr int F4_EPI_WARPS = 8;
+constexpr int F4_THREADS = 64 + 32 * F4_EPI_WARPS;
+constexpr int F4_TMEM_COLS = 512;                   // 2 x 128 accumulator + 6 x 32 scale columns = 448
+constexpr int F4_SF_COL0 = 2 * F4_BN;               // first scale column
+// block-scaled instruction descriptor: A = B = E2M1 (code 1 at bits 7 and 10), both K-major,
+// scale type UE4M3 (bit 23 = 0), N>>3 at bit 17, M>>4 at bit 24, dense K = 64 (bit 31 = 0)
+constexpr uint32_t F4_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(F4_BN >> 3) << 17) | ((uint32_t)(F4_BM >> 4) << 24);
+static_assert(F4_SMEM_BYTES <= 232448, "shared memory budget");
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+               "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// 32 rows x 16 bytes, rows contiguous: 8-row groups 128 bytes apart, no swizzle
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+  const uint32_t lo = (saddr >> 4) & 0x3FFFu;
+  const uint32_t hi = (128u >> 4) | (1u << 14);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void umma_nvfp4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                           uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
+struct F4Args {
+  __nv_bfloat16* out;
+  int64_t ldo;
+  const unsigned char* sfa;   // scale tiles of A: [ceil(M/128)][ktiles4][512]
+  const unsigned char* sfb;   // scale tiles of W: [ceil(N/128)][ktiles4][512]
+  const float* a_scale;       // per-tensor scales (device)
+  const float* w_scale;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int ktiles4;                // K tiles of 64 per row block, padded to a multiple of 4
+  EpiParams ep;
+};
+
+struct F4Step {
+  uint32_t acc[16];
+  uint4 bias[2], gtab[2], gt[2], res[2];
+};
+
+__global__ void __launch_bounds__(F4_THREADS, 1)
+gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const F4Args args) {
+  constexpr int STAGES = F4_STAGES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t tiles_base = smem_u32(smem_raw);
+  const uint32_t ctrl = tiles_base + STAGES * F4_STAGE_BYTES;
+  unsigned char* ctrl_gen = smem_raw + STAGES * F4_STAGE_BYTES;
+  const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
+  const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
+
+  if ((tiles_base & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(&g_fp4_status, 9);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int kblocks = (args.K + F4_BK - 1) / F4_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, F4_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32),
+                 "r"((uint32_t)F4_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------- producer -----------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mt = tile / args.tiles_n, nt = tile % args.tiles_n;
+        const unsigned char* sfa_row = args.sfa + (int64_t)mt * args.ktiles4 * 512;
+        const unsigned char* sfb_row = args.sfb + (int64_t)nt * args.ktiles4 * 512;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
+          const uint32_t sa = tiles_base + stage * F4_STAGE_BYTES;
+          const uint32_t fb = bar_full + 8 * stage;
+          mbar_expect_tx(fb, F4_STAGE_BYTES);
+          tma_load_2d(sa, &tmA, fb, kb * 128, mt * F4_BM);                 // byte coordinates along K
+          tma_load_2d(sa + F4_A_BYTES, &tmB, fb, kb * 128, nt * F4_BN);
+          bulk_load(sa + F4_A_BYTES + F4_B_BYTES, sfa_row + (int64_t)kb * F4_SF_BYTES, F4_SF_BYTES, fb);
+          bulk_load(sa + F4_A_BYTES + F4_B_BYTES + F4_SF_BYTES, sfb_row + (int64_t)kb * F4_SF_BYTES, F4_SF_BYTES, fb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc_phase = 0u;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int a = it & 1;
+        if (!mbar_wait(bar_tempty + 8 * a, ((acc_phase >> a) & 1u) ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
+        acc_phase ^= 1u << a;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * F4_BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_base + stage * F4_STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + F4_A_BYTES);
+          const uint32_t sfa_s = sa + F4_A_BYTES + F4_B_BYTES, sfb_s = sfa_s + F4_SF_BYTES;
+          const uint32_t sfa_t = tmem_base + (uint32_t)(F4_SF_COL0 + stage * 32), sfb_t = sfa_t + 16;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tmem_cp_sf(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
+            tmem_cp_sf(sfb_t + 4 * k, make_sf_desc(sfb_s + 512 * k));
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 64 elements = 32 bytes per instruction inside the 128-byte swizzle row
+            umma_nvfp4(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), F4_IDESC, sfa_t + 4 * k, sfb_t + 4 * k,
+                       (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * a);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps -----------------------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HALF = F4_BN / 2, NCHUNK = HALF / 16;
+    const EpiParams& ep = args.ep;
+    const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(ep.bias);
+    const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
+    const __nv_bfloat16* gt = static_cast<const __nv_bfloat16*>(ep.gate_t);
+    const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(ep.residual);
+    const int64_t N = args.N;
+    const float alpha = __ldg(args.a_scale) * __ldg(args.w_scale);
+    uint32_t full_phase = 0u;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int a = it & 1;
+      const int m0 = (tile / args.tiles_n) * F4_BM;
+      const int64_t nbase = (int64_t)(tile % args.tiles_n) * F4_BN + half * HALF;
+      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const bool row_ok = m < args.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * F4_BN + half * HALF);
+      __nv_bfloat16* orow = args.out + m * args.ldo;
+      const __nv_bfloat16* gtrow = nullptr;
+      if (gtab) gtrow = gt + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N;
+      const __nv_bfloat16* grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
+      const __nv_bfloat16* rrow = res ? res + m * ep.ldr : nullptr;
+
+      F4Step st[2];
+      auto fetch_side = [&](F4Step& s, int c) {
+        const int64_t n = nbase + 16 * c;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int64_t nj = n + 8 * j;
+          const bool in = nj < N;
+          s.bias[j] = (bias && in) ? __ldg(reinterpret_cast<const uint4*>(bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          if (gtab) {
+            s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+            s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          s.res[j] = (res && in && row_ok) ? ldg_nc_u4(rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      fetch_side(st[0], 0);
+      if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
+      full_phase ^= 1u << a;
+      tcgen05_fence_after();
+      if (nbase < N) tmem_ld_32x16(taddr, st[0].acc);
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int64_t n = nbase + 16 * c;
+        if (n >= N) break;
+        F4Step& cur = st[c & 1];
+        tmem_ld_wait();
+        if (c + 1 < NCHUNK && n + 16 < N) {
+          tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
+          fetch_side(st[(c + 1) & 1], c + 1);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (n + 8 * j < N) {
+              float v[8], f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]) * alpha;
+              if (bias) {
+                unpack8(cur.bias[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              if (ep.act == 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+              } else if (ep.act == 2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+              }
+              if (gtab) {
+                float g[8];
+                unpack8(cur.gtab[j], g);
+                unpack8(cur.gt[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+              }
+              if (res) {
+                unpack8(cur.res[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              *reinterpret_cast<uint4*>(orow + n + 8 * j) =
+                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)F4_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- quantiser ----------------------------------------------------------------------------------
+__global__ void absmax_bf16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, int64_t rows, int K,
+                                   float* __restrict__ amax) {
+  const int vec_per_row = K >> 3;
+  const int64_t total = rows * vec_per_row;
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = (int)(i - r * vec_per_row);
+    const uint4 v = ldg_nc_u4(x + r * ld + 8 * c);
+    float f[8];
+    unpack8(v, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));  // m >= 0
+}
+
+__device__ __forceinline__ float e4m3_round(float v) {
+  // round-to-nearest-even onto positive E4M3 (max 448), as a float
+  const __nv_fp8_storage_t s = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(s, __NV_E4M3)));
+}
+__device__ __forceinline__ uint32_t e4m3_bits(float v) { return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
+
+// E2M1 code (sign in bit 3) of v, round-to-nearest-even, saturating at 6
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float a = fabsf(v);
+  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
+  return c | (v < 0.f ? 8u : 0u);
+}
+
+// one thread per (row, 64-element K tile): 4 blocks of 16 -> 32 bytes of codes + 4 scale bytes
+__global__ void quantize_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, unsigned char* __restrict__ q,
+                                      unsigned char* __restrict__ sf, float* __restrict__ scales, int64_t rows, int K,
+                                      int ktiles, int ktiles4) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float amax = fmaxf(scales[0], 1e-30f);
+  const float ts = amax / (6.0f * 448.0f);
+  if (idx == 0) scales[1] = ts;
+  if (idx >= rows * ktiles) return;
+  const int64_t r = idx / ktiles;
+  const int kt = (int)(idx - r * ktiles);
+  const float six_ts = 6.0f * ts;
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int k0 = kt * 64 + b * 16;
+    if (k0 >= K) break;
+    float f[16];
+    unpack8(ldg_nc_u4(x + r * ld + k0), *reinterpret_cast<float(*)[8]>(f));
+    unpack8(ldg_nc_u4(x + r * ld + k0 + 8), *reinterpret_cast<float(*)[8]>(f + 8));
+    float bm = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) bm = fmaxf(bm, fabsf(f[e]));
+    const float sraw = __fdiv_rn(bm, six_ts);
+    const float bs = e4m3_round(sraw);
+    sfw |= e4m3_bits(sraw) << (8 * b);
+    const float denom = bs * ts;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const float sv = denom > 0.f ? __fdiv_rn(f[e], denom) : 0.f;
+      w[e >> 3] |= e2m1_code(sv) << (4 * (e & 7));
+    }
+    *reinterpret_cast<uint2*>(q + r * (int64_t)(K >> 1) + (k0 >> 1)) = make_uint2(w[0], w[1]);
+  }
+  const int64_t tile = (r >> 7) * ktiles4 + kt;
+  const int rr = (int)(r & 127);
+  *reinterpret_cast<uint32_t*>(sf + tile * 512 + (rr & 31) * 16 + (rr >> 5) * 4) = sfw;
+}
+
+static int64_t ktiles4_of(int64_t K) { return ceil_div(ceil_div(K, 64), 4) * 4; }
+
+}  // namespace sana
+
+using namespace sana;
+
+extern "C" int64_t sana_nvfp4_sf_bytes(int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0) return 0;
+  return ceil_div(rows, 128) * ktiles4_of(K) * 512;
+}
+
+extern "C" int sana_nvfp4_quantize(const void* x, int64_t ld, void* q, void* sf, float* scales, int64_t rows, int64_t K,
+                                   void* stream) {
+  SANA_REQUIRE(x && q && sf && scales, "sana_nvfp4_quantize: null pointer");
+  SANA_REQUIRE(rows > 0 && K > 0 && K % 32 == 0 && K < (1 << 30), "sana_nvfp4_quantize: K must be a positive multiple of 32");
+  SANA_REQUIRE(ld >= K && ld % 8 == 0, "sana_nvfp4_quantize: ld must be >= K and a multiple of 8");
+  SANA_REQUIRE(aligned16(x) && aligned16(q) && aligned16(sf) && aligned16(scales), "sana_nvfp4_quantize: alignment");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(scales, 0, 2 * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(scales)");
+  e = cudaMemsetAsync(sf, 0, (size_t)sana_nvfp4_sf_bytes(rows, K), st);
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemsetAsync(sf)");
+  const int64_t vecs = rows * (K / 8);
+  int64_t blocks = ceil_div(vecs, 256 * 8);
+  if (blocks > 4 * (int64_t)sm_count()) blocks = 4 * (int64_t)sm_count();
+  absmax_bf16_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ld, rows, (int)K, scales);
+  SANA_LAUNCH_CHECK("absmax kernel");
+  const int64_t ktiles = ceil_div(K, 64);
+  const int64_t total = rows * ktiles;
+  SANA_REQUIRE(ceil_div(total, 128) < ((int64_t)1 << 31), "sana_nvfp4_quantize: too large");
+  quantize_nvfp4_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, static_cast<unsigned char*>(q), static_cast<unsigned char*>(sf), scales,
+      rows, (int)K, (int)ktiles, (int)ktiles4_of(K));
+  SANA_LAUNCH_CHECK("quantize kernel");
+  return SANA_OK;
+}
+
+extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_scales, const void* Wq, const void* sfw,
+                               const float* w_scales, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                               const sana_gemm_epilogue* ep, void* stream) {
+  SANA_REQUIRE(Aq && sfa && a_scales && Wq && sfw && w_scales && out, "sana_gemm_nvfp4: null pointer");
+  SANA_REQUIRE(M > 0 && N > 0 && K > 0, "sana_gemm_nvfp4: M, N, K must be positive");
+  SANA_REQUIRE(K % 32 == 0 && N % 8 == 0 && ldo >= N && ldo % 8 == 0, "sana_gemm_nvfp4: K %% 32, N %% 8, ldo %% 8 required");
+  SANA_REQUIRE(M < ((int64_t)1 << 31) && N < ((int64_t)1 << 31) && K < ((int64_t)1 << 30), "sana_gemm_nvfp4: size out of range");
+  SANA_REQUIRE(aligned16(Aq) && aligned16(Wq) && aligned16(sfa) && aligned16(sfw) && aligned16(out), "sana_gemm_nvfp4: alignment");
+  EpiParams p;
+  int rc = check_epilogue(ep, N, &p, "sana_gemm_nvfp4");
+  if (rc) return rc;
+  SANA_REQUIRE(!p.residual || (aligned16(p.residual) && p.ldr % 8 == 0), "sana_gemm_nvfp4: residual alignment");
+  SANA_REQUIRE(!p.bias || aligned16(p.bias), "sana_gemm_nvfp4: bias alignment");
+  SANA_REQUIRE(!p.gate_table || (aligned16(p.gate_table) && aligned16(p.gate_t)), "sana_gemm_nvfp4: gate alignment");
+  CUtensorMap tmA, tmB;
+  rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Aq, M, K / 2, K / 2, F4_BM, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, F4_BN, 128);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F4_SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_nvfp4_tc)");
+    attr_done = true;
+  }
+  F4Args a;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.ldo = ldo;
+  a.sfa = static_cast<const unsigned char*>(sfa);
+  a.sfb = static_cast<const unsigned char*>(sfw);
+  a.a_scale = a_scales + 1;  // [amax, tensor scale]
+  a.w_scale = w_scales + 1;
+  a.M = (int)M, a.N = (int)N, a.K = (int)K;
+  a.tiles_m = (int)ceil_div(M, F4_BM);
+  a.tiles_n = (int)ceil_div(N, F4_BN);
+  a.ktiles4 = (int)ktiles4_of(K);
+  a.ep = p;
+  const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  gemm_nvfp4_tc_kernel<<<grid, F4_THREADS, F4_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, a);
+  SANA_LAUNCH_CHECK("gemm_nvfp4_tc kernel");
+  return SANA_OK;
+}
+
+extern "C" int sana_gemm_nvfp4_take_device_status(int* status_out) {
+  if (!status_out) return fail(SANA_ERR_INVALID, "sana_gemm_nvfp4_take_device_status: null pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_fp4_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_fp4_status)");
+  if (v != 0) {
+    int zero = 0;
+    e = cudaMemcpyToSymbol(g_fp4_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_fp4_status)");
+  }
+  *status_out = v;
+  return SANA_OK;
+}

@@ -150,6 +150,36 @@ def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+def _epilogue(M: int, Nn: int, dtype, bias, act, relu_cols, gate, residual):
+    """Fills a GemmEpilogue; returns it with the tensors that must stay alive during the call."""
+    ep = GemmEpilogue()
+    keep = []
+    if bias is not None:
+        if bias.numel() != Nn or bias.dtype != dtype:
+            raise SanaLibraryError("gemm: bias must be [N] in the output dtype")
+        bias = bias.contiguous()
+        keep.append(bias)
+        ep.bias = bias.data_ptr()
+    ep.act = act
+    ep.relu_cols = relu_cols
+    ep.rows_per_batch = 1
+    if gate is not None:
+        table, t, row, rows_per_batch = gate
+        if table.shape != (6, Nn) or t.numel() % (6 * Nn) != 0 or table.dtype != dtype or t.dtype != dtype:
+            raise SanaLibraryError("gemm: gate table must be [6, N] and t [B, 6N] in the output dtype")
+        if (M + rows_per_batch - 1) // rows_per_batch > t.numel() // (6 * Nn):
+            raise SanaLibraryError("gemm: gate t has fewer batch rows than M / rows_per_batch")
+        table, t = table.contiguous(), t.contiguous()
+        keep += [table, t]
+        ep.gate_table, ep.gate_t, ep.gate_row, ep.rows_per_batch = table.data_ptr(), t.data_ptr(), row, rows_per_batch
+    if residual is not None:
+        Mr, Nr, ldr = _rows2d(residual, "gemm residual")
+        if Mr != M or Nr != Nn or residual.dtype != dtype:
+            raise SanaLibraryError("gemm: residual must be [M, N] in the output dtype")
+        ep.residual, ep.ldr = residual.data_ptr(), ldr
+    return ep, keep
+
+
 def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, gate, residual, out):
     _need_cuda(a, w, bias, residual, out)
     M, K, lda = _rows2d(a, "gemm A")
@@ -161,31 +191,7 @@ def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, 
     Mo, No, ldo = _rows2d(out, "gemm out")
     if Mo != M or No != Nn or out.dtype != a.dtype:
         raise SanaLibraryError("gemm: bad output tensor")
-    ep = GemmEpilogue()
-    keep = []
-    if bias is not None:
-        if bias.numel() != Nn or bias.dtype != a.dtype:
-            raise SanaLibraryError("gemm: bias must be [N] in A's dtype")
-        bias = bias.contiguous()
-        keep.append(bias)
-        ep.bias = bias.data_ptr()
-    ep.act = act
-    ep.relu_cols = relu_cols
-    ep.rows_per_batch = 1
-    if gate is not None:
-        table, t, row, rows_per_batch = gate
-        if table.shape != (6, Nn) or t.numel() % (6 * Nn) != 0 or table.dtype != a.dtype or t.dtype != a.dtype:
-            raise SanaLibraryError("gemm: gate table must be [6, N] and t [B, 6N] in A's dtype")
-        if (M + rows_per_batch - 1) // rows_per_batch > t.numel() // (6 * Nn):
-            raise SanaLibraryError("gemm: gate t has fewer batch rows than M / rows_per_batch")
-        table, t = table.contiguous(), t.contiguous()
-        keep += [table, t]
-        ep.gate_table, ep.gate_t, ep.gate_row, ep.rows_per_batch = table.data_ptr(), t.data_ptr(), row, rows_per_batch
-    if residual is not None:
-        Mr, Nr, ldr = _rows2d(residual, "gemm residual")
-        if Mr != M or Nr != Nn or residual.dtype != a.dtype:
-            raise SanaLibraryError("gemm: residual must be [M, N] in A's dtype")
-        ep.residual, ep.ldr = residual.data_ptr(), ldr
+    ep, keep = _epilogue(M, Nn, a.dtype, bias, act, relu_cols, gate, residual)
     lib = _lib.load()
     timed = counters.gemm_timing and fn_name == "sana_gemm" and a.dtype == torch.bfloat16
     if timed:
@@ -219,4 +225,79 @@ def take_gemm_device_status() -> int:
     v = C.c_int(0)
     lib = _lib.load()
     _lib.check(lib.sana_gemm_take_device_status(C.byref(v)), "sana_gemm_take_device_status")
+    return v.value
+
+
+class NvFp4Tensor:
+    """A [rows, K] matrix quantised to NVFP4: ``q`` packed E2M1 codes [rows, K/2] (uint8),
+    ``sf`` E4M3 block scales in the tensor core's 512-byte tiles, ``scales`` = device floats
+    (amax, tensor_scale)."""
+
+    __slots__ = ("q", "sf", "scales", "rows", "K")
+
+    def __init__(self, q, sf, scales, rows, K):
+        self.q, self.sf, self.scales, self.rows, self.K = q, sf, scales, rows, K
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 [rows, K] reconstruction (torch math; for tests and diagnostics only)."""
+        lut = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0],
+                           device=self.q.device)
+        codes = torch.stack([self.q & 15, self.q >> 4], dim=-1).reshape(self.rows, self.K).long()
+        vals = lut[codes]
+        ktiles4 = self.sf.numel() // 512 // ((self.rows + 127) // 128)
+        r = torch.arange(self.rows, device=self.q.device)[:, None]
+        kb = torch.arange(self.K // 16, device=self.q.device)[None, :]
+        off = ((r // 128) * ktiles4 + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+        bs = self.sf.view(torch.float8_e4m3fn).float()[off]
+        return (vals.reshape(self.rows, self.K // 16, 16) * (bs * self.scales[1])[..., None]).reshape(self.rows, self.K)
+
+
+def nvfp4_quantize(x: torch.Tensor) -> NvFp4Tensor:
+    """Quantises a bf16 [rows, K] matrix (contiguous rows) along K; K must be a multiple of 32."""
+    _need_cuda(x)
+    rows, K, ld = _rows2d(x, "nvfp4_quantize x")
+    if x.dtype != torch.bfloat16 or K % 32 != 0:
+        raise SanaLibraryError("nvfp4_quantize: needs a bf16 matrix with K a multiple of 32")
+    lib = _lib.load()
+    q = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(lib.sana_nvfp4_sf_bytes(rows, K), dtype=torch.uint8, device=x.device)
+    scales = torch.empty(4, dtype=torch.float32, device=x.device)
+    _lib.check(lib.sana_nvfp4_quantize(x.data_ptr(), ld, q.data_ptr(), sf.data_ptr(), scales.data_ptr(), rows, K,
+                                       _stream()), "sana_nvfp4_quantize")
+    counters.launches += 2
+    return NvFp4Tensor(q, sf, scales, rows, K)
+
+
+def gemm_nvfp4(a: NvFp4Tensor, w: NvFp4Tensor, bias=None, act: int = ACT_NONE, relu_cols: int = 0, gate=None,
+               residual=None, out=None) -> torch.Tensor:
+    """out [M, N] bf16 = epilogue(dequant(a) @ dequant(w).T) on the block-scaled FP4 tensor cores."""
+    if a.K != w.K:
+        raise SanaLibraryError(f"gemm_nvfp4: K mismatch ({a.K} vs {w.K})")
+    M, Nn, K = a.rows, w.rows, a.K
+    if out is None:
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.q.device)
+    Mo, No, ldo = _rows2d(out, "gemm_nvfp4 out")
+    if Mo != M or No != Nn or out.dtype != torch.bfloat16:
+        raise SanaLibraryError("gemm_nvfp4: bad output tensor")
+    _need_cuda(bias, residual, out)
+    ep, keep = _epilogue(M, Nn, torch.bfloat16, bias, act, relu_cols, gate, residual)
+    lib = _lib.load()
+    timed = counters.gemm_timing
+    if timed:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    _lib.check(lib.sana_gemm_nvfp4(a.q.data_ptr(), a.sf.data_ptr(), a.scales.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(),
+                                   w.scales.data_ptr(), out.data_ptr(), ldo, M, Nn, K, C.byref(ep), _stream()),
+               "sana_gemm_nvfp4")
+    if timed:
+        e1.record()
+        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K))
+    counters.launches += 1
+    return out
+
+
+def take_gemm_nvfp4_device_status() -> int:
+    v = C.c_int(0)
+    lib = _lib.load()
+    _lib.check(lib.sana_gemm_nvfp4_take_device_status(C.byref(v)), "sana_gemm_nvfp4_take_device_status")
     return v.value
