@@ -170,19 +170,56 @@ def run_reference(args) -> None:
     }))
 
 
+def run_gemm_rates(tokens: int, iters: int = 20) -> None:
+    """Device-timed rate of each projection shape of a 1.6B-width block, bf16 and NVFP4
+    (one JSON line; quantisation of the operands is outside the timed region)."""
+    from sana_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    shapes = [("qkv", 3 * C, C), ("proj", C, C), ("expand", 2 * HID, C), ("point", C, HID)]
+    out = {"workload": f"projection rates, {tokens} tokens, hidden {C}", "rows": []}
+    for name, n, k in shapes:
+        a = torch.randn(tokens, k, generator=g, device=dev).bfloat16()
+        w = (torch.randn(n, k, generator=g, device=dev) * 0.02).bfloat16()
+        qa, qw = ops.nvfp4_quantize(a), ops.nvfp4_quantize(w)
+        o = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+        row = {"name": name, "M": tokens, "N": n, "K": k}
+        for kind, fn in (("bf16", lambda: ops.gemm(a, w, out=o)), ("nvfp4", lambda: ops.gemm_nvfp4(qa, qw, out=o))):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            row[kind + "_ms"] = ms
+            row[kind + "_tflops"] = 2.0 * tokens * n * k / (ms * 1e-3) / 1e12
+        out["rows"].append(row)
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--gemm-rates", type=int, default=0, metavar="TOKENS",
+                    help="only time the four projection shapes of a block at this many tokens")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
-    ap.add_argument("--depth", type=int, default=DEPTH)
+    ap.add_argument("--depth", type=int, default=None, help="blocks in the stack (default 20; 1 for nvfp4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.gemm_rates:
+        run_gemm_rates(args.gemm_rates)
         return
     args.warmup = max(args.warmup, 3)
 
@@ -204,15 +241,22 @@ def main() -> None:
     dt = torch.bfloat16
     peaks = load_peaks()
 
-    if args.workload == "stack":
-        depth = args.depth
+    nvfp4 = args.workload == "nvfp4"
+    if args.workload in ("stack", "nvfp4"):
+        depth = args.depth or (1 if nvfp4 else DEPTH)
         b0, b1 = sharding.batch_partition(args.batch, world)[rank]
         Bl = b1 - b0
-        grid, tokens = GRID, GRID[0] * GRID[1]
+        grid = (64, 64) if nvfp4 else GRID
+        tokens = grid[0] * grid[1]
         shard = None
         total_units = args.batch * tokens * depth
-        workload = (f"cfg3: Sana-1.6B stack, {depth} SanaMSBlocks, hidden {C}, {C // 32} LA heads x 32, FFN {HID}, "
-                    f"{GRID[0]}x{GRID[1]} grid = {tokens} tokens, global batch {args.batch}")
+        if nvfp4:
+            workload = (f"cfg5: {depth} SanaMSBlock(s) at Sana-1.6B width with NVFP4 qkv/out/FFN projections (E2M1, E4M3 "
+                        f"scale per 16, fp32 scale per tensor, weights and activations), 64x64 grid = {tokens} tokens, "
+                        f"global batch {args.batch}")
+        else:
+            workload = (f"cfg3: Sana-1.6B stack, {depth} SanaMSBlocks, hidden {C}, {C // 32} LA heads x 32, FFN {HID}, "
+                        f"{GRID[0]}x{GRID[1]} grid = {tokens} tokens, global batch {args.batch}")
         parallelism = f"dp{world}"
         scaling = "strong"
     else:
@@ -231,6 +275,7 @@ def main() -> None:
     for i, blk in enumerate(stack.blocks):
         blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, i, 0.02, dt, dev), strict=True)
     stack.set_sequence_shard(shard)
+    stack.set_nvfp4(nvfp4)
 
     # host-resident inputs (pinned) for the end-to-end leg; device copies for the kernel leg
     g = torch.Generator().manual_seed(1234 + rank)
@@ -298,7 +343,10 @@ def main() -> None:
             "config": {"workload": workload, "parallelism": parallelism, "per_gpu_batch": Bl,
                        "l2": "inputs larger than L2 (>3 GB of weights and activations per step)",
                        "cross_attention_core": "torch SDPA (projections on the tcgen05 GEMM)"},
-            "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel (tcgen05, all 8 projections of a block)",
+            "roofline": {"bound": "tensor",
+                         "kernel": ("gemm_nvfp4_tc_kernel + gemm_bf16_tc_kernel (tcgen05; FP4 and bf16 launches pooled, "
+                                    "against the bf16 peak)") if nvfp4 else
+                         "gemm_bf16_tc_kernel (tcgen05, all 8 projections of a block)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),

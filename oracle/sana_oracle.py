@@ -74,16 +74,20 @@ def lite_la_attn_matmul(q, k, v, eps: float, fp32_attention: bool = True) -> tor
 
 
 def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, eps: float = 1e-15,
-                    fp32_attention: bool = True, keep_dtype: bool = False) -> torch.Tensor:
+                    fp32_attention: bool = True, keep_dtype: bool = False, quant_fn=None) -> torch.Tensor:
     """LiteLA.forward, diffusion/model/nets/sana_blocks.py:265-291 (qk_norm off, no rotary).
 
     ``p`` holds ``qkv.weight`` (+ optional ``qkv.bias``), ``proj.weight``, ``proj.bias``.
     ``keep_dtype`` runs the fp32_attention region in the input dtype instead of fp32 - used
-    only to produce fp64 golden values (upstream's ``.float()`` would truncate them)."""
+    only to produce fp64 golden values (upstream's ``.float()`` would truncate them).
+    ``quant_fn`` (e.g. :func:`nvfp4_fake_quant`) replaces input and weight of both Linear
+    layers by their quantise-dequantise image along the contraction dimension - the
+    "upstream run on the dequantised tensors" reference of the FP4 configuration."""
     B, N, C = x.shape
     heads = heads or C // dim
     hd = C // heads
-    qkv = F.linear(x, p["qkv.weight"], p.get("qkv.bias")).reshape(B, N, 3, C)
+    qf = quant_fn or (lambda v: v)
+    qkv = F.linear(qf(x), qf(p["qkv.weight"]), p.get("qkv.bias")).reshape(B, N, 3, C)
     q, k, v = qkv.unbind(2)
     dtype = q.dtype
     q = q.transpose(-1, -2).reshape(B, C // hd, hd, N)
@@ -91,7 +95,7 @@ def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, ep
     v = v.transpose(-1, -2).reshape(B, C // hd, hd, N)
     out = lite_la_attn_matmul(q, k.transpose(-1, -2), v, eps, fp32_attention and not keep_dtype).to(dtype)
     out = out.view(B, C, N).permute(0, 2, 1)
-    return F.linear(out, p["proj.weight"], p["proj.bias"])
+    return F.linear(qf(out), qf(p["proj.weight"]), p["proj.bias"])
 
 
 def lite_la_state(k_relu: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -111,12 +115,16 @@ def lite_la_apply(q_relu: torch.Tensor, state: torch.Tensor, eps: float) -> torc
     return out[..., :-1] / (out[..., -1:] + eps)
 
 
-def glumbconv_forward(x, p: Params, HW: Sequence[int]) -> torch.Tensor:
+def glumbconv_forward(x, p: Params, HW: Sequence[int], quant_fn=None) -> torch.Tensor:
     """GLUMBConv.forward / _apply_spatial, diffusion/model/nets/basic_modules.py:161-199.
 
     ``HW`` = (H, W) or (T, H, W); with three entries the depthwise conv runs per frame.
-    In-place SiLU after the 1x1 expand (act.py:31), separate SiLU for the gate."""
+    In-place SiLU after the 1x1 expand (act.py:31), separate SiLU for the gate.  ``quant_fn``
+    quantise-dequantises input and weight of the two 1x1 convs along the channel dimension."""
     B, N, C = x.shape
+    qf = quant_fn or (lambda v: v)
+    qw = (lambda w: qf(w.reshape(w.shape[0], -1)).reshape(w.shape)) if quant_fn else (lambda w: w)
+    qc = (lambda v: qf(v.permute(0, 2, 3, 1)).permute(0, 3, 1, 2)) if quant_fn else (lambda v: v)
     if len(HW) == 2:
         H, W = HW
         BT = B
@@ -125,14 +133,14 @@ def glumbconv_forward(x, p: Params, HW: Sequence[int]) -> torch.Tensor:
         BT = B * T
     else:
         raise ValueError("HW must have 2 or 3 entries")
-    x = x.reshape(BT, H, W, C).permute(0, 3, 1, 2)
-    x = F.conv2d(x, p["inverted_conv.conv.weight"], p.get("inverted_conv.conv.bias"))
+    x = qf(x).reshape(BT, H, W, C).permute(0, 3, 1, 2)
+    x = F.conv2d(x, qw(p["inverted_conv.conv.weight"]), p.get("inverted_conv.conv.bias"))
     x = F.silu(x)
     wd = p["depth_conv.conv.weight"]
     x = F.conv2d(x, wd, p.get("depth_conv.conv.bias"), padding=wd.shape[-1] // 2, groups=wd.shape[0])
     a, g = torch.chunk(x, 2, dim=1)
     g = F.silu(g)
-    x = F.conv2d(a * g, p["point_conv.conv.weight"], p.get("point_conv.conv.bias"))
+    x = F.conv2d(qc(a * g), qw(p["point_conv.conv.weight"]), p.get("point_conv.conv.bias"))
     Cout = x.shape[1]
     if len(HW) == 3:
         return x.reshape(BT, Cout, H * W).permute(0, 2, 1).reshape(B, N, Cout)
@@ -160,7 +168,7 @@ def cross_attention_forward(x, cond, p: Params, num_heads: int, mask=None) -> to
 
 def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int], mask=None,
                           linear_head_dim: int = 32, fp32_attention: bool = True,
-                          keep_dtype: bool = False, return_branches: bool = False):
+                          keep_dtype: bool = False, return_branches: bool = False, quant_fn=None):
     """SanaMSBlock.forward with attn_type="linear", ffn_type="glumbconv", drop_path 0,
     diffusion/model/nets/sana_multi_scale.py:145-157.
 
@@ -172,10 +180,10 @@ def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int],
     shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
     a = lite_la_forward(t2i_modulate(layer_norm(x), shift_msa, scale_msa), sub(p, "attn"),
                         heads=C // linear_head_dim, eps=BLOCK_LA_EPS,
-                        fp32_attention=fp32_attention, keep_dtype=keep_dtype)
+                        fp32_attention=fp32_attention, keep_dtype=keep_dtype, quant_fn=quant_fn)
     x = x + gate_msa * a
     x = x + cross_attention_forward(x, y, sub(p, "cross_attn"), num_heads, mask)
-    f = glumbconv_forward(t2i_modulate(layer_norm(x), shift_mlp, scale_mlp), sub(p, "mlp"), HW)
+    f = glumbconv_forward(t2i_modulate(layer_norm(x), shift_mlp, scale_mlp), sub(p, "mlp"), HW, quant_fn=quant_fn)
     x = x + gate_mlp * f
     if return_branches:
         return x, a, f

@@ -34,6 +34,23 @@ def _as2d(x: torch.Tensor) -> torch.Tensor:
     return x.reshape(-1, x.shape[-1])
 
 
+def _project(owner: nn.Module, key: str, x2d: torch.Tensor, w2d: torch.Tensor, **epilogue) -> torch.Tensor:
+    """``x2d @ w2d.T`` with the fused epilogue of :func:`ops.gemm`.  When ``owner.nvfp4`` is set
+    both operands are quantised to NVFP4 first: the activation on every call, the weight once
+    (cached on the module until the parameter is modified or moved)."""
+    if not getattr(owner, "nvfp4", False):
+        return ops.gemm(x2d, w2d, **epilogue)
+    if x2d.dtype != torch.bfloat16:
+        raise NotImplementedError("NVFP4 projections take bf16 activations and weights")
+    cache = owner.__dict__.setdefault("_nvfp4_weights", {})
+    tag = (w2d.data_ptr(), w2d._version, tuple(w2d.shape))
+    entry = cache.get(key)
+    if entry is None or entry[0] != tag:
+        entry = (tag, ops.nvfp4_quantize(w2d.contiguous()))
+        cache[key] = entry
+    return ops.gemm_nvfp4(ops.nvfp4_quantize(x2d), entry[1], **epilogue)
+
+
 class LiteLA(nn.Module):
     """ReLU linear attention.  Same arguments and attributes as upstream's LiteLA (which
     derives from timm's Attention: ``qkv``, ``proj``, ``num_heads``, ``scale``,
@@ -64,6 +81,7 @@ class LiteLA(nn.Module):
         self.q_norm = nn.Identity()
         self.k_norm = nn.Identity()
         self.seq_shard: Optional[SequenceShard] = None
+        self.nvfp4 = False  # quantise the qkv / proj projections to NVFP4
 
     # -- pieces shared with the fused block path --------------------------------------------
     def _core(self, qkv: torch.Tensor, B: int, N: int) -> torch.Tensor:
@@ -90,9 +108,9 @@ class LiteLA(nn.Module):
         if rotary_emb is not None:
             raise NotImplementedError("LiteLA with rotary embeddings is not covered by the CUDA kernels yet")
         B, N, C = x.shape
-        qkv = ops.gemm(_as2d(x), self.qkv.weight, bias=self.qkv.bias)
+        qkv = _project(self, "qkv", _as2d(x), self.qkv.weight, bias=self.qkv.bias)
         o = self._core(qkv, B, N)
-        return ops.gemm(o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
+        return _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
 
     @property
     def module_str(self) -> str:
@@ -152,10 +170,12 @@ class GLUMBConv(nn.Module):
         self.point_conv = ConvLayer(hidden_features, out_feature, 1, use_bias=use_bias[2], act=act[2])
         self.in_features, self.hidden_features, self.out_feature = in_features, hidden_features, out_feature
         self.seq_shard: Optional[SequenceShard] = None
+        self.nvfp4 = False  # quantise the two 1x1 projections to NVFP4
 
     def _expand(self, z2d: torch.Tensor) -> torch.Tensor:
         c = self.inverted_conv.conv
-        return ops.gemm(z2d, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias, act=ops.ACT_SILU)
+        return _project(self, "inverted_conv", z2d, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias,
+                        act=ops.ACT_SILU)
 
     def _depthwise_glu(self, u: torch.Tensor, B: int, N: int, HW: Sequence[int]) -> torch.Tensor:
         if HW is None or len(HW) not in (2, 3):
@@ -178,7 +198,7 @@ class GLUMBConv(nn.Module):
         u = self._expand(_as2d(x))
         g = self._depthwise_glu(u, B, N, HW)
         c = self.point_conv.conv
-        out = ops.gemm(g, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias)
+        out = _project(self, "point_conv", g, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias)
         return out.reshape(B, N, -1)
 
 
@@ -252,6 +272,14 @@ class SanaMSBlock(nn.Module):
         self.attn.seq_shard = shard
         self.mlp.seq_shard = shard
 
+    def set_nvfp4(self, enabled: bool = True) -> None:
+        """Run the qkv, attention-output and the two FFN 1x1 projections on the block-scaled FP4
+        tensor cores (E2M1 values, E4M3 scales per 16 channels, fp32 scale per tensor, for both
+        weights and activations).  Linear-attention state, depthwise conv, LayerNorm and the
+        cross-attention stay in bf16/fp32."""
+        self.attn.nvfp4 = enabled
+        self.mlp.nvfp4 = enabled
+
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, HW=None, image_rotary_emb=None, **kwargs):
         if image_rotary_emb is not None:
@@ -270,17 +298,17 @@ class SanaMSBlock(nn.Module):
             x2 = _as2d((x + gate * a).contiguous())
         else:
             z = ops.ln_modulate(x, table, t, 0, 1, LN_EPS)
-            qkv = ops.gemm(_as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
+            qkv = _project(attn, "qkv", _as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
             o = attn._core(qkv, B, N)
-            x2 = ops.gemm(o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
+            x2 = _project(attn, "proj", o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
         o = ca._attend(x2, y, mask, B)
         x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
         z = ops.ln_modulate(x2.view(B, N, C), table, t, 3, 4, LN_EPS)
         u = mlp._expand(_as2d(z))
         g = mlp._depthwise_glu(u, B, N, HW)
         pc = mlp.point_conv.conv
-        x2 = ops.gemm(g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias, gate=(table, t, 5, N),
-                      residual=x2)
+        x2 = _project(mlp, "point_conv", g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias,
+                      gate=(table, t, 5, N), residual=x2)
         return x2.view(B, N, C)
 
 
@@ -297,6 +325,10 @@ class BlockStack(nn.Module):
     def set_sequence_shard(self, shard: Optional[SequenceShard]) -> None:
         for b in self.blocks:
             b.set_sequence_shard(shard)
+
+    def set_nvfp4(self, enabled: bool = True) -> None:
+        for b in self.blocks:
+            b.set_nvfp4(enabled)
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, HW=None, **kwargs):

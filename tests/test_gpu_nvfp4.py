@@ -88,3 +88,43 @@ def test_gemm_nvfp4_epilogues(variant):
                          gate=dgate, residual=res.to(DEV) if res is not None else None)
     assert nmax_err(out, v) < TOL
     assert ops.take_gemm_nvfp4_device_status() == 0
+
+
+def _fp4_block_case(C, heads, B, HW, L, seed):
+    import sana_b200
+    from sana_b200 import synthetic
+
+    dt = torch.bfloat16
+    shp = synthetic.BlockShape("fp4", C, heads, B, HW, text_len=L)
+    params = synthetic.make_block_params(C, shp.ffn_hidden, seed=seed)
+    x, y, t = synthetic.make_block_inputs(shp, seed=seed)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(params, strict=True)
+    blk = blk.to(DEV, dt)
+    blk.set_nvfp4(True)
+    r = lambda v: v.to(dt).float()
+    p32 = {k: r(v) for k, v in params.items()}
+    ref, a_ref, f_ref = O.sana_ms_block_forward(r(x), r(y), r(t), p32, heads, HW, return_branches=True,
+                                               quant_fn=O.nvfp4_fake_quant)
+    out = blk(x.to(DEV, dt), y.to(DEV, dt), t.to(DEV, dt), None, HW)
+    # the two branches on the oracle's modulated input
+    mod = (p32["scale_shift_table"][None] + r(t).reshape(B, 6, -1)).chunk(6, dim=1)
+    z1 = O.t2i_modulate(O.layer_norm(r(x)), mod[0], mod[1]).to(dt)
+    a = blk.attn(z1.to(DEV), HW=HW)
+    f = blk.mlp(z1.to(DEV), HW=HW)
+    a_ref1 = O.lite_la_forward(z1.float(), O.sub(p32, "attn"), heads=C // 32, eps=1e-8, quant_fn=O.nvfp4_fake_quant)
+    f_ref1 = O.glumbconv_forward(z1.float(), O.sub(p32, "mlp"), HW, quant_fn=O.nvfp4_fake_quant)
+    # and the distance of the FP4 block from the unquantised golden block, for the record
+    gold = O.sana_ms_block_forward(r(x), r(y), r(t), p32, heads, HW)
+    return dict(block=cosine(out, ref), attn=cosine(a, a_ref1), mlp=cosine(f, f_ref1),
+                block_err=nmax_err(out, ref), vs_unquantised=cosine(out, gold))
+
+
+@pytest.mark.parametrize("C,heads,B,HW,L", [(256, 4, 2, (12, 16), 20), (2240, 20, 1, (32, 32), 300)])
+def test_nvfp4_block_cosine(C, heads, B, HW, L):
+    """Block with NVFP4 projections against the oracle block run on the dequantised tensors:
+    cosine >= 0.995 on the LiteLA output, the GLUMBConv output and the block output."""
+    res = _fp4_block_case(C, heads, B, HW, L, seed=3)
+    print(res)
+    assert res["attn"] >= 0.995 and res["mlp"] >= 0.995 and res["block"] >= 0.995, res
+    assert ops.take_gemm_nvfp4_device_status() == 0 and ops.take_gemm_device_status() == 0
