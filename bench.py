@@ -186,7 +186,10 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
         qa, qw = ops.nvfp4_quantize(a), ops.nvfp4_quantize(w)
         o = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
         row = {"name": name, "M": tokens, "N": n, "K": k}
-        for kind, fn in (("bf16", lambda: ops.gemm(a, w, out=o)), ("nvfp4", lambda: ops.gemm_nvfp4(qa, qw, out=o))):
+        for kind, variant, fn in (("bf16_1cta", 1, lambda: ops.gemm(a, w, out=o)),
+                                  ("bf16_2cta", 2, lambda: ops.gemm(a, w, out=o)),
+                                  ("nvfp4", 0, lambda: ops.gemm_nvfp4(qa, qw, out=o))):
+            ops.set_gemm_variant(variant)
             for _ in range(3):
                 fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

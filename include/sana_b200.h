@@ -191,6 +191,11 @@ int sana_gemm_nvfp4_take_device_status(int* status_out);
  * last call (host-synchronising: use in tests / after a failure, not per step). */
 int sana_gemm_take_device_status(int* status_out);
 
+/* Kernel choice of the bf16 sana_gemm (process-wide; for tests and measurements):
+ * 0 = per problem (default: CTA-pair kernel, tcgen05 cta_group::2 with 256-row tiles, when
+ * M >= 2048, else the single-CTA kernel), 1 = always single-CTA, 2 = always CTA-pair. */
+int sana_gemm_set_variant(int variant);
+
 #ifdef __cplusplus
 }
 #endif

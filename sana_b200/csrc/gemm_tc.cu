@@ -350,6 +350,13 @@ static int pick_bn(int64_t M, int64_t N) {
   return best;
 }
 
+int gemm_tc2_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
+                    int64_t N, int64_t K, const EpiParams& ep, cudaStream_t st);
+int gemm_tc2_take_status(int* v);
+
+// 0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA-pair kernel
+static int g_gemm_variant = 0;
+
 int gemm_tc_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
                    int64_t N, int64_t K, const EpiParams& ep, cudaStream_t st) {
   SANA_REQUIRE(aligned16(A) && aligned16(Wt) && aligned16(out), "sana_gemm: pointers must be 16-byte aligned");
@@ -358,6 +365,9 @@ int gemm_tc_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void
   SANA_REQUIRE(!ep.residual || (aligned16(ep.residual) && ep.ldr % 8 == 0), "sana_gemm: residual alignment");
   SANA_REQUIRE(!ep.bias || aligned16(ep.bias), "sana_gemm: bias alignment");
   SANA_REQUIRE(!ep.gate_table || (aligned16(ep.gate_table) && aligned16(ep.gate_t)), "sana_gemm: gate alignment");
+  // CTA pairs pay off once there are enough 256-row tiles to fill the device
+  const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && M >= 2048);
+  if (pair) return gemm_tc2_launch(A, lda, Wt, ldw, out, ldo, M, N, K, ep, st);
   CUtensorMap tmA;
   int rc = make_tmap(&tmA, A, M, K, lda, TC_BM);
   if (rc) return rc;
@@ -388,6 +398,15 @@ extern "C" int sana_gemm_take_device_status(int* status_out) {
     e = cudaMemcpyToSymbol(sana::g_gemm_status, &zero, sizeof(int));
     if (e != cudaSuccess) return sana::cuda_status(e, "cudaMemcpyToSymbol(g_gemm_status)");
   }
-  *status_out = v;
+  int v2 = 0;
+  int rc = sana::gemm_tc2_take_status(&v2);
+  if (rc) return rc;
+  *status_out = v != 0 ? v : (v2 != 0 ? 100 + v2 : 0);  // 1xx = recorded by the CTA-pair kernel
+  return SANA_OK;
+}
+
+extern "C" int sana_gemm_set_variant(int variant) {
+  if (variant < 0 || variant > 2) return sana::fail(SANA_ERR_INVALID, "sana_gemm_set_variant: 0, 1 or 2");
+  sana::g_gemm_variant = variant;
   return SANA_OK;
 }

@@ -1,0 +1,382 @@
+// bf16 projection, CTA-pair variant: two CTAs of a cluster (one SM each) share one 256 x BN
+// output tile.  Each CTA loads its own 128 rows of A and HALF of the W tile (BN/2 rows) into
+// its shared memory (plain TMA loads, no multicast); the pair's leader (cluster rank 0)
+// issues tcgen05.mma.cta_group::2 (M = 256), which reads both halves of W and writes each
+// CTA's 128 accumulator rows into that CTA's tensor memory.  Per SM this moves 30 KiB per K
+// block through shared memory instead of 44 KiB for the same math, which is what keeps the
+// tensor pipe fed.  Epilogue, pipeline and bounded waits are those of the single-CTA kernel.
+//
+// Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' loads; empty[s]
+// and tfull[a] live in both CTAs and are signalled by the leader's tcgen05.commit with a
+// two-CTA arrive mask; tempty[a] lives in the leader and collects the 16 epilogue warps of
+// the pair (the peer's warps arrive remotely).
+#include "tc_common.cuh"
+
+namespace sana {
+
+__device__ int g_gemm2_status = 0;  // soft-error word of this kernel's bounded waits
+
+constexpr int T2_BM = 128;                      // rows per CTA (256 per pair)
+constexpr int T2_BK = 64;
+constexpr int T2_A_BYTES = T2_BM * T2_BK * 2;   // 16 KiB
+constexpr int T2_EPI_WARPS = 8;
+constexpr int T2_THREADS = 64 + 32 * T2_EPI_WARPS;
+constexpr int T2_SMEM_LIMIT = 232448;
+constexpr int T2_CTRL_BYTES = 256;
+
+template <int BN>
+struct T2Cfg {
+  static constexpr int BH = BN / 2;                       // W rows held by each CTA
+  static constexpr int B_BYTES = BH * T2_BK * 2;
+  static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (T2_SMEM_LIMIT - T2_CTRL_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + T2_CTRL_BYTES;
+  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  // D=f32, A=B=bf16, K-major, N>>3 at bit 17, M=256 (>>4) at bit 24
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                    ((uint32_t)(256 >> 4) << 24);
+  static constexpr int HALF = BN / 2;
+  static constexpr int NCHUNK = HALF / 16;
+  static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN must be a multiple of 32 in [64, 256]");
+  static_assert(STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned");
+  static_assert(16 * STAGES + 40 <= T2_CTRL_BYTES, "control block too small");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes are counted on a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives (once all prior MMAs of this thread completed) on the barrier at this offset in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask)
+               : "memory");
+}
+
+struct T2Args {
+  __nv_bfloat16* out;
+  int64_t ldo;
+  int M, N, K;
+  int tiles_m, tiles_n;  // tiles_m counts 256-row pair tiles
+  EpiParams ep;
+};
+
+struct T2Step {
+  uint32_t acc[16];
+  uint4 bias[2], gtab[2], gt[2], res[2];
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
+gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const T2Args args) {
+  using Cfg = T2Cfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t tiles_base = smem_u32(smem_raw);
+  const uint32_t ctrl = tiles_base + STAGES * Cfg::STAGE_BYTES;
+  unsigned char* ctrl_gen = smem_raw + STAGES * Cfg::STAGE_BYTES;
+  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort
+  const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
+  const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
+
+  // the dynamic shared window starts at the same offset in every CTA, so this is cluster-uniform
+  if ((tiles_base & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(&g_gemm2_status, 9);
+    return;
+  }
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int kblocks = (args.K + T2_BK - 1) / T2_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * T2_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates collectively
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) ---------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      const uint32_t full0 = map_to_cta(bar_full, 0);  // the leader's full barriers, cluster address
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile / args.tiles_n) * (2 * T2_BM) + (int)rank * T2_BM;
+        const int n0 = (tile % args.tiles_n) * BN + (int)rank * Cfg::BH;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_gemm2_status)) { ok = false; break; }
+          const uint32_t sa = tiles_base + stage * Cfg::STAGE_BYTES;
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * Cfg::STAGE_BYTES);
+          tma_load_2d_pair(sa, &tmA, full0 + 8 * stage, kb * T2_BK, m0);
+          tma_load_2d_pair(sa + T2_A_BYTES, &tmB, full0 + 8 * stage, kb * T2_BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------
+    if (leader && lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc_phase = 0u;
+      bool ok = true;
+      int it = 0;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+        const int a = it & 1;
+        if (!mbar_wait(bar_tempty + 8 * a, ((acc_phase >> a) & 1u) ^ 1u, abort_flag, 2, &g_gemm2_status)) { ok = false; break; }
+        acc_phase ^= 1u << a;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_gemm2_status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + T2_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < T2_BK / 16; ++k)
+            umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), Cfg::IDESC, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(bar_empty + 8 * stage);  // frees this stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(bar_tfull + 8 * a);  // accumulator complete, both CTAs
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps (both CTAs) -------------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const EpiParams& ep = args.ep;
+    const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(ep.bias);
+    const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
+    const __nv_bfloat16* gt = static_cast<const __nv_bfloat16*>(ep.gate_t);
+    const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(ep.residual);
+    const int64_t N = args.N;
+    const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+    uint32_t full_phase = 0u;
+    bool ok = true;
+    int it = 0;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+      const int a = it & 1;
+      const int m0 = (tile / args.tiles_n) * (2 * T2_BM) + (int)rank * T2_BM;
+      const int64_t nbase = (int64_t)(tile % args.tiles_n) * BN + half * Cfg::HALF;
+      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const bool row_ok = m < args.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
+      __nv_bfloat16* orow = args.out + m * args.ldo;
+      const __nv_bfloat16* gtrow = nullptr;
+      if (gtab) gtrow = gt + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N;
+      const __nv_bfloat16* grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
+      const __nv_bfloat16* rrow = res ? res + m * ep.ldr : nullptr;
+
+      T2Step st[2];
+      auto fetch_side = [&](T2Step& s, int c) {
+        const int64_t n = nbase + 16 * c;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int64_t nj = n + 8 * j;
+          const bool in = nj < N;
+          s.bias[j] = (bias && in) ? __ldg(reinterpret_cast<const uint4*>(bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          if (gtab) {
+            s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+            s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          s.res[j] = (res && in && row_ok) ? ldg_nc_u4(rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      fetch_side(st[0], 0);
+      if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_gemm2_status)) { ok = false; break; }
+      full_phase ^= 1u << a;
+      tcgen05_fence_after();
+      if (nbase < N) tmem_ld_32x16(taddr, st[0].acc);
+#pragma unroll
+      for (int c = 0; c < Cfg::NCHUNK; ++c) {
+        const int64_t n = nbase + 16 * c;
+        if (n >= N) break;
+        T2Step& cur = st[c & 1];
+        tmem_ld_wait();
+        if (c + 1 < Cfg::NCHUNK && n + 16 < N) {
+          tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
+          fetch_side(st[(c + 1) & 1], c + 1);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (n + 8 * j < N) {
+              float v[8], f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]);
+              if (bias) {
+                unpack8(cur.bias[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              if (ep.act == 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+              } else if (ep.act == 2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+              }
+              if (gtab) {
+                float g[8];
+                unpack8(cur.gtab[j], g);
+                unpack8(cur.gt[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+              }
+              if (res) {
+                unpack8(cur.res[j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += f[e];
+              }
+              *reinterpret_cast<uint4*>(orow + n + 8 * j) =
+                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * a);  // the leader's barrier collects both CTAs
+    }
+  }
+
+  // ------------------------------- teardown ---------------------------------------------
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the other CTA may still signal or read it
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+template <int BN>
+static int launch_pair_bn(const void* A, int64_t lda, const void* Wt, int64_t ldw, int64_t M, int64_t N, int64_t K,
+                          T2Args& args, cudaStream_t st) {
+  using Cfg = T2Cfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda * 2, T2_BM, T2_BK);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Wt, N, K, ldw * 2, Cfg::BH, T2_BK);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_bf16_tc2)");
+    attr_done = true;
+  }
+  args.tiles_n = (int)ceil_div(N, BN);
+  const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n;
+  const int64_t max_clusters = sm_count() / 2;
+  const int grid = (int)(2 * (tiles < max_clusters ? tiles : max_clusters));
+  gemm_bf16_tc2_kernel<BN><<<grid, T2_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, args);
+  SANA_LAUNCH_CHECK("gemm_bf16_tc2 kernel");
+  return SANA_OK;
+}
+
+int gemm_tc2_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
+                    int64_t N, int64_t K, const EpiParams& ep, cudaStream_t st) {
+  T2Args args;
+  args.out = static_cast<__nv_bfloat16*>(out);
+  args.ldo = ldo;
+  args.M = (int)M, args.N = (int)N, args.K = (int)K;
+  args.tiles_m = (int)ceil_div(M, 2 * T2_BM);
+  args.tiles_n = 0;
+  args.ep = ep;
+  // tile width: minimise (waves over the CTA pairs) x BN
+  const int cands[4] = {256, 224, 192, 128};
+  const int64_t clusters = sm_count() / 2;
+  int best = 128;
+  int64_t best_cost = -1;
+  for (int bn : cands) {
+    const int64_t cost = ceil_div((int64_t)args.tiles_m * ceil_div(N, bn), clusters) * bn;
+    if (best_cost < 0 || cost < best_cost) best_cost = cost, best = bn;
+  }
+  switch (best) {
+    case 256: return launch_pair_bn<256>(A, lda, Wt, ldw, M, N, K, args, st);
+    case 224: return launch_pair_bn<224>(A, lda, Wt, ldw, M, N, K, args, st);
+    case 192: return launch_pair_bn<192>(A, lda, Wt, ldw, M, N, K, args, st);
+    default: return launch_pair_bn<128>(A, lda, Wt, ldw, M, N, K, args, st);
+  }
+}
+
+int gemm_tc2_take_status(int* v) {
+  cudaError_t e = cudaMemcpyFromSymbol(v, g_gemm2_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_gemm2_status)");
+  if (*v != 0) {
+    int zero = 0;
+    e = cudaMemcpyToSymbol(g_gemm2_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_gemm2_status)");
+  }
+  return SANA_OK;
+}
+
+}  // namespace sana

@@ -220,6 +220,11 @@ def gemm_simt(a, w, bias=None, act: int = ACT_NONE, relu_cols: int = 0, gate=Non
     return _gemm("sana_gemm_simt", a, w, bias, act, relu_cols, gate, residual, out)
 
 
+def set_gemm_variant(variant: int) -> None:
+    """0 = choose per problem, 1 = single-CTA tcgen05 kernel, 2 = CTA-pair (cta_group::2) kernel."""
+    _lib.check(_lib.load().sana_gemm_set_variant(variant), "sana_gemm_set_variant")
+
+
 def take_gemm_device_status() -> int:
     """Code recorded by a timed-out wait inside the tensor-core GEMM (0 = none).  Synchronises."""
     v = C.c_int(0)

@@ -186,6 +186,34 @@ def test_gemm_epilogues(dt, tol, variant):
         assert ops.take_gemm_device_status() == 0
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(256, 224, 64), (300, 448, 2240), (1, 8, 8), (513, 520, 200), (4096, 2240, 5600),
+                                   (2050, 6720, 2240)])
+def test_gemm_bf16_both_tensor_core_kernels(variant, M, N, K):
+    """Single-CTA (1) and CTA-pair / cta_group::2 (2) kernels, forced, with the full epilogue."""
+    B, rpb = 3, (M + 2) // 3
+    a, w = _r(M, K, seed=M).bfloat16(), _r(N, K, seed=N + 1, scale=0.05).bfloat16()
+    bias = _r(N, seed=3).bfloat16()
+    gate = (_r(6, N, seed=4).bfloat16(), _r(B, 6 * N, seed=5).bfloat16(), 2, rpb)
+    res = _r(M, N, seed=6).bfloat16()
+    ref_plain = _gemm_ref(a, w, None, 0, 0, None, None)
+    ref_full = _gemm_ref(a, w, bias, 0, 0, gate, res)
+    ref_silu = _gemm_ref(a, w, bias, ops.ACT_SILU, 0, None, None)
+    ops.set_gemm_variant(variant)
+    try:
+        ad, wd = a.to(DEV), w.to(DEV)
+        out_plain = ops.gemm(ad, wd)
+        out_full = ops.gemm(ad, wd, bias=bias.to(DEV), gate=(gate[0].to(DEV), gate[1].to(DEV), 2, rpb), residual=res.to(DEV))
+        out_silu = ops.gemm(ad, wd, bias=bias.to(DEV), act=ops.ACT_SILU)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_gemm_variant(0)
+    assert ops.take_gemm_device_status() == 0
+    assert nmax_err(out_plain, ref_plain) < BF16_OUT
+    assert nmax_err(out_full, ref_full) < BF16_OUT
+    assert nmax_err(out_silu, ref_silu) < BF16_OUT
+
+
 def test_gemm_strided_operands():
     """A and the output may be column slices of wider tensors (qkv slices, residual views)."""
     M, N, K = 160, 64, 96
