@@ -42,9 +42,12 @@ C, HEADS, HID, DEPTH, GRID, TEXT = 2240, 20, 5600, 20, (128, 128), 300
 GLOBAL_BATCH = 8
 SEQPAR_GRID = (21, 45, 80)
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists for that shape).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core GEMM, averaged over the seven
+# launches of one block at batch 1 (ncu capture summarised in
+# profiles/stack_1600m_16k_tokens_launch_shares.md: 1.993 GB / 7).  The bench's launches carry
+# `per-GPU batch` times the rows, and activations dominate the bytes, so the figure is scaled by
+# the per-GPU batch.
+NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 = 284.7e6
 
 
 def block_roofline_seconds(T: int, B: int, peaks: dict) -> float:
@@ -324,9 +327,17 @@ def main() -> None:
         total_ms = timed(step, args.steps)
     ops.counters.gemm_timing = False
     launches = ops.counters.launches
-    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in ops.counters.gemm_events)
-    gemm_flops = sum(f for _, _, f in ops.counters.gemm_events)
+    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in ops.counters.gemm_events)
+    gemm_flops = sum(f for _, _, f, _ in ops.counters.gemm_events)
     n_gemm = len(ops.counters.gemm_events)
+    by_shape = {}
+    for e0, e1, f, label in ops.counters.gemm_events:
+        ent = by_shape.setdefault(label, [0, 0.0, 0.0])
+        ent[0] += 1
+        ent[1] += e0.elapsed_time(e1)
+        ent[2] += f
+    gemm_breakdown = {k: {"launches": v[0], "avg_ms": v[1] / v[0], "tflops": v[2] / (v[1] * 1e-3) / 1e12}
+                      for k, v in by_shape.items()}
     status = ops.take_gemm_device_status()
 
     for _ in range(2):
@@ -353,13 +364,13 @@ def main() -> None:
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
-                         "share_of_step": gemm_ms / total_ms, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         "share_of_step": gemm_ms / total_ms, "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 * Bl) if args.workload == "stack" else None},
             "block_roofline": {"t_roof_ms_per_step": roof_s * 1e3, "frac": roof_s * 1e3 / ms_per_step,
                                "formula": "F_gemm/P_tensor + 11.5*T*C*e/BW_hbm, per block"},
             "e2e": {"value": total_units / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_h.nbytes + y_h.nbytes + t_h.nbytes, "d2h_bytes_per_step": out_h.nbytes,
                     "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": launches, "gemm_device_status": status, "clocks": clk.summary(),
+            "gemm_breakdown": gemm_breakdown, "gpu_launches": launches, "gemm_device_status": status, "clocks": clk.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
             v, cores, sample = cpu_block_tokens_per_s()

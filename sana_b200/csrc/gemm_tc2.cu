@@ -94,11 +94,6 @@ struct T2Args {
   EpiParams ep;
 };
 
-struct T2Step {
-  uint32_t acc[16];
-  uint4 bias[2], gtab[2], gt[2], res[2];
-};
-
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const T2Args args) {
@@ -208,10 +203,6 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const EpiParams& ep = args.ep;
-    const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(ep.bias);
-    const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
-    const __nv_bfloat16* gt = static_cast<const __nv_bfloat16*>(ep.gate_t);
-    const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(ep.residual);
     const int64_t N = args.N;
     const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
     uint32_t full_phase = 0u;
@@ -224,80 +215,14 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int64_t m = (int64_t)m0 + quad * 32 + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
-      __nv_bfloat16* orow = args.out + m * args.ldo;
-      const __nv_bfloat16* gtrow = nullptr;
-      if (gtab) gtrow = gt + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N;
-      const __nv_bfloat16* grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
-      const __nv_bfloat16* rrow = res ? res + m * ep.ldr : nullptr;
-
-      T2Step st[2];
-      auto fetch_side = [&](T2Step& s, int c) {
-        const int64_t n = nbase + 16 * c;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int64_t nj = n + 8 * j;
-          const bool in = nj < N;
-          s.bias[j] = (bias && in) ? __ldg(reinterpret_cast<const uint4*>(bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
-          if (gtab) {
-            s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
-            s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
-          }
-          s.res[j] = (res && in && row_ok) ? ldg_nc_u4(rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
-        }
-      };
-      fetch_side(st[0], 0);
+      const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
+      EpiStep st[2];
+      epi_prefetch_residual<Cfg::NCHUNK>(row);
+      epi_fetch(row, st[0], 0);  // operands that do not depend on the accumulator: requested before the wait
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_gemm2_status)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      if (nbase < N) tmem_ld_32x16(taddr, st[0].acc);
-#pragma unroll
-      for (int c = 0; c < Cfg::NCHUNK; ++c) {
-        const int64_t n = nbase + 16 * c;
-        if (n >= N) break;
-        T2Step& cur = st[c & 1];
-        tmem_ld_wait();
-        if (c + 1 < Cfg::NCHUNK && n + 16 < N) {
-          tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
-          fetch_side(st[(c + 1) & 1], c + 1);
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (n + 8 * j < N) {
-              float v[8], f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]);
-              if (bias) {
-                unpack8(cur.bias[j], f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] += f[e];
-              }
-              if (ep.act == 1) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
-              } else if (ep.act == 2) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
-              }
-              if (gtab) {
-                float g[8];
-                unpack8(cur.gtab[j], g);
-                unpack8(cur.gt[j], f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
-              }
-              if (res) {
-                unpack8(cur.res[j], f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] += f[e];
-              }
-              *reinterpret_cast<uint4*>(orow + n + 8 * j) =
-                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-            }
-          }
-        }
-      }
+      epi_drain<Cfg::NCHUNK, false>(row, ep, taddr, st, 1.0f);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * a);  // the leader's barrier collects both CTAs

@@ -116,6 +116,128 @@ __device__ __forceinline__ float fast_silu(float x) {
   return x * r;
 }
 
+// ---- fused epilogue of one accumulator row-half ---------------------------------------------
+// An epilogue warp owns 32 accumulator rows (its TMEM lane quadrant) and NCHUNK steps of 16
+// columns.  Per step a lane needs 16 accumulator words plus, for its row, 32 bytes each of
+// bias, gate table, gate timestep vector and residual.  The residual comes from DRAM: its
+// lines are pulled into L2 when the tile starts (long before the accumulator is ready), and
+// every step's operands are loaded into registers one step ahead of their use.
+struct EpiStep {
+  uint32_t acc[16];
+  uint4 bias[2], gtab[2], gt[2], res[2];
+};
+
+struct EpiRow {
+  const __nv_bfloat16 *bias, *grow, *gtrow, *rrow;
+  __nv_bfloat16* orow;
+  int64_t nbase, N;
+  bool row_ok;
+};
+
+__device__ __forceinline__ EpiRow epi_row_setup(const EpiParams& ep, __nv_bfloat16* out, int64_t ldo, int64_t m,
+                                                bool row_ok, int64_t nbase, int64_t N) {
+  EpiRow r;
+  r.bias = static_cast<const __nv_bfloat16*>(ep.bias);
+  const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
+  r.grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
+  r.gtrow = gtab ? static_cast<const __nv_bfloat16*>(ep.gate_t) + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N
+                 : nullptr;
+  r.rrow = ep.residual ? static_cast<const __nv_bfloat16*>(ep.residual) + m * ep.ldr : nullptr;
+  r.orow = out + m * ldo;
+  r.nbase = nbase;
+  r.N = N;
+  r.row_ok = row_ok;
+  return r;
+}
+
+template <int NCHUNK>
+__device__ __forceinline__ void epi_prefetch_residual(const EpiRow& r) {
+  if (r.rrow && r.row_ok) {
+#pragma unroll
+    for (int c = 0; c < NCHUNK; c += 4) {  // 4 steps x 32 bytes = one 128-byte line
+      const int64_t n = r.nbase + 16 * c;
+      if (n < r.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(r.rrow + n));
+    }
+    // the half-row need not start on a line boundary: also touch the line of its last step
+    const int64_t nl = r.nbase + 16 * (NCHUNK - 1);
+    if (nl < r.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(r.rrow + nl));
+  }
+}
+
+__device__ __forceinline__ void epi_fetch(const EpiRow& r, EpiStep& s, int c) {
+  const int64_t n = r.nbase + 16 * c;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int64_t nj = n + 8 * j;
+    const bool in = nj < r.N;
+    s.bias[j] = (r.bias && in) ? __ldg(reinterpret_cast<const uint4*>(r.bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
+    if (r.grow) {
+      s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+      s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    s.res[j] = (r.rrow && in && r.row_ok) ? ldg_nc_u4(r.rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Reads the accumulator (already complete) 16 columns at a time, applies the epilogue and
+// stores bf16.  st[0] must hold the side operands of step 0 (epi_fetch) on entry.
+template <int NCHUNK, bool SCALE>
+__device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, uint32_t taddr, EpiStep (&st)[2],
+                                          float alpha) {
+  if (r.nbase < r.N) tmem_ld_32x16(taddr, st[0].acc);
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int64_t n = r.nbase + 16 * c;
+    if (n >= r.N) break;  // uniform: the rest of this half lies outside the matrix
+    EpiStep& cur = st[c & 1];
+    tmem_ld_wait();
+    if (c + 1 < NCHUNK && n + 16 < r.N) {
+      tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
+      epi_fetch(r, st[(c + 1) & 1], c + 1);
+    }
+    if (r.row_ok) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (n + 8 * j < r.N) {
+          float v[8], f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]);
+          if (SCALE) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] *= alpha;
+          }
+          if (r.bias) {
+            unpack8(cur.bias[j], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += f[e];
+          }
+          if (ep.act == 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+          } else if (ep.act == 2) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+          }
+          if (r.grow) {
+            float g[8];
+            unpack8(cur.gtab[j], g);
+            unpack8(cur.gt[j], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+          }
+          if (r.rrow) {
+            unpack8(cur.res[j], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += f[e];
+          }
+          *reinterpret_cast<uint4*>(r.orow + n + 8 * j) =
+              make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+      }
+    }
+  }
+}
 
 // ---- host helpers -----------------------------------------------------------------------------
 // 2-D tiled tensor map over a row-major [rows, cols] matrix of `elem_bytes`-wide elements, row

@@ -27,7 +27,7 @@ class _Counters:
     def __init__(self):
         self.launches = 0
         self.gemm_timing = False
-        self.gemm_events = []  # (start, end, flops)
+        self.gemm_events = []  # (start, end, flops, label)
 
     def reset(self):
         self.launches = 0
@@ -150,6 +150,11 @@ def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+def _epi_tag(bias, act, gate, residual) -> str:
+    return (" +bias" if bias is not None else "") + (" +silu" if act == ACT_SILU else "") + \
+        (" *gate" if gate is not None else "") + (" +res" if residual is not None else "")
+
+
 def _epilogue(M: int, Nn: int, dtype, bias, act, relu_cols, gate, residual):
     """Fills a GemmEpilogue; returns it with the tensors that must stay alive during the call."""
     ep = GemmEpilogue()
@@ -201,7 +206,7 @@ def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, 
                                      _dtype_code(a.dtype), _stream()), fn_name)
     if timed:
         e1.record()
-        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K))
+        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K, f"bf16 {M}x{Nn}x{K}" + _epi_tag(bias, act, gate, residual)))
     counters.launches += 1
     return out
 
@@ -296,7 +301,7 @@ def gemm_nvfp4(a: NvFp4Tensor, w: NvFp4Tensor, bias=None, act: int = ACT_NONE, r
                "sana_gemm_nvfp4")
     if timed:
         e1.record()
-        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K))
+        counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K, f"nvfp4 {M}x{Nn}x{K}" + _epi_tag(bias, act, gate, residual)))
     counters.launches += 1
     return out
 
