@@ -54,6 +54,17 @@ int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, i
                      int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * RMSNorm with weight over the channel dimension:  y = weight * x * rsqrt(mean_c(x^2) + eps)
+ * Replaces `self.q_norm(q)` / `self.k_norm(k)` of LiteLA (qk_norm=True; RMSNorm over the full
+ * C, diffusion/model/nets/sana_blocks.py:238-243,274-275 with norms.py:216-231) and of the
+ * cross-attention (cross_norm=True, sana_blocks.py:62-64,77-78).
+ *   x, y [rows, C] with row strides ldx / ldy in elements (column slices of the qkv / kv
+ *   projections are fine; y may alias x); weight [C].  fp32 statistics, one rounding on store.
+ */
+int sana_rmsnorm(const void* x, int64_t ldx, const void* weight, void* y, int64_t ldy, int64_t rows,
+                 int64_t C, float eps, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * ReLU linear attention, state reduction:
  *   state[b, h, i, j] = sum_n v1[b, n, h, i] * relu(k[b, n, h, j]),  v1 = [v ; 1]
  * i in [0, 33), j in [0, 32): 32 value rows plus the "ones" row that upstream creates with

@@ -56,6 +56,14 @@ def layer_norm(x: torch.Tensor) -> torch.Tensor:
     return F.layer_norm(x, (x.shape[-1],), None, None, LN_EPS)
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm.forward, diffusion/model/norms.py:216-231 (norm over the last dimension, computed
+    in fp32 - or in x's dtype when that is wider - then cast back)."""
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    n = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (weight.view(*([1] * (x.dim() - 1)), -1) * n).type_as(x)
+
+
 def lite_la_attn_matmul(q, k, v, eps: float, fp32_attention: bool = True) -> torch.Tensor:
     """LiteLA.attn_matmul, diffusion/model/nets/sana_blocks.py:245-263.
 
@@ -74,7 +82,8 @@ def lite_la_attn_matmul(q, k, v, eps: float, fp32_attention: bool = True) -> tor
 
 
 def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, eps: float = 1e-15,
-                    fp32_attention: bool = True, keep_dtype: bool = False, quant_fn=None) -> torch.Tensor:
+                    fp32_attention: bool = True, keep_dtype: bool = False, quant_fn=None,
+                    norm_eps: float = 1e-5) -> torch.Tensor:
     """LiteLA.forward, diffusion/model/nets/sana_blocks.py:265-291 (qk_norm off, no rotary).
 
     ``p`` holds ``qkv.weight`` (+ optional ``qkv.bias``), ``proj.weight``, ``proj.bias``.
@@ -90,6 +99,9 @@ def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, ep
     qkv = F.linear(qf(x), qf(p["qkv.weight"]), p.get("qkv.bias")).reshape(B, N, 3, C)
     q, k, v = qkv.unbind(2)
     dtype = q.dtype
+    if "q_norm.weight" in p:  # qk_norm=True: RMSNorm over the full C, sana_blocks.py:238-243,274-275
+        q = rms_norm(q, p["q_norm.weight"], norm_eps)
+        k = rms_norm(k, p["k_norm.weight"], norm_eps)
     q = q.transpose(-1, -2).reshape(B, C // hd, hd, N)
     k = k.transpose(-1, -2).reshape(B, C // hd, hd, N)
     v = v.transpose(-1, -2).reshape(B, C // hd, hd, N)
@@ -155,6 +167,9 @@ def cross_attention_forward(x, cond, p: Params, num_heads: int, mask=None) -> to
     q = F.linear(x, p["q_linear.weight"], p["q_linear.bias"])
     kv = F.linear(cond, p["kv_linear.weight"], p["kv_linear.bias"]).view(B, -1, 2, C)
     k, v = kv.unbind(2)
+    if "q_norm.weight" in p:  # cross_norm=True: RMSNorm(d_model, eps=1e-6), sana_blocks.py:62-64,77-78
+        q = rms_norm(q, p["q_norm.weight"], 1e-6)
+        k = rms_norm(k, p["k_norm.weight"], 1e-6)
     q = q.view(B, -1, num_heads, hd).transpose(1, 2)
     k = k.view(B, -1, num_heads, hd).transpose(1, 2)
     v = v.view(B, -1, num_heads, hd).transpose(1, 2)

@@ -51,6 +51,24 @@ def _project(owner: nn.Module, key: str, x2d: torch.Tensor, w2d: torch.Tensor, *
     return ops.gemm_nvfp4(ops.nvfp4_quantize(x2d), entry[1], **epilogue)
 
 
+class RMSNorm(nn.Module):
+    """Parameter holder with upstream's RMSNorm state-dict key (``weight``,
+    diffusion/model/norms.py:182-231); the attention modules apply it in place on their
+    q / k projections through the CUDA kernel."""
+
+    def __init__(self, dim: int, scale_factor=1.0, eps: float = 1e-6, norm_dim: int = -1):
+        super().__init__()
+        if norm_dim != -1:
+            raise NotImplementedError("RMSNorm over a dimension other than the last is not covered")
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim) * scale_factor)
+        self.norm_dim = norm_dim
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = x.reshape(-1, x.shape[-1]).clone()
+        return ops.rmsnorm_(y, self.weight, float(self.eps)).reshape(x.shape)
+
+
 class LiteLA(nn.Module):
     """ReLU linear attention.  Same arguments and attributes as upstream's LiteLA (which
     derives from timm's Attention: ``qkv``, ``proj``, ``num_heads``, ``scale``,
@@ -62,8 +80,6 @@ class LiteLA(nn.Module):
                  eps=1e-15, use_bias=False, qk_norm=False, norm_eps=1e-5):
         super().__init__()
         heads = heads or int(out_dim // dim * heads_ratio)
-        if qk_norm:
-            raise NotImplementedError("LiteLA(qk_norm=True) is not covered by the CUDA kernels yet")
         if in_dim != out_dim or out_dim // heads != ops.HEAD_DIM or out_dim % heads != 0:
             raise NotImplementedError("the linear-attention kernels need in_dim == out_dim and head dimension 32")
         self.num_heads = heads
@@ -78,8 +94,12 @@ class LiteLA(nn.Module):
         self.dim = out_dim // heads
         self.eps = eps
         self.kernel_func = nn.ReLU(inplace=False)
-        self.q_norm = nn.Identity()
-        self.k_norm = nn.Identity()
+        if qk_norm:  # RMSNorm over the full channel dimension, before the head split
+            self.q_norm = RMSNorm(in_dim, scale_factor=1.0, eps=norm_eps)
+            self.k_norm = RMSNorm(in_dim, scale_factor=1.0, eps=norm_eps)
+        else:
+            self.q_norm = nn.Identity()
+            self.k_norm = nn.Identity()
         self.seq_shard: Optional[SequenceShard] = None
         self.nvfp4 = False  # quantise the qkv / proj projections to NVFP4
 
@@ -87,6 +107,9 @@ class LiteLA(nn.Module):
     def _core(self, qkv: torch.Tensor, B: int, N: int) -> torch.Tensor:
         """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``)."""
         C = self.out_dim
+        if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
+            ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
+            ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
         state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, self.heads)
         if self.seq_shard is not None:
             self.seq_shard.allreduce_state(state)
@@ -102,7 +125,8 @@ class LiteLA(nn.Module):
         vt = v.permute(0, 3, 1, 2).reshape(B * N, h * d).contiguous()
         state = ops.la_state(kt, vt, B, N, h)
         o = ops.la_apply(qt, state, B, N, h, float(self.eps))
-        return o.to(dt).float().reshape(B, N, h, d).permute(0, 2, 3, 1)
+        # contiguous like upstream's result: callers .view() it as [B, C, N]
+        return o.to(dt).float().reshape(B, N, h, d).permute(0, 2, 3, 1).contiguous()
 
     def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_id=None, block_mask=None):
         if rotary_emb is not None:
@@ -208,22 +232,28 @@ class MultiHeadCrossAttention(nn.Module):
     def __init__(self, d_model, num_heads, attn_drop=0.0, proj_drop=0.0, qk_norm=False, **block_kwargs):
         super().__init__()
         assert d_model % num_heads == 0, "d_model must be divisible by num_heads"
-        if qk_norm:
-            raise NotImplementedError("MultiHeadCrossAttention(qk_norm=True) is not covered yet")
         self.d_model, self.num_heads, self.head_dim = d_model, num_heads, d_model // num_heads
         self.q_linear = nn.Linear(d_model, d_model)
         self.kv_linear = nn.Linear(d_model, d_model * 2)
         self.attn_drop = nn.Dropout(attn_drop)
         self.proj = nn.Linear(d_model, d_model)
         self.proj_drop = nn.Dropout(proj_drop)
-        self.q_norm = nn.Identity()
-        self.k_norm = nn.Identity()
+        if qk_norm:
+            self.q_norm = RMSNorm(d_model, scale_factor=1.0, eps=1e-6)
+            self.k_norm = RMSNorm(d_model, scale_factor=1.0, eps=1e-6)
+        else:
+            self.q_norm = nn.Identity()
+            self.k_norm = nn.Identity()
 
     def _attend(self, x2d: torch.Tensor, cond: torch.Tensor, mask, B: int) -> torch.Tensor:
         """Returns the attention output [B*N, C] before ``proj``."""
         C, h, hd = self.d_model, self.num_heads, self.head_dim
         q = ops.gemm(x2d, self.q_linear.weight, bias=self.q_linear.bias)
-        kv = ops.gemm(_as2d(cond), self.kv_linear.weight, bias=self.kv_linear.bias).view(B, -1, 2, C)
+        kv2d = ops.gemm(_as2d(cond), self.kv_linear.weight, bias=self.kv_linear.bias)
+        if isinstance(self.q_norm, RMSNorm):
+            ops.rmsnorm_(q, self.q_norm.weight, float(self.q_norm.eps))
+            ops.rmsnorm_(kv2d[:, :C], self.k_norm.weight, float(self.k_norm.eps))
+        kv = kv2d.view(B, -1, 2, C)
         k, v = kv.unbind(2)
         q = q.view(B, -1, h, hd).transpose(1, 2)
         k = k.reshape(B, -1, h, hd).transpose(1, 2)

@@ -83,6 +83,21 @@ def ln_modulate(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row
     return z
 
 
+def rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """In-place RMSNorm with weight over the last dimension of a 2-D view (rows may be strided,
+    e.g. the q or k column block of a qkv projection).  Returns ``x``."""
+    _need_cuda(x, weight)
+    rows, Cc, ld = _rows2d(x, "rmsnorm x")
+    if weight.numel() != Cc or weight.dtype != x.dtype:
+        raise SanaLibraryError("rmsnorm: weight must be [C] in x's dtype")
+    weight = weight.contiguous()
+    lib = _lib.load()
+    _lib.check(lib.sana_rmsnorm(x.data_ptr(), ld, weight.data_ptr(), x.data_ptr(), ld, rows, Cc, eps,
+                                _dtype_code(x.dtype), _stream()), "sana_rmsnorm")
+    counters.launches += 1
+    return x
+
+
 def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.Tensor:
     """state[b,h,i,j] = sum_n [v;1][b,n,h,i] * relu(k[b,n,h,j]); k, v are [B*N, H*32] views
     (e.g. column slices of the qkv projection).  Returns fp32 [B, H, 33, 32]."""

@@ -28,16 +28,22 @@ from sana_b200 import synthetic  # noqa: E402
 
 
 def _block(R, C, heads, params, dtype):
-    blk = R.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    qk = "attn.q_norm.weight" in params
+    blk = R.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv", qk_norm=qk,
+                        cross_norm=qk).eval()
     blk.load_state_dict(params, strict=True)
     set_fp32_attention(blk)
     return blk.to(dtype)
 
 
-def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False):
+def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False, qk_norm=False):
     hid = int(C * 2.5)
     shape = synthetic.BlockShape(name, C, heads, B, tuple(HW), text_len=L)
     params = synthetic.make_block_params(C, hid, seed, std=0.05)
+    if qk_norm:  # learned RMSNorm weights on q / k of both attentions (qk_norm=True, cross_norm=True)
+        g = torch.Generator().manual_seed(1000 + seed)
+        for k in ("attn.q_norm.weight", "attn.k_norm.weight", "cross_attn.q_norm.weight", "cross_attn.k_norm.weight"):
+            params[k] = 1.0 + 0.2 * torch.randn(C, generator=g)
     x, y, t = synthetic.make_block_inputs(shape, seed=seed, std=0.05, text_dim=96)
     mask = None
     if with_mask:
@@ -112,17 +118,20 @@ def video_case(R, seed=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--only", default=None, help="regenerate just this fixture")
     a = ap.parse_args()
     torch.manual_seed(0)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     R = load_reference(a.ref)
-    cases = {
-        "small_block_a": small_block_case(R, "a", 64, 4, 2, (6, 5), 9, seed=1),
-        "small_block_masked": small_block_case(R, "m", 64, 2, 2, (4, 7), 11, seed=2, with_mask=True),
-        "small_block_video": video_case(R),
-        "litela_cfg1": litela_cfg1_case(R),
-        "block_cfg2": block_cfg2_case(R),
+    makers = {
+        "small_block_a": lambda: small_block_case(R, "a", 64, 4, 2, (6, 5), 9, seed=1),
+        "small_block_masked": lambda: small_block_case(R, "m", 64, 2, 2, (4, 7), 11, seed=2, with_mask=True),
+        "small_block_video": lambda: video_case(R),
+        "small_block_qknorm": lambda: small_block_case(R, "q", 64, 4, 2, (5, 6), 8, seed=4, with_mask=True, qk_norm=True),
+        "litela_cfg1": lambda: litela_cfg1_case(R),
+        "block_cfg2": lambda: block_cfg2_case(R),
     }
+    cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():
         path = os.path.join(HERE, name + ".pt")
         torch.save(c, path)

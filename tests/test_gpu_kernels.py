@@ -36,6 +36,19 @@ def test_ln_modulate(dt, tol, B, N, C):
         assert z.dtype == dt and nmax_err(z, ref) < tol
 
 
+# ------------------------------------------------------------------ RMSNorm (qk norm)
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
+@pytest.mark.parametrize("rows,C", [(37, 64), (300, 1152), (130, 2240)])
+def test_rmsnorm_in_place_on_a_column_block(dt, tol, rows, C):
+    big = (_r(rows, 3 * C, seed=rows, scale=1.5) + 0.2).to(dt)
+    w = (1.0 + 0.2 * _r(C, seed=1)).to(dt)
+    ref = O.rms_norm(big[:, C:2 * C].double(), w.double(), 1e-5)
+    d = big.to(DEV)
+    ops.rmsnorm_(d[:, C:2 * C], w.to(DEV), 1e-5)
+    assert nmax_err(d[:, C:2 * C], ref) < tol
+    assert torch.equal(d[:, :C].cpu(), big[:, :C]) and torch.equal(d[:, 2 * C:].cpu(), big[:, 2 * C:])
+
+
 # ------------------------------------------------------------------ linear attention core
 def _la_ref(q, k, v, eps):
     """fp64 oracle on token-major [B, N, h, 32] tensors."""

@@ -47,8 +47,6 @@ def test_state_dict_keys_match_upstream(golden):
 
 def test_unsupported_features_raise():
     with pytest.raises(NotImplementedError):
-        sana_b200.LiteLA(64, 64, heads=2, qk_norm=True)
-    with pytest.raises(NotImplementedError):
         sana_b200.SanaMSBlock(64, 4, attn_type="flash", ffn_type="glumbconv")
     with pytest.raises(NotImplementedError):
         sana_b200.SanaMSBlock(64, 4, attn_type="linear", ffn_type="mlp")
@@ -56,6 +54,14 @@ def test_unsupported_features_raise():
         sana_b200.GLUMBConv(64, 160, dilation=2)
     with pytest.raises(NotImplementedError):
         sana_b200.LiteLA(64, 64, heads=4)  # head dimension 16
+
+
+def test_qk_norm_state_dict_keys_match_upstream(golden):
+    g = golden("small_block_qknorm")
+    blk = sana_b200.SanaMSBlock(g["C"], g["heads"], mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv",
+                                qk_norm=True, cross_norm=True)
+    assert set(blk.state_dict()) == set(g["params"])
+    blk.load_state_dict(g["params"], strict=True)
 
 
 def test_no_cpu_path():
