@@ -104,6 +104,28 @@ int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, float* state
                           int64_t H, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * sana_la_state for a token range sharded over the GPUs of one node: the chunk reduction is
+ * fused with the all-reduce of the per-rank partial states over peer memory (NVLink loads and
+ * 4-byte flag stores; no NCCL call, no multicast).  No counterpart upstream (plain LiteLA has
+ * no sequence-parallel path there); the state is a plain sum over tokens, so ranks add.
+ *   k, v, ld, workspace, B, N, H, dtype: as sana_la_state, for THIS rank's tokens.
+ *   state [B, H, 33, 32]: the sum over all ranks, bit-identical on every rank.
+ *   peer_buffers: HOST array of `world` device pointers, entry r = rank r's exchange buffer as
+ *     mapped into this process (peer / symmetric memory), each sana_la_state_sp_buffer_bytes
+ *     (B, H) bytes, zero-filled once before the first step.  Layout: 256 B of arrival flags,
+ *     a block counter at byte 256, a soft-error word at byte 320 (non-zero = 1 + the rank that
+ *     did not arrive within 2 s; the result of that step must be discarded), two state slots
+ *     from byte 1024.
+ *   step: 1, 2, 3, ... the same sequence on every rank, one per call on this buffer set.
+ * Every rank must make the matching call; a rank waits inside the kernel (bounded) for the
+ * others.  Launches on different GPUs only - never emulate several ranks on one GPU.
+ */
+int64_t sana_la_state_sp_buffer_bytes(int64_t B, int64_t H);
+int sana_la_state_sp(const void* k, const void* v, int64_t ld, float* state, void* workspace,
+                     int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype,
+                     void* const* peer_buffers, int rank, int world, uint32_t step, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * ReLU linear attention, apply + normalise:
  *   o[b, n, h, i] = (sum_j state[b,h,i,j] relu(q[b,n,h,j])) / (sum_j state[b,h,32,j] relu(q[b,n,h,j]) + eps)
  * Replaces `out = torch.matmul(vk, relu(q)); out[:, :, :-1] / (out[:, :, -1:] + eps)` and the

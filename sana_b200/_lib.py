@@ -47,6 +47,9 @@ SIGNATURES = {
     "sana_la_state_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "sana_la_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_la_state_noalloc": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "sana_la_state_sp_buffer_bytes": (_i64, [_i64, _i64]),
+    "sana_la_state_sp": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, C.POINTER(C.c_void_p), _i32, _i32,
+                                C.c_uint32, _vp]),
     "sana_la_apply": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_dwconv_glu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_gemm": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),

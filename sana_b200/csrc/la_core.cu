@@ -493,3 +493,155 @@ extern "C" int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, f
   SANA_LAUNCH_CHECK("la_state_reduce kernel (static scratch)");
   return SANA_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Sequence-parallel state: chunk reduction fused with the all-reduce over peer memory.
+//
+// Every rank owns a buffer that all ranks of the node have mapped (peer / symmetric memory):
+//   [0, 256)     arrival flags: word r = last step whose state rank r has published to us
+//   [256, 260)   block counter of the local launch      [320, 324) soft-error word
+//   [1024, ...)  two state slots (step parity) of `slot_elems` floats
+// One launch per step: phase A sums this rank's chunk partials into its own slot; the last
+// block to finish writes `step` into its flag word on every peer (remote 4-byte stores).
+// Phase B waits (bounded) until all peers' flags show `step`, then adds the ranks' slots in
+// rank order - the same order everywhere, so all ranks get bit-identical totals - reading
+// the peers' slots with plain loads over NVLink (no multicast, no TMA).  Slot reuse is safe
+// with two parities: a rank reaches step s+1 only after every peer published step s, which
+// each peer does after it finished reading step s-1.
+// ------------------------------------------------------------------------------------------
+namespace sana {
+
+constexpr int SP_MAX_WORLD = 16;
+constexpr int64_t SP_HEADER_BYTES = 1024;
+constexpr long long SP_WAIT_LIMIT_NS = 2000000000LL;  // 2 s
+
+struct SpPeers {
+  unsigned char* base[SP_MAX_WORLD];
+  int rank, world;
+  uint32_t step;
+  int64_t slot_elems;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(256)
+la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __restrict__ state, int nchunks,
+                                int64_t per_batch, int64_t total, const SpPeers pg) {
+  __shared__ int wait_failed;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned char* mine = pg.base[pg.rank];
+  const int64_t slot_off = SP_HEADER_BYTES + (int64_t)(pg.step & 1u) * pg.slot_elems * (int64_t)sizeof(float);
+  float* my_slot = reinterpret_cast<float*>(mine + slot_off);
+  // ---- phase A: fixed-order sum of this rank's chunk partials, published in its slot
+  float s = 0.f;
+  if (idx < total) {
+    const int64_t b = idx / per_batch, r = idx - b * per_batch;
+    const float* p = partial + b * nchunks * per_batch + r;
+    for (int c = 0; c < nchunks; ++c) s += p[(int64_t)c * per_batch];
+    my_slot[idx] = s;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    wait_failed = 0;
+    unsigned int* counter = reinterpret_cast<unsigned int*>(mine + 256);
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {  // the whole slot is written: tell every peer
+      *counter = 0u;
+      __threadfence_system();
+      for (int r = 0; r < pg.world; ++r)
+        if (r != pg.rank) st_release_sys_u32(reinterpret_cast<uint32_t*>(pg.base[r]) + pg.rank, pg.step);
+    }
+    // ---- phase B: wait for every peer's slot of this step (flags arrive in our own memory)
+    const long long t0 = global_ns();
+    for (int r = 0; r < pg.world && !wait_failed; ++r) {
+      if (r == pg.rank) continue;
+      const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + r;
+      while ((int32_t)(ld_acquire_sys_u32(flag) - pg.step) < 0) {
+        if (global_ns() - t0 > SP_WAIT_LIMIT_NS) {
+          wait_failed = 1;
+          atomicExch(reinterpret_cast<int*>(mine + 320), 1 + r);  // which peer we gave up on
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (idx < total) {
+    float acc = 0.f;
+    if (!wait_failed) {
+      for (int r = 0; r < pg.world; ++r)
+        acc += (r == pg.rank) ? s : ld_relaxed_sys_f32(reinterpret_cast<const float*>(pg.base[r] + slot_off) + idx);
+    } else {
+      acc = s;  // flagged in the soft-error word; the host must not use this result
+    }
+    state[idx] = acc;
+  }
+}
+
+}  // namespace sana
+
+extern "C" int64_t sana_la_state_sp_buffer_bytes(int64_t B, int64_t H) {
+  if (B <= 0 || H <= 0) return 0;
+  return SP_HEADER_BYTES + 2 * B * H * SSIZE * (int64_t)sizeof(float);
+}
+
+extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float* state, void* workspace,
+                                int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype,
+                                void* const* peer_buffers, int rank, int world, uint32_t step, void* stream) {
+  SANA_REQUIRE(k && v && state && workspace && peer_buffers, "sana_la_state_sp: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_state_sp: B, N, H must be positive");
+  SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_state_sp: size out of range");
+  SANA_REQUIRE(world >= 1 && world <= SP_MAX_WORLD && rank >= 0 && rank < world, "sana_la_state_sp: bad rank / world");
+  SANA_REQUIRE(step >= 1, "sana_la_state_sp: steps count from 1 (flags start at 0)");
+  SANA_REQUIRE(ld >= H * HD && ld % 8 == 0, "sana_la_state_sp: ld must be >= H*32 and a multiple of 8");
+  SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(state) && aligned16(workspace), "sana_la_state_sp: alignment");
+  SANA_REQUIRE(workspace_bytes >= sana_la_state_workspace_bytes(B, N, H), "sana_la_state_sp: workspace too small");
+  SANA_REQUIRE(dtype == SANA_BF16 || dtype == SANA_F32, "sana_la_state_sp: unsupported dtype %d", dtype);
+  SpPeers pg;
+  for (int r = 0; r < world; ++r) {
+    SANA_REQUIRE(peer_buffers[r] && aligned16(peer_buffers[r]), "sana_la_state_sp: peer buffer %d missing or misaligned", r);
+    pg.base[r] = static_cast<unsigned char*>(peer_buffers[r]);
+  }
+  pg.rank = rank, pg.world = world, pg.step = step;
+  pg.slot_elems = B * H * SSIZE;
+  int Lc, nchunks;
+  la_state_plan(B, N, H, dtype, &Lc, &nchunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  if (dtype == SANA_BF16) {
+    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
+                                                        static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
+                                                        (int)H, Lc, nchunks);
+  } else {
+    dim3 grid(nchunks, (unsigned)H, (unsigned)B);
+    la_state_f32_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(v), ld,
+                                              partial, (int)N, (int)H, Lc, nchunks);
+  }
+  SANA_LAUNCH_CHECK("la_state kernel (sequence parallel)");
+  const int64_t total = B * H * SSIZE;
+  const int64_t blocks = ceil_div(total, 256);
+  // every block waits inside the kernel for the peers: all blocks must be resident at once
+  SANA_REQUIRE(blocks <= (int64_t)sm_count() * 6, "sana_la_state_sp: B*H too large for a single resident wave");
+  la_state_reduce_exchange_kernel<<<(unsigned)blocks, 256, 0, st>>>(partial, state, nchunks, H * SSIZE, total, pg);
+  SANA_LAUNCH_CHECK("la_state_reduce_exchange kernel");
+  return SANA_OK;
+}

@@ -110,9 +110,14 @@ class LiteLA(nn.Module):
         if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
             ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
             ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
-        state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, self.heads)
-        if self.seq_shard is not None:
-            self.seq_shard.allreduce_state(state)
+        sh = self.seq_shard
+        if sh is not None and sh.fused_state_exchange:
+            # reduction kernel sums the ranks' partial states itself, over peer memory
+            state = sh.fused_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, self.heads)
+        else:
+            state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, self.heads)
+            if sh is not None:
+                sh.allreduce_state(state)
         return ops.la_apply(qkv[:, :C], state, B, N, self.heads, float(self.eps))
 
     def attn_matmul(self, q, k, v: torch.Tensor) -> torch.Tensor:

@@ -116,6 +116,31 @@ def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.
     return state
 
 
+def la_state_sp_buffer_bytes(B: int, H: int) -> int:
+    return _lib.load().sana_la_state_sp_buffer_bytes(B, H)
+
+
+def la_state_sp(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int, peer_ptrs, rank: int, world: int,
+                step: int) -> torch.Tensor:
+    """Like :func:`la_state` for this rank's tokens, with the all-reduce over the ranks fused
+    into the reduction kernel (peer-memory loads, no NCCL).  ``peer_ptrs[r]`` is the device
+    address of rank r's exchange buffer as mapped in this process; ``step`` counts 1, 2, ..."""
+    _need_cuda(k, v)
+    rk, ck, ldk = _rows2d(k, "la_state_sp k")
+    rv, cv, ldv = _rows2d(v, "la_state_sp v")
+    if rk != B * N or rv != B * N or ck != H * HEAD_DIM or cv != H * HEAD_DIM or ldk != ldv or k.dtype != v.dtype:
+        raise SanaLibraryError("la_state_sp: k and v must be [B*N, H*32] with the same row stride and dtype")
+    lib = _lib.load()
+    ws_bytes = lib.sana_la_state_workspace_bytes(B, N, H)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=k.device)
+    state = torch.empty(B, H, STATE_ROWS, HEAD_DIM, dtype=torch.float32, device=k.device)
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    _lib.check(lib.sana_la_state_sp(k.data_ptr(), v.data_ptr(), ldk, state.data_ptr(), ws.data_ptr(), ws.numel(), B, N, H,
+                                    _dtype_code(k.dtype), arr, rank, world, step, _stream()), "sana_la_state_sp")
+    counters.launches += 2
+    return state
+
+
 def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """o[b,n,h,:] = state[b,h,:32] relu(q) / (state[b,h,32] . relu(q) + eps); q [B*N, H*32] view."""

@@ -115,6 +115,48 @@ class SequenceShard:
     def needs_bot(self) -> bool:
         return self.row1 % self.H != 0
 
+    # ---- fused exchange over peer memory ------------------------------------------------
+    def enable_fused_state_exchange(self, B: int, heads: int, device) -> None:
+        """Allocates this rank's exchange buffer in symmetric (peer-mapped) memory and maps the
+        peers' buffers, so that the linear-attention state reduction kernel can do the
+        all-reduce itself (`ops.la_state_sp`) instead of calling NCCL.  Collective over the
+        group; call once, on every rank, before the first forward."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import ops
+
+        nbytes = ops.la_state_sp_buffer_bytes(B, heads)
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # every buffer is zeroed before anybody's first step
+        self._sp_buf, self._sp_handle = buf, hdl
+        self._sp_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._sp_shape = (B, heads)
+        self._sp_step = 0
+
+    @property
+    def fused_state_exchange(self) -> bool:
+        return getattr(self, "_sp_ptrs", None) is not None
+
+    def fused_state(self, k: torch.Tensor, v: torch.Tensor, B: int, heads: int) -> torch.Tensor:
+        """State of the whole sequence from this rank's k, v (fused reduction + all-reduce)."""
+        from . import ops
+
+        if (B, heads) != self._sp_shape:
+            raise ValueError(f"fused exchange was sized for (B, heads) = {self._sp_shape}, got {(B, heads)}")
+        self._sp_step += 1
+        return ops.la_state_sp(k, v, B, self.tokens, heads, self._sp_ptrs, self.rank, self.world, self._sp_step)
+
+    def fused_exchange_status(self) -> int:
+        """Soft-error word of the exchange kernel (0 = every wait completed).  Synchronises."""
+        return int(self._sp_buf[320:324].view(torch.int32).item())
+
     # ---- collectives -------------------------------------------------------------------
     def allreduce_state(self, state: torch.Tensor) -> torch.Tensor:
         """Sums the per-rank partial linear-attention states in place (fp32)."""

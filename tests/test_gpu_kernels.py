@@ -94,6 +94,19 @@ def test_la_state_is_additive_over_token_shards():
     assert nmax_err(parts, full) < 1e-6
 
 
+def test_la_state_sp_with_one_rank_equals_la_state():
+    """The fused reduction + exchange kernel degenerates to the plain reduction for world = 1
+    (several steps in a row on the same exchange buffer: both slot parities)."""
+    B, N, H = 2, 600, 5
+    buf = torch.zeros(ops.la_state_sp_buffer_bytes(B, H), dtype=torch.uint8, device=DEV)
+    for step in (1, 2, 3):
+        qkv = _r(B * N, 3 * H * 32, seed=step).bfloat16().to(DEV)
+        k, v = qkv[:, H * 32:2 * H * 32], qkv[:, 2 * H * 32:]
+        got = ops.la_state_sp(k, v, B, N, H, [buf.data_ptr()], 0, 1, step)
+        assert torch.equal(got, ops.la_state(k, v, B, N, H))
+    assert buf[320:324].view(torch.int32).item() == 0
+
+
 # ------------------------------------------------------------------ depthwise conv + GLU
 def _dw_ref(u, w, b, frames, H, W):
     """fp64 oracle: per-frame conv2d + chunk + SiLU-GLU, channels-last in/out."""

@@ -137,6 +137,56 @@ def _peer_leaves_between_steps(rank, world):
     return "not detected"
 
 
+def _fused_exchange_vs_nccl(rank, world):
+    """Same sharded block, state all-reduce by NCCL vs fused into the reduction kernel over
+    peer memory; several calls in a row exercise the two slot parities."""
+    import sana_b200
+    from sana_b200 import sharding, synthetic
+
+    dev, dt = torch.device("cuda", rank), torch.bfloat16
+    C, heads, grid = 512, 8, (3, 10, 16)
+    shp = synthetic.BlockShape("sp", C, heads, 1, grid, text_len=24)
+    params = synthetic.make_block_params(C, shp.ffn_hidden, seed=2, std=0.05)
+    x, y, t = synthetic.make_block_inputs(shp, seed=2, std=0.05, text_dim=64)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(params, strict=True)
+    blk = blk.to(dev, dt)
+    yd, td = y.to(dev, dt), t.to(dev, dt)
+    sh = sharding.SequenceShard(*grid, rank, world)
+    blk.set_sequence_shard(sh)
+    xs = sh.scatter_tokens(x.to(dev, dt))
+    ref = blk(xs, yd, td, None, grid)  # NCCL all-reduce
+    sh.enable_fused_state_exchange(1, blk.attn.heads, dev)
+    worst = 0.0
+    for i in range(5):
+        xi = xs * (1.0 + 0.25 * i)
+        a = blk(xi, yd, td, None, grid)
+        sh._sp_ptrs_saved, sh._sp_ptrs = sh._sp_ptrs, None  # same input through the NCCL path
+        b = blk(xi, yd, td, None, grid)
+        sh._sp_ptrs = sh._sp_ptrs_saved
+        worst = max(worst, ((a.float() - b.float()).abs().max() / b.float().abs().max()).item())
+    # the fused sum adds the ranks in rank order on every rank: totals are bit-identical
+    C2 = C
+    qkv = torch.randn(sh.tokens, 3 * C2, device=dev, generator=torch.Generator(device=dev).manual_seed(rank)).to(dt)
+    st = sh.fused_state(qkv[:, C2:2 * C2], qkv[:, 2 * C2:], 1, blk.attn.heads)
+    gathered = [torch.empty_like(st) for _ in range(world)]
+    dist.all_gather(gathered, st)
+    same = all(torch.equal(gathered[0], g) for g in gathered)
+    torch.cuda.synchronize()
+    first = ((blk(xs, yd, td, None, grid).float() - ref.float()).abs().max() / ref.float().abs().max()).item()
+    return {"worst": worst, "same": same, "status": sh.fused_exchange_status(), "first": first}
+
+
+def test_fused_state_exchange_matches_nccl_on_two_gpus():
+    _need(2)
+    res = _run(2, _fused_exchange_vs_nccl)
+    assert len(res) == 2, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        assert payload["status"] == 0 and payload["same"], payload
+        assert payload["worst"] < 2e-3 and payload["first"] < 2e-3, payload  # only the summation order differs
+
+
 def test_sequence_parallel_block_on_two_gpus():
     _need(2)
     res = _run(2, _seqpar_vs_single)
