@@ -220,6 +220,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
     ap.add_argument("--depth", type=int, default=None, help="blocks in the stack (default 20; 1 for nvfp4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cross-attn-kernel", action="store_true",
+                    help="use our own cross-attention softmax kernel instead of torch SDPA")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="seqpar: all-reduce the attention state with NCCL instead of the fused peer-memory kernel")
     args = ap.parse_args()
@@ -282,6 +284,9 @@ def main() -> None:
     stack = stack.to(device=dev, dtype=dt)
     for i, blk in enumerate(stack.blocks):
         blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, i, 0.02, dt, dev), strict=True)
+    if args.cross_attn_kernel:
+        for blk in stack.blocks:
+            blk.cross_attn.softmax_core = "kernel"
     stack.set_sequence_shard(shard)
     fused_exchange = shard is not None and world > 1 and not args.nccl_exchange
     if fused_exchange:
@@ -361,7 +366,8 @@ def main() -> None:
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload, "parallelism": parallelism, "per_gpu_batch": Bl,
                        "l2": "inputs larger than L2 (>3 GB of weights and activations per step)",
-                       "cross_attention_core": "torch SDPA (projections on the tcgen05 GEMM)",
+                       "cross_attention_core": ("own warp-MMA flash kernel" if args.cross_attn_kernel else
+                                                "torch SDPA / cuDNN flash (own kernel: --cross-attn-kernel)"),
                        "state_exchange": ("fused into the reduction kernel over peer memory" if fused_exchange else
                                           ("NCCL all-reduce" if shard is not None and world > 1 else "none"))},
             "roofline": {"bound": "tensor",

@@ -157,6 +157,21 @@ int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, c
                     int64_t hid, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Softmax core of the cross-attention (image tokens over text tokens):
+ *   out[b, n, h, :] = softmax_j(q[b,n,h,:] . k[b,j,h,:] / sqrt(head_dim) + (1 - mask[b,j]) * -10000) v[b,j,h,:]
+ * Replaces `F.scaled_dot_product_attention(q, k, v, attn_mask=...)` and the transposes around
+ * it, MultiHeadCrossAttention.forward, diffusion/model/nets/sana_blocks.py:86-93 (the 2-D mask
+ * becomes the additive -10000 bias of :88-90).
+ *   q   [B*N, *] row stride ldq, head h at columns h*head_dim ..   (token-major, no transposes)
+ *   k,v [B*L, *] row stride ldkv (e.g. the two column blocks of the kv projection)
+ *   mask [B, L] of 0/1 in the activation dtype, or NULL;  out [B*N, *] row stride ldo
+ * head_dim a multiple of 8, at most 128.  bf16: warp-level tensor cores, fp32 online softmax.
+ */
+int sana_cross_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv,
+                         const void* mask, void* out, int64_t ldo, int64_t B, int64_t N, int64_t L,
+                         int64_t heads, int64_t head_dim, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Dense projection with fused epilogue:  out = epilogue(A @ Wt^T)
  *   A   [M, K] row stride lda;  Wt [N, K] row stride ldw (torch Linear / 1x1 Conv2d weight
  *   layout);  out [M, N] row stride ldo.

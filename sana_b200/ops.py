@@ -162,6 +162,32 @@ def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: 
     return out
 
 
+def cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Optional[torch.Tensor], B: int, N: int,
+                    L: int, heads: int, head_dim: int) -> torch.Tensor:
+    """softmax(q k^T / sqrt(head_dim) + (1 - mask) * -10000) v, token-major.  q [B*N, heads*head_dim];
+    k, v [B*L, heads*head_dim] views with one row stride; mask [B, L] of 0/1 or None."""
+    _need_cuda(q, k, v, mask)
+    rq, cq, ldq = _rows2d(q, "cross_attention q")
+    rk, ck, ldk = _rows2d(k, "cross_attention k")
+    rv, cv, ldv = _rows2d(v, "cross_attention v")
+    Cc = heads * head_dim
+    if rq != B * N or rk != B * L or rv != B * L or cq != Cc or ck != Cc or cv != Cc or ldk != ldv:
+        raise SanaLibraryError("cross_attention: q must be [B*N, C], k and v [B*L, C] with one row stride")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise SanaLibraryError("cross_attention: q, k, v must share a dtype")
+    if mask is not None:
+        if mask.shape != (B, L):
+            raise SanaLibraryError("cross_attention: mask must be [B, L]")
+        mask = mask.to(q.dtype).contiguous()
+    out = torch.empty(B * N, Cc, dtype=q.dtype, device=q.device)
+    lib = _lib.load()
+    _lib.check(lib.sana_cross_attention(q.data_ptr(), ldq, k.data_ptr(), v.data_ptr(), ldk,
+                                        mask.data_ptr() if mask is not None else None, out.data_ptr(), Cc, B, N, L, heads,
+                                        head_dim, _dtype_code(q.dtype), _stream()), "sana_cross_attention")
+    counters.launches += 1
+    return out
+
+
 def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], W: int, H: int, row0: int = 0,
                halo_top: Optional[torch.Tensor] = None, halo_bot: Optional[torch.Tensor] = None) -> torch.Tensor:
     """3x3 depthwise conv + bias + SiLU-GLU.  u [rows*W, 2*hid] (channels last, image rows

@@ -67,6 +67,12 @@ def test_small_block_bf16_within_budget(golden, name):
     # and no further from golden than 2x what upstream's own bf16 run is (+ one output rounding)
     up = nmax_err(g["block_out_bf16"], ref)
     assert nmax_err(out, ref) < 2 * up + 4e-3
+    # same block with our own cross-attention softmax kernel instead of the library's
+    blk.cross_attn.softmax_core = "kernel"
+    out_k = blk(g["x"].to(DEV, dt), g["y"].to(DEV, dt), g["t"].to(DEV, dt), mask, g["HW"])
+    assert nmax_err(out_k, ref) < TOL_BF16
+    c_ref = O.cross_attention_forward(g["x"].to(dt).float(), g["y"].to(dt).float(), O.sub(p32, "cross_attn"), g["heads"], g["mask"])
+    assert nmax_err(blk.cross_attn(g["x"].to(DEV, dt), g["y"].to(DEV, dt), mask), c_ref) < TOL_BF16
 
 
 def test_attention_processor_installed_on_the_instance(golden):

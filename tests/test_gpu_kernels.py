@@ -107,6 +107,32 @@ def test_la_state_sp_with_one_rank_equals_la_state():
     assert buf[320:324].view(torch.int32).item() == 0
 
 
+# ------------------------------------------------------------------ cross-attention softmax core
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("B,N,L,h,hd,masked", [(2, 30, 9, 4, 16, True), (1, 200, 300, 2, 72, False), (2, 130, 300, 3, 112, True),
+                                               (1, 64, 65, 2, 64, True), (1, 1024, 300, 20, 112, False), (3, 77, 1, 1, 128, False)])
+def test_cross_attention_core(dt, tol, B, N, L, h, hd, masked):
+    """bf16 tolerance: P is rounded to bf16 before the second product (2^-9 per term) plus one
+    rounding of the output."""
+    C = h * hd
+    q = _r(B * N, C, seed=N).to(dt)
+    kv = _r(B * L, 2 * C, seed=L + 1).to(dt)
+    mask = None
+    if masked:
+        mask = torch.ones(B, L)
+        for b in range(B):
+            mask[b, max(1, L - 1 - 2 * b):] = 0
+    qh = q.double().reshape(B, N, h, hd).transpose(1, 2)
+    kh = kv[:, :C].double().reshape(B, L, h, hd).transpose(1, 2)
+    vh = kv[:, C:].double().reshape(B, L, h, hd).transpose(1, 2)
+    am = ((1 - mask.double()) * -10000.0)[:, None, None] if masked else None
+    ref = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=am).transpose(1, 2).reshape(B * N, C)
+    d = kv.to(DEV)
+    out = ops.cross_attention(q.to(DEV), d[:, :C], d[:, C:], mask.to(DEV) if masked else None, B, N, L, h, hd)
+    assert out.dtype == dt and out.shape == (B * N, C)
+    assert nmax_err(out, ref) < tol
+
+
 # ------------------------------------------------------------------ depthwise conv + GLU
 def _dw_ref(u, w, b, frames, H, W):
     """fp64 oracle: per-frame conv2d + chunk + SiLU-GLU, channels-last in/out."""
