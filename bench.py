@@ -208,8 +208,60 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
     print(json.dumps(out))
 
 
+def run_kernel_rates(tokens_side: int, batch: int, iters: int = 20) -> None:
+    """Device-timed rate of each HBM-bound kernel of a 1.6B-width block on `batch` samples of
+    tokens_side x tokens_side tokens (one JSON line).  Bytes are the algorithmic ones: every
+    input element read once, every output element written once; the fraction is of the measured
+    copy bandwidth.  Inputs are far larger than L2 at the default batch."""
+    from sana_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    Wd = Hh = tokens_side
+    N = Wd * Hh
+    rows = batch * N
+    peaks = load_peaks()
+    peak = peaks["hbm_gbs"]
+    LH = C // 32  # linear-attention heads
+    x = torch.randn(rows, C, generator=g, device=dev).bfloat16()
+    table = (torch.randn(6, C, generator=g, device=dev) * 0.1).bfloat16()
+    t = (torch.randn(batch, 6 * C, generator=g, device=dev) * 0.1).bfloat16()
+    qkv = torch.randn(rows, 3 * C, generator=g, device=dev).bfloat16()
+    u = torch.randn(rows, 2 * HID, generator=g, device=dev).bfloat16()
+    dw_w = (torch.randn(2 * HID, 1, 3, 3, generator=g, device=dev) * 0.2).bfloat16()
+    dw_b = (torch.randn(2 * HID, generator=g, device=dev) * 0.1).bfloat16()
+    rms_w = torch.ones(C, device=dev, dtype=torch.bfloat16)
+    state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], batch, N, LH)
+    o = torch.empty(rows, C, dtype=torch.bfloat16, device=dev)
+    cases = [
+        ("ln_modulate", lambda: ops.ln_modulate(x.view(batch, N, C), table, t, 0, 1), 2 * rows * C * 2),
+        ("la_state", lambda: ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], batch, N, LH), 2 * rows * C * 2),
+        ("la_apply", lambda: ops.la_apply(qkv[:, :C], state, batch, N, LH, 1e-8, out=o), 2 * rows * C * 2),
+        ("dwconv_glu", lambda: ops.dwconv_glu(u, dw_w, dw_b, Wd, Hh), rows * 3 * HID * 2),
+        ("rmsnorm", lambda: ops.rmsnorm_(qkv[:, :C], rms_w, 1e-5), 2 * rows * C * 2),
+    ]
+    out = {"workload": f"HBM-bound kernels, {batch} x {Wd}x{Hh} tokens, hidden {C}", "peak_gbs": peak,
+           "peak_source": peaks["source"], "rows": []}
+    for name, fn, nbytes in cases:
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["rows"].append({"name": name, "ms": ms, "bytes": nbytes, "gbs": gbs, "frac": gbs / peak})
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel-rates", type=int, default=0, metavar="SIDE",
+                    help="only time the HBM-bound kernels of a block on --batch samples of SIDE x SIDE tokens")
     ap.add_argument("--gemm-rates", type=int, default=0, metavar="TOKENS",
                     help="only time the four projection shapes of a block at this many tokens")
     ap.add_argument("--gpus", type=int, default=1)
@@ -230,6 +282,9 @@ def main() -> None:
         return
     if args.gemm_rates:
         run_gemm_rates(args.gemm_rates)
+        return
+    if args.kernel_rates:
+        run_kernel_rates(args.kernel_rates, args.batch)
         return
     args.warmup = max(args.warmup, 3)
 

@@ -1,5 +1,6 @@
 // adaLN-single LayerNorm + modulate: one warp per token row, the row held in registers
-// (packed, as loaded) so global memory is read once and written once.
+// (packed, as loaded) so global memory is read once and written once; the per-sample
+// modulation vectors are combined once per block into shared memory.
 #include "common.cuh"
 
 namespace sana {
@@ -28,70 +29,106 @@ struct Vec16<float> {
   }
 };
 
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
+// Shared memory holds, for the batch sample being processed, the two fp32 modulation vectors
+// mul = 1 + (t[scale_row] + table[scale_row]) and add = t[shift_row] + table[shift_row], laid
+// out as planes of float4 (plane p holds elements 4p..4p+3 of every 16-byte vector) so that a
+// warp's reads are conflict-free. A block owns a contiguous range of rows and restages the
+// vectors when the range crosses into the next sample.
 template <typename T, int MAXV>
 __global__ void __launch_bounds__(256)
 ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T* __restrict__ t, T* __restrict__ z,
-                   int64_t rows, int N, int C, int shift_row, int scale_row, float eps) {
+                   int64_t rows, int N, int C, int shift_row, int scale_row, float eps, int rows_per_block) {
   constexpr int VN = Vec16<T>::N;
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  constexpr int PLANES = VN / 4;
+  extern __shared__ float4 ln_smem[];
   const int nvec = C / VN;
-  const int b = (int)(row / N);
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
-  uint4 raw[MAXV];
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int v = lane + 32 * i;
-    if (v < nvec) {
-      raw[i] = ldg_nc_u4(xr + v);
-      float f[VN];
-      Vec16<T>::unpack(raw[i], f);
-#pragma unroll
-      for (int e = 0; e < VN; ++e) sum += f[e];
-    }
-  }
-  const float mean = warp_sum(sum) / (float)C;
-  float sq = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int v = lane + 32 * i;
-    if (v < nvec) {
-      float f[VN];
-      Vec16<T>::unpack(raw[i], f);
-#pragma unroll
-      for (int e = 0; e < VN; ++e) {
-        const float d = f[e] - mean;
-        sq = fmaf(d, d, sq);
+  float4* s_mul = ln_smem;                  // [PLANES][nvec]
+  float4* s_add = ln_smem + PLANES * nvec;  // [PLANES][nvec]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarp = blockDim.x >> 5;
+  const int64_t row0 = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t row1 = (row0 + rows_per_block < rows) ? row0 + rows_per_block : rows;
+  if (row0 >= row1) return;
+  const float inv_c = 1.0f / (float)C;
+  for (int64_t b = row0 / N; b * N < row1; ++b) {
+    const int64_t seg0 = (b * N > row0) ? b * N : row0;
+    const int64_t seg1 = ((b + 1) * N < row1) ? (b + 1) * N : row1;
+    __syncthreads();  // every warp is done with the previous sample's vectors
+    {
+      const T* tsc = t + (b * 6 + scale_row) * C;
+      const T* tsh = t + (b * 6 + shift_row) * C;
+      const T* bsc = table + (int64_t)scale_row * C;
+      const T* bsh = table + (int64_t)shift_row * C;
+      float* fm = reinterpret_cast<float*>(s_mul);
+      float* fa = reinterpret_cast<float*>(s_add);
+      for (int i = threadIdx.x; i < C; i += blockDim.x) {
+        const int v = i / VN, e = i % VN;
+        const int slot = ((e >> 2) * nvec + v) * 4 + (e & 3);
+        fm[slot] = 1.0f + (to_float(tsc[i]) + to_float(bsc[i]));
+        fa[slot] = to_float(tsh[i]) + to_float(bsh[i]);
       }
     }
-  }
-  const float rstd = rsqrtf(warp_sum(sq) / (float)C + eps);
-  const uint4* tsh = reinterpret_cast<const uint4*>(t + ((int64_t)b * 6 + shift_row) * C);
-  const uint4* tsc = reinterpret_cast<const uint4*>(t + ((int64_t)b * 6 + scale_row) * C);
-  const uint4* bsh = reinterpret_cast<const uint4*>(table + (int64_t)shift_row * C);
-  const uint4* bsc = reinterpret_cast<const uint4*>(table + (int64_t)scale_row * C);
-  uint4* zr = reinterpret_cast<uint4*>(z + row * C);
+    __syncthreads();
+    for (int64_t row = seg0 + warp; row < seg1; row += nwarp) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+      uint4 raw[MAXV];
+      float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int v = lane + 32 * i;
-    if (v < nvec) {
-      float f[VN], s1[VN], s2[VN], h1[VN], h2[VN];
-      Vec16<T>::unpack(raw[i], f);
-      Vec16<T>::unpack(__ldg(tsc + v), s1);
-      Vec16<T>::unpack(__ldg(bsc + v), s2);
-      Vec16<T>::unpack(__ldg(tsh + v), h1);
-      Vec16<T>::unpack(__ldg(bsh + v), h2);
+      for (int i = 0; i < MAXV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          raw[i] = ldg_nc_u4(xr + v);
+          float f[VN];
+          Vec16<T>::unpack(raw[i], f);
 #pragma unroll
-      for (int e = 0; e < VN; ++e) f[e] = fmaf((f[e] - mean) * rstd, 1.0f + (s1[e] + s2[e]), h1[e] + h2[e]);
-      zr[v] = Vec16<T>::pack(f);
+          for (int e = 0; e < VN; ++e) sum += f[e];
+        }
+      }
+      const float mean = warp_sum(sum) * inv_c;
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float f[VN];
+          Vec16<T>::unpack(raw[i], f);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) {
+            const float d = f[e] - mean;
+            sq = fmaf(d, d, sq);
+          }
+        }
+      }
+      const float rstd = rsqrtf(warp_sum(sq) * inv_c + eps);
+      uint4* zr = reinterpret_cast<uint4*>(z + row * C);
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float f[VN];
+          Vec16<T>::unpack(raw[i], f);
+#pragma unroll
+          for (int p = 0; p < PLANES; ++p) {
+            const float4 m = s_mul[p * nvec + v];
+            const float4 a = s_add[p * nvec + v];
+            f[4 * p + 0] = fmaf((f[4 * p + 0] - mean) * rstd, m.x, a.x);
+            f[4 * p + 1] = fmaf((f[4 * p + 1] - mean) * rstd, m.y, a.y);
+            f[4 * p + 2] = fmaf((f[4 * p + 2] - mean) * rstd, m.z, a.z);
+            f[4 * p + 3] = fmaf((f[4 * p + 3] - mean) * rstd, m.w, a.w);
+          }
+          zr[v] = Vec16<T>::pack(f);
+        }
+      }
     }
   }
 }
@@ -102,16 +139,27 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
   const int64_t rows = B * N;
   const int nvec = (int)(C / Vec16<T>::N);
   const int per_lane = (nvec + 31) / 32;
-  const unsigned grid = (unsigned)ceil_div(rows, 8);
+  // one wave of blocks (three per SM at 256 threads), each over a contiguous range of rows
+  const int64_t want = (int64_t)sm_count() * 3;
+  int64_t rpb = ceil_div(rows, want);
+  rpb = ceil_div(rpb, 8) * 8;
+  const unsigned grid = (unsigned)ceil_div(rows, rpb);
+  const size_t smem = (size_t)2 * C * sizeof(float);
   const T* xp = static_cast<const T*>(x);
   const T* tb = static_cast<const T*>(table);
   const T* tp = static_cast<const T*>(t);
   T* zp = static_cast<T*>(z);
-#define SANA_LN_CASE(MV)                                                                                   \
-  if (per_lane <= MV) {                                                                                    \
-    ln_modulate_kernel<T, MV><<<grid, 256, 0, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, shift_row, scale_row, eps); \
-    SANA_LAUNCH_CHECK("ln_modulate kernel");                                                               \
-    return SANA_OK;                                                                                        \
+#define SANA_LN_CASE(MV)                                                                                       \
+  if (per_lane <= MV) {                                                                                        \
+    if (smem > 48 * 1024) {                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(ln_modulate_kernel<T, MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                         \
+      if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_modulate)");                       \
+    }                                                                                                          \
+    ln_modulate_kernel<T, MV><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, shift_row, scale_row, \
+                                                       eps, (int)rpb);                                         \
+    SANA_LAUNCH_CHECK("ln_modulate kernel");                                                                   \
+    return SANA_OK;                                                                                            \
   }
   SANA_LN_CASE(5)
   SANA_LN_CASE(9)
