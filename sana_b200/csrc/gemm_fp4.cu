@@ -206,12 +206,13 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * F4_BN + half * HALF);
       const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
       EpiStep st[2];
-      epi_prefetch_residual<NCHUNK>(row);
+      EpiRes res;
+      epi_prefetch_residual<NCHUNK>(row, res);
       epi_fetch(row, st[0], 0);  // operands that do not depend on the accumulator: requested before the wait
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      epi_drain<NCHUNK, true>(row, ep, taddr, st, alpha);
+      epi_drain<NCHUNK, true>(row, ep, taddr, st, res, alpha);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * a);

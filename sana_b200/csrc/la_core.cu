@@ -18,7 +18,8 @@ constexpr int SSIZE = SROWS * HD;  // 1056 floats per head
 constexpr int LA_WARPS = 8;  // heads per CTA
 
 // ------------------------------------------------------------------------------------------
-// state, bf16.  grid (chunks, ceil(H/8), B); warp w -> head hg*8+w, tokens [c*Lc, min(N,(c+1)*Lc)).
+// state, bf16.  grid (ceil(H/8), chunks, B) - head group fastest, so that CTAs running at the
+// same time read whole token rows between them; warp w -> head hg*8+w, tokens [c*Lc, min(N,(c+1)*Lc)).
 // Lane (g = lane>>2, t = lane&3) loads 8 bytes = channels 4g..4g+3 of tokens n+2t, n+2t+1,
 // n+2t+8, n+2t+9 for both k and v.  MMA roles: A = v^T (rows = value channel), B = relu(k).
 //   A rows of M-tile mt: logical row r (<8) -> channel 4r+2mt, row r+8 -> channel 4r+2mt+1
@@ -30,9 +31,9 @@ la_state_bf16_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* 
                      float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int h = blockIdx.y * LA_WARPS + warp;
+  const int h = blockIdx.x * LA_WARPS + warp;
   if (h >= H) return;
-  const int b = blockIdx.z, chunk = blockIdx.x;
+  const int b = blockIdx.z, chunk = blockIdx.y;
   const int n_begin = chunk * Lc;
   const int n_end = min(N, n_begin + Lc);
 
@@ -178,7 +179,7 @@ __global__ void la_state_reduce_kernel(const float* __restrict__ partial, float*
 }
 
 // ------------------------------------------------------------------------------------------
-// apply, bf16.  grid (chunks, ceil(H/8), B); warp -> one head, 16 tokens per step.
+// apply, bf16.  grid (ceil(H/8), chunks, B); warp -> one head, 16 tokens per step.
 // A = relu(q) rows (tokens), B = state^T split into bf16 hi + lo parts (two MMAs, ~2^-17
 // relative error), denominator in plain fp32.  Lane (g, t) loads the 16 contiguous bytes
 // q[token g (and g+8)][8t .. 8t+7]; logical K index kk of K-step s maps to channel
@@ -191,10 +192,10 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
                      __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int h = blockIdx.y * LA_WARPS + warp;
+  const int h = blockIdx.x * LA_WARPS + warp;
   if (h >= H) return;
   const int b = blockIdx.z;
-  const int n_begin = blockIdx.x * Lc, n_end = min(N, n_begin + Lc);
+  const int n_begin = blockIdx.y * Lc, n_end = min(N, n_begin + Lc);
   const float* S = state + ((int64_t)b * H + h) * SSIZE;
 
   uint32_t bhi[4][2][2], blo[4][2][2];
@@ -326,22 +327,41 @@ la_apply_f32_kernel(const float* __restrict__ qp, int64_t ldq, const float* __re
   }
 }
 
-// Host-side split of the token axis: enough CTAs to fill the device, chunks a multiple of 64.
-static void la_chunking(int64_t B, int64_t N, int64_t head_groups, int target_ctas_per_sm, int* Lc, int* nchunks) {
-  const int64_t target = (int64_t)sm_count() * target_ctas_per_sm;
-  int64_t want = ceil_div(target, B * head_groups);
-  if (want < 1) want = 1;
-  int64_t lc = ceil_div(ceil_div(N, want), 64) * 64;
-  if (lc < 64) lc = 64;
-  *Lc = (int)lc;
-  *nchunks = (int)ceil_div(N, lc);
+// Host-side split of the token axis into chunks of Lc tokens (a multiple of 64).  `units` CTAs
+// exist per chunk (samples x head groups) and `slots` CTAs are resident at once; a CTA's time is
+// its Lc tokens plus a fixed cost of `overhead` token-equivalents (state load, or partial-state
+// write + re-read).  Picks the chunk count that minimises waves x (Lc + overhead), i.e. avoids
+// a mostly empty last wave.
+static void la_chunking(int64_t units, int64_t N, int64_t slots, int64_t overhead, int* Lc, int* nchunks) {
+  const int64_t max_chunks = ceil_div(N, 64) < 4096 ? ceil_div(N, 64) : 4096;
+  int64_t best_cost = -1, best_lc = 64;
+  for (int64_t nch = 1; nch <= max_chunks; ++nch) {
+    const int64_t lc = ceil_div(ceil_div(N, nch), 64) * 64;
+    const int64_t real = ceil_div(N, lc);
+    const int64_t cost = ceil_div(units * real, slots) * (lc + overhead);
+    if (best_cost < 0 || cost < best_cost) best_cost = cost, best_lc = lc;
+  }
+  *Lc = (int)best_lc;
+  *nchunks = (int)ceil_div(N, best_lc);
+}
+
+template <typename Kernel>
+static int64_t resident_ctas(Kernel kernel, int threads) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    per_sm = 1;
+  }
+  return (int64_t)per_sm * sm_count();
 }
 
 static void la_state_plan(int64_t B, int64_t N, int64_t H, int dtype, int* Lc, int* nchunks) {
   // The plan must not depend on dtype-specific grids so that the workspace query needs no dtype:
   // use the bf16 head grouping (the fp32 kernel simply launches more, smaller CTAs).
   (void)dtype;
-  la_chunking(B, N, ceil_div(H, LA_WARPS), 2, Lc, nchunks);
+  static const int64_t slots = resident_ctas(la_state_bf16_kernel, LA_WARPS * 32);
+  // a chunk's partial state (33x32 fp32, written and re-read) costs as much as 66 tokens of k+v
+  la_chunking(B * ceil_div(H, LA_WARPS), N, slots, 66, Lc, nchunks);
 }
 
 }  // namespace sana
@@ -369,7 +389,7 @@ extern "C" int sana_la_state(const void* k, const void* v, int64_t ld, float* st
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
   if (dtype == SANA_BF16) {
-    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
     la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
                                                         static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
                                                         (int)H, Lc, nchunks);
@@ -398,13 +418,15 @@ extern "C" int sana_la_apply(const void* q, int64_t ldq, const float* state, voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int Lc, nchunks;
   if (dtype == SANA_BF16) {
-    la_chunking(B, N, ceil_div(H, LA_WARPS), 4, &Lc, &nchunks);
-    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    static const int64_t slots = resident_ctas(la_apply_bf16_kernel, LA_WARPS * 32);
+    // loading a head's state costs about as much as 33 tokens of q + o
+    la_chunking(B * ceil_div(H, LA_WARPS), N, slots, 33, &Lc, &nchunks);
+    dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
     la_apply_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(q), ldq, state,
                                                         static_cast<__nv_bfloat16*>(out), ldo, (int)N, (int)H, Lc,
                                                         eps);
   } else if (dtype == SANA_F32) {
-    la_chunking(B, N, H, 4, &Lc, &nchunks);
+    la_chunking(B * H, N, (int64_t)sm_count() * 8, 33, &Lc, &nchunks);
     dim3 grid(nchunks, (unsigned)H, (unsigned)B);
     la_apply_f32_kernel<<<grid, 128, 0, st>>>(static_cast<const float*>(q), ldq, state, static_cast<float*>(out),
                                               ldo, (int)N, (int)H, Lc, eps);
@@ -478,7 +500,7 @@ extern "C" int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, f
   // Nothing in the scratch has to start at zero: the first launch overwrites every partial
   // state (all 1056 floats of every (batch, chunk, head)) that the second launch reads.
   if (dtype == SANA_BF16) {
-    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
     la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
                                                         static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
                                                         (int)H, Lc, nchunks);
@@ -627,7 +649,7 @@ extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
   if (dtype == SANA_BF16) {
-    dim3 grid(nchunks, (unsigned)ceil_div(H, LA_WARPS), (unsigned)B);
+    dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
     la_state_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
                                                         static_cast<const __nv_bfloat16*>(v), ld, partial, (int)N,
                                                         (int)H, Lc, nchunks);

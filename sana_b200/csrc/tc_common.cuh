@@ -119,12 +119,20 @@ __device__ __forceinline__ float fast_silu(float x) {
 // ---- fused epilogue of one accumulator row-half ---------------------------------------------
 // An epilogue warp owns 32 accumulator rows (its TMEM lane quadrant) and NCHUNK steps of 16
 // columns.  Per step a lane needs 16 accumulator words plus, for its row, 32 bytes each of
-// bias, gate table, gate timestep vector and residual.  The residual comes from DRAM: its
-// lines are pulled into L2 when the tile starts (long before the accumulator is ready), and
-// every step's operands are loaded into registers one step ahead of their use.
+// bias, gate table, gate timestep vector and residual.  The small per-column operands are
+// loaded one step ahead of their use.  The residual comes from DRAM, one 32-byte piece per
+// lane and step, so its latency is hidden twice over: the lane's whole row-half is pulled
+// into L2 by one bulk prefetch when the tile starts (long before the accumulator is ready),
+// and the register loads run EPI_RES_AHEAD steps ahead through a small ring.
+constexpr int EPI_RES_AHEAD = 4;
+
 struct EpiStep {
   uint32_t acc[16];
-  uint4 bias[2], gtab[2], gt[2], res[2];
+  uint4 bias[2], gtab[2], gt[2];
+};
+
+struct EpiRes {
+  uint4 v[EPI_RES_AHEAD][2];
 };
 
 struct EpiRow {
@@ -150,18 +158,24 @@ __device__ __forceinline__ EpiRow epi_row_setup(const EpiParams& ep, __nv_bfloat
   return r;
 }
 
-template <int NCHUNK>
-__device__ __forceinline__ void epi_prefetch_residual(const EpiRow& r) {
-  if (r.rrow && r.row_ok) {
+__device__ __forceinline__ void epi_res_load(const EpiRow& r, uint4 (&v)[2], int c) {
+  const int64_t n = r.nbase + 16 * c;
 #pragma unroll
-    for (int c = 0; c < NCHUNK; c += 4) {  // 4 steps x 32 bytes = one 128-byte line
-      const int64_t n = r.nbase + 16 * c;
-      if (n < r.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(r.rrow + n));
-    }
-    // the half-row need not start on a line boundary: also touch the line of its last step
-    const int64_t nl = r.nbase + 16 * (NCHUNK - 1);
-    if (nl < r.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(r.rrow + nl));
+  for (int j = 0; j < 2; ++j)
+    v[j] = (r.rrow && r.row_ok && n + 8 * j < r.N) ? ldg_nc_u4(r.rrow + n + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Start of a tile: L2 prefetch of the lane's residual row-half (a multiple of 16 bytes at a
+// 16-byte aligned address, as the bulk form requires) and the first EPI_RES_AHEAD steps' loads.
+template <int NCHUNK>
+__device__ __forceinline__ void epi_prefetch_residual(const EpiRow& r, EpiRes& res) {
+  if (r.rrow && r.row_ok && r.nbase < r.N) {
+    const int64_t cols = (r.N - r.nbase < 16 * NCHUNK) ? (r.N - r.nbase) : 16 * NCHUNK;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.rrow + r.nbase), "r"((uint32_t)(cols * 2))
+                 : "memory");
   }
+#pragma unroll
+  for (int c = 0; c < EPI_RES_AHEAD && c < NCHUNK; ++c) epi_res_load(r, res.v[c], c);
 }
 
 __device__ __forceinline__ void epi_fetch(const EpiRow& r, EpiStep& s, int c) {
@@ -175,15 +189,15 @@ __device__ __forceinline__ void epi_fetch(const EpiRow& r, EpiStep& s, int c) {
       s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
       s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
     }
-    s.res[j] = (r.rrow && in && r.row_ok) ? ldg_nc_u4(r.rrow + nj) : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
 // Reads the accumulator (already complete) 16 columns at a time, applies the epilogue and
-// stores bf16.  st[0] must hold the side operands of step 0 (epi_fetch) on entry.
+// stores bf16.  st[0] must hold the side operands of step 0 (epi_fetch) and `res` the first
+// residual steps (epi_prefetch_residual) on entry.
 template <int NCHUNK, bool SCALE>
 __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, uint32_t taddr, EpiStep (&st)[2],
-                                          float alpha) {
+                                          EpiRes& res, float alpha) {
   if (r.nbase < r.N) tmem_ld_32x16(taddr, st[0].acc);
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
@@ -227,7 +241,7 @@ __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, 
             for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
           }
           if (r.rrow) {
-            unpack8(cur.res[j], f);
+            unpack8(res.v[c % EPI_RES_AHEAD][j], f);
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] += f[e];
           }
@@ -236,6 +250,7 @@ __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, 
         }
       }
     }
+    if (c + EPI_RES_AHEAD < NCHUNK) epi_res_load(r, res.v[c % EPI_RES_AHEAD], c + EPI_RES_AHEAD);
   }
 }
 
