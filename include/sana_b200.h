@@ -156,6 +156,12 @@ int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, c
                     const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
                     int64_t hid, int dtype, void* stream);
 
+/* Soft-error word of the bf16 sana_dwconv_glu kernel: a wait for an input row (a bulk-tensor
+ * copy into shared memory) that runs out records 1 here and the warp gives up instead of
+ * spinning forever.  Returns 0 when no wait timed out on the current device since the last
+ * call (host-synchronising: for tests / after a failure, not per step). */
+int sana_dwconv_glu_take_device_status(int* status_out);
+
 /* ---------------------------------------------------------------------------------------
  * Softmax core of the cross-attention (image tokens over text tokens):
  *   out[b, n, h, :] = softmax_j(q[b,n,h,:] . k[b,j,h,:] / sqrt(head_dim) + (1 - mask[b,j]) * -10000) v[b,j,h,:]

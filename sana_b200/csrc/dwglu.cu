@@ -1,45 +1,54 @@
 // 3x3 depthwise conv + bias + SiLU-GLU over channels-last image rows (the Mix-FFN middle).
 //
-// bf16 kernel: a CTA owns a tile of 16 columns x 64 value channels (+ their 64 gate
-// channels) and marches down a segment of rows.  Each input row tile (with a one-column
-// halo, zero-filled at image edges) is staged once in shared memory by 16-byte cp.async
-// through a 10-deep ring (one CTA barrier per two rows); a lane owns one pair of value
-// channels and the gate pair of the same index at two neighbouring columns, reads the four
-// input columns their windows share from shared memory and feeds three rolling fp32
-// accumulators per output (rows y-1, y, y+1) with packed f32x2 FMAs; every input element is
-// read from global memory once per CTA, and the GLU needs no exchange between lanes.
-#include "common.cuh"
+// bf16 kernel: every warp is an independent worker.  It owns two neighbouring output columns
+// x, x+1 and 64 value channels (+ the 64 gate channels of the same index; a lane owns one
+// channel pair of each) and marches down a segment of rows.  Per input row it needs the four
+// pixels x-1 .. x+2 of both channel groups: one 1 KiB box of a 4-D tensor map
+// {channel, value/gate, x, row}, fetched by a bulk-tensor copy into the warp's own ring of
+// DW_STAGES boxes in shared memory (image borders come back as zeros from the out-of-range
+// fill).  Lane 0 refills a box as soon as the warp has consumed it, so there is no CTA-wide
+// barrier and no per-thread address arithmetic in the row loop.  Each loaded row feeds three
+// rolling fp32 accumulators per output (rows y-1, y, y+1) with packed f32x2 FMAs; the GLU
+// needs no exchange between lanes.  Neighbouring warps load overlapping pixels, which costs
+// L2 bandwidth but no DRAM traffic.
+#include "tc_common.cuh"
 
 namespace sana {
 
-constexpr int DW_TW = 16;      // output columns per CTA
-constexpr int DW_CV = 8;       // 8-channel vectors per role per CTA
-constexpr int DW_STAGES = 10;  // ring depth (input rows in flight)
-constexpr int DW_THREADS = 256;
-constexpr int DW_ROW_CHUNKS = (DW_TW + 2) * 2 * DW_CV;  // 16-byte chunks per staged row = 288
-constexpr int DW_STAGE_BYTES = DW_ROW_CHUNKS * 16;
+__device__ int g_dw_status = 0;  // soft-error word: 1 = a wait on an input row timed out
 
-__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
-  const int sz = valid ? 16 : 0;  // src-size 0 => 16 bytes of zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(sz) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+constexpr int DW_TW = 16;       // output columns per CTA (two per warp)
+constexpr int DW_WARPS = 8;
+constexpr int DW_THREADS = 32 * DW_WARPS;
+constexpr int DW_CH = 64;       // value channels per warp (and as many gate channels)
+constexpr int DW_STAGES = 8;    // input rows in flight per warp
+constexpr int DW_BOX_BYTES = 4 * 2 * DW_CH * 2;  // 4 pixels x {value, gate} x 64 channels x bf16 = 1 KiB
+constexpr int DW_RING_BYTES = DW_WARPS * DW_STAGES * DW_BOX_BYTES;
+constexpr int DW_SMEM_BYTES = DW_RING_BYTES + DW_WARPS * DW_STAGES * 8;
+
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
 }
 
-__device__ __forceinline__ float fast_silu(float x) {
-  float e, r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-  return x * r;
+// Bounded wait for an input row; on time-out records the soft error and gives up.
+__device__ __forceinline__ bool dw_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023u) == 0 && clock64() - t0 > TC_WAIT_LIMIT_CYCLES) {
+      atomicExch(&g_dw_status, 1);
+      return false;
+    }
+  }
+  return true;
 }
 
 struct DwArgs {
-  const __nv_bfloat16* u;
-  const __nv_bfloat16* halo_top;
-  const __nv_bfloat16* halo_bot;
   const __nv_bfloat16* weight;  // [2*hid, 9]
   const __nv_bfloat16* bias;    // [2*hid] or null
   __nv_bfloat16* out;
@@ -62,9 +71,9 @@ __device__ __forceinline__ u64 f2_fma(u64 a, u64 b, u64 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-__device__ __forceinline__ u64 f2_add(u64 a, u64 b) {
+__device__ __forceinline__ u64 f2_mul(u64 a, u64 b) {
   u64 d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 // two bf16 in one 32-bit word -> packed (fp32, fp32)
@@ -73,21 +82,78 @@ __device__ __forceinline__ u64 bf2_to_f2(uint32_t v) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(v << 16), "r"(v & 0xffff0000u));
   return r;
 }
+__device__ __forceinline__ float tanh_fast(float x) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// a * silu(g) on a channel pair; silu(g) = h + h * tanh(h) with h = g / 2 (one MUFU op per element)
+__device__ __forceinline__ uint32_t glu_pair(u64 a2, u64 g2) {
+  const u64 h2 = f2_mul(g2, f2_pack(0.5f, 0.5f));
+  float h0, h1, o0, o1;
+  f2_unpack(h2, h0, h1);
+  const u64 s2 = f2_fma(h2, f2_pack(tanh_fast(h0), tanh_fast(h1)), h2);
+  f2_unpack(f2_mul(a2, s2), o0, o1);
+  return pack_bf16(o0, o1);
+}
 
-__global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const DwArgs p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // a lane owns one pair of value channels and the gate pair of the same index, at two
-  // neighbouring columns (x, x+1): the 3x3 window of both outputs shares 4 input columns
-  const int x0 = blockIdx.y * DW_TW;
-  const int x = x0 + 2 * warp;
+__global__ void __launch_bounds__(DW_THREADS, 2)
+dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmTop,
+                       const __grid_constant__ CUtensorMap tmBot, const DwArgs p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int x = blockIdx.y * DW_TW + 2 * warp;  // this warp's columns: x, x + 1
+  if (x >= p.W) return;                         // warps are independent: no CTA-wide barrier below
   const int ys = blockIdx.z * p.seg_rows;
   const int ye = min(p.rows, ys + p.seg_rows);
-  const int C2 = 2 * p.hid;
-  const int c0 = blockIdx.x * (DW_CV * 8) + lane * 2;  // first of this lane's 2 value channels
-  const bool ch_ok = c0 < p.hid;
-  const bool ok0 = ch_ok && (x < p.W), ok1 = ch_ok && (x + 1 < p.W);
+  const int cbase = blockIdx.x * DW_CH;
+  const int c0 = cbase + lane * 2;  // first of this lane's 2 value channels
+  const bool ok0 = c0 < p.hid, ok1 = ok0 && (x + 1 < p.W);
   const int cw = min(c0, p.hid - 2);
+
+  const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * DW_STAGES * DW_BOX_BYTES);
+  const uint32_t bars = smem_u32(smem) + (uint32_t)(DW_RING_BYTES + warp * DW_STAGES * 8);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < DW_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  // input-row slots k = 0 .. nin-1  <->  local rows ys-1 .. ye; the first and last slot exist
+  // only when that row lies in the same frame as its neighbour inside the segment
+  const int nin = ye - ys + 2;
+  const int fr_top = (int)((p.row0 + ys + p.H - 1) % p.H);  // frame row of local row ys-1
+  const bool need_top = fr_top != p.H - 1;
+  const bool need_bot = (int)((p.row0 + ye) % p.H) != 0;
+
+  // lane 0: fetch the row of slot k into ring box `slot`.  A row that does not exist (frame
+  // edge) is never waited for, but its barrier phase is completed all the same so that the
+  // parity of the box's later uses stays in step.
+  auto issue_row = [&](int k, int slot) {
+    if (k >= nin) return;
+    const CUtensorMap* tm = &tmU;
+    int r = ys - 1 + k;
+    if (k == 0) {
+      if (!need_top) {
+        mbar_arrive(bars + 8 * slot);
+        return;
+      }
+      if (ys == 0) tm = &tmTop, r = 0;
+    } else if (k == nin - 1) {
+      if (!need_bot) {
+        mbar_arrive(bars + 8 * slot);
+        return;
+      }
+      if (ye >= p.rows) tm = &tmBot, r = 0;
+    }
+    mbar_expect_tx(bars + 8 * slot, DW_BOX_BYTES);
+    tma_load_4d(ring + slot * DW_BOX_BYTES, tm, bars + 8 * slot, cbase, 0, x - 1, r);
+  };
+  if (lane == 0) {
+#pragma unroll 1
+    for (int k = 0; k < DW_STAGES; ++k) issue_row(k, k);
+  }
 
   // taps as packed pairs: w2[tap][0] = value channels (c, c+1), w2[tap][1] = gate channels
   u64 w2[9][2];
@@ -108,140 +174,161 @@ __global__ void __launch_bounds__(DW_THREADS, 2) dwconv_glu_bf16_kernel(const Dw
     }
   }
 
-  // input-row slots k = 0 .. nin-1  <->  local rows ys-1 .. ye; the first and last slot exist
-  // only when that row lies in the same frame as its neighbour inside the segment
-  const int nin = ye - ys + 2;
-  const int fr_top = (int)((p.row0 + ys + p.H - 1) % p.H);  // frame row of local row ys-1
-  const bool need_top = fr_top != p.H - 1;
-  const bool need_bot = (int)((p.row0 + ye) % p.H) != 0;
-  const int64_t row_elems = (int64_t)p.W * C2;
-  const __nv_bfloat16* top_ptr = !need_top ? nullptr : (ys > 0 ? p.u + (int64_t)(ys - 1) * row_elems : p.halo_top);
-  const __nv_bfloat16* bot_ptr = !need_bot ? nullptr : (ye < p.rows ? p.u + (int64_t)ye * row_elems : p.halo_bot);
-  const __nv_bfloat16* mid_ptr = p.u + (int64_t)ys * row_elems;  // slot 1
-
-  // this thread's (at most two) 16-byte chunks of a staged row: fixed offsets, computed once
-  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-  const int nvec = p.hid >> 3;
-  int64_t src_off[2];
-  uint32_t dst_off[2];
-  bool src_ok[2], has[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int q = tid + i * DW_THREADS;
-    has[i] = q < DW_ROW_CHUNKS;
-    const int px = q >> 4, rem = q & 15, rl = rem >> 3, c = rem & 7;
-    const int gx = x0 - 1 + px;
-    const int gv = blockIdx.x * DW_CV + c;
-    src_ok[i] = has[i] && (gx >= 0) && (gx < p.W) && (gv < nvec);
-    src_off[i] = src_ok[i] ? (int64_t)gx * C2 + rl * p.hid + (gv << 3) : 0;
-    dst_off[i] = q * 16;
-  }
-
-  auto issue_row = [&](int k) {
-    if (k < nin) {
-      const __nv_bfloat16* rp = (k == 0) ? top_ptr : ((k == nin - 1) ? bot_ptr : mid_ptr + (int64_t)(k - 1) * row_elems);
-      if (rp != nullptr) {
-        const uint32_t sbase = smem_base + (k % DW_STAGES) * DW_STAGE_BYTES;
-        cp_async_16(sbase + dst_off[0], rp + src_off[0], src_ok[0]);
-        if (has[1]) cp_async_16(sbase + dst_off[1], rp + src_off[1], src_ok[1]);
-      }
-    }
-    cp_async_commit();
-  };
-
-  u64 acc[3][2][2];  // [output-row slot][column x / x+1][value / gate]
+  // [output-row slot][column x / x+1][value / gate].  A slot is (re)started in its NEXT role,
+  // where the first tap's FMA takes the bias as its addend.
+  u64 acc[3][2][2];
 #pragma unroll
   for (int s = 0; s < 3; ++s)
 #pragma unroll
-    for (int xo = 0; xo < 2; ++xo) acc[s][xo][0] = acc[s][xo][1] = 0ull;
-
-#pragma unroll 1
-  for (int k = 0; k < DW_STAGES - 2; ++k) issue_row(k);
+    for (int xo = 0; xo < 2; ++xo) acc[s][xo][0] = bv[0], acc[s][xo][1] = bv[1];
 
   int fr = fr_top;  // frame row of the input row of the current slot
-  __nv_bfloat16* out_ptr = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + c0;  // output row of slot k is ys-2+k
-  // byte offset of this lane's value word of staged pixel 2*warp (= column x-1), role 0
-  const uint32_t rd_off = (uint32_t)(2 * warp * 256 + lane * 4);
+  int slot = 0;
+  uint32_t parity = 0u;
+  uint32_t box = ring + (uint32_t)(lane * 4);  // this lane's word of pixel x-1, value group, in the current box
+  uint32_t bar = bars;                          // barrier of the current box
+  bool alive = true;
+  const int64_t out_step = (int64_t)p.W * p.hid;
+  __nv_bfloat16* out0 = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + c0;  // output row of slot k is ys-2+k
+  __nv_bfloat16* out1 = out0 + p.hid;
 
-  // One step: consume input slot k (local row r = ys-1+k).  PREV/CUR/NEXT are the accumulator
-  // slots of output rows (r-1, r, r+1); they rotate with k so no register moves are needed.
-  // The CTA synchronises once per two rows (on even k).
-  auto step = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
-    constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
-    if ((k & 1) == 0) {
-      cp_async_wait<DW_STAGES - 4>();  // rows k and k+1 have landed (for this thread's copies)
-      __syncthreads();                 // ... for everybody's; and rows k-2, k-1 are no longer read
-      issue_row(k + DW_STAGES - 2);
-      issue_row(k + DW_STAGES - 1);
+  auto load_cols = [&](u64 (&col)[4][2]) {  // input columns x-1 .. x+2, [value / gate]
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v, g;
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(box + c * 256));
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(g) : "r"(box + c * 256 + 128));
+      col[c][0] = bf2_to_f2(v);
+      col[c][1] = bf2_to_f2(g);
     }
+  };
+  // taps of kernel row `trow` of the loaded input row into accumulator slot S
+  auto taps = [&](u64 (&a)[2][2], const u64 (&col)[4][2], int trow) {
+#pragma unroll
+    for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+      for (int dx = 0; dx < 3; ++dx)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) a[xo][h] = f2_fma(w2[3 * trow + dx][h], col[xo + dx][h], a[xo][h]);
+  };
+  auto taps_start = [&](u64 (&a)[2][2], const u64 (&col)[4][2]) {  // kernel row 0, starting from the bias
+#pragma unroll
+    for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[xo][h] = f2_fma(w2[0][h], col[xo][h], bv[h]);
+        a[xo][h] = f2_fma(w2[1][h], col[xo + 1][h], a[xo][h]);
+        a[xo][h] = f2_fma(w2[2][h], col[xo + 2][h], a[xo][h]);
+      }
+  };
+  auto restart = [&](u64 (&a)[2][2]) {
+#pragma unroll
+    for (int xo = 0; xo < 2; ++xo) a[xo][0] = bv[0], a[xo][1] = bv[1];
+  };
+  auto emit = [&](const u64 (&a)[2][2]) {
+    const uint32_t o0 = glu_pair(a[0][0], a[0][1]);
+    const uint32_t o1 = glu_pair(a[1][0], a[1][1]);
+    if (ok0) *reinterpret_cast<uint32_t*>(out0) = o0;
+    if (ok1) *reinterpret_cast<uint32_t*>(out1) = o1;
+  };
+  auto advance = [&]() {
+    box += DW_BOX_BYTES, bar += 8;
+    if (++slot == DW_STAGES) slot = 0, parity ^= 1u, box -= DW_STAGES * DW_BOX_BYTES, bar -= DW_STAGES * 8;
+    out0 += out_step;
+    out1 += out_step;
+    fr = (fr + 1 == p.H) ? 0 : fr + 1;
+  };
+
+  // One step consumes input slot k (local row r = ys-1+k).  PREV/CUR/NEXT are the accumulator
+  // slots of output rows (r-1, r, r+1); they rotate with k so no register moves are needed.
+  // Input row r is the row BELOW output r-1 (kernel row 2), the centre of output r (kernel row 1)
+  // and the row ABOVE output r+1 (kernel row 0); vertical neighbours must share the frame.
+  //
+  // General step: any k, including the halo slots at both ends of the segment.
+  auto step_any = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
+    constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
     const bool first = (k == 0), last = (k == nin - 1);
     const bool have = first ? need_top : (last ? need_bot : true);
+    bool started = false;
     if (have) {
-      const unsigned char* sp = smem + (k % DW_STAGES) * DW_STAGE_BYTES + rd_off;
-      u64 col[4][2];  // input columns x-1 .. x+2, [value / gate]
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        col[c][0] = bf2_to_f2(*reinterpret_cast<const uint32_t*>(sp + c * 256));
-        col[c][1] = bf2_to_f2(*reinterpret_cast<const uint32_t*>(sp + c * 256 + 128));
+      if (!dw_wait(bar, parity)) {
+        alive = false;
+        return;
       }
-      // input row r is the row BELOW output r-1 (taps 6..8), the centre of output r (taps 3..5)
-      // and the row ABOVE output r+1 (taps 0..2); vertical neighbours must share the frame.
-      if (k >= 2 && fr != 0) {  // output r-1 is inside the segment
-#pragma unroll
-        for (int xo = 0; xo < 2; ++xo)
-#pragma unroll
-          for (int dx = 0; dx < 3; ++dx)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) acc[PREV][xo][h] = f2_fma(w2[6 + dx][h], col[xo + dx][h], acc[PREV][xo][h]);
-      }
-      if (!first && !last) {
-#pragma unroll
-        for (int xo = 0; xo < 2; ++xo)
-#pragma unroll
-          for (int dx = 0; dx < 3; ++dx)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) acc[CUR][xo][h] = f2_fma(w2[3 + dx][h], col[xo + dx][h], acc[CUR][xo][h]);
-      }
+      u64 col[4][2];
+      load_cols(col);
+      if (k >= 2 && fr != 0) taps(acc[PREV], col, 2);  // output r-1 is inside the segment
+      if (!first && !last) taps(acc[CUR], col, 1);
       if (k + 2 < nin && fr != p.H - 1) {  // output r+1 is inside the segment
-#pragma unroll
-        for (int xo = 0; xo < 2; ++xo)
-#pragma unroll
-          for (int dx = 0; dx < 3; ++dx)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) acc[NEXT][xo][h] = f2_fma(w2[dx][h], col[xo + dx][h], acc[NEXT][xo][h]);
+        taps_start(acc[NEXT], col);
+        started = true;
       }
     }
-    if (k >= 2) {  // output row r-1 = ys + k - 2 is complete
-#pragma unroll
-      for (int xo = 0; xo < 2; ++xo) {
-        float a0, a1, g0, g1;
-        f2_unpack(f2_add(acc[PREV][xo][0], bv[0]), a0, a1);
-        f2_unpack(f2_add(acc[PREV][xo][1], bv[1]), g0, g1);
-        if (xo == 0 ? ok0 : ok1)
-          *reinterpret_cast<uint32_t*>(out_ptr + xo * p.hid) = pack_bf16(a0 * fast_silu(g0), a1 * fast_silu(g1));
+    if (k >= 2) emit(acc[PREV]);  // output row r-1 = ys + k - 2 is complete
+    if (!started) restart(acc[NEXT]);
+    // every lane has consumed the box (its values sit in accumulators): lane 0 may refill it
+    __syncwarp();
+    if (lane == 0) issue_row(k + DW_STAGES, slot);
+    advance();
+  };
+  // Interior step: 2 <= k <= nin-3, so the row exists, all three outputs lie inside the segment
+  // and the refill (slot k + DW_STAGES >= 10) is never the top halo.
+  auto step_mid = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
+    constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
+    if (!dw_wait(bar, parity)) {
+      alive = false;
+      return;
+    }
+    u64 col[4][2];
+    load_cols(col);
+    if (fr != 0) taps(acc[PREV], col, 2);
+    taps(acc[CUR], col, 1);
+    if (fr != p.H - 1)
+      taps_start(acc[NEXT], col);
+    else
+      restart(acc[NEXT]);
+    emit(acc[PREV]);
+    __syncwarp();
+    if (lane == 0) {
+      const int kk = k + DW_STAGES;
+      if (kk < nin - 1) {
+        mbar_expect_tx(bar, DW_BOX_BYTES);
+        tma_load_4d(box - (uint32_t)(lane * 4), &tmU, bar, cbase, 0, x - 1, ys - 1 + kk);
+      } else if (kk == nin - 1) {
+        issue_row(kk, slot);
       }
     }
-#pragma unroll
-    for (int xo = 0; xo < 2; ++xo) acc[PREV][xo][0] = acc[PREV][xo][1] = 0ull;  // becomes NEXT of the next step
-    out_ptr += (int64_t)p.W * p.hid;
-    fr = (fr + 1 == p.H) ? 0 : fr + 1;
+    advance();
   };
 
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
-  // six slots per trip so that both the accumulator rotation (period 3) and the barrier
-  // cadence (period 2) are compile-time
+  // three slots per trip so that the accumulator rotation (period 3) is compile-time
+  int k = 0;
+  step_any(0, I0{}, I1{}, I2{});
+  if (alive) step_any(1, I1{}, I2{}, I0{});
+  if (alive) step_any(2, I2{}, I0{}, I1{});  // nin >= 3 always
+  k = 3;
 #pragma unroll 1
-  for (int k = 0; k < nin; k += 6) {
-    step(k, I0{}, I1{}, I2{});
-    if (k + 1 < nin) step(k + 1, I1{}, I2{}, I0{});
-    if (k + 2 < nin) step(k + 2, I2{}, I0{}, I1{});
-    if (k + 3 < nin) step(k + 3, I0{}, I1{}, I2{});
-    if (k + 4 < nin) step(k + 4, I1{}, I2{}, I0{});
-    if (k + 5 < nin) step(k + 5, I2{}, I0{}, I1{});
+  for (; k + 2 <= nin - 3 && alive; k += 3) {
+    step_mid(k, I0{}, I1{}, I2{});
+    if (alive) step_mid(k + 1, I1{}, I2{}, I0{});
+    if (alive) step_mid(k + 2, I2{}, I0{}, I1{});
   }
-  cp_async_wait<0>();
+#pragma unroll 1
+  for (; k < nin && alive; k += 3) {
+    step_any(k, I0{}, I1{}, I2{});
+    if (k + 1 < nin && alive) step_any(k + 1, I1{}, I2{}, I0{});
+    if (k + 2 < nin && alive) step_any(k + 2, I2{}, I0{}, I1{});
+  }
+  if (!alive) {
+    // copies of this warp may still be in flight towards its ring: give them time before the
+    // CTA's shared memory can be handed to another block
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
 }
 
 // Plain fp32 version (parity path): one thread per (row, x, channel pair value/gate).
@@ -296,15 +383,29 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == SANA_BF16) {
     DwArgs a;
-    a.u = static_cast<const __nv_bfloat16*>(u);
-    a.halo_top = static_cast<const __nv_bfloat16*>(halo_top);
-    a.halo_bot = static_cast<const __nv_bfloat16*>(halo_bot);
     a.weight = static_cast<const __nv_bfloat16*>(weight);
     a.bias = static_cast<const __nv_bfloat16*>(bias);
     a.out = static_cast<__nv_bfloat16*>(out);
     a.rows = (int)rows, a.W = (int)W, a.H = (int)H, a.hid = (int)hid, a.row0 = row0;
-    const int64_t gx = ceil_div(hid / 8, DW_CV), gy = ceil_div(W, DW_TW);
-    // rows per CTA: long segments amortise the two halo rows; shorten them until the grid
+    // u as a 4-D tensor {channel, value/gate, x, row}; a box is 64 channels x 2 groups x 4 pixels of one row
+    CUtensorMap tmU, tmTop, tmBot;
+    const uint64_t strides[3] = {(uint64_t)hid * 2, (uint64_t)hid * 4, (uint64_t)W * hid * 4};
+    const uint32_t box[4] = {DW_CH, 2, 4, 1};
+    const uint64_t dims_u[4] = {(uint64_t)hid, 2, (uint64_t)W, (uint64_t)rows};
+    const uint64_t dims_1[4] = {(uint64_t)hid, 2, (uint64_t)W, 1};
+    int rc = make_tmap_tiled(&tmU, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, u, dims_u, strides, box, false);
+    if (rc) return rc;
+    tmTop = tmU, tmBot = tmU;
+    if (halo_top) {
+      rc = make_tmap_tiled(&tmTop, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, halo_top, dims_1, strides, box, false);
+      if (rc) return rc;
+    }
+    if (halo_bot) {
+      rc = make_tmap_tiled(&tmBot, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, halo_bot, dims_1, strides, box, false);
+      if (rc) return rc;
+    }
+    const int64_t gx = ceil_div(hid, DW_CH), gy = ceil_div(W, DW_TW);
+    // rows per warp: long segments amortise the two halo rows; shorten them until the grid
     // covers the device a few times over.
     int seg = 32;
     while (seg > 4 && gx * gy * ceil_div(rows, seg) < 4 * (int64_t)sm_count()) seg >>= 1;
@@ -312,13 +413,12 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
     const int64_t gz = ceil_div(rows, seg);
     SANA_REQUIRE(gy < 65536 && gz < 65536, "sana_dwconv_glu: grid too large");
     static bool attr_set = false;
-    const int smem_bytes = DW_STAGES * DW_STAGE_BYTES;
     if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(dwconv_glu_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+      cudaError_t e = cudaFuncSetAttribute(dwconv_glu_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DW_SMEM_BYTES);
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dwconv_glu)");
       attr_set = true;
     }
-    dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, smem_bytes, st>>>(a);
+    dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, DW_SMEM_BYTES, st>>>(tmU, tmTop, tmBot, a);
   } else if (dtype == SANA_F32) {
     const int64_t total = rows * W * hid;
     dwconv_glu_f32_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
@@ -329,5 +429,19 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
     return fail(SANA_ERR_UNSUPPORTED, "sana_dwconv_glu: unsupported dtype %d", dtype);
   }
   SANA_LAUNCH_CHECK("dwconv_glu kernel");
+  return SANA_OK;
+}
+
+extern "C" int sana_dwconv_glu_take_device_status(int* status_out) {
+  if (!status_out) return fail(SANA_ERR_INVALID, "sana_dwconv_glu_take_device_status: null pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_dw_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_dw_status)");
+  if (v != 0) {
+    int zero = 0;
+    e = cudaMemcpyToSymbol(g_dw_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_dw_status)");
+  }
+  *status_out = v;
   return SANA_OK;
 }

@@ -232,6 +232,21 @@ int make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, con
   return SANA_OK;
 }
 
+int make_tmap_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t d[5], s[5];
+  cuuint32_t b[5], estr[5];
+  for (int i = 0; i < rank; ++i) d[i] = dims[i], b[i] = box[i], estr[i] = 1;
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
+  CUresult r = fn(tm, dtype, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SANA_OK;
+}
+
 // [rows, cols] bf16 matrix, row stride ld elements; box = box_rows x 64 columns.
 static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   return make_tmap_2d(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, rows, cols, ld * 2, box_rows, TC_BK);

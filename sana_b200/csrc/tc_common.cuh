@@ -259,5 +259,9 @@ __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, 
 // stride ld_bytes; box = box_rows x box_cols, 128-byte swizzle, out-of-range reads give zeros.
 int make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, const void* base, int64_t rows,
                  int64_t cols, int64_t ld_bytes, int box_rows, int box_cols);
+// General tiled map of `rank` (<= 5) dimensions, innermost first; strides_bytes has rank-1 entries
+// (dimensions 1 .. rank-1), each a multiple of 16; out-of-range reads give zeros.
+int make_tmap_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 
 }  // namespace sana

@@ -216,6 +216,14 @@ def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+def take_dwconv_glu_device_status() -> int:
+    """Code recorded by a timed-out wait inside the bf16 depthwise kernel (0 = none).  Synchronises."""
+    v = C.c_int(0)
+    lib = _lib.load()
+    _lib.check(lib.sana_dwconv_glu_take_device_status(C.byref(v)), "sana_dwconv_glu_take_device_status")
+    return int(v.value)
+
+
 def _epi_tag(bias, act, gate, residual) -> str:
     return (" +bias" if bias is not None else "") + (" +silu" if act == ACT_SILU else "") + \
         (" *gate" if gate is not None else "") + (" +res" if residual is not None else "")

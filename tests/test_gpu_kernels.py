@@ -155,6 +155,7 @@ def test_dwconv_glu(dt, tol, frames, H, W, hid, bias):
     out = ops.dwconv_glu(u.to(DEV), w.to(DEV), b.to(DEV) if bias else None, W, H)
     assert out.dtype == dt and out.shape == (frames * H * W, hid)
     assert nmax_err(out, ref) < tol
+    assert ops.take_dwconv_glu_device_status() == 0
 
 
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
@@ -177,6 +178,7 @@ def test_dwconv_glu_row_shards_with_halo(dt, tol):
         outs.append(ops.dwconv_glu(rows[r0:r1].reshape(-1, C2).contiguous(), wd, bd, W, H, row0=r0, halo_top=top,
                                    halo_bot=bot))
     assert nmax_err(torch.cat(outs), ref) < tol
+    assert ops.take_dwconv_glu_device_status() == 0
     # CPU oracle of the same sharded computation agrees with the full-grid oracle
     o = O.depthwise_glu_rows(u.double().reshape(frames * H, W, C2)[4:9], u.double().reshape(frames * H, W, C2)[3],
                              u.double().reshape(frames * H, W, C2)[9], w.double(), b.double(), 4, H)
