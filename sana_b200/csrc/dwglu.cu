@@ -21,7 +21,7 @@ constexpr int DW_TW = 16;       // output columns per CTA (two per warp)
 constexpr int DW_WARPS = 8;
 constexpr int DW_THREADS = 32 * DW_WARPS;
 constexpr int DW_CH = 64;       // value channels per warp (and as many gate channels)
-constexpr int DW_STAGES = 8;    // input rows in flight per warp
+constexpr int DW_STAGES = 9;    // input rows in flight per warp (a multiple of 3: see the row loop)
 constexpr int DW_BOX_BYTES = 4 * 2 * DW_CH * 2;  // 4 pixels x {value, gate} x 64 channels x bf16 = 1 KiB
 constexpr int DW_RING_BYTES = DW_WARPS * DW_STAGES * DW_BOX_BYTES;
 constexpr int DW_SMEM_BYTES = DW_RING_BYTES + DW_WARPS * DW_STAGES * 8;
@@ -34,18 +34,23 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
-// Bounded wait for an input row; on time-out records the soft error and gives up.
-__device__ __forceinline__ bool dw_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait for an input row.  On time-out the warp records the soft error, gives copies
+// that may still be in flight towards its ring time to land (the CTA's shared memory must not
+// be handed to another block under them) and exits; warps are independent, so nobody waits
+// for it.  Not returning a flag keeps the row loop free of per-step liveness checks.
+__device__ __forceinline__ void dw_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 1023u) == 0 && clock64() - t0 > TC_WAIT_LIMIT_CYCLES) {
       atomicExch(&g_dw_status, 1);
-      return false;
+      const long long t1 = clock64();
+      while (clock64() - t1 < 2000000LL) {
+      }
+      asm volatile("exit;");
     }
   }
-  return true;
 }
 
 struct DwArgs {
@@ -183,31 +188,31 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
     for (int xo = 0; xo < 2; ++xo) acc[s][xo][0] = bv[0], acc[s][xo][1] = bv[1];
 
   int fr = fr_top;  // frame row of the input row of the current slot
-  int slot = 0;
-  uint32_t parity = 0u;
-  uint32_t box = ring + (uint32_t)(lane * 4);  // this lane's word of pixel x-1, value group, in the current box
-  uint32_t bar = bars;                          // barrier of the current box
-  bool alive = true;
+  const uint32_t ring_lane = ring + (uint32_t)(lane * 4);  // this lane's word of pixel x-1, value group, box 0
   const int64_t out_step = (int64_t)p.W * p.hid;
   __nv_bfloat16* out0 = p.out + ((int64_t)(ys - 2) * p.W + x) * p.hid + c0;  // output row of slot k is ys-2+k
   __nv_bfloat16* out1 = out0 + p.hid;
 
-  auto load_cols = [&](u64 (&col)[4][2]) {  // input columns x-1 .. x+2, [value / gate]
+  // input columns x-1 .. x+2 of the box at shared address `b` (this lane's word), [value / gate]
+  auto load_cols = [&](uint32_t b, u64 (&col)[4][2]) {
+    uint32_t w[8];
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[0]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+128];" : "=r"(w[1]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+256];" : "=r"(w[2]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+384];" : "=r"(w[3]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+512];" : "=r"(w[4]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+640];" : "=r"(w[5]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+768];" : "=r"(w[6]) : "r"(b));
+    asm volatile("ld.shared.b32 %0, [%1+896];" : "=r"(w[7]) : "r"(b));
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v, g;
-      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(box + c * 256));
-      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(g) : "r"(box + c * 256 + 128));
-      col[c][0] = bf2_to_f2(v);
-      col[c][1] = bf2_to_f2(g);
-    }
+    for (int c = 0; c < 4; ++c) col[c][0] = bf2_to_f2(w[2 * c]), col[c][1] = bf2_to_f2(w[2 * c + 1]);
   };
-  // taps of kernel row `trow` of the loaded input row into accumulator slot S
+  // taps of kernel row `trow` of the loaded input row into an accumulator slot
   auto taps = [&](u64 (&a)[2][2], const u64 (&col)[4][2], int trow) {
 #pragma unroll
-    for (int xo = 0; xo < 2; ++xo)
+    for (int dx = 0; dx < 3; ++dx)
 #pragma unroll
-      for (int dx = 0; dx < 3; ++dx)
+      for (int xo = 0; xo < 2; ++xo)
 #pragma unroll
         for (int h = 0; h < 2; ++h) a[xo][h] = f2_fma(w2[3 * trow + dx][h], col[xo + dx][h], a[xo][h]);
   };
@@ -215,11 +220,13 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
 #pragma unroll
     for (int xo = 0; xo < 2; ++xo)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        a[xo][h] = f2_fma(w2[0][h], col[xo][h], bv[h]);
-        a[xo][h] = f2_fma(w2[1][h], col[xo + 1][h], a[xo][h]);
-        a[xo][h] = f2_fma(w2[2][h], col[xo + 2][h], a[xo][h]);
-      }
+      for (int h = 0; h < 2; ++h) a[xo][h] = f2_fma(w2[0][h], col[xo][h], bv[h]);
+#pragma unroll
+    for (int dx = 1; dx < 3; ++dx)
+#pragma unroll
+      for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) a[xo][h] = f2_fma(w2[dx][h], col[xo + dx][h], a[xo][h]);
   };
   auto restart = [&](u64 (&a)[2][2]) {
 #pragma unroll
@@ -232,31 +239,27 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
     if (ok1) *reinterpret_cast<uint32_t*>(out1) = o1;
   };
   auto advance = [&]() {
-    box += DW_BOX_BYTES, bar += 8;
-    if (++slot == DW_STAGES) slot = 0, parity ^= 1u, box -= DW_STAGES * DW_BOX_BYTES, bar -= DW_STAGES * 8;
     out0 += out_step;
     out1 += out_step;
     fr = (fr + 1 == p.H) ? 0 : fr + 1;
   };
 
-  // One step consumes input slot k (local row r = ys-1+k).  PREV/CUR/NEXT are the accumulator
-  // slots of output rows (r-1, r, r+1); they rotate with k so no register moves are needed.
-  // Input row r is the row BELOW output r-1 (kernel row 2), the centre of output r (kernel row 1)
-  // and the row ABOVE output r+1 (kernel row 0); vertical neighbours must share the frame.
+  // One step consumes input slot k (local row r = ys-1+k) from ring box `slot`.  PREV/CUR/NEXT
+  // are the accumulator slots of output rows (r-1, r, r+1); they rotate with k so no register
+  // moves are needed.  Input row r is the row BELOW output r-1 (kernel row 2), the centre of
+  // output r (kernel row 1) and the row ABOVE output r+1 (kernel row 0); vertical neighbours
+  // must share the frame.
   //
   // General step: any k, including the halo slots at both ends of the segment.
-  auto step_any = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
+  auto step_any = [&](int k, int slot, uint32_t parity, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
     const bool first = (k == 0), last = (k == nin - 1);
     const bool have = first ? need_top : (last ? need_bot : true);
     bool started = false;
     if (have) {
-      if (!dw_wait(bar, parity)) {
-        alive = false;
-        return;
-      }
+      dw_wait(bars + 8 * slot, parity);
       u64 col[4][2];
-      load_cols(col);
+      load_cols(ring_lane + slot * DW_BOX_BYTES, col);
       if (k >= 2 && fr != 0) taps(acc[PREV], col, 2);  // output r-1 is inside the segment
       if (!first && !last) taps(acc[CUR], col, 1);
       if (k + 2 < nin && fr != p.H - 1) {  // output r+1 is inside the segment
@@ -271,29 +274,26 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
     if (lane == 0) issue_row(k + DW_STAGES, slot);
     advance();
   };
-  // Interior step: 2 <= k <= nin-3, so the row exists, all three outputs lie inside the segment
-  // and the refill (slot k + DW_STAGES >= 10) is never the top halo.
-  auto step_mid = [&](int k, auto PREVc, auto CURc, auto NEXTc) {
+  // Interior step away from frame edges: 2 <= k <= nin-3 and the input row is neither the
+  // first nor the last of its frame, so the row exists, all three outputs take it and the
+  // refill (slot k + DW_STAGES) is never the top halo.  One branch-free block - the FMAs, the
+  // conversions and the previous row's GLU - which is what lets the few resident warps overlap
+  // their fixed-latency dependencies.
+  auto step_mid = [&](int k, int slot, uint32_t parity, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
-    if (!dw_wait(bar, parity)) {
-      alive = false;
-      return;
-    }
+    dw_wait(bars + 8 * slot, parity);
     u64 col[4][2];
-    load_cols(col);
-    if (fr != 0) taps(acc[PREV], col, 2);
+    load_cols(ring_lane + slot * DW_BOX_BYTES, col);
+    taps(acc[PREV], col, 2);
     taps(acc[CUR], col, 1);
-    if (fr != p.H - 1)
-      taps_start(acc[NEXT], col);
-    else
-      restart(acc[NEXT]);
+    taps_start(acc[NEXT], col);
     emit(acc[PREV]);
     __syncwarp();
     if (lane == 0) {
       const int kk = k + DW_STAGES;
       if (kk < nin - 1) {
-        mbar_expect_tx(bar, DW_BOX_BYTES);
-        tma_load_4d(box - (uint32_t)(lane * 4), &tmU, bar, cbase, 0, x - 1, ys - 1 + kk);
+        mbar_expect_tx(bars + 8 * slot, DW_BOX_BYTES);
+        tma_load_4d(ring + slot * DW_BOX_BYTES, &tmU, bars + 8 * slot, cbase, 0, x - 1, ys - 1 + kk);
       } else if (kk == nin - 1) {
         issue_row(kk, slot);
       }
@@ -304,30 +304,25 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
-  // three slots per trip so that the accumulator rotation (period 3) is compile-time
-  int k = 0;
-  step_any(0, I0{}, I1{}, I2{});
-  if (alive) step_any(1, I1{}, I2{}, I0{});
-  if (alive) step_any(2, I2{}, I0{}, I1{});  // nin >= 3 always
-  k = 3;
+  static_assert(DW_STAGES % 3 == 0, "a trip of three steps must not straddle the end of the ring");
+  // Trips of three steps keep the accumulator rotation (k mod 3) compile-time; the ring box
+  // advances by three per trip.  A trip whose three rows are all interior and away from frame
+  // edges runs the lean steps, any other trip the general ones.
+  int slot = 0;
+  uint32_t par = 0u;  // parity of ring pass k / DW_STAGES
 #pragma unroll 1
-  for (; k + 2 <= nin - 3 && alive; k += 3) {
-    step_mid(k, I0{}, I1{}, I2{});
-    if (alive) step_mid(k + 1, I1{}, I2{}, I0{});
-    if (alive) step_mid(k + 2, I2{}, I0{}, I1{});
-  }
-#pragma unroll 1
-  for (; k < nin && alive; k += 3) {
-    step_any(k, I0{}, I1{}, I2{});
-    if (k + 1 < nin && alive) step_any(k + 1, I1{}, I2{}, I0{});
-    if (k + 2 < nin && alive) step_any(k + 2, I2{}, I0{}, I1{});
-  }
-  if (!alive) {
-    // copies of this warp may still be in flight towards its ring: give them time before the
-    // CTA's shared memory can be handed to another block
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
+  for (int k = 0; k < nin; k += 3) {
+    if (k >= 2 && k + 2 <= nin - 3 && fr >= 1 && fr + 2 <= p.H - 2) {
+      step_mid(k, slot, par, I0{}, I1{}, I2{});
+      step_mid(k + 1, slot + 1, par, I1{}, I2{}, I0{});
+      step_mid(k + 2, slot + 2, par, I2{}, I0{}, I1{});
+    } else {
+      step_any(k, slot, par, I0{}, I1{}, I2{});
+      if (k + 1 < nin) step_any(k + 1, slot + 1, par, I1{}, I2{}, I0{});
+      if (k + 2 < nin) step_any(k + 2, slot + 2, par, I2{}, I0{}, I1{});
     }
+    slot += 3;
+    if (slot == DW_STAGES) slot = 0, par ^= 1u;
   }
 }
 
