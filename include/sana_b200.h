@@ -53,6 +53,16 @@ const char* sana_last_error(void);
 int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
                      int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream);
 
+/* Same kernel with the rows of `table` and of `t` named separately, for modulation layouts
+ * other than the block's [6, C] / [B, 6*C]:  scale_b = table[table_scale_row] +
+ * t[b, t_scale_row] with table [table_rows, C] and t [B, t_rows, C] (same for shift).
+ * Replaces `T2IFinalLayer.forward` up to its linear (sana_blocks.py:919-925):
+ * `t2i_modulate(norm_final(x), shift, scale)` with (shift, scale) =
+ * (scale_shift_table[None] + t[:, None]).chunk(2, dim=1), i.e. table_rows = 2, t_rows = 1. */
+int sana_ln_modulate_rows(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
+                          int64_t C, int table_rows, int table_shift_row, int table_scale_row, int t_rows,
+                          int t_shift_row, int t_scale_row, float eps, int dtype, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * RMSNorm with weight over the channel dimension:  y = weight * x * rsqrt(mean_c(x^2) + eps)
  * Replaces `self.q_norm(q)` / `self.k_norm(k)` of LiteLA (qk_norm=True; RMSNorm over the full
@@ -183,7 +193,7 @@ int sana_cross_attention(const void* q, int64_t ldq, const void* k, const void* 
  *   layout);  out [M, N] row stride ldo.
  * Epilogue, in this order, all in fp32 with one rounding on store:
  *   v = acc;  v += bias[n];  act;  v *= gate_b[n];  v += residual[m, n]
- *   act: 0 none, 1 SiLU, 2 ReLU on columns n < relu_cols
+ *   act: 0 none, 1 SiLU, 2 ReLU on columns n < relu_cols, 3 GELU (tanh form)
  *   gate_b[n] = gate_table[gate_row, n] + gate_t[m / rows_per_batch, gate_row*N + n]
  * Replaces self.qkv / self.proj (sana_blocks.py:268,289), q_linear / kv_linear / proj of the
  * cross-attention (sana_blocks.py:74-75,95), inverted_conv (+ in-place SiLU) and point_conv
@@ -194,7 +204,7 @@ int sana_cross_attention(const void* q, int64_t ldq, const void* k, const void* 
  */
 typedef struct sana_gemm_epilogue {
   const void* bias;       /* [N] or NULL */
-  int32_t act;            /* 0 none, 1 SiLU, 2 ReLU on columns < relu_cols */
+  int32_t act;            /* 0 none, 1 SiLU, 2 ReLU on columns < relu_cols, 3 GELU (tanh form) */
   int32_t gate_row;       /* row of the [6, N] table (2 = gate_msa, 5 = gate_mlp) */
   int64_t relu_cols;
   const void* gate_table; /* [6, N] or NULL */
@@ -249,6 +259,31 @@ int sana_gemm_take_device_status(int* status_out);
  * 0 = per problem (default: CTA-pair kernel, tcgen05 cta_group::2 with 256-row tiles, when
  * M >= 2048, else the single-CTA kernel), 1 = always single-CTA, 2 = always CTA-pair. */
 int sana_gemm_set_variant(int variant);
+
+/* ---------------------------------------------------------------------------------------
+ * Steps either side of the block loop of `SanaMS.forward`
+ * (diffusion/model/nets/sana_multi_scale.py:338-386).
+ *
+ * sana_patchify: latent x [B, Cin, H, W] -> rows [B*(H/p)*(W/p), Cin*p*p] (row stride ldo),
+ *   column (c*p + i)*p + j = x[b, c, hp*p + i, wp*p + j].  With the conv weight
+ *   [embed, Cin, p, p] viewed as [embed, Cin*p*p], sana_gemm on these rows is
+ *   `PatchEmbedMS.forward` (sana_blocks.py:1263-1268: Conv2d kernel = stride = p, flatten(2),
+ *   transpose(1, 2)); the sin-cos position table goes in as the GEMM's residual.
+ * sana_unpatchify: tokens [B*Hp*Wp, p*p*Cout] (row stride ld) -> images [B, Cout, Hp*p, Wp*p];
+ *   replaces `SanaMS.unpatchify` (sana_multi_scale.py:409-421, einsum "nhwpqc->nchpwq").
+ * sana_timestep_embedding: t [B] fp32 -> out [B, dim] of `dtype`, cos | sin halves with
+ *   frequencies exp(-ln(max_period) k / (dim/2)); replaces
+ *   `TimestepEmbedder.timestep_embedding` (sana_blocks.py:981-1000).
+ * sana_silu: out = x * sigmoid(x) on n elements; the `nn.SiLU()` in front of `t_block`'s
+ *   linear (sana_multi_scale.py:241), whose input is also needed without the activation.
+ */
+int sana_patchify(const void* x, void* out, int64_t ldo, int64_t B, int64_t Cin, int64_t H, int64_t W, int64_t p,
+                  int dtype, void* stream);
+int sana_unpatchify(const void* tok, int64_t ld, void* out, int64_t B, int64_t Cout, int64_t Hp, int64_t Wp, int64_t p,
+                    int dtype, void* stream);
+int sana_timestep_embedding(const float* t, void* out, int64_t B, int64_t dim, float max_period, int dtype,
+                            void* stream);
+int sana_silu(const void* x, void* out, int64_t n, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -227,6 +227,94 @@ def adaln_single(t_scalar: torch.Tensor, p: Params, dtype=torch.float32) -> torc
 
 
 # ----------------------------------------------------------------------------------------
+# The whole multi-scale DiT forward (the steps either side of the block loop).
+# ----------------------------------------------------------------------------------------
+def sincos_1d(embed_dim: int, pos):
+    """get_1d_sincos_pos_embed_from_grid, diffusion/model/nets/sana.py:447-465 (numpy, float64
+    frequencies; sin half first, then cos)."""
+    import numpy as np
+
+    omega = np.arange(embed_dim // 2, dtype=np.float64)
+    omega /= embed_dim / 2.0
+    omega = 1.0 / 10000**omega
+    out = np.einsum("m,d->md", pos.reshape(-1), omega)
+    return np.concatenate([np.sin(out), np.cos(out)], axis=1)
+
+
+def sincos_pos_embed_2d(embed_dim: int, grid_size, pe_interpolation: float = 1.0, base_size: int = 16):
+    """get_2d_sincos_pos_embed (+ _from_grid), sana.py:416-444: float32 coordinates, meshgrid
+    with w first, reshape to [2, 1, w, h]; the first half of the channels encodes grid[0]."""
+    import numpy as np
+
+    grid_h = np.arange(grid_size[0], dtype=np.float32) / (grid_size[0] / base_size) / pe_interpolation
+    grid_w = np.arange(grid_size[1], dtype=np.float32) / (grid_size[1] / base_size) / pe_interpolation
+    grid = np.meshgrid(grid_w, grid_h)
+    grid = np.stack(grid, axis=0)
+    grid = grid.reshape([2, 1, grid_size[1], grid_size[0]])
+    return np.concatenate([sincos_1d(embed_dim // 2, grid[0]), sincos_1d(embed_dim // 2, grid[1])], axis=1)
+
+
+def sana_ms_forward(x, timestep, y, p: Params, *, depth: int, num_heads: int, patch_size: int, out_channels: int,
+                    base_size: int, mask=None, pe_interpolation: float = 1.0, y_norm: bool = False,
+                    norm_eps: float = 1e-5, timestep_norm_scale_factor: float = 1.0, use_pe: bool = True,
+                    linear_head_dim: int = 32, return_parts: bool = False):
+    """SanaMS.forward, diffusion/model/nets/sana_multi_scale.py:326-393, without xformers (the
+    2-D mask goes to every block), sin-cos positions, no cfg embedder, no log-variance head.
+
+    x [B, Cin, H, W]; timestep [B]; y [B, 1, L, Cc]; mask [B, L] or None.  Parameters use the
+    model's state-dict keys (x_embedder.proj.*, t_embedder.mlp.{0,2}.*, t_block.1.*,
+    y_embedder.y_proj.fc{1,2}.*, attention_y_norm.weight, blocks.<i>.*, final_layer.*)."""
+    import torch as _t
+
+    dtype = p["t_block.1.weight"].dtype
+    x = x.to(dtype)
+    if timestep_norm_scale_factor != 1.0:
+        timestep = (timestep.float() / timestep_norm_scale_factor).to(_t.float32)
+    else:
+        timestep = timestep.long().to(_t.float32)
+    y = y.to(dtype)
+    h, w = x.shape[-2] // patch_size, x.shape[-1] // patch_size
+    # PatchEmbedMS.forward, sana_blocks.py:1263-1268
+    x = F.conv2d(x, p["x_embedder.proj.weight"], p["x_embedder.proj.bias"], stride=patch_size)
+    x = x.flatten(2).transpose(1, 2)
+    C = x.shape[-1]
+    if use_pe:
+        pos = _t.from_numpy(sincos_pos_embed_2d(C, (h, w), pe_interpolation=pe_interpolation, base_size=base_size))
+        x = x + pos.unsqueeze(0).to(dtype)
+    # TimestepEmbedder.forward, sana_blocks.py:1002-1005
+    t = timestep_embedding(timestep, p["t_embedder.mlp.0.weight"].shape[1]).to(dtype)
+    t = F.linear(t, p["t_embedder.mlp.0.weight"], p["t_embedder.mlp.0.bias"])
+    t = F.linear(F.silu(t), p["t_embedder.mlp.2.weight"], p["t_embedder.mlp.2.bias"])
+    t0 = F.linear(F.silu(t), p["t_block.1.weight"], p["t_block.1.bias"])
+    # CaptionEmbedder.forward in eval mode (sana_blocks.py:1123-1138): the GELU(tanh) MLP only
+    y = F.linear(y, p["y_embedder.y_proj.fc1.weight"], p["y_embedder.y_proj.fc1.bias"])
+    y = F.linear(F.gelu(y, approximate="tanh"), p["y_embedder.y_proj.fc2.weight"], p["y_embedder.y_proj.fc2.bias"])
+    if y_norm:
+        y = rms_norm(y, p["attention_y_norm.weight"], norm_eps)
+    if mask is not None:
+        mask = mask.to(_t.int16)
+        mask = mask.repeat(y.shape[0] // mask.shape[0], 1) if mask.shape[0] != y.shape[0] else mask
+        mask = mask.squeeze(1).squeeze(1)
+    parts = {"x_embed": x, "t": t, "t0": t0, "y": y}
+    for i in range(depth):
+        x = sana_ms_block_forward(x, y, t0, sub(p, f"blocks.{i}"), num_heads, (h, w), mask,
+                                  linear_head_dim=linear_head_dim)
+    parts["x_blocks"] = x
+    # T2IFinalLayer.forward, sana_blocks.py:919-925
+    shift, scale = (p["final_layer.scale_shift_table"][None] + t[:, None]).chunk(2, dim=1)
+    x = t2i_modulate(layer_norm(x), shift, scale)
+    x = F.linear(x, p["final_layer.linear.weight"], p["final_layer.linear.bias"])
+    # unpatchify, sana_multi_scale.py:409-421
+    c, ps = out_channels, patch_size
+    x = x.reshape(shape=(x.shape[0], h, w, ps, ps, c))
+    x = _t.einsum("nhwpqc->nchpwq", x)
+    imgs = x.reshape(shape=(x.shape[0], c, h * ps, w * ps))
+    if return_parts:
+        return imgs, parts
+    return imgs
+
+
+# ----------------------------------------------------------------------------------------
 # Sequence-parallel restatement (no upstream counterpart for LiteLA: the state is a plain
 # sum over tokens, so shards add; the depthwise conv needs one row of halo inside a frame).
 # The partition rule mirrors the contiguous-rank layout of upstream's context-parallel

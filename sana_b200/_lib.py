@@ -43,6 +43,8 @@ SIGNATURES = {
     "sana_abi_version": (_i32, []),
     "sana_last_error": (C.c_char_p, []),
     "sana_ln_modulate": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _f32, _i32, _vp]),
+    "sana_ln_modulate_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
+                                     _vp]),
     "sana_rmsnorm": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_la_state_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "sana_la_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
@@ -62,6 +64,10 @@ SIGNATURES = {
     "sana_nvfp4_quantize": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "sana_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _vp]),
     "sana_gemm_nvfp4_take_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "sana_patchify": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sana_unpatchify": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sana_timestep_embedding": (_i32, [_vp, _vp, _i64, _i64, _f32, _i32, _vp]),
+    "sana_silu": (_i32, [_vp, _vp, _i64, _i32, _vp]),
 }
 
 _lock = threading.Lock()

@@ -39,12 +39,19 @@ __device__ __forceinline__ float epi_silu<float>(float x) { return x / (1.0f + e
 template <>
 __device__ __forceinline__ float epi_silu<__nv_bfloat16>(float x) { return silu(x); }
 
+// GELU, tanh form (nn.GELU(approximate="tanh")): 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
 // scalar form (SIMT kernel)
 template <typename T>
 __device__ __forceinline__ float epi_scalar(float v, int64_t m, int64_t n, int64_t N, const EpiParams& p) {
   if (p.bias) v += to_f32(static_cast<const T*>(p.bias)[n]);
   if (p.act == 1) v = epi_silu<T>(v);
   else if (p.act == 2 && n < p.relu_cols) v = fmaxf(v, 0.f);
+  else if (p.act == 3) v = gelu_tanh(v);
   if (p.gate_table) {
     const int64_t b = m / p.rows_per_batch;
     const float g = to_f32(static_cast<const T*>(p.gate_table)[(int64_t)p.gate_row * N + n]) +
@@ -76,6 +83,9 @@ __device__ __forceinline__ uint4 epi_vec8_bf16(float (&v)[8], int64_t m, int64_t
 #pragma unroll
     for (int e = 0; e < 8; ++e)
       if (n + e < p.relu_cols) v[e] = fmaxf(v[e], 0.f);
+  } else if (p.act == 3) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
   }
   if (p.gate_table) {
     float g[8];
@@ -107,7 +117,7 @@ inline int check_epilogue(const sana_gemm_epilogue* ep, int64_t N, EpiParams* ou
     p.relu_cols = ep->relu_cols;
     p.act = ep->act;
     p.gate_row = ep->gate_row;
-    if (p.act < 0 || p.act > 2) return fail(SANA_ERR_INVALID, "%s: act must be 0, 1 or 2", who);
+    if (p.act < 0 || p.act > 3) return fail(SANA_ERR_INVALID, "%s: act must be 0, 1, 2 or 3", who);
     if (p.gate_table) {
       if (!p.gate_t) return fail(SANA_ERR_INVALID, "%s: gate_t required with gate_table", who);
       if (p.gate_row < 0 || p.gate_row > 5) return fail(SANA_ERR_INVALID, "%s: gate_row out of range", who);

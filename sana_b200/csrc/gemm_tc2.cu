@@ -315,6 +315,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
               for (int e = 0; e < 8; ++e)
                 if (n + 8 * h + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+            } else if (ep.act == 3) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
             }
             if (row.grow) {
               float g[8];

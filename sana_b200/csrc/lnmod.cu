@@ -46,7 +46,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <typename T, int MAXV>
 __global__ void __launch_bounds__(256)
 ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T* __restrict__ t, T* __restrict__ z,
-                   int64_t rows, int N, int C, int shift_row, int scale_row, float eps, int rows_per_block) {
+                   int64_t rows, int N, int C, int tb_shift, int tb_scale, int t_rows, int t_shift, int t_scale,
+                   float eps, int rows_per_block) {
   constexpr int VN = Vec16<T>::N;
   constexpr int PLANES = VN / 4;
   extern __shared__ float4 ln_smem[];
@@ -65,10 +66,10 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
     const int64_t seg1 = ((b + 1) * N < row1) ? (b + 1) * N : row1;
     __syncthreads();  // every warp is done with the previous sample's vectors
     {
-      const T* tsc = t + (b * 6 + scale_row) * C;
-      const T* tsh = t + (b * 6 + shift_row) * C;
-      const T* bsc = table + (int64_t)scale_row * C;
-      const T* bsh = table + (int64_t)shift_row * C;
+      const T* tsc = t + (b * t_rows + t_scale) * C;
+      const T* tsh = t + (b * t_rows + t_shift) * C;
+      const T* bsc = table + (int64_t)tb_scale * C;
+      const T* bsh = table + (int64_t)tb_shift * C;
       float* fm = reinterpret_cast<float*>(s_mul);
       float* fa = reinterpret_cast<float*>(s_add);
       for (int i = threadIdx.x; i < C; i += blockDim.x) {
@@ -135,7 +136,7 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
 
 template <typename T>
 static int launch_ln(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N, int64_t C,
-                     int shift_row, int scale_row, float eps, cudaStream_t st) {
+                     int tb_shift, int tb_scale, int t_rows, int t_shift, int t_scale, float eps, cudaStream_t st) {
   const int64_t rows = B * N;
   const int nvec = (int)(C / Vec16<T>::N);
   const int per_lane = (nvec + 31) / 32;
@@ -156,8 +157,8 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
                                            (int)smem);                                                         \
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_modulate)");                       \
     }                                                                                                          \
-    ln_modulate_kernel<T, MV><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, shift_row, scale_row, \
-                                                       eps, (int)rpb);                                         \
+    ln_modulate_kernel<T, MV><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, tb_shift, tb_scale,   \
+                                                       t_rows, t_shift, t_scale, eps, (int)rpb);               \
     SANA_LAUNCH_CHECK("ln_modulate kernel");                                                                   \
     return SANA_OK;                                                                                            \
   }
@@ -173,18 +174,33 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
 
 using namespace sana;
 
-extern "C" int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
-                                int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream) {
+extern "C" int sana_ln_modulate_rows(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
+                                     int64_t C, int table_rows, int table_shift_row, int table_scale_row, int t_rows,
+                                     int t_shift_row, int t_scale_row, float eps, int dtype, void* stream) {
   SANA_REQUIRE(x && table && t && z, "sana_ln_modulate: null pointer");
   SANA_REQUIRE(B > 0 && N > 0 && C > 0, "sana_ln_modulate: sizes must be positive");
   SANA_REQUIRE(C % 8 == 0 && C * (dtype == SANA_F32 ? 4 : 2) <= 16384,
                "sana_ln_modulate: C must be a multiple of 8 and a row at most 16 KiB");
-  SANA_REQUIRE(shift_row >= 0 && shift_row < 6 && scale_row >= 0 && scale_row < 6, "sana_ln_modulate: bad table row");
+  SANA_REQUIRE(table_rows > 0 && table_shift_row >= 0 && table_shift_row < table_rows && table_scale_row >= 0 &&
+                   table_scale_row < table_rows,
+               "sana_ln_modulate: bad table row");
+  SANA_REQUIRE(t_rows > 0 && t_shift_row >= 0 && t_shift_row < t_rows && t_scale_row >= 0 && t_scale_row < t_rows,
+               "sana_ln_modulate: bad row of t");
   SANA_REQUIRE(aligned16(x) && aligned16(table) && aligned16(t) && aligned16(z),
                "sana_ln_modulate: pointers must be 16-byte aligned");
   SANA_REQUIRE(B * N < ((int64_t)1 << 31) * 8, "sana_ln_modulate: too many rows");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == SANA_BF16) return launch_ln<__nv_bfloat16>(x, table, t, z, B, N, C, shift_row, scale_row, eps, st);
-  if (dtype == SANA_F32) return launch_ln<float>(x, table, t, z, B, N, C, shift_row, scale_row, eps, st);
+  if (dtype == SANA_BF16)
+    return launch_ln<__nv_bfloat16>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
+                                    t_scale_row, eps, st);
+  if (dtype == SANA_F32)
+    return launch_ln<float>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
+                            t_scale_row, eps, st);
   return fail(SANA_ERR_UNSUPPORTED, "sana_ln_modulate: unsupported dtype %d", dtype);
+}
+
+extern "C" int sana_ln_modulate(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N,
+                                int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream) {
+  return sana_ln_modulate_rows(x, table, t, z, B, N, C, 6, shift_row, scale_row, 6, shift_row, scale_row, eps, dtype,
+                               stream);
 }

@@ -232,6 +232,9 @@ __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, 
 #pragma unroll
             for (int e = 0; e < 8; ++e)
               if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+          } else if (ep.act == 3) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
           }
           if (r.grow) {
             float g[8];

@@ -17,7 +17,7 @@ from ._lib import SANA_BF16, SANA_F32, GemmEpilogue, SanaLibraryError
 HEAD_DIM = 32
 STATE_ROWS = HEAD_DIM + 1
 
-ACT_NONE, ACT_SILU, ACT_RELU_COLS = 0, 1, 2
+ACT_NONE, ACT_SILU, ACT_RELU_COLS, ACT_GELU_TANH = 0, 1, 2, 3
 
 
 class _Counters:
@@ -81,6 +81,86 @@ def ln_modulate(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row
                                     shift_row, scale_row, eps, _dtype_code(x.dtype), _stream()), "sana_ln_modulate")
     counters.launches += 1
     return z
+
+
+def ln_modulate_rows(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, table_shift_row: int, table_scale_row: int,
+                     t_shift_row: int, t_scale_row: int, eps: float = 1e-6) -> torch.Tensor:
+    """Like :func:`ln_modulate` with table [R, C] and t [B, Rt, C] and the rows named separately
+    (the final layer: table [2, C], t [B, 1, C], rows (0, 1) of the table and row 0 of t twice)."""
+    _need_cuda(x, table, t)
+    B, N, Cc = x.shape
+    x = x.contiguous()
+    table = table.contiguous()
+    t = t.reshape(B, -1, Cc).contiguous()
+    if table.dim() != 2 or table.shape[1] != Cc or table.dtype != x.dtype or t.dtype != x.dtype:
+        raise SanaLibraryError("ln_modulate_rows: table must be [R, C] and t [B, Rt, C] in x's dtype")
+    z = torch.empty_like(x)
+    lib = _lib.load()
+    _lib.check(lib.sana_ln_modulate_rows(x.data_ptr(), table.data_ptr(), t.data_ptr(), z.data_ptr(), B, N, Cc,
+                                         table.shape[0], table_shift_row, table_scale_row, t.shape[1], t_shift_row,
+                                         t_scale_row, eps, _dtype_code(x.dtype), _stream()), "sana_ln_modulate_rows")
+    counters.launches += 1
+    return z
+
+
+def patchify(x: torch.Tensor, p: int) -> torch.Tensor:
+    """Latent [B, Cin, H, W] -> patch rows [B*(H/p)*(W/p), Cin*p*p] (the unfold of a stride-p,
+    kernel-p convolution; column order matches the conv weight viewed as [embed, Cin*p*p])."""
+    _need_cuda(x)
+    B, Cin, H, W = x.shape
+    x = x.contiguous()
+    out = torch.empty(B * (H // p) * (W // p), Cin * p * p, dtype=x.dtype, device=x.device)
+    _lib.check(_lib.load().sana_patchify(x.data_ptr(), out.data_ptr(), out.stride(0), B, Cin, H, W, p,
+                                         _dtype_code(x.dtype), _stream()), "sana_patchify")
+    counters.launches += 1
+    return out
+
+
+def unpatchify(tok: torch.Tensor, B: int, Cout: int, Hp: int, Wp: int, p: int) -> torch.Tensor:
+    """Token rows [B*Hp*Wp, p*p*Cout] -> images [B, Cout, Hp*p, Wp*p]."""
+    _need_cuda(tok)
+    rows, cols, ld = _rows2d(tok, "unpatchify tokens")
+    if rows != B * Hp * Wp or cols != p * p * Cout:
+        raise SanaLibraryError(f"unpatchify: expected [{B * Hp * Wp}, {p * p * Cout}] token rows, got {tuple(tok.shape)}")
+    out = torch.empty(B, Cout, Hp * p, Wp * p, dtype=tok.dtype, device=tok.device)
+    _lib.check(_lib.load().sana_unpatchify(tok.data_ptr(), ld, out.data_ptr(), B, Cout, Hp, Wp, p,
+                                           _dtype_code(tok.dtype), _stream()), "sana_unpatchify")
+    counters.launches += 1
+    return out
+
+
+def timestep_embedding(t: torch.Tensor, dim: int, dtype: torch.dtype, max_period: float = 10000.0) -> torch.Tensor:
+    """Sinusoidal features [B, dim] (cos half, then sin half) of fp32 timesteps t [B]."""
+    _need_cuda(t)
+    t = t.reshape(-1).to(torch.float32).contiguous()
+    out = torch.empty(t.numel(), dim, dtype=dtype, device=t.device)
+    _lib.check(_lib.load().sana_timestep_embedding(t.data_ptr(), out.data_ptr(), t.numel(), dim, max_period,
+                                                   _dtype_code(dtype), _stream()), "sana_timestep_embedding")
+    counters.launches += 1
+    return out
+
+
+def silu(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().sana_silu(x.data_ptr(), out.data_ptr(), x.numel(), _dtype_code(x.dtype), _stream()),
+               "sana_silu")
+    counters.launches += 1
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """Out-of-place RMSNorm with weight over the last dimension of a 2-D tensor."""
+    _need_cuda(x, weight)
+    rows, Cc, ld = _rows2d(x, "rmsnorm x")
+    if weight.numel() != Cc or weight.dtype != x.dtype:
+        raise SanaLibraryError("rmsnorm: weight must be [C] in x's dtype")
+    out = torch.empty(rows, Cc, dtype=x.dtype, device=x.device)
+    _lib.check(_lib.load().sana_rmsnorm(x.data_ptr(), ld, weight.contiguous().data_ptr(), out.data_ptr(), Cc, rows, Cc,
+                                        eps, _dtype_code(x.dtype), _stream()), "sana_rmsnorm")
+    counters.launches += 1
+    return out
 
 
 def rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -225,7 +305,7 @@ def take_dwconv_glu_device_status() -> int:
 
 
 def _epi_tag(bias, act, gate, residual) -> str:
-    return (" +bias" if bias is not None else "") + (" +silu" if act == ACT_SILU else "") + \
+    return (" +bias" if bias is not None else "") + (" +silu" if act == ACT_SILU else " +gelu" if act == ACT_GELU_TANH else "") + \
         (" *gate" if gate is not None else "") + (" +res" if residual is not None else "")
 
 

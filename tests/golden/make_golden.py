@@ -115,6 +115,50 @@ def video_case(R, seed=3):
     return small_block_case(R, "video", 64, 4, 1, (3, 5, 8), 7, seed)
 
 
+SANA_MS_SMALL = dict(input_size=8, patch_size=1, in_channels=32, hidden_size=64, depth=2, num_heads=2, mlp_ratio=2.5,
+                     class_dropout_prob=0.0, pred_sigma=False, caption_channels=48, model_max_length=10, y_norm=True,
+                     attn_type="linear", ffn_type="glumbconv", mlp_acts=("silu", "silu", None), linear_head_dim=32,
+                     use_pe=True, norm_eps=1e-5, y_norm_scale_factor=0.01)
+
+
+def sana_ms_case(R, seed=5):
+    """The whole SanaMS.forward of a two-block model on a 6 x 8 latent (non-square on purpose:
+    the position table depends on the h / w order), every parameter drawn at random so that no
+    zero-initialised projection hides an error.  Stores the inputs, the state dict and the output
+    in fp32 and bf16."""
+    cfg = dict(SANA_MS_SMALL)
+    g = torch.Generator().manual_seed(seed)
+    m = R.sana_multi_scale.SanaMS(**cfg, use_fp32_attention=True).eval()
+    sd = m.state_dict()
+    params = {}
+    for k, v in sd.items():
+        if k == "pos_embed":
+            params[k] = v.clone()  # unused buffer of the base class at a fixed size
+        elif k.endswith("norm.weight") or k.endswith("attention_y_norm.weight"):
+            params[k] = v + 0.2 * v * torch.randn(v.shape, generator=g)
+        elif k == "y_embedder.y_embedding":
+            params[k] = v.clone()
+        else:
+            params[k] = torch.randn(v.shape, generator=g) * (0.3 if v.dim() == 1 else 1.5 / v[0].numel() ** 0.5)
+    B, L = 2, 10
+    x = torch.randn(B, 32, 6, 8, generator=g)
+    timestep = torch.tensor([37.0, 912.0])
+    y = torch.randn(B, 1, L, 48, generator=g)
+    mask = torch.ones(B, L, dtype=torch.int64)
+    mask[1, 6:] = 0
+    out = {"cfg": cfg, "params": params, "x": x, "timestep": timestep, "y": y, "mask": mask}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            m.load_state_dict(params, strict=True)
+            set_fp32_attention(m)
+            mm = m.to(dt)
+            mm.pos_embed_ms = None  # upstream caches the position table by shape only, not by dtype
+            out[f"out_{tag}"] = mm(x, timestep, y, mask=mask)
+            out[f"out_nomask_{tag}"] = mm(x, timestep, y, mask=torch.ones(B, L, dtype=torch.int64))
+            m = m.float()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -130,6 +174,7 @@ def main():
         "small_block_qknorm": lambda: small_block_case(R, "q", 64, 4, 2, (5, 6), 8, seed=4, with_mask=True, qk_norm=True),
         "litela_cfg1": lambda: litela_cfg1_case(R),
         "block_cfg2": lambda: block_cfg2_case(R),
+        "sana_ms_small": lambda: sana_ms_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():
