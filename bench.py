@@ -1,13 +1,16 @@
 #!/usr/bin/env python
 """Benchmark of the Linear-DiT block hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload stack|seqpar]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload stack|seqpar|nvfp4|dit]
 
 Default workload ("stack"): the Sana-1.6B transformer stack - 20 SanaMSBlocks, hidden 2240,
 70 linear-attention heads x 32, FFN hidden 5600, bf16, 128x128 latent grid = 16 384 tokens,
 300 text tokens - at global batch 8, batch-data-parallel over N GPUs (8/N images per GPU, no
 collective in the forward; "strong" scaling).  One step = one forward of the stack over this
 rank's images.  value = block-tokens/s of the whole job = 8 * 16384 * 20 / step time.
+
+"dit": the same stack inside the whole DiT forward (latents in, latents out: patch embedding,
+embedders, final layer, unpatchify), same unit.  "nvfp4": one block with FP4 projections.
 
 "seqpar": one block on a 21x45x80 = 75 600-token grid, rows sharded over the N GPUs
 (linear-attention state all-reduce + one-row conv halos); value = tokens/s of the block.
@@ -44,10 +47,10 @@ SEQPAR_GRID = (21, 45, 80)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core GEMM, averaged over the seven
 # launches of one block at batch 1 (ncu capture summarised in
-# profiles/stack_1600m_16k_tokens_launch_shares.md: 1.993 GB / 7).  The bench's launches carry
+# profiles/stack_1600m_16k_tokens_launch_shares.md: 1.958 GB / 7).  The bench's launches carry
 # `per-GPU batch` times the rows, and activations dominate the bytes, so the figure is scaled by
 # the per-GPU batch.
-NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 = 284.7e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 = 279.7e6
 
 
 def block_roofline_seconds(T: int, B: int, peaks: dict) -> float:
@@ -268,7 +271,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4", "dit"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
     ap.add_argument("--depth", type=int, default=None, help="blocks in the stack (default 20; 1 for nvfp4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -307,7 +310,8 @@ def main() -> None:
     peaks = load_peaks()
 
     nvfp4 = args.workload == "nvfp4"
-    if args.workload in ("stack", "nvfp4"):
+    whole = args.workload == "dit"
+    if args.workload in ("stack", "nvfp4", "dit"):
         depth = args.depth or (1 if nvfp4 else DEPTH)
         b0, b1 = sharding.batch_partition(args.batch, world)[rank]
         Bl = b1 - b0
@@ -319,6 +323,10 @@ def main() -> None:
             workload = (f"cfg5: {depth} SanaMSBlock(s) at Sana-1.6B width with NVFP4 qkv/out/FFN projections (E2M1, E4M3 "
                         f"scale per 16, fp32 scale per tensor, weights and activations), 64x64 grid = {tokens} tokens, "
                         f"global batch {args.batch}")
+        elif whole:
+            workload = (f"whole Sana-1.6B DiT forward (patch embed + position table, timestep / caption embedders, "
+                        f"{depth} SanaMSBlocks, final layer, unpatchify), {GRID[0]}x{GRID[1]} latent x 32 channels = "
+                        f"{tokens} tokens, {TEXT} caption tokens x 2304, global batch {args.batch}")
         else:
             workload = (f"cfg3: Sana-1.6B stack, {depth} SanaMSBlocks, hidden {C}, {C // 32} LA heads x 32, FFN {HID}, "
                         f"{GRID[0]}x{GRID[1]} grid = {tokens} tokens, global batch {args.batch}")
@@ -335,8 +343,22 @@ def main() -> None:
         parallelism = f"sp{world}"
         scaling = "strong"
 
-    stack = sana_b200.BlockStack(C, HEADS, depth).eval()
-    stack = stack.to(device=dev, dtype=dt)
+    model = None
+    if whole:
+        model = sana_b200.SanaMS(input_size=GRID[0], patch_size=1, in_channels=32, hidden_size=C, depth=depth,
+                                 num_heads=HEADS, mlp_ratio=2.5, class_dropout_prob=0.0, pred_sigma=False,
+                                 caption_channels=2304, model_max_length=TEXT, y_norm=True, y_norm_scale_factor=0.01,
+                                 attn_type="linear", ffn_type="glumbconv", linear_head_dim=32).eval()
+        model = model.to(device=dev, dtype=dt)
+        gen = torch.Generator(device=dev).manual_seed(99)
+        for name, prm in model.named_parameters():
+            if not name.startswith("blocks.") and "norm" not in name:
+                prm.data.copy_((torch.randn(prm.shape, generator=gen, device=dev) * 0.02).to(dt))
+        stack = sana_b200.BlockStack(C, HEADS, 0)
+        stack.blocks = model.blocks
+    else:
+        stack = sana_b200.BlockStack(C, HEADS, depth).eval()
+        stack = stack.to(device=dev, dtype=dt)
     for i, blk in enumerate(stack.blocks):
         blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, i, 0.02, dt, dev), strict=True)
     if args.cross_attn_kernel:
@@ -354,16 +376,26 @@ def main() -> None:
     y_h = torch.randn(Bl, TEXT, C, generator=g).to(dt).pin_memory()
     t_h = (torch.randn(Bl, 6 * C, generator=g) * 0.1).to(dt).pin_memory()
     out_h = torch.empty(Bl, tokens, C, dtype=dt).pin_memory()
+    if whole:  # latents, caption features and timesteps instead of token-major block inputs
+        x_h = torch.randn(Bl, 32, grid[0], grid[1], generator=g).to(dt).pin_memory()
+        y_h = torch.randn(Bl, 1, TEXT, 2304, generator=g).to(dt).pin_memory()
+        t_h = torch.randint(0, 1000, (Bl,), generator=g).to(torch.float32).pin_memory()
+        out_h = torch.empty(Bl, 32, grid[0], grid[1], dtype=dt).pin_memory()
     x_d, y_d, t_d = x_h.to(dev), y_h.to(dev), t_h.to(dev)
 
+    def forward(xd, yd, td):
+        if whole:
+            return model(xd, td, yd, mask=None)
+        return stack(xd, yd, td, None, grid)
+
     def step():
-        return stack(x_d, y_d, t_d, None, grid)
+        return forward(x_d, y_d, t_d)
 
     def step_e2e():
         xd = x_h.to(dev, non_blocking=True)
         yd = y_h.to(dev, non_blocking=True)
         td = t_h.to(dev, non_blocking=True)
-        out_h.copy_(stack(xd, yd, td, None, grid), non_blocking=True)
+        out_h.copy_(forward(xd, yd, td), non_blocking=True)
 
     def sync_all():
         if world > 1:
