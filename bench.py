@@ -53,7 +53,7 @@ SEQPAR_GRID = (21, 45, 80)
 NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 = 279.7e6
 
 
-def block_roofline_seconds(T: int, B: int, peaks: dict) -> float:
+def block_roofline_seconds(T: int, B: int, peaks: dict, C: int = C) -> float:
     """Serial sum of per-kernel bounds for one block: tensor time of the GEMM FLOPs plus HBM
     time of the bandwidth-bound kernels (linear-attention core 4*T*C*e + depthwise-GLU 3*T*hid*e)."""
     f_gemm = 27.0 * T * C * C + 4.0 * B * TEXT * C * C + 4.0 * T * TEXT * C
@@ -271,7 +271,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4", "dit"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4", "dit", "small"])
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the forward as one CUDA graph (sana_b200.graphs.GraphedForward)")
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
     ap.add_argument("--depth", type=int, default=None, help="blocks in the stack (default 20; 1 for nvfp4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -311,11 +313,16 @@ def main() -> None:
 
     nvfp4 = args.workload == "nvfp4"
     whole = args.workload == "dit"
-    if args.workload in ("stack", "nvfp4", "dit"):
-        depth = args.depth or (1 if nvfp4 else DEPTH)
+    small = args.workload == "small"
+    # widths: Sana-1.6B everywhere except "small" (Sana-0.6B: hidden 1152, 16 heads, FFN 2880, 28 blocks)
+    C, HEADS, HID = (1152, 16, 2880) if small else (globals()["C"], globals()["HEADS"], globals()["HID"])
+    if args.workload in ("stack", "nvfp4", "dit", "small"):
+        depth = args.depth or (1 if nvfp4 else (28 if small else DEPTH))
+        if small and args.batch == GLOBAL_BATCH:
+            args.batch = 4 * world
         b0, b1 = sharding.batch_partition(args.batch, world)[rank]
         Bl = b1 - b0
-        grid = (64, 64) if nvfp4 else GRID
+        grid = (64, 64) if nvfp4 else ((32, 32) if small else GRID)
         tokens = grid[0] * grid[1]
         shard = None
         total_units = args.batch * tokens * depth
@@ -323,6 +330,10 @@ def main() -> None:
             workload = (f"cfg5: {depth} SanaMSBlock(s) at Sana-1.6B width with NVFP4 qkv/out/FFN projections (E2M1, E4M3 "
                         f"scale per 16, fp32 scale per tensor, weights and activations), 64x64 grid = {tokens} tokens, "
                         f"global batch {args.batch}")
+        elif small:
+            workload = (f"cfg2 width: Sana-0.6B stack, {depth} SanaMSBlocks, hidden {C}, FFN {HID}, 32x32 grid = {tokens} "
+                        f"tokens (512 px), global batch {args.batch}" + (", one CUDA graph per step" if args.graph else
+                                                                         ", eager launches"))
         elif whole:
             workload = (f"whole Sana-1.6B DiT forward (patch embed + position table, timestep / caption embedders, "
                         f"{depth} SanaMSBlocks, final layer, unpatchify), {GRID[0]}x{GRID[1]} latent x 32 channels = "
@@ -388,6 +399,17 @@ def main() -> None:
             return model(xd, td, yd, mask=None)
         return stack(xd, yd, td, None, grid)
 
+    if args.graph:
+        from sana_b200.graphs import GraphedForward
+
+        if shard is not None and world > 1:
+            raise SystemExit("--graph is not offered with the fused state exchange (its step counter is a launch argument)")
+        eager = forward
+        graphed = GraphedForward(lambda a, b, c: eager(a, b, c), x_d, y_d, t_d)
+        forward = lambda xd, yd, td: graphed(xd, yd, td)  # noqa: E731
+    else:
+        eager = forward
+
     def step():
         return forward(x_d, y_d, t_d)
 
@@ -424,6 +446,15 @@ def main() -> None:
         total_ms = timed(step, args.steps)
     ops.counters.gemm_timing = False
     launches = ops.counters.launches
+    eager_ms = None
+    if args.graph:
+        # a replayed graph runs no Python: per-GEMM events and the launch count come from an
+        # eager pass of the same steps (also the "before" figure of the graph)
+        ops.counters.reset()
+        ops.counters.gemm_timing = True
+        eager_ms = timed(lambda: eager(x_d, y_d, t_d), args.steps)
+        ops.counters.gemm_timing = False
+        launches = ops.counters.launches
     gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in ops.counters.gemm_events)
     gemm_flops = sum(f for _, _, f, _ in ops.counters.gemm_events)
     n_gemm = len(ops.counters.gemm_events)
@@ -446,7 +477,7 @@ def main() -> None:
         value = total_units / (ms_per_step * 1e-3)
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
         T_local = Bl * tokens
-        roof_s = block_roofline_seconds(T_local, Bl, peaks) * depth
+        roof_s = block_roofline_seconds(T_local, Bl, peaks, C) * depth
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
@@ -464,7 +495,8 @@ def main() -> None:
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
-                         "share_of_step": gemm_ms / total_ms, "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 * Bl) if args.workload == "stack" else None},
+                         "share_of_step": gemm_ms / (eager_ms or total_ms), "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 * Bl) if args.workload == "stack" else None},
+            "cuda_graph": bool(args.graph), "eager_ms_per_step": (eager_ms / args.steps) if eager_ms else None,
             "block_roofline": {"t_roof_ms_per_step": roof_s * 1e3, "frac": roof_s * 1e3 / ms_per_step,
                                "formula": "F_gemm/P_tensor + 11.5*T*C*e/BW_hbm, per block"},
             "e2e": {"value": total_units / (e2e_ms / args.steps * 1e-3), "unit": UNIT,

@@ -106,3 +106,17 @@ def test_position_table_matches_oracle():
     a = dit.sincos_pos_embed_2d(64, (6, 8), base_size=8)
     b = O.sincos_pos_embed_2d(64, (6, 8), base_size=8)
     assert (a == b).all()
+
+
+def test_graph_replay_matches_eager(golden):
+    """One CUDA graph of the whole forward gives the eager result bit for bit, also on new inputs."""
+    from sana_b200.graphs import GraphedForward
+
+    g = golden("sana_ms_small")
+    m = _model(g, torch.bfloat16)
+    x, ts, y = g["x"].to(DEV).bfloat16(), g["timestep"].to(DEV), g["y"].to(DEV).bfloat16()
+    mask = g["mask"].to(DEV)
+    fwd = GraphedForward(m, x, ts, y, mask=mask)
+    assert torch.equal(fwd(x, ts, y), m(x, ts, y, mask=mask))
+    x2, ts2 = (x * 0.5 + 0.1).contiguous(), torch.tensor([5.0, 700.0], device=DEV)
+    assert torch.equal(fwd(x2, ts2, y), m(x2, ts2, y, mask=mask))
