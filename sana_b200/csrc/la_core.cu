@@ -50,7 +50,7 @@ la_state_bf16_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* 
   const __nv_bfloat16* kbase = kp + (int64_t)b * N * ld + col;
   const __nv_bfloat16* vbase = vp + (int64_t)b * N * ld + col;
 
-  constexpr int U = 2;  // 16-token steps in flight per iteration
+  constexpr int U = 3;  // 16-token steps in flight per iteration
   for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
     uint2 kr[U][4], vr[U][4];
 #pragma unroll
@@ -224,9 +224,8 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
   const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
   __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
 
-  constexpr int U = 2;
-  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
-    uint4 qr[U][2];
+  constexpr int U = 4;  // 16-token steps per batch of loads
+  auto load = [&](uint4 (&qr)[U][2], int n0) {
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -234,6 +233,8 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
         const int tok = n0 + 16 * u + g + 8 * r;
         qr[u][r] = (tok < n_end) ? ldg_nc_u4(qbase + (int64_t)tok * ldq) : make_uint4(0u, 0u, 0u, 0u);
       }
+  };
+  auto compute = [&](const uint4 (&qr)[U][2], int n0) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       uint32_t a[2][4];  // [row half][word]
@@ -284,6 +285,12 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
         }
       }
     }
+  };
+  uint4 qa[U][2];
+#pragma unroll 1
+  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
+    load(qa, n0);
+    compute(qa, n0);
   }
 }
 
