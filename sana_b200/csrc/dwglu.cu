@@ -17,9 +17,10 @@ namespace sana {
 
 __device__ int g_dw_status = 0;  // soft-error word: 1 = a wait on an input row timed out
 
-constexpr int DW_TW = 16;       // output columns per CTA (two per warp)
-constexpr int DW_WARPS = 8;
+constexpr int DW_WARPS = 8;  // single-warp CTAs measured 30 % slower
+constexpr int DW_TW = 2 * DW_WARPS;  // output columns per CTA (two per warp)
 constexpr int DW_THREADS = 32 * DW_WARPS;
+constexpr int DW_CTAS_PER_SM = 16 / DW_WARPS;  // 16 resident warps (register-limited)
 constexpr int DW_CH = 64;       // value channels per warp (and as many gate channels)
 constexpr int DW_STAGES = 9;    // input rows in flight per warp (a multiple of 3: see the row loop)
 constexpr int DW_BOX_BYTES = 4 * 2 * DW_CH * 2;  // 4 pixels x {value, gate} x 64 channels x bf16 = 1 KiB
@@ -102,7 +103,7 @@ __device__ __forceinline__ uint32_t glu_pair(u64 a2, u64 g2) {
   return pack_bf16(o0, o1);
 }
 
-__global__ void __launch_bounds__(DW_THREADS, 2)
+__global__ void __launch_bounds__(DW_THREADS, DW_CTAS_PER_SM)
 dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmTop,
                        const __grid_constant__ CUtensorMap tmBot, const DwArgs p) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -400,10 +401,15 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
       if (rc) return rc;
     }
     const int64_t gx = ceil_div(hid, DW_CH), gy = ceil_div(W, DW_TW);
-    // rows per warp: long segments amortise the two halo rows; shorten them until the grid
-    // covers the device a few times over.
-    int seg = 32;
-    while (seg > 4 && gx * gy * ceil_div(rows, seg) < 4 * (int64_t)sm_count()) seg >>= 1;
+    // rows per warp: long segments amortise the two halo rows and the warp's set-up; shorten them
+    // until the grid covers the device a few times over.
+    // (a warp's set-up - 36 weight loads, 9 row fetches - costs about ten rows of work)
+    const int64_t slots = (int64_t)sm_count() * DW_CTAS_PER_SM;
+    // measured at 1.6B width: 128-256 rows per warp are 17 % faster than 32 as long as at least
+    // four waves of CTAs remain
+    int seg = 256;
+    while (seg > 32 && gx * gy * ceil_div(rows, seg) < 4 * slots) seg >>= 1;
+    while (seg > 4 && gx * gy * ceil_div(rows, seg) < 2 * slots) seg >>= 1;
     a.seg_rows = seg;
     const int64_t gz = ceil_div(rows, seg);
     SANA_REQUIRE(gy < 65536 && gz < 65536, "sana_dwconv_glu: grid too large");
