@@ -22,7 +22,8 @@ constexpr int DW_TW = 2 * DW_WARPS;  // output columns per CTA (two per warp)
 constexpr int DW_THREADS = 32 * DW_WARPS;
 constexpr int DW_CTAS_PER_SM = 16 / DW_WARPS;  // 16 resident warps (register-limited)
 constexpr int DW_CH = 64;       // value channels per warp (and as many gate channels)
-constexpr int DW_STAGES = 9;    // input rows in flight per warp (a multiple of 3: see the row loop)
+constexpr int DW_STAGES = 9;    // input rows in flight per warp
+constexpr int DW_SLOTS = DW_STAGES / 3;  // the ring is filled and drained three rows at a time
 constexpr int DW_BOX_BYTES = 4 * 2 * DW_CH * 2;  // 4 pixels x {value, gate} x 64 channels x bf16 = 1 KiB
 constexpr int DW_RING_BYTES = DW_WARPS * DW_STAGES * DW_BOX_BYTES;
 constexpr int DW_SMEM_BYTES = DW_RING_BYTES + DW_WARPS * DW_STAGES * 8;
@@ -104,8 +105,9 @@ __device__ __forceinline__ uint32_t glu_pair(u64 a2, u64 g2) {
 }
 
 __global__ void __launch_bounds__(DW_THREADS, DW_CTAS_PER_SM)
-dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmTop,
-                       const __grid_constant__ CUtensorMap tmBot, const DwArgs p) {
+dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU3, const __grid_constant__ CUtensorMap tmU,
+                       const __grid_constant__ CUtensorMap tmTop, const __grid_constant__ CUtensorMap tmBot,
+                       const DwArgs p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int x = blockIdx.y * DW_TW + 2 * warp;  // this warp's columns: x, x + 1
@@ -118,10 +120,11 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
   const int cw = min(c0, p.hid - 2);
 
   const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * DW_STAGES * DW_BOX_BYTES);
+  // the ring is refilled in slots of three rows (one trip of the row loop), one barrier per slot
   const uint32_t bars = smem_u32(smem) + (uint32_t)(DW_RING_BYTES + warp * DW_STAGES * 8);
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < DW_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    for (int s = 0; s < DW_SLOTS; ++s) mbar_init(bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
@@ -133,32 +136,41 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
   const bool need_top = fr_top != p.H - 1;
   const bool need_bot = (int)((p.row0 + ye) % p.H) != 0;
 
-  // lane 0: fetch the row of slot k into ring box `slot`.  A row that does not exist (frame
-  // edge) is never waited for, but its barrier phase is completed all the same so that the
-  // parity of the box's later uses stays in step.
-  auto issue_row = [&](int k, int slot) {
-    if (k >= nin) return;
-    const CUtensorMap* tm = &tmU;
-    int r = ys - 1 + k;
-    if (k == 0) {
-      if (!need_top) {
-        mbar_arrive(bars + 8 * slot);
-        return;
-      }
-      if (ys == 0) tm = &tmTop, r = 0;
-    } else if (k == nin - 1) {
-      if (!need_bot) {
-        mbar_arrive(bars + 8 * slot);
-        return;
-      }
-      if (ye >= p.rows) tm = &tmBot, r = 0;
+  // does input slot k hold a row? (the halo slots at both ends only inside a frame)
+  auto exists = [&](int k) { return k < nin && (k != 0 || need_top) && (k != nin - 1 || need_bot); };
+  // lane 0: fetch input slots kk, kk+1, kk+2 into ring slot `slot` (three boxes of 1 KiB).  Rows
+  // strictly inside the segment come as one three-row copy; a slot that touches the halo slots
+  // is fetched row by row from whichever tensor holds each row.  A slot without any row is never
+  // waited for, but its barrier phase is completed all the same so that the parity of later
+  // passes stays in step.
+  auto refill = [&](int kk, int slot) {
+    if (kk >= nin) return;
+    const uint32_t bar = bars + 8 * slot, dst = ring + slot * (3 * DW_BOX_BYTES);
+    if (kk >= 1 && kk + 2 <= nin - 2) {
+      mbar_expect_tx(bar, 3 * DW_BOX_BYTES);
+      tma_load_4d(dst, &tmU3, bar, cbase, 0, x - 1, ys - 1 + kk);
+      return;
     }
-    mbar_expect_tx(bars + 8 * slot, DW_BOX_BYTES);
-    tma_load_4d(ring + slot * DW_BOX_BYTES, tm, bars + 8 * slot, cbase, 0, x - 1, r);
+    int n = 0;
+    for (int j = 0; j < 3; ++j) n += exists(kk + j) ? 1 : 0;
+    if (n == 0) {
+      mbar_arrive(bar);
+      return;
+    }
+    mbar_expect_tx(bar, n * DW_BOX_BYTES);
+    for (int j = 0; j < 3; ++j) {
+      const int k = kk + j;
+      if (!exists(k)) continue;
+      const CUtensorMap* tm = &tmU;
+      int r = ys - 1 + k;
+      if (k == 0 && ys == 0) tm = &tmTop, r = 0;
+      if (k == nin - 1 && ye >= p.rows) tm = &tmBot, r = 0;
+      tma_load_4d(dst + j * DW_BOX_BYTES, tm, bar, cbase, 0, x - 1, r);
+    }
   };
   if (lane == 0) {
 #pragma unroll 1
-    for (int k = 0; k < DW_STAGES; ++k) issue_row(k, k);
+    for (int s = 0; s < DW_SLOTS; ++s) refill(3 * s, s);
   }
 
   // taps as packed pairs: w2[tap][0] = value channels (c, c+1), w2[tap][1] = gate channels
@@ -252,15 +264,14 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
   // must share the frame.
   //
   // General step: any k, including the halo slots at both ends of the segment.
-  auto step_any = [&](int k, int slot, uint32_t parity, auto PREVc, auto CURc, auto NEXTc) {
+  auto step_any = [&](int k, int row_slot, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
     const bool first = (k == 0), last = (k == nin - 1);
     const bool have = first ? need_top : (last ? need_bot : true);
     bool started = false;
     if (have) {
-      dw_wait(bars + 8 * slot, parity);
       u64 col[4][2];
-      load_cols(ring_lane + slot * DW_BOX_BYTES, col);
+      load_cols(ring_lane + row_slot * DW_BOX_BYTES, col);
       if (k >= 2 && fr != 0) taps(acc[PREV], col, 2);  // output r-1 is inside the segment
       if (!first && !last) taps(acc[CUR], col, 1);
       if (k + 2 < nin && fr != p.H - 1) {  // output r+1 is inside the segment
@@ -270,60 +281,48 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_con
     }
     if (k >= 2) emit(acc[PREV]);  // output row r-1 = ys + k - 2 is complete
     if (!started) restart(acc[NEXT]);
-    // every lane has consumed the box (its values sit in accumulators): lane 0 may refill it
-    __syncwarp();
-    if (lane == 0) issue_row(k + DW_STAGES, slot);
     advance();
   };
   // Interior step away from frame edges: 2 <= k <= nin-3 and the input row is neither the
-  // first nor the last of its frame, so the row exists, all three outputs take it and the
-  // refill (slot k + DW_STAGES) is never the top halo.  One branch-free block - the FMAs, the
-  // conversions and the previous row's GLU - which is what lets the few resident warps overlap
-  // their fixed-latency dependencies.
-  auto step_mid = [&](int k, int slot, uint32_t parity, auto PREVc, auto CURc, auto NEXTc) {
+  // first nor the last of its frame, so the row exists and all three outputs take it.  One
+  // branch-free block - the FMAs, the conversions and the previous row's GLU - which is what
+  // lets the few resident warps overlap their fixed-latency dependencies.
+  auto step_mid = [&](int row_slot, auto PREVc, auto CURc, auto NEXTc) {
     constexpr int PREV = decltype(PREVc)::value, CUR = decltype(CURc)::value, NEXT = decltype(NEXTc)::value;
-    dw_wait(bars + 8 * slot, parity);
     u64 col[4][2];
-    load_cols(ring_lane + slot * DW_BOX_BYTES, col);
+    load_cols(ring_lane + row_slot * DW_BOX_BYTES, col);
     taps(acc[PREV], col, 2);
     taps(acc[CUR], col, 1);
     taps_start(acc[NEXT], col);
     emit(acc[PREV]);
-    __syncwarp();
-    if (lane == 0) {
-      const int kk = k + DW_STAGES;
-      if (kk < nin - 1) {
-        mbar_expect_tx(bars + 8 * slot, DW_BOX_BYTES);
-        tma_load_4d(ring + slot * DW_BOX_BYTES, &tmU, bars + 8 * slot, cbase, 0, x - 1, ys - 1 + kk);
-      } else if (kk == nin - 1) {
-        issue_row(kk, slot);
-      }
-    }
     advance();
   };
 
   using I0 = std::integral_constant<int, 0>;
   using I1 = std::integral_constant<int, 1>;
   using I2 = std::integral_constant<int, 2>;
-  static_assert(DW_STAGES % 3 == 0, "a trip of three steps must not straddle the end of the ring");
-  // Trips of three steps keep the accumulator rotation (k mod 3) compile-time; the ring box
-  // advances by three per trip.  A trip whose three rows are all interior and away from frame
-  // edges runs the lean steps, any other trip the general ones.
+  // Trips of three steps keep the accumulator rotation (k mod 3) compile-time and match the
+  // ring's slots: one wait before the trip, one refill after it.  A trip whose three rows are
+  // all interior and away from frame edges runs the lean steps, any other trip the general ones.
   int slot = 0;
   uint32_t par = 0u;  // parity of ring pass k / DW_STAGES
 #pragma unroll 1
   for (int k = 0; k < nin; k += 3) {
+    if (exists(k) || exists(k + 1) || exists(k + 2)) dw_wait(bars + 8 * slot, par);
+    const int rs = 3 * slot;
     if (k >= 2 && k + 2 <= nin - 3 && fr >= 1 && fr + 2 <= p.H - 2) {
-      step_mid(k, slot, par, I0{}, I1{}, I2{});
-      step_mid(k + 1, slot + 1, par, I1{}, I2{}, I0{});
-      step_mid(k + 2, slot + 2, par, I2{}, I0{}, I1{});
+      step_mid(rs, I0{}, I1{}, I2{});
+      step_mid(rs + 1, I1{}, I2{}, I0{});
+      step_mid(rs + 2, I2{}, I0{}, I1{});
     } else {
-      step_any(k, slot, par, I0{}, I1{}, I2{});
-      if (k + 1 < nin) step_any(k + 1, slot + 1, par, I1{}, I2{}, I0{});
-      if (k + 2 < nin) step_any(k + 2, slot + 2, par, I2{}, I0{}, I1{});
+      step_any(k, rs, I0{}, I1{}, I2{});
+      if (k + 1 < nin) step_any(k + 1, rs + 1, I1{}, I2{}, I0{});
+      if (k + 2 < nin) step_any(k + 2, rs + 2, I2{}, I0{}, I1{});
     }
-    slot += 3;
-    if (slot == DW_STAGES) slot = 0, par ^= 1u;
+    // every lane has consumed the slot (its values sit in accumulators): lane 0 may refill it
+    __syncwarp();
+    if (lane == 0) refill(k + DW_STAGES, slot);
+    if (++slot == DW_SLOTS) slot = 0, par ^= 1u;
   }
 }
 
@@ -384,13 +383,19 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
     a.out = static_cast<__nv_bfloat16*>(out);
     a.rows = (int)rows, a.W = (int)W, a.H = (int)H, a.hid = (int)hid, a.row0 = row0;
     // u as a 4-D tensor {channel, value/gate, x, row}; a box is 64 channels x 2 groups x 4 pixels of one row
-    CUtensorMap tmU, tmTop, tmBot;
+    CUtensorMap tmU3, tmU, tmTop, tmBot;
     const uint64_t strides[3] = {(uint64_t)hid * 2, (uint64_t)hid * 4, (uint64_t)W * hid * 4};
     const uint32_t box[4] = {DW_CH, 2, 4, 1};
     const uint64_t dims_u[4] = {(uint64_t)hid, 2, (uint64_t)W, (uint64_t)rows};
     const uint64_t dims_1[4] = {(uint64_t)hid, 2, (uint64_t)W, 1};
+    const uint32_t box3[4] = {DW_CH, 2, 4, 3};
     int rc = make_tmap_tiled(&tmU, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, u, dims_u, strides, box, false);
     if (rc) return rc;
+    tmU3 = tmU;  // with fewer than three rows the three-row copy is never issued
+    if (rows >= 3) {
+      rc = make_tmap_tiled(&tmU3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, u, dims_u, strides, box3, false);
+      if (rc) return rc;
+    }
     tmTop = tmU, tmBot = tmU;
     if (halo_top) {
       rc = make_tmap_tiled(&tmTop, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, halo_top, dims_1, strides, box, false);
@@ -419,7 +424,7 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dwconv_glu)");
       attr_set = true;
     }
-    dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, DW_SMEM_BYTES, st>>>(tmU, tmTop, tmBot, a);
+    dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, DW_SMEM_BYTES, st>>>(tmU3, tmU, tmTop, tmBot, a);
   } else if (dtype == SANA_F32) {
     const int64_t total = rows * W * hid;
     dwconv_glu_f32_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
