@@ -378,7 +378,9 @@ def main() -> None:
     stack.set_sequence_shard(shard)
     fused_exchange = shard is not None and world > 1 and not args.nccl_exchange
     if fused_exchange:
+        shard.device_steps = bool(args.graph)  # the exchange kernels number their own steps under graph replay
         shard.enable_fused_state_exchange(1, C // 32, dev)
+        shard.enable_fused_halo_exchange(SEQPAR_GRID[2] * 2 * HID, dt, dev)
     stack.set_nvfp4(nvfp4)
 
     # host-resident inputs (pinned) for the end-to-end leg; device copies for the kernel leg
@@ -402,8 +404,8 @@ def main() -> None:
     if args.graph:
         from sana_b200.graphs import GraphedForward
 
-        if shard is not None and world > 1:
-            raise SystemExit("--graph is not offered with the fused state exchange (its step counter is a launch argument)")
+        if shard is not None and world > 1 and args.nccl_exchange:
+            raise SystemExit("--graph needs the peer-memory exchanges (drop --nccl-exchange)")
         eager = forward
         graphed = GraphedForward(lambda a, b, c: eager(a, b, c), x_d, y_d, t_d)
         forward = lambda xd, yd, td: graphed(xd, yd, td)  # noqa: E731
@@ -486,7 +488,8 @@ def main() -> None:
                        "l2": "inputs larger than L2 (>3 GB of weights and activations per step)",
                        "cross_attention_core": ("own warp-MMA flash kernel" if args.cross_attn_kernel else
                                                 "torch SDPA / cuDNN flash (own kernel: --cross-attn-kernel)"),
-                       "state_exchange": ("fused into the reduction kernel over peer memory" if fused_exchange else
+                       "state_exchange": ("state all-reduce fused into the reduction kernel, conv halo rows pushed by one kernel, both "
+                                          "over peer memory" if fused_exchange else
                                           ("NCCL all-reduce" if shard is not None and world > 1 else "none"))},
             "roofline": {"bound": "tensor",
                          "kernel": ("gemm_nvfp4_tc_kernel + gemm_bf16_tc_kernel (tcgen05; FP4 and bf16 launches pooled, "

@@ -126,7 +126,9 @@ int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, float* state
  *     a block counter at byte 256, a soft-error word at byte 320 (non-zero = 1 + the rank that
  *     did not arrive within 2 s; the result of that step must be discarded), two state slots
  *     from byte 1024.
- *   step: 1, 2, 3, ... the same sequence on every rank, one per call on this buffer set.
+ *   step: 1, 2, 3, ... the same sequence on every rank, one per call on this buffer set; or 0
+ *     on every call of every rank: the kernel numbers the steps itself (a word in the buffer),
+ *     which lets the launch be captured in a CUDA graph and replayed.
  * Every rank must make the matching call; a rank waits inside the kernel (bounded) for the
  * others.  Launches on different GPUs only - never emulate several ranks on one GPU.
  */
@@ -134,6 +136,26 @@ int64_t sana_la_state_sp_buffer_bytes(int64_t B, int64_t H);
 int sana_la_state_sp(const void* k, const void* v, int64_t ld, float* state, void* workspace,
                      int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int dtype,
                      void* const* peer_buffers, int rank, int world, uint32_t step, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Conv halo rows of a row-sharded token grid over peer memory: this rank's first row of the
+ * depthwise conv's input goes into the upper neighbour's `bot` slot and its last row into the
+ * lower neighbour's `top` slot (remote stores), a release-store of the step number tells the
+ * neighbours, and the kernel returns once their rows have arrived here (bounded wait, 2 s;
+ * soft-error word at byte 20 of the buffer: 1 = upper, 2 = lower neighbour missing).  No
+ * counterpart upstream; replaces two NCCL send/recv pairs per block.
+ *   first_row / last_row: [row_bytes] device rows (may be null when that neighbour is null).
+ *   mine / upper / lower: exchange buffers of this rank and of ranks -1 / +1 as mapped into this
+ *     process (peer / symmetric memory; null where no neighbour shares a frame),
+ *     sana_halo_exchange_buffer_bytes(row_bytes) each, zero-filled once before the first step.
+ *     After the call `top` is at mine + 1024 and `bot` at mine + 1024 + row_bytes.
+ *   step: as in sana_la_state_sp (1, 2, 3, ... on every rank, or 0 everywhere for graph replay).
+ * One slot per side suffices because every block runs a sana_la_state_sp exchange between two
+ * halo exchanges.  Launches on different GPUs only.
+ */
+int64_t sana_halo_exchange_buffer_bytes(int64_t row_bytes);
+int sana_halo_exchange(const void* first_row, const void* last_row, int64_t row_bytes, void* mine, void* upper,
+                       void* lower, uint32_t step, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * ReLU linear attention, apply + normalise:

@@ -52,6 +52,8 @@ SIGNATURES = {
     "sana_la_state_sp_buffer_bytes": (_i64, [_i64, _i64]),
     "sana_la_state_sp": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, C.POINTER(C.c_void_p), _i32, _i32,
                                 C.c_uint32, _vp]),
+    "sana_halo_exchange_buffer_bytes": (_i64, [_i64]),
+    "sana_halo_exchange": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, C.c_uint32, _vp]),
     "sana_la_apply": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_cross_attention": (_i32, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_dwconv_glu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

@@ -529,6 +529,9 @@ extern "C" int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, f
 // Every rank owns a buffer that all ranks of the node have mapped (peer / symmetric memory):
 //   [0, 256)     arrival flags: word r = last step whose state rank r has published to us
 //   [256, 260)   block counter of the local launch      [320, 324) soft-error word
+//   [260, 264)   exit counter, [264, 268) number of the last completed step (step = 0 in the call
+//                means "the next one": the kernel numbers its steps itself, so that the same launch
+//                can be replayed from a CUDA graph)
 //   [1024, ...)  two state slots (step parity) of `slot_elems` floats
 // One launch per step: phase A sums this rank's chunk partials into its own slot; the last
 // block to finish writes `step` into its flag word on every peer (remote 4-byte stores).
@@ -576,7 +579,10 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
   __shared__ int wait_failed;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   unsigned char* mine = pg.base[pg.rank];
-  const int64_t slot_off = SP_HEADER_BYTES + (int64_t)(pg.step & 1u) * pg.slot_elems * (int64_t)sizeof(float);
+  // the step word only changes when the last block of a launch exits, so every block of this
+  // launch reads the same value
+  const uint32_t step = pg.step ? pg.step : *reinterpret_cast<volatile uint32_t*>(mine + 264) + 1u;
+  const int64_t slot_off = SP_HEADER_BYTES + (int64_t)(step & 1u) * pg.slot_elems * (int64_t)sizeof(float);
   float* my_slot = reinterpret_cast<float*>(mine + slot_off);
   // ---- phase A: fixed-order sum of this rank's chunk partials, published in its slot
   float s = 0.f;
@@ -596,14 +602,14 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
       *counter = 0u;
       __threadfence_system();
       for (int r = 0; r < pg.world; ++r)
-        if (r != pg.rank) st_release_sys_u32(reinterpret_cast<uint32_t*>(pg.base[r]) + pg.rank, pg.step);
+        if (r != pg.rank) st_release_sys_u32(reinterpret_cast<uint32_t*>(pg.base[r]) + pg.rank, step);
     }
     // ---- phase B: wait for every peer's slot of this step (flags arrive in our own memory)
     const long long t0 = global_ns();
     for (int r = 0; r < pg.world && !wait_failed; ++r) {
       if (r == pg.rank) continue;
       const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + r;
-      while ((int32_t)(ld_acquire_sys_u32(flag) - pg.step) < 0) {
+      while ((int32_t)(ld_acquire_sys_u32(flag) - step) < 0) {
         if (global_ns() - t0 > SP_WAIT_LIMIT_NS) {
           wait_failed = 1;
           atomicExch(reinterpret_cast<int*>(mine + 320), 1 + r);  // which peer we gave up on
@@ -623,6 +629,13 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
     }
     state[idx] = acc;
   }
+  if (threadIdx.x == 0) {  // the last block to leave records the step as completed
+    unsigned int* exits = reinterpret_cast<unsigned int*>(mine + 260);
+    if (atomicAdd(exits, 1u) == gridDim.x - 1) {
+      *exits = 0u;
+      *reinterpret_cast<volatile uint32_t*>(mine + 264) = step;
+    }
+  }
 }
 
 }  // namespace sana
@@ -639,7 +652,6 @@ extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float*
   SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_state_sp: B, N, H must be positive");
   SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_state_sp: size out of range");
   SANA_REQUIRE(world >= 1 && world <= SP_MAX_WORLD && rank >= 0 && rank < world, "sana_la_state_sp: bad rank / world");
-  SANA_REQUIRE(step >= 1, "sana_la_state_sp: steps count from 1 (flags start at 0)");
   SANA_REQUIRE(ld >= H * HD && ld % 8 == 0, "sana_la_state_sp: ld must be >= H*32 and a multiple of 8");
   SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(state) && aligned16(workspace), "sana_la_state_sp: alignment");
   SANA_REQUIRE(workspace_bytes >= sana_la_state_workspace_bytes(B, N, H), "sana_la_state_sp: workspace too small");

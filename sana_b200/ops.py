@@ -221,6 +221,25 @@ def la_state_sp(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int, peer_p
     return state
 
 
+def halo_exchange_buffer_bytes(row_bytes: int) -> int:
+    return _lib.load().sana_halo_exchange_buffer_bytes(row_bytes)
+
+
+def halo_exchange(first_row: Optional[torch.Tensor], last_row: Optional[torch.Tensor], row_bytes: int, mine: int,
+                  upper: Optional[int], lower: Optional[int], step: int) -> None:
+    """Pushes this rank's boundary rows into the neighbours' halo slots over peer memory and
+    waits for theirs (see sana_halo_exchange).  ``mine`` / ``upper`` / ``lower`` are device
+    addresses of the exchange buffers (None where there is no neighbour in the same frame)."""
+    _need_cuda(first_row, last_row)
+    for r in (first_row, last_row):
+        if r is not None and (not r.is_contiguous() or r.numel() * r.element_size() != row_bytes):
+            raise SanaLibraryError("halo_exchange: rows must be contiguous and row_bytes long")
+    _lib.check(_lib.load().sana_halo_exchange(first_row.data_ptr() if first_row is not None else None,
+                                              last_row.data_ptr() if last_row is not None else None, row_bytes, mine,
+                                              upper, lower, step, _stream()), "sana_halo_exchange")
+    counters.launches += 1
+
+
 def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """o[b,n,h,:] = state[b,h,:32] relu(q) / (state[b,h,32] . relu(q) + eps); q [B*N, H*32] view."""

@@ -144,6 +144,43 @@ class SequenceShard:
     def fused_state_exchange(self) -> bool:
         return getattr(self, "_sp_ptrs", None) is not None
 
+    def enable_fused_halo_exchange(self, row_elems: int, dtype: torch.dtype, device) -> None:
+        """Allocates this rank's halo buffer in symmetric memory and maps the neighbours', so
+        that `exchange_halo` moves the conv halo rows with one kernel over peer memory
+        (`ops.halo_exchange`) instead of NCCL send/recv.  ``row_elems`` = W * 2 * hid elements of
+        ``dtype`` per image row.  Collective over the group; call once on every rank."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import ops
+
+        row_bytes = row_elems * torch.empty((), dtype=dtype).element_size()
+        buf = symm_mem.empty(ops.halo_exchange_buffer_bytes(row_bytes), dtype=torch.uint8, device=device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        self._halo_buf, self._halo_handle = buf, hdl
+        self._halo_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._halo_row = (row_elems, dtype, row_bytes)
+        self._halo_step = 0
+
+    @property
+    def fused_halo_exchange(self) -> bool:
+        return getattr(self, "_halo_ptrs", None) is not None
+
+    def fused_halo_status(self) -> int:
+        """Soft-error word of the halo kernel (0 = every wait completed).  Synchronises."""
+        return int(self._halo_buf[20:24].view(torch.int32).item())
+
+    # With `device_steps` the exchange kernels number their steps themselves (a word in the
+    # exchange buffer) instead of taking the number as a launch argument: required for CUDA-graph
+    # replay, where the host does not run between steps.  Set it on every rank or on none.
+    device_steps: bool = False
+
     def fused_state(self, k: torch.Tensor, v: torch.Tensor, B: int, heads: int) -> torch.Tensor:
         """State of the whole sequence from this rank's k, v (fused reduction + all-reduce)."""
         from . import ops
@@ -151,7 +188,8 @@ class SequenceShard:
         if (B, heads) != self._sp_shape:
             raise ValueError(f"fused exchange was sized for (B, heads) = {self._sp_shape}, got {(B, heads)}")
         self._sp_step += 1
-        return ops.la_state_sp(k, v, B, self.tokens, heads, self._sp_ptrs, self.rank, self.world, self._sp_step)
+        return ops.la_state_sp(k, v, B, self.tokens, heads, self._sp_ptrs, self.rank, self.world,
+                               0 if self.device_steps else self._sp_step)
 
     def fused_exchange_status(self) -> int:
         """Soft-error word of the exchange kernel (0 = every wait completed).  Synchronises."""
@@ -168,6 +206,19 @@ class SequenceShard:
         """u [rows*W, C2] local rows.  Returns (halo_top, halo_bot) = the neighbour's last /
         first row ([W, C2]) where that row is in the same frame, else None."""
         W = self.W
+        if self.world > 1 and self.fused_halo_exchange:
+            from . import ops as K
+
+            row_elems, dtype, row_bytes = self._halo_row
+            if W * u.shape[1] != row_elems or u.dtype != dtype:
+                raise ValueError("fused halo exchange was sized for another row")
+            up = self._halo_ptrs[self.rank - 1] if self.needs_top() else None
+            down = self._halo_ptrs[self.rank + 1] if self.needs_bot() else None
+            self._halo_step += 1
+            K.halo_exchange(u[:W].reshape(-1) if up else None, u[-W:].reshape(-1) if down else None, row_bytes,
+                            self._halo_ptrs[self.rank], up, down, 0 if self.device_steps else self._halo_step)
+            rows = self._halo_buf[1024:1024 + 2 * row_bytes].view(dtype).view(2, W, u.shape[1])
+            return (rows[0] if up else None), (rows[1] if down else None)
         top = torch.empty(W, u.shape[1], dtype=u.dtype, device=u.device) if self.needs_top() else None
         bot = torch.empty(W, u.shape[1], dtype=u.dtype, device=u.device) if self.needs_bot() else None
         if self.world == 1:

@@ -177,6 +177,65 @@ def _fused_exchange_vs_nccl(rank, world):
     return {"worst": worst, "same": same, "status": sh.fused_exchange_status(), "first": first}
 
 
+def _fused_halo_and_graph(rank, world):
+    """Sharded block with both exchanges over peer memory (state all-reduce fused into the
+    reduction kernel, conv halo rows pushed by the halo kernel) against the NCCL paths, then
+    the same block replayed from one CUDA graph with the kernels numbering their own steps."""
+    import sana_b200
+    from sana_b200 import sharding, synthetic
+    from sana_b200.graphs import GraphedForward
+
+    dev, dt = torch.device("cuda", rank), torch.bfloat16
+    C, heads, grid = 512, 8, (2, 11, 16)  # 22 rows: the cut at row 11 is a frame boundary for world 2 ...
+    out = {}
+    for name, g in (("frame_cut", (2, 11, 16)), ("inner_cut", (1, 22, 16))):  # ... and inside a frame here
+        shp = synthetic.BlockShape("sp", C, heads, 1, g, text_len=24)
+        params = synthetic.make_block_params(C, shp.ffn_hidden, seed=3, std=0.05)
+        x, y, t = synthetic.make_block_inputs(shp, seed=3, std=0.05, text_dim=64)
+        blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+        blk.load_state_dict(params, strict=True)
+        blk = blk.to(dev, dt)
+        yd, td = y.to(dev, dt), t.to(dev, dt)
+        sh = sharding.SequenceShard(*g, rank, world)
+        blk.set_sequence_shard(sh)
+        xs = sh.scatter_tokens(x.to(dev, dt))
+        ref = [blk(xs * (1.0 + 0.25 * i), yd, td, None, g) for i in range(3)]  # NCCL all-reduce + send/recv
+        sh.enable_fused_state_exchange(1, blk.attn.heads, dev)
+        sh.enable_fused_halo_exchange(g[2] * 2 * shp.ffn_hidden, dt, dev)
+        worst = 0.0
+        for i in range(3):
+            a = blk(xs * (1.0 + 0.25 * i), yd, td, None, g)
+            worst = max(worst, ((a.float() - ref[i].float()).abs().max() / ref[i].float().abs().max()).item())
+        torch.cuda.synchronize()
+        dist.barrier()
+        # graph replay: fresh shard state so that every rank starts the device-side numbering together
+        sh2 = sharding.SequenceShard(*g, rank, world, device_steps=True)
+        blk.set_sequence_shard(sh2)
+        sh2.enable_fused_state_exchange(1, blk.attn.heads, dev)
+        sh2.enable_fused_halo_exchange(g[2] * 2 * shp.ffn_hidden, dt, dev)
+        fwd = GraphedForward(lambda a: blk(a, yd, td, None, g), xs)
+        gworst = 0.0
+        for i in range(3):
+            a = fwd(xs * (1.0 + 0.25 * i))
+            gworst = max(gworst, ((a.float() - ref[i].float()).abs().max() / ref[i].float().abs().max()).item())
+        torch.cuda.synchronize()
+        out[name] = {"worst": worst, "graph_worst": gworst, "halo_status": sh.fused_halo_status() + sh2.fused_halo_status(),
+                     "state_status": sh.fused_exchange_status() + sh2.fused_exchange_status()}
+        dist.barrier()
+    return out
+
+
+def test_fused_halo_exchange_and_graph_replay_on_two_gpus():
+    _need(2)
+    res = _run(2, _fused_halo_and_graph)
+    assert len(res) == 2, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        for name, p in payload.items():
+            assert p["halo_status"] == 0 and p["state_status"] == 0, (name, p)
+            assert p["worst"] < 2e-3 and p["graph_worst"] < 2e-3, (name, p)  # only the state summation order differs
+
+
 def test_fused_state_exchange_matches_nccl_on_two_gpus():
     _need(2)
     res = _run(2, _fused_exchange_vs_nccl)
