@@ -74,6 +74,15 @@ int sana_ln_modulate_rows(const void* x, const void* table, const void* t, void*
 int sana_rmsnorm(const void* x, int64_t ldx, const void* weight, void* y, int64_t ldy, int64_t rows,
                  int64_t C, float eps, int dtype, void* stream);
 
+/* Rotary embedding of q or k, in place, before the ReLU feature map: replaces
+ * `apply_rotary_emb(q, rotary_emb, use_real_unbind_dim=-2)` in `LiteLA.forward`
+ * (sana_blocks.py:282-284 with :1549-1586): channel pairs (2i, 2i+1) of every head,
+ * y = x * cos + rot(x) * sin in fp32, rounded once to `dtype`.
+ *   x [B*N, C] view (row stride ld), e.g. the q or k column block of the qkv projection;
+ *   cos_table, sin_table [N, head_dim] fp32, indexed by the token's position inside its sample. */
+int sana_rope(void* x, int64_t ld, const float* cos_table, const float* sin_table, int64_t B, int64_t N, int64_t C,
+              int64_t head_dim, int dtype, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * ReLU linear attention, state reduction:
  *   state[b, h, i, j] = sum_n v1[b, n, h, i] * relu(k[b, n, h, j]),  v1 = [v ; 1]

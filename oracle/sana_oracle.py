@@ -81,10 +81,21 @@ def lite_la_attn_matmul(q, k, v, eps: float, fp32_attention: bool = True) -> tor
     return out[:, :, :-1] / (out[:, :, -1:] + eps)
 
 
+def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """apply_rotary_emb(..., use_real=True, use_real_unbind_dim=-2), sana_blocks.py:1549-1586:
+    x [B, h, D, S], cos / sin [S, D]."""
+    cos = cos[None, None].transpose(-1, -2)
+    sin = sin[None, None].transpose(-1, -2)
+    x_real, x_imag = x.reshape(*x.shape[:-2], -1, 2, x.shape[-1]).unbind(-2)  # [B, h, D/2, S]
+    x_rotated = torch.stack([-x_imag, x_real], dim=-2).flatten(2, 3)
+    return (x.float() * cos + x_rotated.float() * sin).to(x.dtype)
+
+
 def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, eps: float = 1e-15,
                     fp32_attention: bool = True, keep_dtype: bool = False, quant_fn=None,
-                    norm_eps: float = 1e-5) -> torch.Tensor:
-    """LiteLA.forward, diffusion/model/nets/sana_blocks.py:265-291 (qk_norm off, no rotary).
+                    norm_eps: float = 1e-5, rotary_emb=None) -> torch.Tensor:
+    """LiteLA.forward, diffusion/model/nets/sana_blocks.py:265-291; ``rotary_emb`` = (cos, sin)
+    [N, dim] rotates q and k before the ReLU (:282-284).
 
     ``p`` holds ``qkv.weight`` (+ optional ``qkv.bias``), ``proj.weight``, ``proj.bias``.
     ``keep_dtype`` runs the fp32_attention region in the input dtype instead of fp32 - used
@@ -105,6 +116,9 @@ def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, ep
     q = q.transpose(-1, -2).reshape(B, C // hd, hd, N)
     k = k.transpose(-1, -2).reshape(B, C // hd, hd, N)
     v = v.transpose(-1, -2).reshape(B, C // hd, hd, N)
+    if rotary_emb is not None:
+        q = apply_rotary_emb(q, rotary_emb[0], rotary_emb[1])
+        k = apply_rotary_emb(k, rotary_emb[0], rotary_emb[1])
     out = lite_la_attn_matmul(q, k.transpose(-1, -2), v, eps, fp32_attention and not keep_dtype).to(dtype)
     out = out.view(B, C, N).permute(0, 2, 1)
     return F.linear(qf(out), qf(p["proj.weight"]), p["proj.bias"])
@@ -183,7 +197,7 @@ def cross_attention_forward(x, cond, p: Params, num_heads: int, mask=None) -> to
 
 def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int], mask=None,
                           linear_head_dim: int = 32, fp32_attention: bool = True,
-                          keep_dtype: bool = False, return_branches: bool = False, quant_fn=None):
+                          keep_dtype: bool = False, return_branches: bool = False, quant_fn=None, rotary_emb=None):
     """SanaMSBlock.forward with attn_type="linear", ffn_type="glumbconv", drop_path 0,
     diffusion/model/nets/sana_multi_scale.py:145-157.
 
@@ -195,7 +209,8 @@ def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int],
     shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
     a = lite_la_forward(t2i_modulate(layer_norm(x), shift_msa, scale_msa), sub(p, "attn"),
                         heads=C // linear_head_dim, eps=BLOCK_LA_EPS,
-                        fp32_attention=fp32_attention, keep_dtype=keep_dtype, quant_fn=quant_fn)
+                        fp32_attention=fp32_attention, keep_dtype=keep_dtype, quant_fn=quant_fn,
+                        rotary_emb=rotary_emb)
     x = x + gate_msa * a
     x = x + cross_attention_forward(x, y, sub(p, "cross_attn"), num_heads, mask)
     f = glumbconv_forward(t2i_modulate(layer_norm(x), shift_mlp, scale_mlp), sub(p, "mlp"), HW, quant_fn=quant_fn)

@@ -46,6 +46,7 @@ SIGNATURES = {
     "sana_ln_modulate_rows": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32,
                                      _vp]),
     "sana_rmsnorm": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "sana_rope": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_la_state_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "sana_la_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_la_state_noalloc": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp]),

@@ -102,3 +102,65 @@ extern "C" int sana_rmsnorm(const void* x, int64_t ldx, const void* weight, void
   SANA_LAUNCH_CHECK("rmsnorm kernel");
   return SANA_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Rotary embedding on the q or k column block of a qkv projection, in place, before the ReLU
+// feature map: channel pairs (2i, 2i+1) of every 32-channel head are rotated with per-position
+// tables, y = x * cos + rot(x) * sin with rot(x)[2i] = -x[2i+1], rot(x)[2i+1] = x[2i]; fp32
+// arithmetic, one rounding on store.  One thread per channel pair.
+// ------------------------------------------------------------------------------------------
+namespace sana {
+
+template <typename T>
+__device__ __forceinline__ float rope_ld(const T* p);
+template <>
+__device__ __forceinline__ float rope_ld<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float rope_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void rope_st(T* p, float v);
+template <>
+__device__ __forceinline__ void rope_st<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void rope_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void rope_kernel(T* x, int64_t ld, const float* __restrict__ cosv, const float* __restrict__ sinv,
+                            int64_t rows, int N, int C, int D) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int half = C >> 1;
+  if (idx >= rows * half) return;
+  const int64_t row = idx / half;
+  const int c = (int)(idx - row * half) * 2;  // even channel of the pair
+  const int d = c % D;                       // position inside the head
+  const int64_t pos = row % N;
+  T* px = x + row * ld + c;
+  const float a = rope_ld(px), b = rope_ld(px + 1);
+  const float* cr = cosv + pos * D + d;
+  const float* sr = sinv + pos * D + d;
+  rope_st(px, a * cr[0] + (-b) * sr[0]);
+  rope_st(px + 1, b * cr[1] + a * sr[1]);
+}
+
+}  // namespace sana
+
+extern "C" int sana_rope(void* x, int64_t ld, const float* cos_table, const float* sin_table, int64_t B, int64_t N,
+                         int64_t C, int64_t head_dim, int dtype, void* stream) {
+  SANA_REQUIRE(x && cos_table && sin_table, "sana_rope: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && C > 0 && head_dim > 0, "sana_rope: sizes must be positive");
+  SANA_REQUIRE(head_dim % 2 == 0 && C % head_dim == 0, "sana_rope: C must be whole heads of an even dimension");
+  SANA_REQUIRE(ld >= C && N < ((int64_t)1 << 31) && C < ((int64_t)1 << 30), "sana_rope: bad stride or size");
+  const int64_t total = B * N * (C / 2);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)ceil_div(total, 256);
+  if (dtype == SANA_BF16)
+    rope_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(x), ld, cos_table, sin_table, B * N,
+                                                    (int)N, (int)C, (int)head_dim);
+  else if (dtype == SANA_F32)
+    rope_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(x), ld, cos_table, sin_table, B * N, (int)N, (int)C,
+                                            (int)head_dim);
+  else
+    return fail(SANA_ERR_UNSUPPORTED, "sana_rope: unsupported dtype %d", dtype);
+  SANA_LAUNCH_CHECK("rope kernel");
+  return SANA_OK;
+}

@@ -39,11 +39,15 @@ def _as2d(x: torch.Tensor) -> torch.Tensor:
 def _project(owner: nn.Module, key: str, x2d: torch.Tensor, w2d: torch.Tensor, **epilogue) -> torch.Tensor:
     """``x2d @ w2d.T`` with the fused epilogue of :func:`ops.gemm`.  When ``owner.nvfp4`` is set
     both operands are quantised to NVFP4 first: the activation on every call, the weight once
-    (cached on the module until the parameter is modified or moved)."""
+    (cached on the module until the parameter is modified or moved) - or never, when a packed
+    weight was installed by ``weight_pack.load_nvfp4_weights``."""
     if not getattr(owner, "nvfp4", False):
         return ops.gemm(x2d, w2d, **epilogue)
     if x2d.dtype != torch.bfloat16:
         raise NotImplementedError("NVFP4 projections take bf16 activations and weights")
+    packed = owner.__dict__.get("_nvfp4_packed")
+    if packed is not None and key in packed:
+        return ops.gemm_nvfp4(ops.nvfp4_quantize(x2d), packed[key], **epilogue)
     cache = owner.__dict__.setdefault("_nvfp4_weights", {})
     tag = (w2d.data_ptr(), w2d._version, tuple(w2d.shape))
     entry = cache.get(key)
@@ -106,12 +110,19 @@ class LiteLA(nn.Module):
         self.nvfp4 = False  # quantise the qkv / proj projections to NVFP4
 
     # -- pieces shared with the fused block path --------------------------------------------
-    def _core(self, qkv: torch.Tensor, B: int, N: int) -> torch.Tensor:
-        """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``)."""
+    def _core(self, qkv: torch.Tensor, B: int, N: int, rotary_emb=None) -> torch.Tensor:
+        """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``).
+        ``rotary_emb`` = (cos, sin), each [N, head_dim]: rotates q and k before the ReLU."""
         C = self.out_dim
         if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
             ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
             ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
+        if rotary_emb is not None:
+            if self.seq_shard is not None:
+                raise NotImplementedError("rotary embeddings on a sequence shard are not covered")
+            cos, sin = rotary_emb
+            ops.rope_(qkv[:, :C], cos, sin, B, N, self.dim)
+            ops.rope_(qkv[:, C:2 * C], cos, sin, B, N, self.dim)
         sh = self.seq_shard
         if sh is not None and sh.fused_state_exchange:
             # reduction kernel sums the ranks' partial states itself, over peer memory
@@ -136,11 +147,9 @@ class LiteLA(nn.Module):
         return o.to(dt).float().reshape(B, N, h, d).permute(0, 2, 3, 1).contiguous()
 
     def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_id=None, block_mask=None):
-        if rotary_emb is not None:
-            raise NotImplementedError("LiteLA with rotary embeddings is not covered by the CUDA kernels yet")
         B, N, C = x.shape
         qkv = _project(self, "qkv", _as2d(x), self.qkv.weight, bias=self.qkv.bias)
-        o = self._core(qkv, B, N)
+        o = self._core(qkv, B, N, rotary_emb)
         return _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
 
     @property
@@ -330,8 +339,6 @@ class SanaMSBlock(nn.Module):
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, HW=None, image_rotary_emb=None, **kwargs):
-        if image_rotary_emb is not None:
-            raise NotImplementedError("rotary embeddings are not covered by the CUDA kernels yet")
         B, N, C = x.shape
         x2 = _as2d(x.contiguous())
         table = self.scale_shift_table
@@ -347,7 +354,7 @@ class SanaMSBlock(nn.Module):
         else:
             z = ops.ln_modulate(x, table, t, 0, 1, LN_EPS)
             qkv = _project(attn, "qkv", _as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
-            o = attn._core(qkv, B, N)
+            o = attn._core(qkv, B, N, image_rotary_emb)
             x2 = _project(attn, "proj", o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
         o = ca._attend(x2, y, mask, B)
         x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)

@@ -178,6 +178,20 @@ def rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return x
 
 
+def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, head_dim: int = HEAD_DIM) -> torch.Tensor:
+    """In-place rotary embedding of a [B*N, C] view (q or k block of a qkv projection) with
+    per-position tables cos, sin [N, head_dim] (any float dtype; used in fp32).  Returns ``x``."""
+    _need_cuda(x, cos, sin)
+    rows, Cc, ld = _rows2d(x, "rope x")
+    if rows != B * N or tuple(cos.shape) != (N, head_dim) or tuple(sin.shape) != (N, head_dim):
+        raise SanaLibraryError(f"rope: expected x [{B * N}, C] and tables [{N}, {head_dim}]")
+    cf, sf = cos.to(torch.float32).contiguous(), sin.to(torch.float32).contiguous()
+    _lib.check(_lib.load().sana_rope(x.data_ptr(), ld, cf.data_ptr(), sf.data_ptr(), B, N, Cc, head_dim,
+                                     _dtype_code(x.dtype), _stream()), "sana_rope")
+    counters.launches += 1
+    return x
+
+
 def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.Tensor:
     """state[b,h,i,j] = sum_n [v;1][b,n,h,i] * relu(k[b,n,h,j]); k, v are [B*N, H*32] views
     (e.g. column slices of the qkv projection).  Returns fp32 [B, H, 33, 32]."""

@@ -36,7 +36,7 @@ def _block(R, C, heads, params, dtype):
     return blk.to(dtype)
 
 
-def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False, qk_norm=False):
+def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False, qk_norm=False, rope=False):
     hid = int(C * 2.5)
     shape = synthetic.BlockShape(name, C, heads, B, tuple(HW), text_len=L)
     params = synthetic.make_block_params(C, hid, seed, std=0.05)
@@ -52,6 +52,12 @@ def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False, qk_norm
             mask[b, L - 1 - b:] = 0
     out = {"C": C, "heads": heads, "B": B, "HW": tuple(HW), "L": L, "params": params, "x": x, "y": y, "t": t,
            "mask": mask}
+    rot = None
+    if rope:  # per-position rotation tables [N, 32] (any angles; pairs need not share an angle upstream)
+        g = torch.Generator().manual_seed(2000 + seed)
+        ang = torch.rand(shape.tokens, 32, generator=g) * 6.28
+        rot = (torch.cos(ang), torch.sin(ang))
+        out["rope_cos"], out["rope_sin"] = rot
     with torch.no_grad():
         for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
             blk = _block(R, C, heads, params, dt)
@@ -60,10 +66,10 @@ def small_block_case(R, name, C, heads, B, HW, L, seed, with_mask=False, qk_norm
             mod = (blk.scale_shift_table[None] + tt.reshape(B, 6, -1)).chunk(6, dim=1)
             z1 = R.t2i_modulate(blk.norm1(xx), mod[0], mod[1])
             out[f"attn_in_{tag}"] = z1
-            out[f"attn_out_{tag}"] = blk.attn(z1, HW=tuple(HW))
+            out[f"attn_out_{tag}"] = blk.attn(z1, HW=tuple(HW), rotary_emb=rot)
             out[f"mlp_out_{tag}"] = blk.mlp(z1, HW=tuple(HW))  # GLUMBConv on the same modulated input
             out[f"cross_out_{tag}"] = blk.cross_attn(xx, yy, mask)
-            out[f"block_out_{tag}"] = blk(xx, yy, tt, mask, tuple(HW))
+            out[f"block_out_{tag}"] = blk(xx, yy, tt, mask, tuple(HW), rot)
     return out
 
 
@@ -172,6 +178,7 @@ def main():
         "small_block_masked": lambda: small_block_case(R, "m", 64, 2, 2, (4, 7), 11, seed=2, with_mask=True),
         "small_block_video": lambda: video_case(R),
         "small_block_qknorm": lambda: small_block_case(R, "q", 64, 4, 2, (5, 6), 8, seed=4, with_mask=True, qk_norm=True),
+        "small_block_rope": lambda: small_block_case(R, "r", 64, 4, 2, (4, 6), 8, seed=6, rope=True),
         "litela_cfg1": lambda: litela_cfg1_case(R),
         "block_cfg2": lambda: block_cfg2_case(R),
         "sana_ms_small": lambda: sana_ms_case(R),

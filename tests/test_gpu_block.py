@@ -247,3 +247,27 @@ def test_sequence_shards_emulated_on_one_gpu():
         assert torch.equal(torch.cat(outs), g_full)
     ref = _golden_on_rounded(x, y, t, params, heads, shp.grid, None, dt)
     assert nmax_err(full, ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_block_with_rotary_embedding(golden, dt, tol):
+    """q and k rotated before the ReLU feature map (image_rotary_emb of the block / rotary_emb of
+    LiteLA) against upstream in fp32 and against the fp32 evaluation on rounded tensors in bf16."""
+    g = golden("small_block_rope")
+    rot = (g["rope_cos"].to(DEV), g["rope_sin"].to(DEV))
+    blk = _block(g["C"], g["heads"], g["params"], dt)
+    r = (lambda v: v.to(dt).float()) if dt != torch.float32 else (lambda v: v)
+    p = {k: r(v) for k, v in g["params"].items()}
+    tag = "f32" if dt == torch.float32 else "bf16"
+    z1 = g[f"attn_in_{tag}"]
+    a_ref = O.lite_la_forward(z1.float(), O.sub(p, "attn"), heads=g["C"] // 32, eps=O.BLOCK_LA_EPS,
+                              rotary_emb=(g["rope_cos"], g["rope_sin"]))
+    assert nmax_err(blk.attn(z1.to(DEV), HW=g["HW"], rotary_emb=rot), a_ref) < tol
+    ref = O.sana_ms_block_forward(r(g["x"]), r(g["y"]), r(g["t"]), p, g["heads"], g["HW"], g["mask"],
+                                  rotary_emb=(g["rope_cos"], g["rope_sin"]))
+    out = blk(g["x"].to(DEV, dt), g["y"].to(DEV, dt), g["t"].to(DEV, dt), None, g["HW"], rot)
+    assert nmax_err(out, ref) < tol
+    if dt == torch.float32:
+        assert nmax_err(out, g["block_out_f32"]) < TOL_F32
+    # without the tables the result differs: the rotation is really applied
+    assert nmax_err(blk(g["x"].to(DEV, dt), g["y"].to(DEV, dt), g["t"].to(DEV, dt), None, g["HW"]), ref) > 10 * tol

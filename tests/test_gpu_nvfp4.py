@@ -128,3 +128,37 @@ def test_nvfp4_block_cosine(C, heads, B, HW, L):
     print(res)
     assert res["attn"] >= 0.995 and res["mlp"] >= 0.995 and res["block"] >= 0.995, res
     assert ops.take_gemm_nvfp4_device_status() == 0 and ops.take_gemm_device_status() == 0
+
+
+def test_weight_pack_round_trip(tmp_path):
+    """Pack the FP4 projection weights of a block, store, load into a fresh block whose bf16
+    weights were wiped: the loaded block reproduces the packing block's FP4 output bit for bit
+    (so it runs from the packed codes, not from re-quantised weights)."""
+    import sana_b200
+    from sana_b200 import synthetic
+
+    C, heads, grid = 256, 4, (8, 8)
+    shp = synthetic.BlockShape("p", C, heads, 2, grid, text_len=12)
+    params = synthetic.make_block_params(C, shp.ffn_hidden, seed=7, std=0.05)
+    x, y, t = synthetic.make_block_inputs(shp, seed=7, std=0.05, text_dim=64)
+    mk = lambda: sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    a = mk()
+    a.load_state_dict(params, strict=True)
+    a = a.to(DEV, torch.bfloat16)
+    pack = sana_b200.pack_nvfp4_weights(a)
+    assert len(pack) == 4 * 4 and all(v.device.type == "cpu" for v in pack.values())
+    path = tmp_path / "block.nvfp4.pt"
+    torch.save(pack, path)
+    a.set_nvfp4(True)
+    xd, yd, td = x.to(DEV, torch.bfloat16), y.to(DEV, torch.bfloat16), t.to(DEV, torch.bfloat16)
+    ref = a(xd, yd, td, None, grid)
+    b = mk()
+    b.load_state_dict(params, strict=True)
+    b = b.to(DEV, torch.bfloat16)
+    assert sana_b200.load_nvfp4_weights(b, torch.load(path)) == 4
+    for w in (b.attn.qkv.weight, b.attn.proj.weight, b.mlp.inverted_conv.conv.weight, b.mlp.point_conv.conv.weight):
+        w.data.zero_()  # the bf16 copies are not consulted any more
+    assert torch.equal(b(xd, yd, td, None, grid), ref)
+    with pytest.raises(ValueError):
+        sana_b200.load_nvfp4_weights(sana_b200.SanaMSBlock(2 * C, heads, mlp_ratio=2.5, attn_type="linear",
+                                                           ffn_type="glumbconv"), pack)
