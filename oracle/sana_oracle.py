@@ -124,6 +124,23 @@ def lite_la_forward(x, p: Params, heads: Optional[int] = None, dim: int = 32, ep
     return F.linear(qf(out), qf(p["proj.weight"]), p["proj.bias"])
 
 
+def pag_identity_forward(x, p: Params, chunks: int, heads: Optional[int] = None, eps: float = 1e-15,
+                         rotary_emb=None) -> torch.Tensor:
+    """PAGIdentitySelfAttnProcessorLiteLA (chunks = 2) / PAGCFGIdentitySelfAttnProcessorLiteLA
+    (chunks = 3), diffusion/model/nets/sana_blocks.py:573-675: the last chunk of the batch takes
+    "identity attention" (value projection straight into ``proj``), the others LiteLA."""
+    parts = x.chunk(chunks)
+    x_org, x_ptb = torch.cat(parts[:-1]), parts[-1]
+    C = x.shape[-1]
+    out = lite_la_forward(x_org, p, heads=heads, eps=eps, rotary_emb=rotary_emb)
+    v_weight = p["qkv.weight"][C * 2:C * 3, :]
+    x_ptb = torch.matmul(x_ptb, v_weight.t()).to(out.dtype)
+    if p.get("qkv.bias") is not None:
+        x_ptb = (x_ptb + p["qkv.bias"][C * 2:C * 3]).to(out.dtype)
+    x_ptb = F.linear(x_ptb, p["proj.weight"], p["proj.bias"])
+    return torch.cat([out, x_ptb])
+
+
 def lite_la_state(k_relu: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Token-major restatement of the first product of attn_matmul (sana_blocks.py:255-256):
     k_relu, v: [B, N, h, d] -> state [B, h, d+1, d] with state[b,h,i,j] = sum_n v1[n,i] k[n,j],

@@ -4,7 +4,8 @@
 // issues tcgen05.mma.cta_group::2 (M = 256), which reads both halves of W and writes each
 // CTA's 128 accumulator rows into that CTA's tensor memory.  Per SM this moves 30 KiB per K
 // block through shared memory instead of 44 KiB for the same math, which is what keeps the
-// tensor pipe fed.  Epilogue, pipeline and bounded waits are those of the single-CTA kernel.
+// tensor pipe fed.  Pipeline and bounded waits are those of the single-CTA kernel; the epilogue
+// goes through shared-memory boxes and bulk-tensor copies (see the epilogue warps below).
 //
 // Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' loads; empty[s]
 // and tfull[a] live in both CTAs and are signalled by the leader's tcgen05.commit with a

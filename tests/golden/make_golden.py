@@ -121,6 +121,25 @@ def video_case(R, seed=3):
     return small_block_case(R, "video", 64, 4, 1, (3, 5, 8), 7, seed)
 
 
+def pag_case(R, seed=8):
+    """Upstream's two perturbed-attention-guidance processors on a LiteLA (eps of the block)."""
+    C, N = 64, 30
+    g = torch.Generator().manual_seed(seed)
+    params = {k[len("attn."):]: v for k, v in synthetic.make_block_params(C, 160, seed, std=0.05).items()
+              if k.startswith("attn.")}
+    x = torch.randn(6, N, C, generator=g) * 0.5
+    out = {"C": C, "params": params, "x": x}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            m = R.LiteLA(C, C, heads=C // 32, eps=1e-8).eval()
+            m.load_state_dict(params, strict=True)
+            set_fp32_attention(m)
+            m = m.to(dt)
+            out[f"pag_{tag}"] = R.sana_blocks.PAGIdentitySelfAttnProcessorLiteLA(m)(x.to(dt))
+            out[f"pagcfg_{tag}"] = R.sana_blocks.PAGCFGIdentitySelfAttnProcessorLiteLA(m)(x.to(dt))
+    return out
+
+
 SANA_MS_SMALL = dict(input_size=8, patch_size=1, in_channels=32, hidden_size=64, depth=2, num_heads=2, mlp_ratio=2.5,
                      class_dropout_prob=0.0, pred_sigma=False, caption_channels=48, model_max_length=10, y_norm=True,
                      attn_type="linear", ffn_type="glumbconv", mlp_acts=("silu", "silu", None), linear_head_dim=32,
@@ -182,6 +201,7 @@ def main():
         "litela_cfg1": lambda: litela_cfg1_case(R),
         "block_cfg2": lambda: block_cfg2_case(R),
         "sana_ms_small": lambda: sana_ms_case(R),
+        "pag_litela": lambda: pag_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():

@@ -271,3 +271,30 @@ def test_block_with_rotary_embedding(golden, dt, tol):
         assert nmax_err(out, g["block_out_f32"]) < TOL_F32
     # without the tables the result differs: the rotation is really applied
     assert nmax_err(blk(g["x"].to(DEV, dt), g["y"].to(DEV, dt), g["t"].to(DEV, dt), None, g["HW"]), ref) > 10 * tol
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_pag_processors(golden, dt, tol):
+    """The two perturbed-attention-guidance processors, installed the way upstream's sampler
+    installs them (attn.forward = Processor(attn)), against upstream's own classes."""
+    from sana_b200 import processors
+
+    g = golden("pag_litela")
+    C = g["C"]
+    attn = sana_b200.LiteLA(C, C, heads=C // 32, eps=1e-8).eval()
+    attn.load_state_dict(g["params"], strict=True)
+    attn = attn.to(DEV, dt)
+    x = g["x"].to(DEV, dt)
+    r = (lambda v: v.to(dt).float()) if dt != torch.float32 else (lambda v: v)
+    p = {k: r(v) for k, v in g["params"].items()}
+    for cls, chunks, key in ((processors.PAGIdentitySelfAttnProcessorLiteLA, 2, "pag"),
+                             (processors.PAGCFGIdentitySelfAttnProcessorLiteLA, 3, "pagcfg")):
+        attn.forward = cls(attn)
+        try:
+            out = attn.forward(x, HW=(5, 6))
+        finally:
+            del attn.forward
+        ref = O.pag_identity_forward(r(g["x"]), p, chunks, eps=O.BLOCK_LA_EPS)
+        assert out.shape == ref.shape and nmax_err(out, ref) < tol
+        if dt == torch.float32:
+            assert nmax_err(out, g[f"{key}_f32"]) < TOL_F32
