@@ -26,10 +26,12 @@ constexpr int F4_A_BYTES = F4_BM * 128;             // 16 KiB
 constexpr int F4_B_BYTES = F4_BN * 128;             // 16 KiB
 constexpr int F4_SF_BYTES = 4 * 512;                // four 512-byte scale tiles per operand and stage
 constexpr int F4_STAGE_BYTES = F4_A_BYTES + F4_B_BYTES + 2 * F4_SF_BYTES;  // 36 KiB
-constexpr int F4_STAGES = 6;
+constexpr int F4_STAGES = 5;
 constexpr int F4_CTRL_BYTES = 256;
-constexpr int F4_SMEM_BYTES = F4_STAGES * F4_STAGE_BYTES + F4_CTRL_BYTES;
 constexpr int F4_EPI_WARPS = 8;
+constexpr int F4_EPI_BYTES = F4_EPI_WARPS * EPI_BOX_BYTES;  // one 32 x 64 box per epilogue warp (tc_common.cuh)
+constexpr int F4_SMEM_BYTES = F4_STAGES * F4_STAGE_BYTES + F4_EPI_BYTES + F4_CTRL_BYTES;
+static_assert(16 * F4_STAGES + 40 + 8 * F4_EPI_WARPS <= F4_CTRL_BYTES, "control block too small");
 constexpr int F4_THREADS = 64 + 32 * F4_EPI_WARPS;
 constexpr int F4_TMEM_COLS = 512;                   // 2 x 128 accumulator + 6 x 32 scale columns = 448
 constexpr int F4_SF_COL0 = 2 * F4_BN;               // first scale column
@@ -79,14 +81,20 @@ struct F4Args {
 };
 
 __global__ void __launch_bounds__(F4_THREADS, 1)
-gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const F4Args args) {
+gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes,
+                     const F4Args args) {
   constexpr int STAGES = F4_STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t tiles_base = smem_u32(smem_raw);
-  const uint32_t ctrl = tiles_base + STAGES * F4_STAGE_BYTES;
-  unsigned char* ctrl_gen = smem_raw + STAGES * F4_STAGE_BYTES;
+  const uint32_t epi_base = tiles_base + STAGES * F4_STAGE_BYTES;  // staging boxes of the epilogue warps
+  unsigned char* epi_gen = smem_raw + STAGES * F4_STAGE_BYTES;
+  const uint32_t ctrl = epi_base + F4_EPI_BYTES;
+  unsigned char* ctrl_gen = epi_gen + F4_EPI_BYTES;
+  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort | res[EPI_WARPS]
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const uint32_t bar_res = ctrl + 16 * STAGES + 40;
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
 
@@ -107,10 +115,13 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, F4_EPI_WARPS);
     }
+    for (int w = 0; w < F4_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmOut) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmRes) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32),
@@ -188,35 +199,51 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else {
     // ------------------------------- epilogue warps -----------------------------------
+    // staged epilogue (tc_common.cuh): a warp owns 32 rows x 64 columns = one box
+    const int ew = warp - 2;
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ew >> 2;
     constexpr int HALF = F4_BN / 2, NCHUNK = HALF / 16;
+    static_assert(HALF == EPI_BOX_COLS, "one staging box per epilogue warp");
     const EpiParams& ep = args.ep;
     const int64_t N = args.N;
+    const bool has_res = ep.residual != nullptr;
     const float alpha = __ldg(args.a_scale) * __ldg(args.w_scale);
+    EpiBox eb;
+    eb.box_s = epi_base + (uint32_t)(ew * EPI_BOX_BYTES);
+    eb.row_g = epi_gen + ew * EPI_BOX_BYTES + lane * 128;
+    eb.res_bar = bar_res + 8 * ew;
+    eb.res_phase = 0u;
+    eb.swz = (uint32_t)(lane & 7);
     uint32_t full_phase = 0u;
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       const int a = it & 1;
-      const int m0 = (tile / args.tiles_n) * F4_BM;
+      const int m_box = (tile / args.tiles_n) * F4_BM + quad * 32;
       const int64_t nbase = (int64_t)(tile % args.tiles_n) * F4_BN + half * HALF;
-      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * F4_BN + half * HALF);
       const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
+      const bool box_rows_in = m_box < args.M;
+      const bool use_res = has_res && box_rows_in;
+      epi_box_begin<1>(eb, row, use_res, lane, m_box, &tmRes);
       EpiStep st[2];
-      EpiRes res;
-      epi_prefetch_residual<NCHUNK>(row, res);
       epi_fetch(row, st[0], 0);  // operands that do not depend on the accumulator: requested before the wait
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      epi_drain<NCHUNK, true>(row, ep, taddr, st, res, alpha);
+      if (!epi_box_drain<NCHUNK, true>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, alpha,
+                                       abort_flag, &g_fp4_status)) {
+        ok = false;
+        break;
+      }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
     }
+    if (lane == 0) bulk_wait_all();  // the boxes stay valid until the last stores have drained
   }
 
   __syncwarp();
@@ -377,9 +404,19 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   a.tiles_n = (int)ceil_div(N, F4_BN);
   a.ktiles4 = (int)ktiles4_of(K);
   a.ep = p;
+  // output and residual as 32-row x 64-column boxes (the residual map is a copy when unused)
+  CUtensorMap tmOut, tmRes;
+  rc = make_tmap_2d(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, M, N, ldo * 2, 32, EPI_BOX_COLS);
+  if (rc) return rc;
+  tmRes = tmOut;
+  if (p.residual) {
+    rc = make_tmap_2d(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.residual, M, N, p.ldr * 2, 32, EPI_BOX_COLS);
+    if (rc) return rc;
+  }
   const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_nvfp4_tc_kernel<<<grid, F4_THREADS, F4_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, a);
+  gemm_nvfp4_tc_kernel<<<grid, F4_THREADS, F4_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmOut, tmRes,
+                                                                                               a);
   SANA_LAUNCH_CHECK("gemm_nvfp4_tc kernel");
   return SANA_OK;
 }

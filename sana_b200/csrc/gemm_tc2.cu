@@ -25,9 +25,6 @@ constexpr int T2_THREADS = 64 + 32 * T2_EPI_WARPS;
 constexpr int T2_SMEM_LIMIT = 232448;
 constexpr int T2_CTRL_BYTES = 256;
 
-constexpr int T2_BOX_COLS = 64;                           // epilogue staging box: 32 rows x 64 columns
-constexpr int T2_BOX_BYTES = 32 * T2_BOX_COLS * 2;         // 4 KiB, rows of 128 bytes (128-byte swizzle)
-
 template <int BN>
 struct T2Cfg {
   static constexpr int BH = BN / 2;                       // W rows held by each CTA
@@ -35,8 +32,8 @@ struct T2Cfg {
   static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES;
   static constexpr int HALF = BN / 2;                     // columns per epilogue warp
   static constexpr int NCHUNK = HALF / 16;
-  static constexpr int NBOX = HALF / T2_BOX_COLS;         // staging boxes per epilogue warp
-  static constexpr int EPI_BYTES = T2_EPI_WARPS * NBOX * T2_BOX_BYTES;
+  static constexpr int NBOX = HALF / EPI_BOX_COLS;         // staging boxes per epilogue warp
+  static constexpr int EPI_BYTES = T2_EPI_WARPS * NBOX * EPI_BOX_BYTES;
   static constexpr int MAX_STAGES = (T2_SMEM_LIMIT - T2_CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + T2_CTRL_BYTES;
@@ -49,19 +46,6 @@ struct T2Cfg {
   static_assert(STAGES >= 4, "too few pipeline stages");
   static_assert(16 * STAGES + 40 + 8 * T2_EPI_WARPS <= T2_CTRL_BYTES, "control block too small");
 };
-
-// ---- bulk-tensor store side of the epilogue ---------------------------------------------------
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t smem_src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(tmap), "r"(smem_src), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all of this thread's bulk stores have finished READING shared memory (the staging boxes are free again)
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// generic-proxy writes to shared memory become visible to the async proxy (the bulk store)
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -228,14 +212,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else {
     // ------------------------------- epilogue warps (both CTAs) -------------------------
-    // A warp owns 32 accumulator rows (its TMEM lane quadrant) and one column half, i.e. NBOX
-    // boxes of 32 rows x 64 columns.  All of its global traffic is bulk-tensor copies through
-    // the box buffers in shared memory (rows of 128 bytes, 128-byte swizzle, so a lane reading
-    // or writing its own row hits no bank conflict): the residual box is loaded while the
-    // accumulator is still being computed, each lane adds its row in place, and the finished
-    // box is stored by one bulk copy, which also clips rows >= M and columns >= N.  Per-lane
-    // 16-byte loads and stores of 32 different rows would cost the SM sixteen times as many
-    // memory requests, which is what bounded this epilogue before.
+    // staged epilogue (tc_common.cuh): a warp owns 32 rows x one column half = NBOX boxes
     const int ew = warp - 2;
     const int quad = warp & 3;
     const int half = ew >> 2;
@@ -243,11 +220,13 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int64_t N = args.N;
     const bool has_res = ep.residual != nullptr;
     const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
-    const uint32_t box_s = epi_base + (uint32_t)(ew * Cfg::NBOX * T2_BOX_BYTES);
-    unsigned char* box_g = epi_gen + ew * Cfg::NBOX * T2_BOX_BYTES + lane * 128;  // this lane's row of box 0
-    const uint32_t res_bar = bar_res + 8 * ew;
-    const uint32_t swz = (uint32_t)(lane & 7);
-    uint32_t full_phase = 0u, res_phase = 0u;
+    EpiBox eb;
+    eb.box_s = epi_base + (uint32_t)(ew * Cfg::NBOX * EPI_BOX_BYTES);
+    eb.row_g = epi_gen + ew * Cfg::NBOX * EPI_BOX_BYTES + lane * 128;
+    eb.res_bar = bar_res + 8 * ew;
+    eb.res_phase = 0u;
+    eb.swz = (uint32_t)(lane & 7);
+    uint32_t full_phase = 0u;
     bool ok = true;
     int it = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
@@ -258,93 +237,18 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
       const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
-      // the previous tile's stores have read the boxes; then the residual may overwrite them
-      if (lane == 0) bulk_wait_read_all();
-      __syncwarp();
       const bool box_rows_in = m_box < args.M;  // otherwise the whole box lies below the matrix: no copies
       const bool use_res = has_res && box_rows_in;
-      if (use_res && lane == 0 && nbase < N) {
-        int nb = 0;
-#pragma unroll
-        for (int j = 0; j < Cfg::NBOX; ++j) nb += (nbase + T2_BOX_COLS * j < N) ? 1 : 0;
-        mbar_expect_tx(res_bar, (uint32_t)(nb * T2_BOX_BYTES));
-#pragma unroll
-        for (int j = 0; j < Cfg::NBOX; ++j)
-          if (nbase + T2_BOX_COLS * j < N)
-            tma_load_2d(box_s + j * T2_BOX_BYTES, &tmRes, res_bar, (int)(nbase + T2_BOX_COLS * j), m_box);
-      }
+      epi_box_begin<Cfg::NBOX>(eb, row, use_res, lane, m_box, &tmRes);
       EpiStep st[2];
       epi_fetch(row, st[0], 0);  // operands that do not depend on the accumulator: requested before the wait
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_gemm2_status)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      if (nbase < N) {
-        tmem_ld_32x16(taddr, st[0].acc);
-        if (use_res) {
-          if (!mbar_wait(res_bar, res_phase, abort_flag, 5, &g_gemm2_status)) { ok = false; break; }
-          res_phase ^= 1u;
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < Cfg::NCHUNK; ++c) {
-        const int64_t n = nbase + 16 * c;
-        if (n >= N) break;  // uniform: the rest of this half lies outside the matrix
-        constexpr int CPB = T2_BOX_COLS / 16;  // 16-column steps per box
-        const int j = c / CPB, cc = c % CPB;
-        EpiStep& cur = st[c & 1];
-        tmem_ld_wait();
-        const bool more = (c + 1 < Cfg::NCHUNK) && (n + 16 < N);
-        if (more) {
-          tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
-          epi_fetch(row, st[(c + 1) & 1], c + 1);
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (n + 8 * h < N) {
-            float v[8], f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * h + e]);
-            if (row.bias) {
-              unpack8(cur.bias[h], f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] += f[e];
-            }
-            if (ep.act == 1) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
-            } else if (ep.act == 2) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                if (n + 8 * h + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
-            } else if (ep.act == 3) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
-            }
-            if (row.grow) {
-              float g[8];
-              unpack8(cur.gtab[h], g);
-              unpack8(cur.gt[h], f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
-            }
-            // 16-byte piece (2*cc + h) of this lane's 128-byte row of box j, swizzled by the row
-            uint4* slot = reinterpret_cast<uint4*>(box_g + j * T2_BOX_BYTES + ((((uint32_t)(2 * cc + h)) ^ swz) << 4));
-            if (use_res) {
-              unpack8(*slot, f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] += f[e];
-            }
-            *slot = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-          }
-        }
-        if (cc == CPB - 1 || !more) {  // box j is complete
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && box_rows_in) {
-            tma_store_2d(&tmOut, box_s + j * T2_BOX_BYTES, (int)(nbase + T2_BOX_COLS * j), m_box);
-            bulk_commit();
-          }
-        }
+      if (!epi_box_drain<Cfg::NCHUNK, false>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, 1.0f,
+                                             abort_flag, &g_gemm2_status)) {
+        ok = false;
+        break;
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -377,10 +281,10 @@ static int launch_pair_bn(const void* A, int64_t lda, const void* Wt, int64_t ld
   if (rc) return rc;
   // output and residual as 32-row x 64-column boxes (the residual map is a copy when unused)
   CUtensorMap tmOut, tmRes;
-  rc = make_tmap_2d(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.out, M, N, args.ldo * 2, 32, T2_BOX_COLS);
+  rc = make_tmap_2d(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.out, M, N, args.ldo * 2, 32, EPI_BOX_COLS);
   if (rc) return rc;
   if (args.ep.residual) {
-    rc = make_tmap_2d(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.ep.residual, M, N, args.ep.ldr * 2, 32, T2_BOX_COLS);
+    rc = make_tmap_2d(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, args.ep.residual, M, N, args.ep.ldr * 2, 32, EPI_BOX_COLS);
     if (rc) return rc;
   } else {
     tmRes = tmOut;

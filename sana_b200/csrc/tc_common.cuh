@@ -257,6 +257,140 @@ __device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, 
   }
 }
 
+// ---- staged epilogue: shared-memory boxes + bulk-tensor copies --------------------------------
+// An epilogue warp owns 32 accumulator rows (its TMEM lane quadrant) and NBOX boxes of 32 rows
+// x 64 columns.  All of its global traffic is bulk-tensor copies through the box buffers in
+// shared memory (rows of 128 bytes, 128-byte swizzle, so a lane reading or writing its own row
+// hits no bank conflict): the residual box is loaded while the accumulator is still being
+// computed, each lane adds its row in place, and the finished box is stored by one bulk copy,
+// which also clips rows >= M and columns >= N.  Per-lane 16-byte loads and stores of 32
+// different rows cost the SM sixteen times as many memory requests, which bounded the epilogue.
+constexpr int EPI_BOX_COLS = 64;
+constexpr int EPI_BOX_BYTES = 32 * EPI_BOX_COLS * 2;  // 4 KiB
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk stores have finished READING shared memory (the staging boxes are free again)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// generic-proxy writes to shared memory become visible to the async proxy (the bulk store)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+struct EpiBox {
+  uint32_t box_s;        // shared address of this warp's box 0
+  unsigned char* row_g;  // generic address of this lane's 128-byte row of box 0
+  uint32_t res_bar;      // mbarrier counting the residual loads of a tile
+  uint32_t res_phase;
+  uint32_t swz;          // lane & 7: the row's swizzle of its 16-byte pieces
+};
+
+// Start of a tile (before the accumulator is ready): once the previous tile's stores have read
+// the boxes, the residual boxes of this tile are fetched into them.
+template <int NBOX>
+__device__ __forceinline__ void epi_box_begin(const EpiBox& eb, const EpiRow& row, bool use_res, int lane, int m_box,
+                                              const CUtensorMap* tmRes) {
+  if (lane == 0) bulk_wait_read_all();
+  __syncwarp();
+  if (use_res && lane == 0 && row.nbase < row.N) {
+    int nb = 0;
+#pragma unroll
+    for (int j = 0; j < NBOX; ++j) nb += (row.nbase + EPI_BOX_COLS * j < row.N) ? 1 : 0;
+    mbar_expect_tx(eb.res_bar, (uint32_t)(nb * EPI_BOX_BYTES));
+#pragma unroll
+    for (int j = 0; j < NBOX; ++j)
+      if (row.nbase + EPI_BOX_COLS * j < row.N)
+        tma_load_2d(eb.box_s + j * EPI_BOX_BYTES, tmRes, eb.res_bar, (int)(row.nbase + EPI_BOX_COLS * j), m_box);
+  }
+}
+
+// The accumulator is complete: read it 16 columns at a time, apply the epilogue in the boxes and
+// store them.  st[0] must hold the side operands of step 0 (epi_fetch).  Returns false when the
+// wait for the residual was abandoned.
+template <int NCHUNK, bool SCALE>
+__device__ __forceinline__ bool epi_box_drain(EpiBox& eb, const EpiRow& row, const EpiParams& ep, uint32_t taddr,
+                                              EpiStep (&st)[2], bool use_res, bool box_rows_in, int lane, int m_box,
+                                              const CUtensorMap* tmOut, float alpha, volatile int* abort_flag,
+                                              int* status_word) {
+  const int64_t nbase = row.nbase, N = row.N;
+  if (nbase < N) {
+    tmem_ld_32x16(taddr, st[0].acc);
+    if (use_res) {
+      if (!mbar_wait(eb.res_bar, eb.res_phase, abort_flag, 5, status_word)) return false;
+      eb.res_phase ^= 1u;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int64_t n = nbase + 16 * c;
+    if (n >= N) break;  // uniform: the rest of this half lies outside the matrix
+    constexpr int CPB = EPI_BOX_COLS / 16;  // 16-column steps per box
+    const int j = c / CPB, cc = c % CPB;
+    EpiStep& cur = st[c & 1];
+    tmem_ld_wait();
+    const bool more = (c + 1 < NCHUNK) && (n + 16 < N);
+    if (more) {
+      tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
+      epi_fetch(row, st[(c + 1) & 1], c + 1);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (n + 8 * h < N) {
+        float v[8], f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * h + e]);
+        if (SCALE) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] *= alpha;
+        }
+        if (row.bias) {
+          unpack8(cur.bias[h], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += f[e];
+        }
+        if (ep.act == 1) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+        } else if (ep.act == 2) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (n + 8 * h + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+        } else if (ep.act == 3) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+        }
+        if (row.grow) {
+          float g[8];
+          unpack8(cur.gtab[h], g);
+          unpack8(cur.gt[h], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+        }
+        // 16-byte piece (2*cc + h) of this lane's 128-byte row of box j, swizzled by the row
+        uint4* slot = reinterpret_cast<uint4*>(eb.row_g + j * EPI_BOX_BYTES + ((((uint32_t)(2 * cc + h)) ^ eb.swz) << 4));
+        if (use_res) {
+          unpack8(*slot, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += f[e];
+        }
+        *slot = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+      }
+    }
+    if (cc == CPB - 1 || !more) {  // box j is complete
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && box_rows_in) {
+        tma_store_2d(tmOut, eb.box_s + j * EPI_BOX_BYTES, (int)(nbase + EPI_BOX_COLS * j), m_box);
+        bulk_commit();
+      }
+    }
+  }
+  return true;
+}
+
 // ---- host helpers -----------------------------------------------------------------------------
 // 2-D tiled tensor map over a row-major [rows, cols] matrix of `elem_bytes`-wide elements, row
 // stride ld_bytes; box = box_rows x box_cols, 128-byte swizzle, out-of-range reads give zeros.
