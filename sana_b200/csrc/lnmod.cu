@@ -80,15 +80,20 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
       }
     }
     __syncthreads();
-    for (int64_t row = seg0 + warp; row < seg1; row += nwarp) {
+    auto load = [&](uint4 (&raw)[MAXV], int64_t row) {
       const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
-      uint4 raw[MAXV];
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) raw[i] = ldg_nc_u4(xr + v);
+      }
+    };
+    auto process = [&](const uint4 (&raw)[MAXV], int64_t row) {
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < MAXV; ++i) {
         const int v = lane + 32 * i;
         if (v < nvec) {
-          raw[i] = ldg_nc_u4(xr + v);
           float f[VN];
           Vec16<T>::unpack(raw[i], f);
 #pragma unroll
@@ -130,6 +135,18 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
           zr[v] = Vec16<T>::pack(f);
         }
       }
+    };
+    // two register sets in ping-pong: the next row's loads are in flight while this row is
+    // reduced, modulated and stored
+    uint4 ra[MAXV], rb[MAXV];
+    int64_t row = seg0 + warp;
+    if (row < seg1) load(ra, row);
+    for (; row < seg1; row += 2 * nwarp) {
+      const int64_t r1 = row + nwarp, r2 = row + 2 * nwarp;
+      if (r1 < seg1) load(rb, r1);
+      process(ra, row);
+      if (r2 < seg1) load(ra, r2);
+      if (r1 < seg1) process(rb, r1);
     }
   }
 }
@@ -140,11 +157,6 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
   const int64_t rows = B * N;
   const int nvec = (int)(C / Vec16<T>::N);
   const int per_lane = (nvec + 31) / 32;
-  // one wave of blocks (three per SM at 256 threads), each over a contiguous range of rows
-  const int64_t want = (int64_t)sm_count() * 3;
-  int64_t rpb = ceil_div(rows, want);
-  rpb = ceil_div(rpb, 8) * 8;
-  const unsigned grid = (unsigned)ceil_div(rows, rpb);
   const size_t smem = (size_t)2 * C * sizeof(float);
   const T* xp = static_cast<const T*>(x);
   const T* tb = static_cast<const T*>(table);
@@ -157,6 +169,16 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
                                            (int)smem);                                                         \
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_modulate)");                       \
     }                                                                                                          \
+    /* one wave of blocks (as many as are resident), each over a contiguous range of rows */                  \
+    int per_sm = 0;                                                                                            \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_kernel<T, MV>, 256, smem) !=        \
+            cudaSuccess || per_sm < 1) {                                                                       \
+      cudaGetLastError();                                                                                      \
+      per_sm = 1;                                                                                              \
+    }                                                                                                          \
+    int64_t rpb = ceil_div(rows, (int64_t)sm_count() * per_sm);                                                \
+    rpb = ceil_div(rpb, 8) * 8;                                                                                \
+    const unsigned grid = (unsigned)ceil_div(rows, rpb);                                                       \
     ln_modulate_kernel<T, MV><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, tb_shift, tb_scale,   \
                                                        t_rows, t_shift, t_scale, eps, (int)rpb);               \
     SANA_LAUNCH_CHECK("ln_modulate kernel");                                                                   \
