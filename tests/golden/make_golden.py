@@ -2,7 +2,7 @@
 
 Run on a machine with a checkout of NVlabs/Sana:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <checkout of NVlabs/Sana>   (or SANA_REFERENCE=<checkout>)
 
 Each fixture stores the seeded inputs, the parameters (upstream state-dict keys) and the
 outputs of upstream's LiteLA / GLUMBConv / SanaMSBlock forward, in fp32 and (for the block)
@@ -186,7 +186,8 @@ def sana_ms_case(R, seed=5):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("SANA_REFERENCE"), required="SANA_REFERENCE" not in os.environ,
+                    help="checkout of NVlabs/Sana")
     ap.add_argument("--only", default=None, help="regenerate just this fixture")
     a = ap.parse_args()
     torch.manual_seed(0)

@@ -107,7 +107,7 @@ def _install_third_party_shims() -> None:
         tc.colored = lambda s, *a, **k: s
 
 
-def load_reference(root: str = "/root/reference"):
+def load_reference(root: str):
     """Returns a namespace with the upstream ``LiteLA``, ``GLUMBConv``, ``SanaMSBlock``,
     ``MultiHeadCrossAttention``, ``TimestepEmbedder`` and ``t2i_modulate``."""
     if root in _LOADED:
