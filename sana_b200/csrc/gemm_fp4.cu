@@ -225,7 +225,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * F4_BN + half * HALF);
-      const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
+      const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
       const bool box_rows_in = m_box < args.M;
       const bool use_res = has_res && box_rows_in;
       epi_box_begin<1>(eb, row, use_res, lane, m_box, &tmRes);

@@ -33,17 +33,20 @@ template <int BN>
 struct TcCfg {
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (TC_SMEM_LIMIT - TC_CTRL_BYTES) / STAGE_BYTES;
+  static constexpr int HALF = BN / 2;              // columns per epilogue warp
+  static constexpr int NCHUNK = HALF / 16;         // 16-column steps per epilogue warp
+  static constexpr int NBOX = HALF / EPI_BOX_COLS;  // staging boxes per epilogue warp (tc_common.cuh)
+  static constexpr int EPI_BYTES = TC_EPI_WARPS * NBOX * EPI_BOX_BYTES;
+  static constexpr int MAX_STAGES = (TC_SMEM_LIMIT - TC_CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TC_CTRL_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + TC_CTRL_BYTES;
   static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
   // instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7, 10), both K-major, N>>3 at 17, M>>4 at 24
   static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TC_BM >> 4) << 24);
-  static constexpr int HALF = BN / 2;        // columns per epilogue warp
-  static constexpr int NCHUNK = HALF / 16;   // 16-column steps per epilogue warp
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
+  static_assert(BN == 128 || BN == 256, "the staged epilogue needs column halves that are whole 64-column boxes");
   static_assert(STAGES >= 3, "not enough shared memory for the ring");
+  static_assert(16 * STAGES + 40 + 8 * TC_EPI_WARPS <= TC_CTRL_BYTES, "control block too small");
 };
 
 struct TcArgs {
@@ -56,16 +59,21 @@ struct TcArgs {
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs args) {
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes,
+                    const TcArgs args) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t tiles_base = smem_u32(smem_raw);                // swizzled tiles need 1024-byte alignment
-  const uint32_t ctrl = tiles_base + STAGES * Cfg::STAGE_BYTES;  // control block after the ring
-  unsigned char* ctrl_gen = smem_raw + STAGES * Cfg::STAGE_BYTES;
-  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort
+  const uint32_t epi_base = tiles_base + STAGES * Cfg::STAGE_BYTES;  // staging boxes of the epilogue warps
+  unsigned char* epi_gen = smem_raw + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t ctrl = epi_base + Cfg::EPI_BYTES;                   // control block after them
+  unsigned char* ctrl_gen = epi_gen + Cfg::EPI_BYTES;
+  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort | res[EPI_WARPS]
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const uint32_t bar_res = ctrl + 16 * STAGES + 40;
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
 
@@ -87,10 +95,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS);
     }
+    for (int w = 0; w < TC_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmOut) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmRes) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32),
@@ -159,33 +170,47 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // warp w reads TMEM lanes 32*(w%4)..+31 (hardware rule) and the left or right half of the
     // tile's columns; 16 columns per step, operands of step c+1 in flight while step c is
     // computed and stored.
+    const int ew = warp - 2;
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ew >> 2;
     const EpiParams& ep = args.ep;
     const int64_t N = args.N;
+    const bool has_res = ep.residual != nullptr;
+    EpiBox eb;
+    eb.box_s = epi_base + (uint32_t)(ew * Cfg::NBOX * EPI_BOX_BYTES);
+    eb.row_g = epi_gen + ew * Cfg::NBOX * EPI_BOX_BYTES + lane * 128;
+    eb.res_bar = bar_res + 8 * ew;
+    eb.res_phase = 0u;
+    eb.swz = (uint32_t)(lane & 7);
     uint32_t full_phase = 0u;  // bit a = phase of accumulator buffer a
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       const int a = it & 1;
-      const int m0 = (tile / args.tiles_n) * TC_BM;
+      const int m_box = (tile / args.tiles_n) * TC_BM + quad * 32;
       const int64_t nbase = (int64_t)(tile % args.tiles_n) * BN + half * Cfg::HALF;
-      const int64_t m = (int64_t)m0 + quad * 32 + lane;
+      const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
-      const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
+      const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
+      const bool box_rows_in = m_box < args.M;  // otherwise the whole box lies below the matrix: no copies
+      const bool use_res = has_res && box_rows_in;
+      epi_box_begin<Cfg::NBOX>(eb, row, use_res, lane, m_box, &tmRes);
       EpiStep st[2];
-      EpiRes res;
-      epi_prefetch_residual<Cfg::NCHUNK>(row, res);
       epi_fetch(row, st[0], 0);  // operands that do not depend on the accumulator: requested before the wait
       if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_gemm_status)) { ok = false; break; }
       full_phase ^= 1u << a;
       tcgen05_fence_after();
-      epi_drain<Cfg::NCHUNK, false>(row, ep, taddr, st, res, 1.0f);
+      if (!epi_box_drain<Cfg::NCHUNK, false>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, 1.0f,
+                                             abort_flag, &g_gemm_status)) {
+        ok = false;
+        break;
+      }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
     }
+    if (lane == 0) bulk_wait_all();  // the boxes stay valid until the last stores have drained
   }
 
   // ------------------------------- teardown ---------------------------------------------
@@ -256,9 +281,17 @@ template <int BN>
 static int launch_bn(const CUtensorMap& tmA, const void* Wt, int64_t ldw, int64_t N, int64_t K, TcArgs& args,
                      cudaStream_t st) {
   using Cfg = TcCfg<BN>;
-  CUtensorMap tmB;
+  CUtensorMap tmB, tmOut, tmRes;
   int rc = make_tmap(&tmB, Wt, N, K, ldw, BN);
   if (rc) return rc;
+  // output and residual as 32-row x 64-column boxes (the residual map is a copy when unused)
+  rc = make_tmap(&tmOut, args.out, args.M, N, args.ldo, 32);
+  if (rc) return rc;
+  tmRes = tmOut;
+  if (args.ep.residual) {
+    rc = make_tmap(&tmRes, args.ep.residual, args.M, N, args.ep.ldr, 32);
+    if (rc) return rc;
+  }
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -269,14 +302,14 @@ static int launch_bn(const CUtensorMap& tmA, const void* Wt, int64_t ldw, int64_
   args.tiles_n = (int)ceil_div(N, BN);
   const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_bf16_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, args);
+  gemm_bf16_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmOut, tmRes, args);
   SANA_LAUNCH_CHECK("gemm_bf16_tc kernel");
   return SANA_OK;
 }
 
 // Tile width: minimise (waves over the SMs) x BN, i.e. padded work including the last partial wave.
 static int pick_bn(int64_t M, int64_t N) {
-  const int cands[4] = {256, 224, 192, 128};
+  const int cands[2] = {256, 128};
   const int64_t sms = sm_count();
   const int64_t tm = ceil_div(M, TC_BM);
   int best = 128;
@@ -319,8 +352,6 @@ int gemm_tc_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void
   args.ep = ep;
   switch (pick_bn(M, N)) {
     case 256: return launch_bn<256>(tmA, Wt, ldw, N, K, args, st);
-    case 224: return launch_bn<224>(tmA, Wt, ldw, N, K, args, st);
-    case 192: return launch_bn<192>(tmA, Wt, ldw, N, K, args, st);
     default: return launch_bn<128>(tmA, Wt, ldw, N, K, args, st);
   }
 }

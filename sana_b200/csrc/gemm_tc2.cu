@@ -236,7 +236,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);
-      const EpiRow row = epi_row_setup(ep, args.out, args.ldo, m, row_ok, nbase, N);
+      const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
       const bool box_rows_in = m_box < args.M;  // otherwise the whole box lies below the matrix: no copies
       const bool use_res = has_res && box_rows_in;
       epi_box_begin<Cfg::NBOX>(eb, row, use_res, lane, m_box, &tmRes);

@@ -116,66 +116,32 @@ __device__ __forceinline__ float fast_silu(float x) {
   return x * r;
 }
 
-// ---- fused epilogue of one accumulator row-half ---------------------------------------------
+// ---- fused epilogue: per-row set-up and the small per-column operands ------------------------
 // An epilogue warp owns 32 accumulator rows (its TMEM lane quadrant) and NCHUNK steps of 16
-// columns.  Per step a lane needs 16 accumulator words plus, for its row, 32 bytes each of
-// bias, gate table, gate timestep vector and residual.  The small per-column operands are
-// loaded one step ahead of their use.  The residual comes from DRAM, one 32-byte piece per
-// lane and step, so its latency is hidden twice over: the lane's whole row-half is pulled
-// into L2 by one bulk prefetch when the tile starts (long before the accumulator is ready),
-// and the register loads run EPI_RES_AHEAD steps ahead through a small ring.
-constexpr int EPI_RES_AHEAD = 4;
-
+// columns.  Per step a lane needs 16 accumulator words plus 32 bytes each of bias, gate table
+// and gate timestep vector (the same for every row: broadcast loads, issued one step ahead of
+// their use); the residual and the output go through the staged boxes below.
 struct EpiStep {
   uint32_t acc[16];
   uint4 bias[2], gtab[2], gt[2];
 };
 
-struct EpiRes {
-  uint4 v[EPI_RES_AHEAD][2];
-};
-
 struct EpiRow {
-  const __nv_bfloat16 *bias, *grow, *gtrow, *rrow;
-  __nv_bfloat16* orow;
+  const __nv_bfloat16 *bias, *grow, *gtrow;
   int64_t nbase, N;
-  bool row_ok;
 };
 
-__device__ __forceinline__ EpiRow epi_row_setup(const EpiParams& ep, __nv_bfloat16* out, int64_t ldo, int64_t m,
-                                                bool row_ok, int64_t nbase, int64_t N) {
+// m = this lane's row, row_ok = it lies inside the matrix (else sample 0's gate vector is read)
+__device__ __forceinline__ EpiRow epi_row_setup(const EpiParams& ep, int64_t m, bool row_ok, int64_t nbase, int64_t N) {
   EpiRow r;
   r.bias = static_cast<const __nv_bfloat16*>(ep.bias);
   const __nv_bfloat16* gtab = static_cast<const __nv_bfloat16*>(ep.gate_table);
   r.grow = gtab ? gtab + (int64_t)ep.gate_row * N : nullptr;
   r.gtrow = gtab ? static_cast<const __nv_bfloat16*>(ep.gate_t) + ((row_ok ? m / ep.rows_per_batch : 0) * 6 + ep.gate_row) * N
                  : nullptr;
-  r.rrow = ep.residual ? static_cast<const __nv_bfloat16*>(ep.residual) + m * ep.ldr : nullptr;
-  r.orow = out + m * ldo;
   r.nbase = nbase;
   r.N = N;
-  r.row_ok = row_ok;
   return r;
-}
-
-__device__ __forceinline__ void epi_res_load(const EpiRow& r, uint4 (&v)[2], int c) {
-  const int64_t n = r.nbase + 16 * c;
-#pragma unroll
-  for (int j = 0; j < 2; ++j)
-    v[j] = (r.rrow && r.row_ok && n + 8 * j < r.N) ? ldg_nc_u4(r.rrow + n + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
-}
-
-// Start of a tile: L2 prefetch of the lane's residual row-half (a multiple of 16 bytes at a
-// 16-byte aligned address, as the bulk form requires) and the first EPI_RES_AHEAD steps' loads.
-template <int NCHUNK>
-__device__ __forceinline__ void epi_prefetch_residual(const EpiRow& r, EpiRes& res) {
-  if (r.rrow && r.row_ok && r.nbase < r.N) {
-    const int64_t cols = (r.N - r.nbase < 16 * NCHUNK) ? (r.N - r.nbase) : 16 * NCHUNK;
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.rrow + r.nbase), "r"((uint32_t)(cols * 2))
-                 : "memory");
-  }
-#pragma unroll
-  for (int c = 0; c < EPI_RES_AHEAD && c < NCHUNK; ++c) epi_res_load(r, res.v[c], c);
 }
 
 __device__ __forceinline__ void epi_fetch(const EpiRow& r, EpiStep& s, int c) {
@@ -189,71 +155,6 @@ __device__ __forceinline__ void epi_fetch(const EpiRow& r, EpiStep& s, int c) {
       s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
       s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
-}
-
-// Reads the accumulator (already complete) 16 columns at a time, applies the epilogue and
-// stores bf16.  st[0] must hold the side operands of step 0 (epi_fetch) and `res` the first
-// residual steps (epi_prefetch_residual) on entry.
-template <int NCHUNK, bool SCALE>
-__device__ __forceinline__ void epi_drain(const EpiRow& r, const EpiParams& ep, uint32_t taddr, EpiStep (&st)[2],
-                                          EpiRes& res, float alpha) {
-  if (r.nbase < r.N) tmem_ld_32x16(taddr, st[0].acc);
-#pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) {
-    const int64_t n = r.nbase + 16 * c;
-    if (n >= r.N) break;  // uniform: the rest of this half lies outside the matrix
-    EpiStep& cur = st[c & 1];
-    tmem_ld_wait();
-    if (c + 1 < NCHUNK && n + 16 < r.N) {
-      tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), st[(c + 1) & 1].acc);
-      epi_fetch(r, st[(c + 1) & 1], c + 1);
-    }
-    if (r.row_ok) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        if (n + 8 * j < r.N) {
-          float v[8], f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(cur.acc[8 * j + e]);
-          if (SCALE) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] *= alpha;
-          }
-          if (r.bias) {
-            unpack8(cur.bias[j], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += f[e];
-          }
-          if (ep.act == 1) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
-          } else if (ep.act == 2) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              if (n + 8 * j + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
-          } else if (ep.act == 3) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
-          }
-          if (r.grow) {
-            float g[8];
-            unpack8(cur.gtab[j], g);
-            unpack8(cur.gt[j], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
-          }
-          if (r.rrow) {
-            unpack8(res.v[c % EPI_RES_AHEAD][j], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += f[e];
-          }
-          *reinterpret_cast<uint4*>(r.orow + n + 8 * j) =
-              make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        }
-      }
-    }
-    if (c + EPI_RES_AHEAD < NCHUNK) epi_res_load(r, res.v[c % EPI_RES_AHEAD], c + EPI_RES_AHEAD);
   }
 }
 
