@@ -272,6 +272,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="stack", choices=["stack", "seqpar", "nvfp4", "dit", "small"])
+    ap.add_argument("--tokens-side", type=int, default=None,
+                    help="stack / dit workloads: side of the square token grid (default 128 = 16 384 tokens)")
     ap.add_argument("--graph", action="store_true",
                     help="replay the forward as one CUDA graph (sana_b200.graphs.GraphedForward)")
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
@@ -323,6 +325,8 @@ def main() -> None:
         b0, b1 = sharding.batch_partition(args.batch, world)[rank]
         Bl = b1 - b0
         grid = (64, 64) if nvfp4 else ((32, 32) if small else GRID)
+        if args.tokens_side and not (nvfp4 or small):
+            grid = (args.tokens_side, args.tokens_side)
         tokens = grid[0] * grid[1]
         shard = None
         total_units = args.batch * tokens * depth
@@ -336,11 +340,11 @@ def main() -> None:
                                                                          ", eager launches"))
         elif whole:
             workload = (f"whole Sana-1.6B DiT forward (patch embed + position table, timestep / caption embedders, "
-                        f"{depth} SanaMSBlocks, final layer, unpatchify), {GRID[0]}x{GRID[1]} latent x 32 channels = "
+                        f"{depth} SanaMSBlocks, final layer, unpatchify), {grid[0]}x{grid[1]} latent x 32 channels = "
                         f"{tokens} tokens, {TEXT} caption tokens x 2304, global batch {args.batch}")
         else:
             workload = (f"cfg3: Sana-1.6B stack, {depth} SanaMSBlocks, hidden {C}, {C // 32} LA heads x 32, FFN {HID}, "
-                        f"{GRID[0]}x{GRID[1]} grid = {tokens} tokens, global batch {args.batch}")
+                        f"{grid[0]}x{grid[1]} grid = {tokens} tokens, global batch {args.batch}")
         parallelism = f"dp{world}"
         scaling = "strong"
     else:
@@ -356,7 +360,7 @@ def main() -> None:
 
     model = None
     if whole:
-        model = sana_b200.SanaMS(input_size=GRID[0], patch_size=1, in_channels=32, hidden_size=C, depth=depth,
+        model = sana_b200.SanaMS(input_size=grid[0], patch_size=1, in_channels=32, hidden_size=C, depth=depth,
                                  num_heads=HEADS, mlp_ratio=2.5, class_dropout_prob=0.0, pred_sigma=False,
                                  caption_channels=2304, model_max_length=TEXT, y_norm=True, y_norm_scale_factor=0.01,
                                  attn_type="linear", ffn_type="glumbconv", linear_head_dim=32).eval()

@@ -213,6 +213,12 @@ class SanaMS(nn.Module):
         self.final_layer = T2IFinalLayer(hidden_size, self.patch_size, self.out_channels)
         self.logvar_linear = None
         self.pos_embed_ms = None
+        # The blocks' key / value projections of the caption depend on nothing the block loop
+        # computes: with this flag they are all launched on a second stream when the forward
+        # starts and each block waits only for its own (at small latents the GPU has idle SMs for
+        # them; captured in a CUDA graph they become a parallel branch).
+        self.overlap_caption_projections = True
+        self._side_stream = None
 
     @property
     def dtype(self):
@@ -262,8 +268,30 @@ class SanaMS(nn.Module):
                 mask = mask.repeat(y.shape[0] // mask.shape[0], 1)
             mask = mask.squeeze(1).squeeze(1)
 
-        for block in self.blocks:
-            x = block(x, y, t0, mask, (self.h, self.w), None, **kwargs)
+        caption_kv = [None] * len(self.blocks)
+        ready = None
+        if self.overlap_caption_projections and "caption_kv" not in kwargs:
+            cur = torch.cuda.current_stream()
+            if self._side_stream is None or self._side_stream.device != x.device:
+                self._side_stream = torch.cuda.Stream(device=x.device)
+            side = self._side_stream
+            side.wait_stream(cur)  # y is ready
+            ready = []
+            with torch.cuda.stream(side):
+                for i, block in enumerate(self.blocks):
+                    caption_kv[i] = block.cross_attn.project_kv(y)
+                    caption_kv[i].record_stream(cur)
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    ready.append(ev)
+        for i, block in enumerate(self.blocks):
+            if ready is not None:
+                torch.cuda.current_stream().wait_event(ready[i])
+                x = block(x, y, t0, mask, (self.h, self.w), None, caption_kv=caption_kv[i], **kwargs)
+            else:
+                x = block(x, y, t0, mask, (self.h, self.w), None, **kwargs)
+        if ready is not None:
+            torch.cuda.current_stream().wait_stream(self._side_stream)  # rejoin (needed under graph capture)
 
         x = self.final_layer(x, t)  # [B, N, p*p*out]
         return ops.unpatchify(_as2d(x), bs, self.out_channels, self.h, self.w, p)

@@ -266,14 +266,25 @@ class MultiHeadCrossAttention(nn.Module):
             self.q_norm = nn.Identity()
             self.k_norm = nn.Identity()
 
-    def _attend(self, x2d: torch.Tensor, cond: torch.Tensor, mask, B: int) -> torch.Tensor:
-        """Returns the attention output [B*N, C] before ``proj``."""
+    def project_kv(self, cond: torch.Tensor) -> torch.Tensor:
+        """Key / value projection of the text tokens, [B*L, 2C] (k | v), with the optional k norm
+        applied.  It depends on the caption only, so a caller may compute it ahead of the block
+        (on another stream, or once for several denoising steps) and pass it to ``_attend``."""
+        C = self.d_model
+        kv2d = ops.gemm(_as2d(cond), self.kv_linear.weight, bias=self.kv_linear.bias)
+        if isinstance(self.k_norm, RMSNorm):
+            ops.rmsnorm_(kv2d[:, :C], self.k_norm.weight, float(self.k_norm.eps))
+        return kv2d
+
+    def _attend(self, x2d: torch.Tensor, cond: torch.Tensor, mask, B: int, kv2d: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Returns the attention output [B*N, C] before ``proj``.  ``kv2d``: the result of
+        :meth:`project_kv` when it was computed ahead of time."""
         C, h, hd = self.d_model, self.num_heads, self.head_dim
         q = ops.gemm(x2d, self.q_linear.weight, bias=self.q_linear.bias)
-        kv2d = ops.gemm(_as2d(cond), self.kv_linear.weight, bias=self.kv_linear.bias)
+        if kv2d is None:
+            kv2d = self.project_kv(cond)
         if isinstance(self.q_norm, RMSNorm):
             ops.rmsnorm_(q, self.q_norm.weight, float(self.q_norm.eps))
-            ops.rmsnorm_(kv2d[:, :C], self.k_norm.weight, float(self.k_norm.eps))
         if mask is not None and (not torch.is_tensor(mask) or mask.ndim != 2):
             raise NotImplementedError("cross-attention mask must be None or a [B, L] 0/1 tensor")
         L = kv2d.shape[0] // B
@@ -356,7 +367,7 @@ class SanaMSBlock(nn.Module):
             qkv = _project(attn, "qkv", _as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
             o = attn._core(qkv, B, N, image_rotary_emb)
             x2 = _project(attn, "proj", o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
-        o = ca._attend(x2, y, mask, B)
+        o = ca._attend(x2, y, mask, B, kwargs.get("caption_kv"))
         x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
         z = ops.ln_modulate(x2.view(B, N, C), table, t, 3, 4, LN_EPS)
         u = mlp._expand(_as2d(z))
