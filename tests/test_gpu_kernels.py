@@ -293,3 +293,21 @@ def test_gemm_full_size_sampled_rows():
     rows = torch.arange(0, M, 129)[:100]
     ref = a[rows].cpu().double() @ w.cpu().double().t()
     assert nmax_err(out[rows], ref) < BF16_OUT
+
+
+def test_dwconv_glu_long_segments_sampled_channels():
+    """Full 1.6B width on four 128-row frames: the launch uses 256-row segments (two frames per
+    warp, so frame edges fall inside a segment); checked on a sample of channels against the
+    fp64 oracle evaluated on those channels only."""
+    frames, H, W, hid = 4, 128, 128, 5600
+    C2 = 2 * hid
+    g = torch.Generator(device=DEV).manual_seed(11)
+    u = (torch.randn(frames * H * W, C2, generator=g, device=DEV) * 0.7).bfloat16()
+    w = (torch.randn(C2, 1, 3, 3, generator=g, device=DEV) * 0.3).bfloat16()
+    b = (torch.randn(C2, generator=g, device=DEV) * 0.2).bfloat16()
+    out = ops.dwconv_glu(u, w, b, W, H)
+    assert ops.take_dwconv_glu_device_status() == 0
+    pick = torch.tensor([0, 1, 63, 64, 65, 2047, 2048, 5535, 5567, 5568, 5598, 5599], device=DEV)
+    both = torch.cat([pick, pick + hid])
+    ref = _dw_ref(u[:, both].cpu(), w[both].cpu(), b[both].cpu(), frames, H, W)
+    assert nmax_err(out[:, pick], ref) < BF16_OUT
