@@ -4,7 +4,7 @@ CUDA kernels for sm_100a behind a C ABI (include/sana_b200.h, built into
 sana_b200/lib/libsana_b200.so by ``python -m sana_b200.build``) and drop-in PyTorch modules
 that keep upstream's signatures.  There is no CPU path.
 """
-from . import ops, sharding, synthetic  # noqa: F401
+from . import graphs, ops, sharding, synthetic  # noqa: F401
 from ._lib import SanaLibraryError, load as load_library  # noqa: F401
 from .modules import BlockStack, ConvLayer, GLUMBConv, LiteLA, MultiHeadCrossAttention, RMSNorm, SanaMSBlock  # noqa: F401
 from .weight_pack import load_nvfp4_weights, pack_nvfp4_weights  # noqa: F401
