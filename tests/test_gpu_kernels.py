@@ -280,6 +280,33 @@ def test_gemm_strided_operands():
     assert nmax_err(outbuf[:, N:], ref) < BF16_OUT and torch.all(outbuf[:, :N] == 0)
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(2050, 328, 200), (77, 72, 64), (2307, 2240, 136)])
+def test_gemm_staged_epilogue_edges(variant, M, N, K):
+    """The bulk-tensor epilogue on ragged tiles: rows and columns that end inside a 32 x 64 box,
+    the output a column slice of a wider buffer (its neighbours must stay untouched), the
+    residual read in place from the output location, bias + gate on top."""
+    rpb = 500
+    B = (M + rpb - 1) // rpb
+    a = _r(M, K, seed=M).bfloat16().to(DEV)
+    w = _r(N, K, seed=N, scale=0.1).bfloat16().to(DEV)
+    bias = _r(N, seed=3, scale=0.2).bfloat16().to(DEV)
+    table = _r(6, N, seed=4, scale=0.3).bfloat16().to(DEV)
+    t = _r(B, 6 * N, seed=5, scale=0.3).bfloat16().to(DEV)
+    buf = _r(M, N + 128, seed=6).bfloat16().to(DEV)
+    before = buf.clone()
+    view = buf[:, 64:64 + N]
+    ref = _gemm_ref(a.cpu(), w.cpu(), bias.cpu(), 0, 0, (table.cpu(), t.cpu(), 2, rpb), before[:, 64:64 + N].cpu())
+    ops.set_gemm_variant(variant)
+    try:
+        ops.gemm(a, w, bias=bias, gate=(table, t, 2, rpb), residual=view, out=view)
+    finally:
+        ops.set_gemm_variant(0)
+    assert nmax_err(view, ref) < BF16_OUT
+    assert torch.equal(buf[:, :64], before[:, :64]) and torch.equal(buf[:, 64 + N:], before[:, 64 + N:])
+    assert ops.take_gemm_device_status() == 0
+
+
 def test_gemm_full_size_sampled_rows():
     """The 1.6B-width QKV projection at 16 384 tokens, checked on rows sampled from every
     128-row tile position against the CPU oracle."""
