@@ -190,6 +190,20 @@ def glumbconv_forward(x, p: Params, HW: Sequence[int], quant_fn=None) -> torch.T
     return x.reshape(B, Cout, N).permute(0, 2, 1)
 
 
+def glumbconv_temp_forward(x, p: Params, HW: Sequence[int]) -> torch.Tensor:
+    """GLUMBConvTemp.forward without frame mask and context parallelism,
+    diffusion/model/nets/basic_modules.py:238-266: GLUMBConv per frame, then
+    ``x + t_conv(x)`` with t_conv a (3, 1) convolution over (frames, pixels)."""
+    B, N, C = x.shape
+    T, H, W = HW
+    s = glumbconv_forward(x, p, HW)  # [B, N, C], frames stacked along N
+    xr = s.reshape(B, T, H * W, C).permute(0, 3, 1, 2)  # [B, C, T, HW]
+    wt = p["t_conv.weight"]
+    t_out = F.conv2d(xr, wt, None, padding=(wt.shape[2] // 2, 0))
+    out = xr + t_out
+    return out.permute(0, 2, 3, 1).reshape(B, N, C)
+
+
 def cross_attention_forward(x, cond, p: Params, num_heads: int, mask=None) -> torch.Tensor:
     """MultiHeadCrossAttention.forward, SDPA branch (no xformers),
     diffusion/model/nets/sana_blocks.py:69-98.  ``mask``: None or [B, L] of 0/1."""

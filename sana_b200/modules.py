@@ -242,6 +242,55 @@ class GLUMBConv(nn.Module):
         return out.reshape(B, N, -1)
 
 
+class GLUMBConvTemp(GLUMBConv):
+    """Mix-FFN of the video blocks: GLUMBConv per frame, then a 3-tap convolution along the
+    frame axis that mixes channels (``t_conv``: Conv2d(C, C, (3, 1)), no bias, zero padding in
+    time) added to the spatial result (diffusion/model/nets/basic_modules.py:200-257).  Token-
+    major, the three taps are three projections of the same tensor shifted by one frame, each
+    accumulated through the GEMM's residual epilogue."""
+
+    def __init__(self, in_features: int, hidden_features: int, out_feature=None, kernel_size=3, stride=1,
+                 padding=None, use_bias=False, norm=(None, None, None), act=("silu", "silu", None), t_kernel_size=3):
+        super().__init__(in_features, hidden_features, out_feature=out_feature, kernel_size=kernel_size, stride=stride,
+                         padding=padding, use_bias=use_bias, norm=norm, act=act)
+        if t_kernel_size != 3:
+            raise NotImplementedError("GLUMBConvTemp: only the 3-tap temporal convolution is covered")
+        C = self.out_feature
+        self.t_conv = nn.Conv2d(C, C, kernel_size=(t_kernel_size, 1), stride=1, padding=(t_kernel_size // 2, 0), bias=False)
+        nn.init.zeros_(self.t_conv.weight)
+
+    def _taps(self):
+        """The three [C, C] tap matrices as contiguous copies, rebuilt when the weight changes."""
+        w = self.t_conv.weight
+        tag = (w.data_ptr(), w._version, w.dtype, w.device)
+        cached = self.__dict__.get("_tap_cache")
+        if cached is None or cached[0] != tag:
+            cached = (tag, [w[:, :, k, 0].contiguous() for k in range(3)])
+            self.__dict__["_tap_cache"] = cached
+        return cached[1]
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, HW=None, **kwargs) -> torch.Tensor:
+        if HW is None or len(HW) != 3:
+            raise ValueError("HW must be a tuple of (T, H, W)")
+        if kwargs.get("frame_valid_mask") is not None:
+            raise NotImplementedError("frame_valid_mask is not covered")
+        if self.seq_shard is not None:
+            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
+        B, N, C = x.shape
+        T, H, W = HW
+        hw = H * W
+        s = _as2d(super().forward(x, HW=HW))  # spatial result, token-major [B*N, C]
+        w_prev, w_mid, w_next = self._taps()
+        y = ops.gemm(s, w_mid, residual=s)  # x + centre tap
+        for b in range(B):  # frames t >= 1 take frame t-1, frames t <= T-2 take frame t+1 (zero padding at the ends)
+            lo, hi = b * N, (b + 1) * N
+            if T > 1:
+                ops.gemm(s[lo:hi - hw], w_prev, residual=y[lo + hw:hi], out=y[lo + hw:hi])
+                ops.gemm(s[lo + hw:hi], w_next, residual=y[lo:hi - hw], out=y[lo:hi - hw])
+        return y.reshape(B, N, C)
+
+
 class MultiHeadCrossAttention(nn.Module):
     """Softmax attention of image tokens over the text tokens (upstream's SDPA branch), with
     the projections on the GEMM kernel and the softmax core on its own kernel."""

@@ -140,6 +140,24 @@ def pag_case(R, seed=8):
     return out
 
 
+def glumbconv_temp_case(R, seed=9):
+    """Upstream's GLUMBConvTemp (video Mix-FFN) on 3 frames of 5 x 8 tokens, two samples."""
+    C, hid, HW, B = 64, 160, (3, 5, 8), 2
+    g = torch.Generator().manual_seed(seed)
+    params = {k[len("mlp."):]: v for k, v in synthetic.make_block_params(C, hid, seed, std=0.05).items()
+              if k.startswith("mlp.")}
+    params["t_conv.weight"] = torch.randn(C, C, 3, 1, generator=g) * 0.05
+    x = torch.randn(B, HW[0] * HW[1] * HW[2], C, generator=g) * 0.5
+    out = {"C": C, "hid": hid, "HW": HW, "params": params, "x": x}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            m = R.basic_modules.GLUMBConvTemp(in_features=C, hidden_features=hid, use_bias=(True, True, False),
+                                              norm=(None, None, None), act=("silu", "silu", None)).eval()
+            m.load_state_dict(params, strict=True)
+            out[f"out_{tag}"] = m.to(dt)(x.to(dt), HW=HW)
+    return out
+
+
 SANA_MS_SMALL = dict(input_size=8, patch_size=1, in_channels=32, hidden_size=64, depth=2, num_heads=2, mlp_ratio=2.5,
                      class_dropout_prob=0.0, pred_sigma=False, caption_channels=48, model_max_length=10, y_norm=True,
                      attn_type="linear", ffn_type="glumbconv", mlp_acts=("silu", "silu", None), linear_head_dim=32,
@@ -203,6 +221,7 @@ def main():
         "block_cfg2": lambda: block_cfg2_case(R),
         "sana_ms_small": lambda: sana_ms_case(R),
         "pag_litela": lambda: pag_case(R),
+        "glumbconv_temp": lambda: glumbconv_temp_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():

@@ -299,3 +299,19 @@ def test_pag_processors(golden, dt, tol):
         assert out.shape == ref.shape and nmax_err(out, ref) < tol
         if dt == torch.float32:
             assert nmax_err(out, g[f"{key}_f32"]) < TOL_F32
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_glumbconv_temp(golden, dt, tol):
+    """Video Mix-FFN: per-frame GLUMBConv + 3-tap temporal channel mix, against upstream."""
+    g = golden("glumbconv_temp")
+    m = sana_b200.GLUMBConvTemp(in_features=g["C"], hidden_features=g["hid"], use_bias=(True, True, False),
+                                norm=(None, None, None), act=("silu", "silu", None)).eval()
+    m.load_state_dict(g["params"], strict=True)
+    m = m.to(DEV, dt)
+    out = m(g["x"].to(DEV, dt), HW=g["HW"])
+    r = (lambda v: v.to(dt).float()) if dt != torch.float32 else (lambda v: v)
+    ref = O.glumbconv_temp_forward(r(g["x"]), {k: r(v) for k, v in g["params"].items()}, g["HW"])
+    assert out.shape == ref.shape and nmax_err(out, ref) < tol
+    if dt == torch.float32:
+        assert nmax_err(out, g["out_f32"]) < TOL_F32
