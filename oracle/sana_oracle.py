@@ -300,6 +300,21 @@ def sincos_pos_embed_2d(embed_dim: int, grid_size, pe_interpolation: float = 1.0
     return np.concatenate([sincos_1d(embed_dim // 2, grid[0]), sincos_1d(embed_dim // 2, grid[1])], axis=1)
 
 
+def final_layer_forward(x, t, p: Params) -> torch.Tensor:
+    """T2IFinalLayer.forward / forward_frame_aware, diffusion/model/nets/sana_blocks.py:907-925:
+    t [B, C], or [B, 1, F, C] with one modulation vector per frame.  Keys: scale_shift_table,
+    linear.weight, linear.bias."""
+    B, N, C = x.shape
+    if t.dim() > 2:
+        num_frames = t.shape[2]
+        shift, scale = (p["scale_shift_table"][None, None, :, :] + t.transpose(1, 2)).chunk(2, dim=-2)
+        x = t2i_modulate(layer_norm(x).reshape(B, num_frames, -1, C), shift, scale).reshape(B, N, C)
+    else:
+        shift, scale = (p["scale_shift_table"][None] + t[:, None]).chunk(2, dim=1)
+        x = t2i_modulate(layer_norm(x), shift, scale)
+    return F.linear(x, p["linear.weight"], p["linear.bias"])
+
+
 def sana_ms_forward(x, timestep, y, p: Params, *, depth: int, num_heads: int, patch_size: int, out_channels: int,
                     base_size: int, mask=None, pe_interpolation: float = 1.0, y_norm: bool = False,
                     norm_eps: float = 1e-5, timestep_norm_scale_factor: float = 1.0, use_pe: bool = True,

@@ -157,9 +157,16 @@ class T2IFinalLayer(nn.Module):
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
-        if t.dim() > 2:
-            raise NotImplementedError("frame-aware final layer (video) is not covered")
         B, N, C = x.shape
+        if t.dim() > 2:
+            # frame-aware (sana_blocks.py:907-917): t [B, 1, F, C], one modulation vector per frame;
+            # the frames of a sample are contiguous token ranges, so (sample, frame) acts as the batch
+            F_ = t.shape[2]
+            if N % F_:
+                raise ValueError("the token count must be a multiple of the number of frames")
+            z = ops.ln_modulate_rows(x.reshape(B * F_, N // F_, C), self.scale_shift_table,
+                                     t.reshape(B * F_, 1, C), 0, 1, 0, 0, 1e-6).reshape(B, N, C)
+            return ops.gemm(_as2d(z), self.linear.weight, bias=self.linear.bias).view(B, N, -1)
         z = ops.ln_modulate_rows(x, self.scale_shift_table, t.reshape(B, 1, C), 0, 1, 0, 0, 1e-6)
         return ops.gemm(_as2d(z), self.linear.weight, bias=self.linear.bias).view(B, N, -1)
 

@@ -158,6 +158,20 @@ def glumbconv_temp_case(R, seed=9):
     return out
 
 
+def final_layer_case(R, seed=10):
+    """Upstream's T2IFinalLayer with one modulation vector per sample and per frame."""
+    C, B, Fr, P = 64, 2, 3, 10
+    g = torch.Generator().manual_seed(seed)
+    m = R.sana_blocks.T2IFinalLayer(C, 1, 32).eval()
+    params = {k: torch.randn(v.shape, generator=g) * 0.2 for k, v in m.state_dict().items()}
+    m.load_state_dict(params, strict=True)
+    x = torch.randn(B, Fr * P, C, generator=g)
+    t = torch.randn(B, C, generator=g) * 0.3
+    tf = torch.randn(B, 1, Fr, C, generator=g) * 0.3
+    with torch.no_grad():
+        return {"C": C, "params": params, "x": x, "t": t, "t_frames": tf, "out": m(x, t), "out_frames": m(x, tf)}
+
+
 SANA_MS_SMALL = dict(input_size=8, patch_size=1, in_channels=32, hidden_size=64, depth=2, num_heads=2, mlp_ratio=2.5,
                      class_dropout_prob=0.0, pred_sigma=False, caption_channels=48, model_max_length=10, y_norm=True,
                      attn_type="linear", ffn_type="glumbconv", mlp_acts=("silu", "silu", None), linear_head_dim=32,
@@ -222,6 +236,7 @@ def main():
         "sana_ms_small": lambda: sana_ms_case(R),
         "pag_litela": lambda: pag_case(R),
         "glumbconv_temp": lambda: glumbconv_temp_case(R),
+        "final_layer": lambda: final_layer_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():

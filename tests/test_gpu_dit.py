@@ -120,3 +120,17 @@ def test_graph_replay_matches_eager(golden):
     assert torch.equal(fwd(x, ts, y), m(x, ts, y, mask=mask))
     x2, ts2 = (x * 0.5 + 0.1).contiguous(), torch.tensor([5.0, 700.0], device=DEV)
     assert torch.equal(fwd(x2, ts2, y), m(x2, ts2, y, mask=mask))
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_final_layer_per_sample_and_per_frame(golden, dt, tol):
+    g = golden("final_layer")
+    m = dit.T2IFinalLayer(g["C"], 1, 32).eval()
+    m.load_state_dict(g["params"], strict=True)
+    m = m.to(DEV, dt)
+    r = (lambda v: v.to(dt).float()) if dt != torch.float32 else (lambda v: v)
+    p = {k: r(v) for k, v in g["params"].items()}
+    for key in ("t", "t_frames"):
+        out = m(g["x"].to(DEV, dt), g[key].to(DEV, dt))
+        ref = O.final_layer_forward(r(g["x"]), r(g[key]), p)
+        assert out.shape == ref.shape and nmax_err(out, ref) < tol
