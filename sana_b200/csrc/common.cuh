@@ -33,6 +33,19 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();  // SMs of the current device (cached per device)
 
+// One flag per device for set-up that must happen once on every device the process uses
+// (function attributes live in a device's context).  A lost race repeats harmless work.
+struct OncePerDevice {
+  bool done[64] = {};
+  bool first_time() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return true;
+    if (done[d]) return false;
+    done[d] = true;
+    return true;
+  }
+};
+
 // ---- small device helpers -------------------------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }

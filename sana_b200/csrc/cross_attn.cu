@@ -251,11 +251,10 @@ static int launch_ca_bf16(const void* q, int64_t ldq, const void* k, const void*
   const int nkc = (int)ceil_div(L, CA_BK);
   const int smem_bytes = (CA_BQ + 4 * CA_BK) * (HDP + 8) * 2 + nkc * CA_BK * 4;
   if (smem_bytes > 227 * 1024) return fail(SANA_ERR_UNSUPPORTED, "sana_cross_attention: too many keys (%lld)", (long long)L);
-  static bool attr_done = false;
-  if (!attr_done) {
+  static OncePerDevice attr_once;
+  if (attr_once.first_time()) {
     cudaError_t e = cudaFuncSetAttribute(cross_attn_bf16_kernel<HDP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(cross_attn)");
-    attr_done = true;
   }
   const dim3 grid((unsigned)ceil_div(N, CA_BQ), (unsigned)heads, (unsigned)B);
   const float scale_log2e = 1.4426950408889634f / sqrtf((float)hd);

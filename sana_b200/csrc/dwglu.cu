@@ -418,11 +418,10 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
     a.seg_rows = seg;
     const int64_t gz = ceil_div(rows, seg);
     SANA_REQUIRE(gy < 65536 && gz < 65536, "sana_dwconv_glu: grid too large");
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OncePerDevice attr_once;
+    if (attr_once.first_time()) {
       cudaError_t e = cudaFuncSetAttribute(dwconv_glu_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DW_SMEM_BYTES);
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dwconv_glu)");
-      attr_set = true;
     }
     dwconv_glu_bf16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)gz), DW_THREADS, DW_SMEM_BYTES, st>>>(tmU3, tmU, tmTop, tmBot, a);
   } else if (dtype == SANA_F32) {

@@ -386,11 +386,10 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, F4_BN, 128);
   if (rc) return rc;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static OncePerDevice attr_once;
+  if (attr_once.first_time()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F4_SMEM_BYTES);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_nvfp4_tc)");
-    attr_done = true;
   }
   F4Args a;
   a.out = static_cast<__nv_bfloat16*>(out);

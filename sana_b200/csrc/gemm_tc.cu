@@ -292,12 +292,11 @@ static int launch_bn(const CUtensorMap& tmA, const void* Wt, int64_t ldw, int64_
     rc = make_tmap(&tmRes, args.ep.residual, args.M, N, args.ep.ldr, 32);
     if (rc) return rc;
   }
-  static bool attr_done = false;
-  if (!attr_done) {
+  static OncePerDevice attr_once;
+  if (attr_once.first_time()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_bf16_tc)");
-    attr_done = true;
   }
   args.tiles_n = (int)ceil_div(N, BN);
   const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n;

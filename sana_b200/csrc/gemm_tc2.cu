@@ -289,12 +289,11 @@ static int launch_pair_bn(const void* A, int64_t lda, const void* Wt, int64_t ld
   } else {
     tmRes = tmOut;
   }
-  static bool attr_done = false;
-  if (!attr_done) {
+  static OncePerDevice attr_once;
+  if (attr_once.first_time()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_bf16_tc2)");
-    attr_done = true;
   }
   args.tiles_n = (int)ceil_div(N, BN);
   const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n;
