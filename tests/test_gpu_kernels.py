@@ -145,7 +145,8 @@ def _dw_ref(u, w, b, frames, H, W):
 
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, BF16_OUT)])
 @pytest.mark.parametrize("frames,H,W,hid,bias", [(1, 6, 5, 8, True), (2, 4, 7, 160, True), (3, 5, 8, 72, False),
-                                                  (1, 32, 32, 2880, True), (4, 9, 33, 200, True), (1, 70, 17, 64, True)])
+                                                  (1, 32, 32, 2880, True), (4, 9, 33, 200, True), (1, 70, 17, 64, True),
+                                                  (1, 4, 2, 16, True), (1, 1, 1, 8, True), (1, 2, 9, 24, False)])
 def test_dwconv_glu(dt, tol, frames, H, W, hid, bias):
     C2 = 2 * hid
     u = _r(frames * H * W, C2, seed=hid + W).to(dt)
