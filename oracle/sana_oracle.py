@@ -158,6 +158,80 @@ def lite_la_apply(q_relu: torch.Tensor, state: torch.Tensor, eps: float) -> torc
     return out[..., :-1] / (out[..., -1:] + eps)
 
 
+def wan_rotary_freqs(head_dim: int, fhw: Sequence[int], theta: float = 10000.0, max_seq_len: int = 1024,
+                     fhw_dim: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """WanRotaryPosEmbed, diffusion/model/nets/sana_blocks.py:1361-1410 (with
+    get_1d_rotary_pos_embed(use_real=False, freqs_dtype=float64), :1483-1547): complex128
+    [1, 1, f*h*w, head_dim/2]; the head's channel pairs are split into a frame, a row and a column
+    group, each rotating by its own coordinate."""
+    if fhw_dim is not None:
+        t_dim, h_dim, w_dim = fhw_dim
+    else:
+        h_dim = w_dim = 2 * (head_dim // 6)
+        t_dim = head_dim - h_dim - w_dim
+    f, h, w = fhw
+    parts = []
+    for dim, count, shape in ((t_dim, f, (f, 1, 1)), (h_dim, h, (1, h, 1)), (w_dim, w, (1, 1, w))):
+        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64)[: dim // 2] / dim))
+        ang = torch.outer(torch.arange(max_seq_len)[:count], inv)
+        parts.append(torch.polar(torch.ones_like(ang), ang).view(*shape, -1).expand(f, h, w, -1))
+    return torch.cat(parts, dim=-1).reshape(1, 1, f * h * w, -1)
+
+
+def rotate_pairs_complex(x: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
+    """The inner `apply_rotary_emb` of LiteLAReLURope.forward, sana_blocks.py:359-362:
+    x [B, h, D, N], freqs complex [1, 1, N, D/2]; channel pairs (2p, 2p+1) multiply, as complex
+    numbers in float64, by freqs[n, p]; the result is cast back to x's dtype."""
+    xr = torch.view_as_complex(x.permute(0, 1, 3, 2).to(torch.float64).unflatten(3, (-1, 2)))
+    out = torch.view_as_real(xr * freqs).flatten(3, 4).permute(0, 1, 3, 2)
+    return out.type_as(x)
+
+
+def lite_la_relu_rope_forward(x, p: Params, heads: int, rotary_emb: torch.Tensor, eps: float = 1e-15,
+                              fp32_attention: bool = False, norm_eps: float = 1e-5) -> torch.Tensor:
+    """LiteLAReLURope.forward, diffusion/model/nets/sana_blocks.py:339-388: ReLU feature map first,
+    then the rotation on the numerator's q and k only; the normaliser uses the unrotated ones.
+    Rounds where upstream rounds (in bf16 the two matmuls and `z` run in bf16 unless
+    ``fp32_attention``)."""
+    B, N, C = x.shape
+    hd = C // heads
+    qkv = F.linear(x, p["qkv.weight"], p.get("qkv.bias")).reshape(B, N, 3, C)
+    q, k, v = qkv.unbind(2)
+    dtype = q.dtype
+    if "q_norm.weight" in p:  # qk_norm=True, sana_blocks.py:329-331,346-347
+        q = rms_norm(q, p["q_norm.weight"], norm_eps)
+        k = rms_norm(k, p["k_norm.weight"], norm_eps)
+    q = F.relu(q.transpose(-1, -2).reshape(B, heads, hd, N))
+    k = F.relu(k.transpose(-1, -2).reshape(B, heads, hd, N))
+    v = v.transpose(-1, -2).reshape(B, heads, hd, N)
+    q_rot = rotate_pairs_complex(q, rotary_emb)
+    k_rot = rotate_pairs_complex(k, rotary_emb)
+    if fp32_attention:
+        q_rot, k_rot, v = q_rot.float(), k_rot.float(), v.float()
+    z = 1 / (k.sum(dim=-1, keepdim=True).transpose(-2, -1) @ q + eps)
+    vk = torch.matmul(v, k_rot.transpose(-1, -2))
+    out = torch.matmul(vk, q_rot)
+    out = (out * z).to(dtype)
+    out = out.view(B, C, N).permute(0, 2, 1)
+    return F.linear(out, p["proj.weight"], p["proj.bias"])
+
+
+def lite_la_rope_state(k_relu: torch.Tensor, k_rot: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Token-major restatement of `vk` and of the key sum of LiteLAReLURope (sana_blocks.py:380-382):
+    k_relu, k_rot, v [B, N, h, d] -> state [B, h, d+1, d]; rows 0..d-1 hold
+    sum_n v[n, i] k_rot[n, j], row d holds sum_n k_relu[n, j] (unrotated)."""
+    vk = torch.einsum("bnhi,bnhj->bhij", v, k_rot)
+    return torch.cat([vk, k_relu.sum(1)[:, :, None, :]], dim=2)
+
+
+def lite_la_rope_apply(q_relu: torch.Tensor, q_rot: torch.Tensor, state: torch.Tensor, eps: float) -> torch.Tensor:
+    """Second product and normalisation (sana_blocks.py:380,383-385), token-major:
+    q_relu, q_rot [B, N, h, d], state [B, h, d+1, d] -> [B, N, h, d]."""
+    num = torch.einsum("bhij,bnhj->bnhi", state[:, :, :-1], q_rot)
+    den = torch.einsum("bhj,bnhj->bnh", state[:, :, -1], q_relu)
+    return num / (den[..., None] + eps)
+
+
 def glumbconv_forward(x, p: Params, HW: Sequence[int], quant_fn=None) -> torch.Tensor:
     """GLUMBConv.forward / _apply_spatial, diffusion/model/nets/basic_modules.py:161-199.
 

@@ -158,6 +158,31 @@ def glumbconv_temp_case(R, seed=9):
     return out
 
 
+def litela_relu_rope_case(R, seed=11):
+    """Upstream's LiteLAReLURope (Sana-Video self-attention: ReLU, then a complex rotation of the
+    numerator's q and k) with WanRotaryPosEmbed frequencies; heads of 48 channels, with and
+    without qk_norm."""
+    C, heads, fhw, B = 96, 2, (2, 3, 5), 2
+    N = fhw[0] * fhw[1] * fhw[2]
+    g = torch.Generator().manual_seed(seed)
+    params = {"qkv.weight": torch.randn(3 * C, C, generator=g) * 0.08,
+              "proj.weight": torch.randn(C, C, generator=g) * 0.08,
+              "proj.bias": torch.randn(C, generator=g) * 0.05}
+    norm = {"q_norm.weight": 1.0 + 0.1 * torch.randn(C, generator=g),
+            "k_norm.weight": 1.0 + 0.1 * torch.randn(C, generator=g)}
+    x = torch.randn(B, N, C, generator=g) * 0.7
+    rope = R.sana_blocks.WanRotaryPosEmbed(attention_head_dim=C // heads, patch_size=(1, 1, 1), max_seq_len=1024)
+    freqs = rope(fhw, torch.device("cpu"))
+    out = {"C": C, "heads": heads, "fhw": fhw, "params": params, "norm_params": norm, "x": x, "freqs": freqs}
+    with torch.no_grad():
+        for qk_norm, tag_n in ((False, ""), (True, "_qknorm")):
+            for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+                m = R.sana_blocks.LiteLAReLURope(C, C, heads=heads, eps=1e-8, qk_norm=qk_norm).eval()
+                m.load_state_dict({**params, **(norm if qk_norm else {})}, strict=True)
+                out[f"out{tag_n}_{tag}"] = m.to(dt)(x.to(dt), rotary_emb=freqs)
+    return out
+
+
 def final_layer_case(R, seed=10):
     """Upstream's T2IFinalLayer with one modulation vector per sample and per frame."""
     C, B, Fr, P = 64, 2, 3, 10
@@ -237,6 +262,7 @@ def main():
         "pag_litela": lambda: pag_case(R),
         "glumbconv_temp": lambda: glumbconv_temp_case(R),
         "final_layer": lambda: final_layer_case(R),
+        "litela_relu_rope": lambda: litela_relu_rope_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():
