@@ -178,6 +178,36 @@ int sana_la_apply(const void* q, int64_t ldq, const float* state, void* out, int
                   int64_t N, int64_t H, float eps, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * ReLU linear attention with the rotation AFTER the feature map (self-attention of Sana-Video),
+ * for heads of D channels, D a multiple of 16 in [16, 128] (upstream's 2B video model: 112):
+ *   rot(x)[n, 2p]   = x[n, 2p] cos[n, p] - x[n, 2p+1] sin[n, p]
+ *   rot(x)[n, 2p+1] = x[n, 2p] sin[n, p] + x[n, 2p+1] cos[n, p]          (channel pairs of a head)
+ *   state[b, h, i, j] = sum_n v[b,n,h,i] rot(relu(k))[b,n,h,j]  (i < D);  state[b, h, D, j] = sum_n relu(k[b,n,h,j])
+ *   o[b, n, h, i] = (sum_j state[b,h,i,j] rot(relu(q))[b,n,h,j]) / (sum_j state[b,h,D,j] relu(q[b,n,h,j]) + eps)
+ * Replaces, in LiteLAReLURope.forward (diffusion/model/nets/sana_blocks.py:339-388), the ReLU
+ * (:355-357), the complex multiplication by `rotary_emb` of q and k (:359-365), `vk = v @ k_rotated^T`
+ * (:382), `z = 1 / (k.sum(-1)^T @ q + eps)` with the UNROTATED q and k (:380), `out = vk @ q_rotated`
+ * (:383) and `out * z` with the cast back to the model dtype (:385), written token-major so that no
+ * transpose precedes the output projection (:387-388).
+ *   k, v, q, out [B*N, *] rows of H*D contiguous channels (head-major), row strides in elements
+ *   cos_table, sin_table [N, D/2] fp32: real and imaginary part of upstream's complex128
+ *     `rotary_emb[0, 0]` (WanRotaryPosEmbed.forward, sana_blocks.py:1393-1410), indexed by the
+ *     token's position inside its sample
+ *   state [B, H, D+1, D] fp32; workspace: sana_la_rope_state_workspace_bytes(B, N, H, D) bytes,
+ *     16-byte aligned, holds per-chunk partial states added in a fixed order (bit-reproducible).
+ * bf16: the rotated q and k are rounded to bf16 (as upstream's `type_as`) and the state enters the
+ * second product rounded to bf16 (as upstream's bf16 `vk`); sums accumulate in fp32 and the
+ * normaliser is computed in fp32.  fp32: plain fp32 arithmetic.
+ */
+int64_t sana_la_rope_state_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D);
+int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
+                       float* state, void* workspace, int64_t workspace_bytes, int64_t B, int64_t N, int64_t H,
+                       int64_t D, int dtype, void* stream);
+int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_table, const float* sin_table,
+                       const float* state, void* out, int64_t ldo, int64_t B, int64_t N, int64_t H, int64_t D,
+                       float eps, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * 3x3 depthwise conv + bias + SiLU-GLU on channels-last rows:
  *   w[y, x, c]  = b[c] + sum_{dy,dx} K[c, dy, dx] * u[y+dy-1, x+dx-1, c]   (zero outside a frame)
  *   out[y, x, c] = w[y, x, c] * silu(w[y, x, hid + c]),  c in [0, hid)

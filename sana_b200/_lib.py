@@ -56,6 +56,9 @@ SIGNATURES = {
     "sana_halo_exchange_buffer_bytes": (_i64, [_i64]),
     "sana_halo_exchange": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, C.c_uint32, _vp]),
     "sana_la_apply": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "sana_la_rope_state_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
+    "sana_la_rope_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sana_la_rope_apply": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_cross_attention": (_i32, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_dwconv_glu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_gemm": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "la_plan.cuh"
 
 namespace sana {
 
@@ -332,34 +333,6 @@ la_apply_f32_kernel(const float* __restrict__ qp, int64_t ldq, const float* __re
       *reinterpret_cast<float4*>(orow + 4 * i4) = make_float4(r[0], r[1], r[2], r[3]);
     }
   }
-}
-
-// Host-side split of the token axis into chunks of Lc tokens (a multiple of 64).  `units` CTAs
-// exist per chunk (samples x head groups) and `slots` CTAs are resident at once; a CTA's time is
-// its Lc tokens plus a fixed cost of `overhead` token-equivalents (state load, or partial-state
-// write + re-read).  Picks the chunk count that minimises waves x (Lc + overhead), i.e. avoids
-// a mostly empty last wave.
-static void la_chunking(int64_t units, int64_t N, int64_t slots, int64_t overhead, int* Lc, int* nchunks) {
-  const int64_t max_chunks = ceil_div(N, 64) < 4096 ? ceil_div(N, 64) : 4096;
-  int64_t best_cost = -1, best_lc = 64;
-  for (int64_t nch = 1; nch <= max_chunks; ++nch) {
-    const int64_t lc = ceil_div(ceil_div(N, nch), 64) * 64;
-    const int64_t real = ceil_div(N, lc);
-    const int64_t cost = ceil_div(units * real, slots) * (lc + overhead);
-    if (best_cost < 0 || cost < best_cost) best_cost = cost, best_lc = lc;
-  }
-  *Lc = (int)best_lc;
-  *nchunks = (int)ceil_div(N, best_lc);
-}
-
-template <typename Kernel>
-static int64_t resident_ctas(Kernel kernel, int threads) {
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) {
-    cudaGetLastError();
-    per_sm = 1;
-  }
-  return (int64_t)per_sm * sm_count();
 }
 
 static void la_state_plan(int64_t B, int64_t N, int64_t H, int dtype, int* Lc, int* nchunks) {

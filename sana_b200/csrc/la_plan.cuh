@@ -1,0 +1,35 @@
+// Host-side launch planning shared by the linear-attention kernels.
+#pragma once
+#include "common.cuh"
+
+namespace sana {
+
+// Host-side split of the token axis into chunks of Lc tokens (a multiple of 64).  `units` CTAs
+// exist per chunk (samples x head groups) and `slots` CTAs are resident at once; a CTA's time is
+// its Lc tokens plus a fixed cost of `overhead` token-equivalents (state load, or partial-state
+// write + re-read).  Picks the chunk count that minimises waves x (Lc + overhead), i.e. avoids
+// a mostly empty last wave.
+inline void la_chunking(int64_t units, int64_t N, int64_t slots, int64_t overhead, int* Lc, int* nchunks) {
+  const int64_t max_chunks = ceil_div(N, 64) < 4096 ? ceil_div(N, 64) : 4096;
+  int64_t best_cost = -1, best_lc = 64;
+  for (int64_t nch = 1; nch <= max_chunks; ++nch) {
+    const int64_t lc = ceil_div(ceil_div(N, nch), 64) * 64;
+    const int64_t real = ceil_div(N, lc);
+    const int64_t cost = ceil_div(units * real, slots) * (lc + overhead);
+    if (best_cost < 0 || cost < best_cost) best_cost = cost, best_lc = lc;
+  }
+  *Lc = (int)best_lc;
+  *nchunks = (int)ceil_div(N, best_lc);
+}
+
+template <typename Kernel>
+inline int64_t resident_ctas(Kernel kernel, int threads, size_t dynamic_smem = 0) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dynamic_smem) != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    per_sm = 1;
+  }
+  return (int64_t)per_sm * sm_count();
+}
+
+}  // namespace sana

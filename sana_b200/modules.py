@@ -14,7 +14,7 @@ ours.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
@@ -158,6 +158,102 @@ class LiteLA(nn.Module):
 
     def __repr__(self):
         return f"EPS{self.eps}-" + super().__repr__()
+
+
+def wan_rotary_freqs(head_dim: int, fhw: Sequence[int], theta: float = 10000.0, max_seq_len: int = 1024,
+                     fhw_dim: Optional[Sequence[int]] = None, device=None) -> torch.Tensor:
+    """Frequencies of upstream's WanRotaryPosEmbed (sana_blocks.py:1361-1410): complex128
+    [1, 1, f*h*w, head_dim/2].  The channel pairs of a head split into a frame, a row and a column
+    group; group g of a token at (f, h, w) rotates by coordinate * theta^(-2i / dim_g)."""
+    if fhw_dim is not None:
+        t_dim, h_dim, w_dim = fhw_dim
+        if t_dim + h_dim + w_dim != head_dim:
+            raise ValueError(f"head_dim {head_dim} must equal sum(fhw_dim) {t_dim + h_dim + w_dim}")
+    else:
+        h_dim = w_dim = 2 * (head_dim // 6)
+        t_dim = head_dim - h_dim - w_dim
+    f, h, w = (int(v) for v in fhw)
+    if max(f, h, w) > max_seq_len:
+        raise ValueError("a grid side exceeds max_seq_len")
+    groups = []
+    for dim, shape in ((t_dim, (f, 1, 1)), (h_dim, (1, h, 1)), (w_dim, (1, 1, w))):
+        rate = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device)[: dim // 2] / dim))
+        angle = torch.outer(torch.arange(max(shape), device=device), rate)
+        groups.append(torch.polar(torch.ones_like(angle), angle).view(*shape, -1).expand(f, h, w, -1))
+    return torch.cat(groups, dim=-1).reshape(1, 1, f * h * w, -1)
+
+
+class LiteLAReLURope(nn.Module):
+    """Linear attention with the ReLU feature map first and the rotation after it, on the
+    numerator's q and k only (upstream's LiteLAReLURope, sana_blocks.py:304-388; self-attention of
+    Sana-Video).  Same constructor arguments, attributes and state-dict keys as upstream.
+    ``rotary_emb`` is upstream's complex tensor [1, 1, N, head_dim/2] (or a (cos, sin) pair of fp32
+    [N, head_dim/2] tables); its fp32 tables are cached per tensor."""
+
+    PAD_VAL = 1
+
+    def __init__(self, in_dim: int, out_dim: int, heads: Optional[int] = None, heads_ratio: float = 1.0, dim=32,
+                 eps=1e-15, use_bias=False, qk_norm=False, norm_eps=1e-5):
+        super().__init__()
+        heads = heads or int(out_dim // dim * heads_ratio)
+        head_dim = out_dim // heads
+        if in_dim != out_dim or out_dim % heads != 0 or head_dim % 16 != 0 or not 16 <= head_dim <= 128:
+            raise NotImplementedError("the kernels need in_dim == out_dim and a head dimension that is a multiple "
+                                      "of 16 in [16, 128]")
+        self.num_heads = heads
+        self.scale = (in_dim // heads) ** -0.5
+        self.qkv = nn.Linear(in_dim, in_dim * 3, bias=use_bias)
+        self.attn_drop = nn.Dropout(0.0)
+        self.proj = nn.Linear(in_dim, in_dim)
+        self.proj_drop = nn.Dropout(0.0)
+        self.in_dim = in_dim
+        self.out_dim = out_dim
+        self.heads = heads
+        self.dim = head_dim
+        self.eps = eps
+        self.kernel_func = nn.ReLU(inplace=False)
+        if qk_norm:
+            self.q_norm = RMSNorm(in_dim, scale_factor=1.0, eps=norm_eps)
+            self.k_norm = RMSNorm(in_dim, scale_factor=1.0, eps=norm_eps)
+        else:
+            self.q_norm = nn.Identity()
+            self.k_norm = nn.Identity()
+        self.qkv_store_buffer = None
+        self.nvfp4 = False
+        self._tables = None  # (key, cos, sin)
+
+    def rotary_tables(self, rotary_emb, N: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        """fp32 [N, head_dim/2] cos / sin tables of ``rotary_emb`` on ``device``."""
+        if isinstance(rotary_emb, (tuple, list)):
+            cos, sin = rotary_emb
+            return (cos.to(device=device, dtype=torch.float32).contiguous(),
+                    sin.to(device=device, dtype=torch.float32).contiguous())
+        key = (rotary_emb.data_ptr(), rotary_emb._version, tuple(rotary_emb.shape), str(device))
+        if self._tables is None or self._tables[0] != key:
+            if not rotary_emb.is_complex() or rotary_emb.numel() != N * (self.dim // 2):
+                raise ValueError("rotary_emb must be complex [1, 1, N, head_dim / 2]")
+            fr = rotary_emb.reshape(N, self.dim // 2)
+            self._tables = (key, fr.real.to(device=device, dtype=torch.float32).contiguous(),
+                            fr.imag.to(device=device, dtype=torch.float32).contiguous())
+        return self._tables[1], self._tables[2]
+
+    def _core(self, qkv: torch.Tensor, B: int, N: int, rotary_emb) -> torch.Tensor:
+        """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``)."""
+        C = self.out_dim
+        if rotary_emb is None:
+            raise ValueError("LiteLAReLURope needs rotary_emb")
+        if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
+            ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
+            ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
+        cos, sin = self.rotary_tables(rotary_emb, N, qkv.device)
+        state = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, N, self.heads, self.dim)
+        return ops.la_rope_apply(qkv[:, :C], cos, sin, state, B, N, self.heads, self.dim, float(self.eps))
+
+    def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_mask=None, **kwargs):
+        B, N, C = x.shape
+        qkv = _project(self, "qkv", _as2d(x), self.qkv.weight, bias=self.qkv.bias)
+        o = self._core(qkv, B, N, rotary_emb)
+        return _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
 
 
 class ConvLayer(nn.Module):

@@ -275,6 +275,57 @@ def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: 
     return out
 
 
+def _rope_tables(cos: torch.Tensor, sin: torch.Tensor, N: int, D: int, what: str) -> None:
+    for tb in (cos, sin):
+        if tb.shape != (N, D // 2) or tb.dtype != torch.float32 or not tb.is_contiguous():
+            raise SanaLibraryError(f"{what}: cos / sin tables must be contiguous fp32 [N, head_dim / 2]")
+
+
+def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, H: int,
+                  D: int) -> torch.Tensor:
+    """State of the ReLU-then-rotate linear attention (see sana_la_rope_state): k, v [B*N, H*D]
+    views, cos / sin fp32 [N, D/2].  Returns fp32 [B, H, D+1, D]; row D is the unrotated key sum."""
+    _need_cuda(k, v, cos, sin)
+    rk, ck, ldk = _rows2d(k, "la_rope_state k")
+    rv, cv, ldv = _rows2d(v, "la_rope_state v")
+    if rk != B * N or rv != B * N or ck != H * D or cv != H * D or ldk != ldv or k.dtype != v.dtype:
+        raise SanaLibraryError("la_rope_state: k and v must be [B*N, H*D] with the same row stride and dtype")
+    _rope_tables(cos, sin, N, D, "la_rope_state")
+    lib = _lib.load()
+    ws_bytes = lib.sana_la_rope_state_workspace_bytes(B, N, H, D)
+    if ws_bytes <= 0:
+        raise SanaLibraryError(f"la_rope_state: head dimension {D} is not a multiple of 16 in [16, 128]")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=k.device)
+    state = torch.empty(B, H, D + 1, D, dtype=torch.float32, device=k.device)
+    _lib.check(lib.sana_la_rope_state(k.data_ptr(), v.data_ptr(), ldk, cos.data_ptr(), sin.data_ptr(), state.data_ptr(),
+                                      ws.data_ptr(), ws.numel(), B, N, H, D, _dtype_code(k.dtype), _stream()),
+               "sana_la_rope_state")
+    counters.launches += 2  # partial states + fixed-order reduction
+    return state
+
+
+def la_rope_apply(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int,
+                  D: int, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o = state[:D] rot(relu(q)) / (state[D] . relu(q) + eps), token-major; q [B*N, H*D] view."""
+    _need_cuda(q, cos, sin, state)
+    rq, cq, ldq = _rows2d(q, "la_rope_apply q")
+    if rq != B * N or cq != H * D:
+        raise SanaLibraryError("la_rope_apply: q must be [B*N, H*D]")
+    _rope_tables(cos, sin, N, D, "la_rope_apply")
+    if state.shape != (B, H, D + 1, D) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise SanaLibraryError("la_rope_apply: state must be contiguous fp32 [B, H, D+1, D]")
+    if out is None:
+        out = torch.empty(B * N, H * D, dtype=q.dtype, device=q.device)
+    ro, co, ldo = _rows2d(out, "la_rope_apply out")
+    if ro != B * N or co != H * D or out.dtype != q.dtype:
+        raise SanaLibraryError("la_rope_apply: bad output tensor")
+    _lib.check(_lib.load().sana_la_rope_apply(q.data_ptr(), ldq, cos.data_ptr(), sin.data_ptr(), state.data_ptr(),
+                                              out.data_ptr(), ldo, B, N, H, D, eps, _dtype_code(q.dtype), _stream()),
+               "sana_la_rope_apply")
+    counters.launches += 1
+    return out
+
+
 def cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Optional[torch.Tensor], B: int, N: int,
                     L: int, heads: int, head_dim: int) -> torch.Tensor:
     """softmax(q k^T / sqrt(head_dim) + (1 - mask) * -10000) v, token-major.  q [B*N, heads*head_dim];

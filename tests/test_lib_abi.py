@@ -79,6 +79,27 @@ def test_invalid_arguments_of_the_newer_entry_points(lib):
     assert b"gate_t" in lib.sana_last_error()
 
 
+def test_invalid_arguments_of_the_rotated_linear_attention(lib):
+    p = C.c_void_p(0x1000)
+    bf = _lib.SANA_BF16
+    assert lib.sana_la_rope_state_workspace_bytes(1, 64, 2, 40) == 0  # head dimension not a multiple of 16
+    assert lib.sana_la_rope_state_workspace_bytes(1, 64, 2, 144) == 0  # wider than 128
+    assert lib.sana_la_rope_state_workspace_bytes(0, 64, 2, 112) == 0
+    assert lib.sana_la_rope_state_workspace_bytes(1, 4096, 20, 112) >= 20 * 113 * 112 * 4
+    assert lib.sana_la_rope_state(None, p, 224, p, p, p, p, 1 << 30, 1, 64, 2, 112, bf, None) == -1
+    assert b"null" in lib.sana_last_error()
+    assert lib.sana_la_rope_state(p, p, 224, p, p, p, p, 1 << 30, 1, 64, 2, 40, bf, None) == -1
+    assert b"head dimension" in lib.sana_last_error()
+    assert lib.sana_la_rope_state(p, p, 200, p, p, p, p, 1 << 30, 1, 64, 2, 112, bf, None) == -1  # ld < H*D
+    assert lib.sana_la_rope_state(p, p, 224, p, p, p, p, 16, 1, 64, 2, 112, bf, None) == -1  # workspace too small
+    assert b"workspace" in lib.sana_last_error()
+    assert lib.sana_la_rope_state(p, p, 224, p, p, p, p, 1 << 30, 1, 64, 2, 112, 9, None) == -1  # dtype
+    assert lib.sana_la_rope_apply(p, 224, p, p, p, None, 224, 1, 64, 2, 112, 1e-8, bf, None) == -1
+    assert lib.sana_la_rope_apply(p, 224, p, p, p, p, 100, 1, 64, 2, 112, 1e-8, bf, None) == -1  # ldo < H*D
+    assert lib.sana_la_rope_apply(p, 224, p, p, p, p, 224, 1, 64, 2, 24, 1e-8, bf, None) == -1
+    assert lib.sana_la_rope_apply(p, 224, C.c_void_p(0x1004), p, p, p, 224, 1, 64, 2, 112, 1e-8, bf, None) == -1  # alignment
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libsana_b200.so")
