@@ -195,9 +195,10 @@ int sana_la_apply(const void* q, int64_t ldq, const float* state, void* out, int
  *     token's position inside its sample
  *   state [B, H, D+1, D] fp32; workspace: sana_la_rope_state_workspace_bytes(B, N, H, D) bytes,
  *     16-byte aligned, holds per-chunk partial states added in a fixed order (bit-reproducible).
- * bf16: the rotated q and k are rounded to bf16 (as upstream's `type_as`) and the state enters the
- * second product rounded to bf16 (as upstream's bf16 `vk`); sums accumulate in fp32 and the
- * normaliser is computed in fp32.  fp32: plain fp32 arithmetic.
+ * bf16: both products are tcgen05.mma instructions accumulating in tensor memory (fp32); the rotated
+ * q and k are rounded to bf16 (as upstream's `type_as`) and the state enters the second product
+ * rounded to bf16 (as upstream's bf16 `vk`); the key sum and the normaliser are computed in fp32.
+ * fp32: plain fp32 arithmetic.
  */
 int64_t sana_la_rope_state_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D);
 int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
@@ -206,6 +207,10 @@ int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* co
 int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_table, const float* sin_table,
                        const float* state, void* out, int64_t ldo, int64_t B, int64_t N, int64_t H, int64_t D,
                        float eps, int dtype, void* stream);
+/* Soft-error word of the bf16 sana_la_rope_state kernel, whose tensor-core waits are bounded: 0 when
+ * no wait has timed out on the current device since the last call (host-synchronising: for tests and
+ * after a failure, not per step). */
+int sana_la_rope_take_device_status(int* status_out);
 
 /* ---------------------------------------------------------------------------------------
  * 3x3 depthwise conv + bias + SiLU-GLU on channels-last rows:

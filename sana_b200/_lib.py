@@ -64,6 +64,7 @@ SIGNATURES = {
     "sana_gemm": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),
     "sana_gemm_simt": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),
     "sana_gemm_take_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "sana_la_rope_take_device_status": (_i32, [C.POINTER(C.c_int)]),
     "sana_dwconv_glu_take_device_status": (_i32, [C.POINTER(C.c_int)]),
     "sana_gemm_set_variant": (_i32, [_i32]),
     "sana_nvfp4_sf_bytes": (_i64, [_i64, _i64]),

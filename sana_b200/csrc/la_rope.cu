@@ -6,29 +6,30 @@
 //   out[n][i]   = (sum_j state[i][j] * rot(relu(q[n]))[j]) / (sum_j state[D][j] * relu(q[n][j]) + eps)
 //   rot(x)[2p] = x[2p] cos[n][p] - x[2p+1] sin[n][p],  rot(x)[2p+1] = x[2p] sin[n][p] + x[2p+1] cos[n][p]
 //
-// bf16: one CTA per (head, token chunk, sample).  A tile of 64 tokens is loaded 16 bytes per
-// lane, passed through ReLU and the rotation once, and written to shared memory as bf16; the
-// products run on warp-level bf16 tensor-core instructions with fp32 accumulation, fed by
-// ldmatrix from rows padded by 16 bytes (conflict-free).  The key sum and the normaliser stay
-// in fp32 on the CUDA cores.  fp32: plain FFMA kernels (the parity path).
-#include "common.cuh"
+// bf16: one CTA per (head, token chunk, sample).  Tiles of 32 tokens (the raw rows and their
+// cos / sin rows) arrive through cp.async one tile ahead of their use; a staging pass applies ReLU
+// and the rotation once per element and writes the bf16 operand tiles in the 128-byte-swizzled
+// layouts the 5th-generation tensor cores read; the products are tcgen05.mma instructions that
+// accumulate in tensor memory.  The key sum and the normaliser stay in fp32 on the CUDA cores.
+// fp32: plain FFMA kernels (the parity path).
 #include "la_plan.cuh"
+#include "tc_common.cuh"
 
 namespace sana {
 
 constexpr int LR_THREADS = 256;
-constexpr int LR_TOK = 64;   // tokens per tile, bf16 kernels
+constexpr int LR_TOK = 32;   // tokens per tile, bf16 kernels
 constexpr int LR_TOKF = 16;  // tokens per tile, fp32 kernels
 
-__device__ __forceinline__ void lr_ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+// 16 bytes global -> shared; `valid` false writes zeros and reads nothing
+__device__ __forceinline__ void lr_cp_async_16(uint32_t smem_addr, const void* gptr, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(sz) : "memory");
 }
-__device__ __forceinline__ void lr_ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+__device__ __forceinline__ void lr_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void lr_cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
 // ReLU of 8 bf16 channels (4 rotation pairs) of one token: x = relu(raw) in fp32, and
@@ -48,30 +49,67 @@ __device__ __forceinline__ void lr_relu_rotate8(const uint4 raw, const float4 c,
 }
 
 // ------------------------------------------------------------------------------------------
-// state, bf16.  grid (H, chunks, B) - heads fastest, so that CTAs running at the same time read
-// whole token rows between them.  Staging: 16 lanes per token (lane group `grp` owns channels
-// 8 grp .. 8 grp + 7 and keeps their key sum in registers), 16 tokens per pass, 4 passes per tile;
-// two CTAs per SM, so that one stages while the other multiplies.
-// Products: warp w < D/16 owns value channels 16 w .. 16 w + 15 (one M tile) against all D key
-// channels; tokens are the contraction index, so both operands are read with ldmatrix.trans from
-// the token-major tiles.
+// state, bf16, on the 5th-generation tensor cores.  grid (H, chunks, B) - heads fastest, so that
+// CTAs running at the same time read whole token rows between them.  Staging: 16 lanes per token
+// (lane group `grp` owns channels 8 grp .. 8 grp + 7 and keeps their key sum in registers),
+// 16 tokens per pass, 2 passes per tile.  The product sum_n v[n][i] krot[n][j] of a 32-token tile
+// is two tcgen05.mma instructions (M = 128 value channels of which D are used, N = D key
+// channels, K = 16 tokens each) that accumulate in tensor memory over the whole chunk.  Tokens are the contraction index and the
+// tiles are token-major, i.e. both operands are "MN-major": a tile is [64-channel block][token]
+// [128 bytes], 128-byte swizzled (16-byte chunk index XOR token & 7), 8-token groups 1024 bytes
+// apart, channel blocks 4096 bytes apart.  v goes from global memory straight into its operand
+// tile with cp.async; the conversion pass writes the rotated k into the other.
+// One thread issues the products; every thread waits (bounded) for the previous tile's products
+// before the tiles are overwritten.  A time-out records a code in g_lr_status, and the CTA leaves
+// through the common teardown, which frees its tensor memory.
 // ------------------------------------------------------------------------------------------
+__device__ int g_lr_status = 0;
+
 template <int D>
-__global__ void __launch_bounds__(LR_THREADS, 2)
-la_rope_state_bf16_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int64_t ld,
-                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                          float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
-  constexpr int G = D / 8;        // 16-byte groups per token row
-  constexpr int ROW = D + 8;      // padded row, elements
-  constexpr int ROWB = ROW * 2;   // bytes
-  constexpr int MT = D / 16;      // M tiles = warps that multiply
-  constexpr int NP = D / 16;      // pairs of N tiles
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Ks = smem;                   // [64][ROW] rotated relu(k)
-  unsigned char* Vs = smem + LR_TOK * ROWB;   // [64][ROW] v
-  const uint32_t Ks_u = (uint32_t)__cvta_generic_to_shared(Ks);
-  const uint32_t Vs_u = (uint32_t)__cvta_generic_to_shared(Vs);
+struct LrTc {
+  static constexpr int BLK = LR_TOK * 128;          // one 64-channel block of a tile
+  static constexpr int TILE = 2 * BLK;              // 128 channels
+  static constexpr int RAWB = D * 2;
+  static constexpr int STAGE = 3 * LR_TOK * RAWB;   // raw k | cos | sin rows of one tile
+  static constexpr int OFF_A = TILE;                // rotated k | v[2] | stage[2] | control
+  static constexpr int OFF_STAGE = 3 * TILE;
+  static constexpr int OFF_CTRL = OFF_STAGE + 2 * STAGE;
+  static constexpr int BYTES = OFF_CTRL + 64;
+  static constexpr uint32_t TMEM_COLS = 128;
+  // D = f32 (bit 4), A = B = bf16 (bits 7, 10), A and B MN-major (bits 15, 16), N >> 3 at 17, M >> 4 at 24
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
+                                    ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+  static_assert(TILE >= 16 * D * 4, "the key-sum scratch reuses the rotated-k tile");
+};
+
+// MN-major, 128-byte-swizzled operand: bits 0-13 address >> 4, 16-29 byte offset between 64-element
+// blocks along M / N (>> 4), 32-45 byte offset between 8-row groups along K (1024 >> 4), 46-47
+// descriptor version 1, 61-63 layout 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t lr_desc_mn(uint32_t saddr, uint32_t block_stride_bytes) {
+  const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | ((block_stride_bytes >> 4) << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+template <int D>
+__global__ void __launch_bounds__(LR_THREADS, 3)
+la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int64_t ld,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                        float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
+  using T = LrTc<D>;
+  constexpr int G = D / 8;
+  constexpr int RAWB = T::RAWB;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const uint32_t sm_u = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((sm_u & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (tid == 0) atomicExch(&g_lr_status, 9);
+    return;
+  }
+  const uint32_t B_u = sm_u, A_u = sm_u + T::OFF_A, stage_u = sm_u + T::OFF_STAGE, ctrl = sm_u + T::OFF_CTRL;
+  const uint32_t bar_mma = ctrl;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::OFF_CTRL + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::OFF_CTRL + 12);
   const int slot = tid >> 4, grp = tid & 15;
   const int h = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
   const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
@@ -80,162 +118,284 @@ la_rope_state_bf16_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloa
   const __nv_bfloat16* kbase = kp + (int64_t)b * N * ld + col;
   const __nv_bfloat16* vbase = vp + (int64_t)b * N * ld + col;
 
+  if (tid == 0) {
+    mbar_init(bar_mma, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 8), "r"(T::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // byte offset of (token row, 16-byte channel group) inside an operand tile
+  auto tile_off = [&](int row) -> uint32_t {
+    return (uint32_t)((grp >> 3) * T::BLK + row * 128 + (((grp & 7) ^ (row & 7)) << 4));
+  };
+  auto issue = [&](int n0, int buf) {
+    if (loader) {
+#pragma unroll
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        const int row = 16 * r + slot, tok = n0 + row;
+        const bool ok = tok < n_end;
+        const int64_t t = ok ? tok : n_begin;
+        const uint32_t st = stage_u + buf * T::STAGE + row * RAWB + grp * 16;
+        lr_cp_async_16(st, kbase + t * ld, ok);
+        lr_cp_async_16(st + LR_TOK * RAWB, cos_t + t * (D / 2) + 4 * grp, ok);
+        lr_cp_async_16(st + 2 * LR_TOK * RAWB, sin_t + t * (D / 2) + 4 * grp, ok);
+        lr_cp_async_16(A_u + buf * T::TILE + tile_off(row), vbase + t * ld, ok);
+      }
+    }
+    lr_cp_async_commit();
+  };
+
   float ksum[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) ksum[e] = 0.f;
-  float acc[2 * NP][4];
-#pragma unroll
-  for (int n = 0; n < 2 * NP; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 
-  for (int n0 = n_begin; n0 < n_end; n0 += LR_TOK) {
+  issue(n_begin, 0);
+  bool aborted = false;
+  int it = 0;
+  for (int n0 = n_begin; n0 < n_end; n0 += LR_TOK, ++it) {
+    const int buf = it & 1;
+    // the products of the previous tile have read the rotated-k tile and v[buf ^ 1]; this barrier also
+    // orders the previous conversion's reads of stage[buf ^ 1] before the copies issued below
+    bool ok = true;
+    if (it > 0) ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 1, &g_lr_status);
+    if (__syncthreads_or(!ok)) {
+      aborted = true;
+      break;
+    }
+    if (n0 + LR_TOK < n_end) {
+      issue(n0 + LR_TOK, buf ^ 1);
+      lr_cp_async_wait<1>();
+    } else {
+      lr_cp_async_wait<0>();
+    }
+    __syncthreads();
     if (loader) {
+      const unsigned char* st = smem + T::OFF_STAGE + buf * T::STAGE;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {  // two passes at a time keep the staging registers low
-        uint4 kr[2], vr[2];
-        float4 cr[2], sr[2];
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        const int row = 16 * r + slot;
+        const uint4 raw = *reinterpret_cast<const uint4*>(st + row * RAWB + grp * 16);
+        const float4 c = *reinterpret_cast<const float4*>(st + LR_TOK * RAWB + row * RAWB + grp * 16);
+        const float4 s = *reinterpret_cast<const float4*>(st + 2 * LR_TOK * RAWB + row * RAWB + grp * 16);
+        float x[8];
+        uint4 rot;
+        lr_relu_rotate8(raw, c, s, x, &rot);
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int tok = n0 + 16 * (2 * half + r) + slot;
-          if (tok < n_end) {
-            kr[r] = ldg_nc_u4(kbase + (int64_t)tok * ld);
-            vr[r] = ldg_nc_u4(vbase + (int64_t)tok * ld);
-            cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
-            sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
-          } else {
-            kr[r] = vr[r] = make_uint4(0u, 0u, 0u, 0u);
-            cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          float x[8];
-          uint4 rot;
-          lr_relu_rotate8(kr[r], cr[r], sr[r], x, &rot);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ksum[e] += x[e];
-          const int row = 16 * (2 * half + r) + slot;
-          *reinterpret_cast<uint4*>(Ks + row * ROWB + grp * 16) = rot;
-          *reinterpret_cast<uint4*>(Vs + row * ROWB + grp * 16) = vr[r];
-        }
+        for (int e = 0; e < 8; ++e) ksum[e] += x[e];
+        *reinterpret_cast<uint4*>(smem + tile_off(row)) = rot;
       }
     }
+    fence_proxy_async_smem();  // this thread's stores and completed copies, before the tensor core reads them
     __syncthreads();
-    if (warp < MT) {
+    if (tid == 0) {
+      tcgen05_fence_after();
+      const uint64_t adesc = lr_desc_mn(A_u + buf * T::TILE, T::BLK), bdesc = lr_desc_mn(B_u, T::BLK);
 #pragma unroll
-      for (int ks = 0; ks < LR_TOK / 16; ++ks) {
-        uint32_t af[4];
-        {
-          const int row = ks * 16 + (lane & 7) + (lane >> 4) * 8, ch = warp * 16 + ((lane >> 3) & 1) * 8;
-          lr_ldsm_x4_trans(af, Vs_u + row * ROWB + ch * 2);
-        }
-#pragma unroll
-        for (int np = 0; np < NP; ++np) {
-          uint32_t bf[4];
-          const int row = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ch = np * 16 + (lane >> 4) * 8;
-          lr_ldsm_x4_trans(bf, Ks_u + row * ROWB + ch * 2);
-          mma_bf16_16816(acc[2 * np], af[0], af[1], af[2], af[3], bf[0], bf[1]);
-          mma_bf16_16816(acc[2 * np + 1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
-        }
-      }
+      for (int k = 0; k < LR_TOK / 16; ++k)  // 16 tokens = two 8-token groups = 2048 bytes (address field is >> 4)
+        umma_bf16(tmem_base, adesc + (uint64_t)(128 * k), bdesc + (uint64_t)(128 * k), T::IDESC, (it | k) != 0 ? 1u : 0u);
+      umma_commit(bar_mma);
     }
-    __syncthreads();
   }
+  lr_cp_async_wait<0>();  // nothing of this thread is still in flight, whichever way the loop ended
+  if (!aborted) {
+    const bool ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 2, &g_lr_status);
+    if (__syncthreads_or(!ok)) aborted = true;
+  }
+  tcgen05_fence_after();
 
   float* out = partial + (((int64_t)b * nchunks + chunk) * H + h) * (int64_t)((D + 1) * D);
-  if (warp < MT) {
-    const int g = lane >> 2, t = lane & 3;
+  if (!aborted) {
+    // warp w reads TMEM lanes 32 (w & 3) .. + 31 (hardware rule) = value channels, and every second
+    // 16-column step = key channels
+    const int quad = warp & 3, i = quad * 32 + lane;
+    for (int c = warp >> 2; c < D / 16; c += 2) {
+      uint32_t r[16];
+      tmem_ld_32x16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 16), r);
+      tmem_ld_wait();
+      if (i < D) {
+        float4* dst = reinterpret_cast<float4*>(out + i * D + c * 16);
 #pragma unroll
-    for (int nt = 0; nt < 2 * NP; ++nt) {
-      const int i = warp * 16 + g, j = nt * 8 + 2 * t;
-      *reinterpret_cast<float2*>(out + i * D + j) = make_float2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<float2*>(out + (i + 8) * D + j) = make_float2(acc[nt][2], acc[nt][3]);
+        for (int e = 0; e < 4; ++e)
+          dst[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]), __uint_as_float(r[4 * e + 2]),
+                               __uint_as_float(r[4 * e + 3]));
+      }
+    }
+    // key sum: the 16 token slots add in a fixed order
+    float* red = reinterpret_cast<float*>(smem);  // [16][D]; the rotated-k tile is no longer read
+    if (loader) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[slot * D + 8 * grp + e] = ksum[e];
+    }
+    __syncthreads();
+    if (tid < D) {
+      float s = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) s += red[r * D + tid];
+      out[D * D + tid] = s;
     }
   }
-  // key sum: the 16 token slots add in a fixed order
-  float* red = reinterpret_cast<float*>(smem);  // [16][D]; the tiles are no longer read
-  if (loader) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) red[slot * D + 8 * grp + e] = ksum[e];
-  }
+  tcgen05_fence_before();
   __syncthreads();
-  if (tid < D) {
-    float s = 0.f;
-#pragma unroll
-    for (int r = 0; r < 16; ++r) s += red[r * D + tid];
-    out[D * D + tid] = s;
+  if (warp == 0) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T::TMEM_COLS) : "memory");
   }
 }
 
 // ------------------------------------------------------------------------------------------
-// apply, bf16.  grid (H, chunks, B).  The head's state is converted once to bf16 in shared memory
-// ([i][j], j contiguous = the "col" B operand), the key-sum row stays fp32.  Staging as in the
-// state kernel; the 16 lanes of a token also reduce its normaliser with shuffles.  Products:
-// warp w owns tokens 16 (w & 3) .. + 15 of the tile and the value channels of half (w >> 2).
-// The results go back through the token tile so that global stores are 16 bytes per lane.
+// apply, bf16, on the 5th-generation tensor cores.  grid (H, chunks, B).  Per tile of 128 tokens:
+// out[n][i] = sum_j qrot[n][j] S[i][j] is D / 16 tcgen05.mma instructions (M = 128 tokens, N = D
+// value channels, K = 16 key channels each), both operands K-major (rows of 64 channels = 128
+// bytes, 128-byte swizzled, 8-row groups 1024 bytes apart, 64-channel blocks one after the other).
+// The state tile is converted to bf16 once per CTA; the token tile is filled 32 tokens at a time
+// by the staging pass (cp.async one sub-tile ahead, ReLU + rotation + normaliser as in the state
+// kernel).  Epilogue: warp w reads TMEM lanes 32 (w & 3) .. + 31 (= tokens) and every second
+// 16-column step, scales by 1 / (normaliser + eps), and writes bf16 rows (padded by 16 bytes) into
+// the token tile, which the products have finished reading; global stores are then 16 bytes per
+// lane, 16 lanes per token.  Waits are bounded as in the state kernel.
 // ------------------------------------------------------------------------------------------
+constexpr int LR_MTOK = 128;  // tokens per product tile of the apply kernel
+
 template <int D>
-__global__ void __launch_bounds__(LR_THREADS)
-la_rope_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ cos_t,
-                          const float* __restrict__ sin_t, const float* __restrict__ state,
-                          __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+struct LrTcApply {
+  static constexpr int KB = (D + 63) / 64;            // 64-channel blocks along the key channels
+  static constexpr int S_BLK = D * 128;               // one block of the state tile: D rows x 128 bytes
+  static constexpr int S_BYTES = KB * S_BLK;
+  static constexpr int Q_BLK = LR_MTOK * 128;         // one block of the token tile
+  static constexpr int OROWB = 2 * D + 16;            // result rows, padded
+  static constexpr int Q_BYTES = (KB * Q_BLK > LR_MTOK * OROWB ? KB * Q_BLK : LR_MTOK * OROWB + 1023) / 1024 * 1024;
+  static constexpr int RAWB = D * 2;
+  static constexpr int STAGE = 3 * LR_TOK * RAWB;     // raw q | cos | sin rows of 32 tokens
+  static constexpr int OFF_Q = S_BYTES;               // state | tokens | stage[2] | key sum | 1/normaliser | control
+  static constexpr int OFF_STAGE = OFF_Q + Q_BYTES;
+  static constexpr int OFF_KSUM = OFF_STAGE + 2 * STAGE;
+  static constexpr int OFF_RDEN = OFF_KSUM + D * 4;
+  static constexpr int OFF_CTRL = OFF_RDEN + LR_MTOK * 4;
+  static constexpr int BYTES = OFF_CTRL + 64;
+  static constexpr uint32_t TMEM_COLS = 128;
+  // D = f32 (bit 4), A = B = bf16 (bits 7, 10), both K-major, N >> 3 at 17, M >> 4 at 24
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+  static_assert(S_BYTES % 1024 == 0 && OFF_CTRL % 8 == 0, "swizzled tiles need 1024-byte alignment");
+};
+
+template <int D>
+__global__ void __launch_bounds__(LR_THREADS, 2)
+la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, const float* __restrict__ state,
+                        __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+  using T = LrTcApply<D>;
   constexpr int G = D / 8;
-  constexpr int ROW = D + 8;
-  constexpr int ROWB = ROW * 2;
-  constexpr int KS = D / 16;       // k-steps over the key channels
-  constexpr int NTW = D / 16;      // N tiles (value channels / 8) per warp: half of D / 8
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Ss = smem;                                  // [D + 8][ROW] bf16 state, 8 spare rows
-  unsigned char* Qs = Ss + (D + 8) * ROWB;                   // [64][ROW] rotated relu(q), then the results
-  float* ksum_s = reinterpret_cast<float*>(Qs + LR_TOK * ROWB);  // [D]
-  float* rden_s = ksum_s + D;                                // [64] 1 / (normaliser + eps)
-  const uint32_t Ss_u = (uint32_t)__cvta_generic_to_shared(Ss);
-  const uint32_t Qs_u = (uint32_t)__cvta_generic_to_shared(Qs);
+  constexpr int RAWB = T::RAWB;
+  constexpr int SUBS = LR_MTOK / LR_TOK;  // staging sub-tiles per product tile
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const uint32_t sm_u = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((sm_u & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (tid == 0) atomicExch(&g_lr_status, 9);
+    return;
+  }
+  unsigned char* Qs = smem + T::OFF_Q;
+  float* ksum_s = reinterpret_cast<float*>(smem + T::OFF_KSUM);
+  float* rden_s = reinterpret_cast<float*>(smem + T::OFF_RDEN);
+  const uint32_t S_u = sm_u, Q_u = sm_u + T::OFF_Q, stage_u = sm_u + T::OFF_STAGE, ctrl = sm_u + T::OFF_CTRL;
+  const uint32_t bar_mma = ctrl;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::OFF_CTRL + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::OFF_CTRL + 12);
   const int slot = tid >> 4, grp = tid & 15;
   const int h = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
   const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
   const bool loader = grp < G;
+  const int64_t col = (int64_t)h * D + 8 * grp;
+  const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
+  __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
 
-  const float* sg = state + ((int64_t)b * H + h) * (int64_t)((D + 1) * D);
-  for (int e = tid; e < D * (D / 2); e += LR_THREADS) {
-    const int i = e / (D / 2), jp = e % (D / 2);
-    const float2 s2 = __ldg(reinterpret_cast<const float2*>(sg + i * D + 2 * jp));
-    *reinterpret_cast<uint32_t*>(Ss + i * ROWB + jp * 4) = pack_bf16(s2.x, s2.y);
+  if (tid == 0) {
+    mbar_init(bar_mma, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int e = tid; e < 8 * (ROW / 2); e += LR_THREADS)  // spare rows: read by the last odd tile, never used
-    *reinterpret_cast<uint32_t*>(Ss + D * ROWB + e * 4) = 0u;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 8), "r"(T::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  auto issue = [&](int n0, int buf) {  // 32 tokens from n0 into stage[buf]
+    if (loader) {
+#pragma unroll
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        const int row = 16 * r + slot, tok = n0 + row;
+        const bool ok = tok < n_end;
+        const int64_t t = ok ? tok : n_begin;
+        const uint32_t st = stage_u + buf * T::STAGE + row * RAWB + grp * 16;
+        lr_cp_async_16(st, qbase + t * ldq, ok);
+        lr_cp_async_16(st + LR_TOK * RAWB, cos_t + t * (D / 2) + 4 * grp, ok);
+        lr_cp_async_16(st + 2 * LR_TOK * RAWB, sin_t + t * (D / 2) + 4 * grp, ok);
+      }
+    }
+    lr_cp_async_commit();
+  };
+  issue(n_begin, 0);
+
+  // the head's state as the B operand: row i (value channel), 16-byte chunks of 8 key channels
+  const float* sg = state + ((int64_t)b * H + h) * (int64_t)((D + 1) * D);
+  for (int e = tid; e < D * G; e += LR_THREADS) {
+    const int i = e / G, c = e % G;
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(sg + i * D + 8 * c));
+    const float4 hi = __ldg(reinterpret_cast<const float4*>(sg + i * D + 8 * c + 4));
+    const uint4 pk = make_uint4(pack_bf16(lo.x, lo.y), pack_bf16(lo.z, lo.w), pack_bf16(hi.x, hi.y), pack_bf16(hi.z, hi.w));
+    *reinterpret_cast<uint4*>(smem + (c >> 3) * T::S_BLK + i * 128 + (((c & 7) ^ (i & 7)) << 4)) = pk;
+  }
   if (tid < D) ksum_s[tid] = __ldg(sg + D * D + tid);
+  tcgen05_fence_before();
   __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
 
   float kreg[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) kreg[e] = loader ? ksum_s[8 * grp + e] : 0.f;
-  const int64_t col = (int64_t)h * D + 8 * grp;
-  const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
-  __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
-  const int mtile = warp & 3, nhalf = warp >> 2;
 
-  for (int n0 = n_begin; n0 < n_end; n0 += LR_TOK) {
-    {
-      uint4 qr[4];
-      float4 cr[4], sr[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int tok = n0 + 16 * r + slot;
-        if (loader && tok < n_end) {
-          qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
-          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
-          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
-        } else {
-          qr[r] = make_uint4(0u, 0u, 0u, 0u);
-          cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+  bool aborted = false;
+  int sub = 0;  // staging sub-tiles consumed so far; its parity is the stage buffer
+  int tile = 0;
+  for (int m0 = n_begin; m0 < n_end; m0 += LR_MTOK, ++tile) {
+#pragma unroll 1
+    for (int ss = 0; ss < SUBS; ++ss, ++sub) {
+      const int buf = sub & 1, n0 = m0 + ss * LR_TOK;
+      // everybody has left the previous conversion (stage[buf ^ 1]) and, at ss = 0, the previous tile's stores
+      __syncthreads();
+      if (n0 + LR_TOK < n_end) {  // sub-tiles past the end of the chunk are all zeros and need no copy
+        issue(n0 + LR_TOK, buf ^ 1);
+        lr_cp_async_wait<1>();
+      } else {
+        lr_cp_async_wait<0>();
       }
+      __syncthreads();
+      const unsigned char* st = smem + T::OFF_STAGE + buf * T::STAGE;
+      const bool live = n0 < n_end;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        const int row = 16 * r + slot, trow = ss * LR_TOK + row;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        float4 c = make_float4(0.f, 0.f, 0.f, 0.f), s = c;
+        if (loader && live) {
+          raw = *reinterpret_cast<const uint4*>(st + row * RAWB + grp * 16);
+          c = *reinterpret_cast<const float4*>(st + LR_TOK * RAWB + row * RAWB + grp * 16);
+          s = *reinterpret_cast<const float4*>(st + 2 * LR_TOK * RAWB + row * RAWB + grp * 16);
+        }
         float x[8];
         uint4 rot;
-        lr_relu_rotate8(qr[r], cr[r], sr[r], x, &rot);
+        lr_relu_rotate8(raw, c, s, x, &rot);
         float den = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) den = fmaf(x[e], kreg[e], den);
@@ -244,54 +404,62 @@ la_rope_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, con
         den += __shfl_xor_sync(0xffffffffu, den, 2);
         den += __shfl_xor_sync(0xffffffffu, den, 4);
         den += __shfl_xor_sync(0xffffffffu, den, 8);
-        const int row = 16 * r + slot;
-        if (grp == 0) rden_s[row] = 1.0f / (den + eps);
-        if (loader) *reinterpret_cast<uint4*>(Qs + row * ROWB + grp * 16) = rot;
+        if (grp == 0) rden_s[trow] = 1.0f / (den + eps);
+        if (loader)
+          *reinterpret_cast<uint4*>(Qs + (grp >> 3) * T::Q_BLK + trow * 128 + (((grp & 7) ^ (trow & 7)) << 4)) = rot;
       }
     }
+    fence_proxy_async_smem();  // this thread's stores, before the tensor core reads them
     __syncthreads();
-    float acc[NTW][4];
+    if (tid == 0) {
+      tcgen05_fence_after();
 #pragma unroll
-    for (int n = 0; n < NTW; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      uint32_t af[4];
-      {
-        const int row = mtile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ch = ks * 16 + (lane >> 4) * 8;
-        lr_ldsm_x4(af, Qs_u + row * ROWB + ch * 2);
+      for (int ks = 0; ks < D / 16; ++ks) {  // 16 key channels = 32 bytes inside a 128-byte row
+        const uint64_t adesc = make_smem_desc(Q_u + (ks >> 2) * T::Q_BLK + (ks & 3) * 32);
+        const uint64_t bdesc = make_smem_desc(S_u + (ks >> 2) * T::S_BLK + (ks & 3) * 32);
+        umma_bf16(tmem_base, adesc, bdesc, T::IDESC, ks != 0 ? 1u : 0u);
       }
-#pragma unroll
-      for (int np = 0; np < (NTW + 1) / 2; ++np) {
-        uint32_t bf[4];
-        // value channels 8 (nhalf NTW + 2 np) .. + 15; beyond D only the spare rows are touched
-        const int row = (nhalf * NTW + 2 * np) * 8 + (lane >> 4) * 8 + (lane & 7), ch = ks * 16 + ((lane >> 3) & 1) * 8;
-        lr_ldsm_x4(bf, Ss_u + row * ROWB + ch * 2);
-        mma_bf16_16816(acc[2 * np], af[0], af[1], af[2], af[3], bf[0], bf[1]);
-        if (2 * np + 1 < NTW) mma_bf16_16816(acc[2 * np + 1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
-      }
+      umma_commit(bar_mma);
     }
-    __syncthreads();  // every warp has read its q fragments: the tile can take the results
+    const bool ok = mbar_wait(bar_mma, (uint32_t)(tile & 1), abort_flag, 3, &g_lr_status);
+    if (__syncthreads_or(!ok)) {
+      aborted = true;
+      break;
+    }
+    tcgen05_fence_after();
     {
-      const int g = lane >> 2, t = lane & 3;
-      const int r0 = mtile * 16 + g;
-      const float d0 = rden_s[r0], d1 = rden_s[r0 + 8];
+      const int quad = warp & 3, trow = quad * 32 + lane;
+      const float rd = rden_s[trow];
+      for (int c = warp >> 2; c < D / 16; c += 2) {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 16), r);
+        tmem_ld_wait();
+        uint32_t pk[8];
 #pragma unroll
-      for (int nt = 0; nt < NTW; ++nt) {
-        const int i = (nhalf * NTW + nt) * 8 + 2 * t;
-        *reinterpret_cast<uint32_t*>(Qs + r0 * ROWB + i * 2) = pack_bf16(acc[nt][0] * d0, acc[nt][1] * d0);
-        *reinterpret_cast<uint32_t*>(Qs + (r0 + 8) * ROWB + i * 2) = pack_bf16(acc[nt][2] * d1, acc[nt][3] * d1);
+        for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(__uint_as_float(r[2 * e]) * rd, __uint_as_float(r[2 * e + 1]) * rd);
+        uint4* dst = reinterpret_cast<uint4*>(Qs + trow * T::OROWB + c * 32);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
       }
     }
+    tcgen05_fence_before();
     __syncthreads();
     if (loader) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int tok = n0 + 16 * r + slot, row = 16 * r + slot;
+      for (int r = 0; r < LR_MTOK / 16; ++r) {
+        const int trow = 16 * r + slot, tok = m0 + trow;
         if (tok < n_end)
-          *reinterpret_cast<uint4*>(obase + (int64_t)tok * ldo) = *reinterpret_cast<const uint4*>(Qs + row * ROWB + grp * 16);
+          *reinterpret_cast<uint4*>(obase + (int64_t)tok * ldo) = *reinterpret_cast<const uint4*>(Qs + trow * T::OROWB + grp * 16);
       }
     }
-    // the next tile's staging writes exactly the elements this thread has just read
+  }
+  lr_cp_async_wait<0>();  // nothing of this thread is still in flight, whichever way the loop ended
+  (void)aborted;
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T::TMEM_COLS) : "memory");
   }
 }
 
@@ -427,31 +595,31 @@ __global__ void la_rope_reduce_kernel(const float* __restrict__ partial, float* 
 // ---- host side -------------------------------------------------------------------------------
 template <int D>
 struct LrSizes {
-  static constexpr size_t state_bf16 = 2 * LR_TOK * (D + 8) * 2;  // also >= 16 * D floats of the final key-sum pass
-  static constexpr size_t apply_bf16 = (size_t)(D + 8) * (D + 8) * 2 + LR_TOK * (D + 8) * 2 + (D + LR_TOK) * 4;
+  static constexpr size_t state_tc = LrTc<D>::BYTES;
+  static constexpr size_t apply_tc = LrTcApply<D>::BYTES;
   static constexpr size_t apply_f32 = ((size_t)D * (D + 1) + D + 2 * LR_TOKF * D) * 4;
 };
-static_assert(LrSizes<16>::state_bf16 >= 16 * 16 * 4 && LrSizes<128>::state_bf16 >= 16 * 128 * 4, "key-sum scratch");
 
 template <int D>
 static int lr_prepare() {
   static OncePerDevice once;
   if (!once.first_time()) return SANA_OK;
-  cudaError_t e = cudaFuncSetAttribute(la_rope_apply_bf16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)LrSizes<D>::apply_bf16);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(la_rope_apply_f32_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(la_rope_apply_f32_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)LrSizes<D>::apply_f32);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(la_rope_state_bf16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)LrSizes<D>::state_bf16);
+    e = cudaFuncSetAttribute(la_rope_apply_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)LrSizes<D>::apply_tc);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(la_rope_state_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)LrSizes<D>::state_tc);
   return cuda_status(e, "la_rope: cudaFuncSetAttribute");
 }
 
 // Chunking of the token axis.  Does not depend on dtype, so that the workspace query needs none.
 template <int D>
 static void lr_state_plan(int64_t B, int64_t N, int64_t H, int* Lc, int* nchunks) {
-  static const int64_t per_sm = resident_ctas(la_rope_state_bf16_kernel<D>, LR_THREADS, LrSizes<D>::state_bf16) / sm_count();
+  lr_prepare<D>();  // the occupancy query needs the shared-memory attribute
+  static const int64_t per_sm = resident_ctas(la_rope_state_tc_kernel<D>, LR_THREADS, LrSizes<D>::state_tc) / sm_count();
   // a chunk's partial state ((D+1) x D fp32, written and re-read) costs as much as ~2 D tokens of k + v
   la_chunking(B * H, N, per_sm * sm_count(), 2 * D, Lc, nchunks);
 }
@@ -465,7 +633,7 @@ static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t
   lr_state_plan<D>(B, N, H, &Lc, &nchunks);
   if (dtype == SANA_BF16) {
     dim3 grid((unsigned)H, nchunks, (unsigned)B);
-    la_rope_state_bf16_kernel<D><<<grid, LR_THREADS, LrSizes<D>::state_bf16, st>>>(
+    la_rope_state_tc_kernel<D><<<grid, LR_THREADS, LrSizes<D>::state_tc, st>>>(
         static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ld, cos_t, sin_t, partial, (int)N,
         (int)H, Lc, nchunks);
   } else {
@@ -488,11 +656,11 @@ static int lr_apply(const void* q, int64_t ldq, const float* cos_t, const float*
   int Lc, nchunks;
   if (dtype == SANA_BF16) {
     static const int64_t per_sm =
-        resident_ctas(la_rope_apply_bf16_kernel<D>, LR_THREADS, LrSizes<D>::apply_bf16) / sm_count();
+        resident_ctas(la_rope_apply_tc_kernel<D>, LR_THREADS, LrSizes<D>::apply_tc) / sm_count();
     // loading the head's state costs about as much as D / 2 tokens of q + out
     la_chunking(B * H, N, per_sm * sm_count(), D / 2, &Lc, &nchunks);
     dim3 grid((unsigned)H, nchunks, (unsigned)B);
-    la_rope_apply_bf16_kernel<D><<<grid, LR_THREADS, LrSizes<D>::apply_bf16, st>>>(
+    la_rope_apply_tc_kernel<D><<<grid, LR_THREADS, LrSizes<D>::apply_tc, st>>>(
         static_cast<const __nv_bfloat16*>(q), ldq, cos_t, sin_t, state, static_cast<__nv_bfloat16*>(out), ldo, (int)N,
         (int)H, Lc, eps);
   } else {
@@ -586,4 +754,18 @@ extern "C" int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_t
   LR_DISPATCH(D, LR_APPLY)
 #undef LR_APPLY
   return fail(SANA_ERR_INVALID, "sana_la_rope_apply: head dimension %lld", (long long)D);
+}
+
+extern "C" int sana_la_rope_take_device_status(int* status_out) {
+  if (!status_out) return fail(SANA_ERR_INVALID, "sana_la_rope_take_device_status: null pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_lr_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_lr_status)");
+  if (v != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_lr_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_lr_status)");
+  }
+  *status_out = v;
+  return SANA_OK;
 }

@@ -388,6 +388,13 @@ def take_dwconv_glu_device_status() -> int:
     return int(v.value)
 
 
+def take_la_rope_device_status() -> int:
+    """Code recorded by a timed-out wait inside the bf16 la_rope_state kernel (0 = none).  Synchronises."""
+    v = C.c_int(0)
+    _lib.check(_lib.load().sana_la_rope_take_device_status(C.byref(v)), "sana_la_rope_take_device_status")
+    return int(v.value)
+
+
 def _epi_tag(bias, act, gate, residual) -> str:
     return (" +bias" if bias is not None else "") + (" +silu" if act == ACT_SILU else " +gelu" if act == ACT_GELU_TANH else "") + \
         (" *gate" if gate is not None else "") + (" +res" if residual is not None else "")

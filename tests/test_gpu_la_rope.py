@@ -61,6 +61,7 @@ def test_la_rope_state_apply(dt, tol_state, tol_out, B, N, H, D):
     assert nmax_err(out.reshape(B, N, H, D), o_ref) < tol_out
     # bit-reproducible (fixed reduction order)
     assert torch.equal(state, ops.la_rope_state(d[:, C:2 * C], d[:, 2 * C:], cos, sin, B, N, H, D))
+    assert ops.take_la_rope_device_status() == 0  # no bounded wait timed out
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])

@@ -98,6 +98,7 @@ def test_invalid_arguments_of_the_rotated_linear_attention(lib):
     assert lib.sana_la_rope_apply(p, 224, p, p, p, p, 100, 1, 64, 2, 112, 1e-8, bf, None) == -1  # ldo < H*D
     assert lib.sana_la_rope_apply(p, 224, p, p, p, p, 224, 1, 64, 2, 24, 1e-8, bf, None) == -1
     assert lib.sana_la_rope_apply(p, 224, C.c_void_p(0x1004), p, p, p, 224, 1, 64, 2, 112, 1e-8, bf, None) == -1  # alignment
+    assert lib.sana_la_rope_take_device_status(None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch):
