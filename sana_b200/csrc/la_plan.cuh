@@ -32,4 +32,25 @@ inline int64_t resident_ctas(Kernel kernel, int threads, size_t dynamic_smem = 0
   return (int64_t)per_sm * sm_count();
 }
 
+// The same for a kernel that allocates `tmem_cols` columns of tensor memory: the runtime's occupancy
+// query answers 1 for such kernels whatever they allocate, so the limits are applied here - 64 K
+// registers (allocated per warp in units of 8 per thread), 228 KiB of shared memory of which
+// every resident CTA also takes 1 KiB for the system, 2048 threads, 512 tensor-memory columns.
+template <typename Kernel>
+inline int64_t resident_ctas_tmem(Kernel kernel, int threads, size_t dynamic_smem, int tmem_cols) {
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+    cudaGetLastError();
+    return sm_count();
+  }
+  const int64_t regs = ((int64_t)(attr.numRegs > 0 ? attr.numRegs : 32) + 7) / 8 * 8;
+  int64_t per_sm = 65536 / (regs * threads);
+  const int64_t by_smem = (228 * 1024) / (int64_t)(dynamic_smem + attr.sharedSizeBytes + 1024);
+  if (by_smem < per_sm) per_sm = by_smem;
+  if (2048 / threads < per_sm) per_sm = 2048 / threads;
+  if (512 / tmem_cols < per_sm) per_sm = 512 / tmem_cols;
+  if (per_sm < 1) per_sm = 1;
+  return per_sm * sm_count();
+}
+
 }  // namespace sana

@@ -6,12 +6,12 @@
 //   out[n][i]   = (sum_j state[i][j] * rot(relu(q[n]))[j]) / (sum_j state[D][j] * relu(q[n][j]) + eps)
 //   rot(x)[2p] = x[2p] cos[n][p] - x[2p+1] sin[n][p],  rot(x)[2p+1] = x[2p] sin[n][p] + x[2p+1] cos[n][p]
 //
-// bf16: one CTA per (head, token chunk, sample).  Tiles of 32 tokens (the raw rows and their
-// cos / sin rows) arrive through cp.async one tile ahead of their use; a staging pass applies ReLU
-// and the rotation once per element and writes the bf16 operand tiles in the 128-byte-swizzled
-// layouts the 5th-generation tensor cores read; the products are tcgen05.mma instructions that
-// accumulate in tensor memory.  The key sum and the normaliser stay in fp32 on the CUDA cores.
-// fp32: plain FFMA kernels (the parity path).
+// bf16: one CTA per (head, token chunk, sample), 3-4 CTAs per SM.  The raw rows of the next 32
+// tokens and their cos / sin rows wait in registers while the current ones are processed; a
+// staging pass applies ReLU and the rotation once per element and writes the bf16 operand tiles
+// in the 128-byte-swizzled layouts the 5th-generation tensor cores read; the products are
+// tcgen05.mma instructions that accumulate in tensor memory.  The key sum and the normaliser stay
+// in fp32 on the CUDA cores.  fp32: plain FFMA kernels (the parity path).
 #include "la_plan.cuh"
 #include "tc_common.cuh"
 
@@ -54,8 +54,8 @@ __device__ __forceinline__ void lr_relu_rotate8(const uint4 raw, const float4 c,
 // (lane group `grp` owns channels 8 grp .. 8 grp + 7 and keeps their key sum in registers),
 // 16 tokens per pass, 2 passes per tile.  The product sum_n v[n][i] krot[n][j] of a 32-token tile
 // is two tcgen05.mma instructions (M = 128 value channels of which D are used, N = D key
-// channels, K = 16 tokens each) that accumulate in tensor memory over the whole chunk.  Tokens are the contraction index and the
-// tiles are token-major, i.e. both operands are "MN-major": a tile is [64-channel block][token]
+// channels, K = 16 tokens each) that accumulate in tensor memory over the whole chunk.  Tokens are
+// the contraction index and the tiles are token-major, i.e. both operands are "MN-major": a tile is [64-channel block][token]
 // [128 bytes], 128-byte swizzled (16-byte chunk index XOR token & 7), 8-token groups 1024 bytes
 // apart, channel blocks 4096 bytes apart.  v goes from global memory straight into its operand
 // tile with cp.async; the conversion pass writes the rotated k into the other.
@@ -69,11 +69,8 @@ template <int D>
 struct LrTc {
   static constexpr int BLK = LR_TOK * 128;          // one 64-channel block of a tile
   static constexpr int TILE = 2 * BLK;              // 128 channels
-  static constexpr int RAWB = D * 2;
-  static constexpr int STAGE = 3 * LR_TOK * RAWB;   // raw k | cos | sin rows of one tile
-  static constexpr int OFF_A = TILE;                // rotated k | v[2] | stage[2] | control
-  static constexpr int OFF_STAGE = 3 * TILE;
-  static constexpr int OFF_CTRL = OFF_STAGE + 2 * STAGE;
+  static constexpr int OFF_A = TILE;                // rotated k | v[2] | control
+  static constexpr int OFF_CTRL = 3 * TILE;
   static constexpr int BYTES = OFF_CTRL + 64;
   static constexpr uint32_t TMEM_COLS = 128;
   // D = f32 (bit 4), A = B = bf16 (bits 7, 10), A and B MN-major (bits 15, 16), N >> 3 at 17, M >> 4 at 24
@@ -92,13 +89,12 @@ __device__ __forceinline__ uint64_t lr_desc_mn(uint32_t saddr, uint32_t block_st
 }
 
 template <int D>
-__global__ void __launch_bounds__(LR_THREADS, 3)
+__global__ void __launch_bounds__(LR_THREADS, 4)
 la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int64_t ld,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                         float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
   using T = LrTc<D>;
   constexpr int G = D / 8;
-  constexpr int RAWB = T::RAWB;
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sm_u = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -106,7 +102,7 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
     if (tid == 0) atomicExch(&g_lr_status, 9);
     return;
   }
-  const uint32_t B_u = sm_u, A_u = sm_u + T::OFF_A, stage_u = sm_u + T::OFF_STAGE, ctrl = sm_u + T::OFF_CTRL;
+  const uint32_t B_u = sm_u, A_u = sm_u + T::OFF_A, ctrl = sm_u + T::OFF_CTRL;
   const uint32_t bar_mma = ctrl;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::OFF_CTRL + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::OFF_CTRL + 12);
@@ -137,18 +133,30 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
   auto tile_off = [&](int row) -> uint32_t {
     return (uint32_t)((grp >> 3) * T::BLK + row * 128 + (((grp & 7) ^ (row & 7)) << 4));
   };
-  auto issue = [&](int n0, int buf) {
+  // raw k rows and their cos / sin rows of the NEXT tile wait in registers; v goes straight into its tile
+  uint4 kr[LR_TOK / 16];
+  float4 cr[LR_TOK / 16], sr[LR_TOK / 16];
+  auto fetch = [&](int n0) {
+#pragma unroll
+    for (int r = 0; r < LR_TOK / 16; ++r) {
+      const int tok = n0 + 16 * r + slot;
+      if (loader && tok < n_end) {
+        kr[r] = ldg_nc_u4(kbase + (int64_t)tok * ld);
+        cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
+        sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
+      } else {
+        kr[r] = make_uint4(0u, 0u, 0u, 0u);
+        cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  };
+  auto issue_v = [&](int n0, int buf) {
     if (loader) {
 #pragma unroll
       for (int r = 0; r < LR_TOK / 16; ++r) {
         const int row = 16 * r + slot, tok = n0 + row;
         const bool ok = tok < n_end;
-        const int64_t t = ok ? tok : n_begin;
-        const uint32_t st = stage_u + buf * T::STAGE + row * RAWB + grp * 16;
-        lr_cp_async_16(st, kbase + t * ld, ok);
-        lr_cp_async_16(st + LR_TOK * RAWB, cos_t + t * (D / 2) + 4 * grp, ok);
-        lr_cp_async_16(st + 2 * LR_TOK * RAWB, sin_t + t * (D / 2) + 4 * grp, ok);
-        lr_cp_async_16(A_u + buf * T::TILE + tile_off(row), vbase + t * ld, ok);
+        lr_cp_async_16(A_u + buf * T::TILE + tile_off(row), vbase + (int64_t)(ok ? tok : n_begin) * ld, ok);
       }
     }
     lr_cp_async_commit();
@@ -158,41 +166,36 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
 #pragma unroll
   for (int e = 0; e < 8; ++e) ksum[e] = 0.f;
 
-  issue(n_begin, 0);
+  fetch(n_begin);
+  issue_v(n_begin, 0);
   bool aborted = false;
   int it = 0;
   for (int n0 = n_begin; n0 < n_end; n0 += LR_TOK, ++it) {
     const int buf = it & 1;
-    // the products of the previous tile have read the rotated-k tile and v[buf ^ 1]; this barrier also
-    // orders the previous conversion's reads of stage[buf ^ 1] before the copies issued below
+    // the products of the previous tile have read the rotated-k tile and v[buf ^ 1]
     bool ok = true;
     if (it > 0) ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 1, &g_lr_status);
     if (__syncthreads_or(!ok)) {
       aborted = true;
       break;
     }
-    if (n0 + LR_TOK < n_end) {
-      issue(n0 + LR_TOK, buf ^ 1);
+    if (loader) {
+#pragma unroll
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        float x[8];
+        uint4 rot;
+        lr_relu_rotate8(kr[r], cr[r], sr[r], x, &rot);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ksum[e] += x[e];
+        *reinterpret_cast<uint4*>(smem + tile_off(16 * r + slot)) = rot;
+      }
+    }
+    if (n0 + LR_TOK < n_end) {  // the next tile: its loads fly during this tile's products and the next wait
+      fetch(n0 + LR_TOK);
+      issue_v(n0 + LR_TOK, buf ^ 1);
       lr_cp_async_wait<1>();
     } else {
       lr_cp_async_wait<0>();
-    }
-    __syncthreads();
-    if (loader) {
-      const unsigned char* st = smem + T::OFF_STAGE + buf * T::STAGE;
-#pragma unroll
-      for (int r = 0; r < LR_TOK / 16; ++r) {
-        const int row = 16 * r + slot;
-        const uint4 raw = *reinterpret_cast<const uint4*>(st + row * RAWB + grp * 16);
-        const float4 c = *reinterpret_cast<const float4*>(st + LR_TOK * RAWB + row * RAWB + grp * 16);
-        const float4 s = *reinterpret_cast<const float4*>(st + 2 * LR_TOK * RAWB + row * RAWB + grp * 16);
-        float x[8];
-        uint4 rot;
-        lr_relu_rotate8(raw, c, s, x, &rot);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ksum[e] += x[e];
-        *reinterpret_cast<uint4*>(smem + tile_off(row)) = rot;
-      }
     }
     fence_proxy_async_smem();  // this thread's stores and completed copies, before the tensor core reads them
     __syncthreads();
@@ -257,8 +260,8 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
 // value channels, K = 16 key channels each), both operands K-major (rows of 64 channels = 128
 // bytes, 128-byte swizzled, 8-row groups 1024 bytes apart, 64-channel blocks one after the other).
 // The state tile is converted to bf16 once per CTA; the token tile is filled 32 tokens at a time
-// by the staging pass (cp.async one sub-tile ahead, ReLU + rotation + normaliser as in the state
-// kernel).  Epilogue: warp w reads TMEM lanes 32 (w & 3) .. + 31 (= tokens) and every second
+// by the staging pass (the next 32 tokens already in registers; ReLU + rotation as in the state
+// kernel, and the 16 lanes of a token reduce its normaliser with shuffles).  Epilogue: warp w reads TMEM lanes 32 (w & 3) .. + 31 (= tokens) and every second
 // 16-column step, scales by 1 / (normaliser + eps), and writes bf16 rows (padded by 16 bytes) into
 // the token tile, which the products have finished reading; global stores are then 16 bytes per
 // lane, 16 lanes per token.  Waits are bounded as in the state kernel.
@@ -273,11 +276,8 @@ struct LrTcApply {
   static constexpr int Q_BLK = LR_MTOK * 128;         // one block of the token tile
   static constexpr int OROWB = 2 * D + 16;            // result rows, padded
   static constexpr int Q_BYTES = (KB * Q_BLK > LR_MTOK * OROWB ? KB * Q_BLK : LR_MTOK * OROWB + 1023) / 1024 * 1024;
-  static constexpr int RAWB = D * 2;
-  static constexpr int STAGE = 3 * LR_TOK * RAWB;     // raw q | cos | sin rows of 32 tokens
-  static constexpr int OFF_Q = S_BYTES;               // state | tokens | stage[2] | key sum | 1/normaliser | control
-  static constexpr int OFF_STAGE = OFF_Q + Q_BYTES;
-  static constexpr int OFF_KSUM = OFF_STAGE + 2 * STAGE;
+  static constexpr int OFF_Q = S_BYTES;               // state | tokens | key sum | 1/normaliser | control
+  static constexpr int OFF_KSUM = OFF_Q + Q_BYTES;
   static constexpr int OFF_RDEN = OFF_KSUM + D * 4;
   static constexpr int OFF_CTRL = OFF_RDEN + LR_MTOK * 4;
   static constexpr int BYTES = OFF_CTRL + 64;
@@ -288,13 +288,12 @@ struct LrTcApply {
 };
 
 template <int D>
-__global__ void __launch_bounds__(LR_THREADS, 2)
+__global__ void __launch_bounds__(LR_THREADS, 3)
 la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, const float* __restrict__ state,
                         __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
   using T = LrTcApply<D>;
   constexpr int G = D / 8;
-  constexpr int RAWB = T::RAWB;
   constexpr int SUBS = LR_MTOK / LR_TOK;  // staging sub-tiles per product tile
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sm_u = smem_u32(smem);
@@ -306,7 +305,7 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
   unsigned char* Qs = smem + T::OFF_Q;
   float* ksum_s = reinterpret_cast<float*>(smem + T::OFF_KSUM);
   float* rden_s = reinterpret_cast<float*>(smem + T::OFF_RDEN);
-  const uint32_t S_u = sm_u, Q_u = sm_u + T::OFF_Q, stage_u = sm_u + T::OFF_STAGE, ctrl = sm_u + T::OFF_CTRL;
+  const uint32_t S_u = sm_u, Q_u = sm_u + T::OFF_Q, ctrl = sm_u + T::OFF_CTRL;
   const uint32_t bar_mma = ctrl;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::OFF_CTRL + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::OFF_CTRL + 12);
@@ -329,22 +328,24 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
-  auto issue = [&](int n0, int buf) {  // 32 tokens from n0 into stage[buf]
-    if (loader) {
+  // raw q rows and their cos / sin rows of the NEXT 32 tokens wait in registers
+  uint4 qr[LR_TOK / 16];
+  float4 cr[LR_TOK / 16], sr[LR_TOK / 16];
+  auto fetch = [&](int n0) {
 #pragma unroll
-      for (int r = 0; r < LR_TOK / 16; ++r) {
-        const int row = 16 * r + slot, tok = n0 + row;
-        const bool ok = tok < n_end;
-        const int64_t t = ok ? tok : n_begin;
-        const uint32_t st = stage_u + buf * T::STAGE + row * RAWB + grp * 16;
-        lr_cp_async_16(st, qbase + t * ldq, ok);
-        lr_cp_async_16(st + LR_TOK * RAWB, cos_t + t * (D / 2) + 4 * grp, ok);
-        lr_cp_async_16(st + 2 * LR_TOK * RAWB, sin_t + t * (D / 2) + 4 * grp, ok);
+    for (int r = 0; r < LR_TOK / 16; ++r) {
+      const int tok = n0 + 16 * r + slot;
+      if (loader && tok < n_end) {
+        qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
+        cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
+        sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
+      } else {
+        qr[r] = make_uint4(0u, 0u, 0u, 0u);
+        cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    lr_cp_async_commit();
   };
-  issue(n_begin, 0);
+  fetch(n_begin);
 
   // the head's state as the B operand: row i (value channel), 16-byte chunks of 8 key channels
   const float* sg = state + ((int64_t)b * H + h) * (int64_t)((D + 1) * D);
@@ -366,36 +367,18 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
   for (int e = 0; e < 8; ++e) kreg[e] = loader ? ksum_s[8 * grp + e] : 0.f;
 
   bool aborted = false;
-  int sub = 0;  // staging sub-tiles consumed so far; its parity is the stage buffer
   int tile = 0;
   for (int m0 = n_begin; m0 < n_end; m0 += LR_MTOK, ++tile) {
+    if (tile > 0) __syncthreads();  // everybody has stored the previous tile's results out of the token tile
 #pragma unroll 1
-    for (int ss = 0; ss < SUBS; ++ss, ++sub) {
-      const int buf = sub & 1, n0 = m0 + ss * LR_TOK;
-      // everybody has left the previous conversion (stage[buf ^ 1]) and, at ss = 0, the previous tile's stores
-      __syncthreads();
-      if (n0 + LR_TOK < n_end) {  // sub-tiles past the end of the chunk are all zeros and need no copy
-        issue(n0 + LR_TOK, buf ^ 1);
-        lr_cp_async_wait<1>();
-      } else {
-        lr_cp_async_wait<0>();
-      }
-      __syncthreads();
-      const unsigned char* st = smem + T::OFF_STAGE + buf * T::STAGE;
-      const bool live = n0 < n_end;
+    for (int ss = 0; ss < SUBS; ++ss) {
+      const int n0 = m0 + ss * LR_TOK;
 #pragma unroll
       for (int r = 0; r < LR_TOK / 16; ++r) {
-        const int row = 16 * r + slot, trow = ss * LR_TOK + row;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        float4 c = make_float4(0.f, 0.f, 0.f, 0.f), s = c;
-        if (loader && live) {
-          raw = *reinterpret_cast<const uint4*>(st + row * RAWB + grp * 16);
-          c = *reinterpret_cast<const float4*>(st + LR_TOK * RAWB + row * RAWB + grp * 16);
-          s = *reinterpret_cast<const float4*>(st + 2 * LR_TOK * RAWB + row * RAWB + grp * 16);
-        }
+        const int trow = ss * LR_TOK + 16 * r + slot;
         float x[8];
         uint4 rot;
-        lr_relu_rotate8(raw, c, s, x, &rot);
+        lr_relu_rotate8(qr[r], cr[r], sr[r], x, &rot);
         float den = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) den = fmaf(x[e], kreg[e], den);
@@ -408,6 +391,7 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
         if (loader)
           *reinterpret_cast<uint4*>(Qs + (grp >> 3) * T::Q_BLK + trow * 128 + (((grp & 7) ^ (trow & 7)) << 4)) = rot;
       }
+      fetch(n0 + LR_TOK);  // zeros past the end of the chunk
     }
     fence_proxy_async_smem();  // this thread's stores, before the tensor core reads them
     __syncthreads();
@@ -453,7 +437,6 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
       }
     }
   }
-  lr_cp_async_wait<0>();  // nothing of this thread is still in flight, whichever way the loop ended
   (void)aborted;
   tcgen05_fence_before();
   __syncthreads();
@@ -619,9 +602,9 @@ static int lr_prepare() {
 template <int D>
 static void lr_state_plan(int64_t B, int64_t N, int64_t H, int* Lc, int* nchunks) {
   lr_prepare<D>();  // the occupancy query needs the shared-memory attribute
-  static const int64_t per_sm = resident_ctas(la_rope_state_tc_kernel<D>, LR_THREADS, LrSizes<D>::state_tc) / sm_count();
+  static const int64_t per_sm = resident_ctas_tmem(la_rope_state_tc_kernel<D>, LR_THREADS, LrSizes<D>::state_tc, LrTc<D>::TMEM_COLS) / sm_count();
   // a chunk's partial state ((D+1) x D fp32, written and re-read) costs as much as ~2 D tokens of k + v
-  la_chunking(B * H, N, per_sm * sm_count(), 2 * D, Lc, nchunks);
+  la_chunking(B * H, N, per_sm * sm_count(), 2 * D + 128, Lc, nchunks);
 }
 
 template <int D>
@@ -656,7 +639,7 @@ static int lr_apply(const void* q, int64_t ldq, const float* cos_t, const float*
   int Lc, nchunks;
   if (dtype == SANA_BF16) {
     static const int64_t per_sm =
-        resident_ctas(la_rope_apply_tc_kernel<D>, LR_THREADS, LrSizes<D>::apply_tc) / sm_count();
+        resident_ctas_tmem(la_rope_apply_tc_kernel<D>, LR_THREADS, LrSizes<D>::apply_tc, LrTcApply<D>::TMEM_COLS) / sm_count();
     // loading the head's state costs about as much as D / 2 tokens of q + out
     la_chunking(B * H, N, per_sm * sm_count(), D / 2, &Lc, &nchunks);
     dim3 grid((unsigned)H, nchunks, (unsigned)B);
