@@ -237,12 +237,21 @@ def run_kernel_rates(tokens_side: int, batch: int, iters: int = 20) -> None:
     rms_w = torch.ones(C, device=dev, dtype=torch.bfloat16)
     state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], batch, N, LH)
     o = torch.empty(rows, C, dtype=torch.bfloat16, device=dev)
+    # the video model's self-attention at the same width: 20 heads of 112 channels, rotation after the ReLU
+    VH, VD = C // 112, 112
+    ang = torch.randn(N, VD // 2, generator=g, device=dev)
+    rcos, rsin = ang.cos().contiguous(), ang.sin().contiguous()
+    rstate = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], rcos, rsin, batch, N, VH, VD)
     cases = [
         ("ln_modulate", lambda: ops.ln_modulate(x.view(batch, N, C), table, t, 0, 1), 2 * rows * C * 2),
         ("la_state", lambda: ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], batch, N, LH), 2 * rows * C * 2),
         ("la_apply", lambda: ops.la_apply(qkv[:, :C], state, batch, N, LH, 1e-8, out=o), 2 * rows * C * 2),
         ("dwconv_glu", lambda: ops.dwconv_glu(u, dw_w, dw_b, Wd, Hh), rows * 3 * HID * 2),
         ("rmsnorm", lambda: ops.rmsnorm_(qkv[:, :C], rms_w, 1e-5), 2 * rows * C * 2),
+        ("la_rope_state", lambda: ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], rcos, rsin, batch, N, VH, VD),
+         2 * rows * C * 2),
+        ("la_rope_apply", lambda: ops.la_rope_apply(qkv[:, :C], rcos, rsin, rstate, batch, N, VH, VD, 1e-8, out=o),
+         2 * rows * C * 2),
     ]
     out = {"workload": f"HBM-bound kernels, {batch} x {Wd}x{Hh} tokens, hidden {C}", "peak_gbs": peak,
            "peak_source": peaks["source"], "rows": []}
