@@ -325,6 +325,35 @@ def sana_ms_block_forward(x, y, t, p: Params, num_heads: int, HW: Sequence[int],
     return x
 
 
+def sana_video_block_forward(x, y, t, p: Params, num_heads: int, THW: Sequence[int], rotary_emb, mask=None,
+                             linear_head_dim: int = 112) -> torch.Tensor:
+    """SanaVideoMSBlock.forward with attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp" (or
+    "glumbconv" when ``p`` has no ``mlp.t_conv.weight``), drop_path 0, no additional attention,
+    diffusion/model/nets/sana_multi_scale_video.py:256-333; a ``t`` of more than two dimensions
+    ([B, 1, F, 6C]: one modulation per frame) takes forward_frame_aware (:204-254)."""
+    B, N, C = x.shape
+    heads = C // linear_head_dim
+    mlp = glumbconv_temp_forward if "mlp.t_conv.weight" in p else glumbconv_forward
+    if t.dim() > 2:
+        Fr = t.shape[2]
+        tt = t.reshape(B, Fr, 6, -1)
+        mod = (p["scale_shift_table"][None, None, :, :] + tt).chunk(6, dim=-2)  # each [B, F, 1, C]
+        shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
+        z = t2i_modulate(layer_norm(x).reshape(B, Fr, -1, C), shift_msa, scale_msa).reshape(B, N, C)
+        a = lite_la_relu_rope_forward(z, sub(p, "attn"), heads, rotary_emb, eps=BLOCK_LA_EPS)
+        x = x + (gate_msa * a.reshape(B, Fr, -1, C)).reshape(B, N, C)
+        x = x + cross_attention_forward(x, y, sub(p, "cross_attn"), num_heads, mask)
+        z = t2i_modulate(layer_norm(x).reshape(B, Fr, -1, C), shift_mlp, scale_mlp).reshape(B, N, C)
+        return x + (gate_mlp * mlp(z, sub(p, "mlp"), THW).reshape(B, Fr, -1, C)).reshape(B, N, C)
+    mod = (p["scale_shift_table"][None] + t.reshape(B, 6, -1)).chunk(6, dim=1)
+    shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
+    a = lite_la_relu_rope_forward(t2i_modulate(layer_norm(x), shift_msa, scale_msa), sub(p, "attn"), heads, rotary_emb,
+                                  eps=BLOCK_LA_EPS)
+    x = x + gate_msa * a
+    x = x + cross_attention_forward(x, y, sub(p, "cross_attn"), num_heads, mask)
+    return x + gate_mlp * mlp(t2i_modulate(layer_norm(x), shift_mlp, scale_mlp), sub(p, "mlp"), THW)
+
+
 def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: int = 10000) -> torch.Tensor:
     """TimestepEmbedder.timestep_embedding, diffusion/model/nets/sana_blocks.py:980-999."""
     half = dim // 2

@@ -32,17 +32,18 @@ __device__ __forceinline__ void lr_cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-// ReLU of 8 bf16 channels (4 rotation pairs) of one token: x = relu(raw) in fp32, and
-// rot = the rotated pairs packed back to bf16.
-__device__ __forceinline__ void lr_relu_rotate8(const uint4 raw, const float4 c, const float4 s, float (&x)[8],
+// ReLU of 8 bf16 channels (4 rotation pairs) of one token: x[p] = the pair relu(raw[2p], raw[2p+1])
+// in fp32 (the ReLU runs on the packed bf16 pair), and rot = the rotated pairs packed back to bf16.
+__device__ __forceinline__ void lr_relu_rotate8(const uint4 raw, const float4 c, const float4 s, float2 (&x)[4],
                                                 uint4* rot) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
   uint32_t o[4];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    const float x0 = fmaxf(bf16_lo(w[p]), 0.f), x1 = fmaxf(bf16_hi(w[p]), 0.f);
-    x[2 * p] = x0, x[2 * p + 1] = x1;
+    const uint32_t r = relu_bf16x2(w[p]);
+    const float x0 = bf16_lo(r), x1 = bf16_hi(r);
+    x[p] = make_float2(x0, x1);
     o[p] = pack_bf16(x0 * cc[p] - x1 * ss[p], x0 * ss[p] + x1 * cc[p]);
   }
   *rot = make_uint4(o[0], o[1], o[2], o[3]);
@@ -162,9 +163,9 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
     lr_cp_async_commit();
   };
 
-  float ksum[8];
+  float2 ksum[4];  // packed fp32 adds
 #pragma unroll
-  for (int e = 0; e < 8; ++e) ksum[e] = 0.f;
+  for (int e = 0; e < 4; ++e) ksum[e] = make_float2(0.f, 0.f);
 
   fetch(n_begin);
   issue_v(n_begin, 0);
@@ -182,11 +183,11 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
     if (loader) {
 #pragma unroll
       for (int r = 0; r < LR_TOK / 16; ++r) {
-        float x[8];
+        float2 x[4];
         uint4 rot;
         lr_relu_rotate8(kr[r], cr[r], sr[r], x, &rot);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ksum[e] += x[e];
+        for (int e = 0; e < 4; ++e) ksum[e] = __fadd2_rn(ksum[e], x[e]);
         *reinterpret_cast<uint4*>(smem + tile_off(16 * r + slot)) = rot;
       }
     }
@@ -236,7 +237,7 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
     float* red = reinterpret_cast<float*>(smem);  // [16][D]; the rotated-k tile is no longer read
     if (loader) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) red[slot * D + 8 * grp + e] = ksum[e];
+      for (int e = 0; e < 4; ++e) *reinterpret_cast<float2*>(red + slot * D + 8 * grp + 2 * e) = ksum[e];
     }
     __syncthreads();
     if (tid < D) {
@@ -362,9 +363,10 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  float kreg[8];
+  float2 kreg[4];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) kreg[e] = loader ? ksum_s[8 * grp + e] : 0.f;
+  for (int e = 0; e < 4; ++e)
+    kreg[e] = loader ? *reinterpret_cast<const float2*>(ksum_s + 8 * grp + 2 * e) : make_float2(0.f, 0.f);
 
   bool aborted = false;
   int tile = 0;
@@ -376,12 +378,13 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
 #pragma unroll
       for (int r = 0; r < LR_TOK / 16; ++r) {
         const int trow = ss * LR_TOK + 16 * r + slot;
-        float x[8];
+        float2 x[4];
         uint4 rot;
         lr_relu_rotate8(qr[r], cr[r], sr[r], x, &rot);
-        float den = 0.f;
+        float2 den2 = __fmul2_rn(x[0], kreg[0]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) den = fmaf(x[e], kreg[e], den);
+        for (int e = 1; e < 4; ++e) den2 = __ffma2_rn(x[e], kreg[e], den2);
+        float den = den2.x + den2.y;
         // all 32 lanes take part: the 16 lanes of a token are one half of a warp
         den += __shfl_xor_sync(0xffffffffu, den, 1);
         den += __shfl_xor_sync(0xffffffffu, den, 2);

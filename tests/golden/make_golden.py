@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from ref_loader import load_reference, set_fp32_attention  # noqa: E402
+from ref_loader import load_reference, load_video_module, set_fp32_attention  # noqa: E402
 
 from sana_b200 import synthetic  # noqa: E402
 
@@ -183,6 +183,37 @@ def litela_relu_rope_case(R, seed=11):
     return out
 
 
+def video_block_case(ref_root, R, seed=12):
+    """Upstream's SanaVideoMSBlock (LiteLAReLURope + cross-attention + GLUMBConvTemp) on 3 frames of
+    4 x 5 tokens, with one modulation per sample and with one per frame."""
+    V = load_video_module(ref_root)
+    C, heads, lin_dim, hid, THW, B, L = 96, 2, 48, 240, (3, 4, 5), 2, 7
+    N = THW[0] * THW[1] * THW[2]
+    g = torch.Generator().manual_seed(seed)
+    params = synthetic.make_block_params(C, hid, seed, std=0.06)
+    params["mlp.t_conv.weight"] = torch.randn(C, C, 3, 1, generator=g) * 0.05
+    x = torch.randn(B, N, C, generator=g) * 0.7
+    y = torch.randn(B, L, C, generator=g) * 0.7
+    t = torch.randn(B, 6 * C, generator=g) * 0.3
+    t_frames = torch.randn(B, 1, THW[0], 6 * C, generator=g) * 0.3
+    mask = torch.ones(B, L)
+    mask[1, 5:] = 0
+    rope = R.sana_blocks.WanRotaryPosEmbed(attention_head_dim=lin_dim, patch_size=(1, 1, 1), max_seq_len=1024)
+    freqs = rope(THW, torch.device("cpu"))
+    # the block parameters are regenerated from the seed (sana_b200.synthetic.make_block_params); only t_conv is stored
+    out = {"C": C, "heads": heads, "linear_head_dim": lin_dim, "hid": hid, "THW": THW, "param_seed": seed, "param_std": 0.06,
+           "t_conv": params["mlp.t_conv.weight"], "x": x, "y": y, "t": t, "t_frames": t_frames, "mask": mask, "freqs": freqs}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            m = V.SanaVideoMSBlock(C, heads, mlp_ratio=hid / C, attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp",
+                                   linear_head_dim=lin_dim).eval()
+            m.load_state_dict(params, strict=True)
+            m = m.to(dt)
+            out[f"out_{tag}"] = m(x.to(dt), y.to(dt), t.to(dt), mask=mask, THW=THW, rotary_emb=freqs)
+            out[f"out_frames_{tag}"] = m(x.to(dt), y.to(dt), t_frames.to(dt), mask=mask, THW=THW, rotary_emb=freqs)
+    return out
+
+
 def final_layer_case(R, seed=10):
     """Upstream's T2IFinalLayer with one modulation vector per sample and per frame."""
     C, B, Fr, P = 64, 2, 3, 10
@@ -263,6 +294,7 @@ def main():
         "glumbconv_temp": lambda: glumbconv_temp_case(R),
         "final_layer": lambda: final_layer_case(R),
         "litela_relu_rope": lambda: litela_relu_rope_case(R),
+        "video_block": lambda: video_block_case(a.ref, R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():

@@ -153,6 +153,19 @@ def load_reference(root: str):
     return ns
 
 
+def load_video_module(root: str):
+    """Upstream's ``sana_multi_scale_video`` (SanaVideoMSBlock).  Its one import outside the nets,
+    ``diffusion.model.wan.model.BlockHook`` (a type annotation), is stubbed: the real module needs
+    diffusers."""
+    load_reference(root)
+    if "diffusion.model.wan.model" not in sys.modules:
+        _ns("diffusion.model.wan")
+        wm = types.ModuleType("diffusion.model.wan.model")
+        wm.BlockHook = object
+        sys.modules["diffusion.model.wan.model"] = wm
+    return importlib.import_module("diffusion.model.nets.sana_multi_scale_video")
+
+
 def set_fp32_attention(module: nn.Module) -> None:
     """What upstream ``build_model(use_fp32_attention=True)`` does for every shipped config."""
     for m in module.modules():
