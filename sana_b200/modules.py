@@ -386,6 +386,39 @@ class GLUMBConvTemp(GLUMBConv):
                 ops.gemm(s[lo + hw:hi], w_next, residual=y[lo:hi - hw], out=y[lo:hi - hw])
         return y.reshape(B, N, C)
 
+    @torch.no_grad()
+    def forward_gated(self, z: torch.Tensor, HW, x2: torch.Tensor, table: torch.Tensor, t2: torch.Tensor, row: int,
+                      rows_per_vec: int) -> torch.Tensor:
+        """``x2 + gate * forward(z)`` for the video block, [B*N, C]: ``gate`` = table[row] + t2[v, row] for
+        the v-th run of ``rows_per_vec`` tokens (one modulation vector per sample, or per frame).  The
+        spatial result enters through one fused multiply-add, the three temporal taps through the
+        gate + residual epilogue of their projections."""
+        if HW is None or len(HW) != 3:
+            raise ValueError("HW must be a tuple of (T, H, W)")
+        if self.seq_shard is not None:
+            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
+        B, N, C = z.shape
+        T, H, W = HW
+        hw = H * W
+        s = _as2d(GLUMBConv.forward(self, z, HW=HW))
+        vecs = (B * N) // rows_per_vec
+        gate = (table[row].float()[None] + t2.reshape(vecs, 6, C)[:, row].float()).to(s.dtype)  # [vecs, C]
+        y = torch.addcmul(x2.view(vecs, rows_per_vec, C), gate[:, None, :], s.view(vecs, rows_per_vec, C)).view(B * N, C)
+        w_prev, w_mid, w_next = self._taps()
+        per_sample = N // rows_per_vec  # modulation vectors per sample: 1, or T
+        y = ops.gemm(s, w_mid, gate=(table, t2, row, rows_per_vec), residual=y, out=y)
+        for b in range(B):
+            lo, hi = b * N, (b + 1) * N
+            if T > 1:
+                v0 = b * per_sample
+                # output frames 1 .. T-1 take frame t-1: their vectors start one frame later when per frame
+                t_hi = t2[v0 + (1 if per_sample > 1 else 0):v0 + per_sample]
+                ops.gemm(s[lo:hi - hw], w_prev, gate=(table, t_hi, row, rows_per_vec), residual=y[lo + hw:hi],
+                         out=y[lo + hw:hi])
+                ops.gemm(s[lo + hw:hi], w_next, gate=(table, t2[v0:v0 + per_sample], row, rows_per_vec),
+                         residual=y[lo:hi - hw], out=y[lo:hi - hw])
+        return y
+
 
 class MultiHeadCrossAttention(nn.Module):
     """Softmax attention of image tokens over the text tokens (upstream's SDPA branch), with
@@ -520,6 +553,76 @@ class SanaMSBlock(nn.Module):
         pc = mlp.point_conv.conv
         x2 = _project(mlp, "point_conv", g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias,
                       gate=(table, t, 5, N), residual=x2)
+        return x2.view(B, N, C)
+
+
+class SanaVideoMSBlock(nn.Module):
+    """The block of Sana-Video (upstream's SanaVideoMSBlock, sana_multi_scale_video.py:65-333):
+    modulate -> self-attention (``LiteLAReLURope`` or ``LiteLA``) -> gate + residual -> cross-attention
+    + residual -> modulate -> Mix-FFN (``GLUMBConvTemp`` or ``GLUMBConv``) -> gate + residual, on a
+    (T, H, W) token grid.  ``t`` is [B, 6C] (one modulation per sample) or [B, 1, F, 6C] (one per
+    frame, upstream's forward_frame_aware).  Same constructor arguments and state-dict keys as
+    upstream for the covered options."""
+
+    def __init__(self, hidden_size, num_heads, mlp_ratio=4.0, drop_path=0.0, qk_norm=False, attn_type="flash",
+                 ffn_type="mlp", mlp_acts=("silu", "silu", None), linear_head_dim=32, cross_norm=False,
+                 cross_attn_image_embeds=False, t_kernel_size=3, additional_flash_attn=False,
+                 flash_attn_window_count=None, **block_kwargs):
+        super().__init__()
+        if attn_type not in ("linear", "LiteLAReLURope") or ffn_type not in ("glumbconv", "GLUMBConvTemp"):
+            raise NotImplementedError("SanaVideoMSBlock here covers attn_type 'linear' / 'LiteLAReLURope' with "
+                                      "ffn_type 'glumbconv' / 'GLUMBConvTemp'")
+        if drop_path != 0.0 or cross_attn_image_embeds or additional_flash_attn:
+            raise NotImplementedError("drop_path, image-embedding cross-attention and the additional softmax "
+                                      "attention are not covered")
+        self.hidden_size = hidden_size
+        self.norm1 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
+        attn_cls = LiteLA if attn_type == "linear" else LiteLAReLURope
+        self.attn = attn_cls(hidden_size, hidden_size, heads=hidden_size // linear_head_dim, eps=1e-8, qk_norm=qk_norm)
+        self.flash_attn_additional = None
+        self.cross_attn_image_embeds = False
+        self.cross_attn = MultiHeadCrossAttention(hidden_size, num_heads, qk_norm=cross_norm, **block_kwargs)
+        self.norm2 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
+        ffn = dict(in_features=hidden_size, hidden_features=int(hidden_size * mlp_ratio), use_bias=(True, True, False),
+                   norm=(None, None, None), act=mlp_acts)
+        self.mlp = GLUMBConv(**ffn) if ffn_type == "glumbconv" else GLUMBConvTemp(t_kernel_size=t_kernel_size, **ffn)
+        self.drop_path = nn.Identity()
+        self.scale_shift_table = nn.Parameter(torch.randn(6, hidden_size) / hidden_size ** 0.5)
+        self.block_hook = None
+
+    @torch.no_grad()
+    def forward(self, x, y, t, mask=None, THW=None, rotary_emb=None, chunk_index=None, **kwargs):
+        if chunk_index is not None or kwargs.get("kv_cache") is not None or kwargs.get("save_kv_cache") is not None:
+            raise NotImplementedError("chunked / cached (autoregressive) inference is not covered")
+        if self.block_hook is not None:
+            raise NotImplementedError("block hooks are not covered")
+        B, N, C = x.shape
+        if t.dim() > 2:  # [B, 1, F, 6C]: one modulation per frame = per run of N / F tokens
+            frames = t.shape[2]
+            if N % frames:
+                raise ValueError("the token count is not a multiple of the frame count of t")
+            rows = N // frames
+        else:
+            rows = N
+        t2 = t.reshape(B * (N // rows), 6 * C)
+        x2 = _as2d(x.contiguous())
+        table = self.scale_shift_table
+        attn, mlp, ca = self.attn, self.mlp, self.cross_attn
+        z = ops.ln_modulate(x2.view(-1, rows, C), table, t2, 0, 1, LN_EPS)
+        qkv = _project(attn, "qkv", _as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
+        o = attn._core(qkv, B, N, rotary_emb)
+        x2 = _project(attn, "proj", o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t2, 2, rows), residual=x2)
+        o = ca._attend(x2, y, mask, B, kwargs.get("caption_kv"))
+        x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
+        z = ops.ln_modulate(x2.view(-1, rows, C), table, t2, 3, 4, LN_EPS)
+        if isinstance(mlp, GLUMBConvTemp):
+            x2 = mlp.forward_gated(z.view(B, N, C), THW, x2, table, t2, 5, rows)
+        else:
+            u = mlp._expand(_as2d(z))
+            g = mlp._depthwise_glu(u, B, N, THW)
+            pc = mlp.point_conv.conv
+            x2 = _project(mlp, "point_conv", g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias,
+                          gate=(table, t2, 5, rows), residual=x2)
         return x2.view(B, N, C)
 
 

@@ -153,3 +153,56 @@ def test_module_video_head_width(dt, tol):
         out = m(x.to(DEV, dt), rotary_emb=freqs.to(DEV))
         again = m(x.to(DEV, dt), rotary_emb=(freqs[0, 0].real.float(), freqs[0, 0].imag.float()))
     assert nmax_err(out, ref) < tol and torch.equal(out, again)
+
+
+# ------------------------------------------------------------------ the video block against upstream's outputs
+def _video_params(g):
+    from sana_b200 import synthetic
+    p = synthetic.make_block_params(g["C"], g["hid"], g["param_seed"], std=g["param_std"])
+    p["mlp.t_conv.weight"] = g["t_conv"]
+    return p
+
+
+@pytest.mark.parametrize("tname", ["t", "t_frames"])
+@pytest.mark.parametrize("tag,dt,tol", [("f32", torch.float32, 1e-5), ("bf16", torch.bfloat16, 2e-2)])
+def test_video_block_matches_upstream_fixture(golden, tag, dt, tol, tname):
+    """SanaVideoMSBlock: LiteLAReLURope + cross-attention + GLUMBConvTemp, one modulation per sample
+    (t [B, 6C]) and one per frame (t [B, 1, F, 6C])."""
+    g = golden("video_block")
+    C = g["C"]
+    blk = sana_b200.SanaVideoMSBlock(C, g["heads"], mlp_ratio=g["hid"] / C, attn_type="LiteLAReLURope",
+                                     ffn_type="GLUMBConvTemp", linear_head_dim=g["linear_head_dim"])
+    blk.load_state_dict(_video_params(g), strict=True)
+    blk = blk.to(DEV, dt).eval()
+    with torch.no_grad():
+        out = blk(g["x"].to(DEV, dt), g["y"].to(DEV, dt), g[tname].to(DEV, dt), mask=g["mask"].to(DEV), THW=g["THW"],
+                  rotary_emb=g["freqs"])
+    key = "out_" if tname == "t" else "out_frames_"
+    assert out.dtype == dt and nmax_err(out, g[key + "f32"]) < tol
+    if dt == torch.bfloat16:  # no further from upstream's fp32 result than upstream's own bf16 run, up to rounding noise
+        assert nmax_err(out, g[key + "f32"]) < 2 * nmax_err(g[key + "bf16"], g[key + "f32"]) + 4e-3
+
+
+def test_video_block_with_spatial_ffn_and_plain_linear_attention():
+    """The other covered options: GLUMBConv per frame, and LiteLA (no rotation) as the self-attention."""
+    from sana_b200 import synthetic
+    C, hid, THW, B, L = 64, 160, (2, 4, 6), 2, 5
+    N = THW[0] * THW[1] * THW[2]
+    p = synthetic.make_block_params(C, hid, 21, std=0.06)
+    x, y, t = _r(B, N, C, seed=1, scale=0.7), _r(B, L, C, seed=2, scale=0.7), _r(B, 6 * C, seed=3, scale=0.3)
+    blk = sana_b200.SanaVideoMSBlock(C, 2, mlp_ratio=hid / C, attn_type="linear", ffn_type="glumbconv", linear_head_dim=32)
+    blk.load_state_dict(p, strict=True)
+    blk = blk.to(DEV).eval()
+    ref = O.sana_ms_block_forward(x, y, t, p, 2, THW)
+    with torch.no_grad():
+        out = blk(x.to(DEV), y.to(DEV), t.to(DEV), THW=THW)
+    assert nmax_err(out, ref) < 1e-5
+    fr = sana_b200.wan_rotary_freqs(16, THW)
+    blk2 = sana_b200.SanaVideoMSBlock(C, 2, mlp_ratio=hid / C, attn_type="LiteLAReLURope", ffn_type="glumbconv",
+                                      linear_head_dim=16)
+    blk2.load_state_dict(p, strict=True)
+    blk2 = blk2.to(DEV).eval()
+    ref2 = O.sana_video_block_forward(x, y, t, p, 2, THW, fr, linear_head_dim=16)
+    with torch.no_grad():
+        out2 = blk2(x.to(DEV), y.to(DEV), t.to(DEV), THW=THW, rotary_emb=fr)
+    assert nmax_err(out2, ref2) < 1e-5

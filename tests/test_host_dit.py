@@ -52,3 +52,23 @@ def test_video_ffn_keeps_upstreams_keys(golden):
                                 norm=(None, None, None), act=("silu", "silu", None))
     assert set(m.state_dict().keys()) == set(g["params"].keys())
     assert float(m.t_conv.weight.detach().abs().sum()) == 0.0  # zero-initialised like upstream
+
+
+def test_video_block_state_dict_keys_and_guards():
+    import sana_b200
+    blk = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp",
+                                     linear_head_dim=48)
+    assert set(blk.state_dict()) == {
+        "scale_shift_table", "attn.qkv.weight", "attn.proj.weight", "attn.proj.bias", "cross_attn.q_linear.weight",
+        "cross_attn.q_linear.bias", "cross_attn.kv_linear.weight", "cross_attn.kv_linear.bias", "cross_attn.proj.weight",
+        "cross_attn.proj.bias", "mlp.inverted_conv.conv.weight", "mlp.inverted_conv.conv.bias",
+        "mlp.depth_conv.conv.weight", "mlp.depth_conv.conv.bias", "mlp.point_conv.conv.weight", "mlp.t_conv.weight"}
+    assert blk.attn.dim == 48 and blk.attn.heads == 2
+    import pytest
+    with pytest.raises(NotImplementedError):
+        sana_b200.SanaVideoMSBlock(96, 2, attn_type="flash", ffn_type="GLUMBConvTemp")
+    with pytest.raises(NotImplementedError):
+        sana_b200.SanaVideoMSBlock(96, 2, attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp", linear_head_dim=48,
+                                   additional_flash_attn="flash")
+    with pytest.raises(NotImplementedError):
+        sana_b200.LiteLAReLURope(80, 80, heads=2)  # heads of 40 channels
