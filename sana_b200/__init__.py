@@ -6,11 +6,11 @@ that keep upstream's signatures.  There is no CPU path.
 """
 from . import graphs, ops, sharding, synthetic  # noqa: F401
 from ._lib import SanaLibraryError, load as load_library  # noqa: F401
-from .modules import (BlockStack, ConvLayer, GLUMBConv, GLUMBConvTemp, LiteLA, LiteLAReLURope,  # noqa: F401
+from .modules import (BlockStack, ChunkedLiteLAReLURope, ConvLayer, GLUMBConv, GLUMBConvTemp, LiteLA, LiteLAReLURope,  # noqa: F401
                       MultiHeadCrossAttention, RMSNorm, SanaMSBlock, SanaVideoMSBlock, wan_rotary_freqs)
 from .weight_pack import load_nvfp4_weights, pack_nvfp4_weights  # noqa: F401
 from .dit import CaptionEmbedder, PatchEmbedMS, SanaMS, T2IFinalLayer, TimestepEmbedder  # noqa: F401
 
-__all__ = ["LiteLA", "LiteLAReLURope", "wan_rotary_freqs", "GLUMBConv", "GLUMBConvTemp", "ConvLayer", "MultiHeadCrossAttention", "SanaMSBlock", "SanaVideoMSBlock", "BlockStack", "RMSNorm",
+__all__ = ["LiteLA", "LiteLAReLURope", "ChunkedLiteLAReLURope", "wan_rotary_freqs", "GLUMBConv", "GLUMBConvTemp", "ConvLayer", "MultiHeadCrossAttention", "SanaMSBlock", "SanaVideoMSBlock", "BlockStack", "RMSNorm",
            "SanaMS", "pack_nvfp4_weights", "load_nvfp4_weights", "PatchEmbedMS", "TimestepEmbedder", "CaptionEmbedder", "T2IFinalLayer", "ops",
            "sharding", "synthetic", "load_library", "SanaLibraryError"]

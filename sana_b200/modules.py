@@ -256,6 +256,17 @@ class LiteLAReLURope(nn.Module):
         return _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
 
 
+class ChunkedLiteLAReLURope(LiteLAReLURope):
+    """Upstream's ChunkedLiteLAReLURope (sana_blocks.py:1790-1914) sums ``vk`` over chunks of
+    ``chunk_size`` tokens to bound its temporaries; the result is the same sum.  The state kernel here
+    already walks the tokens in tiles and keeps nothing token-sized, so ``chunk_size`` is accepted and
+    has no effect."""
+
+    def __init__(self, *args, chunk_size=200_000, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.chunk_size = chunk_size
+
+
 class ConvLayer(nn.Module):
     """Parameter holder with upstream's ``conv`` / ``norm`` / ``act`` attributes
     (basic_modules.py:32-99) so checkpoints load unchanged; GLUMBConv reads the weights and
@@ -569,16 +580,16 @@ class SanaVideoMSBlock(nn.Module):
                  cross_attn_image_embeds=False, t_kernel_size=3, additional_flash_attn=False,
                  flash_attn_window_count=None, **block_kwargs):
         super().__init__()
-        if attn_type not in ("linear", "LiteLAReLURope") or ffn_type not in ("glumbconv", "GLUMBConvTemp"):
-            raise NotImplementedError("SanaVideoMSBlock here covers attn_type 'linear' / 'LiteLAReLURope' with "
-                                      "ffn_type 'glumbconv' / 'GLUMBConvTemp'")
+        attn_classes = {"linear": LiteLA, "LiteLAReLURope": LiteLAReLURope, "ChunkedLiteLAReLURope": ChunkedLiteLAReLURope}
+        if attn_type not in attn_classes or ffn_type not in ("glumbconv", "GLUMBConvTemp"):
+            raise NotImplementedError("SanaVideoMSBlock here covers attn_type 'linear' / 'LiteLAReLURope' / "
+                                      "'ChunkedLiteLAReLURope' with ffn_type 'glumbconv' / 'GLUMBConvTemp'")
         if drop_path != 0.0 or cross_attn_image_embeds or additional_flash_attn:
             raise NotImplementedError("drop_path, image-embedding cross-attention and the additional softmax "
                                       "attention are not covered")
         self.hidden_size = hidden_size
         self.norm1 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
-        attn_cls = LiteLA if attn_type == "linear" else LiteLAReLURope
-        self.attn = attn_cls(hidden_size, hidden_size, heads=hidden_size // linear_head_dim, eps=1e-8, qk_norm=qk_norm)
+        self.attn = attn_classes[attn_type](hidden_size, hidden_size, heads=hidden_size // linear_head_dim, eps=1e-8, qk_norm=qk_norm)
         self.flash_attn_additional = None
         self.cross_attn_image_embeds = False
         self.cross_attn = MultiHeadCrossAttention(hidden_size, num_heads, qk_norm=cross_norm, **block_kwargs)
