@@ -138,6 +138,18 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
   uint4 kr[LR_TOK / 16];
   float4 cr[LR_TOK / 16], sr[LR_TOK / 16];
   auto fetch = [&](int n0) {
+    if (n0 + LR_TOK <= n_end) {  // whole tile (uniform): no per-row tests, nothing to clear
+      if (loader) {
+#pragma unroll
+        for (int r = 0; r < LR_TOK / 16; ++r) {
+          const int64_t tok = n0 + 16 * r + slot;
+          kr[r] = ldg_nc_u4(kbase + tok * ld);
+          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + tok * (D / 2) + 4 * grp));
+          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + tok * (D / 2) + 4 * grp));
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int r = 0; r < LR_TOK / 16; ++r) {
       const int tok = n0 + 16 * r + slot;
@@ -174,8 +186,9 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
   for (int n0 = n_begin; n0 < n_end; n0 += LR_TOK, ++it) {
     const int buf = it & 1;
     // the products of the previous tile have read the rotated-k tile and v[buf ^ 1]
+    // (one warp polls the barrier; the others park at the CTA barrier and spend no issue slots)
     bool ok = true;
-    if (it > 0) ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 1, &g_lr_status);
+    if (it > 0 && warp == 0) ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 1, &g_lr_status);
     if (__syncthreads_or(!ok)) {
       aborted = true;
       break;
@@ -211,7 +224,8 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
   }
   lr_cp_async_wait<0>();  // nothing of this thread is still in flight, whichever way the loop ended
   if (!aborted) {
-    const bool ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 2, &g_lr_status);
+    bool ok = true;
+    if (warp == 0) ok = mbar_wait(bar_mma, (uint32_t)((it - 1) & 1), abort_flag, 2, &g_lr_status);
     if (__syncthreads_or(!ok)) aborted = true;
   }
   tcgen05_fence_after();
@@ -332,7 +346,24 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
   // raw q rows and their cos / sin rows of the NEXT 32 tokens wait in registers
   uint4 qr[LR_TOK / 16];
   float4 cr[LR_TOK / 16], sr[LR_TOK / 16];
+#pragma unroll
+  for (int r = 0; r < LR_TOK / 16; ++r) {  // lanes without a channel group keep zeros: they join the shuffles
+    qr[r] = make_uint4(0u, 0u, 0u, 0u);
+    cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   auto fetch = [&](int n0) {
+    if (n0 + LR_TOK <= n_end) {  // whole sub-tile (uniform): no per-row tests, nothing to clear
+      if (loader) {
+#pragma unroll
+        for (int r = 0; r < LR_TOK / 16; ++r) {
+          const int64_t tok = n0 + 16 * r + slot;
+          qr[r] = ldg_nc_u4(qbase + tok * ldq);
+          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + tok * (D / 2) + 4 * grp));
+          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + tok * (D / 2) + 4 * grp));
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int r = 0; r < LR_TOK / 16; ++r) {
       const int tok = n0 + 16 * r + slot;
@@ -408,7 +439,8 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
       }
       umma_commit(bar_mma);
     }
-    const bool ok = mbar_wait(bar_mma, (uint32_t)(tile & 1), abort_flag, 3, &g_lr_status);
+    bool ok = true;  // one warp polls; the others park at the CTA barrier
+    if (warp == 0) ok = mbar_wait(bar_mma, (uint32_t)(tile & 1), abort_flag, 3, &g_lr_status);
     if (__syncthreads_or(!ok)) {
       aborted = true;
       break;
