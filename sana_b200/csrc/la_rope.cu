@@ -91,7 +91,7 @@ __device__ __forceinline__ uint64_t lr_desc_mn(uint32_t saddr, uint32_t block_st
 
 template <int D>
 __global__ void __launch_bounds__(LR_THREADS, 4)
-la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int64_t ld,
+la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int ld,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                         float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
   using T = LrTc<D>;
@@ -112,8 +112,8 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
   const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
   const bool loader = grp < G;
   const int64_t col = (int64_t)h * D + 8 * grp;
-  const __nv_bfloat16* kbase = kp + (int64_t)b * N * ld + col;
-  const __nv_bfloat16* vbase = vp + (int64_t)b * N * ld + col;
+  const __nv_bfloat16* kbase = kp + (int64_t)b * N * (int64_t)ld + col;
+  const __nv_bfloat16* vbase = vp + (int64_t)b * N * (int64_t)ld + col;
 
   if (tid == 0) {
     mbar_init(bar_mma, 1);
@@ -142,10 +142,10 @@ la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat1
       if (loader) {
 #pragma unroll
         for (int r = 0; r < LR_TOK / 16; ++r) {
-          const int64_t tok = n0 + 16 * r + slot;
-          kr[r] = ldg_nc_u4(kbase + tok * ld);
-          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + tok * (D / 2) + 4 * grp));
-          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + tok * (D / 2) + 4 * grp));
+          const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
+          kr[r] = ldg_nc_u4(kbase + (int64_t)tok * ld);
+          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
+          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
         }
       }
       return;
@@ -304,9 +304,9 @@ struct LrTcApply {
 
 template <int D>
 __global__ void __launch_bounds__(LR_THREADS, 3)
-la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ cos_t,
+la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, const float* __restrict__ state,
-                        __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+                        __nv_bfloat16* __restrict__ op, int ldo, int N, int H, int Lc, float eps) {
   using T = LrTcApply<D>;
   constexpr int G = D / 8;
   constexpr int SUBS = LR_MTOK / LR_TOK;  // staging sub-tiles per product tile
@@ -329,8 +329,8 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
   const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
   const bool loader = grp < G;
   const int64_t col = (int64_t)h * D + 8 * grp;
-  const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
-  __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
+  const __nv_bfloat16* qbase = qp + (int64_t)b * N * (int64_t)ldq + col;
+  __nv_bfloat16* obase = op + (int64_t)b * N * (int64_t)ldo + col;
 
   if (tid == 0) {
     mbar_init(bar_mma, 1);
@@ -356,10 +356,10 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
       if (loader) {
 #pragma unroll
         for (int r = 0; r < LR_TOK / 16; ++r) {
-          const int64_t tok = n0 + 16 * r + slot;
-          qr[r] = ldg_nc_u4(qbase + tok * ldq);
-          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + tok * (D / 2) + 4 * grp));
-          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + tok * (D / 2) + 4 * grp));
+          const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
+          qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
+          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
+          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
         }
       }
       return;
@@ -421,7 +421,7 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const
         den += __shfl_xor_sync(0xffffffffu, den, 2);
         den += __shfl_xor_sync(0xffffffffu, den, 4);
         den += __shfl_xor_sync(0xffffffffu, den, 8);
-        if (grp == 0) rden_s[trow] = 1.0f / (den + eps);
+        if (grp == 0) rden_s[trow] = __fdividef(1.0f, den + eps);  // MUFU reciprocal, 2 ulp
         if (loader)
           *reinterpret_cast<uint4*>(Qs + (grp >> 3) * T::Q_BLK + trow * 128 + (((grp & 7) ^ (trow & 7)) << 4)) = rot;
       }
@@ -652,8 +652,8 @@ static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t
   if (dtype == SANA_BF16) {
     dim3 grid((unsigned)H, nchunks, (unsigned)B);
     la_rope_state_tc_kernel<D><<<grid, LR_THREADS, LrSizes<D>::state_tc, st>>>(
-        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ld, cos_t, sin_t, partial, (int)N,
-        (int)H, Lc, nchunks);
+        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), (int)ld, cos_t, sin_t, partial,
+        (int)N, (int)H, Lc, nchunks);
   } else {
     dim3 grid(nchunks, (unsigned)H, (unsigned)B);
     la_rope_state_f32_kernel<D><<<grid, LR_THREADS, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(v),
@@ -679,8 +679,8 @@ static int lr_apply(const void* q, int64_t ldq, const float* cos_t, const float*
     la_chunking(B * H, N, per_sm * sm_count(), D / 2, &Lc, &nchunks);
     dim3 grid((unsigned)H, nchunks, (unsigned)B);
     la_rope_apply_tc_kernel<D><<<grid, LR_THREADS, LrSizes<D>::apply_tc, st>>>(
-        static_cast<const __nv_bfloat16*>(q), ldq, cos_t, sin_t, state, static_cast<__nv_bfloat16*>(out), ldo, (int)N,
-        (int)H, Lc, eps);
+        static_cast<const __nv_bfloat16*>(q), (int)ldq, cos_t, sin_t, state, static_cast<__nv_bfloat16*>(out), (int)ldo,
+        (int)N, (int)H, Lc, eps);
   } else {
     la_chunking(B * H, N, (int64_t)sm_count() * 2, D / 2, &Lc, &nchunks);
     dim3 grid(nchunks, (unsigned)H, (unsigned)B);
@@ -742,7 +742,7 @@ extern "C" int sana_la_rope_state(const void* k, const void* v, int64_t ld, cons
   SANA_REQUIRE(lr_head_dim_ok(D), "sana_la_rope_state: head dimension must be a multiple of 16 in [16, 128]");
   SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536, "sana_la_rope_state: size out of range");
   SANA_REQUIRE(dtype == SANA_BF16 || dtype == SANA_F32, "sana_la_rope_state: unsupported dtype");
-  SANA_REQUIRE(ld >= H * D && ld % 8 == 0, "sana_la_rope_state: ld must be >= H*D and a multiple of 8");
+  SANA_REQUIRE(ld >= H * D && ld % 8 == 0 && ld < (1LL << 31), "sana_la_rope_state: ld must be >= H*D, a multiple of 8 and below 2^31");
   SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(cos_table) && aligned16(sin_table) && aligned16(state) &&
                    aligned16(workspace),
                "sana_la_rope_state: pointers must be 16-byte aligned");
@@ -763,8 +763,8 @@ extern "C" int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_t
   SANA_REQUIRE(lr_head_dim_ok(D), "sana_la_rope_apply: head dimension must be a multiple of 16 in [16, 128]");
   SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536, "sana_la_rope_apply: size out of range");
   SANA_REQUIRE(dtype == SANA_BF16 || dtype == SANA_F32, "sana_la_rope_apply: unsupported dtype");
-  SANA_REQUIRE(ldq >= H * D && ldq % 8 == 0 && ldo >= H * D && ldo % 8 == 0,
-               "sana_la_rope_apply: row strides must be >= H*D and multiples of 8");
+  SANA_REQUIRE(ldq >= H * D && ldq % 8 == 0 && ldo >= H * D && ldo % 8 == 0 && ldq < (1LL << 31) && ldo < (1LL << 31),
+               "sana_la_rope_apply: row strides must be >= H*D, multiples of 8 and below 2^31");
   SANA_REQUIRE(aligned16(q) && aligned16(cos_table) && aligned16(sin_table) && aligned16(state) && aligned16(out),
                "sana_la_rope_apply: pointers must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
