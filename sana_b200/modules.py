@@ -220,6 +220,7 @@ class LiteLAReLURope(nn.Module):
             self.k_norm = nn.Identity()
         self.qkv_store_buffer = None
         self.nvfp4 = False
+        self.seq_shard: Optional[SequenceShard] = None
         self._tables = None  # (key, cos, sin)
 
     def rotary_tables(self, rotary_emb, N: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -245,8 +246,20 @@ class LiteLAReLURope(nn.Module):
         if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
             ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
             ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
-        cos, sin = self.rotary_tables(rotary_emb, N, qkv.device)
+        sh = self.seq_shard
+        if sh is None:
+            cos, sin = self.rotary_tables(rotary_emb, N, qkv.device)
+        else:
+            # this rank holds tokens [a, b) of every sample; ``rotary_emb`` covers the whole grid.  The state is
+            # a plain sum over tokens, so the ranks' partial states add.
+            a, b = sh.token_range
+            if b - a != N:
+                raise ValueError("the token count does not match this rank's share of the grid")
+            cos, sin = self.rotary_tables(rotary_emb, sh.frames * sh.H * sh.W, qkv.device)
+            cos, sin = cos[a:b].contiguous(), sin[a:b].contiguous()
         state = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, N, self.heads, self.dim)
+        if sh is not None:
+            sh.allreduce_state(state)
         return ops.la_rope_apply(qkv[:, :C], cos, sin, state, B, N, self.heads, self.dim, float(self.eps))
 
     def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_mask=None, **kwargs):
@@ -600,6 +613,15 @@ class SanaVideoMSBlock(nn.Module):
         self.drop_path = nn.Identity()
         self.scale_shift_table = nn.Parameter(torch.randn(6, hidden_size) / hidden_size ** 0.5)
         self.block_hook = None
+
+    def set_sequence_shard(self, shard: Optional[SequenceShard]) -> None:
+        """Run this block on one rank's slice of the token grid (see sharding.SequenceShard): the partial
+        attention states are summed over the ranks, the depthwise conv takes its halo rows from the
+        neighbours.  The temporal Mix-FFN is not covered on shards (frames would have to be exchanged)."""
+        if shard is not None and isinstance(self.mlp, GLUMBConvTemp):
+            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
+        self.attn.seq_shard = shard
+        self.mlp.seq_shard = shard
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, THW=None, rotary_emb=None, chunk_index=None, **kwargs):

@@ -206,3 +206,37 @@ def test_video_block_with_spatial_ffn_and_plain_linear_attention():
     with torch.no_grad():
         out2 = blk2(x.to(DEV), y.to(DEV), t.to(DEV), THW=THW, rotary_emb=fr)
     assert nmax_err(out2, ref2) < 1e-5
+
+
+def test_rotated_attention_on_sequence_shards_emulated_on_one_gpu():
+    """A (frames x rows) grid cut into contiguous row ranges: per-shard states with the shard's slice of
+    the rotation tables add up to the full state, and the per-shard outputs concatenate to the full
+    output.  The module on a one-rank shard equals the unsharded module."""
+    from sana_b200 import sharding
+    frames, H, W, heads, D = 3, 6, 8, 2, 48
+    C, N = heads * D, 3 * 6 * 8
+    qkv = _r(N, 3 * C, seed=7).bfloat16().to(DEV)
+    freqs = sana_b200.wan_rotary_freqs(D, (frames, H, W))
+    cos, sin = freqs[0, 0].real.float().to(DEV).contiguous(), freqs[0, 0].imag.float().to(DEV).contiguous()
+    full_state = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, 1, N, heads, D)
+    full_out = ops.la_rope_apply(qkv[:, :C], cos, sin, full_state, 1, N, heads, D, 1e-8)
+    for world in (2, 4):
+        shards = [sharding.SequenceShard(frames, H, W, r, world) for r in range(world)]
+        parts = []
+        for s in shards:
+            a, b = s.token_range
+            parts.append(ops.la_rope_state(qkv[a:b, C:2 * C], qkv[a:b, 2 * C:], cos[a:b].contiguous(), sin[a:b].contiguous(),
+                                           1, b - a, heads, D))
+        total = torch.stack(parts).sum(0)
+        assert nmax_err(total, full_state) < 1e-6
+        outs = [ops.la_rope_apply(qkv[s.token_range[0]:s.token_range[1], :C], cos[s.token_range[0]:s.token_range[1]].contiguous(),
+                                  sin[s.token_range[0]:s.token_range[1]].contiguous(), total, 1, s.tokens, heads, D, 1e-8)
+                for s in shards]
+        assert nmax_err(torch.cat(outs), full_out) < 1e-2
+    m = sana_b200.LiteLAReLURope(C, C, heads=heads, eps=1e-8).to(DEV, torch.bfloat16).eval()
+    x = _r(1, N, C, seed=8).bfloat16().to(DEV)
+    with torch.no_grad():
+        ref = m(x, rotary_emb=freqs)
+        m.seq_shard = sharding.SequenceShard(frames, H, W, 0, 1)
+        got = m(x, rotary_emb=freqs)
+    assert torch.equal(ref, got)
