@@ -152,3 +152,43 @@ def test_rank_failure_surfaces_as_error_not_hang():
     res = _run(2, _dies_before_collective, timeout_s=8, join_s=60)
     assert res[1][0] == "error" and "injected" in res[1][1]
     assert 0 in res and res[0][0] == "error", res
+
+
+def _seqpar_rotated_attention(rank, world):
+    """The video self-attention (ReLU, then rotation) on this rank's tokens: its slice of the rotation
+    table, its partial (D+1) x D state, one all-reduce, the apply on its own tokens."""
+    from oracle import sana_oracle as O
+    from sana_b200 import sharding
+
+    torch.set_num_threads(2)
+    C, heads, frames, H, W = 96, 2, 3, 5, 4
+    d, N = C // heads, 3 * 5 * 4
+    g = torch.Generator().manual_seed(3)
+    p = {"qkv.weight": torch.randn(3 * C, C, generator=g, dtype=torch.float64) * 0.1,
+         "proj.weight": torch.randn(C, C, generator=g, dtype=torch.float64) * 0.1,
+         "proj.bias": torch.randn(C, generator=g, dtype=torch.float64) * 0.1}
+    x = torch.randn(1, N, C, generator=g, dtype=torch.float64)
+    freqs = O.wan_rotary_freqs(d, (frames, H, W))
+    full = O.lite_la_relu_rope_forward(x, p, heads, freqs, eps=O.BLOCK_LA_EPS)
+    sh = sharding.SequenceShard(frames, H, W, rank, world)
+    a, b = sh.token_range
+    xs = sh.scatter_tokens(x)
+    q, k, v = torch.nn.functional.linear(xs, p["qkv.weight"]).reshape(1, sh.tokens, 3, heads, d).unbind(2)
+    q, k = q.relu(), k.relu()
+    fr = freqs[0, 0, a:b][None, :, None, :]
+    rot = lambda t: torch.view_as_real(torch.view_as_complex(t.unflatten(-1, (-1, 2)).contiguous()) * fr).flatten(-2)
+    state = O.lite_la_rope_state(k, rot(k), v)
+    sh.allreduce_state(state)
+    o = O.lite_la_rope_apply(q, rot(q), state, O.BLOCK_LA_EPS).reshape(1, sh.tokens, C)
+    out = torch.nn.functional.linear(o, p["proj.weight"], p["proj.bias"])
+    ref = full[:, a:b]
+    return ((out - ref).abs().max() / ref.abs().max()).item()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_rotated_attention_matches_single_process(world):
+    res = _run(world, _seqpar_rotated_attention)
+    assert len(res) == world, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        assert payload < 1e-12, payload
