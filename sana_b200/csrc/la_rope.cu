@@ -351,19 +351,18 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
     qr[r] = make_uint4(0u, 0u, 0u, 0u);
     cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  auto fetch = [&](int n0) {
-    if (n0 + LR_TOK <= n_end) {  // whole sub-tile (uniform): no per-row tests, nothing to clear
-      if (loader) {
+  auto fetch_whole = [&](int n0) {  // all 32 tokens lie inside the chunk: no per-row tests, nothing to clear
+    if (loader) {
 #pragma unroll
-        for (int r = 0; r < LR_TOK / 16; ++r) {
-          const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
-          qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
-          cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
-          sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
-        }
+      for (int r = 0; r < LR_TOK / 16; ++r) {
+        const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
+        qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
+        cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
+        sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
       }
-      return;
     }
+  };
+  auto fetch = [&](int n0) {  // zeros past the end of the chunk
 #pragma unroll
     for (int r = 0; r < LR_TOK / 16; ++r) {
       const int tok = n0 + 16 * r + slot;
@@ -403,9 +402,7 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
   int tile = 0;
   for (int m0 = n_begin; m0 < n_end; m0 += LR_MTOK, ++tile) {
     if (tile > 0) __syncthreads();  // everybody has stored the previous tile's results out of the token tile
-#pragma unroll 1
-    for (int ss = 0; ss < SUBS; ++ss) {
-      const int n0 = m0 + ss * LR_TOK;
+    auto convert = [&](int ss) {  // the 32 tokens waiting in registers -> rows 32 ss .. of the token tile
 #pragma unroll
       for (int r = 0; r < LR_TOK / 16; ++r) {
         const int trow = ss * LR_TOK + 16 * r + slot;
@@ -425,7 +422,19 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
         if (loader)
           *reinterpret_cast<uint4*>(Qs + (grp >> 3) * T::Q_BLK + trow * 128 + (((grp & 7) ^ (trow & 7)) << 4)) = rot;
       }
-      fetch(n0 + LR_TOK);  // zeros past the end of the chunk
+    };
+    if (m0 + LR_MTOK + LR_TOK <= n_end) {  // this tile and the sub-tile after it lie inside the chunk (uniform)
+#pragma unroll
+      for (int ss = 0; ss < SUBS; ++ss) {
+        convert(ss);
+        fetch_whole(m0 + (ss + 1) * LR_TOK);
+      }
+    } else {
+#pragma unroll 1
+      for (int ss = 0; ss < SUBS; ++ss) {
+        convert(ss);
+        fetch(m0 + (ss + 1) * LR_TOK);
+      }
     }
     fence_proxy_async_smem();  // this thread's stores, before the tensor core reads them
     __syncthreads();
