@@ -72,3 +72,25 @@ def test_video_block_state_dict_keys_and_guards():
                                    additional_flash_attn="flash")
     with pytest.raises(NotImplementedError):
         sana_b200.LiteLAReLURope(80, 80, heads=2)  # heads of 40 channels
+
+
+def test_video_block_refuses_uncovered_call_options():
+    import pytest
+    import torch
+    import sana_b200
+    blk = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp",
+                                     linear_head_dim=48)
+    x, y, t = torch.zeros(1, 24, 96), torch.zeros(1, 3, 96), torch.zeros(1, 6 * 96)
+    with pytest.raises(NotImplementedError):
+        blk(x, y, t, THW=(2, 3, 4), chunk_index=[0, 1])
+    with pytest.raises(NotImplementedError):
+        blk(x, y, t, THW=(2, 3, 4), kv_cache=[None])
+    with pytest.raises(ValueError):
+        blk(x, y, torch.zeros(1, 1, 5, 6 * 96), THW=(2, 3, 4))  # 24 tokens are not 5 frames
+    with pytest.raises(NotImplementedError):
+        blk.set_sequence_shard(sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1))  # temporal Mix-FFN on a shard
+    plain = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="LiteLAReLURope", ffn_type="glumbconv",
+                                       linear_head_dim=48)
+    sh = sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1)
+    plain.set_sequence_shard(sh)
+    assert plain.attn.seq_shard is sh and plain.mlp.seq_shard is sh
