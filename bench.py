@@ -14,6 +14,9 @@ embedders, final layer, unpatchify), same unit.  "nvfp4": one block with FP4 pro
 
 "seqpar": one block on a 21x45x80 = 75 600-token grid, rows sharded over the N GPUs
 (linear-attention state all-reduce + one-row conv halos); value = tokens/s of the block.
+The default line carries the same measurement as the sub-record "seqpar" at every N (graph
+replay and eager launches, the NCCL exchanges beside the fused peer-memory ones, a per-kernel
+breakdown, and the error of this rank's rows against the unsharded block run on the same GPU).
 
 Timing: W >= 3 warm-up steps, then K steps between barrier + synchronize, CUDA events on the
 compute stream, max over ranks.  Every step reads > 3 GB of weights and activations (inputs
@@ -21,7 +24,9 @@ larger than the 126 MB L2), so no explicit L2 flush is needed.
 
 --impl reference times the CPU restatement of upstream's block (oracle/) on the host cores
 (upstream is pure PyTorch; its own modules cannot travel to a box without a checkout, the
-restatement is pinned bit-for-bit to them by the golden fixtures).
+restatement is pinned bit-for-bit to them by the golden fixtures).  Both arms also report
+"gpu_eager_baseline": the same restatement - plain torch ops, i.e. cuBLAS / cuDNN kernels - run
+on the GPU in bf16 on one block of 16 384 tokens, outside every timed region of the product.
 """
 from __future__ import annotations
 
@@ -46,10 +51,10 @@ GLOBAL_BATCH = 8
 SEQPAR_GRID = (21, 45, 80)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core GEMM, averaged over the seven
-# launches of one block at batch 1 (ncu capture summarised in
-# profiles/stack_1600m_16k_tokens_launch_shares.md: 1.958 GB / 7).  The bench's launches carry
+# launches of one block at batch 1 (one ncu capture: 1.958 GB / 7).  The bench's launches carry
 # `per-GPU batch` times the rows, and activations dominate the bytes, so the figure is scaled by
-# the per-GPU batch.
+# the per-GPU batch.  A profiler figure cannot be taken inside a timed run; "traffic_algorithmic"
+# next to it is computed from the shapes of the launches this run timed.
 NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 = 279.7e6
 
 
@@ -166,6 +171,10 @@ def run_reference(args) -> None:
         dt = time.perf_counter() - t0
     val = shp.tokens * args.steps / dt
     sample = f"1 block x {shp.tokens} tokens (64x64 grid) per step, fp32, CPU restatement of upstream's block"
+    gpu_eager = None
+    if torch.cuda.is_available():  # the practical bar, reported beside the CPU figure (not the arm's value)
+        torch.cuda.set_device(0)
+        gpu_eager = gpu_eager_block_tokens_per_s(torch.device("cuda", 0))
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -173,6 +182,7 @@ def run_reference(args) -> None:
         "config": {"workload": "cfg3: Sana-1.6B stack (20 blocks, hidden 2240, 16384 tokens, batch 8)", "sample": sample},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_eager_baseline": gpu_eager,
     }))
 
 
@@ -270,6 +280,200 @@ def run_kernel_rates(tokens_side: int, batch: int, iters: int = 20) -> None:
     print(json.dumps(out))
 
 
+def gpu_eager_block_tokens_per_s(dev, grid=GRID, iters: int = 5) -> dict:
+    """The practical bar: upstream's block as plain torch ops (the restatement in oracle/, which is
+    op for op upstream's eager forward) on the GPU in bf16 - cuBLAS GEMMs, cuDNN depthwise conv and
+    attention, separate elementwise kernels - on one block of grid[0] x grid[1] tokens at 1.6B width.
+    A baseline leg like the CPU one: run after, and outside, every timed region of the product."""
+    from oracle import sana_oracle as O
+    from sana_b200 import synthetic
+
+    dt = torch.bfloat16
+    tokens = grid[0] * grid[1]
+    params = synthetic.make_block_params_on_device(C, HID, 0, 0.02, dt, dev)
+    g = torch.Generator(device=dev).manual_seed(77)
+    x = torch.randn(1, tokens, C, generator=g, device=dev).to(dt)
+    y = torch.randn(1, TEXT, C, generator=g, device=dev).to(dt)
+    t = (torch.randn(1, 6 * C, generator=g, device=dev) * 0.1).to(dt)
+    with torch.no_grad():
+        for _ in range(3):
+            O.sana_ms_block_forward(x, y, t, params, HEADS, grid)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            O.sana_ms_block_forward(x, y, t, params, HEADS, grid)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"value": tokens / (ms * 1e-3), "unit": UNIT, "ms_per_block": ms, "dtype": "bf16",
+            "what": f"eager torch ops (cuBLAS / cuDNN) of upstream's SanaMSBlock, 1 block x {tokens} tokens at 1.6B width, "
+                    f"mean of {iters} runs, CUDA events"}
+
+
+class KernelTimer:
+    """Per-kernel-group device time of eager steps: while active, every operator wrapper of
+    sana_b200.ops (and the two NCCL exchanges of the sequence shard, and torch's attention call)
+    is bracketed by CUDA events on the current stream."""
+
+    GROUPS = {"gemm": "gemm", "gemm_nvfp4": "gemm", "ln_modulate": "ln_modulate", "la_state": "la_state (+exchange)",
+              "la_state_sp": "la_state (+exchange)", "la_apply": "la_apply", "dwconv_glu": "dwconv_glu",
+              "cross_attention": "cross_attention_core", "nvfp4_quantize": "nvfp4_quantize", "rmsnorm_": "rmsnorm",
+              "halo_exchange": "conv_halo"}
+
+    def __init__(self):
+        self.events = []
+        self._saved = []
+
+    def _wrap(self, owner, name, label):
+        fn = getattr(owner, name)
+        events = self.events
+
+        def timed(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            events.append((label, e0, e1))
+            return r
+
+        self._saved.append((owner, name, fn))
+        setattr(owner, name, timed)
+
+    def __enter__(self):
+        import torch.nn.functional as F
+
+        from sana_b200 import ops, sharding
+
+        for name, label in self.GROUPS.items():
+            self._wrap(ops, name, label)
+        self._wrap(F, "scaled_dot_product_attention", "cross_attention_core")
+        self._wrap(sharding.SequenceShard, "allreduce_state", "nccl_allreduce")
+        return self
+
+    def __exit__(self, *a):
+        for owner, name, fn in reversed(self._saved):
+            setattr(owner, name, fn)
+        self._saved = []
+
+    def summary(self, steps: int) -> dict:
+        torch.cuda.synchronize()
+        out = {}
+        for label, e0, e1 in self.events:
+            ent = out.setdefault(label, {"launch_groups": 0, "ms_per_step": 0.0})
+            ent["launch_groups"] += 1
+            ent["ms_per_step"] += e0.elapsed_time(e1)
+        for ent in out.values():
+            ent["launch_groups"] //= max(steps, 1)
+            ent["ms_per_step"] /= max(steps, 1)
+        return out
+
+
+def seqpar_record(world: int, rank: int, dev, steps: int = 20, warmup: int = 3) -> dict:
+    """cfg 4 on this job's GPUs: one SanaMSBlock at 1.6B width on the 21x45x80 = 75 600-token grid,
+    the 945 image rows sharded over the ranks; the linear-attention state all-reduce and the conv halo
+    rows go through the fused peer-memory kernels.  Timed as CUDA-graph replay and as eager launches
+    (max over ranks), then with NCCL doing both exchanges, then once more with events around every
+    operator.  This rank's output rows are compared with the unsharded block run on the same GPU."""
+    import torch.distributed as dist
+
+    import sana_b200
+    from sana_b200 import ops, sharding, synthetic
+    from sana_b200.graphs import GraphedForward
+
+    dt = torch.bfloat16
+    total = SEQPAR_GRID[0] * SEQPAR_GRID[1] * SEQPAR_GRID[2]
+    blk = sana_b200.SanaMSBlock(C, HEADS, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval().to(dev, dt)
+    blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, 0, 0.02, dt, dev), strict=True)
+    g = torch.Generator(device=dev).manual_seed(4321)  # the same full sequence on every rank
+    x_full = torch.randn(1, total, C, generator=g, device=dev).to(dt)
+    y = torch.randn(1, TEXT, C, generator=g, device=dev).to(dt)
+    t = (torch.randn(1, 6 * C, generator=g, device=dev) * 0.1).to(dt)
+    full = blk(x_full, y, t, None, SEQPAR_GRID)  # unsharded, on this GPU, outside any timed region
+    shard = sharding.SequenceShard(*SEQPAR_GRID, rank, world, device_steps=True)
+    blk.set_sequence_shard(shard)
+    a, b = shard.token_range
+    xs = shard.scatter_tokens(x_full)
+    fused = world > 1
+    if fused:
+        shard.enable_fused_state_exchange(1, C // 32, dev)
+        shard.enable_fused_halo_exchange(SEQPAR_GRID[2] * 2 * HID, dt, dev)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        for _ in range(warmup):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        sync_all()
+        return ms.item()
+
+    eager = lambda: blk(xs, y, t, None, SEQPAR_GRID)  # noqa: E731
+    out = eager()
+    err = ((out.float() - full[:, a:b].float()).abs().max() / full.float().abs().max()).item()
+    eager_ms = timed(eager, steps)
+    sync_all()
+    graphed = GraphedForward(lambda v: blk(v, y, t, None, SEQPAR_GRID), xs)
+    sync_all()
+    graph_ms = timed(lambda: graphed(xs), steps)
+    gerr = ((graphed(xs).float() - full[:, a:b].float()).abs().max() / full.float().abs().max()).item()
+    nccl_ms = None
+    if fused:  # the same block with NCCL all-reduce + send/recv instead of the peer-memory kernels
+        saved = shard._sp_ptrs, shard._halo_ptrs
+        shard._sp_ptrs = shard._halo_ptrs = None
+        nccl_ms = timed(eager, max(steps // 2, 5))
+        shard._sp_ptrs, shard._halo_ptrs = saved
+    sync_all()
+    bsteps = 5
+    with KernelTimer() as kt:
+        for _ in range(bsteps):
+            eager()
+        breakdown = kt.summary(bsteps)
+    state_status = shard.fused_exchange_status() if fused else 0
+    halo_status = shard.fused_halo_status() if fused else 0
+    gemm_status = ops.take_gemm_device_status()
+    sync_all()
+    stats = torch.tensor([err, gerr, float(state_status), float(halo_status)], device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    stats = stats.tolist()
+    top = max(breakdown.items(), key=lambda kv: kv[1]["ms_per_step"])
+    comm = {k: v["ms_per_step"] for k, v in breakdown.items() if k in ("la_state (+exchange)", "conv_halo")}
+    peaks = load_peaks()
+    roof_s = block_roofline_seconds(shard.tokens, 1, peaks, C)
+    del graphed, full, x_full
+    torch.cuda.empty_cache()
+    return {
+        "workload": f"cfg4: one SanaMSBlock, hidden {C}, 21x45x80 = {total} tokens, 945 image rows sharded over {world} GPU(s)",
+        "tokens_per_s": total / (graph_ms * 1e-3), "ms_per_step": graph_ms, "mode": "CUDA-graph replay of the sharded block",
+        "eager_tokens_per_s": total / (eager_ms * 1e-3), "eager_ms_per_step": eager_ms,
+        "nccl_exchange_tokens_per_s": (total / (nccl_ms * 1e-3)) if nccl_ms else None, "nccl_exchange_ms_per_step": nccl_ms,
+        "exchange": ("state all-reduce fused into the reduction kernel + conv halo rows pushed by one kernel, both over "
+                     "peer memory (plain loads / stores, no multicast)") if fused else "none (one GPU)",
+        "steps": steps, "warmup": warmup, "rows_per_rank": [r1 - r0 for r0, r1 in shard.ranges],
+        "parity_nmax_err": stats[0], "parity_nmax_err_graph": stats[1],
+        "parity_against": "the unsharded block on the same GPU, this rank's rows, max over ranks",
+        "state_exchange_status": int(stats[2]), "halo_exchange_status": int(stats[3]), "gemm_device_status": gemm_status,
+        "kernel_breakdown_rank0_eager": breakdown,
+        "largest_kernel_group": {"name": top[0], "ms_per_step": top[1]["ms_per_step"]},
+        "exchange_kernels_ms_per_step": comm,
+        "block_roofline": {"t_roof_ms": roof_s * 1e3, "frac": roof_s * 1e3 / graph_ms},
+    }
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel-rates", type=int, default=0, metavar="SIDE",
@@ -292,6 +496,9 @@ def main() -> None:
                     help="use our own cross-attention softmax kernel instead of torch SDPA")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="seqpar: all-reduce the attention state with NCCL instead of the fused peer-memory kernel")
+    ap.add_argument("--no-seqpar", action="store_true",
+                    help="stack workload: leave out the sequence-parallel sub-record (cfg 4 on the same GPUs)")
+    ap.add_argument("--no-gpu-eager-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -514,6 +721,7 @@ def main() -> None:
     gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in ops.counters.gemm_events)
     gemm_flops = sum(f for _, _, f, _ in ops.counters.gemm_events)
     n_gemm = len(ops.counters.gemm_events)
+    gemm_bytes = sum(ops.counters.gemm_bytes)  # A + W + out (+ residual) of every timed launch, each once
     by_shape = {}
     for e0, e1, f, label in ops.counters.gemm_events:
         ent = by_shape.setdefault(label, [0, 0.0, 0.0])
@@ -530,6 +738,17 @@ def main() -> None:
     torch.cuda.synchronize()
     e2e_state["up"] = [None, None]  # the timed run starts cold: its first upload is not pre-issued
     e2e_ms = timed(step_e2e, args.steps, finish_e2e)
+
+    # one more eager step with events around every operator: the per-kernel shares of a step
+    with KernelTimer() as kt:
+        eager(x_d, y_d, t_d)
+        kernel_breakdown = kt.summary(1)
+    dw_status = ops.take_dwconv_glu_device_status()
+    sp_status = (shard.fused_exchange_status(), shard.fused_halo_status()) if fused_exchange else (0, 0)
+    seqpar = None
+    if args.workload == "stack" and not args.no_seqpar:
+        sync_all()
+        seqpar = seqpar_record(world, rank, dev)
 
     if rank == 0:
         ms_per_step = total_ms / args.steps
@@ -555,19 +774,39 @@ def main() -> None:
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
-                         "share_of_step": gemm_ms / (eager_ms or total_ms), "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 * Bl) if args.workload == "stack" else None},
+                         "share_of_step": gemm_ms / (eager_ms or total_ms),
+                         "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH_BATCH1 * Bl) if args.workload == "stack" else None,
+                         "traffic_source": "one ncu capture at batch 1 (1.958 GB over the 7 launches of a block), scaled by the per-GPU batch",
+                         "traffic_algorithmic": gemm_bytes / max(n_gemm, 1)},
             "cuda_graph": bool(args.graph), "eager_ms_per_step": (eager_ms / args.steps) if eager_ms else None,
             "block_roofline": {"t_roof_ms_per_step": roof_s * 1e3, "frac": roof_s * 1e3 / ms_per_step,
                                "formula": "F_gemm/P_tensor + 11.5*T*C*e/BW_hbm, per block"},
             "e2e": {"value": total_units / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_h.nbytes + y_h.nbytes + t_h.nbytes, "d2h_bytes_per_step": out_h.nbytes,
                     "ms_per_step": e2e_ms / args.steps},
-            "gemm_breakdown": gemm_breakdown, "gpu_launches": launches, "gemm_device_status": status, "clocks": clk.summary(),
+            "gemm_breakdown": gemm_breakdown, "kernel_breakdown_ms_per_step": kernel_breakdown, "gpu_launches": launches,
+            "gemm_device_status": status, "dwconv_device_status": dw_status,
+            "state_exchange_status": sp_status[0], "halo_exchange_status": sp_status[1], "clocks": clk.summary(),
         }
+        if seqpar is not None:
+            out["seqpar"] = seqpar
+        if world == 1 and not args.no_gpu_eager_baseline:
+            out["gpu_eager_baseline"] = gpu_eager_block_tokens_per_s(dev)
         if world == 1 and not args.no_cpu_baseline:
             v, cores, sample = cpu_block_tokens_per_s()
             out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        bad = {k: out[k] for k in ("gemm_device_status", "dwconv_device_status", "state_exchange_status",
+                                   "halo_exchange_status") if out[k]}
+        if seqpar is not None:
+            bad.update({"seqpar." + k: seqpar[k] for k in ("state_exchange_status", "halo_exchange_status",
+                                                           "gemm_device_status") if seqpar[k]})
+        if bad:
+            out["failed"] = f"a bounded device wait ran out, the results above are not valid: {bad}"
         print(json.dumps(out))
+        if bad:
+            if world > 1:
+                dist.destroy_process_group()
+            sys.exit(1)
     if world > 1:
         dist.destroy_process_group()
 

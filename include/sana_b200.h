@@ -133,8 +133,9 @@ int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, float* state
  *     mapped into this process (peer / symmetric memory), each sana_la_state_sp_buffer_bytes
  *     (B, H) bytes, zero-filled once before the first step.  Layout: 256 B of arrival flags,
  *     a block counter at byte 256, a soft-error word at byte 320 (non-zero = 1 + the rank that
- *     did not arrive within 2 s; the result of that step must be discarded), two state slots
- *     from byte 1024.
+ *     did not arrive within the wait limit - 2 s unless changed with
+ *     sana_exchange_set_wait_limit_ns; the result of that step must be discarded), two state
+ *     slots from byte 1024.
  *   step: 1, 2, 3, ... the same sequence on every rank, one per call on this buffer set; or 0
  *     on every call of every rank: the kernel numbers the steps itself (a word in the buffer),
  *     which lets the launch be captured in a CUDA graph and replayed.
@@ -150,8 +151,9 @@ int sana_la_state_sp(const void* k, const void* v, int64_t ld, float* state, voi
  * Conv halo rows of a row-sharded token grid over peer memory: this rank's first row of the
  * depthwise conv's input goes into the upper neighbour's `bot` slot and its last row into the
  * lower neighbour's `top` slot (remote stores), a release-store of the step number tells the
- * neighbours, and the kernel returns once their rows have arrived here (bounded wait, 2 s;
- * soft-error word at byte 20 of the buffer: 1 = upper, 2 = lower neighbour missing).  No
+ * neighbours, and the kernel returns once their rows have arrived here (bounded wait per
+ * neighbour, 2 s unless changed with sana_exchange_set_wait_limit_ns; soft-error word at byte 20
+ * of the buffer: bit 0 = the upper, bit 1 = the lower neighbour did not arrive).  No
  * counterpart upstream; replaces two NCCL send/recv pairs per block.
  *   first_row / last_row: [row_bytes] device rows (may be null when that neighbour is null).
  *   mine / upper / lower: exchange buffers of this rank and of ranks -1 / +1 as mapped into this
@@ -165,6 +167,12 @@ int sana_la_state_sp(const void* k, const void* v, int64_t ld, float* state, voi
 int64_t sana_halo_exchange_buffer_bytes(int64_t row_bytes);
 int sana_halo_exchange(const void* first_row, const void* last_row, int64_t row_bytes, void* mine, void* upper,
                        void* lower, uint32_t step, void* stream);
+
+/* Limit of the waits for a peer GPU inside sana_la_state_sp and sana_halo_exchange, in
+ * nanoseconds (process-wide, read at launch; 0 restores the default of 2 s).  A wait that runs
+ * out records its code in the buffer's soft-error word and the kernel returns; the step's result
+ * must then be discarded.  No counterpart upstream (NCCL's own watchdog plays this role there). */
+int sana_exchange_set_wait_limit_ns(int64_t ns);
 
 /* ---------------------------------------------------------------------------------------
  * ReLU linear attention, apply + normalise:

@@ -505,8 +505,8 @@ def depthwise_glu_rows(u_rows, halo_top, halo_bot, wd, bd, row0: int, H: int) ->
     (ignored when that row lies in another frame, where upstream zero-pads).  Same math as
     basic_modules.py:164-167 applied per frame."""
     R, W, C2 = u_rows.shape
-    out = torch.empty(R, W, C2 // 2, dtype=u_rows.dtype)
-    zero = torch.zeros(W, C2, dtype=u_rows.dtype)
+    out = torch.empty(R, W, C2 // 2, dtype=u_rows.dtype, device=u_rows.device)
+    zero = torch.zeros(W, C2, dtype=u_rows.dtype, device=u_rows.device)
     for r in range(R):
         g = row0 + r
         fr = g % H
@@ -516,6 +516,50 @@ def depthwise_glu_rows(u_rows, halo_top, halo_bot, wd, bd, row0: int, H: int) ->
         w = F.conv2d(F.pad(tile, (1, 1, 0, 0)), wd, bd, groups=C2)  # [1, C2, 1, W]
         a, gt = torch.chunk(w[0, :, 0], 2, dim=0)
         out[r] = (a * F.silu(gt)).permute(1, 0)
+    return out
+
+
+def sana_ms_block_rows(x, y, t, p: Params, num_heads: int, HW: Sequence[int], rows: Sequence[int], mask=None,
+                       linear_head_dim: int = 32) -> Dict[int, torch.Tensor]:
+    """Rows of :func:`sana_ms_block_forward`'s output for one sample, without evaluating the whole
+    block: ``rows`` are global image rows (frame * H + row) of the (T, H, W) or (H, W) grid and the
+    result maps each to its [W, C] output.  Only the linear-attention state needs every token (k and v
+    of the whole sequence); everything after it is local to a token, except the 3x3 depthwise conv,
+    which reads the rows above and below inside the same frame.  Same operations in the same order as
+    the full function (sana_multi_scale.py:145-157), so in fp64 the two agree to rounding; it exists
+    so that a 75 600-token block can be checked on sampled rows in seconds of CPU time."""
+    B, N, C = x.shape
+    assert B == 1
+    H, W = HW[-2], HW[-1]
+    heads = C // linear_head_dim
+    mod = (p["scale_shift_table"][None] + t.reshape(B, 6, -1)).chunk(6, dim=1)
+    shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = mod
+    pa, pm = sub(p, "attn"), sub(p, "mlp")
+    z = t2i_modulate(layer_norm(x), shift_msa, scale_msa)
+    wqkv = pa["qkv.weight"]
+    kv = F.linear(z, wqkv[C:])
+    k = F.relu(kv[..., :C]).reshape(B, N, heads, linear_head_dim)
+    v = kv[..., C:].reshape(B, N, heads, linear_head_dim)
+    state = lite_la_state(k, v)
+    w1 = pm["inverted_conv.conv.weight"]
+    w3 = pm["point_conv.conv.weight"]
+    wd, bd = pm["depth_conv.conv.weight"], pm.get("depth_conv.conv.bias")
+    out = {}
+    for r in rows:
+        fr = r % H
+        need = [g for g in (r - 1, r, r + 1) if 0 <= fr + (g - r) < H]
+        tok = torch.cat([torch.arange(g * W, (g + 1) * W) for g in need])
+        q = F.relu(F.linear(z[:, tok], wqkv[:C])).reshape(B, -1, heads, linear_head_dim)
+        o = lite_la_apply(q, state, BLOCK_LA_EPS).reshape(B, -1, C)
+        x1 = x[:, tok] + gate_msa * F.linear(o, pa["proj.weight"], pa["proj.bias"])
+        x2 = x1 + cross_attention_forward(x1, y, sub(p, "cross_attn"), num_heads, mask)
+        z2 = t2i_modulate(layer_norm(x2), shift_mlp, scale_mlp)
+        u = F.silu(F.linear(z2, w1.reshape(w1.shape[0], C), pm.get("inverted_conv.conv.bias")))
+        u = {g: u[0, i * W:(i + 1) * W] for i, g in enumerate(need)}
+        gl = depthwise_glu_rows(u[r][None], u.get(r - 1), u.get(r + 1), wd, bd, r, H)[0]  # [W, hid]
+        f = F.linear(gl, w3.reshape(w3.shape[0], -1), pm.get("point_conv.conv.bias"))
+        i0 = need.index(r) * W
+        out[r] = x2[0, i0:i0 + W] + gate_mlp[0] * f
     return out
 
 

@@ -55,6 +55,7 @@ SIGNATURES = {
                                 C.c_uint32, _vp]),
     "sana_halo_exchange_buffer_bytes": (_i64, [_i64]),
     "sana_halo_exchange": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, C.c_uint32, _vp]),
+    "sana_exchange_set_wait_limit_ns": (_i32, [_i64]),
     "sana_la_apply": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_la_rope_state_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "sana_la_rope_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

@@ -28,7 +28,16 @@ int sm_count() {
   return cached[dev];
 }
 
+static long long g_exchange_wait_ns = 2000000000LL;
+long long exchange_wait_limit_ns() { return g_exchange_wait_ns; }
+
 }  // namespace sana
+
+extern "C" int sana_exchange_set_wait_limit_ns(int64_t ns) {
+  if (ns < 0) return sana::fail(SANA_ERR_INVALID, "sana_exchange_set_wait_limit_ns: negative limit");
+  sana::g_exchange_wait_ns = ns == 0 ? 2000000000LL : (long long)ns;
+  return SANA_OK;
+}
 
 extern "C" int sana_abi_version(void) { return 1; }
 extern "C" const char* sana_last_error(void) { return sana::g_err; }

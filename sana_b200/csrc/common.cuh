@@ -33,6 +33,10 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int sm_count();  // SMs of the current device (cached per device)
 
+// Limit, in nanoseconds, of the waits for a peer GPU inside the sequence-parallel exchange
+// kernels (process-wide; set by sana_exchange_set_wait_limit_ns, 2 s unless changed).
+long long exchange_wait_limit_ns();
+
 // One flag per device for set-up that must happen once on every device the process uses
 // (function attributes live in a device's context).  A lost race repeats harmless work.
 struct OncePerDevice {

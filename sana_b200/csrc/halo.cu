@@ -7,7 +7,7 @@
 //   [0, 4)    last step whose row the UPPER neighbour (rank - 1) has delivered into `top`
 //   [4, 8)    last step whose row the LOWER neighbour (rank + 1) has delivered into `bot`
 //   [8, 12)   block counter   [12, 16) exit counter   [16, 20) last completed step
-//   [20, 24)  soft-error word (1 = the upper, 2 = the lower neighbour did not arrive in time)
+//   [20, 24)  soft-error word (bit 0 = the upper, bit 1 = the lower neighbour did not arrive in time)
 //   [1024, 1024 + row_bytes)                  `top`: the row above this rank's first row
 //   [1024 + row_bytes, 1024 + 2 * row_bytes)  `bot`: the row below its last row
 // One slot per side is enough: a neighbour writes step s+1's row only after its next
@@ -19,7 +19,6 @@
 namespace sana {
 
 constexpr int64_t HALO_HEADER_BYTES = 1024;
-constexpr long long HALO_WAIT_LIMIT_NS = 2000000000LL;  // 2 s
 
 struct HaloArgs {
   const uint4* first_row;  // this rank's first row (goes to the upper neighbour's `bot`), or null
@@ -29,6 +28,7 @@ struct HaloArgs {
   unsigned char* lower;    // rank + 1's buffer, or null
   int64_t row_vecs;        // 16-byte vectors per row
   uint32_t step;           // 0 = numbered by the kernel
+  long long wait_limit_ns; // how long the waiting block waits for each neighbour
 };
 
 __device__ __forceinline__ uint32_t halo_ld_acquire(const uint32_t* p) {
@@ -70,12 +70,13 @@ __global__ void __launch_bounds__(256) halo_exchange_kernel(const HaloArgs a) {
       if (a.upper) halo_st_release(reinterpret_cast<uint32_t*>(a.upper) + 1, step);  // I am its lower neighbour
       if (a.lower) halo_st_release(reinterpret_cast<uint32_t*>(a.lower) + 0, step);  // I am its upper neighbour
       // ---- wait for the neighbours' rows (their flags arrive in my own memory)
-      const long long t0 = halo_ns();
+      // each side has its own clock, and the soft-error word collects one bit per side
       for (int side = 0; side < 2; ++side) {
         if (!(side == 0 ? a.upper : a.lower)) continue;
+        const long long t0 = halo_ns();
         while ((int32_t)(halo_ld_acquire(hdr + side) - step) < 0) {
-          if (halo_ns() - t0 > HALO_WAIT_LIMIT_NS) {
-            atomicExch(reinterpret_cast<int*>(hdr + 5), 1 + side);
+          if (halo_ns() - t0 > a.wait_limit_ns) {
+            atomicOr(reinterpret_cast<int*>(hdr + 5), 1 << side);
             break;
           }
         }
@@ -114,6 +115,7 @@ extern "C" int sana_halo_exchange(const void* first_row, const void* last_row, i
   a.lower = static_cast<unsigned char*>(lower);
   a.row_vecs = row_bytes / 16;
   a.step = step;
+  a.wait_limit_ns = exchange_wait_limit_ns();
   int64_t blocks = ceil_div(a.row_vecs, 256 * 4);
   if (blocks > 64) blocks = 64;  // all resident at once: the last block to finish its copy waits for the peers
   if (blocks < 1) blocks = 1;

@@ -518,13 +518,13 @@ namespace sana {
 
 constexpr int SP_MAX_WORLD = 16;
 constexpr int64_t SP_HEADER_BYTES = 1024;
-constexpr long long SP_WAIT_LIMIT_NS = 2000000000LL;  // 2 s
 
 struct SpPeers {
   unsigned char* base[SP_MAX_WORLD];
   int rank, world;
   uint32_t step;
   int64_t slot_elems;
+  long long wait_limit_ns;  // how long a block waits for the peers before it gives up
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -583,7 +583,7 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
       if (r == pg.rank) continue;
       const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine) + r;
       while ((int32_t)(ld_acquire_sys_u32(flag) - step) < 0) {
-        if (global_ns() - t0 > SP_WAIT_LIMIT_NS) {
+        if (global_ns() - t0 > pg.wait_limit_ns) {
           wait_failed = 1;
           atomicExch(reinterpret_cast<int*>(mine + 320), 1 + r);  // which peer we gave up on
           break;
@@ -636,6 +636,7 @@ extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float*
   }
   pg.rank = rank, pg.world = world, pg.step = step;
   pg.slot_elems = B * H * SSIZE;
+  pg.wait_limit_ns = exchange_wait_limit_ns();
   int Lc, nchunks;
   la_state_plan(B, N, H, dtype, &Lc, &nchunks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -424,6 +424,11 @@ class GLUMBConvTemp(GLUMBConv):
         B, N, C = z.shape
         T, H, W = HW
         hw = H * W
+        if N != T * hw or rows_per_vec not in (N, hw):
+            # the taps of the previous / next frame take their gates by shifting t2 one vector, which is
+            # only right when a vector covers a whole sample or exactly one frame
+            raise ValueError(f"GLUMBConvTemp: modulation runs of {rows_per_vec} tokens fit neither a sample ({N}) "
+                             f"nor a frame ({hw}) of the {tuple(HW)} grid")
         s = _as2d(GLUMBConv.forward(self, z, HW=HW))
         vecs = (B * N) // rows_per_vec
         gate = (table[row].float()[None] + t2.reshape(vecs, 6, C)[:, row].float()).to(s.dtype)  # [vecs, C]
@@ -635,6 +640,9 @@ class SanaVideoMSBlock(nn.Module):
             if N % frames:
                 raise ValueError("the token count is not a multiple of the frame count of t")
             rows = N // frames
+            if isinstance(self.mlp, GLUMBConvTemp) and (THW is None or frames != THW[0]):
+                raise ValueError(f"t carries {frames} modulation vectors per sample but the grid has "
+                                 f"{None if THW is None else THW[0]} frames: the temporal Mix-FFN needs one per frame")
         else:
             rows = N
         t2 = t.reshape(B * (N // rows), 6 * C)

@@ -28,10 +28,12 @@ class _Counters:
         self.launches = 0
         self.gemm_timing = False
         self.gemm_events = []  # (start, end, flops, label)
+        self.gemm_bytes = []   # operand + result bytes of each timed launch, every element once
 
     def reset(self):
         self.launches = 0
         self.gemm_events = []
+        self.gemm_bytes = []
 
 
 counters = _Counters()
@@ -254,6 +256,11 @@ def halo_exchange(first_row: Optional[torch.Tensor], last_row: Optional[torch.Te
     counters.launches += 1
 
 
+def set_exchange_wait_limit(seconds: float) -> None:
+    """Limit of the waits for a peer GPU inside the fused exchange kernels (0 = the default, 2 s)."""
+    _lib.check(_lib.load().sana_exchange_set_wait_limit_ns(int(seconds * 1e9)), "sana_exchange_set_wait_limit_ns")
+
+
 def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """o[b,n,h,:] = state[b,h,:32] relu(q) / (state[b,h,32] . relu(q) + eps); q [B*N, H*32] view."""
@@ -452,6 +459,7 @@ def _gemm(fn_name: str, a: torch.Tensor, w: torch.Tensor, bias, act, relu_cols, 
     if timed:
         e1.record()
         counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K, f"bf16 {M}x{Nn}x{K}" + _epi_tag(bias, act, gate, residual)))
+        counters.gemm_bytes.append(2.0 * (M * K + Nn * K + M * Nn * (2 if residual is not None else 1)))
     counters.launches += 1
     return out
 
@@ -547,6 +555,7 @@ def gemm_nvfp4(a: NvFp4Tensor, w: NvFp4Tensor, bias=None, act: int = ACT_NONE, r
     if timed:
         e1.record()
         counters.gemm_events.append((e0, e1, 2.0 * M * Nn * K, f"nvfp4 {M}x{Nn}x{K}" + _epi_tag(bias, act, gate, residual)))
+        counters.gemm_bytes.append(0.5625 * (M * K + Nn * K) + 2.0 * M * Nn * (2 if residual is not None else 1))
     counters.launches += 1
     return out
 

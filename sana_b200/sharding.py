@@ -173,8 +173,27 @@ class SequenceShard:
         return getattr(self, "_halo_ptrs", None) is not None
 
     def fused_halo_status(self) -> int:
-        """Soft-error word of the halo kernel (0 = every wait completed).  Synchronises."""
+        """Soft-error word of the halo kernel (0 = every wait completed; bit 0 = the upper, bit 1 =
+        the lower neighbour did not arrive in time).  Synchronises."""
         return int(self._halo_buf[20:24].view(torch.int32).item())
+
+    def check(self) -> None:
+        """Raises :class:`PeerLostError` when a wait for a peer inside one of the fused exchange
+        kernels ran out since the buffers were set up (the kernel then carried on with this rank's
+        data only, so every result since is wrong).  Reads two words from the device, i.e.
+        synchronises: call it where the host waits for the device anyway (after a denoising step,
+        before results leave the GPU), not per block."""
+        state = self.fused_exchange_status() if self.fused_state_exchange else 0
+        halo = self.fused_halo_status() if self.fused_halo_exchange else 0
+        if state or halo:
+            who = []
+            if state:
+                who.append(f"rank {state - 1} did not publish its attention state")
+            if halo & 1:
+                who.append(f"rank {self.rank - 1} did not deliver its conv halo row")
+            if halo & 2:
+                who.append(f"rank {self.rank + 1} did not deliver its conv halo row")
+            raise PeerLostError(f"rank {self.rank}: " + "; ".join(who) + " within the exchange wait limit")
 
     # With `device_steps` the exchange kernels number their steps themselves (a word in the
     # exchange buffer) instead of taking the number as a launch argument: required for CUDA-graph

@@ -92,6 +92,34 @@ def _seqpar_vs_single(rank, world):
     return ((out.float() - ref).abs().max() / full.float().abs().max()).item()
 
 
+def _seqpar_full_size(rank, world):
+    """The sequence-parallel configuration at its stated size - hidden 2240, 21 x 45 x 80 = 75 600
+    tokens - with both exchanges over peer memory, against the unsharded block on the same GPU."""
+    import sana_b200
+    from sana_b200 import sharding, synthetic
+
+    dev, dt = torch.device("cuda", rank), torch.bfloat16
+    C, heads, hid, grid = 2240, 20, 5600, (21, 45, 80)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval().to(dev, dt)
+    blk.load_state_dict(synthetic.make_block_params_on_device(C, hid, 0, 0.02, dt, dev), strict=True)
+    g = torch.Generator(device=dev).manual_seed(11)
+    x = torch.randn(1, grid[0] * grid[1] * grid[2], C, generator=g, device=dev).to(dt)
+    y = torch.randn(1, 300, C, generator=g, device=dev).to(dt)
+    t = (torch.randn(1, 6 * C, generator=g, device=dev) * 0.1).to(dt)
+    full = blk(x, y, t, None, grid)
+    sh = sharding.SequenceShard(*grid, rank, world)
+    blk.set_sequence_shard(sh)
+    sh.enable_fused_state_exchange(1, C // 32, dev)
+    sh.enable_fused_halo_exchange(grid[2] * 2 * hid, dt, dev)
+    a, b = sh.token_range
+    worst = 0.0
+    for i in range(3):
+        out = blk(sh.scatter_tokens(x), y, t, None, grid)
+        worst = max(worst, ((out.float() - full[:, a:b].float()).abs().max() / full.float().abs().max()).item())
+    sh.check()  # raises if a wait for the peer ran out
+    return worst
+
+
 def _stack_batch_parallel(rank, world):
     import sana_b200
     from sana_b200 import sharding, synthetic
@@ -253,6 +281,15 @@ def test_sequence_parallel_block_on_two_gpus():
     for r, (status, payload) in res.items():
         assert status == "ok", payload
         assert payload < 1e-2, payload  # same kernels; only the state summation order differs
+
+
+def test_sequence_parallel_block_at_full_size_on_two_gpus():
+    _need(2)
+    res = _run(2, _seqpar_full_size)
+    assert len(res) == 2, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        assert payload < 1e-2, payload
 
 
 def test_batch_parallel_stack_on_two_gpus():

@@ -87,6 +87,8 @@ def test_video_block_refuses_uncovered_call_options():
         blk(x, y, t, THW=(2, 3, 4), kv_cache=[None])
     with pytest.raises(ValueError):
         blk(x, y, torch.zeros(1, 1, 5, 6 * 96), THW=(2, 3, 4))  # 24 tokens are not 5 frames
+    with pytest.raises(ValueError):
+        blk(x, y, torch.zeros(1, 1, 4, 6 * 96), THW=(2, 3, 4))  # 4 modulation vectors for a 2-frame grid
     with pytest.raises(NotImplementedError):
         blk.set_sequence_shard(sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1))  # temporal Mix-FFN on a shard
     plain = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="LiteLAReLURope", ffn_type="glumbconv",

@@ -10,13 +10,16 @@ This file is collected last on purpose: if it fails, a run that stops at the fir
 has already run every other test.  It calls the entry point through the C ABI directly, on
 two different problems in a row (the second must not see leftovers of the first), and
 compares with `sana_la_state` within the tolerance of the state tests (normalised max error
-<= 1e-5; both run the same kernels in the same order, so the results are in fact equal).
+<= 1e-5; both run the same kernels in the same order, so the results are in fact equal) and,
+independently of that entry point, with the CPU oracle's state evaluated in fp64 on the same
+values.
 """
 import ctypes as C
 
 import pytest
 import torch
 
+from oracle import sana_oracle as O
 from sana_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -48,6 +51,13 @@ def _both(lib, qkv, B, N, H):
     return out, ref
 
 
+def _oracle_state(qkv, B, N, H):
+    Cc = H * 32
+    k = torch.relu(qkv[:, Cc:2 * Cc].double().cpu()).reshape(B, N, H, 32)
+    v = qkv[:, 2 * Cc:].double().cpu().reshape(B, N, H, 32)
+    return O.lite_la_state(k, v)
+
+
 def test_noalloc_matches_workspace_entry_point_twice_in_a_row(lib):
     g = torch.Generator().manual_seed(0)
     # first call: large enough to use many chunks of the built-in scratch
@@ -55,12 +65,14 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(lib):
     qkv = torch.randn(B * N, 3 * H * 32, generator=g).bfloat16().cuda()
     out1, ref1 = _both(lib, qkv, B, N, H)
     assert torch.isfinite(out1).all() and _nmax(out1, ref1) <= TOL
+    assert _nmax(out1.cpu(), _oracle_state(qkv, B, N, H)) <= TOL
     # second call, different shape and dtype, smaller footprint: stale partials of the first
     # call are still in the scratch and must not leak into the result
     B, N, H = 1, 333, 5
     qkv = torch.randn(B * N, 3 * H * 32, generator=g).cuda()
     out2, ref2 = _both(lib, qkv, B, N, H)
     assert torch.isfinite(out2).all() and _nmax(out2, ref2) <= TOL
+    assert _nmax(out2.cpu(), _oracle_state(qkv, B, N, H)) <= TOL
     # and the first problem again gives the first answer again
     B, N, H = 2, 4096, 36
     qkv = torch.randn(B * N, 3 * H * 32, generator=torch.Generator().manual_seed(0)).bfloat16().cuda()
