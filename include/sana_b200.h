@@ -255,11 +255,22 @@ int sana_dwconv_glu_take_device_status(int* status_out);
  *   q   [B*N, *] row stride ldq, head h at columns h*head_dim ..   (token-major, no transposes)
  *   k,v [B*L, *] row stride ldkv (e.g. the two column blocks of the kv projection)
  *   mask [B, L] of 0/1 in the activation dtype, or NULL;  out [B*N, *] row stride ldo
- * head_dim a multiple of 8, at most 128.  bf16: warp-level tensor cores, fp32 online softmax.
+ * head_dim a multiple of 8, at most 128.  bf16 with 17 <= L <= 304 and head_dim >= 16: persistent
+ * tcgen05 kernel - both products on the 5th-generation tensor cores with the scores and the
+ * probabilities in tensor memory, fp32 softmax in the exp2 domain, K / V of a (sample, head)
+ * resident in shared memory; other bf16 shapes: warp-level tensor cores with an online softmax.
+ * fp32: plain FMA (parity path).
  */
 int sana_cross_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv,
                          const void* mask, void* out, int64_t ldo, int64_t B, int64_t N, int64_t L,
                          int64_t heads, int64_t head_dim, int dtype, void* stream);
+/* Kernel choice of the bf16 sana_cross_attention (process-wide; for tests and measurements):
+ * 0 = per problem (default), 1 = always the warp-level kernel, 2 = the tcgen05 kernel (shapes it
+ * does not cover are then refused). */
+int sana_cross_attention_set_variant(int variant);
+/* Soft-error word of the tcgen05 cross-attention kernel, whose waits are bounded: 0 when no wait
+ * has timed out on the current device since the last call (host-synchronising). */
+int sana_cross_attention_take_device_status(int* status_out);
 
 /* ---------------------------------------------------------------------------------------
  * Dense projection with fused epilogue:  out = epilogue(A @ Wt^T)

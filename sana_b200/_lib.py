@@ -61,6 +61,8 @@ SIGNATURES = {
     "sana_la_rope_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_la_rope_apply": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_cross_attention": (_i32, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sana_cross_attention_set_variant": (_i32, [_i32]),
+    "sana_cross_attention_take_device_status": (_i32, [C.POINTER(C.c_int)]),
     "sana_dwconv_glu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_gemm": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),
     "sana_gemm_simt": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _i32, _vp]),

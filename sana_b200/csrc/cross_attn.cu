@@ -265,9 +265,28 @@ static int launch_ca_bf16(const void* q, int64_t ldq, const void* k, const void*
   return SANA_OK;
 }
 
+// tensor-core kernel (cross_attn_tc.cu)
+bool cross_attn_tc_supported(int64_t L, int64_t hd);
+int cross_attn_tc_launch(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv, const void* mask,
+                         void* out, int64_t ldo, int64_t B, int64_t N, int64_t L, int heads, int hd, cudaStream_t st);
+int cross_attn_tc_take_status(int* v);
+
+static int g_ca_variant = 0;  // 0 = per problem, 1 = warp-level kernel, 2 = tcgen05 kernel
+
 }  // namespace sana
 
 using namespace sana;
+
+extern "C" int sana_cross_attention_set_variant(int variant) {
+  SANA_REQUIRE(variant >= 0 && variant <= 2, "sana_cross_attention_set_variant: variant must be 0, 1 or 2");
+  g_ca_variant = variant;
+  return SANA_OK;
+}
+
+extern "C" int sana_cross_attention_take_device_status(int* status_out) {
+  SANA_REQUIRE(status_out, "sana_cross_attention_take_device_status: null pointer");
+  return cross_attn_tc_take_status(status_out);
+}
 
 extern "C" int sana_cross_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv,
                                     const void* mask, void* out, int64_t ldo, int64_t B, int64_t N, int64_t L,
@@ -283,6 +302,11 @@ extern "C" int sana_cross_attention(const void* q, int64_t ldq, const void* k, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int hd = (int)head_dim;
   if (dtype == SANA_BF16) {
+    const bool tc_ok = cross_attn_tc_supported(L, head_dim);
+    SANA_REQUIRE(g_ca_variant != 2 || tc_ok,
+                 "sana_cross_attention: the tcgen05 kernel covers 17..304 keys and heads of 16..128 channels");
+    if (tc_ok && g_ca_variant != 1)
+      return cross_attn_tc_launch(q, ldq, k, v, ldkv, mask, out, ldo, B, N, L, (int)heads, hd, st);
     const int hdp = (hd + 15) / 16 * 16;
     switch (hdp) {
       case 16: case 32: return launch_ca_bf16<32>(q, ldq, k, v, ldkv, mask, out, ldo, B, N, L, (int)heads, hd, st);

@@ -595,8 +595,18 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
   if (idx < total) {
     float acc = 0.f;
     if (!wait_failed) {
-      for (int r = 0; r < pg.world; ++r)
-        acc += (r == pg.rank) ? s : ld_relaxed_sys_f32(reinterpret_cast<const float*>(pg.base[r] + slot_off) + idx);
+      // all remote loads are issued before the first addition (each takes a few microseconds over
+      // NVLink; chained behind the additions they would cost that once per peer), then the ranks'
+      // values are added in rank order
+      float part[SP_MAX_WORLD];
+#pragma unroll
+      for (int r = 0; r < SP_MAX_WORLD; ++r)
+        part[r] = (r < pg.world && r != pg.rank)
+                      ? ld_relaxed_sys_f32(reinterpret_cast<const float*>(pg.base[r] + slot_off) + idx)
+                      : 0.f;
+#pragma unroll
+      for (int r = 0; r < SP_MAX_WORLD; ++r)
+        if (r < pg.world) acc += (r == pg.rank) ? s : part[r];
     } else {
       acc = s;  // flagged in the soft-error word; the host must not use this result
     }

@@ -359,6 +359,18 @@ def cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Opt
     return out
 
 
+def set_cross_attention_variant(variant: int) -> None:
+    """0 = choose per problem, 1 = warp-level kernel, 2 = tcgen05 kernel (bf16 sana_cross_attention)."""
+    _lib.check(_lib.load().sana_cross_attention_set_variant(variant), "sana_cross_attention_set_variant")
+
+
+def take_cross_attention_device_status() -> int:
+    """Code recorded by a timed-out wait inside the tcgen05 cross-attention kernel (0 = none).  Synchronises."""
+    v = C.c_int(0)
+    _lib.check(_lib.load().sana_cross_attention_take_device_status(C.byref(v)), "sana_cross_attention_take_device_status")
+    return int(v.value)
+
+
 def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], W: int, H: int, row0: int = 0,
                halo_top: Optional[torch.Tensor] = None, halo_bot: Optional[torch.Tensor] = None) -> torch.Tensor:
     """3x3 depthwise conv + bias + SiLU-GLU.  u [rows*W, 2*hid] (channels last, image rows
