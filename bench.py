@@ -186,6 +186,34 @@ def run_reference(args) -> None:
     }))
 
 
+def fp4_library_rate(M: int, N: int, K: int, iters: int = 20) -> dict:
+    """The measured FP4 peak: torch._scaled_mm on float4_e2m1fn_x2 operands with E4M3 scales per 16
+    elements (the vendor library's block-scaled FP4 GEMM), same shape, random codes and scales.  Reported
+    beside our kernels as the denominator of their roofline; never on the product's path."""
+    if not hasattr(torch, "float4_e2m1fn_x2"):
+        return {"fp4_library": "unavailable: this torch has no float4_e2m1fn_x2"}
+    dev = torch.device("cuda", 0)
+    try:
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
+        b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
+        sf = lambda rows: (torch.rand(((rows + 127) // 128) * (((K // 16) + 3) // 4) * 512, device=dev) * 2).to(  # noqa: E731
+            torch.float8_e4m3fn)
+        sa, sb = sf(M), sf(N)
+        fn = lambda: torch._scaled_mm(a, b.t(), sa, sb, out_dtype=torch.bfloat16)  # noqa: E731
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        return {"fp4_library_ms": ms, "fp4_library_tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+    except Exception as e:  # noqa: BLE001 - the probe must not take the measurement down
+        return {"fp4_library": f"unavailable: {type(e).__name__}: {str(e)[:160]}"}
+
+
 def run_gemm_rates(tokens: int, iters: int = 20) -> None:
     """Device-timed rate of each projection shape of a 1.6B-width block, bf16 and NVFP4
     (one JSON line; quantisation of the operands is outside the timed region)."""
@@ -204,7 +232,8 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
         row = {"name": name, "M": tokens, "N": n, "K": k}
         for kind, variant, fn in (("bf16_1cta", 1, lambda: ops.gemm(a, w, out=o)),
                                   ("bf16_2cta", 2, lambda: ops.gemm(a, w, out=o)),
-                                  ("nvfp4", 0, lambda: ops.gemm_nvfp4(qa, qw, out=o))):
+                                  ("nvfp4_1cta", 1, lambda: ops.gemm_nvfp4(qa, qw, out=o)),
+                                  ("nvfp4_2cta", 2, lambda: ops.gemm_nvfp4(qa, qw, out=o))):
             ops.set_gemm_variant(variant)
             for _ in range(3):
                 fn()
@@ -217,6 +246,8 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
             ms = e0.elapsed_time(e1) / iters
             row[kind + "_ms"] = ms
             row[kind + "_tflops"] = 2.0 * tokens * n * k / (ms * 1e-3) / 1e12
+        ops.set_gemm_variant(0)
+        row.update(fp4_library_rate(tokens, n, k, iters))
         out["rows"].append(row)
     print(json.dumps(out))
 

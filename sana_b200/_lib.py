@@ -10,7 +10,8 @@ import os
 import threading
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "lib", "libsana_b200.so")
+# SANA_B200_LIBRARY names another build of the same library (e.g. one compiled with tuning counters)
+LIB_PATH = os.environ.get("SANA_B200_LIBRARY") or os.path.join(PKG, "lib", "libsana_b200.so")
 
 SANA_F32 = 0
 SANA_BF16 = 1

@@ -24,6 +24,17 @@ namespace sana {
 
 __device__ int g_cax_status = 0;
 
+// Optional cycle accounting of the roles (compiled in with -DSANA_CX_PROFILE, for tuning only): sums over all
+// CTAs of the cycles one thread of each role spent in its waits and in its work.
+#ifdef SANA_CX_PROFILE
+__device__ unsigned long long g_cax_prof[16];
+#define CX_T0() const long long cx_t0__ = clock64()
+#define CX_ACC(slot, on) do { if (on) atomicAdd(&g_cax_prof[slot], (unsigned long long)(clock64() - cx_t0__)); } while (0)
+#else
+#define CX_T0() do { } while (0)
+#define CX_ACC(slot, on) do { } while (0)
+#endif
+
 constexpr int CX_LP_MAX = 304;                       // keys, padded to a multiple of 16
 constexpr int CX_KV_BLK = CX_LP_MAX * 128;           // one 64-channel block of K or V (38 912 bytes)
 constexpr int CX_Q_BLK = 128 * 128;                  // one 64-channel block of a Q tile
@@ -97,97 +108,152 @@ __device__ __forceinline__ uint64_t cx_desc_mn(uint32_t saddr, uint32_t block_st
   return ((uint64_t)hi << 32) | lo;
 }
 
-// One group of 16 scores of this lane's row (columns jb .. jb + 15 of the key axis) folded into the running maximum,
-// in the scaled domain t = s * c + bias[j]; columns j >= lvalid (padding) are left out.
-template <bool MASK>
-__device__ __forceinline__ float cx_max16(const uint32_t (&cur)[16], float mx, int jb, int lvalid, float c, const float* bias) {
-  if (jb + 16 <= lvalid) {
+// ---- softmax of one key chunk, one pass -------------------------------------------------------------
+// A lane owns one query row; its state is the shift m (scaled log2 domain) and partial row sums.  The chunk
+// is walked in steps of 32 scores (two register sets in ping-pong: the next step's tcgen05.ld is in flight
+// while this one is processed).  A step computes u = s c (+ bias) - m, checks u <= 8 and writes
+// p = 2^u over the scores as bf16 pairs.  When some lane of the warp finds u > 8 (the running shift was too
+// small by more than 2^8) the warp takes the fix-up: that lane raises its shift, and everything it has
+// accumulated under the old one - the probabilities already written for this chunk, its row sums and, in
+// the second chunk, the output accumulator (after the first chunk's product has completed) - is scaled by
+// 2^(old - new).  Exact either way; the fix-up is rare because the first step of a row seeds the shift
+// with the maximum of its first 32 scores.
+struct CxRare {
+  uint32_t o_taddr;    // this lane's row of the output accumulator
+  int hdn16;           // its width in 16-column groups
+  uint32_t bar_pva;    // completes when the first chunk's product of this tile is done
+  uint32_t pva_parity;
+  volatile int* abort_flag;
+};
+
+__device__ __forceinline__ float cx_max32(const float (&u)[32]) {
+  float a0 = fmaxf(u[0], u[1]), a1 = fmaxf(u[2], u[3]), a2 = fmaxf(u[4], u[5]), a3 = fmaxf(u[6], u[7]);
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float s = __uint_as_float(cur[e]);
-      mx = fmaxf(mx, MASK ? fmaf(s, c, bias[jb + e]) : s);
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float s = __uint_as_float(cur[e]);
-      if (jb + e < lvalid) mx = fmaxf(mx, MASK ? fmaf(s, c, bias[jb + e]) : s);
-    }
+  for (int e = 8; e < 32; e += 4) {
+    a0 = fmaxf(a0, u[e]);
+    a1 = fmaxf(a1, u[e + 1]);
+    a2 = fmaxf(a2, u[e + 2]);
+    a3 = fmaxf(a3, u[e + 3]);
   }
-  return mx;
+  return fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
 }
 
-// Row maximum of `ncols` scores (a multiple of 16) starting at tensor-memory address `taddr`; two register sets
-// in ping-pong so that the next group's load is in flight while this one is reduced.
-template <bool MASK>
-__device__ __forceinline__ float cx_row_max(uint32_t taddr, int ncols, int j0, int lvalid, float c, const float* bias) {
-  float mx = -INFINITY;
-  uint32_t r0[16], r1[16];
-  tmem_ld_32x16(taddr, r0);
-  const int groups = ncols >> 4;
-  for (int g = 0; g < groups; g += 2) {
-    tmem_ld_wait();
-    if (g + 1 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
-    mx = cx_max16<MASK>(r0, mx, j0 + 16 * g, lvalid, c, bias);
-    if (g + 1 < groups) {
-      tmem_ld_wait();
-      if (g + 2 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
-      mx = cx_max16<MASK>(r1, mx, j0 + 16 * (g + 1), lvalid, c, bias);
-    }
-  }
-  return MASK ? mx : mx * c;  // c > 0
-}
-
-// p = 2^(t - m) for one group of 16 scores, written over the scores as 8 columns of bf16 pairs at `pdst`; the
-// two partial row sums are updated.
-template <bool MASK>
-__device__ __forceinline__ void cx_exp16(const uint32_t (&cur)[16], uint32_t pdst, int jb, int lvalid, float c, float nm,
-                                         const float* bias, float& sum0, float& sum1) {
-  float p[16];
-  if (jb + 16 <= lvalid) {
+// returns false when a wait inside the fix-up was abandoned
+template <bool MASK, bool CHUNK_B>
+__device__ __forceinline__ bool cx_step(const uint32_t (&sc)[32], int step, int ncols, uint32_t s_taddr, int j0, int jlim,
+                                        float c, const float* bias, float& m, float (&sum)[4], bool seed, const CxRare& rare) {
+  const int jb = j0 + 32 * step;
+  const bool full = 32 * step + 32 <= ncols;  // otherwise 16 columns were loaded
+  float u[32];
+  if (seed) {  // first step of the row: the shift is the maximum of its scores
+    float t[32];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float s = __uint_as_float(cur[e]);
-      p[e] = cx_exp2(MASK ? fmaf(s, c, bias[jb + e] + nm) : fmaf(s, c, nm));
+    for (int e = 0; e < 32; ++e) {
+      const float s = __uint_as_float(sc[e]);
+      t[e] = MASK ? fmaf(s, c, bias[jb + e]) : s * c;
+      if (jb + e >= jlim || (!full && e >= 16)) t[e] = -INFINITY;
     }
-  } else {
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float s = __uint_as_float(cur[e]);
-      const float t = MASK ? fmaf(s, c, bias[jb + e] + nm) : fmaf(s, c, nm);  // bias holds LP entries
-      p[e] = (jb + e < lvalid) ? cx_exp2(t) : 0.f;
-    }
+    m = cx_max32(t);
   }
-  uint32_t pk[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    pk[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
-    sum0 += p[2 * e];
-    sum1 += p[2 * e + 1];
-  }
-  tmem_st_32x8(pdst, pk);
-}
-
-// The same walk for the exponentials.  Group g's probabilities land on columns 8g .. 8g+7 of the chunk, whose
-// scores were consumed by an earlier group (or are already in registers); the group in flight lies above them.
-template <bool MASK>
-__device__ __forceinline__ float cx_row_exp(uint32_t taddr, int ncols, int j0, int lvalid, float c, float m, const float* bias) {
-  float sum0 = 0.f, sum1 = 0.f;
-  uint32_t r0[16], r1[16];
-  tmem_ld_32x16(taddr, r0);
-  const int groups = ncols >> 4;
   const float nm = -m;
-  for (int g = 0; g < groups; g += 2) {
-    tmem_ld_wait();
-    if (g + 1 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
-    cx_exp16<MASK>(r0, taddr + 8u * (uint32_t)g, j0 + 16 * g, lvalid, c, nm, bias, sum0, sum1);
-    if (g + 1 < groups) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const float s = __uint_as_float(sc[e]);
+    u[e] = MASK ? fmaf(s, c, bias[jb + e] + nm) : fmaf(s, c, nm);
+  }
+  if (jb + 32 > jlim || !full) {  // padding keys and columns that were not loaded
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (jb + e >= jlim || (!full && e >= 16)) u[e] = -INFINITY;
+  }
+  const float gmax = cx_max32(u);
+  if (__any_sync(0xffffffffu, gmax > 8.0f)) {
+    // ---- fix-up (rare): lanes with gmax > 8 move their shift up by gmax
+    const float d = gmax > 8.0f ? gmax : 0.f;
+    const float alpha = cx_exp2(-d);
+    tmem_st_wait();  // this lane's earlier probability writes have landed
+    for (int g = 0; g < step; ++g) {  // probabilities of this chunk written so far: 16 columns per step
+      uint32_t pk[16];
+      tmem_ld_32x16(s_taddr + 16u * (uint32_t)g, pk);
       tmem_ld_wait();
-      if (g + 2 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
-      cx_exp16<MASK>(r1, taddr + 8u * (uint32_t)(g + 1), j0 + 16 * (g + 1), lvalid, c, nm, bias, sum0, sum1);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(bf16_lo(pk[e]) * alpha, bf16_hi(pk[e]) * alpha);
+      tmem_st_32x16(s_taddr + 16u * (uint32_t)g, pk);
+    }
+    if (CHUNK_B) {
+      if (!mbar_wait(rare.bar_pva, rare.pva_parity, rare.abort_flag, 14, &g_cax_status)) return false;
+      tcgen05_fence_after();
+      for (int g = 0; g < rare.hdn16; ++g) {
+        uint32_t o[16];
+        tmem_ld_32x16(rare.o_taddr + 16u * (uint32_t)g, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+        tmem_st_32x16(rare.o_taddr + 16u * (uint32_t)g, o);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sum[q] *= alpha;
+    m += d;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) u[e] -= d;
+  }
+  uint32_t pk[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const float p0 = cx_exp2(u[2 * e]), p1 = cx_exp2(u[2 * e + 1]);
+    pk[e] = pack_bf16(p0, p1);
+    sum[(2 * e) & 3] += p0;
+    sum[(2 * e + 1) & 3] += p1;
+  }
+  // the write lands on columns whose scores were consumed by an earlier step (or are in registers already)
+  if (full) {
+    tmem_st_32x16(s_taddr + 16u * (uint32_t)step, pk);
+  } else {
+    uint32_t lo[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) lo[e] = pk[e];
+    tmem_st_32x8(s_taddr + 16u * (uint32_t)step, lo);
+  }
+  return true;
+}
+
+__device__ __forceinline__ void cx_load_step(uint32_t s_taddr, int step, int ncols, uint32_t (&r)[32]) {
+  if (32 * step + 32 <= ncols) {
+    tmem_ld_32x32(s_taddr + 32u * (uint32_t)step, r);
+  } else {
+    uint32_t lo[16];
+    tmem_ld_32x16(s_taddr + 32u * (uint32_t)step, lo);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) r[e] = lo[e], r[e + 16] = 0u;
+  }
+}
+
+template <bool MASK, bool CHUNK_B>
+__device__ __forceinline__ bool cx_chunk(uint32_t s_taddr, int ncols, int j0, int jlim, float c, const float* bias, float& m,
+                                         float (&sum)[4], const CxRare& rare) {
+  uint32_t r0[32], r1[32];
+  const int nsteps = (ncols + 31) >> 5;
+  cx_load_step(s_taddr, 0, ncols, r0);
+  for (int st = 0; st < nsteps; st += 2) {
+    tmem_ld_wait();
+    if (st + 1 < nsteps) cx_load_step(s_taddr, st + 1, ncols, r1);
+    if (!cx_step<MASK, CHUNK_B>(r0, st, ncols, s_taddr, j0, jlim, c, bias, m, sum, !CHUNK_B && st == 0, rare)) return false;
+    if (st + 1 < nsteps) {
+      tmem_ld_wait();
+      if (st + 2 < nsteps) cx_load_step(s_taddr, st + 2, ncols, r0);
+      if (!cx_step<MASK, CHUNK_B>(r1, st + 1, ncols, s_taddr, j0, jlim, c, bias, m, sum, false, rare)) return false;
     }
   }
-  return sum0 + sum1;
+  return true;
+}
+
+// One lane waits on the barrier, the warp follows (thirty-two pollers would take issue slots from the warps
+// that share the scheduler).
+__device__ __forceinline__ bool cx_warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, code, &g_cax_status) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 template <bool MASK>
@@ -254,47 +320,52 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t ph_sa = 0, ph_sb = 0, ph_kv = 0;
     int prev_bh = -1;
     bool ok = true;
+    CxRare rare;
+    rare.o_taddr = lane_addr + CX_COL_O;
+    rare.hdn16 = a.HDN >> 4;
+    rare.bar_pva = bar_pva;
+    rare.abort_flag = abort_flag;
     for (int it = 0; it < n_items && ok; ++it) {
       const int bh = (int)((t_begin + it) / a.nqt);
       if (MASK && bh != prev_bh) {  // the bias vector of this sample is in shared memory once K / V have been requested
-        if (!mbar_wait(bar_kv_full, ph_kv, abort_flag, 11, &g_cax_status)) { ok = false; break; }
+        if (!cx_warp_wait(bar_kv_full, ph_kv, abort_flag, 11, lane)) { ok = false; break; }
       }
       if (bh != prev_bh) ph_kv ^= 1u;
       prev_bh = bh;
-      // ---- chunk A: fixes the shift of the row
-      if (!mbar_wait(bar_sa, ph_sa, abort_flag, 12, &g_cax_status)) { ok = false; break; }
+      rare.pva_parity = (uint32_t)(it & 1);
+      float m = 0.f;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      // ---- chunk A: its first step seeds the shift of the row
+      {
+        CX_T0();
+        if (!cx_warp_wait(bar_sa, ph_sa, abort_flag, 12, lane)) { ok = false; break; }
+        CX_ACC(0, tid == 0);
+      }
       ph_sa ^= 1u;
       tcgen05_fence_after();
-      float m = cx_row_max<MASK>(lane_addr, a.NA, 0, a.L, c, bias);
-      float l = cx_row_exp<MASK>(lane_addr, a.NA, 0, a.L, c, m, bias);
+      {
+        CX_T0();
+        if (!cx_chunk<MASK, false>(lane_addr, a.NA, 0, a.L, c, bias, m, sum, rare)) { ok = false; break; }
+        CX_ACC(1, tid == 0);
+      }
       tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pa);
-      // ---- chunk B: same shift unless its maximum is more than 2^8 above it
-      if (!mbar_wait(bar_sb, ph_sb, abort_flag, 13, &g_cax_status)) { ok = false; break; }
+      // ---- chunk B
+      {
+        CX_T0();
+        if (!cx_warp_wait(bar_sb, ph_sb, abort_flag, 13, lane)) { ok = false; break; }
+        CX_ACC(2, tid == 0);
+      }
       ph_sb ^= 1u;
       tcgen05_fence_after();
-      const float mb = cx_row_max<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, bias);
-      if (__any_sync(0xffffffffu, mb > m + 8.0f)) {
-        // rare: rescale what chunk A has accumulated.  P_A V_A of this tile must have finished.
-        if (!mbar_wait(bar_pva, (uint32_t)(it & 1), abort_flag, 14, &g_cax_status)) { ok = false; break; }
-        tcgen05_fence_after();
-        const float m_new = fmaxf(m, mb);
-        const float alpha = cx_exp2(m - m_new);
-        for (int g = 0; g < (a.HDN >> 4); ++g) {
-          uint32_t o[16];
-          tmem_ld_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
-        }
-        l *= alpha;
-        m = m_new;
+      {
+        CX_T0();
+        if (!cx_chunk<MASK, true>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, bias, m, sum, rare)) { ok = false; break; }
+        CX_ACC(3, tid == 0);
       }
-      l += cx_row_exp<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, m, bias);
-      lbuf[(it & 1) * 128 + row] = l;
+      lbuf[(it & 1) * 128 + row] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
       tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
@@ -314,16 +385,19 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int64_t item = t_begin + it;
       const int bh = (int)(item / a.nqt), qt = (int)(item - (int64_t)bh * a.nqt);
       const int b = bh / a.heads, h = bh - b * a.heads;
-      if (!mbar_wait(bar_o_full, ph_o, abort_flag, 15, &g_cax_status)) { ok = false; break; }
+      {
+        CX_T0();
+        if (!cx_warp_wait(bar_o_full, ph_o, abort_flag, 15, lane)) { ok = false; break; }
+        CX_ACC(10, tid == 128);
+      }
       ph_o ^= 1u;
+      CX_T0();
       tcgen05_fence_after();
       const float inv = 1.0f / lbuf[(it & 1) * 128 + row];
       if (lane == 0) bulk_wait_read_all();  // the previous tile's stores have read the staging rows
       __syncwarp();
-      for (int g = 0; g < (a.HDN >> 4); ++g) {
-        uint32_t o[16];
-        tmem_ld_32x16(lane_addr + 16u * (uint32_t)g, o);
-        tmem_ld_wait();
+      const int groups = a.HDN >> 4;
+      auto emit = [&](const uint32_t (&o)[16], int g) {
         const int blk = g >> 2, cc = g & 3;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -332,6 +406,18 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(o[8 * hh + e]) * inv;
           uint4* slot = reinterpret_cast<uint4*>(stage_row + blk * 4096 + ((((uint32_t)(2 * cc + hh)) ^ swz) << 4));
           *slot = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+      };
+      uint32_t o0[16], o1[16];
+      tmem_ld_32x16(lane_addr, o0);
+      for (int g = 0; g < groups; g += 2) {
+        tmem_ld_wait();
+        if (g + 1 < groups) tmem_ld_32x16(lane_addr + 16u * (uint32_t)(g + 1), o1);
+        emit(o0, g);
+        if (g + 1 < groups) {
+          tmem_ld_wait();
+          if (g + 2 < groups) tmem_ld_32x16(lane_addr + 16u * (uint32_t)(g + 2), o0);
+          emit(o1, g + 1);
         }
       }
       tcgen05_fence_before();
@@ -345,6 +431,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           bulk_commit();
         }
       }
+      CX_ACC(11, tid == 128);
     }
     if (lane == 0) bulk_wait_all();
   } else if (warp == 8) {
@@ -358,7 +445,9 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int bh = (int)(item / a.nqt), qt = (int)(item - (int64_t)bh * a.nqt);
       const int b = bh / a.heads, h = bh - b * a.heads;
       if (it > 0) {
-        if (!mbar_wait(bar_q_free, ph_qfree, abort_flag, 16, &g_cax_status)) { ok = false; break; }
+        CX_T0();
+        if (!cx_warp_wait(bar_q_free, ph_qfree, abort_flag, 16, lane)) { ok = false; break; }
+        CX_ACC(12, lane == 0);
         ph_qfree ^= 1u;
       }
       if (lane == 0) {
@@ -367,7 +456,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       if (bh != prev_bh) {
         if (prev_bh >= 0) {  // every product that reads the previous K / V (and every reader of the bias) is done
-          if (!mbar_wait(bar_kv_free, ph_kvfree, abort_flag, 17, &g_cax_status)) { ok = false; break; }
+          if (!cx_warp_wait(bar_kv_free, ph_kvfree, abort_flag, 17, lane)) { ok = false; break; }
           ph_kvfree ^= 1u;
         }
         if (MASK) {
@@ -415,13 +504,18 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_bf16_ts(tmem_base + CX_COL_O, p_tmem + 8u * (uint32_t)ks, bdesc + (uint64_t)(128 * ks), idesc_o,
                      (chunk_b || ks != 0) ? 1u : 0u);
     };
+#ifdef SANA_CX_PROFILE
+    const long long cx_loop0 = clock64();
+#endif
     for (int it = 0; it < n_items && ok; ++it) {
       const int bh = (int)((t_begin + it) / a.nqt);
       if (bh != prev_bh) {  // the pipeline was drained: start it again on the new K / V
+        CX_T0();
         if (!mbar_wait(bar_kv_full, ph_kv, abort_flag, 1, &g_cax_status)) { ok = false; break; }
         ph_kv ^= 1u;
         if (!mbar_wait(bar_q_full, ph_q, abort_flag, 2, &g_cax_status)) { ok = false; break; }
         ph_q ^= 1u;
+        CX_ACC(4, true);
         tcgen05_fence_after();
         issue_s(false);
         umma_commit(bar_sa);
@@ -431,23 +525,35 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         prev_bh = bh;
       }
       const bool next_same = it + 1 < n_items && (int)((t_begin + it + 1) / a.nqt) == bh;
-      if (!mbar_wait(bar_pa, ph_pa, abort_flag, 3, &g_cax_status)) { ok = false; break; }
+      {
+        CX_T0();
+        if (!mbar_wait(bar_pa, ph_pa, abort_flag, 3, &g_cax_status)) { ok = false; break; }
+        CX_ACC(5, true);
+      }
       ph_pa ^= 1u;
       if (it > 0) {
+        CX_T0();
         if (!mbar_wait(bar_o_free, ph_ofree, abort_flag, 4, &g_cax_status)) { ok = false; break; }
         ph_ofree ^= 1u;
+        CX_ACC(6, true);
       }
       tcgen05_fence_after();
       issue_pv(false);
       umma_commit(bar_pva);
       if (next_same) {
+        CX_T0();
         if (!mbar_wait(bar_q_full, ph_q, abort_flag, 5, &g_cax_status)) { ok = false; break; }
         ph_q ^= 1u;
+        CX_ACC(7, true);
         tcgen05_fence_after();
         issue_s(false);
         umma_commit(bar_sa);
       }
-      if (!mbar_wait(bar_pb, ph_pb, abort_flag, 6, &g_cax_status)) { ok = false; break; }
+      {
+        CX_T0();
+        if (!mbar_wait(bar_pb, ph_pb, abort_flag, 6, &g_cax_status)) { ok = false; break; }
+        CX_ACC(8, true);
+      }
       ph_pb ^= 1u;
       tcgen05_fence_after();
       issue_pv(true);
@@ -460,6 +566,9 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(bar_kv_free);
       }
     }
+#ifdef SANA_CX_PROFILE
+    atomicAdd(&g_cax_prof[9], (unsigned long long)(clock64() - cx_loop0));
+#endif
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -522,6 +631,19 @@ int cross_attn_tc_launch(const void* q, int64_t ldq, const void* k, const void* 
   SANA_LAUNCH_CHECK("cross_attn_tc kernel");
   return SANA_OK;
 }
+
+#ifdef SANA_CX_PROFILE
+extern "C" int sana_debug_cax_prof(unsigned long long* out16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out16, g_cax_prof, 16 * sizeof(unsigned long long));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_cax_prof)");
+  if (reset) {
+    unsigned long long zero[16] = {};
+    e = cudaMemcpyToSymbol(g_cax_prof, zero, sizeof(zero));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_cax_prof)");
+  }
+  return SANA_OK;
+}
+#endif
 
 int cross_attn_tc_take_status(int* v) {
   cudaError_t e = cudaMemcpyFromSymbol(v, g_cax_status, sizeof(int));

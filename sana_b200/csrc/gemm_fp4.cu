@@ -256,6 +256,238 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
+
+// ---- CTA-pair variant -----------------------------------------------------------------------------
+// Two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2): each CTA loads its own
+// 128 rows of A with their scale tiles, HALF of the W tile (128 rows) and the scale tiles of the whole W
+// tile; the pair's leader copies the scales into tensor memory and issues the block-scaled MMAs with
+// M = 256.  Per SM and K block this moves 38 KiB through L2 and shared memory for twice the math of
+// the 128 x 128 kernel (36 KiB), which is what that kernel was bound by.  Tensor memory holds ONE
+// 256-column accumulator (two would leave no room for the scale columns): the epilogue of a tile does
+// not overlap the next tile's MMAs, but the loads run ahead through it (four stages of K = 256).
+// All four operand streams are bulk-tensor copies (the scale buffers as [tiles, 128] words, so that
+// tiles past the end arrive as zeros), counted on the leader's barrier.
+constexpr int P4_BM = 128, P4_BN = 256;
+constexpr int P4_A_BYTES = P4_BM * 128;             // 16 KiB
+constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 16 KiB: this CTA's half of the W tile
+constexpr int P4_SFA_BYTES = 4 * 512;               // scale tiles of this CTA's A rows, K = 256
+constexpr int P4_SFB_BYTES = 2 * 4 * 512;           // scale tiles of all 256 W rows
+constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;  // 38 KiB
+constexpr int P4_STAGES = 4;
+constexpr int P4_EPI_WARPS = 8;
+constexpr int P4_NBOX = (P4_BN / 2) / EPI_BOX_COLS;  // staging boxes per epilogue warp
+constexpr int P4_EPI_BYTES = P4_EPI_WARPS * P4_NBOX * EPI_BOX_BYTES;
+constexpr int P4_CTRL_BYTES = 256;
+constexpr int P4_SMEM_BYTES = P4_STAGES * P4_STAGE_BYTES + P4_EPI_BYTES + P4_CTRL_BYTES;
+constexpr int P4_THREADS = 64 + 32 * P4_EPI_WARPS;
+constexpr int P4_SF_COL0 = P4_BN;                   // scale columns follow the accumulator
+constexpr int P4_SF_COLS = 16 + 32;                 // per stage: A 4 x 4, W 4 x 8
+constexpr uint32_t P4_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(P4_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+static_assert(P4_SMEM_BYTES <= 232448, "shared memory budget");
+static_assert(P4_STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned");
+static_assert(P4_SF_COL0 + P4_STAGES * P4_SF_COLS <= 512, "tensor memory budget");
+static_assert(16 * P4_STAGES + 40 + 8 * P4_EPI_WARPS <= P4_CTRL_BYTES, "control block too small");
+
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                                uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
+struct P4Args {
+  __nv_bfloat16* out;
+  int64_t ldo;
+  const float* a_scale;
+  const float* w_scale;
+  int M, N, K;
+  int tiles_m, tiles_n;  // 256 x 256 pair tiles
+  int ktiles4;
+  EpiParams ep;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P4_THREADS, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes,
+                       const P4Args args) {
+  constexpr int STAGES = P4_STAGES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t tiles_base = smem_u32(smem_raw);
+  const uint32_t epi_base = tiles_base + STAGES * P4_STAGE_BYTES;
+  unsigned char* epi_gen = smem_raw + STAGES * P4_STAGE_BYTES;
+  const uint32_t ctrl = epi_base + P4_EPI_BYTES;
+  unsigned char* ctrl_gen = epi_gen + P4_EPI_BYTES;
+  // control layout: full[STAGES] | empty[STAGES] | tfull | (pad) | tempty | (pad) | tmem ptr | abort | res[EPI_WARPS]
+  const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
+  const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
+  const uint32_t bar_res = ctrl + 16 * STAGES + 40;
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
+
+  if ((tiles_base & 1023u) != 0u) {  // cluster-uniform: the dynamic window starts at the same offset in every CTA
+    if (threadIdx.x == 0) atomicExch(&g_fp4_status, 9);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int kblocks = (args.K + F4_BK - 1) / F4_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, 2 * P4_EPI_WARPS);
+    for (int w = 0; w < P4_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmSFA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmSFB) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmOut) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmRes) : "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates collectively
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 16 * STAGES + 32), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------- loads (both CTAs) ----------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      const uint32_t full0 = map_to_cta(bar_full, 0);  // the leader's full barriers, cluster address
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int mt = tile / args.tiles_n, nt = tile % args.tiles_n;
+        const int m0 = mt * 256 + (int)rank * P4_BM;          // this CTA's A rows
+        const int n0 = nt * P4_BN + (int)rank * (P4_BN / 2);  // this CTA's half of the W rows
+        const int sfa_row = (2 * mt + (int)rank) * args.ktiles4;  // scale tiles: row blocks of 128, K-fastest
+        const int sfb_row = (2 * nt) * args.ktiles4;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
+          const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * P4_STAGE_BYTES);
+          const uint32_t fb = full0 + 8 * stage;
+          tma_load_2d_pair(sa, &tmA, fb, kb * 128, m0);  // byte coordinates along K
+          tma_load_2d_pair(sa + P4_A_BYTES, &tmB, fb, kb * 128, n0);
+          tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES, &tmSFA, fb, 0, sfa_row + 4 * kb);
+          tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES, &tmSFB, fb, 0, sfb_row + 4 * kb);
+          tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + 4 * 512, &tmSFB, fb, 0, sfb_row + args.ktiles4 + 4 * kb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------
+    if (leader && lane == 0) {
+      uint32_t stage = 0, phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (!mbar_wait(bar_tempty, acc_phase ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
+        acc_phase ^= 1u;
+        tcgen05_fence_after();
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + P4_A_BYTES);
+          const uint32_t sfa_s = sa + P4_A_BYTES + P4_B_BYTES, sfb_s = sfa_s + P4_SFA_BYTES;
+          const uint32_t sfa_t = tmem_base + (uint32_t)(P4_SF_COL0 + stage * P4_SF_COLS), sfb_t = sfa_t + 16;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tmem_cp_sf_pair(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
+            tmem_cp_sf_pair(sfb_t + 8 * k, make_sf_desc(sfb_s + 512 * k));             // W rows 0..127 of the tile
+            tmem_cp_sf_pair(sfb_t + 8 * k + 4, make_sf_desc(sfb_s + 4 * 512 + 512 * k));  // W rows 128..255
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_nvfp4_pair(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k,
+                            sfb_t + 8 * k, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(bar_empty + 8 * stage);  // frees this stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(bar_tfull);  // accumulator complete, both CTAs
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps (both CTAs) -------------------------
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;
+    constexpr int HALF = P4_BN / 2, NCHUNK = HALF / 16;
+    const EpiParams& ep = args.ep;
+    const int64_t N = args.N;
+    const bool has_res = ep.residual != nullptr;
+    const float alpha = __ldg(args.a_scale) * __ldg(args.w_scale);
+    const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+    EpiBox eb;
+    eb.box_s = epi_base + (uint32_t)(ew * P4_NBOX * EPI_BOX_BYTES);
+    eb.row_g = epi_gen + ew * P4_NBOX * EPI_BOX_BYTES + lane * 128;
+    eb.res_bar = bar_res + 8 * ew;
+    eb.res_phase = 0u;
+    eb.swz = (uint32_t)(lane & 7);
+    uint32_t full_phase = 0u;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int m_box = (tile / args.tiles_n) * 256 + (int)rank * P4_BM + quad * 32;
+      const int64_t nbase = (int64_t)(tile % args.tiles_n) * P4_BN + half * HALF;
+      const int64_t m = (int64_t)m_box + lane;
+      const bool row_ok = m < args.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * HALF);
+      const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
+      const bool box_rows_in = m_box < args.M;
+      const bool use_res = has_res && box_rows_in;
+      epi_box_begin<P4_NBOX>(eb, row, use_res, lane, m_box, &tmRes);
+      EpiStep st[2];
+      epi_fetch(row, st[0], 0);
+      if (!mbar_wait(bar_tfull, full_phase, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
+      full_phase ^= 1u;
+      tcgen05_fence_after();
+      if (!epi_box_drain<NCHUNK, true>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, alpha, abort_flag,
+                                       &g_fp4_status)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0);  // the leader's barrier collects both CTAs
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the other CTA may still signal or read it
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // ---- quantiser ----------------------------------------------------------------------------------
 __global__ void absmax_bf16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, int64_t rows, int K,
                                    float* __restrict__ amax) {
@@ -381,7 +613,57 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   SANA_REQUIRE(!p.residual || (aligned16(p.residual) && p.ldr % 8 == 0), "sana_gemm_nvfp4: residual alignment");
   SANA_REQUIRE(!p.bias || aligned16(p.bias), "sana_gemm_nvfp4: bias alignment");
   SANA_REQUIRE(!p.gate_table || (aligned16(p.gate_table) && aligned16(p.gate_t)), "sana_gemm_nvfp4: gate alignment");
-  CUtensorMap tmA, tmB;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // output and residual as 32-row x 64-column boxes (the residual map is a copy when unused)
+  CUtensorMap tmA, tmB, tmOut, tmRes;
+  rc = make_tmap_2d(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, M, N, ldo * 2, 32, EPI_BOX_COLS);
+  if (rc) return rc;
+  tmRes = tmOut;
+  if (p.residual) {
+    rc = make_tmap_2d(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.residual, M, N, p.ldr * 2, 32, EPI_BOX_COLS);
+    if (rc) return rc;
+  }
+  const int variant = gemm_variant();
+  if (variant == 2 || (variant == 0 && M >= 2048)) {
+    // CTA pairs on 256 x 256 tiles
+    rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Aq, M, K / 2, K / 2, P4_BM, 128);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, P4_BN / 2, 128);
+    if (rc) return rc;
+    // the scale buffers as [tiles, 128 words]: a box is the four 512-byte tiles of one K block
+    const int64_t kt4 = ktiles4_of(K);
+    CUtensorMap tmSFA, tmSFB;
+    {
+      const uint64_t dims_a[2] = {128, (uint64_t)(ceil_div(M, 128) * kt4)}, dims_b[2] = {128, (uint64_t)(ceil_div(N, 128) * kt4)};
+      const uint64_t strides[1] = {512};
+      const uint32_t box[2] = {128, 4};
+      rc = make_tmap_tiled(&tmSFA, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, sfa, dims_a, strides, box, false);
+      if (rc) return rc;
+      rc = make_tmap_tiled(&tmSFB, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, sfw, dims_b, strides, box, false);
+      if (rc) return rc;
+    }
+    static OncePerDevice pair_once;
+    if (pair_once.first_time()) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P4_SMEM_BYTES);
+      if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_nvfp4_pair)");
+    }
+    P4Args a;
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.ldo = ldo;
+    a.a_scale = a_scales + 1;  // [amax, tensor scale]
+    a.w_scale = w_scales + 1;
+    a.M = (int)M, a.N = (int)N, a.K = (int)K;
+    a.tiles_m = (int)ceil_div(M, 256);
+    a.tiles_n = (int)ceil_div(N, P4_BN);
+    a.ktiles4 = (int)kt4;
+    a.ep = p;
+    const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
+    const int64_t max_clusters = sm_count() / 2;
+    const int grid = (int)(2 * (tiles < max_clusters ? tiles : max_clusters));
+    gemm_nvfp4_pair_kernel<<<grid, P4_THREADS, P4_SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmOut, tmRes, a);
+    SANA_LAUNCH_CHECK("gemm_nvfp4_pair kernel");
+    return SANA_OK;
+  }
   rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Aq, M, K / 2, K / 2, F4_BM, 128);
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, F4_BN, 128);
@@ -403,19 +685,9 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   a.tiles_n = (int)ceil_div(N, F4_BN);
   a.ktiles4 = (int)ktiles4_of(K);
   a.ep = p;
-  // output and residual as 32-row x 64-column boxes (the residual map is a copy when unused)
-  CUtensorMap tmOut, tmRes;
-  rc = make_tmap_2d(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, M, N, ldo * 2, 32, EPI_BOX_COLS);
-  if (rc) return rc;
-  tmRes = tmOut;
-  if (p.residual) {
-    rc = make_tmap_2d(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.residual, M, N, p.ldr * 2, 32, EPI_BOX_COLS);
-    if (rc) return rc;
-  }
   const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_nvfp4_tc_kernel<<<grid, F4_THREADS, F4_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmOut, tmRes,
-                                                                                               a);
+  gemm_nvfp4_tc_kernel<<<grid, F4_THREADS, F4_SMEM_BYTES, st>>>(tmA, tmB, tmOut, tmRes, a);
   SANA_LAUNCH_CHECK("gemm_nvfp4_tc kernel");
   return SANA_OK;
 }

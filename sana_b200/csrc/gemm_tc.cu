@@ -327,6 +327,7 @@ int gemm_tc2_take_status(int* v);
 
 // 0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA-pair kernel
 static int g_gemm_variant = 0;
+int gemm_variant() { return g_gemm_variant; }
 
 int gemm_tc_launch(const void* A, int64_t lda, const void* Wt, int64_t ldw, void* out, int64_t ldo, int64_t M,
                    int64_t N, int64_t K, const EpiParams& ep, cudaStream_t st) {
