@@ -20,6 +20,16 @@ namespace sana {
 
 __device__ int g_fp4_status = 0;
 
+// Optional cycle accounting of the CTA-pair kernel's roles (compiled in with -DSANA_F4_PROFILE, for tuning only)
+#ifdef SANA_F4_PROFILE
+__device__ unsigned long long g_f4_prof[8];
+#define F4_T0() const long long f4_t0__ = clock64()
+#define F4_ACC(slot, on) do { if (on) atomicAdd(&g_f4_prof[slot], (unsigned long long)(clock64() - f4_t0__)); } while (0)
+#else
+#define F4_T0() do { } while (0)
+#define F4_ACC(slot, on) do { } while (0)
+#endif
+
 constexpr int F4_BM = 128, F4_BN = 128;
 constexpr int F4_BK = 256;                          // elements per stage = 128 bytes per row
 constexpr int F4_A_BYTES = F4_BM * 128;             // 16 KiB
@@ -258,30 +268,31 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 
 // ---- CTA-pair variant -----------------------------------------------------------------------------
-// Two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2): each CTA loads its own
-// 128 rows of A with their scale tiles, HALF of the W tile (128 rows) and the scale tiles of the whole W
+// Two CTAs of a cluster share one 256 x 128 output tile (tcgen05 cta_group::2): each CTA loads its own
+// 128 rows of A with their scale tiles, HALF of the W tile (64 rows) and the scale tile of the whole W
 // tile; the pair's leader copies the scales into tensor memory and issues the block-scaled MMAs with
-// M = 256.  Per SM and K block this moves 38 KiB through L2 and shared memory for twice the math of
-// the 128 x 128 kernel (36 KiB), which is what that kernel was bound by.  Tensor memory holds ONE
-// 256-column accumulator (two would leave no room for the scale columns): the epilogue of a tile does
-// not overlap the next tile's MMAs, but the loads run ahead through it (four stages of K = 256).
+// M = 256.  Per SM and K block this moves 28 KiB through L2 and shared memory for the math the
+// 128 x 128 kernel moves 36 KiB for, and six stages fit.  Two 128-column accumulators alternate, so the
+// epilogue of a tile runs under the MMAs of the next one; a 256 x 256 tile with the one accumulator
+// that fits beside the scale columns ran its MMAs at the same rate but left its epilogue (a third of
+// the tile's time at K = 2240) exposed.
 // All four operand streams are bulk-tensor copies (the scale buffers as [tiles, 128] words, so that
 // tiles past the end arrive as zeros), counted on the leader's barrier.
-constexpr int P4_BM = 128, P4_BN = 256;
+constexpr int P4_BM = 128, P4_BN = 128;
 constexpr int P4_A_BYTES = P4_BM * 128;             // 16 KiB
-constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 16 KiB: this CTA's half of the W tile
+constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 8 KiB: this CTA's half of the W tile
 constexpr int P4_SFA_BYTES = 4 * 512;               // scale tiles of this CTA's A rows, K = 256
-constexpr int P4_SFB_BYTES = 2 * 4 * 512;           // scale tiles of all 256 W rows
-constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;  // 38 KiB
-constexpr int P4_STAGES = 4;
+constexpr int P4_SFB_BYTES = 4 * 512;               // scale tiles of the 128 W rows
+constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;  // 28 KiB
+constexpr int P4_STAGES = 6;
 constexpr int P4_EPI_WARPS = 8;
 constexpr int P4_NBOX = (P4_BN / 2) / EPI_BOX_COLS;  // staging boxes per epilogue warp
 constexpr int P4_EPI_BYTES = P4_EPI_WARPS * P4_NBOX * EPI_BOX_BYTES;
 constexpr int P4_CTRL_BYTES = 256;
 constexpr int P4_SMEM_BYTES = P4_STAGES * P4_STAGE_BYTES + P4_EPI_BYTES + P4_CTRL_BYTES;
 constexpr int P4_THREADS = 64 + 32 * P4_EPI_WARPS;
-constexpr int P4_SF_COL0 = P4_BN;                   // scale columns follow the accumulator
-constexpr int P4_SF_COLS = 16 + 32;                 // per stage: A 4 x 4, W 4 x 8
+constexpr int P4_SF_COL0 = 2 * P4_BN;               // scale columns follow the two accumulators
+constexpr int P4_SF_COLS = 16 + 16;                 // per stage: A 4 x 4, W 4 x 4
 constexpr uint32_t P4_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(P4_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 static_assert(P4_SMEM_BYTES <= 232448, "shared memory budget");
 static_assert(P4_STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned");
@@ -307,7 +318,7 @@ struct P4Args {
   const float* a_scale;
   const float* w_scale;
   int M, N, K;
-  int tiles_m, tiles_n;  // 256 x 256 pair tiles
+  int tiles_m, tiles_n;  // 256 x 128 pair tiles
   int ktiles4;
   EpiParams ep;
 };
@@ -324,7 +335,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   unsigned char* epi_gen = smem_raw + STAGES * P4_STAGE_BYTES;
   const uint32_t ctrl = epi_base + P4_EPI_BYTES;
   unsigned char* ctrl_gen = epi_gen + P4_EPI_BYTES;
-  // control layout: full[STAGES] | empty[STAGES] | tfull | (pad) | tempty | (pad) | tmem ptr | abort | res[EPI_WARPS]
+  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort | res[EPI_WARPS]
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
   const uint32_t bar_res = ctrl + 16 * STAGES + 40;
@@ -347,8 +358,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_tfull, 1);
-    mbar_init(bar_tempty, 2 * P4_EPI_WARPS);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * P4_EPI_WARPS);
+    }
     for (int w = 0; w < P4_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -381,9 +394,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int m0 = mt * 256 + (int)rank * P4_BM;          // this CTA's A rows
         const int n0 = nt * P4_BN + (int)rank * (P4_BN / 2);  // this CTA's half of the W rows
         const int sfa_row = (2 * mt + (int)rank) * args.ktiles4;  // scale tiles: row blocks of 128, K-fastest
-        const int sfb_row = (2 * nt) * args.ktiles4;
+        const int sfb_row = nt * args.ktiles4;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
+          {
+            F4_T0();
+            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
+            F4_ACC(5, leader);
+          }
           const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
           if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * P4_STAGE_BYTES);
           const uint32_t fb = full0 + 8 * stage;
@@ -391,7 +408,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tma_load_2d_pair(sa + P4_A_BYTES, &tmB, fb, kb * 128, n0);
           tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES, &tmSFA, fb, 0, sfa_row + 4 * kb);
           tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES, &tmSFB, fb, 0, sfb_row + 4 * kb);
-          tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + 4 * 512, &tmSFB, fb, 0, sfb_row + args.ktiles4 + 4 * kb);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -405,12 +421,26 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (leader && lane == 0) {
       uint32_t stage = 0, phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        if (!mbar_wait(bar_tempty, acc_phase ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
-        acc_phase ^= 1u;
+      int it = 0;
+#ifdef SANA_F4_PROFILE
+      const long long f4_loop0 = clock64();
+#endif
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+        const int a = it & 1;
+        {
+          F4_T0();
+          if (!mbar_wait(bar_tempty + 8 * a, ((acc_phase >> a) & 1u) ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
+          F4_ACC(0, true);
+        }
+        acc_phase ^= 1u << a;
         tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * P4_BN);
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
+          {
+            F4_T0();
+            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
+            F4_ACC(1, true);
+          }
           tcgen05_fence_after();
           const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + P4_A_BYTES);
@@ -419,18 +449,20 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             tmem_cp_sf_pair(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
-            tmem_cp_sf_pair(sfb_t + 8 * k, make_sf_desc(sfb_s + 512 * k));             // W rows 0..127 of the tile
-            tmem_cp_sf_pair(sfb_t + 8 * k + 4, make_sf_desc(sfb_s + 4 * 512 + 512 * k));  // W rows 128..255
+            tmem_cp_sf_pair(sfb_t + 4 * k, make_sf_desc(sfb_s + 512 * k));
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_nvfp4_pair(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k,
-                            sfb_t + 8 * k, (kb | k) != 0 ? 1u : 0u);
+            umma_nvfp4_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k, sfb_t + 4 * k,
+                            (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(bar_empty + 8 * stage);  // frees this stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit_pair(bar_tfull);  // accumulator complete, both CTAs
+        if (ok) umma_commit_pair(bar_tfull + 8 * a);  // accumulator complete, both CTAs
       }
+#ifdef SANA_F4_PROFILE
+      atomicAdd(&g_f4_prof[2], (unsigned long long)(clock64() - f4_loop0));
+#endif
     }
   } else {
     // ------------------------------- epilogue warps (both CTAs) -------------------------
@@ -451,29 +483,37 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     eb.swz = (uint32_t)(lane & 7);
     uint32_t full_phase = 0u;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    int it = 0;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+      const int a = it & 1;
       const int m_box = (tile / args.tiles_n) * 256 + (int)rank * P4_BM + quad * 32;
       const int64_t nbase = (int64_t)(tile % args.tiles_n) * P4_BN + half * HALF;
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * HALF);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * P4_BN + half * HALF);
       const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
       const bool box_rows_in = m_box < args.M;
       const bool use_res = has_res && box_rows_in;
       epi_box_begin<P4_NBOX>(eb, row, use_res, lane, m_box, &tmRes);
       EpiStep st[2];
       epi_fetch(row, st[0], 0);
-      if (!mbar_wait(bar_tfull, full_phase, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
-      full_phase ^= 1u;
+      {
+        F4_T0();
+        if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
+        F4_ACC(3, threadIdx.x == 64 && leader);
+      }
+      full_phase ^= 1u << a;
       tcgen05_fence_after();
+      F4_T0();
       if (!epi_box_drain<NCHUNK, true>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, alpha, abort_flag,
                                        &g_fp4_status)) {
         ok = false;
         break;
       }
+      F4_ACC(4, threadIdx.x == 64 && leader);
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty0);  // the leader's barrier collects both CTAs
+      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * a);  // the leader's barrier collects both CTAs
     }
     if (lane == 0) bulk_wait_all();
   }
@@ -625,7 +665,7 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   }
   const int variant = gemm_variant();
   if (variant == 2 || (variant == 0 && M >= 2048)) {
-    // CTA pairs on 256 x 256 tiles
+    // CTA pairs on 256 x 128 tiles
     rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Aq, M, K / 2, K / 2, P4_BM, 128);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, P4_BN / 2, 128);
@@ -691,6 +731,19 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   SANA_LAUNCH_CHECK("gemm_nvfp4_tc kernel");
   return SANA_OK;
 }
+
+#ifdef SANA_F4_PROFILE
+extern "C" int sana_debug_f4_prof(unsigned long long* out8, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out8, g_f4_prof, 8 * sizeof(unsigned long long));
+  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_f4_prof)");
+  if (reset) {
+    unsigned long long zero[8] = {};
+    e = cudaMemcpyToSymbol(g_f4_prof, zero, sizeof(zero));
+    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_f4_prof)");
+  }
+  return SANA_OK;
+}
+#endif
 
 extern "C" int sana_gemm_nvfp4_take_device_status(int* status_out) {
   if (!status_out) return fail(SANA_ERR_INVALID, "sana_gemm_nvfp4_take_device_status: null pointer");

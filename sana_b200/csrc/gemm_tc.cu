@@ -15,6 +15,11 @@
 // CTA-wide abort flag and all roles fall through to the common teardown (TMEM is freed).
 #include <mutex>
 
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "tc_common.cuh"
 
 namespace sana {
@@ -242,25 +247,45 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-int make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, const void* base, int64_t rows,
-                 int64_t cols, int64_t ld_bytes, int box_rows, int box_cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
-  (void)elem_bytes;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return SANA_OK;
-}
+// Encoded maps are kept in a process-wide cache keyed by everything that goes into them (data type,
+// base address, extents, strides, box, swizzle): a forward pass asks for the same few dozen maps on
+// every step, and an encode call costs about as much as a small kernel launch.  A map depends only
+// on its key, not on the contents of memory or on the device, so a stale entry cannot exist; the
+// cache is emptied when it reaches its size limit.
+struct TmapKey {
+  uint64_t w[14];
+  bool operator==(const TmapKey& o) const { return memcmp(w, o.w, sizeof(w)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t v : k.w) h = (h ^ v) * 1099511628211ull;
+    return (size_t)h;
+  }
+};
+static std::mutex g_tmap_mutex;
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+constexpr size_t TMAP_CACHE_LIMIT = 8192;
 
 int make_tmap_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  if (rank < 1 || rank > 5) return fail(SANA_ERR_INVALID, "tensor map rank %d out of range", rank);
+  TmapKey key = {};
+  key.w[0] = (uint64_t)dtype | ((uint64_t)rank << 8) | ((uint64_t)(swizzle128 ? 1 : 0) << 16);
+  key.w[1] = (uint64_t)reinterpret_cast<uintptr_t>(base);
+  for (int i = 0; i < rank; ++i) key.w[2 + i] = dims[i];
+  for (int i = 0; i + 1 < rank; ++i) key.w[7 + i] = strides_bytes[i];
+  for (int i = 0; i < rank; ++i) key.w[11 + i / 2] |= (uint64_t)box[i] << (32 * (i & 1));
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *tm = it->second;
+      return SANA_OK;
+    }
+  }
   cuuint64_t d[5], s[5];
   cuuint32_t b[5], estr[5];
   for (int i = 0; i < rank; ++i) d[i] = dims[i], b[i] = box[i], estr[i] = 1;
@@ -269,7 +294,19 @@ int make_tmap_tiled(CUtensorMap* tm, CUtensorMapDataType dtype, int rank, const 
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(SANA_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  if (g_tmap_cache.size() >= TMAP_CACHE_LIMIT) g_tmap_cache.clear();
+  g_tmap_cache.emplace(key, *tm);
   return SANA_OK;
+}
+
+int make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, const void* base, int64_t rows,
+                 int64_t cols, int64_t ld_bytes, int box_rows, int box_cols) {
+  (void)elem_bytes;
+  const uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+  const uint64_t strides[1] = {(uint64_t)ld_bytes};
+  const uint32_t box[2] = {(uint32_t)box_cols, (uint32_t)box_rows};
+  return make_tmap_tiled(tm, dtype, 2, base, dims, strides, box, true);
 }
 
 // [rows, cols] bf16 matrix, row stride ld elements; box = box_rows x 64 columns.

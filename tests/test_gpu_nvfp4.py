@@ -45,7 +45,7 @@ GEMM_SHAPES = [(128, 128, 256), (128, 128, 64), (200, 136, 96), (1, 8, 32), (513
 
 @pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
 def kernel_variant(request):
-    """Both tensor-core kernels behind sana_gemm_nvfp4: 128 x 128 tiles on one CTA, 256 x 256 on a CTA pair."""
+    """Both tensor-core kernels behind sana_gemm_nvfp4: 128 x 128 tiles on one CTA, 256 x 128 on a CTA pair."""
     ops.set_gemm_variant(request.param)
     yield request.param
     ops.set_gemm_variant(0)
