@@ -370,6 +370,8 @@ class KernelTimer:
     GROUPS = {"gemm": "gemm", "gemm_nvfp4": "gemm", "ln_modulate": "ln_modulate", "la_state": "la_state (+exchange)",
               "la_state_sp": "la_state (+exchange)", "la_apply": "la_apply", "dwconv_glu": "dwconv_glu",
               "cross_attention": "cross_attention_core", "nvfp4_quantize": "nvfp4_quantize", "rmsnorm_": "rmsnorm",
+              "ln_modulate_fp4": "ln_modulate", "la_apply_fp4": "la_apply", "nvfp4_quantize_scaled": "nvfp4_quantize",
+              "nvfp4_scale_roll": "nvfp4_scale_roll",
               "halo_exchange": "conv_halo"}
 
     def __init__(self):
@@ -547,10 +549,13 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch of the stack workload")
     ap.add_argument("--depth", type=int, default=None, help="blocks in the stack (default 20; 1 for nvfp4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cross-attn-kernel", action="store_true",
-                    help="use our own cross-attention softmax kernel instead of torch SDPA")
     ap.add_argument("--nccl-exchange", action="store_true",
                     help="seqpar: all-reduce the attention state with NCCL instead of the fused peer-memory kernel")
+    ap.add_argument("--measured-scaling", action="store_true",
+                    help="nvfp4: quantise every activation with its own measured maximum (two more passes per tensor) "
+                         "instead of in the kernel that produces it with the previous step's maximum")
+    ap.add_argument("--sdpa-cross-attn", action="store_true",
+                    help="use torch SDPA (the vendor flash kernel) for the cross-attention softmax core, for comparison")
     ap.add_argument("--no-seqpar", action="store_true",
                     help="stack workload: leave out the sequence-parallel sub-record (cfg 4 on the same GPUs)")
     ap.add_argument("--no-gpu-eager-baseline", action="store_true")
@@ -647,16 +652,16 @@ def main() -> None:
         stack = stack.to(device=dev, dtype=dt)
     for i, blk in enumerate(stack.blocks):
         blk.load_state_dict(synthetic.make_block_params_on_device(C, HID, i, 0.02, dt, dev), strict=True)
-    if args.cross_attn_kernel:
-        for blk in stack.blocks:
-            blk.cross_attn.softmax_core = "kernel"
     stack.set_sequence_shard(shard)
     fused_exchange = shard is not None and world > 1 and not args.nccl_exchange
     if fused_exchange:
         shard.device_steps = bool(args.graph)  # the exchange kernels number their own steps under graph replay
         shard.enable_fused_state_exchange(1, C // 32, dev)
         shard.enable_fused_halo_exchange(SEQPAR_GRID[2] * 2 * HID, dt, dev)
-    stack.set_nvfp4(nvfp4)
+    stack.set_nvfp4(nvfp4, delayed_scaling=nvfp4 and not args.measured_scaling, margin=1.0)
+    if args.sdpa_cross_attn:
+        for blk in stack.blocks:
+            blk.cross_attn.softmax_core = "sdpa"
 
     # host-resident inputs (pinned) for the end-to-end leg; device copies for the kernel leg
     g = torch.Generator().manual_seed(1234 + rank)
@@ -785,7 +790,10 @@ def main() -> None:
         ent[2] += f
     gemm_breakdown = {k: {"launches": v[0], "avg_ms": v[1] / v[0], "tflops": v[2] / (v[1] * 1e-3) / 1e12}
                       for k, v in by_shape.items()}
-    status = ops.take_gemm_device_status()
+    status = ops.take_gemm_device_status() | ops.take_gemm_nvfp4_device_status() | ops.take_cross_attention_device_status()
+    fp4_ms = sum(e0.elapsed_time(e1) for e0, e1, _, lab in ops.counters.gemm_events if lab.startswith("nvfp4"))
+    fp4_flops = sum(f for _, _, f, lab in ops.counters.gemm_events if lab.startswith("nvfp4"))
+    n_fp4 = sum(1 for ev in ops.counters.gemm_events if ev[3].startswith("nvfp4"))
 
     for _ in range(2):
         step_e2e()
@@ -811,14 +819,30 @@ def main() -> None:
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
         T_local = Bl * tokens
         roof_s = block_roofline_seconds(T_local, Bl, peaks, C) * depth
+        fp4_roofline = None
+        if nvfp4 and fp4_ms > 0:
+            lib = fp4_library_rate(T_local, 2 * HID, C)  # the vendor FP4 GEMM on the largest projection of the block
+            fp4_ach = fp4_flops / (fp4_ms * 1e-3) / 1e12
+            fp4_roofline = {"bound": "tensor", "kernel": "gemm_nvfp4_pair_kernel (tcgen05 cta_group::2, kind::mxf4nvf4, block 16)",
+                            "achieved": fp4_ach, "unit": "TFLOP/s", "launches": n_fp4, "avg_launch_ms": fp4_ms / n_fp4,
+                            "peak": lib.get("fp4_library_tflops"),
+                            "peak_source": ("measured in this run: torch._scaled_mm on float4_e2m1fn_x2 operands with E4M3 scales per "
+                                            f"16 (the vendor library's block-scaled FP4 GEMM), {T_local}x{2 * HID}x{C}")
+                            if "fp4_library_tflops" in lib else lib.get("fp4_library"),
+                            "frac": (fp4_ach / lib["fp4_library_tflops"]) if "fp4_library_tflops" in lib else None,
+                            "share_of_step": fp4_ms / (eager_ms or total_ms)}
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload, "parallelism": parallelism, "per_gpu_batch": Bl,
                        "l2": "inputs larger than L2 (>3 GB of weights and activations per step)",
-                       "cross_attention_core": ("own warp-MMA flash kernel" if args.cross_attn_kernel else
-                                                "torch SDPA / cuDNN flash (own kernel: --cross-attn-kernel)"),
+                       "cross_attention_core": ("torch SDPA (vendor flash kernel), for comparison" if args.sdpa_cross_attn else
+                                                "own tcgen05 kernel (sana_cross_attention); --sdpa-cross-attn times the vendor kernel"),
+                       "activation_scaling": (("per-tensor maximum measured on every call (two more passes per activation)"
+                                               if args.measured_scaling else
+                                               "delayed: FP4 written by the producing kernels with the previous step's maxima")
+                                              if nvfp4 else None),
                        "state_exchange": ("state all-reduce fused into the reduction kernel, conv halo rows pushed by one kernel, both "
                                           "over peer memory" if fused_exchange else
                                           ("NCCL all-reduce" if shard is not None and world > 1 else "none"))},
@@ -839,6 +863,7 @@ def main() -> None:
             "e2e": {"value": total_units / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": x_h.nbytes + y_h.nbytes + t_h.nbytes, "d2h_bytes_per_step": out_h.nbytes,
                     "ms_per_step": e2e_ms / args.steps},
+            "fp4_roofline": fp4_roofline,
             "gemm_breakdown": gemm_breakdown, "kernel_breakdown_ms_per_step": kernel_breakdown, "gpu_launches": launches,
             "gemm_device_status": status, "dwconv_device_status": dw_status,
             "state_exchange_status": sp_status[0], "halo_exchange_status": sp_status[1], "clocks": clk.summary(),

@@ -316,8 +316,9 @@ int sana_gemm_simt(const void* A, int64_t lda, const void* Wt, int64_t ldw, void
  * Format: E2M1 values {0, .5, 1, 1.5, 2, 3, 4, 6} with sign, two per byte (even K index in
  * the low nibble), one E4M3 scale per 16 consecutive K elements, one fp32 scale per tensor:
  *   x ~ code * block_scale * tensor_scale,  tensor_scale = amax / (6 * 448),
- *   block_scale = E4M3(block_amax / (6 * tensor_scale)),  code = E2M1(x / (block_scale * tensor_scale))
- * (round to nearest even, saturating).  Block scales are stored in 512-byte tiles of
+ *   block_scale = E4M3(block_amax * (1 / (6 * tensor_scale))),
+ *   code = E2M1(x * (1 / (block_scale * tensor_scale)))
+ * (reciprocals and products in fp32; every step rounds to nearest even, conversions saturate).  Block scales are stored in 512-byte tiles of
  * 128 rows x 4 blocks, byte (r % 32) * 16 + (r / 32) * 4 + b, tiles K-fastest with the K-tile
  * count padded to a multiple of 4 (sana_nvfp4_sf_bytes gives the buffer size).
  *
@@ -325,7 +326,9 @@ int sana_gemm_simt(const void* A, int64_t lda, const void* Wt, int64_t ldw, void
  *   tiles), scales[2] = {amax, tensor_scale} (device floats).  K % 32 == 0.  Three launches:
  *   absolute maximum, then quantise; nothing is read back to the host.
  * sana_gemm_nvfp4: out[M, N] bf16 = epilogue(a_scales[1] * w_scales[1] * Aq @ Wq^T) with the
- *   sana_gemm epilogue.  tcgen05.mma kind::mxf4nvf4 (block 16) with scales in tensor memory.
+ *   sana_gemm epilogue.  tcgen05.mma kind::mxf4nvf4 (block 16) with scales in tensor memory;
+ *   M >= 2048: CTA pairs (cta_group::2) on 256 x 256 tiles, else one CTA on 128 x 128 tiles
+ *   (sana_gemm_set_variant overrides the choice).
  */
 int64_t sana_nvfp4_sf_bytes(int64_t rows, int64_t K);
 int sana_nvfp4_quantize(const void* x, int64_t ld, void* q, void* sf, float* scales, int64_t rows, int64_t K,
@@ -334,6 +337,44 @@ int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_scales, cons
                     const float* w_scales, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
                     const sana_gemm_epilogue* ep, void* stream);
 int sana_gemm_nvfp4_take_device_status(int* status_out);
+
+/* ---------------------------------------------------------------------------------------
+ * Activations quantised where they are produced ("delayed scaling").  Upstream leaves the
+ * quantisation of a projection's input to Transformer Engine's te.Linear
+ * (inference_video_scripts/wm/inference_sana_wm.py:388-406), which measures the tensor's maximum
+ * and quantises in passes of its own; the exact per-tensor maximum of a tensor cannot be known
+ * while it is still being produced.  Here the producing kernel writes E2M1 codes and E4M3 block
+ * scales directly, with the per-tensor scale taken from a record that an EARLIER call has
+ * filled, and notes the largest magnitude it produces for the calls that follow:
+ *   state  n records of four device floats {amax in use, tensor scale in use, amax seen since
+ *          the last roll, unused}.  sana_nvfp4_scale_roll adopts "seen" x margin as the values
+ *          in use (records that saw nothing keep theirs).  A record doubles as the `scales`
+ *          argument of sana_gemm_nvfp4.  Values above the amax in use saturate, so the first
+ *          call on new data should be a measured one (sana_nvfp4_quantize) whose amax is copied
+ *          into the record.
+ *   scale_in = record (uses scale_in[1]);  amax_out = record + 2 (may be NULL).
+ * With the same amax the codes and block scales equal those of sana_nvfp4_quantize applied to
+ * the bf16 tensor bit for bit (the value is rounded to bf16 before it is quantised).
+ *   sana_ln_modulate_fp4   sana_ln_modulate (bf16) whose output goes to q / sf (K = C); z may be
+ *                          NULL (no bf16 copy).  C % 32 == 0.
+ *   sana_la_apply_fp4      sana_la_apply (bf16) whose output goes to fq / sf (K = H * 32); out may
+ *                          be NULL.
+ *   sana_dwconv_glu_amax   sana_dwconv_glu (bf16) that also raises *amax_out to max |out|.
+ *   sana_nvfp4_quantize_scaled   sana_nvfp4_quantize without the measuring pass: scales[0] holds
+ *                          the amax to scale for.
+ * sf buffers must be zero-filled once by their owner (bytes of padding rows / tiles are never
+ * written). */
+int sana_nvfp4_scale_roll(float* state, int64_t n, float margin, void* stream);
+int sana_nvfp4_quantize_scaled(const void* x, int64_t ld, void* q, void* sf, float* scales, int64_t rows, int64_t K,
+                               void* stream);
+int sana_ln_modulate_fp4(const void* x, const void* table, const void* t, void* z, void* q, void* sf,
+                         const float* scale_in, float* amax_out, int64_t B, int64_t N, int64_t C, int shift_row,
+                         int scale_row, float eps, void* stream);
+int sana_la_apply_fp4(const void* q, int64_t ldq, const float* state, void* out, int64_t ldo, void* fq, void* sf,
+                      const float* scale_in, float* amax_out, int64_t B, int64_t N, int64_t H, float eps, void* stream);
+int sana_dwconv_glu_amax(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
+                         const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
+                         int64_t hid, float* amax_out, void* stream);
 
 /* Soft-error word of the tensor-core GEMM: its bounded waits record a code here instead of
  * spinning forever.  Returns 0 when no wait ever timed out on the current device since the

@@ -598,26 +598,30 @@ def _round_to_e4m3(x: torch.Tensor) -> torch.Tensor:
     return x.clamp(max=E4M3_MAX).to(torch.float8_e4m3fn).to(torch.float32)
 
 
-def nvfp4_quantize(x: torch.Tensor):
-    """Quantise along the last dimension (length a multiple of 16).
+def nvfp4_quantize(x: torch.Tensor, amax: Optional[float] = None):
+    """Quantise along the last dimension (length a multiple of 16).  ``amax``: scale for this
+    maximum magnitude instead of the tensor's own (values beyond it saturate).
 
     Returns (codes_value fp32 on the E2M1 grid, block_scale fp32 holding E4M3 values
     [..., K/16], tensor_scale python float) with
     ``dequant = codes_value * block_scale[..., None] * tensor_scale``.
 
-    tensor_scale = amax / (6 * 448); block scale = E4M3(block_amax / (6 * tensor_scale))."""
+    tensor_scale = amax / (6 * 448); block scale = E4M3(block_amax * (1 / (6 * tensor_scale)));
+    code = E2M1(x * (1 / (block_scale * tensor_scale))) - reciprocals and products in fp32, rounded to
+    nearest, the formulation a device quantiser uses (one multiply per element instead of a division)."""
     xf = x.float()
     K = xf.shape[-1]
     assert K % 16 == 0
-    amax = xf.abs().max().clamp(min=1e-30)
-    ts = (amax / (E2M1_MAX * E4M3_MAX)).item()
+    amax = xf.abs().max().clamp(min=1e-30) if amax is None else torch.tensor(float(amax), dtype=torch.float32).clamp(min=1e-30)
+    ts32 = amax / torch.tensor(E2M1_MAX * E4M3_MAX, dtype=torch.float32)  # fp32 throughout, as on the device
+    inv6ts = 1.0 / (torch.tensor(E2M1_MAX, dtype=torch.float32) * ts32)
     blocks = xf.reshape(*xf.shape[:-1], K // 16, 16)
     bamax = blocks.abs().amax(dim=-1)
-    bs = _round_to_e4m3(bamax / (E2M1_MAX * ts))
-    denom = (bs * ts)[..., None]
-    scaled = torch.where(denom > 0, blocks / denom, torch.zeros_like(blocks))
-    vals = _round_to_e2m1(scaled)
-    return vals.reshape(xf.shape), bs, ts
+    bs = _round_to_e4m3(bamax * inv6ts)
+    denom = (bs * ts32)[..., None]
+    inv = torch.where(denom > 0, 1.0 / denom, torch.zeros_like(denom))
+    vals = _round_to_e2m1(blocks * inv)
+    return vals.reshape(xf.shape), bs, ts32.item()
 
 
 def nvfp4_dequantize(vals: torch.Tensor, bs: torch.Tensor, ts: float) -> torch.Tensor:

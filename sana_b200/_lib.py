@@ -75,6 +75,11 @@ SIGNATURES = {
     "sana_nvfp4_quantize": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
     "sana_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(GemmEpilogue), _vp]),
     "sana_gemm_nvfp4_take_device_status": (_i32, [C.POINTER(C.c_int)]),
+    "sana_nvfp4_scale_roll": (_i32, [_vp, _i64, _f32, _vp]),
+    "sana_nvfp4_quantize_scaled": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "sana_ln_modulate_fp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
+    "sana_la_apply_fp4": (_i32, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp]),
+    "sana_dwconv_glu_amax": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "sana_patchify": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_unpatchify": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_timestep_embedding": (_i32, [_vp, _vp, _i64, _i64, _f32, _i32, _vp]),

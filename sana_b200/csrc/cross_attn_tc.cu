@@ -7,38 +7,26 @@
 //                   swizzled, fetched by bulk-tensor copies of a 4-D view (channel, head, key, sample) so that
 //                   channels past the head and keys past L arrive as zeros; one Q tile; an output staging tile.
 //   tensor memory   S_A (keys [0, NA)) at column 0, S_B (keys [NA, LP)) at column 160, O at column 304.
-//   warps 0-7       softmax: lane = query row, two warps per row (warp w and w + 4 share tensor-memory lane
-//                   quadrant w) splitting the columns of a key chunk between them.  Pass 1: row maximum of the own
-//                   columns; the two warps exchange it through shared memory.  Pass 2: p = 2^(s c - m) as bf16
-//                   pairs, kept in registers until BOTH warps have read their scores, then written back over the
-//                   scores (the second product takes its A operand from tensor memory); row sums in fp32.
-//   warps 8-11      epilogue: O / row sum -> bf16 -> staging tile -> bulk-tensor store (rows past N are clipped).
-//   warp 12         bulk-tensor loads (Q per tile, K / V and the mask bias per (sample, head)).
-//   warp 13         one thread issues every tcgen05.mma: S_A, S_B = Q K^T, then O = P_A V_A + P_B V_B.
+//   warps 0-3       softmax: lane = query row.  Row maximum of a key chunk, p = 2^(s c - m), written back over S
+//                   as bf16 pairs (the second product takes its A operand from tensor memory), row sum in fp32.
+//   warps 4-7       epilogue: O / row sum -> bf16 -> staging tile -> bulk-tensor store (rows past N are clipped).
+//   warp 8          bulk-tensor loads (Q per tile, K / V and the mask bias per (sample, head)).
+//   warp 9          one thread issues every tcgen05.mma: S_A, S_B = Q K^T, then O = P_A V_A + P_B V_B.
 // The two key chunks make the pipeline: while the softmax warps work on chunk B of tile i the tensor core runs
 // P_A V_A of tile i and S_A of tile i+1, and while they work on chunk A of tile i+1 it runs P_B V_B of tile i and
-// S_B of tile i+1.  Chunk A fixes the shift m of a row (its exact maximum); chunk B keeps it unless its own
-// maximum exceeds it by more than 2^8, in which case the warps wait for P_A V_A and rescale O in tensor memory
-// (exact either way: softmax is invariant to the shift, and p <= 256 is harmless in bf16 and in the fp32
-// accumulator).  One warp per scheduler could not issue fast enough (about 6 cycles per instruction measured, the
-// special-function unit a quarter busy); two warps per scheduler on the same tile nearly halve the softmax time.
+// S_B of tile i+1.  Chunk A fixes the shift m of a row; chunk B keeps it unless its own maximum exceeds it by
+// more than 2^8, in which case the warp waits for P_A V_A and rescales O in tensor memory (exact either way:
+// softmax is invariant to the shift, and p <= 256 is harmless in bf16 and in the fp32 accumulator).
+// Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 91 us per sample.  The 33 tcgen05.mma of a tile
+// alone take about 4 500 cycles - an instruction with M = 128 costs about 130 cycles whether N is 112 or 256 -
+// and the softmax warps about 8 000; a single-pass softmax with the shift fixed up on the fly and a split of a
+// row's columns over two warps were both tried and were slower (110 - 120 us).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
 #include "tc_common.cuh"
 
 namespace sana {
 
 __device__ int g_cax_status = 0;
-
-// Optional cycle accounting of the roles (compiled in with -DSANA_CX_PROFILE, for tuning only): sums over all
-// CTAs of the cycles one thread of each role spent in its waits and in its work.
-#ifdef SANA_CX_PROFILE
-__device__ unsigned long long g_cax_prof[16];
-#define CX_T0() const long long cx_t0__ = clock64()
-#define CX_ACC(slot, on) do { if (on) atomicAdd(&g_cax_prof[slot], (unsigned long long)(clock64() - cx_t0__)); } while (0)
-#else
-#define CX_T0() do { } while (0)
-#define CX_ACC(slot, on) do { } while (0)
-#endif
 
 constexpr int CX_LP_MAX = 304;                       // keys, padded to a multiple of 16
 constexpr int CX_KV_BLK = CX_LP_MAX * 128;           // one 64-channel block of K or V (38 912 bytes)
@@ -48,12 +36,10 @@ constexpr int CX_OFF_V = CX_OFF_K + 2 * CX_KV_BLK;
 constexpr int CX_OFF_Q = CX_OFF_V + 2 * CX_KV_BLK;
 constexpr int CX_OFF_O = CX_OFF_Q + 2 * CX_Q_BLK;    // staging: [warp][block][32 rows][128 bytes]
 constexpr int CX_OFF_BIAS = CX_OFF_O + 2 * CX_Q_BLK;
-constexpr int CX_OFF_L = CX_OFF_BIAS + CX_LP_MAX * 4;  // row sums, [tile parity][column half][128] floats
-constexpr int CX_OFF_M = CX_OFF_L + 2 * 2 * 128 * 4;   // row maxima exchanged between the two warps of a row, [2][128]
-constexpr int CX_OFF_CTRL = CX_OFF_M + 2 * 128 * 4;
+constexpr int CX_OFF_L = CX_OFF_BIAS + CX_LP_MAX * 4;  // row sums, [2][128] floats
+constexpr int CX_OFF_CTRL = CX_OFF_L + 2 * 128 * 4;
 constexpr int CX_SMEM = CX_OFF_CTRL + 128;
-constexpr int CX_THREADS = 512;  // four warpgroups: 2 x softmax, epilogue, {loads, MMA, two idle warps}
-constexpr int CX_W_EPI = 8, CX_W_LOAD = 12, CX_W_MMA = 13;  // first epilogue warp, load warp, MMA warp
+constexpr int CX_THREADS = 320;
 constexpr uint32_t CX_COL_SB = 160, CX_COL_O = 304;
 static_assert(CX_SMEM <= 232448, "shared memory budget");
 static_assert(CX_KV_BLK % 1024 == 0 && CX_OFF_Q % 1024 == 0 && CX_OFF_O % 1024 == 0, "swizzled tiles need 1024-byte bases");
@@ -102,13 +88,9 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float cx_exp2(float x) {
-#if defined(CX_VAR) && CX_VAR == 1
-  return fmaf(x, 0.001f, 1.0f);
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 // MN-major, 128-byte-swizzled operand (V: keys are the contraction index, channels contiguous): bits 0-13 address
 // >> 4, 16-29 byte offset between 64-channel blocks (>> 4), 32-45 byte offset between 8-key groups (1024 >> 4),
@@ -119,9 +101,8 @@ __device__ __forceinline__ uint64_t cx_desc_mn(uint32_t saddr, uint32_t block_st
   return ((uint64_t)hi << 32) | lo;
 }
 
-// ---- softmax of one key chunk: two passes, the columns split between the two warps of a row --------------
-// One group of 16 scores (columns jb .. jb + 15 of the key axis) folded into four running maxima, in the scaled
-// domain t = s * c + bias[j]; columns j >= lvalid (padding) are left out.
+// One group of 16 scores of this lane's row (columns jb .. jb + 15 of the key axis) folded into the running maximum,
+// in the scaled domain t = s * c + bias[j]; columns j >= lvalid (padding) are left out.
 template <bool MASK>
 __device__ __forceinline__ void cx_max16(const uint32_t (&cur)[16], float (&mx)[4], int jb, int lvalid, float c, const float* bias) {
   if (jb + 16 <= lvalid) {
@@ -139,33 +120,33 @@ __device__ __forceinline__ void cx_max16(const uint32_t (&cur)[16], float (&mx)[
   }
 }
 
-// Row maximum of groups [g0, g1) of 16 scores of the chunk at tensor-memory address `taddr`; two register sets in
-// ping-pong so that the next group's load is in flight while this one is reduced.  -inf when the range is empty
-// or holds padding only.
+// Row maximum of `ncols` scores (a multiple of 16) starting at tensor-memory address `taddr`; two register sets
+// in ping-pong so that the next group's load is in flight while this one is reduced, four running maxima so that
+// the comparisons do not form one long dependent chain.
 template <bool MASK>
-__device__ __forceinline__ float cx_half_max(uint32_t taddr, int g0, int g1, int j0, int lvalid, float c, const float* bias) {
+__device__ __forceinline__ float cx_row_max(uint32_t taddr, int ncols, int j0, int lvalid, float c, const float* bias) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-  if (g0 < g1) {
-    uint32_t r0[16], r1[16];
-    tmem_ld_32x16(taddr + 16u * (uint32_t)g0, r0);
-    for (int g = g0; g < g1; g += 2) {
+  uint32_t r0[16], r1[16];
+  tmem_ld_32x16(taddr, r0);
+  const int groups = ncols >> 4;
+  for (int g = 0; g < groups; g += 2) {
+    tmem_ld_wait();
+    if (g + 1 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
+    cx_max16<MASK>(r0, mx, j0 + 16 * g, lvalid, c, bias);
+    if (g + 1 < groups) {
       tmem_ld_wait();
-      if (g + 1 < g1) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
-      cx_max16<MASK>(r0, mx, j0 + 16 * g, lvalid, c, bias);
-      if (g + 1 < g1) {
-        tmem_ld_wait();
-        if (g + 2 < g1) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
-        cx_max16<MASK>(r1, mx, j0 + 16 * (g + 1), lvalid, c, bias);
-      }
+      if (g + 2 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
+      cx_max16<MASK>(r1, mx, j0 + 16 * (g + 1), lvalid, c, bias);
     }
   }
   const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
   return MASK ? m : m * c;  // c > 0
 }
 
-// p = 2^(t - m) for one group of 16 scores as 8 words of bf16 pairs; two partial row sums are updated.
+// p = 2^(t - m) for one group of 16 scores, written over the scores as 8 columns of bf16 pairs at `pdst`; the
+// two partial row sums are updated.
 template <bool MASK>
-__device__ __forceinline__ void cx_exp16(const uint32_t (&cur)[16], uint32_t (&pk)[8], int jb, int lvalid, float c, float nm,
+__device__ __forceinline__ void cx_exp16(const uint32_t (&cur)[16], uint32_t pdst, int jb, int lvalid, float c, float nm,
                                          const float* bias, float& sum0, float& sum1) {
   float p[16];
   if (jb + 16 <= lvalid) {
@@ -182,61 +163,36 @@ __device__ __forceinline__ void cx_exp16(const uint32_t (&cur)[16], uint32_t (&p
       p[e] = (jb + e < lvalid) ? cx_exp2(t) : 0.f;
     }
   }
+  uint32_t pk[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     pk[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
     sum0 += p[2 * e];
     sum1 += p[2 * e + 1];
   }
+  tmem_st_32x8(pdst, pk);
 }
 
-constexpr int CX_HALF_GROUPS = 5;  // a warp owns at most 5 groups of 16 columns of a chunk (chunks are <= 160 wide)
-
-// Exponentials of groups [g0, g1) of the chunk into registers (pk[g - g0]); returns the row sum of this range.
+// The same walk for the exponentials.  Group g's probabilities land on columns 8g .. 8g+7 of the chunk, whose
+// scores were consumed by an earlier group (or are already in registers); the group in flight lies above them.
 template <bool MASK>
-__device__ __forceinline__ float cx_half_exp(uint32_t taddr, int g0, int g1, int j0, int lvalid, float c, float m,
-                                             const float* bias, uint32_t (&pk)[CX_HALF_GROUPS][8]) {
+__device__ __forceinline__ float cx_row_exp(uint32_t taddr, int ncols, int j0, int lvalid, float c, float m, const float* bias) {
   float sum0 = 0.f, sum1 = 0.f;
+  uint32_t r0[16], r1[16];
+  tmem_ld_32x16(taddr, r0);
+  const int groups = ncols >> 4;
   const float nm = -m;
-  if (g0 < g1) {
-    uint32_t r0[16], r1[16];
-    tmem_ld_32x16(taddr + 16u * (uint32_t)g0, r0);
-#pragma unroll
-    for (int i = 0; i < CX_HALF_GROUPS; i += 2) {
-      const int g = g0 + i;
-      if (g < g1) {
-        tmem_ld_wait();
-        if (g + 1 < g1) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
-        cx_exp16<MASK>(r0, pk[i], j0 + 16 * g, lvalid, c, nm, bias, sum0, sum1);
-        if (i + 1 < CX_HALF_GROUPS && g + 1 < g1) {
-          tmem_ld_wait();
-          if (g + 2 < g1) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
-          cx_exp16<MASK>(r1, pk[i + 1 < CX_HALF_GROUPS ? i + 1 : i], j0 + 16 * (g + 1), lvalid, c, nm, bias, sum0, sum1);
-        }
-      }
+  for (int g = 0; g < groups; g += 2) {
+    tmem_ld_wait();
+    if (g + 1 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 1), r1);
+    cx_exp16<MASK>(r0, taddr + 8u * (uint32_t)g, j0 + 16 * g, lvalid, c, nm, bias, sum0, sum1);
+    if (g + 1 < groups) {
+      tmem_ld_wait();
+      if (g + 2 < groups) tmem_ld_32x16(taddr + 16u * (uint32_t)(g + 2), r0);
+      cx_exp16<MASK>(r1, taddr + 8u * (uint32_t)(g + 1), j0 + 16 * (g + 1), lvalid, c, nm, bias, sum0, sum1);
     }
   }
   return sum0 + sum1;
-}
-
-// The probabilities of groups [g0, g1) go back over the chunk's scores: group g lands on columns 8g .. 8g + 7.
-__device__ __forceinline__ void cx_half_store(uint32_t taddr, int g0, int g1, const uint32_t (&pk)[CX_HALF_GROUPS][8]) {
-#pragma unroll
-  for (int i = 0; i < CX_HALF_GROUPS; ++i)
-    if (g0 + i < g1) tmem_st_32x8(taddr + 8u * (uint32_t)(g0 + i), pk[i]);
-}
-
-// named barrier of the two softmax warps that share a row (64 threads); ids 1..4, 0 is __syncthreads
-__device__ __forceinline__ void cx_pair_sync(int quad) {
-  asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
-}
-
-// One lane waits on the barrier, the warp follows (thirty-two pollers would take issue slots from the warps
-// that share the scheduler).
-__device__ __forceinline__ bool cx_warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int lane) {
-  int ok = 1;
-  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, code, &g_cax_status) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 template <bool MASK>
@@ -274,8 +230,8 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_q_free, 1);
     mbar_init(bar_sa, 1);
     mbar_init(bar_sb, 1);
-    mbar_init(bar_pa, 8);
-    mbar_init(bar_pb, 8);
+    mbar_init(bar_pa, 4);
+    mbar_init(bar_pb, 4);
     mbar_init(bar_pva, 1);
     mbar_init(bar_o_full, 1);
     mbar_init(bar_o_free, 4);
@@ -286,7 +242,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmV) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO) : "memory");
   }
-  if (warp == CX_W_MMA) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ctrl + 96), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -294,147 +250,64 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // The kernel starts with 128 registers per thread (512 threads fill the register file); the softmax
-  // warpgroups, which hold a half chunk of probabilities in registers, take over what the others release.
-  if (warp < CX_W_EPI) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
-  } else if (warp < CX_W_LOAD) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-  } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  }
 
-  if (warp < CX_W_EPI) {
+  if (warp < 4) {
     // ------------------------------------------------------------------ softmax warps
-    const int quad = warp & 3, half = warp >> 2;  // lane quadrant; which part of a chunk's columns
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int row = warp * 32 + lane;
     const float c = a.scale_log2e;
-    float* mbuf = reinterpret_cast<float*>(smem + CX_OFF_M);
-    // column groups (of 16) of the two chunks: the lower warp takes the first ceil(n / 2) groups
-    const int ga = a.NA >> 4, gb = a.NB >> 4;
-    const int a0 = half ? (ga + 1) >> 1 : 0, a1 = half ? ga : (ga + 1) >> 1;
-    const int b0 = half ? (gb + 1) >> 1 : 0, b1 = half ? gb : (gb + 1) >> 1;
-    const int og = a.HDN >> 4;  // groups of 16 columns of O; split the same way for the rescale
-    const int o0 = half ? (og + 1) >> 1 : 0, o1 = half ? og : (og + 1) >> 1;
     uint32_t ph_sa = 0, ph_sb = 0, ph_kv = 0;
     int prev_bh = -1;
     bool ok = true;
     for (int it = 0; it < n_items && ok; ++it) {
       const int bh = (int)((t_begin + it) / a.nqt);
       if (MASK && bh != prev_bh) {  // the bias vector of this sample is in shared memory once K / V have been requested
-        if (!cx_warp_wait(bar_kv_full, ph_kv, abort_flag, 11, lane)) { ok = false; break; }
+        if (!mbar_wait(bar_kv_full, ph_kv, abort_flag, 11, &g_cax_status)) { ok = false; break; }
       }
       if (bh != prev_bh) ph_kv ^= 1u;
       prev_bh = bh;
-      uint32_t pk[CX_HALF_GROUPS][8];
-      // ---- chunk A: its exact maximum is the shift of the row
-      {
-        CX_T0();
-        if (!cx_warp_wait(bar_sa, ph_sa, abort_flag, 12, lane)) { ok = false; break; }
-        CX_ACC(0, tid == 0);
-      }
+      // ---- chunk A: fixes the shift of the row
+      if (!mbar_wait(bar_sa, ph_sa, abort_flag, 12, &g_cax_status)) { ok = false; break; }
       ph_sa ^= 1u;
       tcgen05_fence_after();
-      float m, l;
-      {
-        CX_T0();
-#ifdef SANA_CX_PROFILE
-        const long long q0 = clock64();
-#endif
-#if defined(CX_VAR) && CX_VAR == 6
-        const float mine = 0.f;
-#else
-        const float mine = cx_half_max<MASK>(lane_addr, a0, a1, 0, a.L, c, bias);
-#endif
-#ifdef SANA_CX_PROFILE
-        const long long q1 = clock64();
-#endif
-        mbuf[half * 128 + row] = mine;
-        cx_pair_sync(quad);
-        m = fmaxf(mine, mbuf[(half ^ 1) * 128 + row]);
-#ifdef SANA_CX_PROFILE
-        const long long q2 = clock64();
-#endif
-#if defined(CX_VAR) && CX_VAR == 6
-        l = 1.f;
-#else
-        l = cx_half_exp<MASK>(lane_addr, a0, a1, 0, a.L, c, m, bias, pk);
-#endif
-#ifdef SANA_CX_PROFILE
-        const long long q3 = clock64();
-#endif
-        cx_pair_sync(quad);  // both warps have read their scores (and the exchanged maxima): the columns may be overwritten
-#if !(defined(CX_VAR) && CX_VAR == 6)
-        cx_half_store(lane_addr, a0, a1, pk);
-#endif
-        tmem_st_wait();
-#ifdef SANA_CX_PROFILE
-        if (tid == 0) {
-          atomicAdd(&g_cax_prof[13], (unsigned long long)(q1 - q0));
-          atomicAdd(&g_cax_prof[14], (unsigned long long)(q3 - q2));
-          atomicAdd(&g_cax_prof[15], (unsigned long long)((q2 - q1) + (clock64() - q3)));
-        }
-#endif
-        CX_ACC(1, tid == 0);
-      }
+      float m = cx_row_max<MASK>(lane_addr, a.NA, 0, a.L, c, bias);
+      float l = cx_row_exp<MASK>(lane_addr, a.NA, 0, a.L, c, m, bias);
+      tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pa);
       // ---- chunk B: same shift unless its maximum is more than 2^8 above it
-      {
-        CX_T0();
-        if (!cx_warp_wait(bar_sb, ph_sb, abort_flag, 13, lane)) { ok = false; break; }
-        CX_ACC(2, tid == 0);
-      }
+      if (!mbar_wait(bar_sb, ph_sb, abort_flag, 13, &g_cax_status)) { ok = false; break; }
       ph_sb ^= 1u;
       tcgen05_fence_after();
-      {
-        CX_T0();
-#if defined(CX_VAR) && CX_VAR == 6
-        const float mine = 0.f;
-#else
-        const float mine = cx_half_max<MASK>(lane_addr + CX_COL_SB, b0, b1, a.NA, a.L, c, bias);
-#endif
-        mbuf[half * 128 + row] = mine;
-        cx_pair_sync(quad);
-        const float mb = fmaxf(mine, mbuf[(half ^ 1) * 128 + row]);
-        // both warps of a row see the same m and mb, so they take this branch together
-        if (__any_sync(0xffffffffu, mb > m + 8.0f)) {
-          // rare: rescale what chunk A has accumulated.  P_A V_A of this tile must have finished.
-          if (!cx_warp_wait(bar_pva, (uint32_t)(it & 1), abort_flag, 14, lane)) { ok = false; break; }
-          tcgen05_fence_after();
-          const float m_new = fmaxf(m, mb);
-          const float alpha = cx_exp2(m - m_new);
-          for (int g = o0; g < o1; ++g) {
-            uint32_t o[16];
-            tmem_ld_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
-            tmem_ld_wait();
+      const float mb = cx_row_max<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, bias);
+      if (__any_sync(0xffffffffu, mb > m + 8.0f)) {
+        // rare: rescale what chunk A has accumulated.  P_A V_A of this tile must have finished.
+        if (!mbar_wait(bar_pva, (uint32_t)(it & 1), abort_flag, 14, &g_cax_status)) { ok = false; break; }
+        tcgen05_fence_after();
+        const float m_new = fmaxf(m, mb);
+        const float alpha = cx_exp2(m - m_new);
+        for (int g = 0; g < (a.HDN >> 4); ++g) {
+          uint32_t o[16];
+          tmem_ld_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
-          }
-          l *= alpha;
-          m = m_new;
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
         }
-#if !(defined(CX_VAR) && CX_VAR == 6)
-        l += cx_half_exp<MASK>(lane_addr + CX_COL_SB, b0, b1, a.NA, a.L, c, m, bias, pk);
-#endif
-        lbuf[((it & 1) * 2 + half) * 128 + row] = l;
-        cx_pair_sync(quad);
-#if !(defined(CX_VAR) && CX_VAR == 6)
-        cx_half_store(lane_addr + CX_COL_SB, b0, b1, pk);
-#endif
-        tmem_st_wait();
-        CX_ACC(3, tid == 0);
+        l *= alpha;
+        m = m_new;
       }
+      l += cx_row_exp<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, m, bias);
+      lbuf[(it & 1) * 128 + row] = l;
+      tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pb);
     }
-  } else if (warp < CX_W_LOAD) {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ epilogue warps
-    const int quad = warp - CX_W_EPI;
+    const int quad = warp - 4;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + CX_COL_O;
     const int row = quad * 32 + lane;
     unsigned char* stage_row = smem + CX_OFF_O + quad * (2 * 4096) + lane * 128;  // this lane's row of block 0
@@ -446,19 +319,16 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int64_t item = t_begin + it;
       const int bh = (int)(item / a.nqt), qt = (int)(item - (int64_t)bh * a.nqt);
       const int b = bh / a.heads, h = bh - b * a.heads;
-      {
-        CX_T0();
-        if (!cx_warp_wait(bar_o_full, ph_o, abort_flag, 15, lane)) { ok = false; break; }
-        CX_ACC(10, tid == 32 * CX_W_EPI);
-      }
+      if (!mbar_wait(bar_o_full, ph_o, abort_flag, 15, &g_cax_status)) { ok = false; break; }
       ph_o ^= 1u;
-      CX_T0();
       tcgen05_fence_after();
-      const float inv = 1.0f / (lbuf[((it & 1) * 2) * 128 + row] + lbuf[((it & 1) * 2 + 1) * 128 + row]);
+      const float inv = 1.0f / lbuf[(it & 1) * 128 + row];
       if (lane == 0) bulk_wait_read_all();  // the previous tile's stores have read the staging rows
       __syncwarp();
-      const int groups = a.HDN >> 4;
-      auto emit = [&](const uint32_t (&o)[16], int g) {
+      for (int g = 0; g < (a.HDN >> 4); ++g) {
+        uint32_t o[16];
+        tmem_ld_32x16(lane_addr + 16u * (uint32_t)g, o);
+        tmem_ld_wait();
         const int blk = g >> 2, cc = g & 3;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
@@ -467,18 +337,6 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(o[8 * hh + e]) * inv;
           uint4* slot = reinterpret_cast<uint4*>(stage_row + blk * 4096 + ((((uint32_t)(2 * cc + hh)) ^ swz) << 4));
           *slot = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        }
-      };
-      uint32_t o0[16], o1[16];
-      tmem_ld_32x16(lane_addr, o0);
-      for (int g = 0; g < groups; g += 2) {
-        tmem_ld_wait();
-        if (g + 1 < groups) tmem_ld_32x16(lane_addr + 16u * (uint32_t)(g + 1), o1);
-        emit(o0, g);
-        if (g + 1 < groups) {
-          tmem_ld_wait();
-          if (g + 2 < groups) tmem_ld_32x16(lane_addr + 16u * (uint32_t)(g + 2), o0);
-          emit(o1, g + 1);
         }
       }
       tcgen05_fence_before();
@@ -492,10 +350,9 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           bulk_commit();
         }
       }
-      CX_ACC(11, tid == 32 * CX_W_EPI);
     }
     if (lane == 0) bulk_wait_all();
-  } else if (warp == CX_W_LOAD) {
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ loads
     uint32_t ph_qfree = 0, ph_kvfree = 0;
     int prev_bh = -1;
@@ -506,9 +363,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int bh = (int)(item / a.nqt), qt = (int)(item - (int64_t)bh * a.nqt);
       const int b = bh / a.heads, h = bh - b * a.heads;
       if (it > 0) {
-        CX_T0();
-        if (!cx_warp_wait(bar_q_free, ph_qfree, abort_flag, 16, lane)) { ok = false; break; }
-        CX_ACC(12, lane == 0);
+        if (!mbar_wait(bar_q_free, ph_qfree, abort_flag, 16, &g_cax_status)) { ok = false; break; }
         ph_qfree ^= 1u;
       }
       if (lane == 0) {
@@ -517,7 +372,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       if (bh != prev_bh) {
         if (prev_bh >= 0) {  // every product that reads the previous K / V (and every reader of the bias) is done
-          if (!cx_warp_wait(bar_kv_free, ph_kvfree, abort_flag, 17, lane)) { ok = false; break; }
+          if (!mbar_wait(bar_kv_free, ph_kvfree, abort_flag, 17, &g_cax_status)) { ok = false; break; }
           ph_kvfree ^= 1u;
         }
         if (MASK) {
@@ -538,8 +393,8 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         prev_bh = bh;
       }
     }
-  } else if (warp == CX_W_MMA && lane == 0) {
-    // ------------------------------------------------------------------ tensor-core issue (one thread)
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ tensor-core issue (warp 9, one thread)
     // D = f32 (bit 4), A = B = bf16 (bits 7, 10), N >> 3 at 17, M = 128 (>> 4) at 24; bit 16: B is MN-major
     const uint32_t idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 4) << 24);
     const uint32_t idesc_sa = idesc_base | ((uint32_t)(a.NA >> 3) << 17);
@@ -551,9 +406,6 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     auto issue_s = [&](bool chunk_b) {
       const uint32_t kbase = K_u + (chunk_b ? (uint32_t)a.NA * 128u : 0u);
       const uint32_t d = tmem_base + (chunk_b ? CX_COL_SB : 0u);
-#if defined(CX_VAR) && CX_VAR == 7
-      if (n_items >= 0) return;
-#endif
       for (int ks = 0; ks < ksteps; ++ks) {
         const uint64_t adesc = make_smem_desc(Q_u + (uint32_t)((ks >> 2) * CX_Q_BLK + (ks & 3) * 32));
         const uint64_t bdesc = make_smem_desc(kbase + (uint32_t)((ks >> 2) * CX_KV_BLK + (ks & 3) * 32));
@@ -564,25 +416,17 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int ks_n = (chunk_b ? a.NB : a.NA) >> 4;
       const uint32_t p_tmem = tmem_base + (chunk_b ? CX_COL_SB : 0u);
       const uint64_t bdesc = cx_desc_mn(V_u + (chunk_b ? (uint32_t)a.NA * 128u : 0u), (uint32_t)CX_KV_BLK);
-#if defined(CX_VAR) && CX_VAR == 7
-      if (n_items >= 0) return;
-#endif
       for (int ks = 0; ks < ks_n; ++ks)
         umma_bf16_ts(tmem_base + CX_COL_O, p_tmem + 8u * (uint32_t)ks, bdesc + (uint64_t)(128 * ks), idesc_o,
                      (chunk_b || ks != 0) ? 1u : 0u);
     };
-#ifdef SANA_CX_PROFILE
-    const long long cx_loop0 = clock64();
-#endif
     for (int it = 0; it < n_items && ok; ++it) {
       const int bh = (int)((t_begin + it) / a.nqt);
       if (bh != prev_bh) {  // the pipeline was drained: start it again on the new K / V
-        CX_T0();
         if (!mbar_wait(bar_kv_full, ph_kv, abort_flag, 1, &g_cax_status)) { ok = false; break; }
         ph_kv ^= 1u;
         if (!mbar_wait(bar_q_full, ph_q, abort_flag, 2, &g_cax_status)) { ok = false; break; }
         ph_q ^= 1u;
-        CX_ACC(4, true);
         tcgen05_fence_after();
         issue_s(false);
         umma_commit(bar_sa);
@@ -592,35 +436,23 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         prev_bh = bh;
       }
       const bool next_same = it + 1 < n_items && (int)((t_begin + it + 1) / a.nqt) == bh;
-      {
-        CX_T0();
-        if (!mbar_wait(bar_pa, ph_pa, abort_flag, 3, &g_cax_status)) { ok = false; break; }
-        CX_ACC(5, true);
-      }
+      if (!mbar_wait(bar_pa, ph_pa, abort_flag, 3, &g_cax_status)) { ok = false; break; }
       ph_pa ^= 1u;
       if (it > 0) {
-        CX_T0();
         if (!mbar_wait(bar_o_free, ph_ofree, abort_flag, 4, &g_cax_status)) { ok = false; break; }
         ph_ofree ^= 1u;
-        CX_ACC(6, true);
       }
       tcgen05_fence_after();
       issue_pv(false);
       umma_commit(bar_pva);
       if (next_same) {
-        CX_T0();
         if (!mbar_wait(bar_q_full, ph_q, abort_flag, 5, &g_cax_status)) { ok = false; break; }
         ph_q ^= 1u;
-        CX_ACC(7, true);
         tcgen05_fence_after();
         issue_s(false);
         umma_commit(bar_sa);
       }
-      {
-        CX_T0();
-        if (!mbar_wait(bar_pb, ph_pb, abort_flag, 6, &g_cax_status)) { ok = false; break; }
-        CX_ACC(8, true);
-      }
+      if (!mbar_wait(bar_pb, ph_pb, abort_flag, 6, &g_cax_status)) { ok = false; break; }
       ph_pb ^= 1u;
       tcgen05_fence_after();
       issue_pv(true);
@@ -633,16 +465,13 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(bar_kv_free);
       }
     }
-#ifdef SANA_CX_PROFILE
-    atomicAdd(&g_cax_prof[9], (unsigned long long)(clock64() - cx_loop0));
-#endif
   }
 
   // ---------------------------------------------------------------------- teardown
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == CX_W_MMA) {
+  if (warp == 9) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
@@ -698,19 +527,6 @@ int cross_attn_tc_launch(const void* q, int64_t ldq, const void* k, const void* 
   SANA_LAUNCH_CHECK("cross_attn_tc kernel");
   return SANA_OK;
 }
-
-#ifdef SANA_CX_PROFILE
-extern "C" int sana_debug_cax_prof(unsigned long long* out16, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out16, g_cax_prof, 16 * sizeof(unsigned long long));
-  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_cax_prof)");
-  if (reset) {
-    unsigned long long zero[16] = {};
-    e = cudaMemcpyToSymbol(g_cax_prof, zero, sizeof(zero));
-    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_cax_prof)");
-  }
-  return SANA_OK;
-}
-#endif
 
 int cross_attn_tc_take_status(int* v) {
   cudaError_t e = cudaMemcpyFromSymbol(v, g_cax_status, sizeof(int));

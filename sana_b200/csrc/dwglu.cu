@@ -61,6 +61,7 @@ struct DwArgs {
   __nv_bfloat16* out;
   int rows, W, H, hid, seg_rows;
   int64_t row0;
+  float* amax_out;  // when set: atomically raised to the largest |output| (as stored, bf16)
 };
 
 // packed fp32x2 helpers on 64-bit registers (one instruction per two lanes of math)
@@ -245,11 +246,13 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU3, const __grid_co
 #pragma unroll
     for (int xo = 0; xo < 2; ++xo) a[xo][0] = bv[0], a[xo][1] = bv[1];
   };
+  uint32_t amax_bits = 0u;  // running maximum of |output| per 16-bit half (bf16 bit patterns order like integers)
   auto emit = [&](const u64 (&a)[2][2]) {
     const uint32_t o0 = glu_pair(a[0][0], a[0][1]);
     const uint32_t o1 = glu_pair(a[1][0], a[1][1]);
     if (ok0) *reinterpret_cast<uint32_t*>(out0) = o0;
     if (ok1) *reinterpret_cast<uint32_t*>(out1) = o1;
+    amax_bits = __vmaxu2(amax_bits, __vmaxu2(ok0 ? (o0 & 0x7fff7fffu) : 0u, ok1 ? (o1 & 0x7fff7fffu) : 0u));
   };
   auto advance = [&]() {
     out0 += out_step;
@@ -324,6 +327,12 @@ dwconv_glu_bf16_kernel(const __grid_constant__ CUtensorMap tmU3, const __grid_co
     if (lane == 0) refill(k + DW_STAGES, slot);
     if (++slot == DW_SLOTS) slot = 0, par ^= 1u;
   }
+  if (p.amax_out != nullptr) {
+    float m = fmaxf(bf16_lo(amax_bits), bf16_hi(amax_bits));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax_out), __float_as_uint(m));  // m >= 0
+  }
 }
 
 // Plain fp32 version (parity path): one thread per (row, x, channel pair value/gate).
@@ -363,10 +372,11 @@ __global__ void dwconv_glu_f32_kernel(const float* __restrict__ u, const float* 
 
 using namespace sana;
 
-extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
-                               const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
-                               int64_t hid, int dtype, void* stream) {
+static int dwconv_glu_impl(const void* u, const void* halo_top, const void* halo_bot, const void* weight, const void* bias,
+                           void* out, int64_t rows, int64_t W, int64_t H, int64_t row0, int64_t hid, int dtype,
+                           float* amax_out, void* stream) {
   SANA_REQUIRE(u && weight && out, "sana_dwconv_glu: null pointer");
+  SANA_REQUIRE(!amax_out || dtype == SANA_BF16, "sana_dwconv_glu_amax: bf16 only");
   SANA_REQUIRE(rows > 0 && W > 0 && H > 0 && hid > 0 && row0 >= 0, "sana_dwconv_glu: sizes must be positive");
   SANA_REQUIRE(hid % 8 == 0, "sana_dwconv_glu: hid must be a multiple of 8");
   SANA_REQUIRE(rows < (1 << 24) && W < (1 << 20) && hid < (1 << 20), "sana_dwconv_glu: size out of range");
@@ -382,6 +392,7 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
     a.bias = static_cast<const __nv_bfloat16*>(bias);
     a.out = static_cast<__nv_bfloat16*>(out);
     a.rows = (int)rows, a.W = (int)W, a.H = (int)H, a.hid = (int)hid, a.row0 = row0;
+    a.amax_out = amax_out;
     // u as a 4-D tensor {channel, value/gate, x, row}; a box is 64 channels x 2 groups x 4 pixels of one row
     CUtensorMap tmU3, tmU, tmTop, tmBot;
     const uint64_t strides[3] = {(uint64_t)hid * 2, (uint64_t)hid * 4, (uint64_t)W * hid * 4};
@@ -435,6 +446,19 @@ extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* 
   }
   SANA_LAUNCH_CHECK("dwconv_glu kernel");
   return SANA_OK;
+}
+
+extern "C" int sana_dwconv_glu(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
+                               const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
+                               int64_t hid, int dtype, void* stream) {
+  return dwconv_glu_impl(u, halo_top, halo_bot, weight, bias, out, rows, W, H, row0, hid, dtype, nullptr, stream);
+}
+
+extern "C" int sana_dwconv_glu_amax(const void* u, const void* halo_top, const void* halo_bot, const void* weight,
+                                    const void* bias, void* out, int64_t rows, int64_t W, int64_t H, int64_t row0,
+                                    int64_t hid, float* amax_out, void* stream) {
+  SANA_REQUIRE(amax_out, "sana_dwconv_glu_amax: null pointer");
+  return dwconv_glu_impl(u, halo_top, halo_bot, weight, bias, out, rows, W, H, row0, hid, SANA_BF16, amax_out, stream);
 }
 
 extern "C" int sana_dwconv_glu_take_device_status(int* status_out) {

@@ -14,6 +14,7 @@
 // K = 64 per instruction.  TMEM: two 128-column accumulators + 32 scale columns per stage.
 #include <cuda_fp8.h>
 
+#include "fp4_quant.cuh"
 #include "tc_common.cuh"
 
 namespace sana {
@@ -268,31 +269,33 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 
 // ---- CTA-pair variant -----------------------------------------------------------------------------
-// Two CTAs of a cluster share one 256 x 128 output tile (tcgen05 cta_group::2): each CTA loads its own
-// 128 rows of A with their scale tiles, HALF of the W tile (64 rows) and the scale tile of the whole W
+// Two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2): each CTA loads its own
+// 128 rows of A with their scale tiles, HALF of the W tile (128 rows) and the scale tiles of the whole W
 // tile; the pair's leader copies the scales into tensor memory and issues the block-scaled MMAs with
-// M = 256.  Per SM and K block this moves 28 KiB through L2 and shared memory for the math the
-// 128 x 128 kernel moves 36 KiB for, and six stages fit.  Two 128-column accumulators alternate, so the
-// epilogue of a tile runs under the MMAs of the next one; a 256 x 256 tile with the one accumulator
-// that fits beside the scale columns ran its MMAs at the same rate but left its epilogue (a third of
-// the tile's time at K = 2240) exposed.
+// M = 256.  A block-scaled MMA of K = 64 takes the tensor core about as long for a 128 x 128 tile as for
+// a 256 x 256 one (measured: 262 / 290 / 305 cycles per instruction on 128 x 128, 256 x 128, 256 x 256),
+// so only the largest tile uses it fully.  Tensor memory then holds ONE 256-column accumulator (two would
+// leave no room for the scale columns).  To keep its epilogue off the critical path the epilogue warps
+// first copy the whole accumulator into registers (eight back-to-back tcgen05.ld per warp, a few hundred
+// cycles), hand the buffer back to the MMA issuer, and do the arithmetic and the stores from registers
+// under the next tile's MMAs; they get the registers for that from the load / MMA warps (setmaxnreg).
 // All four operand streams are bulk-tensor copies (the scale buffers as [tiles, 128] words, so that
 // tiles past the end arrive as zeros), counted on the leader's barrier.
-constexpr int P4_BM = 128, P4_BN = 128;
+constexpr int P4_BM = 128, P4_BN = 256;
 constexpr int P4_A_BYTES = P4_BM * 128;             // 16 KiB
-constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 8 KiB: this CTA's half of the W tile
+constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 16 KiB: this CTA's half of the W tile
 constexpr int P4_SFA_BYTES = 4 * 512;               // scale tiles of this CTA's A rows, K = 256
-constexpr int P4_SFB_BYTES = 4 * 512;               // scale tiles of the 128 W rows
-constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;  // 28 KiB
-constexpr int P4_STAGES = 6;
+constexpr int P4_SFB_BYTES = 2 * 4 * 512;           // scale tiles of all 256 W rows
+constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;  // 38 KiB
+constexpr int P4_STAGES = 4;
 constexpr int P4_EPI_WARPS = 8;
 constexpr int P4_NBOX = (P4_BN / 2) / EPI_BOX_COLS;  // staging boxes per epilogue warp
 constexpr int P4_EPI_BYTES = P4_EPI_WARPS * P4_NBOX * EPI_BOX_BYTES;
 constexpr int P4_CTRL_BYTES = 256;
 constexpr int P4_SMEM_BYTES = P4_STAGES * P4_STAGE_BYTES + P4_EPI_BYTES + P4_CTRL_BYTES;
-constexpr int P4_THREADS = 64 + 32 * P4_EPI_WARPS;
-constexpr int P4_SF_COL0 = 2 * P4_BN;               // scale columns follow the two accumulators
-constexpr int P4_SF_COLS = 16 + 16;                 // per stage: A 4 x 4, W 4 x 4
+constexpr int P4_THREADS = 128 + 32 * P4_EPI_WARPS;  // warpgroup 0: loads, MMA, two idle warps; then the epilogue warps
+constexpr int P4_SF_COL0 = P4_BN;                   // scale columns follow the accumulator
+constexpr int P4_SF_COLS = 16 + 32;                 // per stage: A 4 x 4, W 4 x 8
 constexpr uint32_t P4_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(P4_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 static_assert(P4_SMEM_BYTES <= 232448, "shared memory budget");
 static_assert(P4_STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned");
@@ -318,7 +321,7 @@ struct P4Args {
   const float* a_scale;
   const float* w_scale;
   int M, N, K;
-  int tiles_m, tiles_n;  // 256 x 128 pair tiles
+  int tiles_m, tiles_n;  // 256 x 256 pair tiles
   int ktiles4;
   EpiParams ep;
 };
@@ -335,7 +338,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   unsigned char* epi_gen = smem_raw + STAGES * P4_STAGE_BYTES;
   const uint32_t ctrl = epi_base + P4_EPI_BYTES;
   unsigned char* ctrl_gen = epi_gen + P4_EPI_BYTES;
-  // control layout: full[STAGES] | empty[STAGES] | tfull[2] | tempty[2] | tmem ptr | abort | res[EPI_WARPS]
+  // control layout: full[STAGES] | empty[STAGES] | tfull | (pad) | tempty | (pad) | tmem ptr | abort | res[EPI_WARPS]
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
   const uint32_t bar_res = ctrl + 16 * STAGES + 40;
@@ -358,10 +361,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 2 * P4_EPI_WARPS);
-    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, 2 * P4_EPI_WARPS);
     for (int w = 0; w < P4_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -382,7 +383,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
-
+  // 384 threads start with 168 registers each; the epilogue warps, which hold a 128-column slice of the
+  // accumulator, take over what warpgroup 0 (loads, MMA issue, two idle warps) gives up
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------- loads (both CTAs) ----------------------------------
     if (lane == 0) {
@@ -394,13 +398,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int m0 = mt * 256 + (int)rank * P4_BM;          // this CTA's A rows
         const int n0 = nt * P4_BN + (int)rank * (P4_BN / 2);  // this CTA's half of the W rows
         const int sfa_row = (2 * mt + (int)rank) * args.ktiles4;  // scale tiles: row blocks of 128, K-fastest
-        const int sfb_row = nt * args.ktiles4;
+        const int sfb_row = (2 * nt) * args.ktiles4;
         for (int kb = 0; kb < kblocks; ++kb) {
-          {
-            F4_T0();
-            if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
-            F4_ACC(5, leader);
-          }
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_fp4_status)) { ok = false; break; }
           const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
           if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * P4_STAGE_BYTES);
           const uint32_t fb = full0 + 8 * stage;
@@ -408,6 +408,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tma_load_2d_pair(sa + P4_A_BYTES, &tmB, fb, kb * 128, n0);
           tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES, &tmSFA, fb, 0, sfa_row + 4 * kb);
           tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES, &tmSFB, fb, 0, sfb_row + 4 * kb);
+          tma_load_2d_pair(sa + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + 4 * 512, &tmSFB, fb, 0, sfb_row + args.ktiles4 + 4 * kb);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -421,20 +422,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (leader && lane == 0) {
       uint32_t stage = 0, phase = 0, acc_phase = 0;
       bool ok = true;
-      int it = 0;
 #ifdef SANA_F4_PROFILE
       const long long f4_loop0 = clock64();
 #endif
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
-        const int a = it & 1;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         {
           F4_T0();
-          if (!mbar_wait(bar_tempty + 8 * a, ((acc_phase >> a) & 1u) ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
+          if (!mbar_wait(bar_tempty, acc_phase ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
           F4_ACC(0, true);
         }
-        acc_phase ^= 1u << a;
+        acc_phase ^= 1u;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(a * P4_BN);
         for (int kb = 0; kb < kblocks; ++kb) {
           {
             F4_T0();
@@ -449,24 +447,27 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             tmem_cp_sf_pair(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
-            tmem_cp_sf_pair(sfb_t + 4 * k, make_sf_desc(sfb_s + 512 * k));
+            tmem_cp_sf_pair(sfb_t + 8 * k, make_sf_desc(sfb_s + 512 * k));             // W rows 0..127 of the tile
+            tmem_cp_sf_pair(sfb_t + 8 * k + 4, make_sf_desc(sfb_s + 4 * 512 + 512 * k));  // W rows 128..255
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_nvfp4_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k, sfb_t + 4 * k,
-                            (kb | k) != 0 ? 1u : 0u);
+            umma_nvfp4_pair(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k,
+                            sfb_t + 8 * k, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(bar_empty + 8 * stage);  // frees this stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit_pair(bar_tfull + 8 * a);  // accumulator complete, both CTAs
+        if (ok) umma_commit_pair(bar_tfull);  // accumulator complete, both CTAs
       }
 #ifdef SANA_F4_PROFILE
       atomicAdd(&g_f4_prof[2], (unsigned long long)(clock64() - f4_loop0));
 #endif
     }
+  }
   } else {
     // ------------------------------- epilogue warps (both CTAs) -------------------------
-    const int ew = warp - 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int ew = warp - 4;
     const int quad = warp & 3;
     const int half = ew >> 2;
     constexpr int HALF = P4_BN / 2, NCHUNK = HALF / 16;
@@ -483,37 +484,36 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     eb.swz = (uint32_t)(lane & 7);
     uint32_t full_phase = 0u;
     bool ok = true;
-    int it = 0;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
-      const int a = it & 1;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int m_box = (tile / args.tiles_n) * 256 + (int)rank * P4_BM + quad * 32;
       const int64_t nbase = (int64_t)(tile % args.tiles_n) * P4_BN + half * HALF;
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * P4_BN + half * HALF);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * HALF);
       const EpiRow row = epi_row_setup(ep, m, row_ok, nbase, N);
       const bool box_rows_in = m_box < args.M;
       const bool use_res = has_res && box_rows_in;
       epi_box_begin<P4_NBOX>(eb, row, use_res, lane, m_box, &tmRes);
-      EpiStep st[2];
-      epi_fetch(row, st[0], 0);
       {
         F4_T0();
-        if (!mbar_wait(bar_tfull + 8 * a, (full_phase >> a) & 1u, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
-        F4_ACC(3, threadIdx.x == 64 && leader);
+        if (!mbar_wait(bar_tfull, full_phase, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
+        F4_ACC(3, threadIdx.x == 128 && leader);
       }
-      full_phase ^= 1u << a;
+      full_phase ^= 1u;
       tcgen05_fence_after();
       F4_T0();
-      if (!epi_box_drain<NCHUNK, true>(eb, row, ep, taddr, st, use_res, box_rows_in, lane, m_box, &tmOut, alpha, abort_flag,
-                                       &g_fp4_status)) {
+      uint32_t acc[NCHUNK][16];
+      epi_acc_load<NCHUNK>(taddr, acc);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0);  // the accumulator is free again: the leader's barrier collects both CTAs
+      F4_ACC(6, threadIdx.x == 128 && leader);
+      if (!epi_box_drain_regs<NCHUNK, true>(eb, row, ep, acc, use_res, box_rows_in, lane, m_box, &tmOut, alpha, abort_flag,
+                                            &g_fp4_status)) {
         ok = false;
         break;
       }
-      F4_ACC(4, threadIdx.x == 64 && leader);
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * a);  // the leader's barrier collects both CTAs
+      F4_ACC(4, threadIdx.x == 128 && leader);
     }
     if (lane == 0) bulk_wait_all();
   }
@@ -548,20 +548,6 @@ __global__ void absmax_bf16_kernel(const __nv_bfloat16* __restrict__ x, int64_t 
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));  // m >= 0
 }
 
-__device__ __forceinline__ float e4m3_round(float v) {
-  // round-to-nearest-even onto positive E4M3 (max 448), as a float
-  const __nv_fp8_storage_t s = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-  return __half2float(__half(__nv_cvt_fp8_to_halfraw(s, __NV_E4M3)));
-}
-__device__ __forceinline__ uint32_t e4m3_bits(float v) { return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
-
-// E2M1 code (sign in bit 3) of v, round-to-nearest-even, saturating at 6
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-  const float a = fabsf(v);
-  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
-  return c | (v < 0.f ? 8u : 0u);
-}
-
 // one thread per (row, 64-element K tile): 4 blocks of 16 -> 32 bytes of codes + 4 scale bytes
 __global__ void quantize_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld, unsigned char* __restrict__ q,
                                       unsigned char* __restrict__ sf, float* __restrict__ scales, int64_t rows, int K,
@@ -573,36 +559,27 @@ __global__ void quantize_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, int64
   if (idx >= rows * ktiles) return;
   const int64_t r = idx / ktiles;
   const int kt = (int)(idx - r * ktiles);
-  const float six_ts = 6.0f * ts;
+  const float inv6ts = __frcp_rn(6.0f * ts);
   uint32_t sfw = 0;
 #pragma unroll
   for (int b = 0; b < 4; ++b) {
     const int k0 = kt * 64 + b * 16;
     if (k0 >= K) break;
-    float f[16];
-    unpack8(ldg_nc_u4(x + r * ld + k0), *reinterpret_cast<float(*)[8]>(f));
-    unpack8(ldg_nc_u4(x + r * ld + k0 + 8), *reinterpret_cast<float(*)[8]>(f + 8));
+    float f[2][8];
+    unpack8(ldg_nc_u4(x + r * ld + k0), f[0]);
+    unpack8(ldg_nc_u4(x + r * ld + k0 + 8), f[1]);
     float bm = 0.f;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) bm = fmaxf(bm, fabsf(f[e]));
-    const float sraw = __fdiv_rn(bm, six_ts);
-    const float bs = e4m3_round(sraw);
-    sfw |= e4m3_bits(sraw) << (8 * b);
-    const float denom = bs * ts;
-    uint32_t w[2] = {0u, 0u};
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float sv = denom > 0.f ? __fdiv_rn(f[e], denom) : 0.f;
-      w[e >> 3] |= e2m1_code(sv) << (4 * (e & 7));
-    }
-    *reinterpret_cast<uint2*>(q + r * (int64_t)(K >> 1) + (k0 >> 1)) = make_uint2(w[0], w[1]);
+    for (int e = 0; e < 8; ++e) bm = fmaxf(bm, fmaxf(fabsf(f[0][e]), fabsf(f[1][e])));
+    const Fp4Block blk = fp4_block_scale(bm, ts, inv6ts);
+    sfw |= blk.sf_byte << (8 * b);
+    *reinterpret_cast<uint2*>(q + r * (int64_t)(K >> 1) + (k0 >> 1)) = make_uint2(fp4_codes8(f[0], blk.inv), fp4_codes8(f[1], blk.inv));
   }
   const int64_t tile = (r >> 7) * ktiles4 + kt;
   const int rr = (int)(r & 127);
   *reinterpret_cast<uint32_t*>(sf + tile * 512 + (rr & 31) * 16 + (rr >> 5) * 4) = sfw;
 }
 
-static int64_t ktiles4_of(int64_t K) { return ceil_div(ceil_div(K, 64), 4) * 4; }
 
 }  // namespace sana
 
@@ -639,6 +616,51 @@ extern "C" int sana_nvfp4_quantize(const void* x, int64_t ld, void* q, void* sf,
   return SANA_OK;
 }
 
+// Same quantiser with the tensor scale given: scales[0] holds the maximum magnitude to scale for (for example the
+// one measured on an earlier call); nothing is measured here.  Values beyond it saturate.
+extern "C" int sana_nvfp4_quantize_scaled(const void* x, int64_t ld, void* q, void* sf, float* scales, int64_t rows, int64_t K,
+                                          void* stream) {
+  SANA_REQUIRE(x && q && sf && scales, "sana_nvfp4_quantize_scaled: null pointer");
+  SANA_REQUIRE(rows > 0 && K > 0 && K % 32 == 0 && K < (1 << 30), "sana_nvfp4_quantize_scaled: K must be a positive multiple of 32");
+  SANA_REQUIRE(ld >= K && ld % 8 == 0, "sana_nvfp4_quantize_scaled: ld must be >= K and a multiple of 8");
+  SANA_REQUIRE(aligned16(x) && aligned16(q) && aligned16(sf) && aligned16(scales), "sana_nvfp4_quantize_scaled: alignment");
+  const int64_t ktiles = ceil_div(K, 64);
+  const int64_t total = rows * ktiles;
+  SANA_REQUIRE(ceil_div(total, 128) < ((int64_t)1 << 31), "sana_nvfp4_quantize_scaled: too large");
+  quantize_nvfp4_kernel<<<(unsigned)ceil_div(total, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, static_cast<unsigned char*>(q), static_cast<unsigned char*>(sf), scales,
+      rows, (int)K, (int)ktiles, (int)ktiles4_of(K));
+  SANA_LAUNCH_CHECK("quantize kernel");
+  return SANA_OK;
+}
+
+namespace sana {
+// state = n x {amax in use, tensor scale in use, amax seen since the last roll, unused}
+__global__ void nvfp4_scale_roll_kernel(float* state, int n, float margin) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float* s = state + 4 * i;
+  const float seen = s[2];
+  if (seen > 0.f) {
+    const float amax = seen * margin;
+    s[0] = amax;
+    s[1] = fmaxf(amax, 1e-30f) / (6.0f * 448.0f);
+    s[2] = 0.f;
+  }
+}
+}  // namespace sana
+
+// Delayed scaling of activations: the kernels that emit FP4 directly (sana_ln_modulate_fp4, sana_la_apply_fp4) and
+// sana_nvfp4_quantize_scaled use the tensor scale in state[1] and raise state[2] to the largest magnitude they
+// produce (sana_dwconv_glu_amax does the same for its bf16 output); this call adopts what was seen, times `margin`,
+// as the scale of the following calls.  `state` holds n records of four floats.
+extern "C" int sana_nvfp4_scale_roll(float* state, int64_t n, float margin, void* stream) {
+  SANA_REQUIRE(state && n > 0 && n < (1 << 20) && margin > 0.f, "sana_nvfp4_scale_roll: bad arguments");
+  nvfp4_scale_roll_kernel<<<(unsigned)ceil_div(n, 64), 64, 0, static_cast<cudaStream_t>(stream)>>>(state, (int)n, margin);
+  SANA_LAUNCH_CHECK("nvfp4_scale_roll kernel");
+  return SANA_OK;
+}
+
 extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_scales, const void* Wq, const void* sfw,
                                const float* w_scales, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
                                const sana_gemm_epilogue* ep, void* stream) {
@@ -665,7 +687,7 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   }
   const int variant = gemm_variant();
   if (variant == 2 || (variant == 0 && M >= 2048)) {
-    // CTA pairs on 256 x 128 tiles
+    // CTA pairs on 256 x 256 tiles
     rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Aq, M, K / 2, K / 2, P4_BM, 128);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Wq, N, K / 2, K / 2, P4_BN / 2, 128);

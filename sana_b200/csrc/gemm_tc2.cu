@@ -125,7 +125,11 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const uint32_t full0 = map_to_cta(bar_full, 0);  // the leader's full barriers, cluster address
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = (tile / args.tiles_n) * (2 * T2_BM) + (int)rank * T2_BM;
-        const int n0 = (tile % args.tiles_n) * BN + (int)rank * Cfg::BH;
+        // a ragged last tile column is computed at its own width (a multiple of 32): each CTA then holds half of
+        // THAT many W rows, not half of BN
+        const int nt0 = (tile % args.tiles_n) * BN;
+        const int n_this = min(BN, ((args.N - nt0) + 31) & ~31);
+        const int n0 = nt0 + (int)rank * (n_this >> 1);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, &g_gemm2_status)) { ok = false; break; }
           const uint32_t sa = tiles_base + stage * Cfg::STAGE_BYTES;
@@ -153,6 +157,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         acc_phase ^= 1u << a;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+        const int n_this = min(BN, ((args.N - (tile % args.tiles_n) * BN) + 31) & ~31);
+        // same descriptor with this tile's N (>> 3 at bit 17)
+        const uint32_t idesc = (Cfg::IDESC & ~(0x3Fu << 17)) | ((uint32_t)(n_this >> 3) << 17);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_gemm2_status)) { ok = false; break; }
           tcgen05_fence_after();
@@ -160,7 +167,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + T2_A_BYTES);
 #pragma unroll
           for (int k = 0; k < T2_BK / 16; ++k)
-            umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), Cfg::IDESC, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(bar_empty + 8 * stage);  // frees this stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "fp4_quant.cuh"
 #include "la_plan.cuh"
 
 namespace sana {
@@ -188,9 +189,13 @@ __global__ void la_state_reduce_kernel(const float* __restrict__ partial, float*
 // value channel 8*(c>>1) + 2nt + (c&1), so each lane ends with 8 contiguous outputs of a
 // row (one 16-byte store).
 // ------------------------------------------------------------------------------------------
+// With FP4 the kernel also - or only, when op is null - writes the NVFP4 image of its output (the input of the
+// attention's output projection): a head's 32 channels of a token sit in four neighbouring lanes, eight each, so a
+// 16-channel block is a lane pair; the largest magnitude produced is accumulated into sink.amax_out.
+template <bool FP4>
 __global__ void __launch_bounds__(LA_WARPS * 32)
 la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const float* __restrict__ state,
-                     __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps) {
+                     __nv_bfloat16* __restrict__ op, int64_t ldo, int N, int H, int Lc, float eps, const Fp4Sink sink) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int h = blockIdx.x * LA_WARPS + warp;
@@ -224,6 +229,9 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
   const int64_t col = (int64_t)h * HD + 8 * t;
   const __nv_bfloat16* qbase = qp + (int64_t)b * N * ldq + col;
   __nv_bfloat16* obase = op + (int64_t)b * N * ldo + col;
+  const float ts = FP4 ? __ldg(sink.scale_in + 1) : 0.f;
+  const float inv6ts = FP4 ? __frcp_rn(6.0f * ts) : 0.f;
+  float amax_local = 0.f;
 
   constexpr int U = 4;  // 16-token steps per batch of loads
   auto load = [&](uint4 (&qr)[U][2], int n0) {
@@ -275,14 +283,31 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int tok = n0 + 16 * u + g + 8 * r;
-        if (tok < n_end) {
-          const float inv = 1.0f / (den[r] + eps);
-          uint4 o;
-          o.x = pack_bf16(c[0][2 * r] * inv, c[0][2 * r + 1] * inv);
-          o.y = pack_bf16(c[1][2 * r] * inv, c[1][2 * r + 1] * inv);
-          o.z = pack_bf16(c[2][2 * r] * inv, c[2][2 * r + 1] * inv);
-          o.w = pack_bf16(c[3][2 * r] * inv, c[3][2 * r + 1] * inv);
-          *reinterpret_cast<uint4*>(obase + (int64_t)tok * ldo) = o;
+        const bool in = tok < n_end;
+        const float inv = 1.0f / (den[r] + eps);
+        uint4 o;
+        o.x = pack_bf16(c[0][2 * r] * inv, c[0][2 * r + 1] * inv);
+        o.y = pack_bf16(c[1][2 * r] * inv, c[1][2 * r + 1] * inv);
+        o.z = pack_bf16(c[2][2 * r] * inv, c[2][2 * r + 1] * inv);
+        o.w = pack_bf16(c[3][2 * r] * inv, c[3][2 * r + 1] * inv);
+        if (in && (!FP4 || op != nullptr)) *reinterpret_cast<uint4*>(obase + (int64_t)tok * ldo) = o;
+        if (FP4) {  // every lane takes part in the shuffles; rows past the end hold zeros
+          float fq[8];
+          fq[0] = bf16_lo(o.x), fq[1] = bf16_hi(o.x), fq[2] = bf16_lo(o.y), fq[3] = bf16_hi(o.y);
+          fq[4] = bf16_lo(o.z), fq[5] = bf16_hi(o.z), fq[6] = bf16_lo(o.w), fq[7] = bf16_hi(o.w);
+          if (in) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) amax_local = fmaxf(amax_local, fabsf(fq[e]));
+          }
+          uint32_t sb;
+          const uint32_t codes = fp4_quant8_of16(fq, ts, inv6ts, &sb);
+          const uint32_t sb2 = __shfl_down_sync(0xffffffffu, sb, 2);
+          if (in) {
+            const int64_t row = (int64_t)b * N + tok;
+            *reinterpret_cast<uint32_t*>(sink.q + row * (int64_t)(sink.K >> 1) + (col >> 1)) = codes;
+            if (t == 0)  // the head's two 16-channel blocks: scale bytes 2h and 2h + 1 of the row
+              *reinterpret_cast<uint16_t*>(sink.sf + fp4_sf_offset(row, 2 * h, sink.ktiles4)) = (uint16_t)(sb | (sb2 << 8));
+          }
         }
       }
     }
@@ -292,6 +317,11 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
   for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
     load(qa, n0);
     compute(qa, n0);
+  }
+  if (FP4 && sink.amax_out != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax_local = fmaxf(amax_local, __shfl_xor_sync(0xffffffffu, amax_local, o));
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(sink.amax_out), __float_as_uint(amax_local));  // >= 0
   }
 }
 
@@ -398,13 +428,13 @@ extern "C" int sana_la_apply(const void* q, int64_t ldq, const float* state, voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int Lc, nchunks;
   if (dtype == SANA_BF16) {
-    static const int64_t slots = resident_ctas(la_apply_bf16_kernel, LA_WARPS * 32);
+    static const int64_t slots = resident_ctas(la_apply_bf16_kernel<false>, LA_WARPS * 32);
     // loading a head's state costs about as much as 33 tokens of q + o
     la_chunking(B * ceil_div(H, LA_WARPS), N, slots, 33, &Lc, &nchunks);
     dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
-    la_apply_bf16_kernel<<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(q), ldq, state,
-                                                        static_cast<__nv_bfloat16*>(out), ldo, (int)N, (int)H, Lc,
-                                                        eps);
+    la_apply_bf16_kernel<false><<<grid, LA_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(q), ldq, state,
+                                                               static_cast<__nv_bfloat16*>(out), ldo, (int)N, (int)H, Lc,
+                                                               eps, Fp4Sink{});
   } else if (dtype == SANA_F32) {
     la_chunking(B * H, N, (int64_t)sm_count() * 8, 33, &Lc, &nchunks);
     dim3 grid(nchunks, (unsigned)H, (unsigned)B);
@@ -414,6 +444,33 @@ extern "C" int sana_la_apply(const void* q, int64_t ldq, const float* state, voi
     return fail(SANA_ERR_UNSUPPORTED, "sana_la_apply: unsupported dtype %d", dtype);
   }
   SANA_LAUNCH_CHECK("la_apply kernel");
+  return SANA_OK;
+}
+
+extern "C" int sana_la_apply_fp4(const void* q, int64_t ldq, const float* state, void* out, int64_t ldo, void* fq, void* sf,
+                                 const float* scale_in, float* amax_out, int64_t B, int64_t N, int64_t H, float eps,
+                                 void* stream) {
+  SANA_REQUIRE(q && state && fq && sf && scale_in, "sana_la_apply_fp4: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_apply_fp4: B, N, H must be positive");
+  SANA_REQUIRE(N < (1 << 30) && B < 65536 && H < 65536 * LA_WARPS, "sana_la_apply_fp4: size out of range");
+  SANA_REQUIRE(ldq >= H * HD && ldq % 8 == 0 && (!out || (ldo >= H * HD && ldo % 8 == 0)),
+               "sana_la_apply_fp4: row strides must be >= H*32 and multiples of 8");
+  SANA_REQUIRE(aligned16(q) && aligned16(state) && (!out || aligned16(out)) && aligned16(fq) && aligned16(sf),
+               "sana_la_apply_fp4: pointers must be 16-byte aligned");
+  Fp4Sink sink;
+  sink.q = static_cast<unsigned char*>(fq);
+  sink.sf = static_cast<unsigned char*>(sf);
+  sink.scale_in = scale_in;
+  sink.amax_out = amax_out;
+  sink.K = (int)(H * HD);
+  sink.ktiles4 = (int)ktiles4_of(H * HD);
+  int Lc, nchunks;
+  static const int64_t slots = resident_ctas(la_apply_bf16_kernel<true>, LA_WARPS * 32);
+  la_chunking(B * ceil_div(H, LA_WARPS), N, slots, 33, &Lc, &nchunks);
+  dim3 grid((unsigned)ceil_div(H, LA_WARPS), nchunks, (unsigned)B);
+  la_apply_bf16_kernel<true><<<grid, LA_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), ldq, state, static_cast<__nv_bfloat16*>(out), ldo, (int)N, (int)H, Lc, eps, sink);
+  SANA_LAUNCH_CHECK("la_apply (FP4) kernel");
   return SANA_OK;
 }
 

@@ -1,7 +1,7 @@
 // adaLN-single LayerNorm + modulate: one warp per token row, the row held in registers
 // (packed, as loaded) so global memory is read once and written once; the per-sample
 // modulation vectors are combined once per block into shared memory.
-#include "common.cuh"
+#include "fp4_quant.cuh"
 
 namespace sana {
 
@@ -43,11 +43,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 // out as planes of float4 (plane p holds elements 4p..4p+3 of every 16-byte vector) so that a
 // warp's reads are conflict-free. A block owns a contiguous range of rows and restages the
 // vectors when the range crosses into the next sample.
-template <typename T, int MAXV>
+// With FP4 (bf16 only) the kernel also - or only, when z is null - writes the NVFP4 image of its output: the
+// modulated row is rounded to bf16 exactly as it would be stored, then quantised 16 channels at a time (two
+// neighbouring lanes hold a block) with the tensor scale given by the caller; the largest magnitude produced is
+// accumulated into sink.amax_out.
+template <typename T, int MAXV, bool FP4>
 __global__ void __launch_bounds__(256)
 ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T* __restrict__ t, T* __restrict__ z,
                    int64_t rows, int N, int C, int tb_shift, int tb_scale, int t_rows, int t_shift, int t_scale,
-                   float eps, int rows_per_block) {
+                   float eps, int rows_per_block, const Fp4Sink sink) {
   constexpr int VN = Vec16<T>::N;
   constexpr int PLANES = VN / 4;
   extern __shared__ float4 ln_smem[];
@@ -61,6 +65,9 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
   const int64_t row1 = (row0 + rows_per_block < rows) ? row0 + rows_per_block : rows;
   if (row0 >= row1) return;
   const float inv_c = 1.0f / (float)C;
+  const float ts = FP4 ? __ldg(sink.scale_in + 1) : 0.f;
+  const float inv6ts = FP4 ? __frcp_rn(6.0f * ts) : 0.f;
+  float amax_local = 0.f;
   for (int64_t b = row0 / N; b * N < row1; ++b) {
     const int64_t seg0 = (b * N > row0) ? b * N : row0;
     const int64_t seg1 = ((b + 1) * N < row1) ? (b + 1) * N : row1;
@@ -120,7 +127,9 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
 #pragma unroll
       for (int i = 0; i < MAXV; ++i) {
         const int v = lane + 32 * i;
-        if (v < nvec) {
+        const bool in = v < nvec;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (in) {
           float f[VN];
           Vec16<T>::unpack(raw[i], f);
 #pragma unroll
@@ -132,7 +141,27 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
             f[4 * p + 2] = fmaf((f[4 * p + 2] - mean) * rstd, m.z, a.z);
             f[4 * p + 3] = fmaf((f[4 * p + 3] - mean) * rstd, m.w, a.w);
           }
-          zr[v] = Vec16<T>::pack(f);
+          packed = Vec16<T>::pack(f);
+          if (!FP4 || z != nullptr) zr[v] = packed;
+        }
+        if (FP4 && 32 * i < nvec) {  // warp-uniform: some lane of this round holds channels (bf16: VN = 8)
+          float fq[8];
+          fq[0] = bf16_lo(packed.x), fq[1] = bf16_hi(packed.x), fq[2] = bf16_lo(packed.y), fq[3] = bf16_hi(packed.y);
+          fq[4] = bf16_lo(packed.z), fq[5] = bf16_hi(packed.z), fq[6] = bf16_lo(packed.w), fq[7] = bf16_hi(packed.w);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax_local = fmaxf(amax_local, fabsf(fq[e]));
+          uint32_t sb;
+          const uint32_t codes = fp4_quant8_of16(fq, ts, inv6ts, &sb);
+          if (in) *reinterpret_cast<uint32_t*>(sink.q + row * (int64_t)(C >> 1) + 4 * v) = codes;
+          // the four block scales of a 64-channel tile sit in the even lanes of a group of eight
+          if (!in) sb = 0u;
+          const uint32_t s1 = __shfl_down_sync(0xffffffffu, sb, 2), s2 = __shfl_down_sync(0xffffffffu, sb, 4),
+                         s3 = __shfl_down_sync(0xffffffffu, sb, 6);
+          if (in && (lane & 7) == 0) {
+            const int64_t tile = (row >> 7) * sink.ktiles4 + (v >> 3);
+            *reinterpret_cast<uint32_t*>(sink.sf + tile * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4) =
+                sb | (s1 << 8) | (s2 << 16) | (s3 << 24);
+          }
         }
       }
     };
@@ -149,11 +178,17 @@ ln_modulate_kernel(const T* __restrict__ x, const T* __restrict__ table, const T
       if (r1 < seg1) process(rb, r1);
     }
   }
+  if (FP4 && sink.amax_out != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax_local = fmaxf(amax_local, __shfl_xor_sync(0xffffffffu, amax_local, o));
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(sink.amax_out), __float_as_uint(amax_local));  // >= 0
+  }
 }
 
-template <typename T>
+template <typename T, bool FP4>
 static int launch_ln(const void* x, const void* table, const void* t, void* z, int64_t B, int64_t N, int64_t C,
-                     int tb_shift, int tb_scale, int t_rows, int t_shift, int t_scale, float eps, cudaStream_t st) {
+                     int tb_shift, int tb_scale, int t_rows, int t_shift, int t_scale, float eps, cudaStream_t st,
+                     const Fp4Sink& sink) {
   const int64_t rows = B * N;
   const int nvec = (int)(C / Vec16<T>::N);
   const int per_lane = (nvec + 31) / 32;
@@ -165,13 +200,13 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
 #define SANA_LN_CASE(MV)                                                                                       \
   if (per_lane <= MV) {                                                                                        \
     if (smem > 48 * 1024) {                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(ln_modulate_kernel<T, MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+      cudaError_t e = cudaFuncSetAttribute(ln_modulate_kernel<T, MV, FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            (int)smem);                                                         \
       if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_modulate)");                       \
     }                                                                                                          \
     /* one wave of blocks (as many as are resident), each over a contiguous range of rows */                  \
     int per_sm = 0;                                                                                            \
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_kernel<T, MV>, 256, smem) !=        \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ln_modulate_kernel<T, MV, FP4>, 256, smem) !=        \
             cudaSuccess || per_sm < 1) {                                                                       \
       cudaGetLastError();                                                                                      \
       per_sm = 1;                                                                                              \
@@ -179,8 +214,8 @@ static int launch_ln(const void* x, const void* table, const void* t, void* z, i
     int64_t rpb = ceil_div(rows, (int64_t)sm_count() * per_sm);                                                \
     rpb = ceil_div(rpb, 8) * 8;                                                                                \
     const unsigned grid = (unsigned)ceil_div(rows, rpb);                                                       \
-    ln_modulate_kernel<T, MV><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, tb_shift, tb_scale,   \
-                                                       t_rows, t_shift, t_scale, eps, (int)rpb);               \
+    ln_modulate_kernel<T, MV, FP4><<<grid, 256, smem, st>>>(xp, tb, tp, zp, rows, (int)N, (int)C, tb_shift, tb_scale,   \
+                                                       t_rows, t_shift, t_scale, eps, (int)rpb, sink);         \
     SANA_LAUNCH_CHECK("ln_modulate kernel");                                                                   \
     return SANA_OK;                                                                                            \
   }
@@ -212,12 +247,13 @@ extern "C" int sana_ln_modulate_rows(const void* x, const void* table, const voi
                "sana_ln_modulate: pointers must be 16-byte aligned");
   SANA_REQUIRE(B * N < ((int64_t)1 << 31) * 8, "sana_ln_modulate: too many rows");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const Fp4Sink none = {};
   if (dtype == SANA_BF16)
-    return launch_ln<__nv_bfloat16>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
-                                    t_scale_row, eps, st);
+    return launch_ln<__nv_bfloat16, false>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
+                                           t_scale_row, eps, st, none);
   if (dtype == SANA_F32)
-    return launch_ln<float>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
-                            t_scale_row, eps, st);
+    return launch_ln<float, false>(x, table, t, z, B, N, C, table_shift_row, table_scale_row, t_rows, t_shift_row,
+                                   t_scale_row, eps, st, none);
   return fail(SANA_ERR_UNSUPPORTED, "sana_ln_modulate: unsupported dtype %d", dtype);
 }
 
@@ -225,4 +261,25 @@ extern "C" int sana_ln_modulate(const void* x, const void* table, const void* t,
                                 int64_t C, int shift_row, int scale_row, float eps, int dtype, void* stream) {
   return sana_ln_modulate_rows(x, table, t, z, B, N, C, 6, shift_row, scale_row, 6, shift_row, scale_row, eps, dtype,
                                stream);
+}
+
+extern "C" int sana_ln_modulate_fp4(const void* x, const void* table, const void* t, void* z, void* q, void* sf,
+                                    const float* scale_in, float* amax_out, int64_t B, int64_t N, int64_t C, int shift_row,
+                                    int scale_row, float eps, void* stream) {
+  SANA_REQUIRE(x && table && t && q && sf && scale_in, "sana_ln_modulate_fp4: null pointer");
+  SANA_REQUIRE(B > 0 && N > 0 && C > 0, "sana_ln_modulate_fp4: sizes must be positive");
+  SANA_REQUIRE(C % 32 == 0 && C * 2 <= 16384, "sana_ln_modulate_fp4: C must be a multiple of 32 and a row at most 16 KiB");
+  SANA_REQUIRE(shift_row >= 0 && shift_row < 6 && scale_row >= 0 && scale_row < 6, "sana_ln_modulate_fp4: bad table row");
+  SANA_REQUIRE(aligned16(x) && aligned16(table) && aligned16(t) && (!z || aligned16(z)) && aligned16(q) && aligned16(sf),
+               "sana_ln_modulate_fp4: pointers must be 16-byte aligned");
+  SANA_REQUIRE(B * N < ((int64_t)1 << 31) * 8, "sana_ln_modulate_fp4: too many rows");
+  Fp4Sink sink;
+  sink.q = static_cast<unsigned char*>(q);
+  sink.sf = static_cast<unsigned char*>(sf);
+  sink.scale_in = scale_in;
+  sink.amax_out = amax_out;
+  sink.K = (int)C;
+  sink.ktiles4 = (int)ktiles4_of(C);
+  return launch_ln<__nv_bfloat16, true>(x, table, t, z, B, N, C, shift_row, scale_row, 6, shift_row, scale_row, eps,
+                                        static_cast<cudaStream_t>(stream), sink);
 }

@@ -292,6 +292,111 @@ __device__ __forceinline__ bool epi_box_drain(EpiBox& eb, const EpiRow& row, con
   return true;
 }
 
+// ---- the same epilogue on an accumulator that has been copied into registers first ---------------
+// Where a kernel has one accumulator buffer only, the epilogue warps copy their part of it out of tensor
+// memory in one go (NCHUNK back-to-back loads), hand the buffer back to the MMA issuer, and only then do the
+// arithmetic and the stores - which then run under the next tile's MMAs.
+template <int NCHUNK>
+__device__ __forceinline__ void epi_acc_load(uint32_t taddr, uint32_t (&acc)[NCHUNK][16]) {
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) tmem_ld_32x16(taddr + (uint32_t)(16 * c), acc[c]);
+  tmem_ld_wait();
+}
+
+struct EpiSide {
+  uint4 bias[2], gtab[2], gt[2];
+};
+__device__ __forceinline__ void epi_fetch_side(const EpiRow& r, EpiSide& s, int c) {
+  const int64_t n = r.nbase + 16 * c;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int64_t nj = n + 8 * j;
+    const bool in = nj < r.N;
+    s.bias[j] = (r.bias && in) ? __ldg(reinterpret_cast<const uint4*>(r.bias + nj)) : make_uint4(0u, 0u, 0u, 0u);
+    if (r.grow) {
+      s.gtab[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.grow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+      s.gt[j] = in ? __ldg(reinterpret_cast<const uint4*>(r.gtrow + nj)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+template <int NCHUNK, bool SCALE>
+__device__ __forceinline__ bool epi_box_drain_regs(EpiBox& eb, const EpiRow& row, const EpiParams& ep,
+                                                   const uint32_t (&acc)[NCHUNK][16], bool use_res, bool box_rows_in, int lane,
+                                                   int m_box, const CUtensorMap* tmOut, float alpha, volatile int* abort_flag,
+                                                   int* status_word) {
+  const int64_t nbase = row.nbase, N = row.N;
+  EpiSide side[2];
+  if (nbase < N) {
+    epi_fetch_side(row, side[0], 0);
+    if (use_res) {
+      if (!mbar_wait(eb.res_bar, eb.res_phase, abort_flag, 5, status_word)) return false;
+      eb.res_phase ^= 1u;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int64_t n = nbase + 16 * c;
+    if (n >= N) break;  // uniform: the rest of this half lies outside the matrix
+    constexpr int CPB = EPI_BOX_COLS / 16;
+    const int j = c / CPB, cc = c % CPB;
+    const EpiSide& cur = side[c & 1];
+    const bool more = (c + 1 < NCHUNK) && (n + 16 < N);
+    if (more) epi_fetch_side(row, side[(c + 1) & 1], c + 1);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (n + 8 * h < N) {
+        float v[8], f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[c][8 * h + e]);
+        if (SCALE) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] *= alpha;
+        }
+        if (row.bias) {
+          unpack8(cur.bias[h], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += f[e];
+        }
+        if (ep.act == 1) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = fast_silu(v[e]);
+        } else if (ep.act == 2) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (n + 8 * h + e < ep.relu_cols) v[e] = fmaxf(v[e], 0.f);
+        } else if (ep.act == 3) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+        }
+        if (row.grow) {
+          float g[8];
+          unpack8(cur.gtab[h], g);
+          unpack8(cur.gt[h], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] *= (g[e] + f[e]);
+        }
+        uint4* slot = reinterpret_cast<uint4*>(eb.row_g + j * EPI_BOX_BYTES + ((((uint32_t)(2 * cc + h)) ^ eb.swz) << 4));
+        if (use_res) {
+          unpack8(*slot, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += f[e];
+        }
+        *slot = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+      }
+    }
+    if (cc == CPB - 1 || !more) {  // box j is complete
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && box_rows_in) {
+        tma_store_2d(tmOut, eb.box_s + j * EPI_BOX_BYTES, (int)(nbase + EPI_BOX_COLS * j), m_box);
+        bulk_commit();
+      }
+    }
+  }
+  return true;
+}
+
 // ---- CTA pairs (clusters of two, tcgen05 cta_group::2) ------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

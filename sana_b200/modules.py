@@ -7,10 +7,10 @@ keys and forward signatures, computing through libsana_b200's CUDA kernels.
   SanaMSBlock              diffusion/model/nets/sana_multi_scale.py:54-157
 
 Inference only (no autograd through the kernels).  Feature combinations the kernels do not
-cover raise; nothing falls back to eager PyTorch arithmetic.  The one library call left on the
-path is the bf16 softmax core of the cross-attention (torch SDPA, i.e. cuDNN's flash kernel),
-kept because it is faster than our own kernel; ``cross_attn.softmax_core = "kernel"`` selects
-ours.
+cover raise; nothing falls back to eager PyTorch arithmetic.  The cross-attention's softmax core
+runs on the library's own kernel (``cross_attn.softmax_core = "sdpa"`` selects torch SDPA, the
+vendor flash kernel, for comparison; it is also what a head dimension the kernel does not cover
+- not a multiple of 8, or above 128 - takes).
 """
 from __future__ import annotations
 
@@ -36,25 +36,38 @@ def _as2d(x: torch.Tensor) -> torch.Tensor:
     return x.reshape(-1, x.shape[-1])
 
 
-def _project(owner: nn.Module, key: str, x2d: torch.Tensor, w2d: torch.Tensor, **epilogue) -> torch.Tensor:
-    """``x2d @ w2d.T`` with the fused epilogue of :func:`ops.gemm`.  When ``owner.nvfp4`` is set
-    both operands are quantised to NVFP4 first: the activation on every call, the weight once
-    (cached on the module until the parameter is modified or moved) - or never, when a packed
-    weight was installed by ``weight_pack.load_nvfp4_weights``."""
-    if not getattr(owner, "nvfp4", False):
-        return ops.gemm(x2d, w2d, **epilogue)
-    if x2d.dtype != torch.bfloat16:
-        raise NotImplementedError("NVFP4 projections take bf16 activations and weights")
+def _fp4_weight(owner: nn.Module, key: str, w2d: torch.Tensor) -> "ops.NvFp4Tensor":
+    """The NVFP4 image of a projection weight: a packed weight installed by
+    ``weight_pack.load_nvfp4_weights``, else quantised once and cached on the module until the
+    parameter is modified or moved."""
     packed = owner.__dict__.get("_nvfp4_packed")
     if packed is not None and key in packed:
-        return ops.gemm_nvfp4(ops.nvfp4_quantize(x2d), packed[key], **epilogue)
+        return packed[key]
     cache = owner.__dict__.setdefault("_nvfp4_weights", {})
     tag = (w2d.data_ptr(), w2d._version, tuple(w2d.shape))
     entry = cache.get(key)
     if entry is None or entry[0] != tag:
         entry = (tag, ops.nvfp4_quantize(w2d.contiguous()))
         cache[key] = entry
-    return ops.gemm_nvfp4(ops.nvfp4_quantize(x2d), entry[1], **epilogue)
+    return entry[1]
+
+
+def _project(owner: nn.Module, key: str, x2d, w2d: torch.Tensor, **epilogue) -> torch.Tensor:
+    """``x2d @ w2d.T`` with the fused epilogue of :func:`ops.gemm`.  When ``owner.nvfp4`` is set
+    both operands are NVFP4: the weight through :func:`_fp4_weight`; the activation is either
+    already quantised by the kernel that produced it (an ``ops.NvFp4Tensor``) or quantised here,
+    with a measuring pass, on every call."""
+    if isinstance(x2d, ops.NvFp4Tensor):
+        return ops.gemm_nvfp4(x2d, _fp4_weight(owner, key, w2d), **epilogue)
+    if not getattr(owner, "nvfp4", False):
+        return ops.gemm(x2d, w2d, **epilogue)
+    if x2d.dtype != torch.bfloat16:
+        raise NotImplementedError("NVFP4 projections take bf16 activations and weights")
+    qa = ops.nvfp4_quantize(x2d)
+    seen = owner.__dict__.get("_fp4_seen")
+    if seen is not None:  # a calibrating forward: remember the measured scales of this projection's input
+        seen[key] = qa.scales
+    return ops.gemm_nvfp4(qa, _fp4_weight(owner, key, w2d), **epilogue)
 
 
 class RMSNorm(nn.Module):
@@ -110,9 +123,11 @@ class LiteLA(nn.Module):
         self.nvfp4 = False  # quantise the qkv / proj projections to NVFP4
 
     # -- pieces shared with the fused block path --------------------------------------------
-    def _core(self, qkv: torch.Tensor, B: int, N: int, rotary_emb=None) -> torch.Tensor:
+    def _core(self, qkv: torch.Tensor, B: int, N: int, rotary_emb=None, fp4_buf=None):
         """qkv [B*N, 3C] -> normalised attention output [B*N, C] (before ``proj``).
-        ``rotary_emb`` = (cos, sin), each [N, head_dim]: rotates q and k before the ReLU."""
+        ``rotary_emb`` = (cos, sin), each [N, head_dim]: rotates q and k before the ReLU.
+        With ``fp4_buf`` (an ``ops.Fp4Buffers``) the output is written as NVFP4 by the apply kernel
+        and an ``ops.NvFp4Tensor`` is returned."""
         C = self.out_dim
         if isinstance(self.q_norm, RMSNorm):  # in place on the q and k column blocks
             ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
@@ -131,6 +146,8 @@ class LiteLA(nn.Module):
             state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, self.heads)
             if sh is not None:
                 sh.allreduce_state(state)
+        if fp4_buf is not None:
+            return ops.la_apply_fp4(qkv[:, :C], state, B, N, self.heads, float(self.eps), fp4_buf)
         return ops.la_apply(qkv[:, :C], state, B, N, self.heads, float(self.eps))
 
     def attn_matmul(self, q, k, v: torch.Tensor) -> torch.Tensor:
@@ -337,7 +354,7 @@ class GLUMBConv(nn.Module):
         return _project(self, "inverted_conv", z2d, c.weight.reshape(c.out_channels, c.in_channels), bias=c.bias,
                         act=ops.ACT_SILU)
 
-    def _depthwise_glu(self, u: torch.Tensor, B: int, N: int, HW: Sequence[int]) -> torch.Tensor:
+    def _depthwise_glu(self, u: torch.Tensor, B: int, N: int, HW: Sequence[int], amax_out=None) -> torch.Tensor:
         if HW is None or len(HW) not in (2, 3):
             raise ValueError("GLUMBConv.forward needs HW=(H, W) or (T, H, W)")
         H, W = HW[-2], HW[-1]
@@ -351,7 +368,7 @@ class GLUMBConv(nn.Module):
         frames = HW[0] if len(HW) == 3 else 1
         if N != frames * H * W:
             raise ValueError(f"GLUMBConv: N={N} does not match HW={tuple(HW)}")
-        return ops.dwconv_glu(u, c.weight, c.bias, W, H)
+        return ops.dwconv_glu(u, c.weight, c.bias, W, H, amax_out=amax_out)
 
     def forward(self, x: torch.Tensor, HW=None) -> torch.Tensor:
         B, N, C = x.shape
@@ -462,9 +479,10 @@ class MultiHeadCrossAttention(nn.Module):
         self.attn_drop = nn.Dropout(attn_drop)
         self.proj = nn.Linear(d_model, d_model)
         self.proj_drop = nn.Dropout(proj_drop)
-        # softmax core: "kernel" = sana_cross_attention (warp-level tensor cores), "sdpa" =
-        # torch's scaled_dot_product_attention (cuDNN flash on B200), "auto" = sdpa for bf16
-        # (measured 66 us vs 247 us per 16 384-token image at 1.6B width), kernel otherwise
+        # softmax core: "kernel" / "auto" = sana_cross_attention (bf16: the tcgen05 kernel for 17..304 text
+        # tokens, 84 us per 16 384-token image at 1.6B width; the warp-level kernel otherwise), "sdpa" =
+        # torch's scaled_dot_product_attention (the vendor flash kernel, 57 us on the same box), kept
+        # selectable for comparison only
         self.softmax_core = "auto"
         if qk_norm:
             self.q_norm = RMSNorm(d_model, scale_factor=1.0, eps=1e-6)
@@ -496,8 +514,8 @@ class MultiHeadCrossAttention(nn.Module):
             raise NotImplementedError("cross-attention mask must be None or a [B, L] 0/1 tensor")
         L = kv2d.shape[0] // B
         core = self.softmax_core
-        if core == "auto":  # the library's tcgen05 flash kernel is ~3.7x faster than ours in bf16
-            core = "sdpa" if q.dtype == torch.bfloat16 else "kernel"
+        if core == "auto":
+            core = "kernel" if hd % 8 == 0 and hd <= 128 else "sdpa"
         if core == "kernel":
             if hd % 8 != 0 or hd > 128:
                 raise NotImplementedError("the cross-attention kernel needs a head dimension that is a multiple of 8, <= 128")
@@ -547,13 +565,52 @@ class SanaMSBlock(nn.Module):
         self.attn.seq_shard = shard
         self.mlp.seq_shard = shard
 
-    def set_nvfp4(self, enabled: bool = True) -> None:
+    def set_nvfp4(self, enabled: bool = True, delayed_scaling: bool = False, margin: float = 1.0) -> None:
         """Run the qkv, attention-output and the two FFN 1x1 projections on the block-scaled FP4
         tensor cores (E2M1 values, E4M3 scales per 16 channels, fp32 scale per tensor, for both
         weights and activations).  Linear-attention state, depthwise conv, LayerNorm and the
-        cross-attention stay in bf16/fp32."""
+        cross-attention stay in bf16/fp32.
+
+        By default every activation is quantised with its own measured maximum, which costs two more
+        passes over it.  With ``delayed_scaling`` the kernels that produce the four activations write
+        FP4 directly (LayerNorm-modulate, attention apply) or note their maximum on the way (depthwise
+        conv), using per-tensor scales measured on the previous forward (times ``margin``); the first
+        forward after enabling it, and any forward after :meth:`recalibrate_nvfp4`, measures."""
         self.attn.nvfp4 = enabled
         self.mlp.nvfp4 = enabled
+        self.__dict__["_fp4_delayed"] = bool(enabled and delayed_scaling)
+        self.__dict__["_fp4_margin"] = float(margin)
+        self.__dict__["_fp4_state"] = None  # records + buffers, built by the calibrating forward
+
+    def recalibrate_nvfp4(self) -> None:
+        """The next forward measures the activation maxima again (delayed scaling)."""
+        self.__dict__["_fp4_state"] = None
+
+    _FP4_KEYS = (("attn", "qkv"), ("attn", "proj"), ("mlp", "inverted_conv"), ("mlp", "point_conv"))
+
+    def _fp4_calibrate(self, x, y, t, mask, HW, image_rotary_emb, kwargs):
+        """A measuring forward: the four activations' scales are copied into the records."""
+        seen_a, seen_m = {}, {}
+        self.attn.__dict__["_fp4_seen"], self.mlp.__dict__["_fp4_seen"] = seen_a, seen_m
+        self.__dict__["_fp4_delayed"] = False
+        try:
+            out = self.forward(x, y, t, mask, HW, image_rotary_emb, **kwargs)
+        finally:
+            self.__dict__["_fp4_delayed"] = True
+            del self.attn.__dict__["_fp4_seen"], self.mlp.__dict__["_fp4_seen"]
+        records = torch.zeros(4, 4, dtype=torch.float32, device=x.device)
+        for i, (owner, key) in enumerate(self._FP4_KEYS):
+            records[i, :2] = (seen_a if owner == "attn" else seen_m)[key][:2]
+        self.__dict__["_fp4_state"] = {"records": records, "bufs": {}}
+        return out
+
+    def _fp4_buf(self, idx: int, rows: int, K: int, device) -> "ops.Fp4Buffers":
+        st = self.__dict__["_fp4_state"]
+        buf = st["bufs"].get((idx, rows, K))
+        if buf is None:
+            buf = ops.Fp4Buffers(rows, K, device, record=st["records"][idx])
+            st["bufs"][(idx, rows, K)] = buf
+        return buf
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, HW=None, image_rotary_emb=None, **kwargs):
@@ -562,6 +619,31 @@ class SanaMSBlock(nn.Module):
         table = self.scale_shift_table
         t = t.reshape(B, 6 * C)
         attn, mlp, ca = self.attn, self.mlp, self.cross_attn
+        delayed = (self.__dict__.get("_fp4_delayed", False) and x.dtype == torch.bfloat16 and "forward" not in attn.__dict__
+                   and attn.seq_shard is None)
+        if delayed and self.__dict__.get("_fp4_state") is None:
+            return self._fp4_calibrate(x, y, t, mask, HW, image_rotary_emb, kwargs)
+        if delayed:
+            # activations quantised where they are produced, scales from the previous forward
+            rows, hid = B * N, mlp.hidden_features
+            ops.nvfp4_scale_roll(self.__dict__["_fp4_state"]["records"], self.__dict__["_fp4_margin"])
+            zq = ops.ln_modulate_fp4(x, table, t, 0, 1, self._fp4_buf(0, rows, C, x.device), LN_EPS)
+            qkv = _project(attn, "qkv", zq, attn.qkv.weight, bias=attn.qkv.bias)
+            oq = attn._core(qkv, B, N, image_rotary_emb, fp4_buf=self._fp4_buf(1, rows, C, x.device))
+            x2 = _project(attn, "proj", oq, attn.proj.weight, bias=attn.proj.bias, gate=(table, t, 2, N), residual=x2)
+            o = ca._attend(x2, y, mask, B, kwargs.get("caption_kv"))
+            x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
+            zq = ops.ln_modulate_fp4(x2.view(B, N, C), table, t, 3, 4, self._fp4_buf(2, rows, C, x.device), LN_EPS)
+            c1 = mlp.inverted_conv.conv
+            u = _project(mlp, "inverted_conv", zq, c1.weight.reshape(c1.out_channels, c1.in_channels), bias=c1.bias,
+                         act=ops.ACT_SILU)
+            buf = self._fp4_buf(3, rows, hid, x.device)
+            g = mlp._depthwise_glu(u, B, N, HW, amax_out=buf.record[2:3])
+            gq = ops.nvfp4_quantize_scaled(g, buf)
+            pc = mlp.point_conv.conv
+            x2 = _project(mlp, "point_conv", gq, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias,
+                          gate=(table, t, 5, N), residual=x2)
+            return x2.view(B, N, C)
         if "forward" in attn.__dict__:
             # an attention processor was installed on this instance (guidance code does that):
             # keep its semantics, at the cost of the fused epilogues
@@ -681,9 +763,9 @@ class BlockStack(nn.Module):
         for b in self.blocks:
             b.set_sequence_shard(shard)
 
-    def set_nvfp4(self, enabled: bool = True) -> None:
+    def set_nvfp4(self, enabled: bool = True, delayed_scaling: bool = False, margin: float = 1.0) -> None:
         for b in self.blocks:
-            b.set_nvfp4(enabled)
+            b.set_nvfp4(enabled, delayed_scaling, margin)
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, HW=None, **kwargs):

@@ -372,7 +372,8 @@ def take_cross_attention_device_status() -> int:
 
 
 def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], W: int, H: int, row0: int = 0,
-               halo_top: Optional[torch.Tensor] = None, halo_bot: Optional[torch.Tensor] = None) -> torch.Tensor:
+               halo_top: Optional[torch.Tensor] = None, halo_bot: Optional[torch.Tensor] = None,
+               amax_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """3x3 depthwise conv + bias + SiLU-GLU.  u [rows*W, 2*hid] (channels last, image rows
     stacked; frames are H rows tall, global row = row0 + local row); weight [2*hid, 1, 3, 3]
     or [2*hid, 3, 3]; halos [W, 2*hid].  Returns [rows*W, hid]."""
@@ -391,6 +392,15 @@ def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
             raise SanaLibraryError(f"dwconv_glu: {hname} must be contiguous [W, 2*hid] in u's dtype")
     out = torch.empty(T, hid, dtype=u.dtype, device=u.device)
     lib = _lib.load()
+    if amax_out is not None:  # bf16: also raise the device float amax_out[0] to max |out|
+        if u.dtype != torch.bfloat16 or amax_out.dtype != torch.float32:
+            raise SanaLibraryError("dwconv_glu: amax_out needs a bf16 input and an fp32 accumulator")
+        _lib.check(lib.sana_dwconv_glu_amax(u.data_ptr(), halo_top.data_ptr() if halo_top is not None else None,
+                                            halo_bot.data_ptr() if halo_bot is not None else None, weight.data_ptr(),
+                                            bias.contiguous().data_ptr() if bias is not None else None, out.data_ptr(), rows, W,
+                                            H, row0, hid, amax_out.data_ptr(), _stream()), "sana_dwconv_glu_amax")
+        counters.launches += 1
+        return out
     _lib.check(lib.sana_dwconv_glu(u.data_ptr(), halo_top.data_ptr() if halo_top is not None else None,
                                    halo_bot.data_ptr() if halo_bot is not None else None, weight.data_ptr(),
                                    bias.contiguous().data_ptr() if bias is not None else None, out.data_ptr(), rows, W, H,
@@ -541,6 +551,87 @@ def nvfp4_quantize(x: torch.Tensor) -> NvFp4Tensor:
                                        _stream()), "sana_nvfp4_quantize")
     counters.launches += 2
     return NvFp4Tensor(q, sf, scales, rows, K)
+
+
+class Fp4Buffers:
+    """Reusable output buffers of the kernels that emit NVFP4 directly: codes [rows, K/2], scale tiles
+    (zero-filled once: the kernels never write the bytes of padding rows and tiles) and the four-float
+    scale record {amax in use, tensor scale in use, amax seen since the last roll, unused}."""
+
+    def __init__(self, rows: int, K: int, device, record: Optional[torch.Tensor] = None):
+        lib = _lib.load()
+        self.rows, self.K = rows, K
+        self.q = torch.empty(rows, K // 2, dtype=torch.uint8, device=device)
+        self.sf = torch.zeros(lib.sana_nvfp4_sf_bytes(rows, K), dtype=torch.uint8, device=device)
+        self.record = record if record is not None else torch.zeros(4, dtype=torch.float32, device=device)
+
+    def tensor(self) -> NvFp4Tensor:
+        return NvFp4Tensor(self.q, self.sf, self.record, self.rows, self.K)
+
+
+def nvfp4_scale_roll(records: torch.Tensor, margin: float = 1.0) -> None:
+    """records [n, 4] fp32: adopts each record's "amax seen" (x margin) as its amax / tensor scale in use."""
+    _need_cuda(records)
+    if records.dtype != torch.float32 or not records.is_contiguous() or records.shape[-1] != 4:
+        raise SanaLibraryError("nvfp4_scale_roll: records must be contiguous fp32 [n, 4]")
+    _lib.check(_lib.load().sana_nvfp4_scale_roll(records.data_ptr(), records.numel() // 4, margin, _stream()),
+               "sana_nvfp4_scale_roll")
+    counters.launches += 1
+
+
+def nvfp4_quantize_scaled(x: torch.Tensor, buf: Fp4Buffers) -> NvFp4Tensor:
+    """Quantises bf16 x [rows, K] with the amax in buf.record[0] (nothing is measured)."""
+    _need_cuda(x)
+    rows, K, ld = _rows2d(x, "nvfp4_quantize_scaled x")
+    if x.dtype != torch.bfloat16 or (rows, K) != (buf.rows, buf.K):
+        raise SanaLibraryError("nvfp4_quantize_scaled: x must be bf16 of the buffers' shape")
+    _lib.check(_lib.load().sana_nvfp4_quantize_scaled(x.data_ptr(), ld, buf.q.data_ptr(), buf.sf.data_ptr(), buf.record.data_ptr(),
+                                                      rows, K, _stream()), "sana_nvfp4_quantize_scaled")
+    counters.launches += 1
+    return buf.tensor()
+
+
+def ln_modulate_fp4(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row: int, scale_row: int, buf: Fp4Buffers,
+                    eps: float = 1e-6, keep_bf16: bool = False):
+    """:func:`ln_modulate` (bf16) whose output is written as NVFP4 into ``buf`` with the tensor scale of
+    buf.record; the largest magnitude produced is accumulated into the record.  Returns the NvFp4Tensor
+    (and the bf16 tensor too with ``keep_bf16``)."""
+    _need_cuda(x, table, t)
+    B, N, Cc = x.shape
+    x = x.contiguous()
+    table = table.contiguous()
+    t = t.reshape(B, 6 * Cc).contiguous()
+    if x.dtype != torch.bfloat16 or table.shape != (6, Cc) or table.dtype != x.dtype or t.dtype != x.dtype:
+        raise SanaLibraryError("ln_modulate_fp4: bf16 x with table [6, C] and t [B, 6C] in the same dtype")
+    if (buf.rows, buf.K) != (B * N, Cc):
+        raise SanaLibraryError("ln_modulate_fp4: buffers sized for another shape")
+    z = torch.empty_like(x) if keep_bf16 else None
+    rec = buf.record
+    _lib.check(_lib.load().sana_ln_modulate_fp4(x.data_ptr(), table.data_ptr(), t.data_ptr(), z.data_ptr() if keep_bf16 else None,
+                                                buf.q.data_ptr(), buf.sf.data_ptr(), rec.data_ptr(), rec.data_ptr() + 8, B, N, Cc,
+                                                shift_row, scale_row, eps, _stream()), "sana_ln_modulate_fp4")
+    counters.launches += 1
+    return (buf.tensor(), z) if keep_bf16 else buf.tensor()
+
+
+def la_apply_fp4(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float, buf: Fp4Buffers,
+                 keep_bf16: bool = False):
+    """:func:`la_apply` (bf16) whose output is written as NVFP4 into ``buf`` (see :func:`ln_modulate_fp4`)."""
+    _need_cuda(q, state)
+    rq, cq, ldq = _rows2d(q, "la_apply_fp4 q")
+    if rq != B * N or cq != H * HEAD_DIM or q.dtype != torch.bfloat16:
+        raise SanaLibraryError("la_apply_fp4: q must be bf16 [B*N, H*32]")
+    if state.shape != (B, H, STATE_ROWS, HEAD_DIM) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise SanaLibraryError("la_apply_fp4: state must be contiguous fp32 [B, H, 33, 32]")
+    if (buf.rows, buf.K) != (B * N, H * HEAD_DIM):
+        raise SanaLibraryError("la_apply_fp4: buffers sized for another shape")
+    out = torch.empty(B * N, H * HEAD_DIM, dtype=q.dtype, device=q.device) if keep_bf16 else None
+    rec = buf.record
+    _lib.check(_lib.load().sana_la_apply_fp4(q.data_ptr(), ldq, state.data_ptr(), out.data_ptr() if keep_bf16 else None,
+                                             H * HEAD_DIM, buf.q.data_ptr(), buf.sf.data_ptr(), rec.data_ptr(), rec.data_ptr() + 8,
+                                             B, N, H, eps, _stream()), "sana_la_apply_fp4")
+    counters.launches += 1
+    return (buf.tensor(), out) if keep_bf16 else buf.tensor()
 
 
 def gemm_nvfp4(a: NvFp4Tensor, w: NvFp4Tensor, bias=None, act: int = ACT_NONE, relu_cols: int = 0, gate=None,

@@ -148,6 +148,115 @@ def test_nvfp4_block_cosine_at_the_benchmark_shape():
     assert ops.take_gemm_nvfp4_device_status() == 0 and ops.take_gemm_device_status() == 0
 
 
+def _same_fp4(a, b):
+    return torch.equal(a.q, b.q) and torch.equal(a.sf, b.sf)
+
+
+@pytest.mark.parametrize("B,N,C", [(2, 130, 256), (1, 1000, 2240), (3, 64, 96)])
+def test_ln_modulate_writes_the_same_fp4_as_the_two_step_path(B, N, C):
+    """The LayerNorm-modulate kernel that emits NVFP4 directly against ln_modulate (bf16) followed by the
+    stand-alone quantiser: with the same tensor maximum the codes and block scales are equal bit for bit,
+    the bf16 copy it can keep is the plain kernel's output, and it reports the maximum it produced."""
+    dt = torch.bfloat16
+    x = _r(B, N, C, seed=C).to(dt).to(DEV)
+    table = _r(6, C, seed=1, scale=0.3).to(dt).to(DEV)
+    t = _r(B, 6 * C, seed=2, scale=0.3).to(dt).to(DEV)
+    z = ops.ln_modulate(x, table, t, 3, 4)
+    ref = ops.nvfp4_quantize(z.reshape(B * N, C))
+    buf = ops.Fp4Buffers(B * N, C, DEV)
+    buf.record[:2] = ref.scales[:2]
+    got, z2 = ops.ln_modulate_fp4(x, table, t, 3, 4, buf, keep_bf16=True)
+    assert torch.equal(z2, z) and _same_fp4(got, ref)
+    assert buf.record[2].item() == ref.scales[0].item()  # the maximum it saw is the measured one
+    got = ops.ln_modulate_fp4(x, table, t, 3, 4, buf)  # without the bf16 copy
+    assert _same_fp4(got, ref)
+    # against the oracle's quantiser given the same maximum
+    vals, bs, ts = O.nvfp4_quantize(z.reshape(B * N, C).float().cpu(), amax=ref.scales[0].item())
+    assert torch.equal(got.dequantize().cpu(), O.nvfp4_dequantize(vals, bs, ts))
+    # a smaller maximum than the data's: values saturate exactly as in the oracle
+    buf.record[0] = ref.scales[0] * 0.5
+    buf.record[1] = ref.scales[1] * 0.5
+    got = ops.ln_modulate_fp4(x, table, t, 3, 4, buf)
+    vals, bs, ts = O.nvfp4_quantize(z.reshape(B * N, C).float().cpu(), amax=ref.scales[0].item() * 0.5)
+    assert torch.equal(got.dequantize().cpu(), O.nvfp4_dequantize(vals, bs, ts))
+
+
+@pytest.mark.parametrize("B,N,H", [(2, 200, 8), (1, 1024, 70), (1, 77, 3)])
+def test_la_apply_writes_the_same_fp4_as_the_two_step_path(B, N, H):
+    C = H * 32
+    g = torch.Generator().manual_seed(H)
+    qkv = torch.randn(B * N, 3 * C, generator=g).bfloat16().to(DEV)
+    state = ops.la_state(qkv[:, C:2 * C], qkv[:, 2 * C:], B, N, H)
+    o = ops.la_apply(qkv[:, :C], state, B, N, H, 1e-8)
+    if C % 32 != 0:
+        pytest.skip("K must be a multiple of 32")
+    ref = ops.nvfp4_quantize(o)
+    buf = ops.Fp4Buffers(B * N, C, DEV)
+    buf.record[:2] = ref.scales[:2]
+    got, o2 = ops.la_apply_fp4(qkv[:, :C], state, B, N, H, 1e-8, buf, keep_bf16=True)
+    assert torch.equal(o2, o) and _same_fp4(got, ref)
+    assert buf.record[2].item() == ref.scales[0].item()
+    assert _same_fp4(ops.la_apply_fp4(qkv[:, :C], state, B, N, H, 1e-8, buf), ref)
+
+
+def test_dwconv_reports_its_maximum_and_scaled_quantiser_matches():
+    hid, W, H = 160, 12, 9
+    u = _r(2 * H * W, 2 * hid, seed=4).bfloat16().to(DEV)
+    w = _r(2 * hid, 1, 3, 3, seed=5, scale=0.3).bfloat16().to(DEV)
+    b = _r(2 * hid, seed=6, scale=0.2).bfloat16().to(DEV)
+    ref = ops.dwconv_glu(u, w, b, W, H)
+    buf = ops.Fp4Buffers(2 * H * W, hid, DEV)
+    out = ops.dwconv_glu(u, w, b, W, H, amax_out=buf.record[2:3])
+    assert torch.equal(out, ref) and buf.record[2].item() == ref.float().abs().max().item()
+    ops.nvfp4_scale_roll(buf.record.view(1, 4))
+    assert buf.record[0].item() == ref.float().abs().max().item() and buf.record[2].item() == 0.0
+    measured = ops.nvfp4_quantize(ref)
+    assert buf.record[1].item() == measured.scales[1].item()
+    assert _same_fp4(ops.nvfp4_quantize_scaled(ref, buf), measured)
+
+
+@pytest.mark.parametrize("C,heads,B,HW,L", [(256, 4, 2, (12, 16), 20), (2240, 20, 2, (32, 32), 300)])
+def test_delayed_scaling_block(C, heads, B, HW, L):
+    """Block with the activations quantised where they are produced.  The first forward measures; a second
+    forward on the same input uses exactly the measured maxima and therefore reproduces the measuring path
+    bit for bit; a forward on other data runs on the previous forward's maxima (times a margin) and stays
+    within the cosine bar against the oracle block on dequantised tensors."""
+    import sana_b200
+    from sana_b200 import synthetic
+
+    dt = torch.bfloat16
+    shp = synthetic.BlockShape("fp4", C, heads, B, HW, text_len=L)
+    params = synthetic.make_block_params(C, shp.ffn_hidden, seed=11)
+    x, y, t = synthetic.make_block_inputs(shp, seed=11)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(params, strict=True)
+    blk = blk.to(DEV, dt)
+    xd, yd, td = x.to(DEV, dt), y.to(DEV, dt), t.to(DEV, dt)
+    blk.set_nvfp4(True)
+    measured = blk(xd, yd, td, None, HW)
+    blk.set_nvfp4(True, delayed_scaling=True, margin=1.0)
+    first = blk(xd, yd, td, None, HW)   # calibrating forward = the measuring path
+    second = blk(xd, yd, td, None, HW)  # producers emit FP4 with the maxima just measured
+    assert torch.equal(first, measured) and torch.equal(second, measured)
+    before = ops.counters.launches
+    blk(xd, yd, td, None, HW)
+    fused_launches = ops.counters.launches - before
+    blk.set_nvfp4(True)
+    before = ops.counters.launches
+    blk(xd, yd, td, None, HW)
+    assert fused_launches < ops.counters.launches - before  # fewer kernels than the measuring path
+    # other data, scales delayed by one forward (margin 1.25 as a serving loop would use)
+    blk.set_nvfp4(True, delayed_scaling=True, margin=1.25)
+    blk(xd, yd, td, None, HW)
+    x2 = (x * 0.9 + 0.05 * torch.randn(x.shape, generator=torch.Generator().manual_seed(1)))
+    out = blk(x2.to(DEV, dt), yd, td, None, HW)
+    r = lambda v: v.to(dt).float()
+    ref = O.sana_ms_block_forward(r(x2), r(y), r(t), {k: r(v) for k, v in params.items()}, heads, HW,
+                                  quant_fn=O.nvfp4_fake_quant)
+    assert cosine(out, ref) >= 0.995
+    assert ops.take_gemm_nvfp4_device_status() == 0
+
+
 def test_weight_pack_round_trip(tmp_path):
     """Pack the FP4 projection weights of a block, store, load into a fresh block whose bf16
     weights were wiped: the loaded block reproduces the packing block's FP4 output bit for bit
