@@ -212,6 +212,14 @@ int64_t sana_la_rope_state_workspace_bytes(int64_t B, int64_t N, int64_t H, int6
 int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
                        float* state, void* workspace, int64_t workspace_bytes, int64_t B, int64_t N, int64_t H,
                        int64_t D, int dtype, void* stream);
+/* The same state on top of one carried over from earlier token chunks: state = prior + (this call's sum); `prior`
+ * may be `state` itself.  Replaces `cumsum_vk += _vk; cumsum_k_sum += _k.sum(...)` of ChunkCausalAttention.forward
+ * (sana_blocks.py:486-488) and `vk = vk + cusum_vk; k_sum = k_sum + cumsum_k_sum` of CachedCausalAttention.forward
+ * (sana_blocks.py:551-554).  sana_add_f32: out = a + b on n fp32 values (combining two such states). */
+int sana_la_rope_state_add(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
+                           const float* prior, float* state, void* workspace, int64_t workspace_bytes, int64_t B,
+                           int64_t N, int64_t H, int64_t D, int dtype, void* stream);
+int sana_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
 int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_table, const float* sin_table,
                        const float* state, void* out, int64_t ldo, int64_t B, int64_t N, int64_t H, int64_t D,
                        float eps, int dtype, void* stream);

@@ -216,6 +216,94 @@ def lite_la_relu_rope_forward(x, p: Params, heads: int, rotary_emb: torch.Tensor
     return F.linear(out, p["proj.weight"], p["proj.bias"])
 
 
+def _relu_rope_qkv(x, p: Params, heads: int, rotary_emb: torch.Tensor, fp32_attention: bool, norm_eps: float):
+    """The part the three rotated attentions share (sana_blocks.py:413-450): projections, optional q / k norm,
+    head split, ReLU, rotation.  Returns q, k, v, q_rot, k_rot as [B, h, d, N] and the activation dtype."""
+    B, N, C = x.shape
+    hd = C // heads
+    qkv = F.linear(x, p["qkv.weight"], p.get("qkv.bias")).reshape(B, N, 3, C)
+    q, k, v = qkv.unbind(2)
+    dtype = q.dtype
+    if "q_norm.weight" in p:
+        q = rms_norm(q, p["q_norm.weight"], norm_eps)
+        k = rms_norm(k, p["k_norm.weight"], norm_eps)
+    q = F.relu(q.transpose(-1, -2).reshape(B, heads, hd, N))
+    k = F.relu(k.transpose(-1, -2).reshape(B, heads, hd, N))
+    v = v.transpose(-1, -2).reshape(B, heads, hd, N)
+    q_rot = rotate_pairs_complex(q, rotary_emb)
+    k_rot = rotate_pairs_complex(k, rotary_emb)
+    if fp32_attention:
+        q_rot, k_rot, v = q_rot.float(), k_rot.float(), v.float()
+    return q, k, v, q_rot, k_rot, dtype
+
+
+def chunk_causal_forward(x, p: Params, heads: int, rotary_emb: torch.Tensor, HW: Sequence[int], chunk_index=None,
+                         eps: float = 1e-15, fp32_attention: bool = False, norm_eps: float = 1e-5) -> torch.Tensor:
+    """ChunkCausalAttention.forward, diffusion/model/nets/sana_blocks.py:408-496: the frames are cut at
+    ``chunk_index``; a chunk's queries see the state summed over its own and all earlier chunks."""
+    B, N, C = x.shape
+    q, k, v, q_rot, k_rot, dtype = _relu_rope_qkv(x, p, heads, rotary_emb, fp32_attention, norm_eps)
+    f, h, w = HW
+    idx = (list(chunk_index) if chunk_index is not None else [0]) + [f]
+    sizes = [(b - a) * h * w for a, b in zip(idx[:-1], idx[1:])]
+    hd = C // heads
+    cum_vk = torch.zeros(B, heads, hd, hd, dtype=k_rot.dtype)
+    cum_ks = torch.zeros(B, heads, 1, hd, dtype=k_rot.dtype)
+    outs = []
+    for _qr, _kr, _v, _q, _k in zip(q_rot.split(sizes, -1), k_rot.split(sizes, -1), v.split(sizes, -1), q.split(sizes, -1),
+                                    k.split(sizes, -1)):
+        cum_vk += torch.matmul(_v, _kr.transpose(-1, -2))
+        cum_ks += _k.sum(dim=-1, keepdim=True).transpose(-2, -1)
+        z = 1 / (cum_ks @ _q + eps)
+        outs.append((torch.matmul(cum_vk, _qr) * z).to(dtype))
+    out = torch.cat(outs, dim=-1).view(B, C, N).permute(0, 2, 1)
+    return F.linear(out, p["proj.weight"], p["proj.bias"])
+
+
+def cached_causal_forward(x, p: Params, heads: int, rotary_emb: torch.Tensor, kv_cache=None, save_kv_cache: bool = False,
+                          eps: float = 1e-15, fp32_attention: bool = False, norm_eps: float = 1e-5):
+    """CachedCausalAttention.forward, diffusion/model/nets/sana_blocks.py:502-572: this chunk's vk and key sum,
+    plus the pair found in ``kv_cache[0:2]``; with ``save_kv_cache`` the cache takes THIS chunk's own pair
+    (before the addition).  Returns (out, kv_cache) when a cache list is given, else out."""
+    B, N, C = x.shape
+    q, k, v, q_rot, k_rot, dtype = _relu_rope_qkv(x, p, heads, rotary_emb, fp32_attention, norm_eps)
+    k_sum = k.sum(dim=-1, keepdim=True).transpose(-2, -1)
+    vk = torch.matmul(v, k_rot.transpose(-1, -2))
+    if kv_cache is not None:
+        prev_vk, prev_ks = kv_cache[0], kv_cache[1]
+        if save_kv_cache:
+            kv_cache[0], kv_cache[1] = vk.detach().clone(), k_sum.detach().clone()
+        if prev_vk is not None and prev_ks is not None:
+            vk = vk + prev_vk
+            k_sum = k_sum + prev_ks
+    z = 1 / (k_sum @ q + eps)
+    out = (torch.matmul(vk, q_rot) * z).to(dtype)
+    out = F.linear(out.view(B, C, N).permute(0, 2, 1), p["proj.weight"], p["proj.bias"])
+    return (out, kv_cache) if kv_cache is not None else out
+
+
+def cached_glumbconv_temp_forward(x, p: Params, HW: Sequence[int], kv_cache=None, save_kv_cache: bool = False):
+    """CachedGLUMBConvTemp.forward, diffusion/model/nets/basic_modules.py:364-397: GLUMBConv per frame, then the
+    3-tap temporal convolution whose left context is the last frame of the previous chunk (``kv_cache[-1]``,
+    [B, C, 1, H*W]) instead of zero padding; the right side is zero-padded."""
+    B, N, C = x.shape
+    T, H, W = HW
+    s = glumbconv_forward(x, p, HW)
+    xr = s.reshape(B, T, H * W, C).permute(0, 3, 1, 2)  # [B, C, T, HW]
+    wt = p["t_conv.weight"]
+    pad = wt.shape[2] // 2
+    x_in, padded = xr, 0
+    if kv_cache is not None:
+        if kv_cache[-1] is not None:
+            x_in = torch.cat([kv_cache[-1][:, :, -pad:], xr], dim=2)
+            padded = x_in.shape[2] - xr.shape[2]
+        if save_kv_cache:
+            kv_cache[-1] = xr[:, :, -pad:, :].detach().clone()
+    t_out = F.conv2d(x_in, wt, None, padding=(pad, 0))[:, :, padded:]
+    out = (xr + t_out).permute(0, 2, 3, 1).reshape(B, N, C)
+    return (out, kv_cache) if kv_cache is not None else out
+
+
 def lite_la_rope_state(k_relu: torch.Tensor, k_rot: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Token-major restatement of `vk` and of the key sum of LiteLAReLURope (sana_blocks.py:380-382):
     k_relu, k_rot, v [B, N, h, d] -> state [B, h, d+1, d]; rows 0..d-1 hold

@@ -607,16 +607,22 @@ la_rope_apply_f32_kernel(const float* __restrict__ qp, int64_t ldq, const float*
   }
 }
 
-// Adds the per-chunk partial states in chunk order (fixed order => bit-reproducible).
-__global__ void la_rope_reduce_kernel(const float* __restrict__ partial, float* __restrict__ state, int nchunks,
-                                      int64_t per_batch, int64_t total) {
+// Adds the per-chunk partial states in chunk order (fixed order => bit-reproducible), on top of `prior` when
+// one is given (the state carried over from earlier token chunks; it may be the output buffer itself).
+__global__ void la_rope_reduce_kernel(const float* __restrict__ partial, float* state, int nchunks, int64_t per_batch,
+                                      int64_t total, const float* prior) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t b = idx / per_batch, r = idx - b * per_batch;
   const float* p = partial + b * nchunks * per_batch + r;
-  float s = 0.f;
+  float s = prior ? prior[idx] : 0.f;
   for (int c = 0; c < nchunks; ++c) s += p[(int64_t)c * per_batch];
   state[idx] = s;
+}
+
+__global__ void add_f32_kernel(const float* a, const float* b, float* out, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = a[i] + b[i];
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -653,7 +659,7 @@ static void lr_state_plan(int64_t B, int64_t N, int64_t H, int* Lc, int* nchunks
 
 template <int D>
 static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t, const float* sin_t, float* state,
-                    float* partial, int64_t B, int64_t N, int64_t H, int dtype, cudaStream_t st) {
+                    float* partial, int64_t B, int64_t N, int64_t H, int dtype, cudaStream_t st, const float* prior) {
   int rc = lr_prepare<D>();
   if (rc != SANA_OK) return rc;
   int Lc, nchunks;
@@ -670,7 +676,7 @@ static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t
   }
   SANA_LAUNCH_CHECK("la_rope_state kernel");
   const int64_t per_batch = H * (int64_t)((D + 1) * D), total = B * per_batch;
-  la_rope_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(partial, state, nchunks, per_batch, total);
+  la_rope_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(partial, state, nchunks, per_batch, total, prior);
   SANA_LAUNCH_CHECK("la_rope_reduce kernel");
   return SANA_OK;
 }
@@ -743,9 +749,9 @@ extern "C" int64_t sana_la_rope_state_workspace_bytes(int64_t B, int64_t N, int6
   return lr_workspace_bytes(B, N, H, D);
 }
 
-extern "C" int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* cos_table,
-                                  const float* sin_table, float* state, void* workspace, int64_t workspace_bytes,
-                                  int64_t B, int64_t N, int64_t H, int64_t D, int dtype, void* stream) {
+static int la_rope_state_impl(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
+                              const float* prior, float* state, void* workspace, int64_t workspace_bytes, int64_t B,
+                              int64_t N, int64_t H, int64_t D, int dtype, void* stream) {
   SANA_REQUIRE(k && v && cos_table && sin_table && state && workspace, "sana_la_rope_state: null pointer");
   SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_rope_state: B, N, H must be positive");
   SANA_REQUIRE(lr_head_dim_ok(D), "sana_la_rope_state: head dimension must be a multiple of 16 in [16, 128]");
@@ -756,12 +762,34 @@ extern "C" int sana_la_rope_state(const void* k, const void* v, int64_t ld, cons
                    aligned16(workspace),
                "sana_la_rope_state: pointers must be 16-byte aligned");
   SANA_REQUIRE(workspace_bytes >= lr_workspace_bytes(B, N, H, D), "sana_la_rope_state: workspace too small");
+  SANA_REQUIRE(!prior || aligned16(prior), "sana_la_rope_state_add: prior must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
-#define LR_STATE(DD) lr_state<DD>(k, v, ld, cos_table, sin_table, state, partial, B, N, H, dtype, st)
+#define LR_STATE(DD) lr_state<DD>(k, v, ld, cos_table, sin_table, state, partial, B, N, H, dtype, st, prior)
   LR_DISPATCH(D, LR_STATE)
 #undef LR_STATE
   return fail(SANA_ERR_INVALID, "sana_la_rope_state: head dimension %lld", (long long)D);
+}
+
+extern "C" int sana_la_rope_state(const void* k, const void* v, int64_t ld, const float* cos_table,
+                                  const float* sin_table, float* state, void* workspace, int64_t workspace_bytes,
+                                  int64_t B, int64_t N, int64_t H, int64_t D, int dtype, void* stream) {
+  return la_rope_state_impl(k, v, ld, cos_table, sin_table, nullptr, state, workspace, workspace_bytes, B, N, H, D, dtype, stream);
+}
+
+extern "C" int sana_la_rope_state_add(const void* k, const void* v, int64_t ld, const float* cos_table,
+                                      const float* sin_table, const float* prior, float* state, void* workspace,
+                                      int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int dtype,
+                                      void* stream) {
+  SANA_REQUIRE(prior, "sana_la_rope_state_add: null prior");
+  return la_rope_state_impl(k, v, ld, cos_table, sin_table, prior, state, workspace, workspace_bytes, B, N, H, D, dtype, stream);
+}
+
+extern "C" int sana_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream) {
+  SANA_REQUIRE(a && b && out && n > 0, "sana_add_f32: bad arguments");
+  add_f32_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, n);
+  SANA_LAUNCH_CHECK("add_f32 kernel");
+  return SANA_OK;
 }
 
 extern "C" int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_table, const float* sin_table,

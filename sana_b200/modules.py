@@ -297,6 +297,81 @@ class ChunkedLiteLAReLURope(LiteLAReLURope):
         self.chunk_size = chunk_size
 
 
+class ChunkCausalAttention(LiteLAReLURope):
+    """Upstream's ChunkCausalAttention (sana_blocks.py:391-496): the frames of the (T, H, W) grid are cut at
+    ``chunk_index``; the queries of a chunk see the state summed over their own and all earlier chunks.  Per
+    sample and chunk one state launch (added on top of the running state) and one apply launch."""
+
+    def _core(self, qkv: torch.Tensor, B: int, N: int, rotary_emb, HW=None, chunk_index=None) -> torch.Tensor:
+        C, D, H = self.out_dim, self.dim, self.heads
+        if rotary_emb is None or HW is None or len(HW) != 3:
+            raise ValueError("ChunkCausalAttention needs rotary_emb and HW = (T, H, W)")
+        if self.seq_shard is not None:
+            raise NotImplementedError("chunk-causal attention on a sequence shard is not covered")
+        f, h, w = HW
+        if N != f * h * w:
+            raise ValueError(f"N={N} does not match HW={tuple(HW)}")
+        if isinstance(self.q_norm, RMSNorm):
+            ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
+            ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
+        cos, sin = self.rotary_tables(rotary_emb, N, qkv.device)
+        bounds = (list(chunk_index) if chunk_index is not None else [0]) + [f]
+        out = torch.empty(B * N, C, dtype=qkv.dtype, device=qkv.device)
+        for b in range(B):
+            state = None
+            for f0, f1 in zip(bounds[:-1], bounds[1:]):
+                n0, n1 = int(f0) * h * w, int(f1) * h * w
+                if n1 <= n0:
+                    continue
+                rows = slice(b * N + n0, b * N + n1)
+                c, sn = cos[n0:n1], sin[n0:n1]
+                state = ops.la_rope_state(qkv[rows, C:2 * C], qkv[rows, 2 * C:], c, sn, 1, n1 - n0, H, D, prior=state)
+                ops.la_rope_apply(qkv[rows, :C], c, sn, state, 1, n1 - n0, H, D, float(self.eps), out=out[rows])
+        return out
+
+    def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_mask=None, chunk_index=None, **kwargs):
+        B, N, C = x.shape
+        qkv = _project(self, "qkv", _as2d(x), self.qkv.weight, bias=self.qkv.bias)
+        o = self._core(qkv, B, N, rotary_emb, HW=HW, chunk_index=[0] if chunk_index is None else chunk_index)
+        return _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
+
+
+class CachedCausalAttention(LiteLAReLURope):
+    """Upstream's CachedCausalAttention (sana_blocks.py:498-572): one chunk of frames per call; the state of
+    this chunk's tokens is added to the pair found in ``kv_cache[0:2]`` (vk [B, h, d, d] and the key sum
+    [B, h, 1, d], fp32 here), and with ``save_kv_cache`` the cache takes THIS chunk's own pair.  Returns
+    (out, kv_cache) when a cache list is given, like upstream."""
+
+    def _core_cached(self, qkv: torch.Tensor, B: int, N: int, rotary_emb, kv_cache, save_kv_cache: bool) -> torch.Tensor:
+        C, D, H = self.out_dim, self.dim, self.heads
+        if rotary_emb is None:
+            raise ValueError("CachedCausalAttention needs rotary_emb (the frequencies of this chunk's tokens)")
+        if self.seq_shard is not None:
+            raise NotImplementedError("cached attention on a sequence shard is not covered")
+        if isinstance(self.q_norm, RMSNorm):
+            ops.rmsnorm_(qkv[:, :C], self.q_norm.weight, float(self.q_norm.eps))
+            ops.rmsnorm_(qkv[:, C:2 * C], self.k_norm.weight, float(self.k_norm.eps))
+        cos, sin = self.rotary_tables(rotary_emb, N, qkv.device)
+        cur = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, N, H, D)
+        state = cur
+        if kv_cache is not None:
+            prev_vk, prev_ks = kv_cache[0], kv_cache[1]
+            if save_kv_cache:
+                kv_cache[0], kv_cache[1] = cur[:, :, :D].clone(), cur[:, :, D:].clone()
+            if prev_vk is not None and prev_ks is not None:
+                prior = torch.cat([prev_vk.to(torch.float32), prev_ks.to(torch.float32)], dim=2).contiguous()  # layout only
+                state = ops.add_f32(cur, prior)
+        return ops.la_rope_apply(qkv[:, :C], cos, sin, state, B, N, H, D, float(self.eps))
+
+    def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_mask=None, save_kv_cache=False,
+                kv_cache=None, **kwargs):
+        B, N, C = x.shape
+        qkv = _project(self, "qkv", _as2d(x), self.qkv.weight, bias=self.qkv.bias)
+        o = self._core_cached(qkv, B, N, rotary_emb, kv_cache, bool(save_kv_cache))
+        out = _project(self, "proj", o, self.proj.weight, bias=self.proj.bias).reshape(B, N, C)
+        return (out, kv_cache) if kv_cache is not None else out
+
+
 class ConvLayer(nn.Module):
     """Parameter holder with upstream's ``conv`` / ``norm`` / ``act`` attributes
     (basic_modules.py:32-99) so checkpoints load unchanged; GLUMBConv reads the weights and
@@ -429,7 +504,7 @@ class GLUMBConvTemp(GLUMBConv):
 
     @torch.no_grad()
     def forward_gated(self, z: torch.Tensor, HW, x2: torch.Tensor, table: torch.Tensor, t2: torch.Tensor, row: int,
-                      rows_per_vec: int) -> torch.Tensor:
+                      rows_per_vec: int, kv_cache=None, save_kv_cache: bool = False) -> torch.Tensor:
         """``x2 + gate * forward(z)`` for the video block, [B*N, C]: ``gate`` = table[row] + t2[v, row] for
         the v-th run of ``rows_per_vec`` tokens (one modulation vector per sample, or per frame).  The
         spatial result enters through one fused multiply-add, the three temporal taps through the
@@ -447,6 +522,11 @@ class GLUMBConvTemp(GLUMBConv):
             raise ValueError(f"GLUMBConvTemp: modulation runs of {rows_per_vec} tokens fit neither a sample ({N}) "
                              f"nor a frame ({hw}) of the {tuple(HW)} grid")
         s = _as2d(GLUMBConv.forward(self, z, HW=HW))
+        prev = None
+        if kv_cache is not None:  # CachedGLUMBConvTemp: the previous chunk's last frame is the left context
+            prev = self._left_context(kv_cache, B, hw, C, s.dtype)
+            if save_kv_cache:
+                self._save_context(kv_cache, s, B, T, hw, C)
         vecs = (B * N) // rows_per_vec
         gate = (table[row].float()[None] + t2.reshape(vecs, 6, C)[:, row].float()).to(s.dtype)  # [vecs, C]
         y = torch.addcmul(x2.view(vecs, rows_per_vec, C), gate[:, None, :], s.view(vecs, rows_per_vec, C)).view(B * N, C)
@@ -463,7 +543,53 @@ class GLUMBConvTemp(GLUMBConv):
                          out=y[lo + hw:hi])
                 ops.gemm(s[lo + hw:hi], w_next, gate=(table, t2[v0:v0 + per_sample], row, rows_per_vec),
                          residual=y[lo:hi - hw], out=y[lo:hi - hw])
+            if prev is not None:  # frame 0 takes the cached frame through the previous-frame tap, under frame 0's gate
+                v0 = b * per_sample
+                ops.gemm(prev[b], w_prev, gate=(table, t2[v0:v0 + 1], row, hw), residual=y[lo:lo + hw], out=y[lo:lo + hw])
         return y
+
+
+class CachedGLUMBConvTemp(GLUMBConvTemp):
+    """Upstream's CachedGLUMBConvTemp (basic_modules.py:359-397): the temporal convolution's left context is
+    the last frame of the previous chunk, kept in ``kv_cache[-1]`` as [B, C, 1, H*W] (upstream's layout), instead
+    of zero padding; the right side stays zero-padded.  The cached frame is one more projection (the tap of the
+    previous frame) accumulated into the first frame's rows.  Returns (out, kv_cache) when a cache list is given."""
+
+    def _left_context(self, kv_cache, B: int, hw: int, C: int, dtype):
+        """The cached frame as token-major rows [B, hw, C], or None."""
+        if kv_cache is None or kv_cache[-1] is None:
+            return None
+        prev = kv_cache[-1][:, :, -1]  # [B, C, hw]
+        if prev.shape != (B, C, hw):
+            raise ValueError(f"cached frame has shape {tuple(prev.shape)}, expected {(B, C, hw)}")
+        return prev.to(dtype).permute(0, 2, 1).contiguous()
+
+    @staticmethod
+    def _save_context(kv_cache, s: torch.Tensor, B: int, T: int, hw: int, C: int) -> None:
+        kv_cache[-1] = s.view(B, T, hw, C)[:, -1].permute(0, 2, 1)[:, :, None].contiguous()
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, HW=None, save_kv_cache=False, kv_cache=None, **kwargs):
+        if HW is None or len(HW) != 3:
+            raise ValueError("HW must be a tuple of (T, H, W)")
+        B, N, C = x.shape
+        T, H, W = HW
+        hw = H * W
+        s = _as2d(GLUMBConv.forward(self, x, HW=HW))
+        prev = self._left_context(kv_cache, B, hw, C, s.dtype)
+        if kv_cache is not None and save_kv_cache:
+            self._save_context(kv_cache, s, B, T, hw, C)
+        w_prev, w_mid, w_next = self._taps()
+        y = ops.gemm(s, w_mid, residual=s)
+        for b in range(B):
+            lo, hi = b * N, (b + 1) * N
+            if T > 1:
+                ops.gemm(s[lo:hi - hw], w_prev, residual=y[lo + hw:hi], out=y[lo + hw:hi])
+                ops.gemm(s[lo + hw:hi], w_next, residual=y[lo:hi - hw], out=y[lo:hi - hw])
+            if prev is not None:
+                ops.gemm(prev[b], w_prev, residual=y[lo:lo + hw], out=y[lo:lo + hw])
+        out = y.reshape(B, N, C)
+        return (out, kv_cache) if kv_cache is not None else out
 
 
 class MultiHeadCrossAttention(nn.Module):
@@ -680,10 +806,12 @@ class SanaVideoMSBlock(nn.Module):
                  cross_attn_image_embeds=False, t_kernel_size=3, additional_flash_attn=False,
                  flash_attn_window_count=None, **block_kwargs):
         super().__init__()
-        attn_classes = {"linear": LiteLA, "LiteLAReLURope": LiteLAReLURope, "ChunkedLiteLAReLURope": ChunkedLiteLAReLURope}
-        if attn_type not in attn_classes or ffn_type not in ("glumbconv", "GLUMBConvTemp"):
-            raise NotImplementedError("SanaVideoMSBlock here covers attn_type 'linear' / 'LiteLAReLURope' / "
-                                      "'ChunkedLiteLAReLURope' with ffn_type 'glumbconv' / 'GLUMBConvTemp'")
+        attn_classes = {"linear": LiteLA, "LiteLAReLURope": LiteLAReLURope, "ChunkedLiteLAReLURope": ChunkedLiteLAReLURope,
+                        "ChunkCausalAttention": ChunkCausalAttention, "CachedCausalAttention": CachedCausalAttention}
+        ffn_classes = {"glumbconv": GLUMBConv, "GLUMBConvTemp": GLUMBConvTemp, "CachedGLUMBConvTemp": CachedGLUMBConvTemp}
+        if attn_type not in attn_classes or ffn_type not in ffn_classes:
+            raise NotImplementedError(f"SanaVideoMSBlock here covers attn_type {sorted(attn_classes)} with ffn_type "
+                                      f"{sorted(ffn_classes)}")
         if drop_path != 0.0 or cross_attn_image_embeds or additional_flash_attn:
             raise NotImplementedError("drop_path, image-embedding cross-attention and the additional softmax "
                                       "attention are not covered")
@@ -696,7 +824,7 @@ class SanaVideoMSBlock(nn.Module):
         self.norm2 = nn.LayerNorm(hidden_size, elementwise_affine=False, eps=LN_EPS)
         ffn = dict(in_features=hidden_size, hidden_features=int(hidden_size * mlp_ratio), use_bias=(True, True, False),
                    norm=(None, None, None), act=mlp_acts)
-        self.mlp = GLUMBConv(**ffn) if ffn_type == "glumbconv" else GLUMBConvTemp(t_kernel_size=t_kernel_size, **ffn)
+        self.mlp = GLUMBConv(**ffn) if ffn_type == "glumbconv" else ffn_classes[ffn_type](t_kernel_size=t_kernel_size, **ffn)
         self.drop_path = nn.Identity()
         self.scale_shift_table = nn.Parameter(torch.randn(6, hidden_size) / hidden_size ** 0.5)
         self.block_hook = None
@@ -712,8 +840,13 @@ class SanaVideoMSBlock(nn.Module):
 
     @torch.no_grad()
     def forward(self, x, y, t, mask=None, THW=None, rotary_emb=None, chunk_index=None, **kwargs):
-        if chunk_index is not None or kwargs.get("kv_cache") is not None or kwargs.get("save_kv_cache") is not None:
-            raise NotImplementedError("chunked / cached (autoregressive) inference is not covered")
+        kv_cache, save_kv_cache = kwargs.get("kv_cache"), bool(kwargs.get("save_kv_cache"))
+        if chunk_index is not None and not isinstance(self.attn, ChunkCausalAttention):
+            raise NotImplementedError("chunk_index needs attn_type 'ChunkCausalAttention'")
+        plain_temporal = isinstance(self.mlp, GLUMBConvTemp) and not isinstance(self.mlp, CachedGLUMBConvTemp)
+        if kv_cache is not None and (not isinstance(self.attn, CachedCausalAttention) or plain_temporal):
+            raise NotImplementedError("kv_cache needs attn_type 'CachedCausalAttention' (and 'CachedGLUMBConvTemp' or "
+                                      "'glumbconv' as ffn_type)")
         if self.block_hook is not None:
             raise NotImplementedError("block hooks are not covered")
         B, N, C = x.shape
@@ -733,19 +866,28 @@ class SanaVideoMSBlock(nn.Module):
         attn, mlp, ca = self.attn, self.mlp, self.cross_attn
         z = ops.ln_modulate(x2.view(-1, rows, C), table, t2, 0, 1, LN_EPS)
         qkv = _project(attn, "qkv", _as2d(z), attn.qkv.weight, bias=attn.qkv.bias)
-        o = attn._core(qkv, B, N, rotary_emb)
+        if isinstance(attn, ChunkCausalAttention):
+            o = attn._core(qkv, B, N, rotary_emb, HW=THW, chunk_index=[0] if chunk_index is None else list(chunk_index))
+        elif isinstance(attn, CachedCausalAttention):
+            o = attn._core_cached(qkv, B, N, rotary_emb, kv_cache, save_kv_cache)
+        else:
+            o = attn._core(qkv, B, N, rotary_emb)
         x2 = _project(attn, "proj", o, attn.proj.weight, bias=attn.proj.bias, gate=(table, t2, 2, rows), residual=x2)
         o = ca._attend(x2, y, mask, B, kwargs.get("caption_kv"))
         x2 = ops.gemm(o, ca.proj.weight, bias=ca.proj.bias, residual=x2)
         z = ops.ln_modulate(x2.view(-1, rows, C), table, t2, 3, 4, LN_EPS)
         if isinstance(mlp, GLUMBConvTemp):
-            x2 = mlp.forward_gated(z.view(B, N, C), THW, x2, table, t2, 5, rows)
+            cached = isinstance(mlp, CachedGLUMBConvTemp) and kv_cache is not None
+            x2 = mlp.forward_gated(z.view(B, N, C), THW, x2, table, t2, 5, rows, kv_cache=kv_cache if cached else None,
+                                   save_kv_cache=save_kv_cache)
         else:
             u = mlp._expand(_as2d(z))
             g = mlp._depthwise_glu(u, B, N, THW)
             pc = mlp.point_conv.conv
             x2 = _project(mlp, "point_conv", g, pc.weight.reshape(pc.out_channels, pc.in_channels), bias=pc.bias,
                           gate=(table, t2, 5, rows), residual=x2)
+        if kv_cache is not None:
+            return x2.view(B, N, C), kv_cache
         return x2.view(B, N, C)
 
 

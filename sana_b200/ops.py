@@ -288,10 +288,22 @@ def _rope_tables(cos: torch.Tensor, sin: torch.Tensor, N: int, D: int, what: str
             raise SanaLibraryError(f"{what}: cos / sin tables must be contiguous fp32 [N, head_dim / 2]")
 
 
+def add_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a + b for contiguous fp32 tensors of one shape (two attention states)."""
+    _need_cuda(a, b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape or not (a.is_contiguous() and b.is_contiguous()):
+        raise SanaLibraryError("add_f32: two contiguous fp32 tensors of one shape")
+    out = torch.empty_like(a)
+    _lib.check(_lib.load().sana_add_f32(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "sana_add_f32")
+    counters.launches += 1
+    return out
+
+
 def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, H: int,
-                  D: int) -> torch.Tensor:
+                  D: int, prior: Optional[torch.Tensor] = None) -> torch.Tensor:
     """State of the ReLU-then-rotate linear attention (see sana_la_rope_state): k, v [B*N, H*D]
-    views, cos / sin fp32 [N, D/2].  Returns fp32 [B, H, D+1, D]; row D is the unrotated key sum."""
+    views, cos / sin fp32 [N, D/2].  Returns fp32 [B, H, D+1, D]; row D is the unrotated key sum.
+    ``prior``: a state of the same shape carried over from earlier tokens, added in."""
     _need_cuda(k, v, cos, sin)
     rk, ck, ldk = _rows2d(k, "la_rope_state k")
     rv, cv, ldv = _rows2d(v, "la_rope_state v")
@@ -304,6 +316,14 @@ def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torc
         raise SanaLibraryError(f"la_rope_state: head dimension {D} is not a multiple of 16 in [16, 128]")
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=k.device)
     state = torch.empty(B, H, D + 1, D, dtype=torch.float32, device=k.device)
+    if prior is not None:
+        if prior.shape != state.shape or prior.dtype != torch.float32 or not prior.is_contiguous() or not prior.is_cuda:
+            raise SanaLibraryError("la_rope_state: prior must be a contiguous fp32 CUDA tensor [B, H, D+1, D]")
+        _lib.check(lib.sana_la_rope_state_add(k.data_ptr(), v.data_ptr(), ldk, cos.data_ptr(), sin.data_ptr(), prior.data_ptr(),
+                                              state.data_ptr(), ws.data_ptr(), ws.numel(), B, N, H, D, _dtype_code(k.dtype),
+                                              _stream()), "sana_la_rope_state_add")
+        counters.launches += 2
+        return state
     _lib.check(lib.sana_la_rope_state(k.data_ptr(), v.data_ptr(), ldk, cos.data_ptr(), sin.data_ptr(), state.data_ptr(),
                                       ws.data_ptr(), ws.numel(), B, N, H, D, _dtype_code(k.dtype), _stream()),
                "sana_la_rope_state")

@@ -183,6 +183,50 @@ def litela_relu_rope_case(R, seed=11):
     return out
 
 
+def causal_video_case(R, seed=13):
+    """Upstream's autoregressive variants of the Sana-Video block parts: ChunkCausalAttention (frames cut into
+    chunks, state cumulative over chunks), CachedCausalAttention and CachedGLUMBConvTemp (one chunk per call, the
+    state of the previous chunk handed over in a cache list)."""
+    C, heads, fhw, B, hid = 96, 2, (4, 3, 5), 2, 240
+    hw = fhw[1] * fhw[2]
+    N = fhw[0] * hw
+    g = torch.Generator().manual_seed(seed)
+    params = {"qkv.weight": torch.randn(3 * C, C, generator=g) * 0.08,
+              "proj.weight": torch.randn(C, C, generator=g) * 0.08,
+              "proj.bias": torch.randn(C, generator=g) * 0.05}
+    mlp = {k[len("mlp."):]: v for k, v in synthetic.make_block_params(C, hid, seed, std=0.05).items() if k.startswith("mlp.")}
+    mlp["t_conv.weight"] = torch.randn(C, C, 3, 1, generator=g) * 0.05
+    x = torch.randn(B, N, C, generator=g) * 0.7
+    rope = R.sana_blocks.WanRotaryPosEmbed(attention_head_dim=C // heads, patch_size=(1, 1, 1), max_seq_len=1024)
+    freqs = rope(fhw, torch.device("cpu"))
+    chunk_index = [0, 1, 3]  # chunks of 1, 2 and 1 frames
+    out = {"C": C, "heads": heads, "fhw": fhw, "hid": hid, "params": params, "mlp_params": mlp, "x": x, "freqs": freqs,
+           "chunk_index": chunk_index}
+    with torch.no_grad():
+        for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            m = R.sana_blocks.ChunkCausalAttention(C, C, heads=heads, eps=1e-8).eval()
+            m.load_state_dict(params, strict=True)
+            out[f"chunk_{tag}"] = m.to(dt)(x.to(dt), HW=fhw, rotary_emb=freqs, chunk_index=list(chunk_index))
+            # two calls of two frames each: the second sees the first one's state through the cache
+            m = R.sana_blocks.CachedCausalAttention(C, C, heads=heads, eps=1e-8).eval()
+            m.load_state_dict(params, strict=True)
+            m = m.to(dt)
+            f = R.basic_modules.CachedGLUMBConvTemp(in_features=C, hidden_features=hid, use_bias=(True, True, False),
+                                                    norm=(None, None, None), act=("silu", "silu", None)).eval()
+            f.load_state_dict(mlp, strict=True)
+            f = f.to(dt)
+            cache = [None, None, None]
+            half, fr = 2 * hw, freqs.reshape(1, 1, N, -1)
+            for i in range(2):
+                xs = x[:, i * half:(i + 1) * half].to(dt)
+                o, cache = m(xs, HW=(2, fhw[1], fhw[2]), rotary_emb=fr[:, :, i * half:(i + 1) * half], save_kv_cache=True,
+                             kv_cache=cache)
+                out[f"cached_attn{i}_{tag}"] = o
+                o, cache = f(xs, HW=(2, fhw[1], fhw[2]), save_kv_cache=True, kv_cache=cache)
+                out[f"cached_ffn{i}_{tag}"] = o
+    return out
+
+
 def video_block_case(ref_root, R, seed=12):
     """Upstream's SanaVideoMSBlock (LiteLAReLURope + cross-attention + GLUMBConvTemp) on 3 frames of
     4 x 5 tokens, with one modulation per sample and with one per frame."""
@@ -295,6 +339,7 @@ def main():
         "final_layer": lambda: final_layer_case(R),
         "litela_relu_rope": lambda: litela_relu_rope_case(R),
         "video_block": lambda: video_block_case(a.ref, R),
+        "causal_video": lambda: causal_video_case(R),
     }
     cases = {k: mk() for k, mk in makers.items() if a.only in (None, k)}
     for name, c in cases.items():
