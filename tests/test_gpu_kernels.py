@@ -282,11 +282,12 @@ def test_gemm_strided_operands():
 
 
 @pytest.mark.parametrize("variant", [1, 2])
-@pytest.mark.parametrize("M,N,K", [(2050, 328, 200), (77, 72, 64), (2307, 2240, 136)])
+@pytest.mark.parametrize("M,N,K", [(2050, 328, 200), (77, 72, 64), (2307, 2240, 136), (9450, 2240, 136), (9450, 2208, 72)])
 def test_gemm_staged_epilogue_edges(variant, M, N, K):
     """The bulk-tensor epilogue on ragged tiles: rows and columns that end inside a 32 x 64 box,
     the output a column slice of a wider buffer (its neighbours must stay untouched), the
-    residual read in place from the output location, bias + gate on top."""
+    residual read in place from the output location, bias + gate on top.  The 9 450-row cases are one eighth of a 75 600-token
+    grid (37 row tiles of the CTA-pair kernel, the last one 234 rows); N = 2208 ends in a 160-column tile."""
     rpb = 500
     B = (M + rpb - 1) // rpb
     a = _r(M, K, seed=M).bfloat16().to(DEV)
