@@ -117,7 +117,10 @@ extern "C" int sana_halo_exchange(const void* first_row, const void* last_row, i
   a.step = step;
   a.wait_limit_ns = exchange_wait_limit_ns();
   int64_t blocks = ceil_div(a.row_vecs, 256 * 4);
-  if (blocks > 64) blocks = 64;  // all resident at once: the last block to finish its copy waits for the peers
+  // only the block that finishes its copy last waits for the peers (the others exit), so the grid need not be
+  // resident at once; a conv row (a few MB at most) is latency-bound on 64 blocks, a whole frame takes more
+  const int64_t cap = row_bytes > (4 << 20) ? 2 * sm_count() : 64;
+  if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   halo_exchange_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   SANA_LAUNCH_CHECK("halo_exchange kernel");

@@ -481,25 +481,45 @@ class GLUMBConvTemp(GLUMBConv):
             self.__dict__["_tap_cache"] = cached
         return cached[1]
 
+    def _frame_halo(self, s: torch.Tensor, B: int):
+        """On a sequence shard: the frame before this rank's first token and the one after its last token,
+        fetched from the neighbours (upstream: cp_halo_exchange of one frame each side,
+        basic_modules.py:252-263).  (None, None) on one GPU."""
+        sh = self.seq_shard
+        if sh is None:
+            return None, None
+        if B != 1:
+            raise ValueError("sequence-parallel GLUMBConvTemp: batch must be 1")
+        return sh.exchange_frames(s)
+
     @torch.no_grad()
     def forward(self, x: torch.Tensor, HW=None, **kwargs) -> torch.Tensor:
         if HW is None or len(HW) != 3:
             raise ValueError("HW must be a tuple of (T, H, W)")
         if kwargs.get("frame_valid_mask") is not None:
             raise NotImplementedError("frame_valid_mask is not covered")
-        if self.seq_shard is not None:
-            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
         B, N, C = x.shape
         T, H, W = HW
         hw = H * W
         s = _as2d(super().forward(x, HW=HW))  # spatial result, token-major [B*N, C]
+        halo_prev, halo_next = self._frame_halo(s, B)
         w_prev, w_mid, w_next = self._taps()
         y = ops.gemm(s, w_mid, residual=s)  # x + centre tap
-        for b in range(B):  # frames t >= 1 take frame t-1, frames t <= T-2 take frame t+1 (zero padding at the ends)
+        # a token takes the token H*W places before it through the previous-frame tap and the one H*W places
+        # after it through the next-frame tap (zero padding at the ends of a sample); every row gets its
+        # previous-frame term before its next-frame term, on one GPU and on shards alike
+        for b in range(B):
             lo, hi = b * N, (b + 1) * N
-            if T > 1:
+            if N > hw:
                 ops.gemm(s[lo:hi - hw], w_prev, residual=y[lo + hw:hi], out=y[lo + hw:hi])
+        if halo_prev is not None:
+            ops.gemm(halo_prev, w_prev, residual=y[:hw], out=y[:hw])
+        for b in range(B):
+            lo, hi = b * N, (b + 1) * N
+            if N > hw:
                 ops.gemm(s[lo + hw:hi], w_next, residual=y[lo:hi - hw], out=y[lo:hi - hw])
+        if halo_next is not None:
+            ops.gemm(halo_next, w_next, residual=y[N - hw:N], out=y[N - hw:N])
         return y.reshape(B, N, C)
 
     @torch.no_grad()
@@ -511,17 +531,21 @@ class GLUMBConvTemp(GLUMBConv):
         gate + residual epilogue of their projections."""
         if HW is None or len(HW) != 3:
             raise ValueError("HW must be a tuple of (T, H, W)")
-        if self.seq_shard is not None:
-            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
         B, N, C = z.shape
         T, H, W = HW
         hw = H * W
-        if N != T * hw or rows_per_vec not in (N, hw):
+        sh = self.seq_shard
+        if sh is not None and kv_cache is not None:
+            raise NotImplementedError("the cached temporal Mix-FFN on a sequence shard is not covered")
+        whole = N == (T * hw if sh is None else sh.tokens)
+        per_frame_ok = N % hw == 0 and (sh is None or sh.row0 % H == 0)
+        if not whole or not (rows_per_vec == N or (rows_per_vec == hw and per_frame_ok)):
             # the taps of the previous / next frame take their gates by shifting t2 one vector, which is
-            # only right when a vector covers a whole sample or exactly one frame
+            # only right when a vector covers a whole sample or exactly one frame (on a shard: whole frames)
             raise ValueError(f"GLUMBConvTemp: modulation runs of {rows_per_vec} tokens fit neither a sample ({N}) "
                              f"nor a frame ({hw}) of the {tuple(HW)} grid")
         s = _as2d(GLUMBConv.forward(self, z, HW=HW))
+        halo_prev, halo_next = self._frame_halo(s, B)
         prev = None
         if kv_cache is not None:  # CachedGLUMBConvTemp: the previous chunk's last frame is the left context
             prev = self._left_context(kv_cache, B, hw, C, s.dtype)
@@ -531,21 +555,29 @@ class GLUMBConvTemp(GLUMBConv):
         gate = (table[row].float()[None] + t2.reshape(vecs, 6, C)[:, row].float()).to(s.dtype)  # [vecs, C]
         y = torch.addcmul(x2.view(vecs, rows_per_vec, C), gate[:, None, :], s.view(vecs, rows_per_vec, C)).view(B * N, C)
         w_prev, w_mid, w_next = self._taps()
-        per_sample = N // rows_per_vec  # modulation vectors per sample: 1, or T
+        per_sample = N // rows_per_vec  # modulation vectors per sample: 1, or the number of frames held
         y = ops.gemm(s, w_mid, gate=(table, t2, row, rows_per_vec), residual=y, out=y)
         for b in range(B):
             lo, hi = b * N, (b + 1) * N
-            if T > 1:
-                v0 = b * per_sample
-                # output frames 1 .. T-1 take frame t-1: their vectors start one frame later when per frame
+            v0 = b * per_sample
+            if N > hw:
+                # output frames 1 .. take frame t-1: their vectors start one frame later when per frame
                 t_hi = t2[v0 + (1 if per_sample > 1 else 0):v0 + per_sample]
                 ops.gemm(s[lo:hi - hw], w_prev, gate=(table, t_hi, row, rows_per_vec), residual=y[lo + hw:hi],
                          out=y[lo + hw:hi])
+            if prev is not None:  # frame 0 takes the cached frame through the previous-frame tap, under frame 0's gate
+                ops.gemm(prev[b], w_prev, gate=(table, t2[v0:v0 + 1], row, hw), residual=y[lo:lo + hw], out=y[lo:lo + hw])
+        if halo_prev is not None:  # the first frame's worth of rows takes the left neighbour's last one
+            ops.gemm(halo_prev, w_prev, gate=(table, t2[0:1], row, hw), residual=y[:hw], out=y[:hw])
+        for b in range(B):
+            lo, hi = b * N, (b + 1) * N
+            v0 = b * per_sample
+            if N > hw:
                 ops.gemm(s[lo + hw:hi], w_next, gate=(table, t2[v0:v0 + per_sample], row, rows_per_vec),
                          residual=y[lo:hi - hw], out=y[lo:hi - hw])
-            if prev is not None:  # frame 0 takes the cached frame through the previous-frame tap, under frame 0's gate
-                v0 = b * per_sample
-                ops.gemm(prev[b], w_prev, gate=(table, t2[v0:v0 + 1], row, hw), residual=y[lo:lo + hw], out=y[lo:lo + hw])
+        if halo_next is not None:  # ... and the last frame's worth the right neighbour's first one
+            ops.gemm(halo_next, w_next, gate=(table, t2[per_sample - 1:per_sample], row, hw), residual=y[N - hw:N],
+                     out=y[N - hw:N])
         return y
 
 
@@ -832,9 +864,11 @@ class SanaVideoMSBlock(nn.Module):
     def set_sequence_shard(self, shard: Optional[SequenceShard]) -> None:
         """Run this block on one rank's slice of the token grid (see sharding.SequenceShard): the partial
         attention states are summed over the ranks, the depthwise conv takes its halo rows from the
-        neighbours.  The temporal Mix-FFN is not covered on shards (frames would have to be exchanged)."""
-        if shard is not None and isinstance(self.mlp, GLUMBConvTemp):
-            raise NotImplementedError("GLUMBConvTemp on a sequence shard is not covered")
+        neighbours, the temporal Mix-FFN one frame from each neighbour (every rank must then hold at least one
+        frame's worth of rows; with one modulation vector per frame the cuts must lie between frames:
+        ``SequenceShard(..., by_frames=True)``)."""
+        if shard is not None and isinstance(self.mlp, CachedGLUMBConvTemp):
+            raise NotImplementedError("the cached temporal Mix-FFN on a sequence shard is not covered")
         self.attn.seq_shard = shard
         self.mlp.seq_shard = shard
 
@@ -855,9 +889,11 @@ class SanaVideoMSBlock(nn.Module):
             if N % frames:
                 raise ValueError("the token count is not a multiple of the frame count of t")
             rows = N // frames
-            if isinstance(self.mlp, GLUMBConvTemp) and (THW is None or frames != THW[0]):
-                raise ValueError(f"t carries {frames} modulation vectors per sample but the grid has "
-                                 f"{None if THW is None else THW[0]} frames: the temporal Mix-FFN needs one per frame")
+            sh = self.mlp.seq_shard
+            held = None if THW is None else (THW[0] if sh is None else sh.rows // sh.H)  # frames in x
+            if isinstance(self.mlp, GLUMBConvTemp) and frames != held:
+                raise ValueError(f"t carries {frames} modulation vectors per sample but x holds "
+                                 f"{held} frames: the temporal Mix-FFN needs one per frame")
         else:
             rows = N
         t2 = t.reshape(B * (N // rows), 6 * C)

@@ -91,9 +91,15 @@ class SequenceShard:
     rank: int
     world: int
     group: Optional[dist.ProcessGroup] = None
+    # cut between frames only (every rank holds whole frames, like upstream's context parallelism for
+    # video): no conv halo is needed then, and per-frame modulation vectors stay aligned with the shard
+    by_frames: bool = False
 
     def __post_init__(self):
-        self.ranges = row_partition(self.frames * self.H, self.world)
+        if self.by_frames:
+            self.ranges = [(a * self.H, b * self.H) for a, b in row_partition(self.frames, self.world)]
+        else:
+            self.ranges = row_partition(self.frames * self.H, self.world)
         self.row0, self.row1 = self.ranges[self.rank]
 
     @property
@@ -172,6 +178,42 @@ class SequenceShard:
     def fused_halo_exchange(self) -> bool:
         return getattr(self, "_halo_ptrs", None) is not None
 
+    def enable_fused_frame_exchange(self, channels: int, dtype: torch.dtype, device) -> None:
+        """Like :meth:`enable_fused_halo_exchange` for the temporal Mix-FFN's halo (`exchange_frames`): one
+        frame, H * W * channels elements, from each neighbour.  A buffer of its own, so the conv rows and the
+        frames of one block never share a slot.  Collective over the group; call once on every rank.
+        Like the conv rows' buffer it has ONE slot per side, which is safe inside a block (between two
+        exchanges lies the attention's state all-reduce, which no rank passes before every rank has consumed
+        the previous step's slot) but not for a Mix-FFN called on its own in a loop: use the send / receive
+        path there."""
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import ops
+
+        elems = self.H * self.W * channels
+        row_bytes = elems * torch.empty((), dtype=dtype).element_size()
+        buf = symm_mem.empty(ops.halo_exchange_buffer_bytes(row_bytes), dtype=torch.uint8, device=device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        self._frame_buf, self._frame_handle = buf, hdl
+        self._frame_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._frame_row = (channels, dtype, row_bytes)
+        self._frame_step = 0
+
+    @property
+    def fused_frame_exchange(self) -> bool:
+        return getattr(self, "_frame_ptrs", None) is not None
+
+    def fused_frame_status(self) -> int:
+        """Soft-error word of the frame exchange (bits as in :meth:`fused_halo_status`).  Synchronises."""
+        return int(self._frame_buf[20:24].view(torch.int32).item())
+
     def fused_halo_status(self) -> int:
         """Soft-error word of the halo kernel (0 = every wait completed; bit 0 = the upper, bit 1 =
         the lower neighbour did not arrive in time).  Synchronises."""
@@ -185,8 +227,13 @@ class SequenceShard:
         before results leave the GPU), not per block."""
         state = self.fused_exchange_status() if self.fused_state_exchange else 0
         halo = self.fused_halo_status() if self.fused_halo_exchange else 0
-        if state or halo:
+        frame = self.fused_frame_status() if self.fused_frame_exchange else 0
+        if state or halo or frame:
             who = []
+            if frame & 1:
+                who.append(f"rank {self.rank - 1} did not deliver its last frame")
+            if frame & 2:
+                who.append(f"rank {self.rank + 1} did not deliver its first frame")
             if state:
                 who.append(f"rank {state - 1} did not publish its attention state")
             if halo & 1:
@@ -254,6 +301,48 @@ class SequenceShard:
             for req in dist.batch_isend_irecv(ops):
                 req.wait()
         return top, bot
+
+    def exchange_frames(self, s: torch.Tensor) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """s [tokens, C]: this rank's rows of a per-token tensor (batch 1).  Returns (prev, next): the H * W
+        tokens that precede this rank's first token and those that follow its last one, i.e. what a 3-tap
+        convolution along the frame axis needs from the neighbours ([H*W, C] each; None at the two ends of
+        the grid, where the convolution pads with zeros).  Every rank must hold at least one frame's worth
+        of rows, so that both pieces come from the adjacent ranks (upstream exchanges whole frames the same
+        way: basic_modules.py:252-263 through halo_exchange.py:44-127)."""
+        hw = self.H * self.W
+        if min(b - a for a, b in self.ranges) < self.H:
+            raise ValueError(f"a rank holds fewer than {self.H} image rows: the frame halo would span several ranks")
+        if s.shape[0] != self.tokens:
+            raise ValueError("exchange_frames: s must hold this rank's tokens")
+        has_prev, has_next = self.rank > 0, self.rank < self.world - 1
+        if self.world == 1:
+            return None, None
+        if self.fused_frame_exchange:
+            from . import ops as K
+
+            channels, dtype, row_bytes = self._frame_row
+            if s.shape[1] != channels or s.dtype != dtype or not s.is_contiguous():
+                raise ValueError("fused frame exchange was sized for another tensor")
+            up = self._frame_ptrs[self.rank - 1] if has_prev else None
+            down = self._frame_ptrs[self.rank + 1] if has_next else None
+            self._frame_step += 1
+            K.halo_exchange(s[:hw].reshape(-1) if up else None, s[-hw:].reshape(-1) if down else None, row_bytes,
+                            self._frame_ptrs[self.rank], up, down, 0 if self.device_steps else self._frame_step)
+            rows = self._frame_buf[1024:1024 + 2 * row_bytes].view(dtype).view(2, hw, channels)
+            return (rows[0] if up else None), (rows[1] if down else None)
+        prev = torch.empty(hw, s.shape[1], dtype=s.dtype, device=s.device) if has_prev else None
+        nxt = torch.empty(hw, s.shape[1], dtype=s.dtype, device=s.device) if has_next else None
+        ops = []
+        peer = lambda r: r if self.group is None else dist.get_global_rank(self.group, r)
+        if has_prev:
+            ops.append(dist.P2POp(dist.isend, s[:hw].contiguous(), peer(self.rank - 1), self.group))
+            ops.append(dist.P2POp(dist.irecv, prev, peer(self.rank - 1), self.group))
+        if has_next:
+            ops.append(dist.P2POp(dist.isend, s[-hw:].contiguous(), peer(self.rank + 1), self.group))
+            ops.append(dist.P2POp(dist.irecv, nxt, peer(self.rank + 1), self.group))
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+        return prev, nxt
 
     def scatter_tokens(self, x_full: torch.Tensor) -> torch.Tensor:
         """[B, N, C] full sequence -> this rank's [B, tokens, C] slice (a copy)."""

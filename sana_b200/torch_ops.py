@@ -8,6 +8,17 @@ dtypes without touching the GPU.
     torch.ops.sana_b200.la_apply(q, state, B, N, H, eps)
     torch.ops.sana_b200.dwconv_glu(u, weight, bias, W, H, row0, halo_top, halo_bot)
     torch.ops.sana_b200.rmsnorm_(x, weight, eps)          # in place
+    torch.ops.sana_b200.rope_(x, cos, sin, B, N, head_dim)  # in place
+    torch.ops.sana_b200.cross_attention(q, k, v, mask, B, N, L, heads, head_dim)
+    torch.ops.sana_b200.la_rope_state(k, v, cos, sin, B, N, H, D, prior)
+    torch.ops.sana_b200.la_rope_apply(q, cos, sin, state, B, N, H, D, eps)
+    torch.ops.sana_b200.add_f32(a, b)
+    torch.ops.sana_b200.ln_modulate_rows(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps)
+    torch.ops.sana_b200.patchify(x, p) / unpatchify(tok, B, Cout, Hp, Wp, p)
+    torch.ops.sana_b200.timestep_embedding(t, dim, dtype, max_period) / silu(x)
+    torch.ops.sana_b200.nvfp4_quantize(x) -> (codes, scale_tiles, scales)
+    torch.ops.sana_b200.gemm_nvfp4(a_codes, a_sf, a_scales, w_codes, w_sf, w_scales, bias, act, relu_cols,
+                                   gate_table, gate_t, gate_row, rows_per_batch, residual)
 
 They are thin: each forwards to :mod:`sana_b200.ops`, which passes raw device pointers and the
 current stream to libsana_b200.so.  The modules call :mod:`sana_b200.ops` directly (same
@@ -15,7 +26,7 @@ kernels, without the dispatcher's per-call overhead).
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -87,3 +98,143 @@ def rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
 @rmsnorm_.register_fake
 def _(x, weight, eps):
     return None
+
+
+@torch.library.custom_op(f"{_lib_ns}::rope_", mutates_args=("x",))
+def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, head_dim: int) -> None:
+    ops.rope_(x, cos, sin, B, N, head_dim)
+
+
+@rope_.register_fake
+def _(x, cos, sin, B, N, head_dim):
+    return None
+
+
+@torch.library.custom_op(f"{_lib_ns}::cross_attention", mutates_args=())
+def cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Optional[torch.Tensor], B: int, N: int,
+                    L: int, heads: int, head_dim: int) -> torch.Tensor:
+    return ops.cross_attention(q, k, v, mask, B, N, L, heads, head_dim)
+
+
+@cross_attention.register_fake
+def _(q, k, v, mask, B, N, L, heads, head_dim):
+    return q.new_empty(B * N, heads * head_dim)
+
+
+@torch.library.custom_op(f"{_lib_ns}::la_rope_state", mutates_args=())
+def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, H: int,
+                  D: int, prior: Optional[torch.Tensor]) -> torch.Tensor:
+    return ops.la_rope_state(k, v, cos, sin, B, N, H, D, prior=prior)
+
+
+@la_rope_state.register_fake
+def _(k, v, cos, sin, B, N, H, D, prior):
+    return k.new_empty(B, H, D + 1, D, dtype=torch.float32)
+
+
+@torch.library.custom_op(f"{_lib_ns}::la_rope_apply", mutates_args=())
+def la_rope_apply(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int,
+                  D: int, eps: float) -> torch.Tensor:
+    return ops.la_rope_apply(q, cos, sin, state, B, N, H, D, eps)
+
+
+@la_rope_apply.register_fake
+def _(q, cos, sin, state, B, N, H, D, eps):
+    return q.new_empty(B * N, H * D)
+
+
+@torch.library.custom_op(f"{_lib_ns}::add_f32", mutates_args=())
+def add_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    return ops.add_f32(a, b)
+
+
+@add_f32.register_fake
+def _(a, b):
+    return torch.empty_like(a)
+
+
+@torch.library.custom_op(f"{_lib_ns}::ln_modulate_rows", mutates_args=())
+def ln_modulate_rows(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, table_shift_row: int, table_scale_row: int,
+                     t_shift_row: int, t_scale_row: int, eps: float) -> torch.Tensor:
+    return ops.ln_modulate_rows(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps)
+
+
+@ln_modulate_rows.register_fake
+def _(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op(f"{_lib_ns}::patchify", mutates_args=())
+def patchify(x: torch.Tensor, p: int) -> torch.Tensor:
+    return ops.patchify(x, p)
+
+
+@patchify.register_fake
+def _(x, p):
+    B, Cin, H, W = x.shape
+    return x.new_empty(B * (H // p) * (W // p), Cin * p * p)
+
+
+@torch.library.custom_op(f"{_lib_ns}::unpatchify", mutates_args=())
+def unpatchify(tok: torch.Tensor, B: int, Cout: int, Hp: int, Wp: int, p: int) -> torch.Tensor:
+    return ops.unpatchify(tok, B, Cout, Hp, Wp, p)
+
+
+@unpatchify.register_fake
+def _(tok, B, Cout, Hp, Wp, p):
+    return tok.new_empty(B, Cout, Hp * p, Wp * p)
+
+
+@torch.library.custom_op(f"{_lib_ns}::timestep_embedding", mutates_args=())
+def timestep_embedding(t: torch.Tensor, dim: int, dtype: torch.dtype, max_period: float) -> torch.Tensor:
+    return ops.timestep_embedding(t, dim, dtype, max_period)
+
+
+@timestep_embedding.register_fake
+def _(t, dim, dtype, max_period):
+    return t.new_empty(t.numel(), dim, dtype=dtype)
+
+
+@torch.library.custom_op(f"{_lib_ns}::silu", mutates_args=())
+def silu(x: torch.Tensor) -> torch.Tensor:
+    return ops.silu(x)
+
+
+@silu.register_fake
+def _(x):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+def _sf_bytes(rows: int, K: int) -> int:
+    """Bytes of the E4M3 scale tiles of a [rows, K] NVFP4 matrix: 512-byte tiles of 128 rows x 4 blocks of 16."""
+    return ((rows + 127) // 128) * ((K // 16 + 3) // 4) * 512
+
+
+@torch.library.custom_op(f"{_lib_ns}::nvfp4_quantize", mutates_args=())
+def nvfp4_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    t = ops.nvfp4_quantize(x)
+    return t.q, t.sf, t.scales
+
+
+@nvfp4_quantize.register_fake
+def _(x):
+    rows, K = x.shape
+    return (x.new_empty(rows, K // 2, dtype=torch.uint8), x.new_empty(_sf_bytes(rows, K), dtype=torch.uint8),
+            x.new_empty(4, dtype=torch.float32))
+
+
+@torch.library.custom_op(f"{_lib_ns}::gemm_nvfp4", mutates_args=())
+def gemm_nvfp4(a_codes: torch.Tensor, a_sf: torch.Tensor, a_scales: torch.Tensor, w_codes: torch.Tensor,
+               w_sf: torch.Tensor, w_scales: torch.Tensor, bias: Optional[torch.Tensor], act: int, relu_cols: int,
+               gate_table: Optional[torch.Tensor], gate_t: Optional[torch.Tensor], gate_row: int, rows_per_batch: int,
+               residual: Optional[torch.Tensor]) -> torch.Tensor:
+    a = ops.NvFp4Tensor(a_codes, a_sf, a_scales, a_codes.shape[0], 2 * a_codes.shape[1])
+    w = ops.NvFp4Tensor(w_codes, w_sf, w_scales, w_codes.shape[0], 2 * w_codes.shape[1])
+    gate = (gate_table, gate_t, gate_row, rows_per_batch) if gate_table is not None else None
+    return ops.gemm_nvfp4(a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual)
+
+
+@gemm_nvfp4.register_fake
+def _(a_codes, a_sf, a_scales, w_codes, w_sf, w_scales, bias, act, relu_cols, gate_table, gate_t, gate_row,
+      rows_per_batch, residual):
+    return a_codes.new_empty(a_codes.shape[0], w_codes.shape[0], dtype=torch.bfloat16)

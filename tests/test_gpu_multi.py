@@ -253,6 +253,58 @@ def _fused_halo_and_graph(rank, world):
     return out
 
 
+def _video_block_shards(rank, world):
+    """The video block (rotated linear attention + temporal Mix-FFN) on two ranks: the temporal halo through
+    send / receive, then through the peer-memory kernel, against the unsharded block on the same GPU."""
+    import sana_b200
+    from sana_b200 import sharding, synthetic
+
+    dev, dt = torch.device("cuda", rank), torch.bfloat16
+    C, heads, hid, THW, L = 448, 4, 1120, (4, 10, 16), 24
+    F_, H, W = THW
+    N = F_ * H * W
+    g = torch.Generator().manual_seed(5)
+    p = synthetic.make_block_params(C, hid, seed=3, std=0.05)
+    p["mlp.t_conv.weight"] = torch.randn(C, C, 3, 1, generator=g) * 0.03
+    blk = sana_b200.SanaVideoMSBlock(C, heads, mlp_ratio=hid / C, attn_type="LiteLAReLURope", ffn_type="GLUMBConvTemp",
+                                     linear_head_dim=C // heads).eval()
+    blk.load_state_dict(p, strict=True)
+    blk = blk.to(dev, dt)
+    x = (torch.randn(1, N, C, generator=g) * 0.5).to(dev, dt)
+    y = (torch.randn(1, L, C, generator=g) * 0.5).to(dev, dt)
+    fr = sana_b200.wan_rotary_freqs(C // heads, THW)
+    out = {}
+    for name, by_frames, t in (("rows", False, torch.randn(1, 6 * C, generator=g) * 0.2),
+                               ("frames", True, torch.randn(1, 1, F_, 6 * C, generator=g) * 0.2)):
+        t = t.to(dev, dt)
+        blk.set_sequence_shard(None)
+        full = blk(x, y, t, THW=THW, rotary_emb=fr)
+        sh = sharding.SequenceShard(*THW, rank, world, by_frames=by_frames)
+        a, b = sh.token_range
+        tl = t[:, :, a // (H * W):b // (H * W)].contiguous() if by_frames else t
+        blk.set_sequence_shard(sh)
+        ref = full[:, a:b].float()
+        err = lambda o: ((o.float() - ref).abs().max() / full.float().abs().max()).item()
+        worst = err(blk(x[:, a:b].contiguous(), y, tl, THW=THW, rotary_emb=fr))
+        sh.enable_fused_frame_exchange(C, dt, dev)
+        fused = max(err(blk(x[:, a:b].contiguous(), y, tl, THW=THW, rotary_emb=fr)) for _ in range(3))
+        torch.cuda.synchronize()
+        out[name] = {"nccl": worst, "fused": fused, "status": sh.fused_frame_status()}
+        sh.check()
+        dist.barrier()
+    return out
+
+
+def test_video_block_with_temporal_halo_on_two_gpus():
+    _need(2)
+    res = _run(2, _video_block_shards)
+    assert len(res) == 2, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        for name, p in payload.items():
+            assert p["status"] == 0 and p["nccl"] < 1e-2 and p["fused"] < 1e-2, (name, p)
+
+
 def test_fused_halo_exchange_and_graph_replay_on_two_gpus():
     _need(2)
     res = _run(2, _fused_halo_and_graph)

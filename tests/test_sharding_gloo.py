@@ -194,3 +194,59 @@ def test_sequence_parallel_rotated_attention_matches_single_process(world):
     for r, (status, payload) in res.items():
         assert status == "ok", payload
         assert payload < 1e-12, payload
+
+
+def _seqpar_temporal_ffn(rank, world, by_frames=False):
+    """GLUMBConvTemp per shard: the conv's one-row halo, then one frame of the spatial result from each
+    neighbour for the 3-tap convolution along the frame axis (`SequenceShard.exchange_frames`)."""
+    from oracle import sana_oracle as O
+    from sana_b200 import sharding, synthetic
+
+    torch.set_num_threads(2)
+    C, hid, frames, H, W = 32, 80, 4, 5, 4
+    hw, dt = H * W, torch.float64
+    p = {k[4:]: v.to(dt) for k, v in synthetic.make_block_params(C, hid, seed=4, std=0.1).items() if k.startswith("mlp.")}
+    g = torch.Generator().manual_seed(8)
+    p["t_conv.weight"] = torch.randn(C, C, 3, 1, generator=g, dtype=dt) * 0.1
+    x = torch.randn(1, frames * hw, C, generator=g, dtype=dt)
+    full = O.glumbconv_temp_forward(x, p, (frames, H, W))
+    sh = sharding.SequenceShard(frames, H, W, rank, world, by_frames=by_frames)
+    a, b = sh.token_range
+    xs = sh.scatter_tokens(x)[0]
+    lin = torch.nn.functional.linear
+    u = torch.nn.functional.silu(lin(xs, p["inverted_conv.conv.weight"].reshape(-1, C), p["inverted_conv.conv.bias"]))
+    top, bot = sh.exchange_halo(u)
+    gl = O.depthwise_glu_rows(u.reshape(sh.rows, W, -1), top, bot, p["depth_conv.conv.weight"], p["depth_conv.conv.bias"],
+                              sh.row0, H).reshape(sh.tokens, -1)
+    s = lin(gl, p["point_conv.conv.weight"].reshape(C, -1))
+    prev, nxt = sh.exchange_frames(s)
+    assert (prev is None) == (rank == 0) and (nxt is None) == (rank == world - 1)
+    zeros = torch.zeros(hw, C, dtype=dt)
+    ext = torch.cat([zeros if prev is None else prev, s, zeros if nxt is None else nxt])
+    wt, n = p["t_conv.weight"], sh.tokens
+    out = s + lin(ext[:n], wt[:, :, 0, 0]) + lin(ext[hw:hw + n], wt[:, :, 1, 0]) + lin(ext[2 * hw:2 * hw + n], wt[:, :, 2, 0])
+    ref = full[0, a:b]
+    return ((out - ref).abs().max() / ref.abs().max()).item()
+
+
+def _seqpar_temporal_ffn_by_frames(rank, world):
+    return _seqpar_temporal_ffn(rank, world, by_frames=True)
+
+
+@pytest.mark.parametrize("world,fn", [(2, _seqpar_temporal_ffn), (3, _seqpar_temporal_ffn), (4, _seqpar_temporal_ffn),
+                                      (2, _seqpar_temporal_ffn_by_frames), (4, _seqpar_temporal_ffn_by_frames)])
+def test_sequence_parallel_temporal_ffn_matches_single_process(world, fn):
+    res = _run(world, fn)
+    assert len(res) == world, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        assert payload < 1e-12, payload
+
+
+def test_frame_partition_and_frame_halo_guard():
+    from sana_b200 import sharding
+
+    assert sharding.SequenceShard(5, 6, 4, 1, 2, by_frames=True).ranges == [(0, 18), (18, 30)]
+    sh = sharding.SequenceShard(2, 6, 4, 0, 4)  # 3 rows per rank < 6 rows per frame
+    with pytest.raises(ValueError):
+        sh.exchange_frames(torch.zeros(sh.tokens, 8))

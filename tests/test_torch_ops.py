@@ -10,7 +10,9 @@ from sana_b200 import ops
 def test_operators_are_registered_with_fake_implementations():
     from torch._subclasses.fake_tensor import FakeTensorMode
 
-    for name in ("gemm", "ln_modulate", "la_state", "la_apply", "dwconv_glu", "rmsnorm_"):
+    for name in ("gemm", "ln_modulate", "la_state", "la_apply", "dwconv_glu", "rmsnorm_", "rope_", "cross_attention",
+                 "la_rope_state", "la_rope_apply", "add_f32", "ln_modulate_rows", "patchify", "unpatchify",
+                 "timestep_embedding", "silu", "nvfp4_quantize", "gemm_nvfp4"):
         assert hasattr(torch.ops.sana_b200, name), name
     with FakeTensorMode():
         a = torch.empty(100, 64, dtype=torch.bfloat16)
@@ -46,3 +48,67 @@ def test_custom_ops_match_the_direct_path():
     wt = torch.ones(64, dtype=torch.bfloat16, device="cuda")
     torch.ops.sana_b200.rmsnorm_(x, wt, 1e-6)
     assert torch.equal(x, ops.rmsnorm_(ref, wt, 1e-6))
+
+
+def test_remaining_operators_propagate_shapes_without_a_gpu():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    bf = torch.bfloat16
+    with FakeTensorMode():
+        q = torch.empty(2 * 50, 224, dtype=bf)
+        kv = torch.empty(2 * 9, 448, dtype=bf)
+        o = torch.ops.sana_b200.cross_attention(q, kv[:, :224], kv[:, 224:], torch.empty(2, 9), 2, 50, 9, 2, 112)
+        assert o.shape == (100, 224) and o.dtype == bf
+        cos = torch.empty(50, 56)
+        st = torch.ops.sana_b200.la_rope_state(q, q, cos, cos, 2, 50, 2, 112, None)
+        assert st.shape == (2, 2, 113, 112) and st.dtype == torch.float32
+        st2 = torch.ops.sana_b200.la_rope_state(q, q, cos, cos, 2, 50, 2, 112, st)
+        assert torch.ops.sana_b200.add_f32(st, st2).shape == st.shape
+        assert torch.ops.sana_b200.la_rope_apply(q, cos, cos, st, 2, 50, 2, 112, 1e-8).shape == (100, 224)
+        assert torch.ops.sana_b200.rope_(q, torch.empty(50, 32), torch.empty(50, 32), 2, 50, 32) is None
+        z = torch.ops.sana_b200.ln_modulate_rows(torch.empty(2, 50, 64, dtype=bf), torch.empty(2, 64, dtype=bf),
+                                                 torch.empty(2, 1, 64, dtype=bf), 0, 1, 0, 0, 1e-6)
+        assert z.shape == (2, 50, 64)
+        pt = torch.ops.sana_b200.patchify(torch.empty(2, 32, 16, 8, dtype=bf), 2)
+        assert pt.shape == (2 * 8 * 4, 128)
+        assert torch.ops.sana_b200.unpatchify(pt, 2, 32, 8, 4, 2).shape == (2, 32, 16, 8)
+        te = torch.ops.sana_b200.timestep_embedding(torch.empty(3), 256, bf, 10000.0)
+        assert te.shape == (3, 256) and te.dtype == bf
+        assert torch.ops.sana_b200.silu(te).shape == (3, 256)
+        a = torch.empty(300, 64, dtype=bf)
+        qa = torch.ops.sana_b200.nvfp4_quantize(a)
+        assert qa[0].shape == (300, 32) and qa[1].numel() == 3 * 1 * 512 and qa[2].shape == (4,)
+        qw = torch.ops.sana_b200.nvfp4_quantize(torch.empty(96, 64, dtype=bf))
+        out = torch.ops.sana_b200.gemm_nvfp4(*qa, *qw, None, 0, 0, None, None, 0, 1, None)
+        assert out.shape == (300, 96) and out.dtype == bf
+
+
+@pytest.mark.gpu
+def test_remaining_custom_ops_match_the_direct_path():
+    g = torch.Generator().manual_seed(1)
+    bf = torch.bfloat16
+    B, N, L, h, hd = 2, 130, 20, 2, 112
+    q = torch.randn(B * N, h * hd, generator=g).to(bf).cuda()
+    kv = torch.randn(B * L, 2 * h * hd, generator=g).to(bf).cuda()
+    mask = (torch.rand(B, L, generator=g) > 0.2).float().cuda()
+    assert torch.equal(torch.ops.sana_b200.cross_attention(q, kv[:, :h * hd], kv[:, h * hd:], mask, B, N, L, h, hd),
+                       ops.cross_attention(q, kv[:, :h * hd], kv[:, h * hd:], mask, B, N, L, h, hd))
+    ang = torch.randn(N, hd // 2, generator=g).cuda()
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    st = torch.ops.sana_b200.la_rope_state(q, q, cos, sin, B, N, h, hd, None)
+    assert torch.equal(st, ops.la_rope_state(q, q, cos, sin, B, N, h, hd))
+    assert torch.equal(torch.ops.sana_b200.la_rope_state(q, q, cos, sin, B, N, h, hd, st),
+                       ops.la_rope_state(q, q, cos, sin, B, N, h, hd, prior=st))
+    assert torch.equal(torch.ops.sana_b200.la_rope_apply(q, cos, sin, st, B, N, h, hd, 1e-8),
+                       ops.la_rope_apply(q, cos, sin, st, B, N, h, hd, 1e-8))
+    assert torch.equal(torch.ops.sana_b200.add_f32(st, st), st + st)
+    lat = torch.randn(2, 32, 16, 8, generator=g).to(bf).cuda()
+    pt = torch.ops.sana_b200.patchify(lat, 2)
+    assert torch.equal(pt, ops.patchify(lat, 2))
+    assert torch.equal(torch.ops.sana_b200.unpatchify(pt, 2, 32, 8, 4, 2), ops.unpatchify(pt, 2, 32, 8, 4, 2))
+    a = torch.randn(300, 64, generator=g).to(bf).cuda()
+    w = (torch.randn(96, 64, generator=g) * 0.1).to(bf).cuda()
+    qa, qw = torch.ops.sana_b200.nvfp4_quantize(a), torch.ops.sana_b200.nvfp4_quantize(w)
+    da, dw = ops.nvfp4_quantize(a), ops.nvfp4_quantize(w)
+    assert torch.equal(qa[0], da.q) and torch.equal(qa[1], da.sf) and torch.equal(qa[2][:2], da.scales[:2])
+    assert torch.equal(torch.ops.sana_b200.gemm_nvfp4(*qa, *qw, None, 0, 0, None, None, 0, 1, None), ops.gemm_nvfp4(da, dw))
