@@ -20,7 +20,14 @@
 // Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 91 us per sample.  The 33 tcgen05.mma of a tile
 // alone take about 4 500 cycles - an instruction with M = 128 costs about 130 cycles whether N is 112 or 256 -
 // and the softmax warps about 8 000; a single-pass softmax with the shift fixed up on the fly and a split of a
-// row's columns over two warps were both tried and were slower (110 - 120 us).
+// row's columns over two warps were both tried and were slower (110 - 120 us).  So was keeping a whole chunk of
+// the row in registers (160 of 232, taken from the other warpgroups with setmaxnreg) to read tensor memory once
+// instead of twice: 104 us.  What that showed: a tcgen05.ld / tcgen05.st blocks the issuing warp for 50 - 85
+// cycles whether or not others are in flight, so ten back-to-back loads cost as much as ten loads each hidden
+// under the exponentials of the previous group (the two-pass walk below); one MUFU.EX2 per element is 8.4 cycles
+// of the warp's scheduler, 2 550 per tile, which the other three instructions per element only partly overlap;
+// and the CTAs of one launch differ by up to 30 % in run time with the SM they sit on, 18 % of the slowest one's
+// time being the single-buffered Q load and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
 #include "tc_common.cuh"
 
