@@ -448,9 +448,24 @@ def seqpar_record(world: int, rank: int, dev, steps: int = 20, warmup: int = 3) 
     a, b = shard.token_range
     xs = shard.scatter_tokens(x_full)
     fused = world > 1
+    fused_note = None
     if fused:
-        shard.enable_fused_state_exchange(1, C // 32, dev)
-        shard.enable_fused_halo_exchange(SEQPAR_GRID[2] * 2 * HID, dt, dev)
+        # peer-mapped buffers for the two exchange kernels; if the set-up fails on any rank (no peer access on
+        # this box) every rank falls back to the NCCL exchanges and the record says so
+        try:
+            shard.enable_fused_state_exchange(1, C // 32, dev)
+            shard.enable_fused_halo_exchange(SEQPAR_GRID[2] * 2 * HID, dt, dev)
+            mine_ok = 1.0
+        except Exception as e:  # noqa: BLE001
+            mine_ok, fused_note = 0.0, f"{type(e).__name__}: {e}"[:200]
+        flag = torch.tensor([mine_ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() < 1.0:
+            fused = False
+            shard._sp_ptrs = shard._halo_ptrs = None
+            fused_note = fused_note or "peer-memory set-up failed on another rank"
+        else:
+            ops.set_exchange_wait_limit(10.0)  # ranks of a fresh job may reach their first step seconds apart
 
     def sync_all():
         torch.cuda.synchronize()
@@ -519,7 +534,8 @@ def seqpar_record(world: int, rank: int, dev, steps: int = 20, warmup: int = 3) 
         "eager_tokens_per_s": total / (eager_ms * 1e-3), "eager_ms_per_step": eager_ms,
         "nccl_exchange_tokens_per_s": (total / (nccl_ms * 1e-3)) if nccl_ms else None, "nccl_exchange_ms_per_step": nccl_ms,
         "exchange": ("state all-reduce fused into the reduction kernel + conv halo rows pushed by one kernel, both over "
-                     "peer memory (plain loads / stores, no multicast)") if fused else "none (one GPU)",
+                     "peer memory (plain loads / stores, no multicast)") if fused else
+                    ("none (one GPU)" if world == 1 else f"NCCL all-reduce and send / receive (peer-memory set-up failed: {fused_note})"),
         "steps": steps, "warmup": warmup, "rows_per_rank": [r1 - r0 for r0, r1 in shard.ranges],
         "parity_nmax_err": stats[0], "parity_nmax_err_graph": stats[1],
         "parity_against": "the unsharded block on the same GPU, this rank's rows, max over ranks",

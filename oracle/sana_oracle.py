@@ -304,6 +304,34 @@ def cached_glumbconv_temp_forward(x, p: Params, HW: Sequence[int], kv_cache=None
     return (out, kv_cache) if kv_cache is not None else out
 
 
+def chunk_glumbconv_temp_forward(x, p: Params, HW: Sequence[int], chunk_index=None) -> torch.Tensor:
+    """ChunkGLUMBConvTemp.forward without frame mask and context parallelism,
+    diffusion/model/nets/basic_modules.py:273-351: GLUMBConv per frame, then the 3-tap temporal convolution
+    applied chunk by chunk - the frames are cut at ``chunk_index``; a chunk sees the last frame of the chunk
+    before it on its left (zeros before the first chunk) and zeros on its right, so the previous-frame tap
+    crosses chunk boundaries and the next-frame tap does not.  As upstream does, the padded chunks are laid
+    end to end and convolved in one call."""
+    B, N, C = x.shape
+    T, H, W = HW
+    hw = H * W
+    s = glumbconv_forward(x, p, HW)
+    xr = s.reshape(B, T, hw, C).permute(0, 3, 1, 2)  # [B, C, T, HW]
+    wt = p["t_conv.weight"]
+    pad = wt.shape[2] // 2
+    cuts = sorted({0, T, *(int(i) for i in (chunk_index or [0]) if 0 < int(i) < T)})
+    zeros = xr.new_zeros(B, C, pad, hw)
+    pieces, keep, pos = [], [], 0
+    for k, (a, b) in enumerate(zip(cuts, cuts[1:])):
+        left = [] if k == 0 else [xr[:, :, a - pad:a]]
+        pieces += left + [xr[:, :, a:b], zeros]
+        start = pos + (0 if k == 0 else pad)
+        keep.append((start, start + (b - a)))
+        pos = start + (b - a) + pad
+    conv = F.conv2d(torch.cat(pieces, dim=2), wt, None, padding=(pad, 0))
+    t_out = torch.cat([conv[:, :, a:b] for a, b in keep], dim=2)
+    return (xr + t_out).permute(0, 2, 3, 1).reshape(B, N, C)
+
+
 def lite_la_rope_state(k_relu: torch.Tensor, k_rot: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Token-major restatement of `vk` and of the key sum of LiteLAReLURope (sana_blocks.py:380-382):
     k_relu, k_rot, v [B, N, h, d] -> state [B, h, d+1, d]; rows 0..d-1 hold

@@ -481,6 +481,10 @@ class GLUMBConvTemp(GLUMBConv):
             self.__dict__["_tap_cache"] = cached
         return cached[1]
 
+    def _next_tap_ranges(self, T: int, chunk_index=None):
+        """Frame ranges [a, b) inside which a frame sees the frame after it: the whole sample here."""
+        return [(0, T)]
+
     def _frame_halo(self, s: torch.Tensor, B: int):
         """On a sequence shard: the frame before this rank's first token and the one after its last token,
         fetched from the neighbours (upstream: cp_halo_exchange of one frame each side,
@@ -493,7 +497,7 @@ class GLUMBConvTemp(GLUMBConv):
         return sh.exchange_frames(s)
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor, HW=None, **kwargs) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, HW=None, chunk_index=None, **kwargs) -> torch.Tensor:
         if HW is None or len(HW) != 3:
             raise ValueError("HW must be a tuple of (T, H, W)")
         if kwargs.get("frame_valid_mask") is not None:
@@ -501,7 +505,10 @@ class GLUMBConvTemp(GLUMBConv):
         B, N, C = x.shape
         T, H, W = HW
         hw = H * W
-        s = _as2d(super().forward(x, HW=HW))  # spatial result, token-major [B*N, C]
+        ranges = self._next_tap_ranges(T, chunk_index)
+        if self.seq_shard is not None and ranges != [(0, T)]:
+            raise NotImplementedError("the chunked temporal Mix-FFN on a sequence shard is not covered")
+        s = _as2d(GLUMBConv.forward(self, x, HW=HW))  # spatial result, token-major [B*N, C]
         halo_prev, halo_next = self._frame_halo(s, B)
         w_prev, w_mid, w_next = self._taps()
         y = ops.gemm(s, w_mid, residual=s)  # x + centre tap
@@ -515,16 +522,20 @@ class GLUMBConvTemp(GLUMBConv):
         if halo_prev is not None:
             ops.gemm(halo_prev, w_prev, residual=y[:hw], out=y[:hw])
         for b in range(B):
-            lo, hi = b * N, (b + 1) * N
-            if N > hw:
-                ops.gemm(s[lo + hw:hi], w_next, residual=y[lo:hi - hw], out=y[lo:hi - hw])
+            lo = b * N
+            # frames fa .. fb-2 of a range take frames fa+1 .. fb-1; a shard (one range) counts in tokens, its
+            # cuts need not lie between frames
+            for ta, tb in ([(0, N)] if self.seq_shard is not None else [(fa * hw, fb * hw) for fa, fb in ranges]):
+                if tb - ta > hw:
+                    dst = y[lo + ta:lo + tb - hw]
+                    ops.gemm(s[lo + ta + hw:lo + tb], w_next, residual=dst, out=dst)
         if halo_next is not None:
             ops.gemm(halo_next, w_next, residual=y[N - hw:N], out=y[N - hw:N])
         return y.reshape(B, N, C)
 
     @torch.no_grad()
     def forward_gated(self, z: torch.Tensor, HW, x2: torch.Tensor, table: torch.Tensor, t2: torch.Tensor, row: int,
-                      rows_per_vec: int, kv_cache=None, save_kv_cache: bool = False) -> torch.Tensor:
+                      rows_per_vec: int, kv_cache=None, save_kv_cache: bool = False, chunk_index=None) -> torch.Tensor:
         """``x2 + gate * forward(z)`` for the video block, [B*N, C]: ``gate`` = table[row] + t2[v, row] for
         the v-th run of ``rows_per_vec`` tokens (one modulation vector per sample, or per frame).  The
         spatial result enters through one fused multiply-add, the three temporal taps through the
@@ -535,8 +546,9 @@ class GLUMBConvTemp(GLUMBConv):
         T, H, W = HW
         hw = H * W
         sh = self.seq_shard
-        if sh is not None and kv_cache is not None:
-            raise NotImplementedError("the cached temporal Mix-FFN on a sequence shard is not covered")
+        ranges = self._next_tap_ranges(T, chunk_index)
+        if sh is not None and (kv_cache is not None or ranges != [(0, T)]):
+            raise NotImplementedError("the cached / chunked temporal Mix-FFN on a sequence shard is not covered")
         whole = N == (T * hw if sh is None else sh.tokens)
         per_frame_ok = N % hw == 0 and (sh is None or sh.row0 % H == 0)
         if not whole or not (rows_per_vec == N or (rows_per_vec == hw and per_frame_ok)):
@@ -570,15 +582,28 @@ class GLUMBConvTemp(GLUMBConv):
         if halo_prev is not None:  # the first frame's worth of rows takes the left neighbour's last one
             ops.gemm(halo_prev, w_prev, gate=(table, t2[0:1], row, hw), residual=y[:hw], out=y[:hw])
         for b in range(B):
-            lo, hi = b * N, (b + 1) * N
+            lo = b * N
             v0 = b * per_sample
-            if N > hw:
-                ops.gemm(s[lo + hw:hi], w_next, gate=(table, t2[v0:v0 + per_sample], row, rows_per_vec),
-                         residual=y[lo:hi - hw], out=y[lo:hi - hw])
+            for ta, tb in ([(0, N)] if sh is not None else [(fa * hw, fb * hw) for fa, fb in ranges]):
+                if tb - ta > hw:  # the rows of a range except its last frame's worth, under their own frames' gates
+                    tv = t2[v0 + ta // hw:v0 + per_sample] if per_sample > 1 else t2[v0:v0 + 1]
+                    dst = y[lo + ta:lo + tb - hw]
+                    ops.gemm(s[lo + ta + hw:lo + tb], w_next, gate=(table, tv, row, rows_per_vec), residual=dst, out=dst)
         if halo_next is not None:  # ... and the last frame's worth the right neighbour's first one
             ops.gemm(halo_next, w_next, gate=(table, t2[per_sample - 1:per_sample], row, hw), residual=y[N - hw:N],
                      out=y[N - hw:N])
         return y
+
+
+class ChunkGLUMBConvTemp(GLUMBConvTemp):
+    """Upstream's ChunkGLUMBConvTemp (basic_modules.py:273-351), the Mix-FFN that goes with the chunk-causal
+    attention: the frames are cut at ``chunk_index``; the previous-frame tap crosses the cuts (a chunk's first frame
+    sees the last frame of the chunk before it), the next-frame tap does not (a chunk's last frame sees zeros).
+    Here that is the plain temporal Mix-FFN with the next-frame projection issued per chunk."""
+
+    def _next_tap_ranges(self, T: int, chunk_index=None):
+        cuts = sorted({0, T, *(int(i) for i in (chunk_index or [0]) if 0 < int(i) < T)})
+        return list(zip(cuts, cuts[1:]))
 
 
 class CachedGLUMBConvTemp(GLUMBConvTemp):
@@ -840,7 +865,10 @@ class SanaVideoMSBlock(nn.Module):
         super().__init__()
         attn_classes = {"linear": LiteLA, "LiteLAReLURope": LiteLAReLURope, "ChunkedLiteLAReLURope": ChunkedLiteLAReLURope,
                         "ChunkCausalAttention": ChunkCausalAttention, "CachedCausalAttention": CachedCausalAttention}
-        ffn_classes = {"glumbconv": GLUMBConv, "GLUMBConvTemp": GLUMBConvTemp, "CachedGLUMBConvTemp": CachedGLUMBConvTemp}
+        # upstream's own names for the two autoregressive attentions are the lower-case ones
+        attn_classes.update({"chunkcausal": ChunkCausalAttention, "cachedcausal": CachedCausalAttention})
+        ffn_classes = {"glumbconv": GLUMBConv, "GLUMBConvTemp": GLUMBConvTemp, "ChunkGLUMBConvTemp": ChunkGLUMBConvTemp,
+                       "CachedGLUMBConvTemp": CachedGLUMBConvTemp}
         if attn_type not in attn_classes or ffn_type not in ffn_classes:
             raise NotImplementedError(f"SanaVideoMSBlock here covers attn_type {sorted(attn_classes)} with ffn_type "
                                       f"{sorted(ffn_classes)}")
@@ -915,7 +943,7 @@ class SanaVideoMSBlock(nn.Module):
         if isinstance(mlp, GLUMBConvTemp):
             cached = isinstance(mlp, CachedGLUMBConvTemp) and kv_cache is not None
             x2 = mlp.forward_gated(z.view(B, N, C), THW, x2, table, t2, 5, rows, kv_cache=kv_cache if cached else None,
-                                   save_kv_cache=save_kv_cache)
+                                   save_kv_cache=save_kv_cache, chunk_index=chunk_index)
         else:
             u = mlp._expand(_as2d(z))
             g = mlp._depthwise_glu(u, B, N, THW)

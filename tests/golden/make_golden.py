@@ -185,8 +185,8 @@ def litela_relu_rope_case(R, seed=11):
 
 def causal_video_case(R, seed=13):
     """Upstream's autoregressive variants of the Sana-Video block parts: ChunkCausalAttention (frames cut into
-    chunks, state cumulative over chunks), CachedCausalAttention and CachedGLUMBConvTemp (one chunk per call, the
-    state of the previous chunk handed over in a cache list)."""
+    chunks, state cumulative over chunks) with its Mix-FFN ChunkGLUMBConvTemp, CachedCausalAttention and
+    CachedGLUMBConvTemp (one chunk per call, the state of the previous chunk handed over in a cache list)."""
     C, heads, fhw, B, hid = 96, 2, (4, 3, 5), 2, 240
     hw = fhw[1] * fhw[2]
     N = fhw[0] * hw
@@ -207,6 +207,10 @@ def causal_video_case(R, seed=13):
             m = R.sana_blocks.ChunkCausalAttention(C, C, heads=heads, eps=1e-8).eval()
             m.load_state_dict(params, strict=True)
             out[f"chunk_{tag}"] = m.to(dt)(x.to(dt), HW=fhw, rotary_emb=freqs, chunk_index=list(chunk_index))
+            cf = R.basic_modules.ChunkGLUMBConvTemp(in_features=C, hidden_features=hid, use_bias=(True, True, False),
+                                                    norm=(None, None, None), act=("silu", "silu", None)).eval()
+            cf.load_state_dict(mlp, strict=True)
+            out[f"chunk_ffn_{tag}"] = cf.to(dt)(x.to(dt), HW=fhw, chunk_index=list(chunk_index))
             # two calls of two frames each: the second sees the first one's state through the cache
             m = R.sana_blocks.CachedCausalAttention(C, C, heads=heads, eps=1e-8).eval()
             m.load_state_dict(params, strict=True)

@@ -43,6 +43,60 @@ def test_chunk_causal_attention(golden, tag, dt, tol):
 
 
 @pytest.mark.parametrize("tag,dt,tol", CASES)
+def test_chunk_temporal_ffn(golden, tag, dt, tol):
+    """ChunkGLUMBConvTemp: the next-frame tap stops at the chunk cuts, the previous-frame tap crosses them."""
+    g = golden("causal_video")
+    C, fhw, hid = g["C"], g["fhw"], g["hid"]
+    ffn = sana_b200.ChunkGLUMBConvTemp(in_features=C, hidden_features=hid, use_bias=(True, True, False),
+                                       norm=(None, None, None), act=("silu", "silu", None)).eval()
+    ffn.load_state_dict(g["mlp_params"], strict=True)
+    ffn = ffn.to(DEV, dt)
+    x = g["x"].to(DEV, dt)
+    with torch.no_grad():
+        out = ffn(x, HW=fhw, chunk_index=list(g["chunk_index"]))
+        whole = ffn(x, HW=fhw)
+    _close(out, g, "chunk_ffn", dt, tol)
+    mp = {k: v.to(dt).double() for k, v in g["mlp_params"].items()}
+    assert nmax_err(whole, O.glumbconv_temp_forward(g["x"].to(dt).double(), mp, fhw)) < tol
+    assert nmax_err(out, whole) > 1e-3
+
+
+@pytest.mark.parametrize("per_frame", [False, True])
+def test_chunk_causal_video_block_equals_the_parts(golden, per_frame):
+    """SanaVideoMSBlock with upstream's names for the chunk-causal pair ("chunkcausal" + "ChunkGLUMBConvTemp"), fp32:
+    the fused block (gates in the projection epilogues) against the oracle's parts put together as upstream's
+    forward / forward_frame_aware do."""
+    from sana_b200 import synthetic
+    g = golden("causal_video")
+    C, heads, fhw, hid = g["C"], g["heads"], g["fhw"], g["hid"]
+    F_, hw = fhw[0], fhw[1] * fhw[2]
+    B, N, L = 2, F_ * hw, 6
+    p = synthetic.make_block_params(C, hid, 31, std=0.06)
+    gen = torch.Generator().manual_seed(32)
+    p["mlp.t_conv.weight"] = torch.randn(C, C, 3, 1, generator=gen) * 0.05
+    x, y = g["x"], torch.randn(B, L, C, generator=gen) * 0.7
+    t = torch.randn(B, 1, F_, 6 * C, generator=gen) * 0.3 if per_frame else torch.randn(B, 6 * C, generator=gen) * 0.3
+    ci = list(g["chunk_index"])
+    blk = sana_b200.SanaVideoMSBlock(C, heads, mlp_ratio=hid / C, attn_type="chunkcausal", ffn_type="ChunkGLUMBConvTemp",
+                                     linear_head_dim=C // heads)
+    blk.load_state_dict(p, strict=True)
+    blk = blk.to(DEV).eval()
+    with torch.no_grad():
+        out = blk(x.to(DEV), y.to(DEV), t.to(DEV), THW=fhw, rotary_emb=g["freqs"], chunk_index=ci)
+    # the oracle's parts, composed
+    tt = t.reshape(B, F_, 6, C) if per_frame else t.reshape(B, 1, 6, C)
+    mod = (p["scale_shift_table"][None, None] + tt).chunk(6, dim=-2)  # each [B, F or 1, 1, C]
+    rows = lambda v: v.reshape(B, -1, hw if per_frame else N, C)
+    z = O.t2i_modulate(rows(O.layer_norm(x)), mod[0], mod[1]).reshape(B, N, C)
+    a = O.chunk_causal_forward(z, O.sub(p, "attn"), heads, g["freqs"], fhw, ci, eps=O.BLOCK_LA_EPS)
+    x1 = x + (mod[2] * rows(a)).reshape(B, N, C)
+    x1 = x1 + O.cross_attention_forward(x1, y, O.sub(p, "cross_attn"), heads)
+    z = O.t2i_modulate(rows(O.layer_norm(x1)), mod[3], mod[4]).reshape(B, N, C)
+    ref = x1 + (mod[5] * rows(O.chunk_glumbconv_temp_forward(z, O.sub(p, "mlp"), fhw, ci))).reshape(B, N, C)
+    assert nmax_err(out, ref) < 1e-5
+
+
+@pytest.mark.parametrize("tag,dt,tol", CASES)
 def test_cached_attention_and_temporal_ffn_chunk_after_chunk(golden, tag, dt, tol):
     g = golden("causal_video")
     C, heads, fhw, hid = g["C"], g["heads"], g["fhw"], g["hid"]
