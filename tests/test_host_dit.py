@@ -89,8 +89,13 @@ def test_video_block_refuses_uncovered_call_options():
         blk(x, y, torch.zeros(1, 1, 5, 6 * 96), THW=(2, 3, 4))  # 24 tokens are not 5 frames
     with pytest.raises(ValueError):
         blk(x, y, torch.zeros(1, 1, 4, 6 * 96), THW=(2, 3, 4))  # 4 modulation vectors for a 2-frame grid
+    sh1 = sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1)
+    blk.set_sequence_shard(sh1)  # the temporal Mix-FFN runs on shards (one frame from each neighbour) ...
+    assert blk.mlp.seq_shard is sh1
+    cached = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="cachedcausal", ffn_type="CachedGLUMBConvTemp",
+                                        linear_head_dim=48)
     with pytest.raises(NotImplementedError):
-        blk.set_sequence_shard(sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1))  # temporal Mix-FFN on a shard
+        cached.set_sequence_shard(sh1)  # ... its cached variant does not
     plain = sana_b200.SanaVideoMSBlock(96, 2, mlp_ratio=2.5, attn_type="LiteLAReLURope", ffn_type="glumbconv",
                                        linear_head_dim=48)
     sh = sana_b200.sharding.SequenceShard(2, 3, 4, 0, 1)
