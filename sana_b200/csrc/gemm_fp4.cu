@@ -21,16 +21,6 @@ namespace sana {
 
 __device__ int g_fp4_status = 0;
 
-// Optional cycle accounting of the CTA-pair kernel's roles (compiled in with -DSANA_F4_PROFILE, for tuning only)
-#ifdef SANA_F4_PROFILE
-__device__ unsigned long long g_f4_prof[8];
-#define F4_T0() const long long f4_t0__ = clock64()
-#define F4_ACC(slot, on) do { if (on) atomicAdd(&g_f4_prof[slot], (unsigned long long)(clock64() - f4_t0__)); } while (0)
-#else
-#define F4_T0() do { } while (0)
-#define F4_ACC(slot, on) do { } while (0)
-#endif
-
 constexpr int F4_BM = 128, F4_BN = 128;
 constexpr int F4_BK = 256;                          // elements per stage = 128 bytes per row
 constexpr int F4_A_BYTES = F4_BM * 128;             // 16 KiB
@@ -422,23 +412,12 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (leader && lane == 0) {
       uint32_t stage = 0, phase = 0, acc_phase = 0;
       bool ok = true;
-#ifdef SANA_F4_PROFILE
-      const long long f4_loop0 = clock64();
-#endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        {
-          F4_T0();
-          if (!mbar_wait(bar_tempty, acc_phase ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
-          F4_ACC(0, true);
-        }
+        if (!mbar_wait(bar_tempty, acc_phase ^ 1u, abort_flag, 2, &g_fp4_status)) { ok = false; break; }
         acc_phase ^= 1u;
         tcgen05_fence_after();
         for (int kb = 0; kb < kblocks; ++kb) {
-          {
-            F4_T0();
-            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
-            F4_ACC(1, true);
-          }
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3, &g_fp4_status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + P4_A_BYTES);
@@ -459,9 +438,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         if (ok) umma_commit_pair(bar_tfull);  // accumulator complete, both CTAs
       }
-#ifdef SANA_F4_PROFILE
-      atomicAdd(&g_f4_prof[2], (unsigned long long)(clock64() - f4_loop0));
-#endif
     }
   }
   } else {
@@ -494,26 +470,19 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const bool box_rows_in = m_box < args.M;
       const bool use_res = has_res && box_rows_in;
       epi_box_begin<P4_NBOX>(eb, row, use_res, lane, m_box, &tmRes);
-      {
-        F4_T0();
-        if (!mbar_wait(bar_tfull, full_phase, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
-        F4_ACC(3, threadIdx.x == 128 && leader);
-      }
+      if (!mbar_wait(bar_tfull, full_phase, abort_flag, 4, &g_fp4_status)) { ok = false; break; }
       full_phase ^= 1u;
       tcgen05_fence_after();
-      F4_T0();
       uint32_t acc[NCHUNK][16];
       epi_acc_load<NCHUNK>(taddr, acc);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0);  // the accumulator is free again: the leader's barrier collects both CTAs
-      F4_ACC(6, threadIdx.x == 128 && leader);
       if (!epi_box_drain_regs<NCHUNK, true>(eb, row, ep, acc, use_res, box_rows_in, lane, m_box, &tmOut, alpha, abort_flag,
                                             &g_fp4_status)) {
         ok = false;
         break;
       }
-      F4_ACC(4, threadIdx.x == 128 && leader);
     }
     if (lane == 0) bulk_wait_all();
   }
@@ -754,18 +723,6 @@ extern "C" int sana_gemm_nvfp4(const void* Aq, const void* sfa, const float* a_s
   return SANA_OK;
 }
 
-#ifdef SANA_F4_PROFILE
-extern "C" int sana_debug_f4_prof(unsigned long long* out8, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out8, g_f4_prof, 8 * sizeof(unsigned long long));
-  if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyFromSymbol(g_f4_prof)");
-  if (reset) {
-    unsigned long long zero[8] = {};
-    e = cudaMemcpyToSymbol(g_f4_prof, zero, sizeof(zero));
-    if (e != cudaSuccess) return cuda_status(e, "cudaMemcpyToSymbol(g_f4_prof)");
-  }
-  return SANA_OK;
-}
-#endif
 
 extern "C" int sana_gemm_nvfp4_take_device_status(int* status_out) {
   if (!status_out) return fail(SANA_ERR_INVALID, "sana_gemm_nvfp4_take_device_status: null pointer");
