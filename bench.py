@@ -247,6 +247,18 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
             row[kind + "_ms"] = ms
             row[kind + "_tflops"] = 2.0 * tokens * n * k / (ms * 1e-3) / 1e12
         ops.set_gemm_variant(0)
+        # the vendor library on the same operands (torch.matmul = cuBLASLt), for comparison only
+        wt = w.t()
+        for _ in range(3):
+            torch.matmul(a, wt, out=o)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            torch.matmul(a, wt, out=o)
+        e1.record()
+        torch.cuda.synchronize()
+        row["bf16_library_ms"] = e0.elapsed_time(e1) / iters
+        row["bf16_library_tflops"] = 2.0 * tokens * n * k / (row["bf16_library_ms"] * 1e-3) / 1e12
         row.update(fp4_library_rate(tokens, n, k, iters))
         out["rows"].append(row)
     print(json.dumps(out))

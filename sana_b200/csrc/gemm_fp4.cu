@@ -290,10 +290,14 @@ constexpr uint32_t P4_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(P4_BN >> 3) <
 static_assert(P4_SMEM_BYTES <= 232448, "shared memory budget");
 static_assert(P4_STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned");
 static_assert(P4_SF_COL0 + P4_STAGES * P4_SF_COLS <= 512, "tensor memory budget");
-static_assert(16 * P4_STAGES + 40 + 8 * P4_EPI_WARPS <= P4_CTRL_BYTES, "control block too small");
+static_assert(16 * P4_STAGES + 40 + 8 * P4_EPI_WARPS + 8 * P4_STAGES <= P4_CTRL_BYTES, "control block too small");
 
 __device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// arrive (once, on this CTA's barrier) when every tcgen05 operation this thread has issued so far is complete
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void umma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
                                                 uint32_t sfb, uint32_t accumulate) {
@@ -328,10 +332,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   unsigned char* epi_gen = smem_raw + STAGES * P4_STAGE_BYTES;
   const uint32_t ctrl = epi_base + P4_EPI_BYTES;
   unsigned char* ctrl_gen = epi_gen + P4_EPI_BYTES;
-  // control layout: full[STAGES] | empty[STAGES] | tfull | (pad) | tempty | (pad) | tmem ptr | abort | res[EPI_WARPS]
+  // control layout: full[STAGES] | empty[STAGES] | tfull | (pad) | tempty | (pad) | tmem ptr | abort | res[EPI_WARPS] | sf[STAGES]
   const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * STAGES;
   const uint32_t bar_tfull = ctrl + 16 * STAGES, bar_tempty = bar_tfull + 16;
   const uint32_t bar_res = ctrl + 16 * STAGES + 40;
+  const uint32_t bar_sf = bar_res + 8 * P4_EPI_WARPS;  // leader only: the scale copies of a stage have landed in tensor memory
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * STAGES + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * STAGES + 36);
 
@@ -350,6 +355,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, 1);
     }
     mbar_init(bar_tfull, 1);
     mbar_init(bar_tempty, 2 * P4_EPI_WARPS);
@@ -384,7 +390,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       bool ok = true;
       const uint32_t full0 = map_to_cta(bar_full, 0);  // the leader's full barriers, cluster address
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int mt = tile / args.tiles_n, nt = tile % args.tiles_n;
+        int mt, nt;
+        pair_tile_coords(tile, args.tiles_m, args.tiles_n, mt, nt);
         const int m0 = mt * 256 + (int)rank * P4_BM;          // this CTA's A rows
         const int n0 = nt * P4_BN + (int)rank * (P4_BN / 2);  // this CTA's half of the W rows
         const int sfa_row = (2 * mt + (int)rank) * args.ktiles4;  // scale tiles: row blocks of 128, K-fastest
@@ -421,14 +428,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tcgen05_fence_after();
           const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + P4_A_BYTES);
-          const uint32_t sfa_s = sa + P4_A_BYTES + P4_B_BYTES, sfb_s = sfa_s + P4_SFA_BYTES;
           const uint32_t sfa_t = tmem_base + (uint32_t)(P4_SF_COL0 + stage * P4_SF_COLS), sfb_t = sfa_t + 16;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            tmem_cp_sf_pair(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
-            tmem_cp_sf_pair(sfb_t + 8 * k, make_sf_desc(sfb_s + 512 * k));             // W rows 0..127 of the tile
-            tmem_cp_sf_pair(sfb_t + 8 * k + 4, make_sf_desc(sfb_s + 4 * 512 + 512 * k));  // W rows 128..255
-          }
+          // the stage's scales are copied into tensor memory by warp 2, off this thread's instruction stream
+          if (!mbar_wait(bar_sf + 8 * stage, phase, abort_flag, 6, &g_fp4_status)) { ok = false; break; }
+          tcgen05_fence_after();
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_nvfp4_pair(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P4_IDESC, sfa_t + 4 * k,
@@ -437,6 +440,32 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit_pair(bar_tfull);  // accumulator complete, both CTAs
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------- scale copies (leader CTA only) ----------------------
+    // Twelve tcgen05.cp per stage move the stage's scale tiles from shared into tensor memory (each CTA's own
+    // tiles into its own tensor memory).  Issued by the MMA thread they sit between its MMAs in program order;
+    // from a thread of their own they run ahead, under the MMAs of the stage before.
+    if (leader && lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, 7, &g_fp4_status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_base + stage * P4_STAGE_BYTES;
+          const uint32_t sfa_s = sa + P4_A_BYTES + P4_B_BYTES, sfb_s = sfa_s + P4_SFA_BYTES;
+          const uint32_t sfa_t = tmem_base + (uint32_t)(P4_SF_COL0 + stage * P4_SF_COLS), sfb_t = sfa_t + 16;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tmem_cp_sf_pair(sfa_t + 4 * k, make_sf_desc(sfa_s + 512 * k));
+            tmem_cp_sf_pair(sfb_t + 8 * k, make_sf_desc(sfb_s + 512 * k));             // W rows 0..127 of the tile
+            tmem_cp_sf_pair(sfb_t + 8 * k + 4, make_sf_desc(sfb_s + 4 * 512 + 512 * k));  // W rows 128..255
+          }
+          tc_commit_pair_local(bar_sf + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
       }
     }
   }
@@ -461,8 +490,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     uint32_t full_phase = 0u;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      const int m_box = (tile / args.tiles_n) * 256 + (int)rank * P4_BM + quad * 32;
-      const int64_t nbase = (int64_t)(tile % args.tiles_n) * P4_BN + half * HALF;
+      int mt, nt;
+      pair_tile_coords(tile, args.tiles_m, args.tiles_n, mt, nt);
+      const int m_box = mt * 256 + (int)rank * P4_BM + quad * 32;
+      const int64_t nbase = (int64_t)nt * P4_BN + half * HALF;
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * HALF);

@@ -124,10 +124,12 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       bool ok = true;
       const uint32_t full0 = map_to_cta(bar_full, 0);  // the leader's full barriers, cluster address
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m0 = (tile / args.tiles_n) * (2 * T2_BM) + (int)rank * T2_BM;
+        int tm, tn;
+        pair_tile_coords(tile, args.tiles_m, args.tiles_n, tm, tn);
+        const int m0 = tm * (2 * T2_BM) + (int)rank * T2_BM;
         // a ragged last tile column is computed at its own width (a multiple of 32): each CTA then holds half of
         // THAT many W rows, not half of BN
-        const int nt0 = (tile % args.tiles_n) * BN;
+        const int nt0 = tn * BN;
         const int n_this = min(BN, ((args.N - nt0) + 31) & ~31);
         const int n0 = nt0 + (int)rank * (n_this >> 1);
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -157,7 +159,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         acc_phase ^= 1u << a;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-        const int n_this = min(BN, ((args.N - (tile % args.tiles_n) * BN) + 31) & ~31);
+        int tm, tn;
+        pair_tile_coords(tile, args.tiles_m, args.tiles_n, tm, tn);
+        const int n_this = min(BN, ((args.N - tn * BN) + 31) & ~31);
         // same descriptor with this tile's N (>> 3 at bit 17)
         const uint32_t idesc = (Cfg::IDESC & ~(0x3Fu << 17)) | ((uint32_t)(n_this >> 3) << 17);
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -195,8 +199,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     int it = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
       const int a = it & 1;
-      const int m_box = (tile / args.tiles_n) * (2 * T2_BM) + (int)rank * T2_BM + quad * 32;
-      const int64_t nbase = (int64_t)(tile % args.tiles_n) * BN + half * Cfg::HALF;
+      int tm, tn;
+      pair_tile_coords(tile, args.tiles_m, args.tiles_n, tm, tn);
+      const int m_box = tm * (2 * T2_BM) + (int)rank * T2_BM + quad * 32;
+      const int64_t nbase = (int64_t)tn * BN + half * Cfg::HALF;
       const int64_t m = (int64_t)m_box + lane;
       const bool row_ok = m < args.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * Cfg::HALF);

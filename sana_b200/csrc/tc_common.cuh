@@ -441,6 +441,20 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
+// Order of the output tiles.  Row-major order makes the tiles in flight at one time (one per CTA pair) span two
+// tile rows and every tile column, i.e. the whole weight matrix passes through L2 once per wave (50 MB for the
+// 11 200-wide projection).  Walking groups of PAIR_GROUP_M tile rows column by column keeps a wave on a few
+// columns of W and PAIR_GROUP_M row tiles of A instead (about 20 MB), which is what the L2 can hold next to the
+// streaming output.
+constexpr int PAIR_GROUP_M = 8;
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = PAIR_GROUP_M * tiles_n;
+  const int g = tile / per_group, within = tile - g * per_group;
+  const int rows = min(PAIR_GROUP_M, tiles_m - g * PAIR_GROUP_M);
+  tn = within / rows;
+  tm = g * PAIR_GROUP_M + (within - tn * rows);
+}
+
 // ---- host helpers -----------------------------------------------------------------------------
 // kernel choice set by sana_gemm_set_variant: 0 = per problem, 1 = single-CTA kernels, 2 = CTA-pair kernels
 int gemm_variant();
