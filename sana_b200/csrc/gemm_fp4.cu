@@ -270,7 +270,9 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 // cycles), hand the buffer back to the MMA issuer, and do the arithmetic and the stores from registers
 // under the next tile's MMAs; they get the registers for that from the load / MMA warps (setmaxnreg).
 // All four operand streams are bulk-tensor copies (the scale buffers as [tiles, 128] words, so that
-// tiles past the end arrive as zeros), counted on the leader's barrier.
+// tiles past the end arrive as zeros), counted on the leader's barrier.  Roles of warpgroup 0: warp 0 loads,
+// warp 1 issues the MMAs, warp 2 issues the scale copies (a third of the tensor pipe's time when they sat in
+// the MMA thread's instruction stream), warp 3 idle.  Output tiles are walked in groups of eight tile rows.
 constexpr int P4_BM = 128, P4_BN = 256;
 constexpr int P4_A_BYTES = P4_BM * 128;             // 16 KiB
 constexpr int P4_B_BYTES = (P4_BN / 2) * 128;       // 16 KiB: this CTA's half of the W tile
