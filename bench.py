@@ -264,6 +264,55 @@ def run_gemm_rates(tokens: int, iters: int = 20) -> None:
     print(json.dumps(out))
 
 
+def run_gemm_sustained(tokens: int, seconds: float = 2.0) -> None:
+    """The bf16 projections of a block run back to back for `seconds` each way - our kernels, then the vendor
+    library (torch.matmul) on the same operands - so that both are measured under the power cap, the regime of
+    the stack (one JSON line).  Epilogues: plain for the library; ours also with the bias + gate + residual
+    epilogue of the attention projection."""
+    from sana_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    shapes = [("qkv", 3 * C, C), ("proj", C, C), ("expand", 2 * HID, C), ("point", C, HID)]
+    ops_ = []
+    for name, n, k in shapes:
+        a = torch.randn(tokens, k, generator=g, device=dev).bfloat16()
+        w = (torch.randn(n, k, generator=g, device=dev) * 0.02).bfloat16()
+        o = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+        ops_.append((name, a, w, o, 2.0 * tokens * n * k))
+    flops = sum(f for *_, f in ops_)
+
+    def ours():
+        for _, a, w, o, _f in ops_:
+            ops.gemm(a, w, out=o)
+
+    def library():
+        for _, a, w, o, _f in ops_:
+            torch.matmul(a, w.t(), out=o)
+
+    out = {"workload": f"the four projection shapes back to back for {seconds} s each way, {tokens} tokens, hidden {C}"}
+    for tag, fn in (("ours", ours), ("library", library), ("ours_again", ours)):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        n = max(int(seconds * 1e3 / e0.elapsed_time(e1)), 1)
+        with ClockSampler(0) as clk:
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        c = clk.summary()
+        ms = e0.elapsed_time(e1) / n
+        out[tag] = {"ms_per_round": ms, "tflops": flops / (ms * 1e-3) / 1e12, "rounds": n, "clocks": c}
+    print(json.dumps(out))
+
+
 def run_kernel_rates(tokens_side: int, batch: int, iters: int = 20) -> None:
     """Device-timed rate of each HBM-bound kernel of a 1.6B-width block on `batch` samples of
     tokens_side x tokens_side tokens (one JSON line).  Bytes are the algorithmic ones: every
@@ -565,6 +614,9 @@ def main() -> None:
                     help="only time the HBM-bound kernels of a block on --batch samples of SIDE x SIDE tokens")
     ap.add_argument("--gemm-rates", type=int, default=0, metavar="TOKENS",
                     help="only time the four projection shapes of a block at this many tokens")
+    ap.add_argument("--sustained", action="store_true",
+                    help="with --gemm-rates: run our bf16 projections and the vendor library's back to back for two "
+                         "seconds each (both under the power cap)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -590,6 +642,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.gemm_rates and args.sustained:
+        run_gemm_sustained(args.gemm_rates)
         return
     if args.gemm_rates:
         run_gemm_rates(args.gemm_rates)

@@ -41,10 +41,10 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
 // be handed to another block under them) and exits; warps are independent, so nobody waits
 // for it.  Not returning a flag keeps the row loop free of per-step liveness checks.
 __device__ __forceinline__ void dw_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return;
+  if (mbar_try_wait_poll(bar, parity)) return;
   const long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_poll(bar, parity)) {
     if ((++spins & 1023u) == 0 && clock64() - t0 > TC_WAIT_LIMIT_CYCLES) {
       atomicExch(&g_dw_status, 1);
       const long long t1 = clock64();

@@ -19,7 +19,29 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll of a barrier phase.  The last operand is the time the hardware may keep the thread suspended
+// before the poll returns "not yet": without it a waiting warp comes back every few dozen cycles, and the
+// eight epilogue warps of a GEMM CTA, which wait for most of a tile's duration, then spend enough issue slots
+// and power on polling to cost 4 % of the power-capped GEMM rate (1 219 -> 1 265 TFLOP/s over the four
+// projection shapes run for two seconds).
+#ifndef SANA_WAIT_HINT_NS
+#define SANA_WAIT_HINT_NS 1000
+#endif
+#define SANA_STR2(x) #x
+#define SANA_STR(x) SANA_STR2(x)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, " SANA_STR(SANA_WAIT_HINT_NS) ";\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// The same poll without the hint, for warps that are fed row by row and should be back at once (depthwise kernel).
+__device__ __forceinline__ bool mbar_try_wait_poll(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
