@@ -243,7 +243,11 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
         qr[u][r] = (tok < n_end) ? ldg_nc_u4(qbase + (int64_t)tok * ldq) : make_uint4(0u, 0u, 0u, 0u);
       }
   };
-  auto compute = [&](const uint4 (&qr)[U][2], int n0) {
+  // One batch of 16 U tokens.  As soon as a step's rows have been taken out of their registers the same rows
+  // of the NEXT batch are requested into them, so the loads of a whole batch stay in flight under the products
+  // without a second register set.
+  auto compute = [&](uint4 (&qr)[U][2], int n0) {
+    const int n_next = n0 + 16 * U;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       uint32_t a[2][4];  // [row half][word]
@@ -253,6 +257,13 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
         a[r][1] = relu_bf16x2(qr[u][r].y);
         a[r][2] = relu_bf16x2(qr[u][r].z);
         a[r][3] = relu_bf16x2(qr[u][r].w);
+      }
+      if (n_next < n_end) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int tok = n_next + 16 * u + g + 8 * r;
+          qr[u][r] = (tok < n_end) ? ldg_nc_u4(qbase + (int64_t)tok * ldq) : make_uint4(0u, 0u, 0u, 0u);
+        }
       }
       float den[2];
 #pragma unroll
@@ -313,11 +324,9 @@ la_apply_bf16_kernel(const __nv_bfloat16* __restrict__ qp, int64_t ldq, const fl
     }
   };
   uint4 qa[U][2];
+  load(qa, n_begin);
 #pragma unroll 1
-  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) {
-    load(qa, n0);
-    compute(qa, n0);
-  }
+  for (int n0 = n_begin; n0 < n_end; n0 += 16 * U) compute(qa, n0);
   if (FP4 && sink.amax_out != nullptr) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax_local = fmaxf(amax_local, __shfl_xor_sync(0xffffffffu, amax_local, o));
