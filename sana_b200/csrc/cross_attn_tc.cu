@@ -28,6 +28,11 @@
 // of the warp's scheduler, 2 550 per tile, which the other three instructions per element only partly overlap;
 // and the CTAs of one launch differ by up to 30 % in run time with the SM they sit on, 18 % of the slowest one's
 // time being the single-buffered Q load and output store (without them all CTAs run within 7 %).
+// Two query tiles in flight (two softmax warpgroups sharing the schedulers, 128-key chunks so that two S + O
+// pairs fit the 512 columns, results stored straight to global memory) was built too and passed the same
+// tests, at 108 us: with one S buffer per tile a tile's softmax and its own products cannot overlap, and the
+// chain "softmax of a chunk, then that tile's 15 instructions on the tensor core" per chunk outweighs what the
+// second tile fills in.
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
 #include "tc_common.cuh"
 
