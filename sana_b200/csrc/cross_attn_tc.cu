@@ -7,32 +7,33 @@
 //                   swizzled, fetched by bulk-tensor copies of a 4-D view (channel, head, key, sample) so that
 //                   channels past the head and keys past L arrive as zeros; one Q tile; an output staging tile.
 //   tensor memory   S_A (keys [0, NA)) at column 0, S_B (keys [NA, LP)) at column 160, O at column 304.
-//   warps 0-3       softmax: lane = query row.  Row maximum of a key chunk, p = 2^(s c - m), written back over S
-//                   as bf16 pairs (the second product takes its A operand from tensor memory), row sum in fp32.
+//   warps 0-3       softmax of key chunk A: lane = query row.  Row maximum of the chunk (it fixes the row's shift m
+//                   and is handed to the warps of chunk B through shared memory), p = 2^(s c - m) written back
+//                   over S as bf16 pairs (the second product takes its A operand from tensor memory), row sum.
+//   warps 10-13     softmax of key chunk B, on the same rows (lane quadrant = warp & 3) and the other score buffer.
 //   warps 4-7       epilogue: O / row sum -> bf16 -> staging tile -> bulk-tensor store (rows past N are clipped).
 //   warp 8          bulk-tensor loads (Q per tile, K / V and the mask bias per (sample, head)).
 //   warp 9          one thread issues every tcgen05.mma: S_A, S_B = Q K^T, then O = P_A V_A + P_B V_B.
-// The two key chunks make the pipeline: while the softmax warps work on chunk B of tile i the tensor core runs
-// P_A V_A of tile i and S_A of tile i+1, and while they work on chunk A of tile i+1 it runs P_B V_B of tile i and
-// S_B of tile i+1.  Chunk A fixes the shift m of a row; chunk B keeps it unless its own maximum exceeds it by
-// more than 2^8, in which case the warp waits for P_A V_A and rescales O in tensor memory (exact either way:
-// softmax is invariant to the shift, and p <= 256 is harmless in bf16 and in the fp32 accumulator).
-// Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 91 us per sample.  The 33 tcgen05.mma of a tile
-// alone take about 4 500 cycles - an instruction with M = 128 costs about 130 cycles whether N is 112 or 256 -
-// and the softmax warps about 8 000; a single-pass softmax with the shift fixed up on the fly and a split of a
-// row's columns over two warps were both tried and were slower (110 - 120 us).  So was keeping a whole chunk of
-// the row in registers (160 of 232, taken from the other warpgroups with setmaxnreg) to read tensor memory once
-// instead of twice: 104 us.  What that showed: a tcgen05.ld / tcgen05.st blocks the issuing warp for 50 - 85
-// cycles whether or not others are in flight, so ten back-to-back loads cost as much as ten loads each hidden
-// under the exponentials of the previous group (the two-pass walk below); one MUFU.EX2 per element is 8.4 cycles
-// of the warp's scheduler, 2 550 per tile, which the other three instructions per element only partly overlap;
-// and the CTAs of one launch differ by up to 30 % in run time with the SM they sit on, 18 % of the slowest one's
-// time being the single-buffered Q load and output store (without them all CTAs run within 7 %).
-// Two query tiles in flight (two softmax warpgroups sharing the schedulers, 128-key chunks so that two S + O
-// pairs fit the 512 columns, results stored straight to global memory) was built too and passed the same
-// tests, at 108 us: with one S buffer per tile a tile's softmax and its own products cannot overlap, and the
-// chain "softmax of a chunk, then that tile's 15 instructions on the tensor core" per chunk outweighs what the
-// second tile fills in.
+// The two key chunks make the pipeline: P_A V_A of tile i and S_A of tile i+1 follow the probabilities of chunk
+// A, P_B V_B of tile i and S_B of tile i+1 those of chunk B.  Chunk B keeps chunk A's shift unless its own maximum
+// exceeds it by more than 2^8, in which case its warps wait for P_A V_A and rescale O in tensor memory (exact
+// either way: softmax is invariant to the shift, and p <= 256 is harmless in bf16 and in the fp32 accumulator);
+// the factor they applied goes to the epilogue with the two partial row sums.
+// Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 72 us per sample (the vendor's flash kernel
+// through torch: 57 - 61).  History: with ONE softmax warpgroup doing chunk A and then chunk B the kernel took 84 us:
+// the 33 tcgen05.mma of a tile take about 4 500 cycles (an instruction with M = 128 costs about 130 cycles
+// whether N is 112 or 256) but the softmax warps about 8 000, because a tcgen05.ld / tcgen05.st blocks the
+// issuing warp for 50 - 85 cycles whether or not others are in flight and one MUFU.EX2 per element is 8.4
+// cycles of the warp's scheduler (2 550 per tile).  A second warp per scheduler hides the first one's blocking
+// and exponentials; splitting BY CHUNK needs one exchange per tile (the shift).  Variants that were built,
+// passed the tests and were slower: a single-pass softmax with the shift fixed up on the fly (110 us); two
+// warps per row splitting every chunk's columns, two exchanges per chunk (112 us); a whole chunk of the row
+// held in registers to read tensor memory once instead of twice, 232 registers per softmax thread through
+// setmaxnreg (104 us: ten back-to-back loads cost what ten loads hidden under the exponentials of the
+// previous group cost); two query tiles in flight with 128-key chunks and direct stores (108 us: with one S
+// buffer per tile a tile's softmax and its own products cannot overlap).  The CTAs of one launch differ by up
+// to 30 % in run time with the SM they sit on, 18 % of the slowest one's time being the single-buffered Q load
+// and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
 #include "tc_common.cuh"
 
@@ -48,10 +49,11 @@ constexpr int CX_OFF_V = CX_OFF_K + 2 * CX_KV_BLK;
 constexpr int CX_OFF_Q = CX_OFF_V + 2 * CX_KV_BLK;
 constexpr int CX_OFF_O = CX_OFF_Q + 2 * CX_Q_BLK;    // staging: [warp][block][32 rows][128 bytes]
 constexpr int CX_OFF_BIAS = CX_OFF_O + 2 * CX_Q_BLK;
-constexpr int CX_OFF_L = CX_OFF_BIAS + CX_LP_MAX * 4;  // row sums, [2][128] floats
-constexpr int CX_OFF_CTRL = CX_OFF_L + 2 * 128 * 4;
+constexpr int CX_OFF_L = CX_OFF_BIAS + CX_LP_MAX * 4;  // per row, [4][2][128] floats: sum of chunk A, sum of chunk B,
+                                                        // shift fixed by chunk A, factor chunk B put on chunk A's part
+constexpr int CX_OFF_CTRL = CX_OFF_L + 4 * 2 * 128 * 4;
 constexpr int CX_SMEM = CX_OFF_CTRL + 128;
-constexpr int CX_THREADS = 320;
+constexpr int CX_THREADS = 448;  // warps 0-3 softmax of chunk A, 4-7 epilogue, 8 loads, 9 MMA issue, 10-13 softmax of chunk B
 constexpr uint32_t CX_COL_SB = 160, CX_COL_O = 304;
 static_assert(CX_SMEM <= 232448, "shared memory budget");
 static_assert(CX_KV_BLK % 1024 == 0 && CX_OFF_Q % 1024 == 0 && CX_OFF_O % 1024 == 0, "swizzled tiles need 1024-byte bases");
@@ -225,7 +227,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // barriers (8 bytes each)
   const uint32_t bar_kv_full = ctrl, bar_kv_free = ctrl + 8, bar_q_full = ctrl + 16, bar_q_free = ctrl + 24;
   const uint32_t bar_sa = ctrl + 32, bar_sb = ctrl + 40, bar_pa = ctrl + 48, bar_pb = ctrl + 56;
-  const uint32_t bar_pva = ctrl + 64, bar_o_full = ctrl + 72, bar_o_free = ctrl + 80;
+  const uint32_t bar_pva = ctrl + 64, bar_o_full = ctrl + 72, bar_o_free = ctrl + 80, bar_m = ctrl + 88;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + CX_OFF_CTRL + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + CX_OFF_CTRL + 100);
 
@@ -247,6 +249,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_pva, 1);
     mbar_init(bar_o_full, 1);
     mbar_init(bar_o_free, 4);
+    mbar_init(bar_m, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
@@ -264,11 +267,12 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    // ------------------------------------------------------------------ softmax warps
+    // ------------------------------------------------------------------ softmax warps of chunk A
+    // Chunk A fixes the shift m of the row and hands it to the warps of chunk B through shared memory.
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const int row = warp * 32 + lane;
     const float c = a.scale_log2e;
-    uint32_t ph_sa = 0, ph_sb = 0, ph_kv = 0;
+    uint32_t ph_sa = 0, ph_kv = 0;
     int prev_bh = -1;
     bool ok = true;
     for (int it = 0; it < n_items && ok; ++it) {
@@ -278,27 +282,53 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       if (bh != prev_bh) ph_kv ^= 1u;
       prev_bh = bh;
-      // ---- chunk A: fixes the shift of the row
       if (!mbar_wait(bar_sa, ph_sa, abort_flag, 12, &g_cax_status)) { ok = false; break; }
       ph_sa ^= 1u;
       tcgen05_fence_after();
-      float m = cx_row_max<MASK>(lane_addr, a.NA, 0, a.L, c, bias);
-      float l = cx_row_exp<MASK>(lane_addr, a.NA, 0, a.L, c, m, bias);
+      const float m = cx_row_max<MASK>(lane_addr, a.NA, 0, a.L, c, bias);
+      lbuf[(4 + (it & 1)) * 128 + row] = m;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_m);
+      const float l = cx_row_exp<MASK>(lane_addr, a.NA, 0, a.L, c, m, bias);
+      lbuf[(it & 1) * 128 + row] = l;
       tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pa);
-      // ---- chunk B: same shift unless its maximum is more than 2^8 above it
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ softmax warps of chunk B
+    // Same rows (warp & 3 is the lane quadrant), the other score buffer: they run beside the warps of chunk A,
+    // two warps per scheduler, so that one's tensor-memory accesses and exponentials hide under the other's
+    // arithmetic.  Chunk B keeps chunk A's shift unless its own maximum is more than 2^8 above it.
+    const int quad = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int row = quad * 32 + lane;
+    const float c = a.scale_log2e;
+    uint32_t ph_sb = 0, ph_kv = 0, ph_m = 0;
+    int prev_bh = -1;
+    bool ok = true;
+    for (int it = 0; it < n_items && ok; ++it) {
+      const int bh = (int)((t_begin + it) / a.nqt);
+      if (MASK && bh != prev_bh) {
+        if (!mbar_wait(bar_kv_full, ph_kv, abort_flag, 11, &g_cax_status)) { ok = false; break; }
+      }
+      if (bh != prev_bh) ph_kv ^= 1u;
+      prev_bh = bh;
       if (!mbar_wait(bar_sb, ph_sb, abort_flag, 13, &g_cax_status)) { ok = false; break; }
       ph_sb ^= 1u;
       tcgen05_fence_after();
       const float mb = cx_row_max<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, bias);
+      if (!mbar_wait(bar_m, ph_m, abort_flag, 18, &g_cax_status)) { ok = false; break; }
+      ph_m ^= 1u;
+      float m = lbuf[(4 + (it & 1)) * 128 + row];
+      float alpha = 1.0f;
       if (__any_sync(0xffffffffu, mb > m + 8.0f)) {
         // rare: rescale what chunk A has accumulated.  P_A V_A of this tile must have finished.
         if (!mbar_wait(bar_pva, (uint32_t)(it & 1), abort_flag, 14, &g_cax_status)) { ok = false; break; }
         tcgen05_fence_after();
         const float m_new = fmaxf(m, mb);
-        const float alpha = cx_exp2(m - m_new);
+        alpha = cx_exp2(m - m_new);
         for (int g = 0; g < (a.HDN >> 4); ++g) {
           uint32_t o[16];
           tmem_ld_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
@@ -307,11 +337,11 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
           tmem_st_32x16(lane_addr + CX_COL_O + 16u * (uint32_t)g, o);
         }
-        l *= alpha;
         m = m_new;
       }
-      l += cx_row_exp<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, m, bias);
-      lbuf[(it & 1) * 128 + row] = l;
+      const float lb = cx_row_exp<MASK>(lane_addr + CX_COL_SB, a.NB, a.NA, a.L, c, m, bias);
+      lbuf[(2 + (it & 1)) * 128 + row] = lb;
+      lbuf[(6 + (it & 1)) * 128 + row] = alpha;
       tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
@@ -334,7 +364,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (!mbar_wait(bar_o_full, ph_o, abort_flag, 15, &g_cax_status)) { ok = false; break; }
       ph_o ^= 1u;
       tcgen05_fence_after();
-      const float inv = 1.0f / lbuf[(it & 1) * 128 + row];
+      const float inv = 1.0f / fmaf(lbuf[(it & 1) * 128 + row], lbuf[(6 + (it & 1)) * 128 + row], lbuf[(2 + (it & 1)) * 128 + row]);
       if (lane == 0) bulk_wait_read_all();  // the previous tile's stores have read the staging rows
       __syncwarp();
       for (int g = 0; g < (a.HDN >> 4); ++g) {
@@ -405,7 +435,7 @@ cross_attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         prev_bh = bh;
       }
     }
-  } else if (lane == 0) {
+  } else if (warp == 9 && lane == 0) {
     // ------------------------------------------------------------------ tensor-core issue (warp 9, one thread)
     // D = f32 (bit 4), A = B = bf16 (bits 7, 10), N >> 3 at 17, M = 128 (>> 4) at 24; bit 16: B is MN-major
     const uint32_t idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 4) << 24);
