@@ -31,7 +31,8 @@
 // held in registers to read tensor memory once instead of twice, 232 registers per softmax thread through
 // setmaxnreg (104 us: ten back-to-back loads cost what ten loads hidden under the exponentials of the
 // previous group cost); two query tiles in flight with 128-key chunks and direct stores (108 us: with one S
-// buffer per tile a tile's softmax and its own products cannot overlap).  The CTAs of one launch differ by up
+// buffer per tile a tile's softmax and its own products cannot overlap); three key chunks with three softmax
+// warpgroups (94 us: seven more instructions on the tensor core per tile and three warps per scheduler).  The CTAs of one launch differ by up
 // to 30 % in run time with the SM they sit on, 18 % of the slowest one's time being the single-buffered Q load
 // and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
