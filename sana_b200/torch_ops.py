@@ -33,6 +33,10 @@ import torch
 from . import ops
 
 _lib_ns = "sana_b200"
+# the ctypes-level functions, captured before any routing replaces the names in `ops`
+_D = {n: getattr(ops, n) for n in ("gemm", "ln_modulate", "ln_modulate_rows", "la_state", "la_apply", "dwconv_glu", "rmsnorm_",
+                                   "rope_", "cross_attention", "la_rope_state", "la_rope_apply", "add_f32", "patchify",
+                                   "unpatchify", "timestep_embedding", "silu", "nvfp4_quantize", "gemm_nvfp4")}
 
 
 @torch.library.custom_op(f"{_lib_ns}::gemm", mutates_args=())
@@ -40,7 +44,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act: in
          gate_table: Optional[torch.Tensor], gate_t: Optional[torch.Tensor], gate_row: int, rows_per_batch: int,
          residual: Optional[torch.Tensor]) -> torch.Tensor:
     gate = (gate_table, gate_t, gate_row, rows_per_batch) if gate_table is not None else None
-    return ops.gemm(a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual)
+    return _D["gemm"](a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual)
 
 
 @gemm.register_fake
@@ -51,7 +55,7 @@ def _(a, w, bias, act, relu_cols, gate_table, gate_t, gate_row, rows_per_batch, 
 @torch.library.custom_op(f"{_lib_ns}::ln_modulate", mutates_args=())
 def ln_modulate(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, shift_row: int, scale_row: int,
                 eps: float) -> torch.Tensor:
-    return ops.ln_modulate(x, table, t, shift_row, scale_row, eps)
+    return _D["ln_modulate"](x, table, t, shift_row, scale_row, eps)
 
 
 @ln_modulate.register_fake
@@ -61,7 +65,7 @@ def _(x, table, t, shift_row, scale_row, eps):
 
 @torch.library.custom_op(f"{_lib_ns}::la_state", mutates_args=())
 def la_state(k: torch.Tensor, v: torch.Tensor, B: int, N: int, H: int) -> torch.Tensor:
-    return ops.la_state(k, v, B, N, H)
+    return _D["la_state"](k, v, B, N, H)
 
 
 @la_state.register_fake
@@ -71,7 +75,7 @@ def _(k, v, B, N, H):
 
 @torch.library.custom_op(f"{_lib_ns}::la_apply", mutates_args=())
 def la_apply(q: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int, eps: float) -> torch.Tensor:
-    return ops.la_apply(q, state, B, N, H, eps)
+    return _D["la_apply"](q, state, B, N, H, eps)
 
 
 @la_apply.register_fake
@@ -82,7 +86,7 @@ def _(q, state, B, N, H, eps):
 @torch.library.custom_op(f"{_lib_ns}::dwconv_glu", mutates_args=())
 def dwconv_glu(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], W: int, H: int, row0: int,
                halo_top: Optional[torch.Tensor], halo_bot: Optional[torch.Tensor]) -> torch.Tensor:
-    return ops.dwconv_glu(u, weight, bias, W, H, row0=row0, halo_top=halo_top, halo_bot=halo_bot)
+    return _D["dwconv_glu"](u, weight, bias, W, H, row0=row0, halo_top=halo_top, halo_bot=halo_bot)
 
 
 @dwconv_glu.register_fake
@@ -92,7 +96,7 @@ def _(u, weight, bias, W, H, row0, halo_top, halo_bot):
 
 @torch.library.custom_op(f"{_lib_ns}::rmsnorm_", mutates_args=("x",))
 def rmsnorm_(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-    ops.rmsnorm_(x, weight, eps)
+    _D["rmsnorm_"](x, weight, eps)
 
 
 @rmsnorm_.register_fake
@@ -102,7 +106,7 @@ def _(x, weight, eps):
 
 @torch.library.custom_op(f"{_lib_ns}::rope_", mutates_args=("x",))
 def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, head_dim: int) -> None:
-    ops.rope_(x, cos, sin, B, N, head_dim)
+    _D["rope_"](x, cos, sin, B, N, head_dim)
 
 
 @rope_.register_fake
@@ -113,7 +117,7 @@ def _(x, cos, sin, B, N, head_dim):
 @torch.library.custom_op(f"{_lib_ns}::cross_attention", mutates_args=())
 def cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Optional[torch.Tensor], B: int, N: int,
                     L: int, heads: int, head_dim: int) -> torch.Tensor:
-    return ops.cross_attention(q, k, v, mask, B, N, L, heads, head_dim)
+    return _D["cross_attention"](q, k, v, mask, B, N, L, heads, head_dim)
 
 
 @cross_attention.register_fake
@@ -124,7 +128,7 @@ def _(q, k, v, mask, B, N, L, heads, head_dim):
 @torch.library.custom_op(f"{_lib_ns}::la_rope_state", mutates_args=())
 def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, H: int,
                   D: int, prior: Optional[torch.Tensor]) -> torch.Tensor:
-    return ops.la_rope_state(k, v, cos, sin, B, N, H, D, prior=prior)
+    return _D["la_rope_state"](k, v, cos, sin, B, N, H, D, prior=prior)
 
 
 @la_rope_state.register_fake
@@ -135,7 +139,7 @@ def _(k, v, cos, sin, B, N, H, D, prior):
 @torch.library.custom_op(f"{_lib_ns}::la_rope_apply", mutates_args=())
 def la_rope_apply(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int,
                   D: int, eps: float) -> torch.Tensor:
-    return ops.la_rope_apply(q, cos, sin, state, B, N, H, D, eps)
+    return _D["la_rope_apply"](q, cos, sin, state, B, N, H, D, eps)
 
 
 @la_rope_apply.register_fake
@@ -145,7 +149,7 @@ def _(q, cos, sin, state, B, N, H, D, eps):
 
 @torch.library.custom_op(f"{_lib_ns}::add_f32", mutates_args=())
 def add_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return ops.add_f32(a, b)
+    return _D["add_f32"](a, b)
 
 
 @add_f32.register_fake
@@ -156,7 +160,7 @@ def _(a, b):
 @torch.library.custom_op(f"{_lib_ns}::ln_modulate_rows", mutates_args=())
 def ln_modulate_rows(x: torch.Tensor, table: torch.Tensor, t: torch.Tensor, table_shift_row: int, table_scale_row: int,
                      t_shift_row: int, t_scale_row: int, eps: float) -> torch.Tensor:
-    return ops.ln_modulate_rows(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps)
+    return _D["ln_modulate_rows"](x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps)
 
 
 @ln_modulate_rows.register_fake
@@ -166,7 +170,7 @@ def _(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, e
 
 @torch.library.custom_op(f"{_lib_ns}::patchify", mutates_args=())
 def patchify(x: torch.Tensor, p: int) -> torch.Tensor:
-    return ops.patchify(x, p)
+    return _D["patchify"](x, p)
 
 
 @patchify.register_fake
@@ -177,7 +181,7 @@ def _(x, p):
 
 @torch.library.custom_op(f"{_lib_ns}::unpatchify", mutates_args=())
 def unpatchify(tok: torch.Tensor, B: int, Cout: int, Hp: int, Wp: int, p: int) -> torch.Tensor:
-    return ops.unpatchify(tok, B, Cout, Hp, Wp, p)
+    return _D["unpatchify"](tok, B, Cout, Hp, Wp, p)
 
 
 @unpatchify.register_fake
@@ -187,7 +191,7 @@ def _(tok, B, Cout, Hp, Wp, p):
 
 @torch.library.custom_op(f"{_lib_ns}::timestep_embedding", mutates_args=())
 def timestep_embedding(t: torch.Tensor, dim: int, dtype: torch.dtype, max_period: float) -> torch.Tensor:
-    return ops.timestep_embedding(t, dim, dtype, max_period)
+    return _D["timestep_embedding"](t, dim, dtype, max_period)
 
 
 @timestep_embedding.register_fake
@@ -197,7 +201,7 @@ def _(t, dim, dtype, max_period):
 
 @torch.library.custom_op(f"{_lib_ns}::silu", mutates_args=())
 def silu(x: torch.Tensor) -> torch.Tensor:
-    return ops.silu(x)
+    return _D["silu"](x)
 
 
 @silu.register_fake
@@ -212,7 +216,7 @@ def _sf_bytes(rows: int, K: int) -> int:
 
 @torch.library.custom_op(f"{_lib_ns}::nvfp4_quantize", mutates_args=())
 def nvfp4_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    t = ops.nvfp4_quantize(x)
+    t = _D["nvfp4_quantize"](x)
     return t.q, t.sf, t.scales
 
 
@@ -231,10 +235,81 @@ def gemm_nvfp4(a_codes: torch.Tensor, a_sf: torch.Tensor, a_scales: torch.Tensor
     a = ops.NvFp4Tensor(a_codes, a_sf, a_scales, a_codes.shape[0], 2 * a_codes.shape[1])
     w = ops.NvFp4Tensor(w_codes, w_sf, w_scales, w_codes.shape[0], 2 * w_codes.shape[1])
     gate = (gate_table, gate_t, gate_row, rows_per_batch) if gate_table is not None else None
-    return ops.gemm_nvfp4(a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual)
+    return _D["gemm_nvfp4"](a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual)
 
 
 @gemm_nvfp4.register_fake
 def _(a_codes, a_sf, a_scales, w_codes, w_sf, w_scales, bias, act, relu_cols, gate_table, gate_t, gate_row,
       rows_per_batch, residual):
     return a_codes.new_empty(a_codes.shape[0], w_codes.shape[0], dtype=torch.bfloat16)
+
+
+# ---- optional: the modules through the dispatcher ---------------------------------------------------------
+# The modules call `sana_b200.ops` directly (no dispatcher overhead per launch).  For tracing, export or fake-tensor
+# shape propagation of a whole module, route_modules(True) replaces those names in `ops` by wrappers that go
+# through torch.ops.sana_b200 whenever the call uses only what the operator schemas carry (no preallocated output,
+# no NVFP4 side outputs); anything else keeps the direct path.
+
+def _r_gemm(a, w, bias=None, act=ops.ACT_NONE, relu_cols=0, gate=None, residual=None, out=None):
+    if out is not None:
+        return _D["gemm"](a, w, bias=bias, act=act, relu_cols=relu_cols, gate=gate, residual=residual, out=out)
+    gt, tt, gr, rpb = gate if gate is not None else (None, None, 0, 1)
+    return torch.ops.sana_b200.gemm(a, w, bias, act, relu_cols, gt, tt, gr, rpb, residual)
+
+
+def _r_ln_modulate(x, table, t, shift_row, scale_row, eps=1e-6):
+    return torch.ops.sana_b200.ln_modulate(x, table, t, shift_row, scale_row, eps)
+
+
+def _r_la_apply(q, state, B, N, H, eps, out=None):
+    if out is not None:
+        return _D["la_apply"](q, state, B, N, H, eps, out=out)
+    return torch.ops.sana_b200.la_apply(q, state, B, N, H, eps)
+
+
+def _r_dwconv_glu(u, weight, bias, W, H, row0=0, halo_top=None, halo_bot=None, amax_out=None):
+    if amax_out is not None:
+        return _D["dwconv_glu"](u, weight, bias, W, H, row0=row0, halo_top=halo_top, halo_bot=halo_bot, amax_out=amax_out)
+    return torch.ops.sana_b200.dwconv_glu(u, weight, bias, W, H, row0, halo_top, halo_bot)
+
+
+def _r_rmsnorm_(x, weight, eps):
+    torch.ops.sana_b200.rmsnorm_(x, weight, eps)
+    return x
+
+
+def _r_rope_(x, cos, sin, B, N, head_dim=ops.HEAD_DIM):
+    torch.ops.sana_b200.rope_(x, cos, sin, B, N, head_dim)
+    return x
+
+
+def _r_la_rope_state(k, v, cos, sin, B, N, H, D, prior=None):
+    return torch.ops.sana_b200.la_rope_state(k, v, cos, sin, B, N, H, D, prior)
+
+
+def _r_la_rope_apply(q, cos, sin, state, B, N, H, D, eps, out=None):
+    if out is not None:
+        return _D["la_rope_apply"](q, cos, sin, state, B, N, H, D, eps, out=out)
+    return torch.ops.sana_b200.la_rope_apply(q, cos, sin, state, B, N, H, D, eps)
+
+
+def _r_ln_modulate_rows(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps=1e-6):
+    return torch.ops.sana_b200.ln_modulate_rows(x, table, t, table_shift_row, table_scale_row, t_shift_row, t_scale_row, eps)
+
+
+def _r_timestep_embedding(t, dim, dtype, max_period=10000.0):
+    return torch.ops.sana_b200.timestep_embedding(t, dim, dtype, float(max_period))
+
+
+_ROUTED = {"gemm": _r_gemm, "ln_modulate": _r_ln_modulate, "la_state": torch.ops.sana_b200.la_state, "la_apply": _r_la_apply,
+           "dwconv_glu": _r_dwconv_glu, "rmsnorm_": _r_rmsnorm_, "rope_": _r_rope_,
+           "cross_attention": torch.ops.sana_b200.cross_attention, "la_rope_state": _r_la_rope_state,
+           "la_rope_apply": _r_la_rope_apply, "add_f32": torch.ops.sana_b200.add_f32, "ln_modulate_rows": _r_ln_modulate_rows,
+           "patchify": torch.ops.sana_b200.patchify, "unpatchify": torch.ops.sana_b200.unpatchify,
+           "timestep_embedding": _r_timestep_embedding, "silu": torch.ops.sana_b200.silu}
+
+
+def route_modules(enabled: bool = True) -> None:
+    """Send the modules' kernel calls through torch.ops.sana_b200 (True) or straight to the C ABI (False, the default)."""
+    for name, fn in _ROUTED.items():
+        setattr(ops, name, fn if enabled else _D[name])

@@ -112,3 +112,79 @@ def test_remaining_custom_ops_match_the_direct_path():
     da, dw = ops.nvfp4_quantize(a), ops.nvfp4_quantize(w)
     assert torch.equal(qa[0], da.q) and torch.equal(qa[1], da.sf) and torch.equal(qa[2][:2], da.scales[:2])
     assert torch.equal(torch.ops.sana_b200.gemm_nvfp4(*qa, *qw, None, 0, 0, None, None, 0, 1, None), ops.gemm_nvfp4(da, dw))
+
+
+def test_a_whole_block_propagates_shapes_through_the_dispatcher_without_a_gpu():
+    """route_modules(True): the modules' kernel calls go through torch.ops.sana_b200, so fake tensors on a CUDA device
+    that does not exist flow through SanaMSBlock.forward - what tracing and export need."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import sana_b200
+    import sana_b200.torch_ops as T
+
+    old = torch.get_default_dtype()
+    T.route_modules(True)
+    try:
+        torch.set_default_dtype(torch.bfloat16)
+        with FakeTensorMode(), torch.device("cuda"):
+            blk = sana_b200.SanaMSBlock(64, 2, mlp_ratio=2.5, attn_type="linear", ffn_type="glumbconv", qk_norm=True)
+            out = blk(torch.empty(2, 24, 64), torch.empty(2, 5, 64), torch.empty(2, 384), torch.empty(2, 5), (4, 6))
+            assert out.shape == (2, 24, 64) and out.dtype == torch.bfloat16 and out.device.type == "cuda"
+            stack = sana_b200.BlockStack(64, 2, depth=2)
+            assert stack(torch.empty(1, 24, 64), torch.empty(1, 5, 64), torch.empty(1, 384), None, (4, 6)).shape == (1, 24, 64)
+    finally:
+        torch.set_default_dtype(old)
+        T.route_modules(False)
+    assert ops.gemm is T._D["gemm"]  # the direct path is back
+
+
+@pytest.mark.gpu
+def test_routed_block_equals_the_direct_block():
+    import sana_b200
+    import sana_b200.torch_ops as T
+    from sana_b200 import synthetic
+
+    C, heads, hid, HW = 64, 2, 160, (4, 6)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=hid / C, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(synthetic.make_block_params(C, hid, 3, std=0.06), strict=True)
+    blk = blk.cuda().bfloat16()
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 24, C, generator=g).bfloat16().cuda()
+    y = torch.randn(2, 5, C, generator=g).bfloat16().cuda()
+    t = (torch.randn(2, 6 * C, generator=g) * 0.3).bfloat16().cuda()
+    direct = blk(x, y, t, None, HW)
+    T.route_modules(True)
+    try:
+        routed = blk(x, y, t, None, HW)
+    finally:
+        T.route_modules(False)
+    assert torch.equal(routed, direct)
+
+
+@pytest.mark.gpu
+def test_routed_block_traces_as_one_graph():
+    """With the kernel calls routed through the operators, torch.compile captures SanaMSBlock.forward as ONE graph
+    (fullgraph=True would raise on a graph break) and the result equals the direct path bit for bit.  The backend
+    is "eager": what is checked is the tracing, not code generation - the operators are opaque to the compiler."""
+    import sana_b200
+    import sana_b200.torch_ops as T
+    import torch._dynamo as dynamo
+    from sana_b200 import synthetic
+
+    C, heads, hid, HW = 64, 2, 160, (4, 6)
+    blk = sana_b200.SanaMSBlock(C, heads, mlp_ratio=hid / C, attn_type="linear", ffn_type="glumbconv").eval()
+    blk.load_state_dict(synthetic.make_block_params(C, hid, 3, std=0.06), strict=True)
+    blk = blk.cuda().bfloat16()
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 24, C, generator=g).bfloat16().cuda()
+    y = torch.randn(2, 5, C, generator=g).bfloat16().cuda()
+    t = (torch.randn(2, 6 * C, generator=g) * 0.3).bfloat16().cuda()
+    direct = blk(x, y, t, None, HW)
+    T.route_modules(True)
+    try:
+        dynamo.reset()
+        traced = torch.compile(blk, backend="eager", fullgraph=True)
+        assert torch.equal(traced(x, y, t, None, HW), direct)
+    finally:
+        T.route_modules(False)
+        dynamo.reset()
