@@ -32,7 +32,9 @@
 // setmaxnreg (104 us: ten back-to-back loads cost what ten loads hidden under the exponentials of the
 // previous group cost); two query tiles in flight with 128-key chunks and direct stores (108 us: with one S
 // buffer per tile a tile's softmax and its own products cannot overlap); three key chunks with three softmax
-// warpgroups (94 us: seven more instructions on the tensor core per tile and three warps per scheduler).  The CTAs of one launch differ by up
+// warpgroups, or with two warpgroups taking the three chunks in turn so that a chunk's scores are requested two
+// chunks ahead (94 - 95 us either way: seven more instructions on the tensor core and a third round of barriers,
+// first loads and exchanges per tile).  The CTAs of one launch differ by up
 // to 30 % in run time with the SM they sit on, 18 % of the slowest one's time being the single-buffered Q load
 // and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
