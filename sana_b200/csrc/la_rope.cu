@@ -6,8 +6,8 @@
 //   out[n][i]   = (sum_j state[i][j] * rot(relu(q[n]))[j]) / (sum_j state[D][j] * relu(q[n][j]) + eps)
 //   rot(x)[2p] = x[2p] cos[n][p] - x[2p+1] sin[n][p],  rot(x)[2p+1] = x[2p] sin[n][p] + x[2p+1] cos[n][p]
 //
-// bf16: one CTA per (head, token chunk, sample), 3-4 CTAs per SM.  The raw rows of the next 32
-// tokens and their cos / sin rows wait in registers while the current ones are processed; a
+// bf16: one CTA per (head, token chunk, sample), 3 CTAs per SM.  The raw rows of the next 64 (state) or 32
+// (apply) tokens and their cos / sin rows wait in registers while the current ones are processed; a
 // staging pass applies ReLU and the rotation once per element and writes the bf16 operand tiles
 // in the 128-byte-swizzled layouts the 5th-generation tensor cores read; the products are
 // tcgen05.mma instructions that accumulate in tensor memory.  The key sum and the normaliser stay
@@ -18,7 +18,8 @@
 namespace sana {
 
 constexpr int LR_THREADS = 256;
-constexpr int LR_TOK = 32;   // tokens per tile, bf16 kernels
+constexpr int LR_TOK = 64;   // tokens per tile of the bf16 state kernel
+constexpr int LR_TOKA = 32;  // tokens per staging sub-tile of the bf16 apply kernel
 constexpr int LR_TOKF = 16;  // tokens per tile, fp32 kernels
 
 // 16 bytes global -> shared; `valid` false writes zeros and reads nothing
@@ -53,12 +54,12 @@ __device__ __forceinline__ void lr_relu_rotate8(const uint4 raw, const float4 c,
 // state, bf16, on the 5th-generation tensor cores.  grid (H, chunks, B) - heads fastest, so that
 // CTAs running at the same time read whole token rows between them.  Staging: 16 lanes per token
 // (lane group `grp` owns channels 8 grp .. 8 grp + 7 and keeps their key sum in registers),
-// 16 tokens per pass, 2 passes per tile.  The product sum_n v[n][i] krot[n][j] of a 32-token tile
-// is two tcgen05.mma instructions (M = 128 value channels of which D are used, N = D key
+// 16 tokens per pass, 4 passes per tile.  The product sum_n v[n][i] krot[n][j] of a 64-token tile
+// is four tcgen05.mma instructions (M = 128 value channels of which D are used, N = D key
 // channels, K = 16 tokens each) that accumulate in tensor memory over the whole chunk.  Tokens are
 // the contraction index and the tiles are token-major, i.e. both operands are "MN-major": a tile is [64-channel block][token]
 // [128 bytes], 128-byte swizzled (16-byte chunk index XOR token & 7), 8-token groups 1024 bytes
-// apart, channel blocks 4096 bytes apart.  v goes from global memory straight into its operand
+// apart, channel blocks 8192 bytes apart.  v goes from global memory straight into its operand
 // tile with cp.async; the conversion pass writes the rotated k into the other.
 // One thread issues the products; every thread waits (bounded) for the previous tile's products
 // before the tiles are overwritten.  A time-out records a code in g_lr_status, and the CTA leaves
@@ -90,7 +91,7 @@ __device__ __forceinline__ uint64_t lr_desc_mn(uint32_t saddr, uint32_t block_st
 }
 
 template <int D>
-__global__ void __launch_bounds__(LR_THREADS, 4)
+__global__ void __launch_bounds__(LR_THREADS, 3)
 la_rope_state_tc_kernel(const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp, int ld,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                         float* __restrict__ partial, int N, int H, int Lc, int nchunks) {
@@ -309,7 +310,7 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
                         __nv_bfloat16* __restrict__ op, int ldo, int N, int H, int Lc, float eps) {
   using T = LrTcApply<D>;
   constexpr int G = D / 8;
-  constexpr int SUBS = LR_MTOK / LR_TOK;  // staging sub-tiles per product tile
+  constexpr int SUBS = LR_MTOK / LR_TOKA;  // staging sub-tiles per product tile
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sm_u = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -328,7 +329,13 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
   const int h = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
   const int n_begin = chunk * Lc, n_end = min(N, n_begin + Lc);
   const bool loader = grp < G;
-  const int64_t col = (int64_t)h * D + 8 * grp;
+  // With two 64-channel blocks each of the 16 lane groups has a place in the token tile (the groups past the
+  // head's channels fall into the tail of the rows, which the products do not read), so the lanes without
+  // channels run the same loads and stores as the others on the last group's addresses and the staging pass
+  // has no branches; their terms of the normaliser are multiplied by zero.
+  constexpr bool ALL_LANES = T::KB == 2;
+  const int lgrp = ALL_LANES ? min(grp, G - 1) : grp;
+  const int64_t col = (int64_t)h * D + 8 * lgrp;
   const __nv_bfloat16* qbase = qp + (int64_t)b * N * (int64_t)ldq + col;
   __nv_bfloat16* obase = op + (int64_t)b * N * (int64_t)ldo + col;
 
@@ -344,39 +351,28 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
   }
 
   // raw q rows and their cos / sin rows of the NEXT 32 tokens wait in registers
-  uint4 qr[LR_TOK / 16];
-  float4 cr[LR_TOK / 16], sr[LR_TOK / 16];
+  constexpr int RW = LR_TOKA / 16;
+  uint4 qr[RW];
+  float4 cr[RW], sr[RW];
 #pragma unroll
-  for (int r = 0; r < LR_TOK / 16; ++r) {  // lanes without a channel group keep zeros: they join the shuffles
+  for (int r = 0; r < RW; ++r) {  // lanes without a channel group keep zeros: they join the shuffles
     qr[r] = make_uint4(0u, 0u, 0u, 0u);
     cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  auto fetch_whole = [&](int n0) {  // all 32 tokens lie inside the chunk: no per-row tests, nothing to clear
-    if (loader) {
-#pragma unroll
-      for (int r = 0; r < LR_TOK / 16; ++r) {
-        const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
-        qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
-        cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
-        sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
-      }
+  // row r of the 32 tokens from n0; `whole`: all of them lie inside the chunk (no per-row test, nothing to clear)
+  auto fetch_row = [&](int r, int n0, bool whole) {
+    const int tok = n0 + 16 * r + slot;  // 32 x 32 -> 64-bit products
+    if (whole ? (loader || ALL_LANES) : (loader && tok < n_end)) {
+      qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
+      cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * lgrp));
+      sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * lgrp));
+    } else if (!whole) {
+      qr[r] = make_uint4(0u, 0u, 0u, 0u);
+      cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   };
-  auto fetch = [&](int n0) {  // zeros past the end of the chunk
 #pragma unroll
-    for (int r = 0; r < LR_TOK / 16; ++r) {
-      const int tok = n0 + 16 * r + slot;
-      if (loader && tok < n_end) {
-        qr[r] = ldg_nc_u4(qbase + (int64_t)tok * ldq);
-        cr[r] = __ldg(reinterpret_cast<const float4*>(cos_t + (int64_t)tok * (D / 2) + 4 * grp));
-        sr[r] = __ldg(reinterpret_cast<const float4*>(sin_t + (int64_t)tok * (D / 2) + 4 * grp));
-      } else {
-        qr[r] = make_uint4(0u, 0u, 0u, 0u);
-        cr[r] = sr[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    }
-  };
-  fetch(n_begin);
+  for (int r = 0; r < RW; ++r) fetch_row(r, n_begin, false);
 
   // the head's state as the B operand: row i (value channel), 16-byte chunks of 8 key channels
   const float* sg = state + ((int64_t)b * H + h) * (int64_t)((D + 1) * D);
@@ -402,13 +398,16 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
   int tile = 0;
   for (int m0 = n_begin; m0 < n_end; m0 += LR_MTOK, ++tile) {
     if (tile > 0) __syncthreads();  // everybody has stored the previous tile's results out of the token tile
-    auto convert = [&](int ss) {  // the 32 tokens waiting in registers -> rows 32 ss .. of the token tile
+    // the 32 tokens waiting in registers -> rows 32 ss .. of the token tile; each row's registers are asked for
+    // the same row of the next 32 tokens as soon as its values have been taken out
+    auto convert = [&](int ss, bool whole) {
 #pragma unroll
-      for (int r = 0; r < LR_TOK / 16; ++r) {
-        const int trow = ss * LR_TOK + 16 * r + slot;
+      for (int r = 0; r < RW; ++r) {
+        const int trow = ss * LR_TOKA + 16 * r + slot;
         float2 x[4];
         uint4 rot;
         lr_relu_rotate8(qr[r], cr[r], sr[r], x, &rot);
+        fetch_row(r, m0 + (ss + 1) * LR_TOKA, whole);
         float2 den2 = __fmul2_rn(x[0], kreg[0]);
 #pragma unroll
         for (int e = 1; e < 4; ++e) den2 = __ffma2_rn(x[e], kreg[e], den2);
@@ -418,23 +417,17 @@ la_rope_apply_tc_kernel(const __nv_bfloat16* __restrict__ qp, int ldq, const flo
         den += __shfl_xor_sync(0xffffffffu, den, 2);
         den += __shfl_xor_sync(0xffffffffu, den, 4);
         den += __shfl_xor_sync(0xffffffffu, den, 8);
-        if (grp == 0) rden_s[trow] = __fdividef(1.0f, den + eps);  // MUFU reciprocal, 2 ulp
-        if (loader)
+        if (grp == 0 || ALL_LANES) rden_s[trow] = __fdividef(1.0f, den + eps);  // MUFU reciprocal, 2 ulp
+        if (loader || ALL_LANES)
           *reinterpret_cast<uint4*>(Qs + (grp >> 3) * T::Q_BLK + trow * 128 + (((grp & 7) ^ (trow & 7)) << 4)) = rot;
       }
     };
-    if (m0 + LR_MTOK + LR_TOK <= n_end) {  // this tile and the sub-tile after it lie inside the chunk (uniform)
+    if (m0 + LR_MTOK + LR_TOKA <= n_end) {  // this tile and the sub-tile after it lie inside the chunk (uniform)
 #pragma unroll
-      for (int ss = 0; ss < SUBS; ++ss) {
-        convert(ss);
-        fetch_whole(m0 + (ss + 1) * LR_TOK);
-      }
+      for (int ss = 0; ss < SUBS; ++ss) convert(ss, true);
     } else {
 #pragma unroll 1
-      for (int ss = 0; ss < SUBS; ++ss) {
-        convert(ss);
-        fetch(m0 + (ss + 1) * LR_TOK);
-      }
+      for (int ss = 0; ss < SUBS; ++ss) convert(ss, false);
     }
     fence_proxy_async_smem();  // this thread's stores, before the tensor core reads them
     __syncthreads();
