@@ -220,6 +220,18 @@ int sana_la_rope_state_add(const void* k, const void* v, int64_t ld, const float
                            const float* prior, float* state, void* workspace, int64_t workspace_bytes, int64_t B,
                            int64_t N, int64_t H, int64_t D, int dtype, void* stream);
 int sana_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
+/* sana_la_rope_state for a token range sharded over the GPUs of one node: like sana_la_state_sp, the chunk
+ * reduction does the all-reduce of the ranks' partial states over peer memory (same buffer layout, flags, step
+ * numbering, wait limit and soft-error word at byte 320; exchange buffers of
+ * sana_la_rope_state_sp_buffer_bytes(B, H, D) bytes, zero-filled once).  cos_table / sin_table hold the rows of
+ * THIS rank's tokens.  No counterpart upstream (its sequence-parallel video attention gathers the tokens instead:
+ * diffusion/distributed/context_parallel); the state is a plain sum over tokens, so ranks add.  Launches on
+ * different GPUs only. */
+int64_t sana_la_rope_state_sp_buffer_bytes(int64_t B, int64_t H, int64_t D);
+int sana_la_rope_state_sp(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
+                          float* state, void* workspace, int64_t workspace_bytes, int64_t B, int64_t N, int64_t H,
+                          int64_t D, int dtype, void* const* peer_buffers, int rank, int world, uint32_t step,
+                          void* stream);
 int sana_la_rope_apply(const void* q, int64_t ldq, const float* cos_table, const float* sin_table,
                        const float* state, void* out, int64_t ldo, int64_t B, int64_t N, int64_t H, int64_t D,
                        float eps, int dtype, void* stream);

@@ -60,6 +60,9 @@ SIGNATURES = {
     "sana_la_apply": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "sana_la_rope_state_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "sana_la_rope_state": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "sana_la_rope_state_sp_buffer_bytes": (_i64, [_i64, _i64, _i64]),
+    "sana_la_rope_state_sp": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
+                                     C.POINTER(C.c_void_p), _i32, _i32, C.c_uint32, _vp]),
     "sana_la_rope_state_add": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "sana_add_f32": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "sana_la_rope_apply": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),

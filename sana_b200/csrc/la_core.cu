@@ -582,9 +582,6 @@ extern "C" int sana_la_state_noalloc(const void* k, const void* v, int64_t ld, f
 // ------------------------------------------------------------------------------------------
 namespace sana {
 
-constexpr int SP_MAX_WORLD = 16;
-constexpr int64_t SP_HEADER_BYTES = 1024;
-
 struct SpPeers {
   unsigned char* base[SP_MAX_WORLD];
   int rank, world;
@@ -616,7 +613,8 @@ __global__ void __launch_bounds__(256)
 la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __restrict__ state, int nchunks,
                                 int64_t per_batch, int64_t total, const SpPeers pg) {
   __shared__ int wait_failed;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;  // >= total for the 32-channel heads: one element per thread
   unsigned char* mine = pg.base[pg.rank];
   // the step word only changes when the last block of a launch exits, so every block of this
   // launch reads the same value
@@ -624,10 +622,10 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
   const int64_t slot_off = SP_HEADER_BYTES + (int64_t)(step & 1u) * pg.slot_elems * (int64_t)sizeof(float);
   float* my_slot = reinterpret_cast<float*>(mine + slot_off);
   // ---- phase A: fixed-order sum of this rank's chunk partials, published in its slot
-  float s = 0.f;
-  if (idx < total) {
+  for (int64_t idx = first; idx < total; idx += stride) {
     const int64_t b = idx / per_batch, r = idx - b * per_batch;
     const float* p = partial + b * nchunks * per_batch + r;
+    float s = 0.f;
     for (int c = 0; c < nchunks; ++c) s += p[(int64_t)c * per_batch];
     my_slot[idx] = s;
   }
@@ -658,7 +656,8 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
     }
   }
   __syncthreads();
-  if (idx < total) {
+  for (int64_t idx = first; idx < total; idx += stride) {
+    const float s = my_slot[idx];  // this thread's own store of phase A
     float acc = 0.f;
     if (!wait_failed) {
       // all remote loads are issued before the first addition (each takes a few microseconds over
@@ -687,6 +686,24 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
   }
 }
 
+// Launches the kernel above on `total` state elements (`per_batch` per sample) whose chunk partials lie in
+// `partial`.  Every block waits inside the kernel for the peers, so all blocks must be resident at once: the
+// grid is capped at six blocks per SM and the threads stride over the elements.
+int launch_state_reduce_exchange(const float* partial, float* state, int nchunks, int64_t per_batch, int64_t total,
+                                 void* const* peer_buffers, int rank, int world, uint32_t step, cudaStream_t st) {
+  SpPeers pg;
+  for (int r = 0; r < world; ++r) pg.base[r] = static_cast<unsigned char*>(peer_buffers[r]);
+  pg.rank = rank, pg.world = world, pg.step = step;
+  pg.slot_elems = total;
+  pg.wait_limit_ns = exchange_wait_limit_ns();
+  int64_t blocks = ceil_div(total, 256);
+  const int64_t resident = (int64_t)sm_count() * 6;
+  if (blocks > resident) blocks = resident;
+  la_state_reduce_exchange_kernel<<<(unsigned)blocks, 256, 0, st>>>(partial, state, nchunks, per_batch, total, pg);
+  SANA_LAUNCH_CHECK("la_state_reduce_exchange kernel");
+  return SANA_OK;
+}
+
 }  // namespace sana
 
 extern "C" int64_t sana_la_state_sp_buffer_bytes(int64_t B, int64_t H) {
@@ -705,14 +722,8 @@ extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float*
   SANA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(state) && aligned16(workspace), "sana_la_state_sp: alignment");
   SANA_REQUIRE(workspace_bytes >= sana_la_state_workspace_bytes(B, N, H), "sana_la_state_sp: workspace too small");
   SANA_REQUIRE(dtype == SANA_BF16 || dtype == SANA_F32, "sana_la_state_sp: unsupported dtype %d", dtype);
-  SpPeers pg;
-  for (int r = 0; r < world; ++r) {
+  for (int r = 0; r < world; ++r)
     SANA_REQUIRE(peer_buffers[r] && aligned16(peer_buffers[r]), "sana_la_state_sp: peer buffer %d missing or misaligned", r);
-    pg.base[r] = static_cast<unsigned char*>(peer_buffers[r]);
-  }
-  pg.rank = rank, pg.world = world, pg.step = step;
-  pg.slot_elems = B * H * SSIZE;
-  pg.wait_limit_ns = exchange_wait_limit_ns();
   int Lc, nchunks;
   la_state_plan(B, N, H, dtype, &Lc, &nchunks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -728,11 +739,5 @@ extern "C" int sana_la_state_sp(const void* k, const void* v, int64_t ld, float*
                                               partial, (int)N, (int)H, Lc, nchunks);
   }
   SANA_LAUNCH_CHECK("la_state kernel (sequence parallel)");
-  const int64_t total = B * H * SSIZE;
-  const int64_t blocks = ceil_div(total, 256);
-  // every block waits inside the kernel for the peers: all blocks must be resident at once
-  SANA_REQUIRE(blocks <= (int64_t)sm_count() * 6, "sana_la_state_sp: B*H too large for a single resident wave");
-  la_state_reduce_exchange_kernel<<<(unsigned)blocks, 256, 0, st>>>(partial, state, nchunks, H * SSIZE, total, pg);
-  SANA_LAUNCH_CHECK("la_state_reduce_exchange kernel");
-  return SANA_OK;
+  return launch_state_reduce_exchange(partial, state, nchunks, H * SSIZE, B * H * SSIZE, peer_buffers, rank, world, step, st);
 }

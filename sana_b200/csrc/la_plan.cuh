@@ -53,4 +53,13 @@ inline int64_t resident_ctas_tmem(Kernel kernel, int threads, size_t dynamic_sme
   return per_sm * sm_count();
 }
 
+// Chunk reduction fused with the all-reduce over peer memory (la_core.cu), shared by the linear-attention state
+// kernels: sums the `nchunks` partial states of this rank in chunk order, publishes the sum in this rank's
+// exchange buffer and adds the peers' sums in rank order.  `peer_buffers[r]` = rank r's exchange buffer
+// (SP_HEADER_BYTES + 2 * total * 4 bytes, zeroed before the first step) as mapped in this process.
+constexpr int SP_MAX_WORLD = 16;
+constexpr int64_t SP_HEADER_BYTES = 1024;
+int launch_state_reduce_exchange(const float* partial, float* state, int nchunks, int64_t per_batch, int64_t total,
+                                 void* const* peer_buffers, int rank, int world, uint32_t step, cudaStream_t st);
+
 }  // namespace sana

@@ -652,7 +652,8 @@ static void lr_state_plan(int64_t B, int64_t N, int64_t H, int* Lc, int* nchunks
 
 template <int D>
 static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t, const float* sin_t, float* state,
-                    float* partial, int64_t B, int64_t N, int64_t H, int dtype, cudaStream_t st, const float* prior) {
+                    float* partial, int64_t B, int64_t N, int64_t H, int dtype, cudaStream_t st, const float* prior,
+                    void* const* peer_buffers = nullptr, int rank = 0, int world = 1, uint32_t step = 0) {
   int rc = lr_prepare<D>();
   if (rc != SANA_OK) return rc;
   int Lc, nchunks;
@@ -669,6 +670,8 @@ static int lr_state(const void* k, const void* v, int64_t ld, const float* cos_t
   }
   SANA_LAUNCH_CHECK("la_rope_state kernel");
   const int64_t per_batch = H * (int64_t)((D + 1) * D), total = B * per_batch;
+  if (peer_buffers)  // the chunk reduction does the all-reduce over the ranks' token shares as well
+    return launch_state_reduce_exchange(partial, state, nchunks, per_batch, total, peer_buffers, rank, world, step, st);
   la_rope_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(partial, state, nchunks, per_batch, total, prior);
   SANA_LAUNCH_CHECK("la_rope_reduce kernel");
   return SANA_OK;
@@ -744,7 +747,8 @@ extern "C" int64_t sana_la_rope_state_workspace_bytes(int64_t B, int64_t N, int6
 
 static int la_rope_state_impl(const void* k, const void* v, int64_t ld, const float* cos_table, const float* sin_table,
                               const float* prior, float* state, void* workspace, int64_t workspace_bytes, int64_t B,
-                              int64_t N, int64_t H, int64_t D, int dtype, void* stream) {
+                              int64_t N, int64_t H, int64_t D, int dtype, void* stream, void* const* peer_buffers = nullptr,
+                              int rank = 0, int world = 1, uint32_t step = 0) {
   SANA_REQUIRE(k && v && cos_table && sin_table && state && workspace, "sana_la_rope_state: null pointer");
   SANA_REQUIRE(B > 0 && N > 0 && H > 0, "sana_la_rope_state: B, N, H must be positive");
   SANA_REQUIRE(lr_head_dim_ok(D), "sana_la_rope_state: head dimension must be a multiple of 16 in [16, 128]");
@@ -758,7 +762,7 @@ static int la_rope_state_impl(const void* k, const void* v, int64_t ld, const fl
   SANA_REQUIRE(!prior || aligned16(prior), "sana_la_rope_state_add: prior must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
-#define LR_STATE(DD) lr_state<DD>(k, v, ld, cos_table, sin_table, state, partial, B, N, H, dtype, st, prior)
+#define LR_STATE(DD) lr_state<DD>(k, v, ld, cos_table, sin_table, state, partial, B, N, H, dtype, st, prior, peer_buffers, rank, world, step)
   LR_DISPATCH(D, LR_STATE)
 #undef LR_STATE
   return fail(SANA_ERR_INVALID, "sana_la_rope_state: head dimension %lld", (long long)D);
@@ -776,6 +780,23 @@ extern "C" int sana_la_rope_state_add(const void* k, const void* v, int64_t ld, 
                                       void* stream) {
   SANA_REQUIRE(prior, "sana_la_rope_state_add: null prior");
   return la_rope_state_impl(k, v, ld, cos_table, sin_table, prior, state, workspace, workspace_bytes, B, N, H, D, dtype, stream);
+}
+
+extern "C" int64_t sana_la_rope_state_sp_buffer_bytes(int64_t B, int64_t H, int64_t D) {
+  if (B <= 0 || H <= 0 || !lr_head_dim_ok(D)) return 0;
+  return SP_HEADER_BYTES + 2 * B * H * (D + 1) * D * (int64_t)sizeof(float);
+}
+
+extern "C" int sana_la_rope_state_sp(const void* k, const void* v, int64_t ld, const float* cos_table,
+                                     const float* sin_table, float* state, void* workspace, int64_t workspace_bytes,
+                                     int64_t B, int64_t N, int64_t H, int64_t D, int dtype, void* const* peer_buffers,
+                                     int rank, int world, uint32_t step, void* stream) {
+  SANA_REQUIRE(peer_buffers, "sana_la_rope_state_sp: null pointer");
+  SANA_REQUIRE(world >= 1 && world <= SP_MAX_WORLD && rank >= 0 && rank < world, "sana_la_rope_state_sp: bad rank / world");
+  for (int r = 0; r < world; ++r)
+    SANA_REQUIRE(peer_buffers[r] && aligned16(peer_buffers[r]), "sana_la_rope_state_sp: peer buffer %d missing or misaligned", r);
+  return la_rope_state_impl(k, v, ld, cos_table, sin_table, nullptr, state, workspace, workspace_bytes, B, N, H, D, dtype,
+                            stream, peer_buffers, rank, world, step);
 }
 
 extern "C" int sana_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream) {

@@ -274,9 +274,12 @@ class LiteLAReLURope(nn.Module):
                 raise ValueError("the token count does not match this rank's share of the grid")
             cos, sin = self.rotary_tables(rotary_emb, sh.frames * sh.H * sh.W, qkv.device)
             cos, sin = cos[a:b].contiguous(), sin[a:b].contiguous()
-        state = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, N, self.heads, self.dim)
-        if sh is not None:
-            sh.allreduce_state(state)
+        if sh is not None and sh.fused_rope_state_exchange:  # all-reduce inside the reduction kernel
+            state = sh.fused_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, self.heads, self.dim)
+        else:
+            state = ops.la_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, N, self.heads, self.dim)
+            if sh is not None:
+                sh.allreduce_state(state)
         return ops.la_rope_apply(qkv[:, :C], cos, sin, state, B, N, self.heads, self.dim, float(self.eps))
 
     def forward(self, x: torch.Tensor, mask=None, HW=None, rotary_emb=None, block_mask=None, **kwargs):

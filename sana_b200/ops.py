@@ -331,6 +331,35 @@ def la_rope_state(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torc
     return state
 
 
+def la_rope_state_sp_buffer_bytes(B: int, H: int, D: int) -> int:
+    return _lib.load().sana_la_rope_state_sp_buffer_bytes(B, H, D)
+
+
+def la_rope_state_sp(k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, N: int, H: int,
+                     D: int, peer_ptrs, rank: int, world: int, step: int) -> torch.Tensor:
+    """Like :func:`la_rope_state` for this rank's tokens (``cos`` / ``sin`` hold their rows), with the all-reduce
+    over the ranks fused into the reduction kernel (peer-memory loads, no NCCL); arguments as in
+    :func:`la_state_sp`."""
+    _need_cuda(k, v, cos, sin)
+    rk, ck, ldk = _rows2d(k, "la_rope_state_sp k")
+    rv, cv, ldv = _rows2d(v, "la_rope_state_sp v")
+    if rk != B * N or rv != B * N or ck != H * D or cv != H * D or ldk != ldv or k.dtype != v.dtype:
+        raise SanaLibraryError("la_rope_state_sp: k and v must be [B*N, H*D] with the same row stride and dtype")
+    _rope_tables(cos, sin, N, D, "la_rope_state_sp")
+    lib = _lib.load()
+    ws_bytes = lib.sana_la_rope_state_workspace_bytes(B, N, H, D)
+    if ws_bytes <= 0:
+        raise SanaLibraryError(f"la_rope_state_sp: head dimension {D} is not a multiple of 16 in [16, 128]")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=k.device)
+    state = torch.empty(B, H, D + 1, D, dtype=torch.float32, device=k.device)
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    _lib.check(lib.sana_la_rope_state_sp(k.data_ptr(), v.data_ptr(), ldk, cos.data_ptr(), sin.data_ptr(), state.data_ptr(),
+                                         ws.data_ptr(), ws.numel(), B, N, H, D, _dtype_code(k.dtype), arr, rank, world, step,
+                                         _stream()), "sana_la_rope_state_sp")
+    counters.launches += 2
+    return state
+
+
 def la_rope_apply(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, state: torch.Tensor, B: int, N: int, H: int,
                   D: int, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """o = state[:D] rot(relu(q)) / (state[D] . relu(q) + eps), token-major; q [B*N, H*D] view."""

@@ -122,11 +122,13 @@ class SequenceShard:
         return self.row1 % self.H != 0
 
     # ---- fused exchange over peer memory ------------------------------------------------
-    def enable_fused_state_exchange(self, B: int, heads: int, device) -> None:
+    def enable_fused_state_exchange(self, B: int, heads: int, device, head_dim: Optional[int] = None) -> None:
         """Allocates this rank's exchange buffer in symmetric (peer-mapped) memory and maps the
         peers' buffers, so that the linear-attention state reduction kernel can do the
         all-reduce itself (`ops.la_state_sp`) instead of calling NCCL.  Collective over the
-        group; call once, on every rank, before the first forward."""
+        group; call once, on every rank, before the first forward.  With ``head_dim`` the buffer is sized for the
+        rotated attention's [head_dim + 1, head_dim] states (`ops.la_rope_state_sp`, `fused_rope_state`); without,
+        for the 32-channel heads of the plain linear attention (`fused_state`)."""
         import os
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
@@ -134,7 +136,10 @@ class SequenceShard:
 
         from . import ops
 
-        nbytes = ops.la_state_sp_buffer_bytes(B, heads)
+        nbytes = (ops.la_state_sp_buffer_bytes(B, heads) if head_dim is None
+                  else ops.la_rope_state_sp_buffer_bytes(B, heads, head_dim))
+        if nbytes <= 0:
+            raise ValueError(f"no fused state exchange for B = {B}, heads = {heads}, head_dim = {head_dim}")
         buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         buf.zero_()
         group = self.group if self.group is not None else dist.group.WORLD
@@ -143,7 +148,7 @@ class SequenceShard:
         dist.barrier(group=group)  # every buffer is zeroed before anybody's first step
         self._sp_buf, self._sp_handle = buf, hdl
         self._sp_ptrs = [int(p) for p in hdl.buffer_ptrs]
-        self._sp_shape = (B, heads)
+        self._sp_shape = (B, heads) if head_dim is None else (B, heads, head_dim)
         self._sp_step = 0
 
     @property
@@ -242,6 +247,11 @@ class SequenceShard:
                 who.append(f"rank {self.rank + 1} did not deliver its conv halo row")
             raise PeerLostError(f"rank {self.rank}: " + "; ".join(who) + " within the exchange wait limit")
 
+    @property
+    def fused_rope_state_exchange(self) -> bool:
+        """True when the exchange buffer was sized for the rotated attention's states (``head_dim`` given)."""
+        return self.fused_state_exchange and len(self._sp_shape) == 3
+
     # With `device_steps` the exchange kernels number their steps themselves (a word in the
     # exchange buffer) instead of taking the number as a launch argument: required for CUDA-graph
     # replay, where the host does not run between steps.  Set it on every rank or on none.
@@ -256,6 +266,18 @@ class SequenceShard:
         self._sp_step += 1
         return ops.la_state_sp(k, v, B, self.tokens, heads, self._sp_ptrs, self.rank, self.world,
                                0 if self.device_steps else self._sp_step)
+
+    def fused_rope_state(self, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, heads: int,
+                         head_dim: int) -> torch.Tensor:
+        """The rotated attention's state of the whole sequence from this rank's k, v and table rows."""
+        from . import ops
+
+        if (B, heads, head_dim) != self._sp_shape:
+            raise ValueError(f"fused exchange was sized for (B, heads, head_dim) = {self._sp_shape}, "
+                             f"got {(B, heads, head_dim)}")
+        self._sp_step += 1
+        return ops.la_rope_state_sp(k, v, cos, sin, B, self.tokens, heads, head_dim, self._sp_ptrs, self.rank, self.world,
+                                    0 if self.device_steps else self._sp_step)
 
     def fused_exchange_status(self) -> int:
         """Soft-error word of the exchange kernel (0 = every wait completed).  Synchronises."""

@@ -52,6 +52,26 @@ def test_state_exchange_gives_up_on_a_silent_peer(short_wait):
     assert int(solo[320:324].view(torch.int32).item()) == 0
 
 
+def test_rotated_state_exchange_gives_up_on_a_silent_peer(short_wait):
+    """The same for the rotated attention's wider state (the reduction kernel's threads stride over it)."""
+    B, N, H, D = 1, 520, 20, 112
+    g = torch.Generator(device=DEV).manual_seed(1)
+    kv = torch.randn(N, 2 * H * D, generator=g, device=DEV).bfloat16()
+    k, v = kv[:, :H * D], kv[:, H * D:]
+    ang = torch.randn(N, D // 2, generator=g, device=DEV) * 3.0
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    nbytes = ops.la_rope_state_sp_buffer_bytes(B, H, D)
+    mine, silent0, silent2 = (torch.zeros(nbytes, dtype=torch.uint8, device=DEV) for _ in range(3))
+    ops.la_rope_state_sp(k, v, cos, sin, B, N, H, D, [silent0.data_ptr(), mine.data_ptr(), silent2.data_ptr()], 1, 3, 1)
+    torch.cuda.synchronize()
+    assert int(mine[320:324].view(torch.int32).item()) == 1 + 0  # gave up on rank 0, the first it waits for
+    assert int(silent0[4:8].view(torch.int32).item()) == 1 and int(silent2[4:8].view(torch.int32).item()) == 1
+    solo = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    st = ops.la_rope_state_sp(k, v, cos, sin, B, N, H, D, [solo.data_ptr()], 0, 1, 1)
+    assert torch.equal(st, ops.la_rope_state(k, v, cos, sin, B, N, H, D))
+    assert int(solo[320:324].view(torch.int32).item()) == 0 and ops.take_la_rope_device_status() == 0
+
+
 def test_halo_exchange_gives_up_per_side(short_wait):
     row_bytes = 4096
     nbytes = ops.halo_exchange_buffer_bytes(row_bytes)

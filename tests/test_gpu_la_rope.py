@@ -240,3 +240,20 @@ def test_rotated_attention_on_sequence_shards_emulated_on_one_gpu():
         m.seq_shard = sharding.SequenceShard(frames, H, W, 0, 1)
         got = m(x, rotary_emb=freqs)
     assert torch.equal(ref, got)
+
+
+def test_la_rope_state_sp_with_one_rank_equals_la_rope_state():
+    """The reduction fused with the peer-memory exchange degenerates to the plain reduction for world = 1 (three
+    steps on the same buffer: both slot parities).  20 heads of 112 channels: more state elements than one
+    resident wave of threads, so the kernel's threads stride over them."""
+    B, N, H, D = 2, 700, 20, 112
+    buf = torch.zeros(ops.la_rope_state_sp_buffer_bytes(B, H, D), dtype=torch.uint8, device=DEV)
+    cos, sin = (t.to(DEV) for t in _tables(N, D, seed=4)[1:])
+    for step in (1, 2, 3):
+        g = torch.Generator().manual_seed(step)
+        kv = torch.randn(B * N, 2 * H * D, generator=g).bfloat16().to(DEV)
+        k, v = kv[:, :H * D], kv[:, H * D:]
+        got = ops.la_rope_state_sp(k, v, cos, sin, B, N, H, D, [buf.data_ptr()], 0, 1, step)
+        assert torch.equal(got, ops.la_rope_state(k, v, cos, sin, B, N, H, D))
+    assert buf[320:324].view(torch.int32).item() == 0
+    assert ops.la_rope_state_sp_buffer_bytes(B, H, 40) == 0  # heads of 40 channels: not a multiple of 16

@@ -288,8 +288,12 @@ def _video_block_shards(rank, world):
         worst = err(blk(x[:, a:b].contiguous(), y, tl, THW=THW, rotary_emb=fr))
         sh.enable_fused_frame_exchange(C, dt, dev)
         fused = max(err(blk(x[:, a:b].contiguous(), y, tl, THW=THW, rotary_emb=fr)) for _ in range(3))
+        # ... and the attention state's all-reduce inside its reduction kernel as well
+        sh.enable_fused_state_exchange(1, heads, dev, head_dim=C // heads)
+        assert sh.fused_rope_state_exchange
+        fused = max([fused] + [err(blk(x[:, a:b].contiguous(), y, tl, THW=THW, rotary_emb=fr)) for _ in range(3)])
         torch.cuda.synchronize()
-        out[name] = {"nccl": worst, "fused": fused, "status": sh.fused_frame_status()}
+        out[name] = {"nccl": worst, "fused": fused, "status": sh.fused_frame_status() + sh.fused_exchange_status()}
         sh.check()
         dist.barrier()
     return out
