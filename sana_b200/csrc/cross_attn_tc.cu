@@ -34,7 +34,13 @@
 // buffer per tile a tile's softmax and its own products cannot overlap); three key chunks with three softmax
 // warpgroups, or with two warpgroups taking the three chunks in turn so that a chunk's scores are requested two
 // chunks ahead (94 - 95 us either way: seven more instructions on the tensor core and a third round of barriers,
-// first loads and exchanges per tile).  The CTAs of one launch differ by up
+// first loads and exchanges per tile); chunk A's probabilities in the tensor-memory columns behind O (chunks of 192
+// + 112 keys), so that the next tile's S_A can be issued before P_A V_A, with the next query tile prefetched into
+// L2 (no change: per-role cycle counters show a tile period of 7 900 cycles in which the one issuing thread is
+// busy 5 500 - 33 instructions at about 167 cycles each, whatever their N - and each softmax warpgroup works 4 800
+// and waits 2 800 - 3 000 for its scores, i.e. for the 16 - 17 instructions between its probabilities and its
+// next scores plus whatever the other chunk has queued in front of them; the tensor pipe is the shared resource
+// and it is occupied by instruction count, not by arithmetic).  The CTAs of one launch differ by up
 // to 30 % in run time with the SM they sit on, 18 % of the slowest one's time being the single-buffered Q load
 // and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
