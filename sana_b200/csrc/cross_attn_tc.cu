@@ -19,7 +19,7 @@
 // exceeds it by more than 2^8, in which case its warps wait for P_A V_A and rescale O in tensor memory (exact
 // either way: softmax is invariant to the shift, and p <= 256 is harmless in bf16 and in the fp32 accumulator);
 // the factor they applied goes to the epilogue with the two partial row sums.
-// Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 72 us per sample (the vendor's flash kernel
+// Measured (20 heads x 112, 300 keys, 16 384 queries per sample): 72 - 85 us per sample, box to box (the vendor's flash kernel
 // through torch: 57 - 61).  History: with ONE softmax warpgroup doing chunk A and then chunk B the kernel took 84 us:
 // the 33 tcgen05.mma of a tile take about 4 500 cycles (an instruction with M = 128 costs about 130 cycles
 // whether N is 112 or 256) but the softmax warps about 8 000, because a tcgen05.ld / tcgen05.st blocks the
