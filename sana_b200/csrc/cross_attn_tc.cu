@@ -40,7 +40,9 @@
 // busy 5 500 - 33 instructions at about 167 cycles each, whatever their N - and each softmax warpgroup works 4 800
 // and waits 2 800 - 3 000 for its scores, i.e. for the 16 - 17 instructions between its probabilities and its
 // next scores plus whatever the other chunk has queued in front of them; the tensor pipe is the shared resource
-// and it is occupied by instruction count, not by arithmetic).  The CTAs of one launch differ by up
+// and it is occupied by instruction count, not by arithmetic); the whole kernel on CTA pairs (cta_group::2, M = 256,
+// K and V split between the two CTAs, two Q buffers: 80 - 85 us - every SM still executes all 33 instructions of
+// its own tile, so nothing is saved on the tensor pipe and the two CTAs wait for each other).  The CTAs of one launch differ by up
 // to 30 % in run time with the SM they sit on, 18 % of the slowest one's time being the single-buffered Q load
 // and output store (without them all CTAs run within 7 %).
 // Every wait is bounded; a time-out records a code in g_cax_status and all roles leave through the teardown.
