@@ -687,8 +687,9 @@ la_state_reduce_exchange_kernel(const float* __restrict__ partial, float* __rest
 }
 
 // Launches the kernel above on `total` state elements (`per_batch` per sample) whose chunk partials lie in
-// `partial`.  Every block waits inside the kernel for the peers, so all blocks must be resident at once: the
-// grid is capped at six blocks per SM and the threads stride over the elements.
+// `partial`.  Every block waits inside the kernel for the peers, and the block that finishes phase A last is the
+// one that tells them, so all blocks must be resident at once: the grid is capped at what the occupancy query
+// says fits (registers decide: four blocks per SM) and the threads stride over the elements.
 int launch_state_reduce_exchange(const float* partial, float* state, int nchunks, int64_t per_batch, int64_t total,
                                  void* const* peer_buffers, int rank, int world, uint32_t step, cudaStream_t st) {
   SpPeers pg;
@@ -697,7 +698,7 @@ int launch_state_reduce_exchange(const float* partial, float* state, int nchunks
   pg.slot_elems = total;
   pg.wait_limit_ns = exchange_wait_limit_ns();
   int64_t blocks = ceil_div(total, 256);
-  const int64_t resident = (int64_t)sm_count() * 6;
+  static const int64_t resident = resident_ctas(la_state_reduce_exchange_kernel, 256);
   if (blocks > resident) blocks = resident;
   la_state_reduce_exchange_kernel<<<(unsigned)blocks, 256, 0, st>>>(partial, state, nchunks, per_batch, total, pg);
   SANA_LAUNCH_CHECK("la_state_reduce_exchange kernel");

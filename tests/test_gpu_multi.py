@@ -205,6 +205,37 @@ def _fused_exchange_vs_nccl(rank, world):
     return {"worst": worst, "same": same, "status": sh.fused_exchange_status(), "first": first}
 
 
+def _fused_rope_state_full_width(rank, world):
+    """sana_la_rope_state_sp at the video model's width (20 heads of 112 channels: the reduction kernel's threads
+    stride over the 253 120 state elements) on this rank's half of the tokens, against the NCCL all-reduce of the
+    per-rank states; bit-identical totals on every rank; three steps in a row (both slot parities)."""
+    import sana_b200
+    from sana_b200 import ops, sharding
+
+    dev, dt = torch.device("cuda", rank), torch.bfloat16
+    heads, D, grid = 20, 112, (4, 10, 16)
+    C = heads * D
+    sh = sharding.SequenceShard(*grid, rank, world)
+    a, b = sh.token_range
+    fr = sana_b200.wan_rotary_freqs(D, grid).reshape(grid[0] * grid[1] * grid[2], D // 2)
+    cos, sin = fr.real.float().to(dev)[a:b].contiguous(), fr.imag.float().to(dev)[a:b].contiguous()
+    sh.enable_fused_state_exchange(1, heads, dev, head_dim=D)
+    worst, same = 0.0, True
+    for step in range(3):
+        g = torch.Generator(device=dev).manual_seed(10 * step + rank)
+        kv = torch.randn(sh.tokens, 2 * C, device=dev, generator=g).to(dt)
+        k, v = kv[:, :C], kv[:, C:]
+        st = sh.fused_rope_state(k, v, cos, sin, 1, heads, D)
+        ref = ops.la_rope_state(k, v, cos, sin, 1, sh.tokens, heads, D)
+        dist.all_reduce(ref)
+        worst = max(worst, ((st - ref).abs().max() / ref.abs().max()).item())
+        gathered = [torch.empty_like(st) for _ in range(world)]
+        dist.all_gather(gathered, st)
+        same = same and all(torch.equal(gathered[0], x) for x in gathered)
+    torch.cuda.synchronize()
+    return {"worst": worst, "same": same, "status": sh.fused_exchange_status() + ops.take_la_rope_device_status()}
+
+
 def _fused_halo_and_graph(rank, world):
     """Sharded block with both exchanges over peer memory (state all-reduce fused into the
     reduction kernel, conv halo rows pushed by the halo kernel) against the NCCL paths, then
@@ -307,6 +338,15 @@ def test_video_block_with_temporal_halo_on_two_gpus():
         assert status == "ok", payload
         for name, p in payload.items():
             assert p["status"] == 0 and p["nccl"] < 1e-2 and p["fused"] < 1e-2, (name, p)
+
+
+def test_fused_rotated_state_exchange_at_full_width_on_two_gpus():
+    _need(2)
+    res = _run(2, _fused_rope_state_full_width)
+    assert len(res) == 2, res
+    for r, (status, payload) in res.items():
+        assert status == "ok", payload
+        assert payload["status"] == 0 and payload["same"] and payload["worst"] < 1e-5, payload  # only the summation order differs
 
 
 def test_fused_halo_exchange_and_graph_replay_on_two_gpus():
