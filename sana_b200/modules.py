@@ -273,7 +273,11 @@ class LiteLAReLURope(nn.Module):
             if b - a != N:
                 raise ValueError("the token count does not match this rank's share of the grid")
             cos, sin = self.rotary_tables(rotary_emb, sh.frames * sh.H * sh.W, qkv.device)
-            cos, sin = cos[a:b].contiguous(), sin[a:b].contiguous()
+            # this rank's rows of the tables, kept until the tables or the range change
+            cached = getattr(self, "_shard_tables", None)
+            if cached is None or cached[0] is not cos or cached[1] != (a, b):
+                cached = self._shard_tables = (cos, (a, b), cos[a:b].contiguous(), sin[a:b].contiguous())
+            cos, sin = cached[2], cached[3]
         if sh is not None and sh.fused_rope_state_exchange:  # all-reduce inside the reduction kernel
             state = sh.fused_rope_state(qkv[:, C:2 * C], qkv[:, 2 * C:], cos, sin, B, self.heads, self.dim)
         else:
